@@ -1,0 +1,387 @@
+"""bsir -- host-side mirror of the HFusion / HIVM operator surface on top of the C ABI.
+
+The functions keep the reference's op names and attribute spellings
+(``hfusion.elemwise_binary {fun = ...}``, ``hfusion.cast {round_mode = ..., enable_saturate}``,
+``hfusion.reduce_with_index {tie_break_left}``, ...) and take CUDA tensors; each one is a thin
+call into ``libbsir_b200.so`` (``include/bsir_b200.h``).  There is no fallback: if the library
+has not been built, importing :func:`lib` raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Sequence
+
+import torch
+
+_PKG = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LIB_PATH = os.path.join(_PKG, "libbsir_b200.so")
+
+# ---------------------------------------------------------------------------- enums (bsir_b200.h)
+F32, F16, BF16, I8, I16, I32, I64, U8, U16, U32, U64, BOOL = range(12)
+_TORCH2DT = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16, torch.int8: I8, torch.int16: I16,
+             torch.int32: I32, torch.int64: I64, torch.uint8: U8, torch.bool: BOOL}
+for _n, _c in (("uint16", U16), ("uint32", U32), ("uint64", U64)):
+    if hasattr(torch, _n):
+        _TORCH2DT[getattr(torch, _n)] = _c
+_DT2TORCH = {v: k for k, v in _TORCH2DT.items()}
+DTYPE_NAMES = {"f32": F32, "f16": F16, "bf16": BF16, "i8": I8, "i16": I16, "i32": I32, "i64": I64, "u8": U8,
+               "u16": U16, "u32": U32, "u64": U64, "i1": BOOL, "bool": BOOL}
+
+ROUND_MODE = {"rint": 0, "round": 1, "floor": 2, "ceil": 3, "trunc": 4, "odd": 5, "truncwithoverflow": 6}
+OVERFLOW_MODE = {"wrap": 0, "saturate": 1, "ascend_saturate_trunc_via_f16": 2, "ascend_double_round_via_f16": 3}
+UNARY_FN = {"relu": 0, "sqrt": 1, "rsqrt": 2, "rec": 3, "vnot": 4, "tanh": 5, "sin": 6, "cos": 7, "atan": 8, "tan": 9,
+            "absi": 10, "erf": 11, "log2": 12, "log10": 13, "log1p": 14, "exp2": 15, "expm1": 16, "ilogb": 17,
+            "asin": 18, "acos": 19, "asinh": 20, "acosh": 21, "atanh": 22, "sinh": 23, "lgamma": 24, "cosh": 25,
+            "nearbyint": 26, "exp": 100, "log": 101, "abs": 102, "ceil": 103, "floor": 104, "negf": 105,
+            "reciprocal": 106, "round": 107, "square": 110}
+BINARY_FN = {"vor": 0, "vand": 1, "vxor": 2, "minf": 3, "maxf": 4, "powf": 5, "mod": 6, "modui": 7, "shli": 8,
+             "shrsi": 9, "shrui": 10, "ldexp": 11, "ceildivsi": 12, "ceildivui": 13, "floordivsi": 14, "powi": 15,
+             "minnumf": 16, "maxnumf": 17, "atan2": 18, "divfhp": 19, "copysign": 20, "add": 100, "sub": 101,
+             "mul": 102, "div": 103, "div_unsigned": 104, "max_signed": 105, "min_signed": 106,
+             "max_unsigned": 107, "min_unsigned": 108}
+COMPARE_FN = {"veq": 0, "vne": 1, "vle": 2, "vlt": 3, "vge": 4, "vgt": 5, "vule": 6, "vult": 7, "vuge": 8, "vugt": 9}
+REDUCE_KIND = {"sum": 0, "prod": 1, "max": 2, "min": 3, "any": 4, "all": 5, "xori": 6, "ori": 7, "andi": 8}
+RWI_KIND = {"min": 0, "max": 1}
+KERNEL_KIND = {"elemwise_binary": 0, "elemwise_unary": 1, "cast": 2, "rms_norm": 3, "softmax": 4,
+               "quant_per_token": 5, "reduce_with_index": 6, "reduce": 7, "matmul_w8a8": 8, "matmul_w4a16": 9}
+
+
+class BsirError(RuntimeError):
+    def __init__(self, status: int, text: str):
+        super().__init__(f"bsir status {status}: {text}")
+        self.status = status
+
+
+class Operand(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("strides", C.c_int64 * 3), ("scalar_bits", C.c_uint64)]
+
+
+class KernelDesc(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("fn", C.c_int32), ("dtype", C.c_int32), ("dst_dtype", C.c_int32),
+                ("round_mode", C.c_int32), ("overflow_mode", C.c_int32), ("flags", C.c_int32), ("rank", C.c_int32),
+                ("sizes", C.c_int64 * 4), ("eps", C.c_float)]
+
+
+def memref_type(rank: int):
+    class MemRef(C.Structure):
+        _fields_ = [("allocated", C.c_void_p), ("aligned", C.c_void_p), ("offset", C.c_int64),
+                    ("sizes", C.c_int64 * rank), ("strides", C.c_int64 * rank)]
+    return MemRef
+
+
+_MEMREF = {r: memref_type(r) for r in (1, 2, 3)}
+
+
+def memref(t: torch.Tensor, rank: Optional[int] = None):
+    """MLIR memref descriptor of a tensor (base = aligned + offset, strides in elements)."""
+    rank = t.dim() if rank is None else rank
+    m = _MEMREF[rank]()
+    base = t.untyped_storage().data_ptr() if t.numel() else 0
+    m.allocated = base
+    m.aligned = base
+    m.offset = t.storage_offset()
+    for i in range(rank):
+        m.sizes[i] = t.shape[i]
+        m.strides[i] = t.stride(i)
+    return m
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads the C-ABI library.  Raises if it was not built: there is no other compute path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise BsirError(-100, f"{LIB_PATH} is missing: build it with `python ascendnpu-ir_b200/build.py`")
+        L = C.CDLL(LIB_PATH)
+        L.bsir_last_error.restype = C.c_char_p
+        L.bsir_status_string.restype = C.c_char_p
+        L.bsir_version.restype = C.c_char_p
+        L.bsir_get_stream.restype = C.c_void_p
+        L.bsir_launch_count.restype = C.c_int64
+        L.bsir_reduce_with_index_workspace_bytes.restype = C.c_int64
+        L.bsir_matmul_w8a8_workspace_bytes.restype = C.c_int64
+        _lib = L
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise BsirError(rc, lib().bsir_last_error().decode() or lib().bsir_status_string(rc).decode())
+
+
+def _stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _TORCH2DT[t.dtype]
+    except KeyError:
+        raise BsirError(-4, f"unsupported tensor dtype {t.dtype}") from None
+
+
+def _i64arr(v: Sequence[int], n: int = 3):
+    a = (C.c_int64 * n)()
+    for i, x in enumerate(v):
+        a[i] = int(x)
+    return a
+
+
+def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
+    return C.c_void_p(t.data_ptr() if t is not None else 0)
+
+
+def _scalar_bits(v, dtype: torch.dtype) -> int:
+    t = torch.tensor([v], dtype=dtype)
+    nbytes = t.element_size()
+    raw = t.view(torch.uint8).numpy().tobytes() + b"\0" * (8 - nbytes)
+    return int.from_bytes(raw, "little")
+
+
+def _operand(x, shape: Sequence[int], dtype: torch.dtype) -> Operand:
+    o = Operand()
+    if isinstance(x, torch.Tensor):
+        if x.dtype != dtype:
+            raise BsirError(-4, f"operand dtype {x.dtype} != {dtype}")
+        if x.dim() != len(shape):
+            raise BsirError(-2, f"operand rank {x.dim()} != {len(shape)}")
+        o.data = x.data_ptr()
+        for i in range(len(shape)):
+            if x.shape[i] == shape[i]:
+                o.strides[i] = x.stride(i)
+            elif x.shape[i] == 1:
+                o.strides[i] = 0  # inline broadcast
+            else:
+                raise BsirError(-2, f"operand shape {tuple(x.shape)} does not broadcast to {tuple(shape)}")
+    else:
+        o.data = None
+        o.scalar_bits = _scalar_bits(x, dtype)
+    return o
+
+
+def _result_shape(*xs) -> Sequence[int]:
+    ts = [x for x in xs if isinstance(x, torch.Tensor)]
+    if not ts:
+        raise BsirError(-1, "at least one operand must be a tensor")
+    return list(torch.broadcast_shapes(*[t.shape for t in ts]))
+
+
+def _first_tensor(*xs) -> torch.Tensor:
+    return next(x for x in xs if isinstance(x, torch.Tensor))
+
+
+# ---------------------------------------------------------------------------- elementwise
+def elemwise_unary(fun: str, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hfusion.elemwise_unary`` / ``linalg.elemwise_unary`` {fun}."""
+    shape = list(x.shape)
+    out = torch.empty_like(x, memory_format=torch.contiguous_format) if out is None else out
+    op = _operand(x, shape, x.dtype)
+    _check(lib().bsir_elemwise_unary(UNARY_FN[fun], _dt(x), len(shape), _i64arr(shape), C.byref(op), _ptr(out),
+                                     _i64arr(out.stride()), _stream()))
+    return out
+
+
+def elemwise_binary(fun: str, a, b, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hfusion.elemwise_binary`` / ``linalg.elemwise_binary`` {fun}; a or b may be a Python scalar."""
+    ref = _first_tensor(a, b)
+    shape = _result_shape(a, b)
+    out = torch.empty(shape, dtype=ref.dtype, device=ref.device) if out is None else out
+    oa, ob = _operand(a, shape, ref.dtype), _operand(b, shape, ref.dtype)
+    _check(lib().bsir_elemwise_binary(BINARY_FN[fun], _dt(ref), len(shape), _i64arr(shape), C.byref(oa), C.byref(ob),
+                                      _ptr(out), _i64arr(out.stride()), _stream()))
+    return out
+
+
+def vadd(a, b, out=None):
+    """``hivm.hir.vadd``."""
+    return elemwise_binary("add", a, b, out)
+
+
+def vsub(a, b, out=None):
+    return elemwise_binary("sub", a, b, out)
+
+
+def vmul(a, b, out=None):
+    return elemwise_binary("mul", a, b, out)
+
+
+def vdiv(a, b, out=None):
+    return elemwise_binary("div", a, b, out)
+
+
+def compare(compare_fn: str, a, b) -> torch.Tensor:
+    """``hfusion.compare`` {compare_fn}; returns a bool tensor."""
+    ref = _first_tensor(a, b)
+    shape = _result_shape(a, b)
+    out = torch.empty(shape, dtype=torch.bool, device=ref.device)
+    oa, ob = _operand(a, shape, ref.dtype), _operand(b, shape, ref.dtype)
+    _check(lib().bsir_compare(COMPARE_FN[compare_fn], _dt(ref), len(shape), _i64arr(shape), C.byref(oa), C.byref(ob),
+                              _ptr(out), _i64arr(out.stride()), _stream()))
+    return out
+
+
+def select(cond: torch.Tensor, a, b) -> torch.Tensor:
+    """``hfusion.select``: cond ? a : b."""
+    ref = _first_tensor(a, b)
+    shape = _result_shape(cond, a, b)
+    out = torch.empty(shape, dtype=ref.dtype, device=ref.device)
+    oc = _operand(cond, shape, torch.bool)
+    oa, ob = _operand(a, shape, ref.dtype), _operand(b, shape, ref.dtype)
+    _check(lib().bsir_select(_dt(ref), len(shape), _i64arr(shape), C.byref(oc), C.byref(oa), C.byref(ob), _ptr(out),
+                             _i64arr(out.stride()), _stream()))
+    return out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype, round_mode: str = "rint", enable_saturate: bool = False,
+         overflow_mode: Optional[str] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hfusion.cast`` {round_mode, enable_saturate}; ``overflow_mode`` selects a named variant."""
+    ov = OVERFLOW_MODE[overflow_mode] if overflow_mode else (1 if enable_saturate else 0)
+    out = torch.empty(x.shape, dtype=dtype, device=x.device) if out is None else out
+    shape = list(x.shape)
+    _check(lib().bsir_cast(_dt(x), _TORCH2DT[dtype], ROUND_MODE[round_mode], ov, len(shape), _i64arr(shape), _ptr(x),
+                           _i64arr(x.stride()), _ptr(out), _i64arr(out.stride()), _stream()))
+    return out
+
+
+def copy(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hivm.hir.load`` / ``store`` / ``copy``."""
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device) if out is None else out
+    shape = list(x.shape)
+    _check(lib().bsir_copy(_dt(x), len(shape), _i64arr(shape), _ptr(x), _i64arr(x.stride()), _ptr(out),
+                           _i64arr(out.stride()), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------- reductions
+def _rows(x: torch.Tensor):
+    if x.dim() != 2:
+        raise BsirError(-2, "expected a 2-D tensor")
+    if x.shape[1] > 1 and x.stride(1) != 1:
+        raise BsirError(-3, "innermost dimension must be unit-stride")
+    return x.shape[0], x.shape[1], (x.stride(0) if x.shape[0] > 1 else max(x.shape[1], 1))
+
+
+def reduce(kind: str, x: torch.Tensor, dim: int = 1) -> torch.Tensor:
+    """``linalg.reduce`` / ``hivm.hir.vreduce <kind>`` over dim 0 or 1 of a 2-D tensor."""
+    rows, cols, rs = _rows(x)
+    if dim in (1, -1):
+        out = torch.empty(rows, dtype=x.dtype, device=x.device)
+        _check(lib().bsir_reduce_last_axis(REDUCE_KIND[kind], _dt(x), C.c_int64(rows), C.c_int64(cols), _ptr(x),
+                                           C.c_int64(rs), _ptr(out), _stream()))
+    else:
+        out = torch.empty(cols, dtype=x.dtype, device=x.device)
+        _check(lib().bsir_reduce_first_axis(REDUCE_KIND[kind], _dt(x), C.c_int64(rows), C.c_int64(cols), _ptr(x),
+                                            C.c_int64(rs), _ptr(out), _stream()))
+    return out
+
+
+def reduce_with_index(kind: str, x: torch.Tensor, tie_break_left: bool = True, nan_mode: str = "region",
+                      workspace: Optional[torch.Tensor] = None):
+    """``hfusion.reduce_with_index <max|min> {tie_break_left}`` over the last axis -> (values, int32 indices)."""
+    rows, cols, rs = _rows(x)
+    val = torch.empty(rows, dtype=x.dtype, device=x.device)
+    idx = torch.empty(rows, dtype=torch.int32, device=x.device)
+    ws_ptr = _ptr(workspace) if workspace is not None else C.c_void_p(0)
+    ws_bytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    _check(lib().bsir_reduce_with_index(RWI_KIND[kind], _dt(x), int(bool(tie_break_left)),
+                                        {"region": 0, "nan_first": 1}[nan_mode], C.c_int64(rows), C.c_int64(cols),
+                                        _ptr(x), C.c_int64(rs), _ptr(val), _ptr(idx), ws_ptr, C.c_int64(ws_bytes),
+                                        _stream()))
+    return val, idx
+
+
+# ---------------------------------------------------------------------------- fused row patterns
+def rms_norm(x: torch.Tensor, gamma: torch.Tensor, eps: float, want_rstd: bool = False,
+             out: Optional[torch.Tensor] = None):
+    rows, cols, rs = _rows(x)
+    y = torch.empty((rows, cols), dtype=x.dtype, device=x.device) if out is None else out
+    rstd = torch.empty(rows, dtype=x.dtype, device=x.device) if want_rstd else None
+    _check(lib().bsir_rms_norm(_dt(x), C.c_int64(rows), C.c_int64(cols), _ptr(x), C.c_int64(rs), _ptr(gamma),
+                               C.c_float(eps), _ptr(y), C.c_int64(y.stride(0) if rows > 1 else max(cols, 1)),
+                               _ptr(rstd) if want_rstd else C.c_void_p(0), _stream()))
+    return (y, rstd) if want_rstd else y
+
+
+def softmax(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    rows, cols, rs = _rows(x)
+    y = torch.empty((rows, cols), dtype=x.dtype, device=x.device) if out is None else out
+    _check(lib().bsir_softmax(_dt(x), C.c_int64(rows), C.c_int64(cols), _ptr(x), C.c_int64(rs), _ptr(y),
+                              C.c_int64(y.stride(0) if rows > 1 else max(cols, 1)), _stream()))
+    return y
+
+
+def quant_per_token_i8(x: torch.Tensor, round_mode: str = "rint", q: Optional[torch.Tensor] = None,
+                       scale: Optional[torch.Tensor] = None):
+    rows, cols, rs = _rows(x)
+    q = torch.empty((rows, cols), dtype=torch.int8, device=x.device) if q is None else q
+    scale = torch.empty(rows, dtype=torch.float32, device=x.device) if scale is None else scale
+    _check(lib().bsir_quant_per_token_i8(_dt(x), ROUND_MODE[round_mode], C.c_int64(rows), C.c_int64(cols), _ptr(x),
+                                         C.c_int64(rs), _ptr(q), C.c_int64(q.stride(0) if rows > 1 else max(cols, 1)),
+                                         _ptr(scale), _stream()))
+    return q, scale
+
+
+# ---------------------------------------------------------------------------- GEMMs
+def matmul_w8a8(a: torch.Tensor, b: torch.Tensor, scale_a: Optional[torch.Tensor] = None,
+                scale_b: Optional[torch.Tensor] = None, transpose_b: bool = False,
+                out_dtype: torch.dtype = torch.bfloat16, want_acc: bool = False,
+                out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None):
+    """``linalg.matmul`` i8 x i8 -> i32 plus the dequant suffix; b is [k, n] or (transpose_b) [n, k]."""
+    m, k = a.shape
+    n = b.shape[0] if transpose_b else b.shape[1]
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    acc = torch.empty((m, n), dtype=torch.int32, device=a.device) if want_acc else None
+    ws_ptr = _ptr(workspace) if workspace is not None else C.c_void_p(0)
+    ws_bytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
+    _check(lib().bsir_matmul_w8a8(C.c_int64(m), C.c_int64(n), C.c_int64(k), _ptr(a), C.c_int64(a.stride(0)), _ptr(b),
+                                  C.c_int64(b.stride(0)), int(bool(transpose_b)),
+                                  _ptr(scale_a) if scale_a is not None else C.c_void_p(0),
+                                  _ptr(scale_b) if scale_b is not None else C.c_void_p(0), _TORCH2DT[out_dtype],
+                                  _ptr(out), C.c_int64(out.stride(0)), _ptr(acc) if want_acc else C.c_void_p(0),
+                                  ws_ptr, C.c_int64(ws_bytes), _stream()))
+    return (out, acc) if want_acc else out
+
+
+def matmul_w4a16(a: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,
+                 group: int = 128, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    m, k = a.shape
+    n = qweight.shape[1]
+    out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device) if out is None else out
+    _check(lib().bsir_matmul_w4a16(C.c_int64(m), C.c_int64(n), C.c_int64(k), C.c_int64(group), _ptr(a),
+                                   C.c_int64(a.stride(0)), _ptr(qweight), _ptr(scales), _ptr(zeros), _ptr(out),
+                                   C.c_int64(out.stride(0)), _stream()))
+    return out
+
+
+# ---------------------------------------------------------------------------- compiled-kernel ABI
+def register_kernel(name: str, kind: str, *, fn: int = 0, dtype: int = F32, dst_dtype: int = F32,
+                    round_mode: str = "rint", overflow_mode: str = "wrap", flags: int = 0,
+                    sizes: Sequence[int] = (), eps: float = 0.0) -> None:
+    d = KernelDesc()
+    d.kind = KERNEL_KIND[kind]
+    d.fn, d.dtype, d.dst_dtype = fn, dtype, dst_dtype
+    d.round_mode, d.overflow_mode, d.flags = ROUND_MODE[round_mode], OVERFLOW_MODE[overflow_mode], flags
+    d.rank = len(sizes)
+    for i, s in enumerate(sizes):
+        d.sizes[i] = int(s)
+    d.eps = eps
+    _check(lib().bsir_kernel_register(name.encode(), C.byref(d)))
+
+
+def launch(name: str, args: Sequence[Optional[torch.Tensor]], block_dim: int = 1) -> None:
+    """``rtKernelLaunch`` analogue: one bare pointer per memref argument, inputs then outputs."""
+    arr = (C.c_void_p * len(args))(*[(t.data_ptr() if t is not None else None) for t in args])
+    _check(lib().bsir_launch(name.encode(), C.c_uint32(block_dim), arr, C.c_size_t(C.sizeof(arr)), _stream()))
+
+
+def device_error() -> int:
+    return int(lib().bsir_device_error())
+
+
+def launch_count() -> int:
+    return int(lib().bsir_launch_count())

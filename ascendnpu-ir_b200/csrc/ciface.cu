@@ -1,0 +1,255 @@
+// ciface.cu -- definitions of the `_mlir_ciface_*` op-library symbols.
+//
+// Each symbol unpacks MLIR memref descriptors (base = aligned + offset, strides in elements:
+// bishengir/lib/Template/include/Utils.h:72-78) and forwards to the typed entry point.  The
+// symbol tables live in include/bsir_b200_ciface.h and restate what the reference registers
+// (bishengir/lib/Template/lib/Vector/Elementwise/EltWise1D.cpp:1318-1500 and siblings).
+// Work is enqueued on the calling thread's stream (bsir_set_stream).
+#include "common.cuh"
+
+namespace bsir {
+namespace {
+
+template <class M>
+inline const void *base_of(const M *m, int dt) {
+  return static_cast<const char *>(m->aligned) + m->offset * dtype_bytes(dt);
+}
+template <class M>
+inline void *base_of_mut(M *m, int dt) {
+  return static_cast<char *>(m->aligned) + m->offset * dtype_bytes(dt);
+}
+
+template <int RANK, class M>
+int32_t shapes_match(const char *what, const M *a, const M *b) {
+  for (int i = 0; i < RANK; ++i)
+    if (a->sizes[i] != b->sizes[i] && a->sizes[i] != 1)
+      return fail(BSIR_ERR_SHAPE, "%s: operand size %lld vs result size %lld in dim %d", what, (long long)a->sizes[i],
+                  (long long)b->sizes[i], i);
+  return BSIR_OK;
+}
+
+// Operand from a descriptor; a dimension of size 1 against a larger result broadcasts (stride 0),
+// the inline-broadcast form of the HIVM vector ops.
+template <int RANK, class M>
+bsir_operand operand_of(const M *m, const M *dst, int dt) {
+  bsir_operand o{base_of(m, dt), {0, 0, 0}, 0};
+  for (int i = 0; i < RANK; ++i) o.strides[i] = (m->sizes[i] == 1 && dst->sizes[i] != 1) ? 0 : m->strides[i];
+  return o;
+}
+
+template <int RANK, class M>
+int32_t vv(const char *what, int fn, int dt, M *a, M *b, M *dst) {
+  if (!a || !b || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  if (int32_t rc = shapes_match<RANK>(what, a, dst)) return rc;
+  if (int32_t rc = shapes_match<RANK>(what, b, dst)) return rc;
+  bsir_operand oa = operand_of<RANK>(a, dst, dt), ob = operand_of<RANK>(b, dst, dt);
+  return bsir_elemwise_binary(fn, dt, RANK, dst->sizes, &oa, &ob, base_of_mut(dst, dt), dst->strides, nullptr);
+}
+template <int RANK, class M>
+int32_t vs(const char *what, int fn, int dt, M *a, uint64_t scalar_bits, M *dst, bool scalar_first) {
+  if (!a || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  if (int32_t rc = shapes_match<RANK>(what, a, dst)) return rc;
+  bsir_operand oa = operand_of<RANK>(a, dst, dt), os{nullptr, {0, 0, 0}, scalar_bits};
+  return scalar_first
+             ? bsir_elemwise_binary(fn, dt, RANK, dst->sizes, &os, &oa, base_of_mut(dst, dt), dst->strides, nullptr)
+             : bsir_elemwise_binary(fn, dt, RANK, dst->sizes, &oa, &os, base_of_mut(dst, dt), dst->strides, nullptr);
+}
+template <int RANK, class M>
+int32_t v1(const char *what, int fn, int dt, M *a, M *dst) {
+  if (!a || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  if (int32_t rc = shapes_match<RANK>(what, a, dst)) return rc;
+  bsir_operand oa = operand_of<RANK>(a, dst, dt);
+  return bsir_elemwise_unary(fn, dt, RANK, dst->sizes, &oa, base_of_mut(dst, dt), dst->strides, nullptr);
+}
+template <int RANK, class M>
+int32_t vcast(const char *what, int sdt, int ddt, M *src, M *dst, uint32_t cast_mode, int overflow) {
+  if (!src || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  for (int i = 0; i < RANK; ++i)
+    if (src->sizes[i] != dst->sizes[i]) return fail(BSIR_ERR_SHAPE, "%s: size mismatch in dim %d", what, i);
+  // CastMode R/A/F/C/Z/O/OVERFLOW carries the same numbering as hfusion.round_mode
+  // (bishengir/lib/Template/include/Vector/Cast/CastUtils.h:30-38).
+  return bsir_cast(sdt, ddt, static_cast<int32_t>(cast_mode), overflow, RANK, dst->sizes, base_of(src, sdt),
+                   src->strides, base_of_mut(dst, ddt), dst->strides, nullptr);
+}
+
+template <class T>
+inline uint64_t bits_of_scalar(T v) {
+  uint64_t b = 0;
+  memcpy(&b, &v, sizeof(T));
+  return b;
+}
+
+int32_t reduce_ar(const char *what, int kind, int dt, bsir_memref_2d *src, bsir_memref_2d *dst) {
+  if (!src || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  if (src->sizes[1] > 1 && src->strides[1] != 1) return fail(BSIR_ERR_STRIDE, "%s: reduced axis must be unit-stride", what);
+  if (dst->sizes[0] != src->sizes[0]) return fail(BSIR_ERR_SHAPE, "%s: dst rows", what);
+  if (dst->sizes[0] > 1 && dst->strides[0] != 1) return fail(BSIR_ERR_STRIDE, "%s: dst must be dense", what);
+  return bsir_reduce_last_axis(kind, dt, src->sizes[0], src->sizes[1], base_of(src, dt),
+                               src->sizes[0] > 1 ? src->strides[0] : src->sizes[1], base_of_mut(dst, dt), nullptr);
+}
+int32_t reduce_r(const char *what, int kind, int dt, bsir_memref_1d *src, bsir_memref_1d *dst) {
+  if (!src || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  if (src->sizes[0] > 1 && src->strides[0] != 1) return fail(BSIR_ERR_STRIDE, "%s: reduced axis must be unit-stride", what);
+  return bsir_reduce_last_axis(kind, dt, 1, src->sizes[0], base_of(src, dt), src->sizes[0], base_of_mut(dst, dt), nullptr);
+}
+int32_t reduce_ra(const char *what, int kind, int dt, bsir_memref_2d *src, bsir_memref_2d *dst) {
+  if (!src || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  if (src->sizes[1] > 1 && src->strides[1] != 1) return fail(BSIR_ERR_STRIDE, "%s: kept axis must be unit-stride", what);
+  if (dst->sizes[1] != src->sizes[1]) return fail(BSIR_ERR_SHAPE, "%s: dst cols", what);
+  if (dst->sizes[1] > 1 && dst->strides[1] != 1) return fail(BSIR_ERR_STRIDE, "%s: dst must be dense", what);
+  return bsir_reduce_first_axis(kind, dt, src->sizes[0], src->sizes[1], base_of(src, dt),
+                                src->sizes[0] > 1 ? src->strides[0] : src->sizes[1], base_of_mut(dst, dt), nullptr);
+}
+int32_t rwi_ar(const char *what, int kind, int left, int dt, bsir_memref_2d *src, bsir_memref_2d *dv, bsir_memref_2d *di,
+               bsir_memref_1d *tmp) {
+  if (!src || !dv || !di) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  if (src->sizes[1] > 1 && src->strides[1] != 1) return fail(BSIR_ERR_STRIDE, "%s: reduced axis must be unit-stride", what);
+  if ((dv->sizes[0] > 1 && dv->strides[0] != 1) || (di->sizes[0] > 1 && di->strides[0] != 1))
+    return fail(BSIR_ERR_STRIDE, "%s: results must be dense", what);
+  (void)tmp;  // on-chip temp of the reference; the global scratch here has its own zero-fill contract
+  // The device library's NaN rule: the first NaN wins
+  // (bishengir/lib/Template/lib/Vector/Reduction/ReduceR_With_Index.cpp:83-125).
+  return bsir_reduce_with_index(kind, dt, left, BSIR_RWI_NAN_FIRST, src->sizes[0], src->sizes[1], base_of(src, dt),
+                                src->sizes[0] > 1 ? src->strides[0] : src->sizes[1], base_of_mut(dv, dt),
+                                static_cast<int32_t *>(base_of_mut(di, BSIR_I32)), nullptr, 0, nullptr);
+}
+int32_t rwi_r(const char *what, int kind, int left, int dt, bsir_memref_1d *src, bsir_memref_1d *dv, bsir_memref_1d *di) {
+  if (!src || !dv || !di) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  if (src->sizes[0] > 1 && src->strides[0] != 1) return fail(BSIR_ERR_STRIDE, "%s: reduced axis must be unit-stride", what);
+  return bsir_reduce_with_index(kind, dt, left, BSIR_RWI_NAN_FIRST, 1, src->sizes[0], base_of(src, dt), src->sizes[0],
+                                base_of_mut(dv, dt), static_cast<int32_t *>(base_of_mut(di, BSIR_I32)), nullptr, 0, nullptr);
+}
+
+int32_t matmul_i8_half(const char *what, bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_2d *C, int transpose_b) {
+  if (!A || !B || !C) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  const int64_t m = A->sizes[0], k = A->sizes[1];
+  const int64_t n = transpose_b ? B->sizes[0] : B->sizes[1];
+  if ((transpose_b ? B->sizes[1] : B->sizes[0]) != k || C->sizes[0] != m || C->sizes[1] != n)
+    return fail(BSIR_ERR_SHAPE, "%s: shapes do not compose", what);
+  if ((k > 1 && A->strides[1] != 1) || B->strides[1] != 1 || (n > 1 && C->strides[1] != 1))
+    return fail(BSIR_ERR_STRIDE, "%s: innermost dimensions must be unit-stride", what);
+  return bsir_matmul_w8a8(m, n, k, static_cast<const int8_t *>(base_of(A, BSIR_I8)), A->strides[0],
+                          static_cast<const int8_t *>(base_of(B, BSIR_I8)), B->strides[0], transpose_b, nullptr, nullptr,
+                          BSIR_F16, base_of_mut(C, BSIR_F16), C->strides[0], nullptr, nullptr, 0, nullptr);
+}
+
+}  // namespace
+}  // namespace bsir
+
+using namespace bsir;
+
+extern "C" {
+
+#define BSIR_DEF_VV(op, fn, rank, tok)                                                                       \
+  int32_t _mlir_ciface_##op##_##rank##d_##tok(BSIR_MEMREF_T(rank) * src0, BSIR_MEMREF_T(rank) * src1,        \
+                                              BSIR_MEMREF_T(rank) * dst, bsir_memref_1d *) {                 \
+    clear_error();                                                                                           \
+    return vv<rank>(#op "_" #rank "d_" #tok, fn, BSIR_DT_##tok, src0, src1, dst);                            \
+  }
+#define BSIR_DEF_VS(op, fn, rank, tok)                                                                       \
+  int32_t _mlir_ciface_##op##_vs_##rank##d_##tok(BSIR_MEMREF_T(rank) * src0, BSIR_SCALAR_##tok scalar,       \
+                                                 BSIR_MEMREF_T(rank) * dst, bsir_memref_1d *) {              \
+    clear_error();                                                                                           \
+    return vs<rank>(#op "_vs_" #rank "d_" #tok, fn, BSIR_DT_##tok, src0, bits_of_scalar(scalar), dst, false); \
+  }
+#define BSIR_DEF_SV(op, fn, rank, tok)                                                                       \
+  int32_t _mlir_ciface_##op##_sv_##rank##d_##tok(BSIR_SCALAR_##tok scalar, BSIR_MEMREF_T(rank) * src1,       \
+                                                 BSIR_MEMREF_T(rank) * dst, bsir_memref_1d *) {              \
+    clear_error();                                                                                           \
+    return vs<rank>(#op "_sv_" #rank "d_" #tok, fn, BSIR_DT_##tok, src1, bits_of_scalar(scalar), dst, true);  \
+  }
+#define BSIR_DEF_V(op, fn, rank, tok)                                                                        \
+  int32_t _mlir_ciface_##op##_##rank##d_##tok(BSIR_MEMREF_T(rank) * src0, BSIR_MEMREF_T(rank) * dst,         \
+                                              bsir_memref_1d *) {                                            \
+    clear_error();                                                                                           \
+    return v1<rank>(#op "_" #rank "d_" #tok, fn, BSIR_DT_##tok, src0, dst);                                  \
+  }
+#define BSIR_DEF_CAST_MODE(s, d, rank)                                                                       \
+  int32_t _mlir_ciface_vcast_##s##_to_##d##_##rank##d_with_mode(BSIR_MEMREF_T(rank) * src,                   \
+                                                                BSIR_MEMREF_T(rank) * dst, uint32_t cast_mode) { \
+    clear_error();                                                                                           \
+    return vcast<rank>("vcast_" #s "_to_" #d, BSIR_DT_##s, BSIR_DT_##d, src, dst, cast_mode, BSIR_OVERFLOW_SATURATE); \
+  }
+#define BSIR_DEF_CAST_OVERFLOW(s, d, rank)                                                                   \
+  int32_t _mlir_ciface_vcast_##s##_to_##d##_##rank##d_with_overflow(                                         \
+      BSIR_MEMREF_T(rank) * src, BSIR_MEMREF_T(rank) * dst, bsir_memref_1d *, uint32_t cast_mode) {          \
+    clear_error();                                                                                           \
+    return vcast<rank>("vcast_" #s "_to_" #d, BSIR_DT_##s, BSIR_DT_##d, src, dst, cast_mode, BSIR_OVERFLOW_WRAP); \
+  }                                                                                                          \
+  int32_t _mlir_ciface_vcast_##s##_to_##d##_##rank##d_with_overflow_no_size_align(                           \
+      BSIR_MEMREF_T(rank) * src, BSIR_MEMREF_T(rank) * dst, bsir_memref_1d *, uint32_t cast_mode) {          \
+    clear_error();                                                                                           \
+    return vcast<rank>("vcast_" #s "_to_" #d, BSIR_DT_##s, BSIR_DT_##d, src, dst, cast_mode, BSIR_OVERFLOW_WRAP); \
+  }
+#define BSIR_DEF_CAST_TEMP(s, d, rank)                                                                       \
+  int32_t _mlir_ciface_vcast_##s##_to_##d##_##rank##d_with_temp(BSIR_MEMREF_T(rank) * src,                   \
+                                                                BSIR_MEMREF_T(rank) * dst, bsir_memref_1d *, \
+                                                                uint32_t cast_mode) {                        \
+    clear_error();                                                                                           \
+    return vcast<rank>("vcast_" #s "_to_" #d, BSIR_DT_##s, BSIR_DT_##d, src, dst, cast_mode, BSIR_OVERFLOW_SATURATE); \
+  }
+/* initvalue is the identity the caller would have filled dst with; dst is write-only here. */
+#define BSIR_DEF_REDUCE(name, kind, tok)                                                                     \
+  int32_t _mlir_ciface_##name##_ar_##tok(bsir_memref_2d *src0, bsir_memref_2d *dst, bsir_memref_1d *,        \
+                                         BSIR_SCALAR_##tok) {                                                \
+    clear_error();                                                                                           \
+    return reduce_ar(#name "_ar_" #tok, kind, BSIR_DT_##tok, src0, dst);                                     \
+  }                                                                                                          \
+  int32_t _mlir_ciface_##name##_r_##tok(bsir_memref_1d *src0, bsir_memref_1d *dst, bsir_memref_1d *,         \
+                                        BSIR_SCALAR_##tok) {                                                 \
+    clear_error();                                                                                           \
+    return reduce_r(#name "_r_" #tok, kind, BSIR_DT_##tok, src0, dst);                                       \
+  }                                                                                                          \
+  int32_t _mlir_ciface_##name##_ra_##tok(bsir_memref_2d *src0, bsir_memref_2d *dst, bsir_memref_1d *,        \
+                                         BSIR_SCALAR_##tok) {                                                \
+    clear_error();                                                                                           \
+    return reduce_ra(#name "_ra_" #tok, kind, BSIR_DT_##tok, src0, dst);                                     \
+  }
+#define BSIR_DEF_REDUCE_WITH_INDEX(name, kind, left, tok)                                                    \
+  int32_t _mlir_ciface_##name##_ar_##tok(bsir_memref_2d *src0, bsir_memref_2d *dst_value,                    \
+                                         bsir_memref_2d *dst_index, bsir_memref_1d *tmp_buf,                 \
+                                         BSIR_SCALAR_##tok) {                                                \
+    clear_error();                                                                                           \
+    return rwi_ar(#name "_ar_" #tok, kind, left, BSIR_DT_##tok, src0, dst_value, dst_index, tmp_buf);        \
+  }                                                                                                          \
+  int32_t _mlir_ciface_##name##_r_##tok(bsir_memref_1d *src0, bsir_memref_1d *dst_value,                     \
+                                        bsir_memref_1d *dst_index, bsir_memref_1d *, BSIR_SCALAR_##tok) {    \
+    clear_error();                                                                                           \
+    return rwi_r(#name "_r_" #tok, kind, left, BSIR_DT_##tok, src0, dst_value, dst_index);                   \
+  }
+
+BSIR_FOREACH_ELTWISE_VV(BSIR_DEF_VV, 1)
+BSIR_FOREACH_ELTWISE_VV(BSIR_DEF_VV, 2)
+BSIR_FOREACH_ELTWISE_VV(BSIR_DEF_VV, 3)
+BSIR_FOREACH_ELTWISE_VS(BSIR_DEF_VS, 1)
+BSIR_FOREACH_ELTWISE_VS(BSIR_DEF_VS, 2)
+BSIR_FOREACH_ELTWISE_VS(BSIR_DEF_VS, 3)
+BSIR_FOREACH_ELTWISE_SV(BSIR_DEF_SV, 1)
+BSIR_FOREACH_ELTWISE_SV(BSIR_DEF_SV, 2)
+BSIR_FOREACH_ELTWISE_SV(BSIR_DEF_SV, 3)
+BSIR_FOREACH_ELTWISE_V(BSIR_DEF_V, 1)
+BSIR_FOREACH_ELTWISE_V(BSIR_DEF_V, 2)
+BSIR_FOREACH_ELTWISE_V(BSIR_DEF_V, 3)
+BSIR_FOREACH_CAST_WITH_MODE(BSIR_DEF_CAST_MODE, 1)
+BSIR_FOREACH_CAST_WITH_MODE(BSIR_DEF_CAST_MODE, 2)
+BSIR_FOREACH_CAST_WITH_OVERFLOW(BSIR_DEF_CAST_OVERFLOW, 1)
+BSIR_FOREACH_CAST_WITH_OVERFLOW(BSIR_DEF_CAST_OVERFLOW, 2)
+BSIR_FOREACH_CAST_WITH_TEMP(BSIR_DEF_CAST_TEMP, 1)
+BSIR_FOREACH_CAST_WITH_TEMP(BSIR_DEF_CAST_TEMP, 2)
+BSIR_FOREACH_REDUCE(BSIR_DEF_REDUCE)
+BSIR_FOREACH_REDUCE_WITH_INDEX(BSIR_DEF_REDUCE_WITH_INDEX)
+
+int32_t _mlir_ciface_matmul_Xbias_Xdescale_XtransposeA_XtransposeB_TAint8_t_TBint8_t_TChalf(bsir_memref_2d *A,
+                                                                                          bsir_memref_2d *B,
+                                                                                          bsir_memref_2d *C) {
+  clear_error();
+  return matmul_i8_half("matmul_i8_i8_half", A, B, C, 0);
+}
+int32_t _mlir_ciface_matmul_Xbias_Xdescale_XtransposeA_transposeB_TAint8_t_TBint8_t_TChalf(bsir_memref_2d *A,
+                                                                                         bsir_memref_2d *B,
+                                                                                         bsir_memref_2d *C) {
+  clear_error();
+  return matmul_i8_half("matmul_i8_i8T_half", A, B, C, 1);
+}
+
+}  // extern "C"

@@ -1,0 +1,152 @@
+// common.cuh -- shared host/device helpers of the sm_100a backend library.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+
+#include "bsir_b200.h"
+
+namespace bsir {
+
+// ----------------------------------------------------------------------------
+// host: errors, streams, device info
+// ----------------------------------------------------------------------------
+int32_t fail(int32_t status, const char *fmt, ...);  // records the text, returns status
+void clear_error();
+cudaStream_t resolve_stream(void *stream);           // NULL -> the thread's stream
+int32_t check_launch(const char *what);              // cudaGetLastError -> status
+void count_launch(int n = 1);
+
+struct DeviceInfo {
+  int device = -1;
+  int sm_count = 0;
+  int max_smem_optin = 0;
+  int cc_major = 0;
+};
+const DeviceInfo &device_info();  // of the current device (cached per device)
+
+// Library-owned scratch of the current device: grown on demand, zero-filled when
+// (re)allocated.  Kernels that use it keep the "counters are zero between calls"
+// invariant themselves.  Returns nullptr and records an error on failure.
+void *device_workspace(size_t bytes, cudaStream_t stream);
+// Device-side error word (one int per device); kernels OR a code into it when a
+// bounded wait gives up.
+int *device_error_word();
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// dtype helpers
+inline int dtype_bytes(int32_t dt) {
+  switch (dt) {
+    case BSIR_F32: case BSIR_I32: case BSIR_U32: return 4;
+    case BSIR_F16: case BSIR_BF16: case BSIR_I16: case BSIR_U16: return 2;
+    case BSIR_I64: case BSIR_U64: return 8;
+    case BSIR_I8: case BSIR_U8: case BSIR_BOOL: return 1;
+    default: return 0;
+  }
+}
+inline bool dtype_is_float(int32_t dt) { return dt == BSIR_F32 || dt == BSIR_F16 || dt == BSIR_BF16; }
+inline bool dtype_is_unsigned(int32_t dt) { return dt >= BSIR_U8 && dt <= BSIR_BOOL; }
+inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// ----------------------------------------------------------------------------
+// device: element types and conversions
+// ----------------------------------------------------------------------------
+struct alignas(16) Vec16 {
+  uint32_t w[4];
+};
+
+// Streaming (read-once) 16-byte global load / store: keep the data out of L1.
+__device__ __forceinline__ Vec16 ld_stream(const void *p) {
+  Vec16 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3])
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream(void *p, const Vec16 &v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]),
+               "r"(v.w[3])
+               : "memory");
+}
+
+__device__ __forceinline__ float bf16lo_to_f32(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi_to_f32(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+// two f32 -> packed bf16x2 (lo = a, hi = b), round to nearest even
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+__device__ __forceinline__ float f16lo_to_f32(uint32_t w) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(w & 0xffffu)));
+}
+__device__ __forceinline__ float f16hi_to_f32(uint32_t w) {
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(w >> 16)));
+}
+
+// arith.maximumf / minimumf: NaN-propagating, -0 < +0.
+__device__ __forceinline__ float maximumf(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float minimumf(float a, float b) {
+  float r;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+
+// Element traits for the float storage types: how many per 16-byte vector and
+// how to widen / narrow a packed 32-bit word.
+template <int DT> struct FloatTraits;
+template <> struct FloatTraits<BSIR_F32> {
+  static constexpr int kPerWord = 1;
+  __device__ static __forceinline__ void unpack(uint32_t w, float *o) { o[0] = __uint_as_float(w); }
+  __device__ static __forceinline__ uint32_t pack(const float *v) { return __float_as_uint(v[0]); }
+};
+template <> struct FloatTraits<BSIR_BF16> {
+  static constexpr int kPerWord = 2;
+  __device__ static __forceinline__ void unpack(uint32_t w, float *o) {
+    o[0] = bf16lo_to_f32(w);
+    o[1] = bf16hi_to_f32(w);
+  }
+  __device__ static __forceinline__ uint32_t pack(const float *v) { return pack_bf16x2(v[0], v[1]); }
+};
+template <> struct FloatTraits<BSIR_F16> {
+  static constexpr int kPerWord = 2;
+  __device__ static __forceinline__ void unpack(uint32_t w, float *o) {
+    o[0] = f16lo_to_f32(w);
+    o[1] = f16hi_to_f32(w);
+  }
+  __device__ static __forceinline__ uint32_t pack(const float *v) { return pack_f16x2(v[0], v[1]); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max_nan(float v) {  // maximumf across the warp
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = maximumf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warp_max_num(float v) {  // fmaxf (NaN ignored) across the warp
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+}  // namespace bsir

@@ -1,0 +1,642 @@
+// elementwise.cu -- hfusion.elemwise_unary / elemwise_binary / compare / select and the
+// hivm.hir.v* vector ops that lower to them (vadd, vsub, vmul, ...), plus copy.
+//
+// Scalar semantics follow the region builders of the reference
+// (bishengir/lib/Dialect/HFusion/IR/HFusionOps.cpp:434-743): f16/bf16 operands are widened
+// to f32, the op runs in f32, the result is rounded once to nearest even
+// (bishengir/lib/Dialect/HFusion/Transforms/LegalizeBF16.cpp:243-275); integer ops wrap.
+//
+// Two paths.  Contiguous operands (or scalars) with 16-byte aligned bases take the
+// streaming path: 128-bit loads with four vectors in flight per thread, no L1 allocation,
+// streaming stores.  Everything else (strides, inline broadcast with stride 0, odd
+// alignment) takes the indexed path, one element per thread.
+#include "common.cuh"
+
+namespace bsir {
+namespace {
+
+// ------------------------------------------------------------------ scalar function tables
+// The switch sits outside the per-element loops, so one uniform branch serves a whole vector.
+template <int N>
+__device__ __forceinline__ bool unary_f32(int fn, const float *x, float *r) {
+#define U(expr)                                  \
+  {                                              \
+    _Pragma("unroll") for (int i = 0; i < N; ++i) { const float v = x[i]; r[i] = (expr); } \
+    return true;                                 \
+  }
+  switch (fn) {
+    case BSIR_UNARY_RELU: U(maximumf(0.0f, v))
+    case BSIR_UNARY_SQRT: case BSIR_UNARY_SQRT_L: U(__fsqrt_rn(v))
+    case BSIR_UNARY_RSQRT: case BSIR_UNARY_RSQRT_L: U(__fdiv_rn(1.0f, __fsqrt_rn(v)))
+    case BSIR_UNARY_REC: case BSIR_UNARY_RECIPROCAL: U(__fdiv_rn(1.0f, v))
+    case BSIR_UNARY_TANH: case BSIR_UNARY_TANH_L: U(tanhf(v))
+    case BSIR_UNARY_SIN: U(sinf(v))
+    case BSIR_UNARY_COS: U(cosf(v))
+    case BSIR_UNARY_ATAN: U(atanf(v))
+    case BSIR_UNARY_TAN: U(tanf(v))
+    case BSIR_UNARY_ERF: case BSIR_UNARY_ERF_L: U(erff(v))
+    case BSIR_UNARY_LOG2: U(log2f(v))
+    case BSIR_UNARY_LOG10: U(log10f(v))
+    case BSIR_UNARY_LOG1P: U(log1pf(v))
+    case BSIR_UNARY_EXP2: U(exp2f(v))
+    case BSIR_UNARY_EXPM1: U(expm1f(v))
+    case BSIR_UNARY_ASIN: U(asinf(v))
+    case BSIR_UNARY_ACOS: U(acosf(v))
+    case BSIR_UNARY_ASINH: U(asinhf(v))
+    case BSIR_UNARY_ACOSH: U(acoshf(v))
+    case BSIR_UNARY_ATANH: U(atanhf(v))
+    case BSIR_UNARY_SINH: U(sinhf(v))
+    case BSIR_UNARY_LGAMMA: U(lgammaf(v))
+    case BSIR_UNARY_COSH: U(coshf(v))
+    case BSIR_UNARY_NEARBYINT: U(rintf(v))
+    case BSIR_UNARY_EXP: U(expf(v))
+    case BSIR_UNARY_LOG: U(logf(v))
+    case BSIR_UNARY_ABS: U(fabsf(v))
+    case BSIR_UNARY_CEIL: U(ceilf(v))
+    case BSIR_UNARY_FLOOR: U(floorf(v))
+    case BSIR_UNARY_NEGF: U(-v)
+    case BSIR_UNARY_ROUND: U(roundf(v))
+    case BSIR_UNARY_SQUARE: U(__fmul_rn(v, v))
+    default: return false;
+  }
+#undef U
+}
+
+template <int N>
+__device__ __forceinline__ bool binary_f32(int fn, const float *a, const float *b, float *r) {
+#define B(expr)                                  \
+  {                                              \
+    _Pragma("unroll") for (int i = 0; i < N; ++i) { const float x = a[i], y = b[i]; r[i] = (expr); } \
+    return true;                                 \
+  }
+  switch (fn) {
+    case BSIR_BINARY_ADD: B(__fadd_rn(x, y))
+    case BSIR_BINARY_SUB: B(__fsub_rn(x, y))
+    case BSIR_BINARY_MUL: B(__fmul_rn(x, y))
+    case BSIR_BINARY_DIV: case BSIR_BINARY_DIVFHP: B(__fdiv_rn(x, y))
+    case BSIR_BINARY_MAXF: case BSIR_BINARY_MAX_SIGNED: case BSIR_BINARY_MAX_UNSIGNED: B(maximumf(x, y))
+    case BSIR_BINARY_MINF: case BSIR_BINARY_MIN_SIGNED: case BSIR_BINARY_MIN_UNSIGNED: B(minimumf(x, y))
+    case BSIR_BINARY_MAXNUMF: B(fmaxf(x, y))
+    case BSIR_BINARY_MINNUMF: B(fminf(x, y))
+    case BSIR_BINARY_POWF: case BSIR_BINARY_POWF_L: B(powf(x, y))
+    case BSIR_BINARY_MOD: case BSIR_BINARY_MODUI: B(fmodf(x, y))
+    case BSIR_BINARY_LDEXP: B(ldexpf(x, static_cast<int>(y)))
+    case BSIR_BINARY_ATAN2: B(atan2f(x, y))
+    case BSIR_BINARY_COPYSIGN: B(copysignf(x, y))
+    default: return false;
+  }
+#undef B
+}
+
+template <typename T> struct Unsigned;
+template <> struct Unsigned<int8_t> { using type = uint8_t; };
+template <> struct Unsigned<int16_t> { using type = uint16_t; };
+template <> struct Unsigned<int32_t> { using type = uint32_t; };
+template <> struct Unsigned<int64_t> { using type = uint64_t; };
+template <> struct Unsigned<uint8_t> { using type = uint8_t; };
+template <> struct Unsigned<uint16_t> { using type = uint16_t; };
+template <> struct Unsigned<uint32_t> { using type = uint32_t; };
+template <> struct Unsigned<uint64_t> { using type = uint64_t; };
+template <typename T> struct Signed;
+template <> struct Signed<int8_t> { using type = int8_t; };
+template <> struct Signed<int16_t> { using type = int16_t; };
+template <> struct Signed<int32_t> { using type = int32_t; };
+template <> struct Signed<int64_t> { using type = int64_t; };
+template <> struct Signed<uint8_t> { using type = int8_t; };
+template <> struct Signed<uint16_t> { using type = int16_t; };
+template <> struct Signed<uint32_t> { using type = int32_t; };
+template <> struct Signed<uint64_t> { using type = int64_t; };
+
+template <typename T>
+__device__ __forceinline__ T ipowi(T b, T e) {
+  using UT = typename Unsigned<T>::type;
+  using ST = typename Signed<T>::type;
+  if (static_cast<ST>(e) < 0 && T(-1) < T(0)) {
+    if (b == T(1)) return T(1);
+    if (b == T(-1)) return (e & 1) ? T(-1) : T(1);
+    return T(0);
+  }
+  UT r = 1, x = static_cast<UT>(b), n = static_cast<UT>(e);
+  while (n) { if (n & 1) r = static_cast<UT>(r * x); x = static_cast<UT>(x * x); n >>= 1; }
+  return static_cast<T>(r);
+}
+
+template <typename T, int N>
+__device__ __forceinline__ bool unary_int(int fn, const T *x, T *r) {
+  using UT = typename Unsigned<T>::type;
+#define U(expr)                                  \
+  {                                              \
+    _Pragma("unroll") for (int i = 0; i < N; ++i) { const T v = x[i]; r[i] = static_cast<T>(expr); } \
+    return true;                                 \
+  }
+  switch (fn) {
+    case BSIR_UNARY_RELU: U(v > T(0) ? v : T(0))
+    case BSIR_UNARY_VNOT: U(~v)
+    case BSIR_UNARY_ABSI: case BSIR_UNARY_ABS: U(v < T(0) ? static_cast<T>(UT(0) - static_cast<UT>(v)) : v)
+    case BSIR_UNARY_SQUARE: U(static_cast<UT>(v) * static_cast<UT>(v))
+    default: return false;
+  }
+#undef U
+}
+
+template <typename T, int N>
+__device__ __forceinline__ bool binary_int(int fn, const T *a, const T *b, T *r) {
+  using UT = typename Unsigned<T>::type;
+  using ST = typename Signed<T>::type;
+  constexpr int kBits = 8 * sizeof(T);
+  constexpr bool kSigned = T(-1) < T(0);
+#define B(expr)                                  \
+  {                                              \
+    _Pragma("unroll") for (int i = 0; i < N; ++i) { \
+      const T x = a[i], y = b[i];                \
+      const UT ux = static_cast<UT>(x), uy = static_cast<UT>(y); \
+      const ST sx = static_cast<ST>(x), sy = static_cast<ST>(y); \
+      (void)ux; (void)uy; (void)sx; (void)sy;    \
+      r[i] = static_cast<T>(expr);               \
+    }                                            \
+    return true;                                 \
+  }
+  switch (fn) {
+    case BSIR_BINARY_VOR: B(x | y)
+    case BSIR_BINARY_VAND: B(x & y)
+    case BSIR_BINARY_VXOR: B(x ^ y)
+    case BSIR_BINARY_ADD: B(UT(ux + uy))
+    case BSIR_BINARY_SUB: B(UT(ux - uy))
+    case BSIR_BINARY_MUL: B(UT(ux * uy))
+    case BSIR_BINARY_DIV: B(y == T(0) ? T(0) : (kSigned && sy == ST(-1)) ? T(UT(0) - ux) : T(x / y))
+    case BSIR_BINARY_DIV_UNSIGNED: B(uy == 0 ? UT(0) : UT(ux / uy))
+    case BSIR_BINARY_MAX_SIGNED: B(x > y ? x : y)
+    case BSIR_BINARY_MIN_SIGNED: B(x < y ? x : y)
+    case BSIR_BINARY_MAX_UNSIGNED: B(ux > uy ? x : y)
+    case BSIR_BINARY_MIN_UNSIGNED: B(ux < uy ? x : y)
+    case BSIR_BINARY_MOD: B(y == T(0) ? T(0) : (kSigned && sy == ST(-1)) ? T(0) : T(x % y))
+    case BSIR_BINARY_MODUI: B(uy == 0 ? UT(0) : UT(ux % uy))
+    case BSIR_BINARY_SHLI: B(uy >= UT(kBits) ? UT(0) : UT(ux << uy))
+    case BSIR_BINARY_SHRSI:
+      B(kSigned ? (uy >= UT(kBits) ? ST(sx < 0 ? -1 : 0) : ST(sx >> uy)) : ST(uy >= UT(kBits) ? UT(0) : UT(ux >> uy)))
+    case BSIR_BINARY_SHRUI: B(uy >= UT(kBits) ? UT(0) : UT(ux >> uy))
+    case BSIR_BINARY_CEILDIVSI:
+      B(y == T(0) ? T(0) : T(sx / sy + (((sx % sy) != 0 && ((sx < 0) == (sy < 0))) ? 1 : 0)))
+    case BSIR_BINARY_CEILDIVUI: B(uy == 0 ? UT(0) : UT(ux / uy + (ux % uy ? 1 : 0)))
+    case BSIR_BINARY_FLOORDIVSI:
+      B(y == T(0) ? T(0) : T(sx / sy - (((sx % sy) != 0 && ((sx < 0) != (sy < 0))) ? 1 : 0)))
+    case BSIR_BINARY_POWI: B(ipowi<T>(x, y))
+    default: return false;
+  }
+#undef B
+}
+
+// ------------------------------------------------------------------ storage access by dtype
+template <int DT> struct CType;
+template <> struct CType<BSIR_F32> { using type = float; };
+template <> struct CType<BSIR_F16> { using type = uint16_t; };
+template <> struct CType<BSIR_BF16> { using type = uint16_t; };
+template <> struct CType<BSIR_I8> { using type = int8_t; };
+template <> struct CType<BSIR_I16> { using type = int16_t; };
+template <> struct CType<BSIR_I32> { using type = int32_t; };
+template <> struct CType<BSIR_I64> { using type = int64_t; };
+template <> struct CType<BSIR_U8> { using type = uint8_t; };
+template <> struct CType<BSIR_U16> { using type = uint16_t; };
+template <> struct CType<BSIR_U32> { using type = uint32_t; };
+template <> struct CType<BSIR_U64> { using type = uint64_t; };
+template <> struct CType<BSIR_BOOL> { using type = uint8_t; };
+
+template <int DT> struct IsFloat { static constexpr bool value = DT == BSIR_F32 || DT == BSIR_F16 || DT == BSIR_BF16; };
+
+template <int DT>
+__device__ __forceinline__ float widen(typename CType<DT>::type v) {
+  if constexpr (DT == BSIR_F32) return v;
+  else if constexpr (DT == BSIR_F16) return __half2float(__ushort_as_half(v));
+  else return __uint_as_float(static_cast<uint32_t>(v) << 16);
+}
+template <int DT>
+__device__ __forceinline__ typename CType<DT>::type narrow(float v) {
+  if constexpr (DT == BSIR_F32) return v;
+  else if constexpr (DT == BSIR_F16) return __half_as_ushort(__float2half_rn(v));
+  else return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+struct Operand {
+  const void *p;
+  int64_t s0, s1, s2;
+  unsigned long long scalar;  // value bits when p == nullptr
+};
+struct Shape {
+  int64_t n0, n1, n2, total;
+};
+
+template <int DT>
+__device__ __forceinline__ typename CType<DT>::type fetch(const Operand &o, int64_t i0, int64_t i1, int64_t i2) {
+  using T = typename CType<DT>::type;
+  if (o.p == nullptr) {
+    T v;
+    const unsigned long long s = o.scalar;
+    memcpy(&v, &s, sizeof(T));
+    return v;
+  }
+  return static_cast<const T *>(o.p)[i0 * o.s0 + i1 * o.s1 + i2 * o.s2];
+}
+
+enum { kOpUnary = 0, kOpBinary = 1, kOpCompare = 2, kOpSelect = 3, kOpCopy = 4 };
+
+// ------------------------------------------------------------------ indexed (generic) path
+template <int DT, int KIND>
+__global__ void __launch_bounds__(256) indexed_kernel(int fn, Shape sh, Operand a, Operand b, Operand c, void *out,
+                                                      int64_t os0, int64_t os1, int64_t os2, int *bad_fn) {
+  using T = typename CType<DT>::type;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= sh.total) return;
+  const int64_t i2 = idx % sh.n2;
+  const int64_t t = idx / sh.n2;
+  const int64_t i1 = t % sh.n1;
+  const int64_t i0 = t / sh.n1;
+  const int64_t o = i0 * os0 + i1 * os1 + i2 * os2;
+  bool ok = true;
+  if constexpr (KIND == kOpCopy) {
+    static_cast<T *>(out)[o] = fetch<DT>(a, i0, i1, i2);
+  } else if constexpr (KIND == kOpSelect) {
+    const uint8_t cnd = fetch<BSIR_BOOL>(a, i0, i1, i2);
+    static_cast<T *>(out)[o] = cnd ? fetch<DT>(b, i0, i1, i2) : fetch<DT>(c, i0, i1, i2);
+  } else if constexpr (KIND == kOpCompare) {
+    bool r = false;
+    if constexpr (IsFloat<DT>::value) {
+      const float x = widen<DT>(fetch<DT>(a, i0, i1, i2)), y = widen<DT>(fetch<DT>(b, i0, i1, i2));
+      switch (fn) {
+        case BSIR_CMP_VEQ: r = x == y; break;
+        case BSIR_CMP_VNE: r = !(x == y); break;  // unordered-or-not-equal
+        case BSIR_CMP_VLE: r = x <= y; break;
+        case BSIR_CMP_VLT: r = x < y; break;
+        case BSIR_CMP_VGE: r = x >= y; break;
+        case BSIR_CMP_VGT: r = x > y; break;
+        default: ok = false;
+      }
+    } else {
+      using UT = typename Unsigned<T>::type;
+      const T x = fetch<DT>(a, i0, i1, i2), y = fetch<DT>(b, i0, i1, i2);
+      const UT ux = static_cast<UT>(x), uy = static_cast<UT>(y);
+      switch (fn) {
+        case BSIR_CMP_VEQ: r = x == y; break;
+        case BSIR_CMP_VNE: r = x != y; break;
+        case BSIR_CMP_VLE: r = x <= y; break;
+        case BSIR_CMP_VLT: r = x < y; break;
+        case BSIR_CMP_VGE: r = x >= y; break;
+        case BSIR_CMP_VGT: r = x > y; break;
+        case BSIR_CMP_VULE: r = ux <= uy; break;
+        case BSIR_CMP_VULT: r = ux < uy; break;
+        case BSIR_CMP_VUGE: r = ux >= uy; break;
+        case BSIR_CMP_VUGT: r = ux > uy; break;
+        default: ok = false;
+      }
+    }
+    static_cast<uint8_t *>(out)[o] = r ? 1 : 0;
+  } else if constexpr (IsFloat<DT>::value) {
+    float x = widen<DT>(fetch<DT>(a, i0, i1, i2)), r = 0.0f;
+    if constexpr (KIND == kOpUnary) {
+      ok = unary_f32<1>(fn, &x, &r);
+    } else {
+      float y = widen<DT>(fetch<DT>(b, i0, i1, i2));
+      ok = binary_f32<1>(fn, &x, &y, &r);
+    }
+    static_cast<T *>(out)[o] = narrow<DT>(r);
+  } else {
+    T x = fetch<DT>(a, i0, i1, i2), r = 0;
+    if constexpr (KIND == kOpUnary) {
+      ok = unary_int<T, 1>(fn, &x, &r);
+    } else {
+      T y = fetch<DT>(b, i0, i1, i2);
+      ok = binary_int<T, 1>(fn, &x, &y, &r);
+    }
+    if constexpr (DT == BSIR_BOOL) r &= 1;
+    static_cast<T *>(out)[o] = r;
+  }
+  if (!ok && bad_fn) *bad_fn = 1;
+}
+
+// ------------------------------------------------------------------ streaming path
+constexpr int kStreamThreads = 256;
+constexpr int kStreamUnroll = 4;
+
+// a_mode / b_mode: 0 = tensor (contiguous, 16-byte aligned), 1 = scalar.
+template <int DT, int KIND>
+__global__ void __launch_bounds__(kStreamThreads)
+    stream_kernel(int fn, int64_t n, const void *__restrict__ ap, const void *__restrict__ bp,
+                  unsigned long long a_scalar, unsigned long long b_scalar, void *__restrict__ outp) {
+  using T = typename CType<DT>::type;
+  constexpr int kPerVec = 16 / sizeof(T);
+  const int64_t nvec = n / kPerVec;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * (kStreamThreads * kStreamUnroll) + threadIdx.x;
+
+  Vec16 va[kStreamUnroll], vb[kStreamUnroll];
+  T sa, sb;
+  memcpy(&sa, &a_scalar, sizeof(T));
+  memcpy(&sb, &b_scalar, sizeof(T));
+#pragma unroll
+  for (int u = 0; u < kStreamUnroll; ++u) {
+    const int64_t v = base + static_cast<int64_t>(u) * kStreamThreads;
+    if (v < nvec) {
+      if (ap) va[u] = ld_stream(static_cast<const Vec16 *>(ap) + v);
+      if constexpr (KIND == kOpBinary) {
+        if (bp) vb[u] = ld_stream(static_cast<const Vec16 *>(bp) + v);
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kStreamUnroll; ++u) {
+    const int64_t v = base + static_cast<int64_t>(u) * kStreamThreads;
+    if (v >= nvec) continue;
+    Vec16 vo;
+    if constexpr (KIND == kOpCopy) {
+      vo = va[u];
+    } else if constexpr (IsFloat<DT>::value) {
+      constexpr int kPerWord = FloatTraits<DT>::kPerWord;
+      float x[4 * kPerWord], y[4 * kPerWord], r[4 * kPerWord];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        if (ap) FloatTraits<DT>::unpack(va[u].w[w], x + w * kPerWord);
+        else
+          for (int e = 0; e < kPerWord; ++e) x[w * kPerWord + e] = widen<DT>(sa);
+        if constexpr (KIND == kOpBinary) {
+          if (bp) FloatTraits<DT>::unpack(vb[u].w[w], y + w * kPerWord);
+          else
+            for (int e = 0; e < kPerWord; ++e) y[w * kPerWord + e] = widen<DT>(sb);
+        }
+      }
+      if constexpr (KIND == kOpUnary) unary_f32<4 * kPerWord>(fn, x, r);
+      else binary_f32<4 * kPerWord>(fn, x, y, r);
+#pragma unroll
+      for (int w = 0; w < 4; ++w) vo.w[w] = FloatTraits<DT>::pack(r + w * kPerWord);
+    } else {
+      T x[kPerVec], y[kPerVec], r[kPerVec];
+      if (ap) memcpy(x, &va[u], 16);
+      else
+        for (int e = 0; e < kPerVec; ++e) x[e] = sa;
+      if constexpr (KIND == kOpBinary) {
+        if (bp) memcpy(y, &vb[u], 16);
+        else
+          for (int e = 0; e < kPerVec; ++e) y[e] = sb;
+        binary_int<T, kPerVec>(fn, x, y, r);
+      } else {
+        unary_int<T, kPerVec>(fn, x, r);
+      }
+      if constexpr (DT == BSIR_BOOL) {
+        for (int e = 0; e < kPerVec; ++e) r[e] &= 1;
+      }
+      memcpy(&vo, r, 16);
+    }
+    st_stream(static_cast<Vec16 *>(outp) + v, vo);
+  }
+
+  // ragged tail (< one vector): the first threads of block 0, one element each
+  const int64_t tail0 = nvec * kPerVec;
+  if (blockIdx.x == 0 && tail0 + threadIdx.x < n) {
+    const int64_t i = tail0 + threadIdx.x;
+    const T xa = ap ? static_cast<const T *>(ap)[i] : sa;
+    T ro;
+    if constexpr (KIND == kOpCopy) {
+      ro = xa;
+    } else if constexpr (IsFloat<DT>::value) {
+      float x = widen<DT>(xa), r = 0.0f;
+      if constexpr (KIND == kOpUnary) unary_f32<1>(fn, &x, &r);
+      else {
+        float y = widen<DT>(bp ? static_cast<const T *>(bp)[i] : sb);
+        binary_f32<1>(fn, &x, &y, &r);
+      }
+      ro = narrow<DT>(r);
+    } else {
+      T x = xa, r = 0;
+      if constexpr (KIND == kOpUnary) unary_int<T, 1>(fn, &x, &r);
+      else {
+        T y = bp ? static_cast<const T *>(bp)[i] : sb;
+        binary_int<T, 1>(fn, &x, &y, &r);
+      }
+      if constexpr (DT == BSIR_BOOL) r &= 1;
+      ro = r;
+    }
+    static_cast<T *>(outp)[i] = ro;
+  }
+}
+
+// ------------------------------------------------------------------ host dispatch
+bool fn_is_valid(int kind, int fn, int dt) {
+  const bool f = dtype_is_float(dt);
+  if (kind == kOpUnary) {
+    if (f) {
+      switch (fn) {
+        case BSIR_UNARY_VNOT: case BSIR_UNARY_ABSI: case BSIR_UNARY_ILOGB: return false;
+        default: return (fn >= 0 && fn <= 26) || (fn >= 100 && fn <= 112);
+      }
+    }
+    return fn == BSIR_UNARY_RELU || fn == BSIR_UNARY_VNOT || fn == BSIR_UNARY_ABSI || fn == BSIR_UNARY_ABS ||
+           fn == BSIR_UNARY_SQUARE;
+  }
+  if (kind == kOpBinary) {
+    if (f) {
+      switch (fn) {
+        case BSIR_BINARY_ADD: case BSIR_BINARY_SUB: case BSIR_BINARY_MUL: case BSIR_BINARY_DIV:
+        case BSIR_BINARY_DIVFHP: case BSIR_BINARY_MAXF: case BSIR_BINARY_MINF: case BSIR_BINARY_MAXNUMF:
+        case BSIR_BINARY_MINNUMF: case BSIR_BINARY_POWF: case BSIR_BINARY_POWF_L: case BSIR_BINARY_MOD:
+        case BSIR_BINARY_MODUI: case BSIR_BINARY_LDEXP: case BSIR_BINARY_ATAN2: case BSIR_BINARY_COPYSIGN:
+        case BSIR_BINARY_MAX_SIGNED: case BSIR_BINARY_MIN_SIGNED: case BSIR_BINARY_MAX_UNSIGNED:
+        case BSIR_BINARY_MIN_UNSIGNED:
+          return true;
+        default: return false;
+      }
+    }
+    switch (fn) {
+      case BSIR_BINARY_VOR: case BSIR_BINARY_VAND: case BSIR_BINARY_VXOR: case BSIR_BINARY_ADD:
+      case BSIR_BINARY_SUB: case BSIR_BINARY_MUL: case BSIR_BINARY_DIV: case BSIR_BINARY_DIV_UNSIGNED:
+      case BSIR_BINARY_MAX_SIGNED: case BSIR_BINARY_MIN_SIGNED: case BSIR_BINARY_MAX_UNSIGNED:
+      case BSIR_BINARY_MIN_UNSIGNED: case BSIR_BINARY_MOD: case BSIR_BINARY_MODUI: case BSIR_BINARY_SHLI:
+      case BSIR_BINARY_SHRSI: case BSIR_BINARY_SHRUI: case BSIR_BINARY_CEILDIVSI: case BSIR_BINARY_CEILDIVUI:
+      case BSIR_BINARY_FLOORDIVSI: case BSIR_BINARY_POWI:
+        return true;
+      default: return false;
+    }
+  }
+  if (kind == kOpCompare) return f ? (fn >= BSIR_CMP_VEQ && fn <= BSIR_CMP_VGT) : (fn >= BSIR_CMP_VEQ && fn <= BSIR_CMP_VUGT);
+  return true;
+}
+
+struct Prepared {
+  Shape sh;
+  int64_t os[3];
+  bool out_contig;
+};
+
+int32_t prepare(const char *what, int32_t rank, const int64_t *sizes, const int64_t *out_strides, Prepared *p) {
+  if (rank < 1 || rank > 3) return fail(BSIR_ERR_SHAPE, "%s: rank %d (1..3 supported)", what, rank);
+  if (!sizes) return fail(BSIR_ERR_NULL, "%s: sizes is null", what);
+  int64_t n[3] = {1, 1, 1};
+  int64_t os[3] = {0, 0, 0};
+  for (int i = 0; i < rank; ++i) {
+    if (sizes[i] < 0) return fail(BSIR_ERR_SHAPE, "%s: sizes[%d] = %lld", what, i, (long long)sizes[i]);
+    n[3 - rank + i] = sizes[i];
+  }
+  int64_t cs = 1;
+  bool contig = true;
+  for (int i = rank - 1; i >= 0; --i) {
+    const int64_t s = out_strides ? out_strides[i] : cs;
+    os[3 - rank + i] = s;
+    if (sizes[i] != 1 && s != cs) contig = false;
+    cs *= sizes[i];
+  }
+  p->sh = Shape{n[0], n[1], n[2], n[0] * n[1] * n[2]};
+  p->os[0] = os[0]; p->os[1] = os[1]; p->os[2] = os[2];
+  p->out_contig = contig;
+  return BSIR_OK;
+}
+
+// Right-aligns an operand's strides to rank 3; reports whether it is contiguous over `sizes`.
+Operand make_operand(const bsir_operand *o, int32_t rank, const int64_t *sizes, bool *contig) {
+  Operand r{o->data, 0, 0, 0, o->scalar_bits};
+  int64_t s[3] = {0, 0, 0};
+  int64_t cs = 1;
+  bool c = true;
+  for (int i = rank - 1; i >= 0; --i) {
+    s[3 - rank + i] = o->strides[i];
+    if (sizes[i] != 1 && o->strides[i] != cs) c = false;
+    cs *= sizes[i];
+  }
+  r.s0 = s[0]; r.s1 = s[1]; r.s2 = s[2];
+  *contig = c || o->data == nullptr;
+  return r;
+}
+
+template <int KIND, int DT>
+int32_t launch_typed(const char *what, int fn, const Prepared &p, const Operand &a, bool a_c, const Operand &b,
+                     bool b_c, const Operand &c, void *out, cudaStream_t st) {
+  using T = typename CType<DT>::type;
+  const int64_t n = p.sh.total;
+  if (n == 0) return BSIR_OK;
+  const bool can_stream = (KIND == kOpUnary || KIND == kOpBinary || KIND == kOpCopy) && p.out_contig && a_c &&
+                          (KIND != kOpBinary || b_c) && aligned_to(out, 16) && (!a.p || aligned_to(a.p, 16)) &&
+                          (KIND != kOpBinary || !b.p || aligned_to(b.p, 16)) &&
+                          !(KIND == kOpBinary && !a.p && !b.p) && !(KIND != kOpBinary && !a.p);
+  if constexpr (KIND == kOpUnary || KIND == kOpBinary || KIND == kOpCopy) {
+    if (can_stream) {
+      constexpr int kPerVec = 16 / sizeof(T);
+      const int64_t nvec = n / kPerVec;
+      int64_t blocks = ceil_div(nvec, kStreamThreads * kStreamUnroll);
+      if (blocks < 1) blocks = 1;
+      stream_kernel<DT, KIND><<<static_cast<unsigned>(blocks), kStreamThreads, 0, st>>>(
+          fn, n, a.p, KIND == kOpBinary ? b.p : nullptr, a.scalar, b.scalar, out);
+      count_launch();
+      return check_launch(what);
+    }
+  }
+  const int64_t blocks = ceil_div(n, 256);
+  if (blocks > 0x7fffffffLL) return fail(BSIR_ERR_SHAPE, "%s: %lld elements exceed the indexed path", what, (long long)n);
+  indexed_kernel<DT, KIND><<<static_cast<unsigned>(blocks), 256, 0, st>>>(fn, p.sh, a, b, c, out, p.os[0], p.os[1],
+                                                                         p.os[2], nullptr);
+  count_launch();
+  return check_launch(what);
+}
+
+template <int KIND>
+int32_t launch_by_dtype(const char *what, int fn, int dt, const Prepared &p, const Operand &a, bool a_c,
+                        const Operand &b, bool b_c, const Operand &c, void *out, cudaStream_t st) {
+#define D(code) \
+  case code: return launch_typed<KIND, code>(what, fn, p, a, a_c, b, b_c, c, out, st);
+  switch (dt) {
+    D(BSIR_F32) D(BSIR_F16) D(BSIR_BF16) D(BSIR_I8) D(BSIR_I16) D(BSIR_I32) D(BSIR_I64) D(BSIR_U8) D(BSIR_U16)
+    D(BSIR_U32) D(BSIR_U64) D(BSIR_BOOL)
+    default: return fail(BSIR_ERR_DTYPE, "%s: dtype %d", what, dt);
+  }
+#undef D
+}
+
+// Bitwise ops on float storage act on the raw bits (as the device library's vnot/vand/vor do:
+// bishengir/lib/Template/lib/Vector/Elementwise/EltWise1D.cpp:1300-1316).
+int bits_dtype(int dt) { return dt == BSIR_F32 ? BSIR_U32 : (dt == BSIR_F16 || dt == BSIR_BF16) ? BSIR_U16 : dt; }
+
+bool check_align(const void *p, int dt) { return p == nullptr || aligned_to(p, static_cast<size_t>(dtype_bytes(dt))); }
+
+}  // namespace
+}  // namespace bsir
+
+using namespace bsir;
+
+extern "C" {
+
+int32_t bsir_elemwise_unary(int32_t fn, int32_t dtype, int32_t rank, const int64_t *sizes, const bsir_operand *x,
+                            void *out, const int64_t *out_strides, void *stream) {
+  clear_error();
+  if (!x || !out || !x->data) return fail(BSIR_ERR_NULL, "elemwise_unary: null operand");
+  if (dtype_bytes(dtype) == 0) return fail(BSIR_ERR_DTYPE, "elemwise_unary: dtype %d", dtype);
+  if (fn == BSIR_UNARY_VNOT) dtype = bits_dtype(dtype);
+  if (!fn_is_valid(kOpUnary, fn, dtype))
+    return fail(BSIR_ERR_ATTR, "elemwise_unary: fn %d is not defined for dtype %d", fn, dtype);
+  if (!check_align(x->data, dtype) || !check_align(out, dtype)) return fail(BSIR_ERR_ALIGN, "elemwise_unary: misaligned");
+  Prepared p;
+  if (int32_t rc = prepare("elemwise_unary", rank, sizes, out_strides, &p)) return rc;
+  bool ac;
+  Operand a = make_operand(x, rank, sizes, &ac), none{nullptr, 0, 0, 0, 0};
+  return launch_by_dtype<kOpUnary>("elemwise_unary", fn, dtype, p, a, ac, none, true, none, out, resolve_stream(stream));
+}
+
+int32_t bsir_elemwise_binary(int32_t fn, int32_t dtype, int32_t rank, const int64_t *sizes, const bsir_operand *a,
+                             const bsir_operand *b, void *out, const int64_t *out_strides, void *stream) {
+  clear_error();
+  if (!a || !b || !out) return fail(BSIR_ERR_NULL, "elemwise_binary: null operand");
+  if (dtype_bytes(dtype) == 0) return fail(BSIR_ERR_DTYPE, "elemwise_binary: dtype %d", dtype);
+  if (fn == BSIR_BINARY_VAND || fn == BSIR_BINARY_VOR || fn == BSIR_BINARY_VXOR) dtype = bits_dtype(dtype);
+  if (!fn_is_valid(kOpBinary, fn, dtype))
+    return fail(BSIR_ERR_ATTR, "elemwise_binary: fn %d is not defined for dtype %d", fn, dtype);
+  if (!check_align(a->data, dtype) || !check_align(b->data, dtype) || !check_align(out, dtype))
+    return fail(BSIR_ERR_ALIGN, "elemwise_binary: misaligned");
+  Prepared p;
+  if (int32_t rc = prepare("elemwise_binary", rank, sizes, out_strides, &p)) return rc;
+  bool ac, bc;
+  Operand oa = make_operand(a, rank, sizes, &ac), ob = make_operand(b, rank, sizes, &bc), none{nullptr, 0, 0, 0, 0};
+  return launch_by_dtype<kOpBinary>("elemwise_binary", fn, dtype, p, oa, ac, ob, bc, none, out, resolve_stream(stream));
+}
+
+int32_t bsir_compare(int32_t fn, int32_t dtype, int32_t rank, const int64_t *sizes, const bsir_operand *a,
+                     const bsir_operand *b, void *out, const int64_t *out_strides, void *stream) {
+  clear_error();
+  if (!a || !b || !out) return fail(BSIR_ERR_NULL, "compare: null operand");
+  if (dtype_bytes(dtype) == 0) return fail(BSIR_ERR_DTYPE, "compare: dtype %d", dtype);
+  if (!fn_is_valid(kOpCompare, fn, dtype)) return fail(BSIR_ERR_ATTR, "compare: fn %d for dtype %d", fn, dtype);
+  if (!check_align(a->data, dtype) || !check_align(b->data, dtype)) return fail(BSIR_ERR_ALIGN, "compare: misaligned");
+  Prepared p;
+  if (int32_t rc = prepare("compare", rank, sizes, out_strides, &p)) return rc;
+  bool ac, bc;
+  Operand oa = make_operand(a, rank, sizes, &ac), ob = make_operand(b, rank, sizes, &bc), none{nullptr, 0, 0, 0, 0};
+  return launch_by_dtype<kOpCompare>("compare", fn, dtype, p, oa, ac, ob, bc, none, out, resolve_stream(stream));
+}
+
+int32_t bsir_select(int32_t dtype, int32_t rank, const int64_t *sizes, const bsir_operand *cond, const bsir_operand *a,
+                    const bsir_operand *b, void *out, const int64_t *out_strides, void *stream) {
+  clear_error();
+  if (!cond || !a || !b || !out) return fail(BSIR_ERR_NULL, "select: null operand");
+  if (dtype_bytes(dtype) == 0) return fail(BSIR_ERR_DTYPE, "select: dtype %d", dtype);
+  if (!check_align(a->data, dtype) || !check_align(b->data, dtype) || !check_align(out, dtype))
+    return fail(BSIR_ERR_ALIGN, "select: misaligned");
+  Prepared p;
+  if (int32_t rc = prepare("select", rank, sizes, out_strides, &p)) return rc;
+  bool cc, ac, bc;
+  Operand oc = make_operand(cond, rank, sizes, &cc), oa = make_operand(a, rank, sizes, &ac),
+          ob = make_operand(b, rank, sizes, &bc);
+  // select moves bits: use the same-size unsigned type
+  const int dt = dtype_bytes(dtype) == 8 ? BSIR_U64 : dtype_bytes(dtype) == 4 ? BSIR_U32 : dtype_bytes(dtype) == 2 ? BSIR_U16 : BSIR_U8;
+  return launch_by_dtype<kOpSelect>("select", 0, dt, p, oc, cc, oa, ac, ob, out, resolve_stream(stream));
+}
+
+int32_t bsir_copy(int32_t dtype, int32_t rank, const int64_t *sizes, const void *src, const int64_t *src_strides,
+                  void *dst, const int64_t *dst_strides, void *stream) {
+  clear_error();
+  if (!src || !dst) return fail(BSIR_ERR_NULL, "copy: null pointer");
+  if (dtype_bytes(dtype) == 0) return fail(BSIR_ERR_DTYPE, "copy: dtype %d", dtype);
+  if (!check_align(src, dtype) || !check_align(dst, dtype)) return fail(BSIR_ERR_ALIGN, "copy: misaligned");
+  Prepared p;
+  if (int32_t rc = prepare("copy", rank, sizes, dst_strides, &p)) return rc;
+  bsir_operand s{src, {0, 0, 0}, 0};
+  int64_t cs = 1;
+  for (int i = rank - 1; i >= 0; --i) { s.strides[i] = src_strides ? src_strides[i] : cs; cs *= sizes[i]; }
+  bool ac;
+  Operand oa = make_operand(&s, rank, sizes, &ac), none{nullptr, 0, 0, 0, 0};
+  const int dt = dtype_bytes(dtype) == 8 ? BSIR_U64 : dtype_bytes(dtype) == 4 ? BSIR_U32 : dtype_bytes(dtype) == 2 ? BSIR_U16 : BSIR_U8;
+  return launch_by_dtype<kOpCopy>("copy", 0, dt, p, oa, ac, none, true, none, dst, resolve_stream(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,542 @@
+// fused_rows.cu -- the fused last-axis patterns HFusion's op fusion produces (fusion kind
+// LAST_AXIS_PBR, bishengir/lib/Dialect/HFusion/Transforms/OpFusion/FusibleHelper.cpp:387-397):
+// RMSNorm, softmax and per-token dynamic int8 quantisation.  One pass over HBM: a row is
+// read once into registers with 128-bit loads, reduced with warp shuffles (plus one shared
+// memory hop when a row spans several warps) and written once.
+//
+// Row layout: TPR threads share a row (TPR = 32..1024, a power of two, chosen per shape);
+// thread t of the row owns the 16-byte vectors t, t + TPR, t + 2 TPR, ... (VPT of them), so
+// every load and store instruction of a warp covers 512 contiguous bytes.
+//
+// Shapes the register path cannot hold (very long rows, rows that are not a whole number of
+// 16-byte vectors, unaligned bases) go to the multi-pass kernels at the end of the file, which
+// re-read the row from L2 instead.
+#include <cstdlib>
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace bsir {
+namespace {
+
+constexpr int kMaxWarpsPerRow = 32;
+
+struct RowGeom {
+  int64_t rows;
+  int64_t cols;
+  int64_t nvec;  // 16-byte vectors per row
+  int tpr;       // threads per row
+  int rpc;       // rows per CTA
+};
+
+// Cross-thread reduction inside a row group.  `red` points at this row group's slice
+// (kMaxWarpsPerRow floats) of a shared array used by this reduction only.
+template <class Combine, class Shuffle>
+__device__ __forceinline__ float row_reduce(float v, int tpr, float *red, float identity, Combine combine,
+                                            Shuffle warp_red) {
+  v = warp_red(v);
+  if (tpr == 32) return v;
+  const int lane = threadIdx.x & 31;
+  const int warp_in_row = (threadIdx.x % tpr) >> 5;
+  const int nwarps = tpr >> 5;
+  if (lane == 0) red[warp_in_row] = v;
+  __syncthreads();
+  float p = lane < nwarps ? red[lane] : identity;
+  p = warp_red(p);
+  (void)combine;
+  return p;
+}
+
+__device__ __forceinline__ float warp_red_sum(float v) { return warp_sum(v); }
+__device__ __forceinline__ float warp_red_maxnan(float v) { return warp_max_nan(v); }
+__device__ __forceinline__ float warp_red_maxnum(float v) { return warp_max_num(v); }
+
+// hfusion.round_mode applied to an f32 value (result integral, still f32).
+__device__ __forceinline__ float round_by_mode(float x, int mode) {
+  switch (mode) {
+    case BSIR_ROUND_RINT: return rintf(x);
+    case BSIR_ROUND_ROUND: return roundf(x);
+    case BSIR_ROUND_FLOOR: return floorf(x);
+    case BSIR_ROUND_CEIL: return ceilf(x);
+    case BSIR_ROUND_ODD: {
+      const float t = truncf(x);
+      if (t == x) return x;
+      return (fmodf(t, 2.0f) == 0.0f) ? t + (x > 0.0f ? 1.0f : -1.0f) : t;
+    }
+    default: return truncf(x);
+  }
+}
+// integral f32 -> saturated int8, NaN -> 0
+__device__ __forceinline__ int sat_i8(float r) {
+  int i = __float2int_rz(r);  // saturates at the int32 range, NaN -> 0
+  return max(-128, min(127, i));
+}
+
+// ------------------------------------------------------------------ per-token int8 quantisation
+// scale = max|x| / 127 (IEEE divide); q = cast{round_mode, saturate}(x / scale).
+// Rows whose max|x| is 0, inf or NaN quantise to all zeros: every quotient is then 0/0, x/inf
+// or involves a NaN, and NaN saturates to 0.
+//
+// For bf16 rows with a scale in [2^-60, 2^60] the per-element divide is replaced by the
+// reciprocal r = RN(1/scale) and one correction step, q0 = x r, q = fma(fma(-q0, scale, x), r, q0):
+// for every bf16 x with |x / scale| <= 127.5 this rounds to the same integer as the IEEE
+// quotient (checked exhaustively over all bf16 x for thousands of scales by the CPU tests).
+template <int DT, int VPT>
+__global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant_rows_kernel(RowGeom g, const void *__restrict__ xp, int64_t x_stride,
+                                                          int8_t *__restrict__ qp, int64_t q_stride,
+                                                          float *__restrict__ scale_out, int round_mode) {
+  constexpr int kPerWord = FloatTraits<DT>::kPerWord;
+  constexpr int kPerVec = 4 * kPerWord;
+  __shared__ float red[kMaxWarpsPerRow * 32];
+  const int sub = threadIdx.x / g.tpr;
+  const int t = threadIdx.x % g.tpr;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * g.rpc + sub;
+  const bool row_ok = row < g.rows;
+  using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
+  const E *xrow = static_cast<const E *>(xp) + (row_ok ? row : 0) * x_stride;
+
+  Vec16 v[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
+    if (row_ok && vi < g.nvec) v[i] = ld_stream(reinterpret_cast<const Vec16 *>(xrow) + vi);
+    else v[i] = Vec16{{0u, 0u, 0u, 0u}};
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      float e[kPerWord];
+      FloatTraits<DT>::unpack(v[i].w[w], e);
+#pragma unroll
+      for (int k = 0; k < kPerWord; ++k) amax = maximumf(amax, fabsf(e[k]));
+    }
+  }
+  amax = row_reduce(amax, g.tpr, red + sub * kMaxWarpsPerRow, 0.0f, 0, warp_red_maxnan);
+  const float scale = __fdiv_rn(amax, 127.0f);
+  if (row_ok && t == 0) scale_out[row] = scale;
+  if (!row_ok) return;
+
+  const bool degenerate = !(amax > 0.0f && amax < __int_as_float(0x7f800000));
+  const bool fast = DT == BSIR_BF16 && round_mode == BSIR_ROUND_RINT && scale > 8.6736174e-19f && scale < 1.1529215e18f;
+  const float rcp = __frcp_rn(scale);
+  int8_t *qrow = qp + row * q_stride;
+
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
+    if (vi >= g.nvec) continue;
+    uint32_t bytes[kPerVec / 4];
+#pragma unroll
+    for (int w4 = 0; w4 < kPerVec / 4; ++w4) {
+      // four consecutive elements -> one packed word of int8
+      float e[4];
+      if constexpr (kPerWord == 2) {
+        FloatTraits<DT>::unpack(v[i].w[2 * w4], e);
+        FloatTraits<DT>::unpack(v[i].w[2 * w4 + 1], e + 2);
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) e[k] = __uint_as_float(v[i].w[k]);
+      }
+      uint32_t b[4];
+      if (degenerate) {
+        b[0] = b[1] = b[2] = b[3] = 0u;
+      } else if (fast) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float q0 = __fmul_rn(e[k], rcp);
+          const float q1 = __fmaf_rn(__fmaf_rn(-q0, scale, e[k]), rcp, q0);
+          // |q1| < 128: adding 1.5 * 2^23 rounds to nearest even and leaves the integer in the low bits
+          b[k] = __float_as_uint(__fadd_rn(q1, 12582912.0f));
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) b[k] = static_cast<uint32_t>(sat_i8(round_by_mode(__fdiv_rn(e[k], scale), round_mode)));
+      }
+      bytes[w4] = (b[0] & 0xffu) | ((b[1] & 0xffu) << 8) | ((b[2] & 0xffu) << 16) | (b[3] << 24);
+    }
+    if constexpr (kPerVec == 8) {
+      *reinterpret_cast<uint2 *>(qrow + vi * 8) = make_uint2(bytes[0], bytes[1]);
+    } else {
+      *reinterpret_cast<uint32_t *>(qrow + vi * 4) = bytes[0];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// y = cast_rint(gamma32 * (rstd * x32)), rstd = 1 / sqrt(sum(x32^2) * (1/cols) + eps), in the
+// op order of the reference IR
+// (test/bishengir-compile/hfusion/compile-rms-norm-fp16-split-n.mlir:27-61).
+template <int DT, int VPT>
+__global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) rmsnorm_rows_kernel(RowGeom g, const void *__restrict__ xp, int64_t x_stride,
+                                                            const void *__restrict__ gammap, float eps, float avg,
+                                                            void *__restrict__ yp, int64_t y_stride,
+                                                            void *__restrict__ rstd_out) {
+  constexpr int kPerWord = FloatTraits<DT>::kPerWord;
+  __shared__ float red[kMaxWarpsPerRow * 32];
+  using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
+  const int sub = threadIdx.x / g.tpr;
+  const int t = threadIdx.x % g.tpr;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * g.rpc + sub;
+  const bool row_ok = row < g.rows;
+  const E *xrow = static_cast<const E *>(xp) + (row_ok ? row : 0) * x_stride;
+
+  Vec16 v[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
+    if (row_ok && vi < g.nvec) v[i] = ld_stream(reinterpret_cast<const Vec16 *>(xrow) + vi);
+    else v[i] = Vec16{{0u, 0u, 0u, 0u}};
+  }
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      float e[kPerWord];
+      FloatTraits<DT>::unpack(v[i].w[w], e);
+#pragma unroll
+      for (int k = 0; k < kPerWord; ++k) ss = __fmaf_rn(e[k], e[k], ss);
+    }
+  }
+  ss = row_reduce(ss, g.tpr, red + sub * kMaxWarpsPerRow, 0.0f, 0, warp_red_sum);
+  const float mean = __fmul_rn(ss, avg);
+  const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
+  if (!row_ok) return;
+  if (rstd_out && t == 0) {
+    float r1[kPerWord];
+    r1[0] = rstd;
+    if constexpr (kPerWord == 2) r1[1] = 0.0f;
+    const uint32_t packed = FloatTraits<DT>::pack(r1);
+    if constexpr (DT == BSIR_F32) static_cast<float *>(rstd_out)[row] = rstd;
+    else static_cast<uint16_t *>(rstd_out)[row] = static_cast<uint16_t>(packed & 0xffffu);
+  }
+  E *yrow = static_cast<E *>(yp) + row * y_stride;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
+    if (vi >= g.nvec) continue;
+    const Vec16 gv = *(reinterpret_cast<const Vec16 *>(gammap) + vi);  // gamma stays in L1/L2
+    Vec16 o;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      float e[kPerWord], ge[kPerWord], r[kPerWord];
+      FloatTraits<DT>::unpack(v[i].w[w], e);
+      FloatTraits<DT>::unpack(gv.w[w], ge);
+#pragma unroll
+      for (int k = 0; k < kPerWord; ++k) r[k] = __fmul_rn(ge[k], __fmul_rn(rstd, e[k]));
+      o.w[w] = FloatTraits<DT>::pack(r);
+    }
+    st_stream(reinterpret_cast<Vec16 *>(yrow) + vi, o);
+  }
+}
+
+// ------------------------------------------------------------------ softmax
+// m = max over non-NaN x; e = exp(x - m); y = cast_rint(e / sum e)
+// (test/Dialect/Analysis/VFFusion/MaxParallelKind/softmax_small_shape.mlir:86-117).
+// exp runs on the special-function unit (ex2.approx of (x - m) * log2 e, relative error below
+// 3e-6 for the arguments a softmax sees); the division by the row sum is a reciprocal with one
+// correction step.
+template <int DT, int VPT>
+__global__ void __launch_bounds__(VPT * (DT == BSIR_F32 ? 4 : 8) > 32 ? 256 : 1024) softmax_rows_kernel(RowGeom g, const void *__restrict__ xp, int64_t x_stride,
+                                                            void *__restrict__ yp, int64_t y_stride) {
+  constexpr int kPerWord = FloatTraits<DT>::kPerWord;
+  constexpr int kPerVec = 4 * kPerWord;
+  __shared__ float red_max[kMaxWarpsPerRow * 32];
+  __shared__ float red_sum[kMaxWarpsPerRow * 32];
+  using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
+  const int sub = threadIdx.x / g.tpr;
+  const int t = threadIdx.x % g.tpr;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * g.rpc + sub;
+  const bool row_ok = row < g.rows;
+  const E *xrow = static_cast<const E *>(xp) + (row_ok ? row : 0) * x_stride;
+  const float ninf = __int_as_float(0xff800000);
+
+  Vec16 v[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
+    if (row_ok && vi < g.nvec) v[i] = ld_stream(reinterpret_cast<const Vec16 *>(xrow) + vi);
+    else v[i] = Vec16{{0u, 0u, 0u, 0u}};
+  }
+  float e[VPT * kPerVec];
+  float m = ninf;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const bool live = (t + static_cast<int64_t>(i) * g.tpr) < g.nvec;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      FloatTraits<DT>::unpack(v[i].w[w], e + i * kPerVec + w * kPerWord);
+#pragma unroll
+      for (int k = 0; k < kPerWord; ++k) {
+        if (!live) e[i * kPerVec + w * kPerWord + k] = ninf;  // padding: exp -> 0, ignored by the max
+        m = fmaxf(m, e[i * kPerVec + w * kPerWord + k]);      // fmaxf skips NaN = the NaN -> -inf mask
+      }
+    }
+  }
+  m = row_reduce(m, g.tpr, red_max + sub * kMaxWarpsPerRow, ninf, 0, warp_red_maxnum);
+  float s = 0.0f;
+  const float kLog2e = 1.4426950408889634f;
+#pragma unroll
+  for (int j = 0; j < VPT * kPerVec; ++j) {
+    const float d = __fmul_rn(__fsub_rn(e[j], m), kLog2e);
+    float ex;
+    asm("ex2.approx.f32 %0, %1;" : "=f"(ex) : "f"(d));
+    e[j] = ex;
+    s += ex;
+  }
+  // padding lanes hold exp(-inf - m): 0 for any m except -inf, where the live lanes are NaN too.
+  s = row_reduce(s, g.tpr, red_sum + sub * kMaxWarpsPerRow, 0.0f, 0, warp_red_sum);
+  if (!row_ok) return;
+  const float rcp = __frcp_rn(s);
+  E *yrow = static_cast<E *>(yp) + row * y_stride;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
+    if (vi >= g.nvec) continue;
+    Vec16 o;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      float r[kPerWord];
+#pragma unroll
+      for (int k = 0; k < kPerWord; ++k) {
+        const float ev = e[i * kPerVec + w * kPerWord + k];
+        const float q0 = __fmul_rn(ev, rcp);
+        r[k] = __fmaf_rn(__fmaf_rn(-q0, s, ev), rcp, q0);
+      }
+      o.w[w] = FloatTraits<DT>::pack(r);
+    }
+    st_stream(reinterpret_cast<Vec16 *>(yrow) + vi, o);
+  }
+}
+
+// ------------------------------------------------------------------ multi-pass fallbacks
+// One CTA per row, any cols / stride / alignment; the row is re-read from L2 on each pass.
+template <int DT>
+__device__ __forceinline__ float load_elem(const void *p, int64_t i) {
+  if constexpr (DT == BSIR_F32) return static_cast<const float *>(p)[i];
+  else if constexpr (DT == BSIR_F16) return __half2float(__ushort_as_half(static_cast<const uint16_t *>(p)[i]));
+  else return __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t *>(p)[i]) << 16);
+}
+template <int DT>
+__device__ __forceinline__ void store_elem(void *p, int64_t i, float v) {
+  if constexpr (DT == BSIR_F32) static_cast<float *>(p)[i] = v;
+  else if constexpr (DT == BSIR_F16) static_cast<uint16_t *>(p)[i] = __half_as_ushort(__float2half_rn(v));
+  else static_cast<uint16_t *>(p)[i] = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+}
+
+template <class WarpRed>
+__device__ __forceinline__ float block_reduce(float v, float *red, float identity, WarpRed warp_red) {
+  v = warp_red(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  __syncthreads();  // red may still be read from the previous reduction
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float p = lane < nw ? red[lane] : identity;
+  return warp_red(p);
+}
+
+enum { kRowQuant = 0, kRowRms = 1, kRowSoftmax = 2 };
+
+template <int DT, int OP>
+__global__ void __launch_bounds__(256) rows_multipass_kernel(int64_t rows, int64_t cols, const void *__restrict__ xp,
+                                                             int64_t x_stride, const void *__restrict__ gammap,
+                                                             float eps, float avg, void *__restrict__ yp,
+                                                             int64_t y_stride, void *__restrict__ aux, int round_mode) {
+  __shared__ float red[32];
+  const int64_t row = blockIdx.x;
+  if (row >= rows) return;
+  const int64_t xo = row * x_stride, yo = row * y_stride;
+  if constexpr (OP == kRowQuant) {
+    float amax = 0.0f;
+    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) amax = maximumf(amax, fabsf(load_elem<DT>(xp, xo + j)));
+    amax = block_reduce(amax, red, 0.0f, warp_red_maxnan);
+    const float scale = __fdiv_rn(amax, 127.0f);
+    if (threadIdx.x == 0) static_cast<float *>(aux)[row] = scale;
+    const bool degenerate = !(amax > 0.0f && amax < __int_as_float(0x7f800000));
+    int8_t *q = static_cast<int8_t *>(yp) + yo;
+    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x)
+      q[j] = degenerate ? 0 : static_cast<int8_t>(sat_i8(round_by_mode(__fdiv_rn(load_elem<DT>(xp, xo + j), scale), round_mode)));
+  } else if constexpr (OP == kRowRms) {
+    float ss = 0.0f;
+    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) {
+      const float v = load_elem<DT>(xp, xo + j);
+      ss = __fmaf_rn(v, v, ss);
+    }
+    ss = block_reduce(ss, red, 0.0f, warp_red_sum);
+    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(ss, avg), eps)));
+    if (aux && threadIdx.x == 0) store_elem<DT>(aux, row, rstd);
+    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x)
+      store_elem<DT>(yp, yo + j, __fmul_rn(load_elem<DT>(gammap, j), __fmul_rn(rstd, load_elem<DT>(xp, xo + j))));
+  } else {
+    const float ninf = __int_as_float(0xff800000);
+    float m = ninf;
+    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) m = fmaxf(m, load_elem<DT>(xp, xo + j));
+    m = block_reduce(m, red, ninf, warp_red_maxnum);
+    float s = 0.0f;
+    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x) s += expf(__fsub_rn(load_elem<DT>(xp, xo + j), m));
+    s = block_reduce(s, red, 0.0f, warp_red_sum);
+    for (int64_t j = threadIdx.x; j < cols; j += blockDim.x)
+      store_elem<DT>(yp, yo + j, __fdiv_rn(expf(__fsub_rn(load_elem<DT>(xp, xo + j), m)), s));
+  }
+}
+
+// ------------------------------------------------------------------ host side
+int env_int(const char *name, int dflt) {
+  const char *s = std::getenv(name);
+  return s && *s ? std::atoi(s) : dflt;
+}
+
+// Picks threads-per-row and vectors-per-thread: the fewest threads (>= 32, power of two) that
+// keep a thread at or under `max_vpt` vectors.  Returns false when the row does not fit.
+bool pick_geometry(int64_t rows, int64_t cols, int elem_bytes, int max_vpt, int min_tpr, RowGeom *g, int *vpt) {
+  const int per_vec = 16 / elem_bytes;
+  if (cols <= 0 || cols % per_vec) return false;
+  const int64_t nvec = cols / per_vec;
+  int tpr = min_tpr;
+  while (tpr < 1024 && ceil_div(nvec, tpr) > max_vpt) tpr <<= 1;
+  int64_t need = ceil_div(nvec, tpr);
+  // register budget: 16 vectors per thread only up to 256 threads per CTA, 8 up to 512, 4 at 1024
+  while (tpr < 1024 && ((tpr > 256 && need > 8) || (tpr > 128 && need > 16))) { tpr <<= 1; need = ceil_div(nvec, tpr); }
+  if (need > max_vpt || (tpr == 1024 && need > 4) || (tpr == 512 && need > 8)) return false;
+  int v = 1;
+  while (v < need) v <<= 1;
+  // prefer more threads over idle vector slots when a thread would hold mostly padding
+  g->rows = rows; g->cols = cols; g->nvec = nvec; g->tpr = tpr;
+  const int cta = tpr < 128 ? 128 : tpr;
+  g->rpc = cta / tpr;
+  *vpt = v;
+  return true;
+}
+
+bool rows_vector_ok(const void *p, int64_t stride_elems, int elem_bytes) {
+  return aligned_to(p, 16) && (stride_elems * elem_bytes) % 16 == 0;
+}
+
+#define DISPATCH_VPT(vpt, ...)                         \
+  switch (vpt) {                                       \
+    case 1: { constexpr int V = 1; __VA_ARGS__; break; }   \
+    case 2: { constexpr int V = 2; __VA_ARGS__; break; }   \
+    case 4: { constexpr int V = 4; __VA_ARGS__; break; }   \
+    case 8: { constexpr int V = 8; __VA_ARGS__; break; }   \
+    default: { constexpr int V = 16; __VA_ARGS__; break; } \
+  }
+#define DISPATCH_VPT_LE8(vpt, ...)                     \
+  switch (vpt) {                                       \
+    case 1: { constexpr int V = 1; __VA_ARGS__; break; }   \
+    case 2: { constexpr int V = 2; __VA_ARGS__; break; }   \
+    case 4: { constexpr int V = 4; __VA_ARGS__; break; }   \
+    default: { constexpr int V = 8; __VA_ARGS__; break; }  \
+  }
+#define DISPATCH_FLOAT_DT(dt, ...)                                 \
+  switch (dt) {                                                    \
+    case BSIR_F32: { constexpr int D = BSIR_F32; __VA_ARGS__; break; }   \
+    case BSIR_F16: { constexpr int D = BSIR_F16; __VA_ARGS__; break; }   \
+    default: { constexpr int D = BSIR_BF16; __VA_ARGS__; break; }        \
+  }
+
+int32_t check_rows_args(const char *what, int32_t dtype, int64_t rows, int64_t cols, const void *x, int64_t xs,
+                        const void *y, int64_t ys) {
+  if (!dtype_is_float(dtype)) return fail(BSIR_ERR_DTYPE, "%s: dtype %d (f32, f16 or bf16 required)", what, dtype);
+  if (rows < 0 || cols < 0) return fail(BSIR_ERR_SHAPE, "%s: rows=%lld cols=%lld", what, (long long)rows, (long long)cols);
+  if (rows == 0) return BSIR_OK;
+  if (!x || !y) return fail(BSIR_ERR_NULL, "%s: null pointer", what);
+  if (xs < cols || ys < cols) return fail(BSIR_ERR_STRIDE, "%s: row stride smaller than cols", what);
+  if (rows > 0x7fffffffLL) return fail(BSIR_ERR_SHAPE, "%s: too many rows", what);
+  return BSIR_OK;
+}
+
+}  // namespace
+}  // namespace bsir
+
+using namespace bsir;
+
+extern "C" {
+
+int32_t bsir_quant_per_token_i8(int32_t dtype, int32_t round_mode, int64_t rows, int64_t cols, const void *x,
+                                int64_t x_row_stride, int8_t *q, int64_t q_row_stride, float *scale, void *stream) {
+  clear_error();
+  if (int32_t rc = check_rows_args("quant_per_token_i8", dtype, rows, cols, x, x_row_stride, q, q_row_stride)) return rc;
+  if (round_mode < BSIR_ROUND_RINT || round_mode > BSIR_ROUND_TRUNCWITHOVERFLOW)
+    return fail(BSIR_ERR_ATTR, "quant_per_token_i8: round_mode %d", round_mode);
+  if (rows == 0) return BSIR_OK;
+  if (!scale) return fail(BSIR_ERR_NULL, "quant_per_token_i8: scale is null");
+  const int eb = dtype_bytes(dtype);
+  if (!aligned_to(x, eb) || !aligned_to(scale, 4)) return fail(BSIR_ERR_ALIGN, "quant_per_token_i8: misaligned");
+  cudaStream_t st = resolve_stream(stream);
+  RowGeom g;
+  int vpt = 0;
+  const int per_vec = 16 / eb;
+  const bool vec_ok = cols > 0 && rows_vector_ok(x, x_row_stride, eb) && aligned_to(q, per_vec) && q_row_stride % per_vec == 0 &&
+                      pick_geometry(rows, cols, eb, 16, env_int("BSIR_QUANT_TPR", 32), &g, &vpt);
+  if (vec_ok) {
+    const unsigned blocks = static_cast<unsigned>(ceil_div(rows, g.rpc));
+    const unsigned threads = static_cast<unsigned>(g.tpr * g.rpc);
+    DISPATCH_FLOAT_DT(dtype, DISPATCH_VPT(vpt, (quant_rows_kernel<D, V><<<blocks, threads, 0, st>>>(
+                                                    g, x, x_row_stride, q, q_row_stride, scale, round_mode))));
+  } else {
+    DISPATCH_FLOAT_DT(dtype, (rows_multipass_kernel<D, kRowQuant><<<static_cast<unsigned>(rows), 256, 0, st>>>(
+                                 rows, cols, x, x_row_stride, nullptr, 0.0f, 0.0f, q, q_row_stride, scale, round_mode)));
+  }
+  count_launch();
+  return check_launch("quant_per_token_i8");
+}
+
+int32_t bsir_rms_norm(int32_t dtype, int64_t rows, int64_t cols, const void *x, int64_t x_row_stride,
+                      const void *gamma, float eps, void *y, int64_t y_row_stride, void *rstd_out, void *stream) {
+  clear_error();
+  if (int32_t rc = check_rows_args("rms_norm", dtype, rows, cols, x, x_row_stride, y, y_row_stride)) return rc;
+  if (rows == 0) return BSIR_OK;
+  if (!gamma && cols > 0) return fail(BSIR_ERR_NULL, "rms_norm: gamma is null");
+  const int eb = dtype_bytes(dtype);
+  if (!aligned_to(x, eb) || !aligned_to(y, eb) || !aligned_to(gamma, eb) || !aligned_to(rstd_out, eb))
+    return fail(BSIR_ERR_ALIGN, "rms_norm: misaligned");
+  cudaStream_t st = resolve_stream(stream);
+  // 1.0 / float(cols), computed in f32 like the arith.divf of the reference IR
+  const float avg = 1.0f / static_cast<float>(static_cast<uint32_t>(cols));
+  RowGeom g;
+  int vpt = 0;
+  const bool vec_ok = cols > 0 && rows_vector_ok(x, x_row_stride, eb) && rows_vector_ok(y, y_row_stride, eb) &&
+                      aligned_to(gamma, 16) && pick_geometry(rows, cols, eb, 16, env_int("BSIR_RMS_TPR", 32), &g, &vpt);
+  if (vec_ok) {
+    const unsigned blocks = static_cast<unsigned>(ceil_div(rows, g.rpc));
+    const unsigned threads = static_cast<unsigned>(g.tpr * g.rpc);
+    DISPATCH_FLOAT_DT(dtype, DISPATCH_VPT(vpt, (rmsnorm_rows_kernel<D, V><<<blocks, threads, 0, st>>>(
+                                                    g, x, x_row_stride, gamma, eps, avg, y, y_row_stride, rstd_out))));
+  } else {
+    DISPATCH_FLOAT_DT(dtype, (rows_multipass_kernel<D, kRowRms><<<static_cast<unsigned>(rows), 256, 0, st>>>(
+                                 rows, cols, x, x_row_stride, gamma, eps, avg, y, y_row_stride, rstd_out, 0)));
+  }
+  count_launch();
+  return check_launch("rms_norm");
+}
+
+int32_t bsir_softmax(int32_t dtype, int64_t rows, int64_t cols, const void *x, int64_t x_row_stride, void *y,
+                     int64_t y_row_stride, void *stream) {
+  clear_error();
+  if (int32_t rc = check_rows_args("softmax", dtype, rows, cols, x, x_row_stride, y, y_row_stride)) return rc;
+  if (rows == 0 || cols == 0) return BSIR_OK;
+  const int eb = dtype_bytes(dtype);
+  if (!aligned_to(x, eb) || !aligned_to(y, eb)) return fail(BSIR_ERR_ALIGN, "softmax: misaligned");
+  cudaStream_t st = resolve_stream(stream);
+  RowGeom g;
+  int vpt = 0;
+  // exp values live in registers: at most 32 per thread
+  const int max_vpt = eb == 4 ? 8 : 4;
+  const bool vec_ok = rows_vector_ok(x, x_row_stride, eb) && rows_vector_ok(y, y_row_stride, eb) &&
+                      pick_geometry(rows, cols, eb, max_vpt, env_int("BSIR_SOFTMAX_TPR", 32), &g, &vpt);
+  if (vec_ok) {
+    const unsigned blocks = static_cast<unsigned>(ceil_div(rows, g.rpc));
+    const unsigned threads = static_cast<unsigned>(g.tpr * g.rpc);
+    DISPATCH_FLOAT_DT(dtype, DISPATCH_VPT_LE8(vpt, (softmax_rows_kernel<D, V><<<blocks, threads, 0, st>>>(
+                                                        g, x, x_row_stride, y, y_row_stride))));
+  } else {
+    DISPATCH_FLOAT_DT(dtype, (rows_multipass_kernel<D, kRowSoftmax><<<static_cast<unsigned>(rows), 256, 0, st>>>(
+                                 rows, cols, x, x_row_stride, nullptr, 0.0f, 0.0f, y, y_row_stride, nullptr, 0)));
+  }
+  count_launch();
+  return check_launch("softmax");
+}
+
+}  // extern "C"

@@ -1,0 +1,617 @@
+// reduce.cu -- linalg.reduce / hivm.hir.vreduce over one axis of a 2-D view and
+// hfusion.reduce_with_index (argmax / argmin) over the last axis.
+//
+// Combiners are the ones the reference's CPU lowering emits
+// (bishengir/lib/ExecutionEngine/ConvertHIVMToUpstream.cpp:573-753): addf/addi, mulf/muli,
+// maximumf/minimumf (NaN-propagating) and maxsi/minsi/maxui/minui, xori/ori/andi; dst is
+// write-only and starts from the identity (bishengir/lib/Dialect/HIVM/IR/HIVMVectorOps.cpp:571-640).
+// Float sums are accumulated in f32 (f16 sums are promoted by the reference too:
+// bishengir/lib/Dialect/HFusion/Transforms/Normalize.cpp:7679-7716) in a tree order, so they
+// match the sequential CPU order only to rounding; everything else is order-independent.
+#include <climits>
+#include <type_traits>
+
+#include "common.cuh"
+
+namespace bsir {
+namespace {
+
+// ------------------------------------------------------------------ generic reductions
+template <int DT> struct Acc;  // accumulator type per storage type
+template <> struct Acc<BSIR_F32> { using type = float; using elem = float; };
+template <> struct Acc<BSIR_F16> { using type = float; using elem = uint16_t; };
+template <> struct Acc<BSIR_BF16> { using type = float; using elem = uint16_t; };
+template <> struct Acc<BSIR_I8> { using type = int32_t; using elem = int8_t; };
+template <> struct Acc<BSIR_I16> { using type = int32_t; using elem = int16_t; };
+template <> struct Acc<BSIR_I32> { using type = int32_t; using elem = int32_t; };
+template <> struct Acc<BSIR_I64> { using type = long long; using elem = int64_t; };
+template <> struct Acc<BSIR_U8> { using type = uint32_t; using elem = uint8_t; };
+template <> struct Acc<BSIR_U16> { using type = uint32_t; using elem = uint16_t; };
+template <> struct Acc<BSIR_U32> { using type = uint32_t; using elem = uint32_t; };
+template <> struct Acc<BSIR_U64> { using type = unsigned long long; using elem = uint64_t; };
+template <> struct Acc<BSIR_BOOL> { using type = uint32_t; using elem = uint8_t; };
+
+template <int DT>
+__device__ __forceinline__ typename Acc<DT>::type load_acc(const void *p, int64_t i) {
+  using E = typename Acc<DT>::elem;
+  const E v = static_cast<const E *>(p)[i];
+  if constexpr (DT == BSIR_F16) return __half2float(__ushort_as_half(v));
+  else if constexpr (DT == BSIR_BF16) return __uint_as_float(static_cast<uint32_t>(v) << 16);
+  else return static_cast<typename Acc<DT>::type>(v);
+}
+template <int DT>
+__device__ __forceinline__ void store_acc(void *p, int64_t i, typename Acc<DT>::type v) {
+  using E = typename Acc<DT>::elem;
+  if constexpr (DT == BSIR_F16) static_cast<E *>(p)[i] = __half_as_ushort(__float2half_rn(v));
+  else if constexpr (DT == BSIR_BF16) static_cast<E *>(p)[i] = __bfloat16_as_ushort(__float2bfloat16_rn(v));
+  else if constexpr (DT == BSIR_BOOL) static_cast<E *>(p)[i] = static_cast<E>(v & 1u);
+  else static_cast<E *>(p)[i] = static_cast<E>(v);
+}
+
+template <int DT, int KIND>
+__device__ __forceinline__ typename Acc<DT>::type identity() {
+  using A = typename Acc<DT>::type;
+  using E = typename Acc<DT>::elem;
+  if constexpr (std::is_same<A, float>::value) {
+    if (KIND == BSIR_REDUCE_SUM) return 0.0f;
+    if (KIND == BSIR_REDUCE_PROD) return 1.0f;
+    if (KIND == BSIR_REDUCE_MAX || KIND == BSIR_REDUCE_ANY) return __int_as_float(0xff800000);
+    return __int_as_float(0x7f800000);
+  } else {
+    constexpr bool kSigned = std::is_signed<E>::value;
+    constexpr int kBits = DT == BSIR_BOOL ? 1 : 8 * sizeof(E);
+    switch (KIND) {
+      case BSIR_REDUCE_SUM: case BSIR_REDUCE_XORI: case BSIR_REDUCE_ORI: return A(0);
+      case BSIR_REDUCE_PROD: return A(1);
+      case BSIR_REDUCE_MAX: case BSIR_REDUCE_ANY:
+        return kSigned ? static_cast<A>(-(static_cast<long long>(1) << (kBits - 1))) : A(0);
+      case BSIR_REDUCE_MIN: case BSIR_REDUCE_ALL:
+        return kSigned ? static_cast<A>((static_cast<unsigned long long>(1) << (kBits - 1)) - 1)
+                       : static_cast<A>(kBits == 64 ? ~0ull : ((1ull << (kBits % 64)) - 1));
+      default: return static_cast<A>(~0ull);  // andi
+    }
+  }
+}
+
+template <int KIND, typename A>
+__device__ __forceinline__ A combine(A a, A b) {
+  if constexpr (std::is_same<A, float>::value) {
+    if (KIND == BSIR_REDUCE_SUM) return a + b;
+    if (KIND == BSIR_REDUCE_PROD) return a * b;
+    if (KIND == BSIR_REDUCE_MAX || KIND == BSIR_REDUCE_ANY) return maximumf(a, b);
+    return minimumf(a, b);
+  } else {
+    using U = typename std::make_unsigned<A>::type;
+    switch (KIND) {
+      case BSIR_REDUCE_SUM: return static_cast<A>(static_cast<U>(a) + static_cast<U>(b));
+      case BSIR_REDUCE_PROD: return static_cast<A>(static_cast<U>(a) * static_cast<U>(b));
+      case BSIR_REDUCE_MAX: case BSIR_REDUCE_ANY: return a > b ? a : b;
+      case BSIR_REDUCE_MIN: case BSIR_REDUCE_ALL: return a < b ? a : b;
+      case BSIR_REDUCE_XORI: return a ^ b;
+      case BSIR_REDUCE_ORI: return a | b;
+      default: return a & b;
+    }
+  }
+}
+
+template <typename A>
+__device__ __forceinline__ A shfl_xor_any(A v, int o) {
+  if constexpr (sizeof(A) == 8) {
+    unsigned long long u;
+    memcpy(&u, &v, 8);
+    u = __shfl_xor_sync(0xffffffffu, u, o);
+    memcpy(&v, &u, 8);
+    return v;
+  } else {
+    return __shfl_xor_sync(0xffffffffu, v, o);
+  }
+}
+
+// Last axis: `tpr` threads (power of two, 32..256) cooperate on a row.
+template <int DT, int KIND>
+__global__ void __launch_bounds__(256) reduce_last_kernel(int64_t rows, int64_t cols, const void *__restrict__ src,
+                                                          int64_t row_stride, void *__restrict__ dst, int tpr) {
+  using A = typename Acc<DT>::type;
+  __shared__ unsigned long long red[8][8];
+  const int rpc = 256 / tpr;
+  const int sub = threadIdx.x / tpr, t = threadIdx.x % tpr;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * rpc + sub;
+  A acc = identity<DT, KIND>();
+  if (row < rows) {
+    const int64_t base = row * row_stride;
+    for (int64_t j = t; j < cols; j += tpr) acc = combine<KIND, A>(load_acc<DT>(src, base + j), acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc = combine<KIND, A>(acc, shfl_xor_any(acc, o));
+  if (tpr > 32) {
+    const int lane = threadIdx.x & 31, w = t >> 5, nw = tpr >> 5;
+    unsigned long long bits = 0;
+    memcpy(&bits, &acc, sizeof(A));
+    if (lane == 0) red[sub][w] = bits;
+    __syncthreads();
+    A p = identity<DT, KIND>();
+    if (lane < nw) { bits = red[sub][lane]; memcpy(&p, &bits, sizeof(A)); }
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) p = combine<KIND, A>(p, shfl_xor_any(p, o));
+    acc = p;
+  }
+  if (row < rows && t == 0) store_acc<DT>(dst, row, acc);
+}
+
+// First axis: block = 32 columns x 8 row slices.
+template <int DT, int KIND>
+__global__ void __launch_bounds__(256) reduce_first_kernel(int64_t rows, int64_t cols, const void *__restrict__ src,
+                                                           int64_t row_stride, void *__restrict__ dst) {
+  using A = typename Acc<DT>::type;
+  __shared__ unsigned long long red[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int64_t c = static_cast<int64_t>(blockIdx.x) * 32 + cx;
+  A acc = identity<DT, KIND>();
+  if (c < cols)
+    for (int64_t r = ry; r < rows; r += 8) acc = combine<KIND, A>(load_acc<DT>(src, r * row_stride + c), acc);
+  unsigned long long bits = 0;
+  memcpy(&bits, &acc, sizeof(A));
+  red[ry][cx] = bits;
+  __syncthreads();
+  if (ry == 0 && c < cols) {
+#pragma unroll
+    for (int k = 1; k < 8; ++k) {
+      A p;
+      bits = red[k][cx];
+      memcpy(&p, &bits, sizeof(A));
+      acc = combine<KIND, A>(acc, p);
+    }
+    store_acc<DT>(dst, c, acc);
+  }
+}
+
+bool reduce_kind_valid(int kind, int dt) {
+  if (kind < BSIR_REDUCE_SUM || kind > BSIR_REDUCE_ANDI) return false;
+  if (dtype_is_float(dt)) return kind <= BSIR_REDUCE_MIN;
+  return true;
+}
+
+template <int DT, int KIND>
+void launch_reduce(bool last, int64_t rows, int64_t cols, const void *src, int64_t rs, void *dst, cudaStream_t st) {
+  if (last) {
+    int tpr = 32;
+    while (tpr < 256 && cols > tpr * 8) tpr <<= 1;
+    const int rpc = 256 / tpr;
+    reduce_last_kernel<DT, KIND><<<static_cast<unsigned>(ceil_div(rows, rpc)), 256, 0, st>>>(rows, cols, src, rs, dst, tpr);
+  } else {
+    reduce_first_kernel<DT, KIND><<<static_cast<unsigned>(ceil_div(cols, 32)), 256, 0, st>>>(rows, cols, src, rs, dst);
+  }
+}
+
+template <int DT>
+int32_t dispatch_kind(bool last, int kind, int64_t rows, int64_t cols, const void *src, int64_t rs, void *dst,
+                      cudaStream_t st) {
+#define K(k) \
+  case k: launch_reduce<DT, k>(last, rows, cols, src, rs, dst, st); return BSIR_OK;
+  if constexpr (DT == BSIR_F32 || DT == BSIR_F16 || DT == BSIR_BF16) {
+    switch (kind) { K(BSIR_REDUCE_SUM) K(BSIR_REDUCE_PROD) K(BSIR_REDUCE_MAX) K(BSIR_REDUCE_MIN) default: break; }
+  } else {
+    switch (kind) {
+      K(BSIR_REDUCE_SUM) K(BSIR_REDUCE_PROD) K(BSIR_REDUCE_MAX) K(BSIR_REDUCE_MIN) K(BSIR_REDUCE_ANY)
+      K(BSIR_REDUCE_ALL) K(BSIR_REDUCE_XORI) K(BSIR_REDUCE_ORI) K(BSIR_REDUCE_ANDI)
+      default: break;
+    }
+  }
+#undef K
+  return fail(BSIR_ERR_ATTR, "reduce: kind %d", kind);
+}
+
+int32_t reduce_axis(const char *what, bool last, int32_t kind, int32_t dtype, int64_t rows, int64_t cols,
+                    const void *src, int64_t rs, void *dst, void *stream) {
+  clear_error();
+  if (dtype_bytes(dtype) == 0) return fail(BSIR_ERR_DTYPE, "%s: dtype %d", what, dtype);
+  if (!reduce_kind_valid(kind, dtype)) return fail(BSIR_ERR_ATTR, "%s: kind %d for dtype %d", what, kind, dtype);
+  if (rows < 0 || cols < 0) return fail(BSIR_ERR_SHAPE, "%s: rows=%lld cols=%lld", what, (long long)rows, (long long)cols);
+  const int64_t nout = last ? rows : cols;
+  if (nout == 0) return BSIR_OK;
+  if (!dst || (!src && rows * cols > 0)) return fail(BSIR_ERR_NULL, "%s: null pointer", what);
+  if (rs < cols) return fail(BSIR_ERR_STRIDE, "%s: row stride %lld < cols %lld", what, (long long)rs, (long long)cols);
+  if (!aligned_to(src, dtype_bytes(dtype)) || !aligned_to(dst, dtype_bytes(dtype)))
+    return fail(BSIR_ERR_ALIGN, "%s: misaligned", what);
+  cudaStream_t st = resolve_stream(stream);
+  int32_t rc;
+#define D(code) \
+  case code: rc = dispatch_kind<code>(last, kind, rows, cols, src, rs, dst, st); break;
+  switch (dtype) {
+    D(BSIR_F32) D(BSIR_F16) D(BSIR_BF16) D(BSIR_I8) D(BSIR_I16) D(BSIR_I32) D(BSIR_I64) D(BSIR_U8) D(BSIR_U16)
+    D(BSIR_U32) D(BSIR_U64) D(BSIR_BOOL)
+    default: return fail(BSIR_ERR_DTYPE, "%s: dtype %d", what, dtype);
+  }
+#undef D
+  if (rc) return rc;
+  count_launch();
+  return check_launch(what);
+}
+
+// ------------------------------------------------------------------ reduce_with_index
+// A row is cut into segments of up to 256 x VPT 16-byte vectors; one CTA per (segment, row)
+// keeps its segment in registers, finds the segment extreme with a NaN-propagating
+// max/min, then looks for the first (or last) element equal to it.  Partial results go to a
+// scratch array; the CTA that finishes a row last (a counter in the same scratch, left at zero
+// again afterwards) folds the partials in segment order and writes the outputs.
+struct Partial {
+  float val;     // extreme of the segment (of its NaN-free prefix when it holds a NaN)
+  int32_t idx;   // index of that extreme within the row
+  int32_t nan;   // row index of the segment's first NaN, INT_MAX when none
+  int32_t pad;
+};
+
+struct RwiParams {
+  int64_t rows, cols, row_stride;
+  int64_t nvec;       // vectors per row
+  int64_t seg_vecs;   // vectors per segment
+  int nseg;
+  int tie_left;
+  int nan_first;
+};
+
+template <bool IS_MAX>
+__device__ __forceinline__ float ext_nan(float a, float b) { return IS_MAX ? maximumf(a, b) : minimumf(a, b); }
+template <bool IS_MAX>
+__device__ __forceinline__ float ext_num(float a, float b) { return IS_MAX ? fmaxf(a, b) : fminf(a, b); }
+
+template <class F>
+__device__ __forceinline__ float cta_reduce_f(float v, float *red, F f) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = f(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float p = red[lane & 7];
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) p = f(p, __shfl_xor_sync(0xffffffffu, p, o));
+  return p;
+}
+template <class F>
+__device__ __forceinline__ int cta_reduce_i(int v, int *red, F f) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = f(v, __shfl_xor_sync(0xffffffffu, v, o));
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  int p = red[lane & 7];
+#pragma unroll
+  for (int o = 4; o > 0; o >>= 1) p = f(p, __shfl_xor_sync(0xffffffffu, p, o));
+  return p;
+}
+
+template <int DT, int VPT, bool IS_MAX>
+__global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__restrict__ src, void *__restrict__ dst_val,
+                                                  int32_t *__restrict__ dst_idx, unsigned *__restrict__ counters,
+                                                  Partial *__restrict__ partials) {
+  constexpr int kPerWord = FloatTraits<DT>::kPerWord;
+  constexpr int kPerVec = 4 * kPerWord;
+  using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
+  __shared__ float redf[8];
+  __shared__ int redi[8];
+  __shared__ int is_last;
+  const int seg = blockIdx.x;
+  const int64_t row = blockIdx.y;
+  const E *xrow = static_cast<const E *>(src) + row * p.row_stride;
+  const int64_t v0 = static_cast<int64_t>(seg) * p.seg_vecs;
+  const int64_t v1 = min(v0 + p.seg_vecs, p.nvec);
+  const float ident = IS_MAX ? __int_as_float(0xff800000) : __int_as_float(0x7f800000);
+
+  Vec16 v[VPT];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
+    if (vi < v1) v[i] = ld_stream(reinterpret_cast<const Vec16 *>(xrow) + vi);
+  }
+  // pass 1: NaN-propagating extreme
+  float m = ident;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
+    if (vi < v1) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        float e[kPerWord];
+        FloatTraits<DT>::unpack(v[i].w[w], e);
+#pragma unroll
+        for (int k = 0; k < kPerWord; ++k) m = ext_nan<IS_MAX>(m, e[k]);
+      }
+    }
+  }
+  m = cta_reduce_f(m, redf, [](float a, float b) { return ext_nan<IS_MAX>(a, b); });
+
+  int nanpos = INT_MAX;
+  if (m != m) {
+    // rare: the segment holds a NaN.  Find the first one, then redo the extreme on the prefix before it.
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
+      if (vi < v1) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          float e[kPerWord];
+          FloatTraits<DT>::unpack(v[i].w[w], e);
+#pragma unroll
+          for (int k = 0; k < kPerWord; ++k)
+            if (e[k] != e[k]) nanpos = min(nanpos, static_cast<int>(vi * kPerVec + w * kPerWord + k));
+        }
+      }
+    }
+    nanpos = cta_reduce_i(nanpos, redi, [](int a, int b) { return min(a, b); });
+    m = ident;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
+      if (vi < v1) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          float e[kPerWord];
+          FloatTraits<DT>::unpack(v[i].w[w], e);
+#pragma unroll
+          for (int k = 0; k < kPerWord; ++k)
+            if (static_cast<int>(vi * kPerVec + w * kPerWord + k) < nanpos) m = ext_nan<IS_MAX>(m, e[k]);
+        }
+      }
+    }
+    m = cta_reduce_f(m, redf, [](float a, float b) { return ext_nan<IS_MAX>(a, b); });
+  }
+  // pass 2: first (or last) index holding the extreme, among elements before nanpos
+  int best = p.tie_left ? INT_MAX : -1;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
+    if (vi < v1) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        float e[kPerWord];
+        FloatTraits<DT>::unpack(v[i].w[w], e);
+#pragma unroll
+        for (int k = 0; k < kPerWord; ++k) {
+          const int gi = static_cast<int>(vi * kPerVec + w * kPerWord + k);
+          if (e[k] == m && gi < nanpos) best = p.tie_left ? min(best, gi) : max(best, gi);
+        }
+      }
+    }
+  }
+  if (p.tie_left) best = cta_reduce_i(best, redi, [](int a, int b) { return min(a, b); });
+  else best = cta_reduce_i(best, redi, [](int a, int b) { return max(a, b); });
+  // a segment whose prefix is empty or all at the identity reports "nothing better than the start"
+  if (best == INT_MAX || best < 0) best = -1;
+
+  if (p.nseg == 1) {
+    if (threadIdx.x == 0) {
+      float val = m;
+      int idx = best < 0 ? 0 : best;
+      if (nanpos != INT_MAX) {
+        val = __int_as_float(0x7fc00000);
+        if (p.nan_first) idx = nanpos;
+      }
+      float o[kPerWord];
+      o[0] = val;
+      if constexpr (kPerWord == 2) o[1] = 0.0f;
+      const uint32_t packed = FloatTraits<DT>::pack(o);
+      if constexpr (DT == BSIR_F32) static_cast<float *>(dst_val)[row] = val;
+      else static_cast<uint16_t *>(dst_val)[row] = static_cast<uint16_t>(packed & 0xffffu);
+      dst_idx[row] = idx;
+    }
+    return;
+  }
+
+  Partial *mine = partials + row * p.nseg;
+  if (threadIdx.x == 0) {
+    mine[seg] = Partial{m, best, nanpos, 0};
+    __threadfence();
+    const unsigned done = atomicAdd(&counters[row], 1u);
+    is_last = (done == static_cast<unsigned>(p.nseg - 1));
+  }
+  __syncthreads();
+  if (!is_last || threadIdx.x != 0) return;
+  __threadfence();
+  float val = ident;
+  int idx = 0;
+  bool have = false, saw_nan = false;
+  for (int s = 0; s < p.nseg; ++s) {
+    const volatile Partial *q = mine + s;
+    const float sv = q->val;
+    const int si = q->idx, sn = q->nan;
+    if (si >= 0) {
+      // sequential-order combine: strictly better moves the index; on a tie the left rule keeps
+      // the earlier segment and the right rule takes the later one
+      const bool better = IS_MAX ? (sv > val) : (sv < val);
+      const bool tie = sv == val;
+      if (!have || better || (tie && !p.tie_left)) idx = si;
+      val = have ? ext_nan<IS_MAX>(val, sv) : sv;
+      have = true;
+    }
+    if (sn != INT_MAX) {
+      saw_nan = true;
+      if (p.nan_first) idx = sn;
+      break;
+    }
+  }
+  if (saw_nan) val = __int_as_float(0x7fc00000);
+  float o[kPerWord];
+  o[0] = val;
+  if constexpr (kPerWord == 2) o[1] = 0.0f;
+  const uint32_t packed = FloatTraits<DT>::pack(o);
+  if constexpr (DT == BSIR_F32) static_cast<float *>(dst_val)[row] = val;
+  else static_cast<uint16_t *>(dst_val)[row] = static_cast<uint16_t>(packed & 0xffffu);
+  dst_idx[row] = idx;
+  counters[row] = 0u;  // scratch is zero again for the next call
+}
+
+// Scalar fallback: one CTA per row, any stride / alignment / length.
+template <int DT, bool IS_MAX>
+__global__ void __launch_bounds__(256) rwi_scalar_kernel(RwiParams p, const void *__restrict__ src,
+                                                         void *__restrict__ dst_val, int32_t *__restrict__ dst_idx) {
+  __shared__ float redf[8];
+  __shared__ int redi[8];
+  const int64_t row = blockIdx.x;
+  const int64_t base = row * p.row_stride;
+  const float ident = IS_MAX ? __int_as_float(0xff800000) : __int_as_float(0x7f800000);
+  auto at = [&](int64_t j) -> float {
+    if constexpr (DT == BSIR_F32) return static_cast<const float *>(src)[base + j];
+    else if constexpr (DT == BSIR_F16) return __half2float(__ushort_as_half(static_cast<const uint16_t *>(src)[base + j]));
+    else return __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t *>(src)[base + j]) << 16);
+  };
+  int nanpos = INT_MAX;
+  for (int64_t j = threadIdx.x; j < p.cols; j += 256) {
+    const float e = at(j);
+    if (e != e) { nanpos = static_cast<int>(j); break; }
+  }
+  nanpos = cta_reduce_i(nanpos, redi, [](int a, int b) { return min(a, b); });
+  const int64_t lim = nanpos == INT_MAX ? p.cols : nanpos;
+  float m = ident;
+  for (int64_t j = threadIdx.x; j < lim; j += 256) m = ext_nan<IS_MAX>(m, at(j));
+  m = cta_reduce_f(m, redf, [](float a, float b) { return ext_nan<IS_MAX>(a, b); });
+  int best = p.tie_left ? INT_MAX : -1;
+  for (int64_t j = threadIdx.x; j < lim; j += 256)
+    if (at(j) == m) best = p.tie_left ? min(best, static_cast<int>(j)) : max(best, static_cast<int>(j));
+  if (p.tie_left) best = cta_reduce_i(best, redi, [](int a, int b) { return min(a, b); });
+  else best = cta_reduce_i(best, redi, [](int a, int b) { return max(a, b); });
+  if (threadIdx.x == 0) {
+    int idx = (best == INT_MAX || best < 0) ? 0 : best;
+    float val = m;
+    if (nanpos != INT_MAX) {
+      val = __int_as_float(0x7fc00000);
+      if (p.nan_first) idx = nanpos;
+    }
+    if constexpr (DT == BSIR_F32) static_cast<float *>(dst_val)[row] = val;
+    else if constexpr (DT == BSIR_F16) static_cast<uint16_t *>(dst_val)[row] = __half_as_ushort(__float2half_rn(val));
+    else static_cast<uint16_t *>(dst_val)[row] = __bfloat16_as_ushort(__float2bfloat16_rn(val));
+    dst_idx[row] = idx;
+  }
+}
+
+// Segment plan: enough CTAs to fill the device, segments of at most 256 x 16 vectors.
+void plan_segments(int64_t rows, int64_t nvec, int sm_count, int64_t *seg_vecs, int *nseg, int *vpt) {
+  const int64_t target_ctas = static_cast<int64_t>(sm_count > 0 ? sm_count : 148) * 4;
+  int64_t want_seg = rows > 0 ? ceil_div(target_ctas, rows) : 1;
+  if (want_seg < 1) want_seg = 1;
+  int64_t sv = ceil_div(nvec, want_seg);
+  if (sv > 4096) sv = 4096;
+  if (sv < 256) sv = 256;
+  int v = 1;
+  while (v * 256 < sv) v <<= 1;
+  *vpt = v;
+  *seg_vecs = static_cast<int64_t>(v) * 256;
+  *nseg = static_cast<int>(ceil_div(nvec, *seg_vecs));
+  if (*nseg < 1) *nseg = 1;
+}
+
+size_t rwi_scratch_bytes(int64_t rows, int nseg) {
+  const size_t counters = (static_cast<size_t>(rows) * 4 + 255) / 256 * 256;
+  return counters + static_cast<size_t>(rows) * static_cast<size_t>(nseg) * sizeof(Partial);
+}
+
+}  // namespace
+}  // namespace bsir
+
+using namespace bsir;
+
+extern "C" {
+
+int32_t bsir_reduce_last_axis(int32_t kind, int32_t dtype, int64_t rows, int64_t cols, const void *src,
+                              int64_t src_row_stride, void *dst, void *stream) {
+  return reduce_axis("reduce_last_axis", true, kind, dtype, rows, cols, src, src_row_stride, dst, stream);
+}
+int32_t bsir_reduce_first_axis(int32_t kind, int32_t dtype, int64_t rows, int64_t cols, const void *src,
+                               int64_t src_row_stride, void *dst, void *stream) {
+  return reduce_axis("reduce_first_axis", false, kind, dtype, rows, cols, src, src_row_stride, dst, stream);
+}
+
+int64_t bsir_reduce_with_index_workspace_bytes(int64_t rows, int64_t cols) {
+  if (rows <= 0 || cols <= 0) return 0;
+  size_t worst = 0;
+  for (int eb = 2; eb <= 4; eb += 2) {
+    int64_t sv; int ns, v;
+    plan_segments(rows, ceil_div(cols * eb, 16), device_info().sm_count, &sv, &ns, &v);
+    if (ns > 1) { const size_t b = rwi_scratch_bytes(rows, ns); if (b > worst) worst = b; }
+  }
+  return static_cast<int64_t>(worst);
+}
+
+int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie_break_left, int32_t nan_mode, int64_t rows,
+                               int64_t cols, const void *src, int64_t src_row_stride, void *dst_value,
+                               int32_t *dst_index, void *workspace, int64_t workspace_bytes, void *stream) {
+  clear_error();
+  if (!dtype_is_float(dtype)) return fail(BSIR_ERR_DTYPE, "reduce_with_index: dtype %d (f32, f16 or bf16)", dtype);
+  if (kind != BSIR_RWI_MAX && kind != BSIR_RWI_MIN)
+    return fail(BSIR_ERR_ATTR, "reduce_with_index: kind %d (unsigned kinds need integer inputs)", kind);
+  if (nan_mode != BSIR_RWI_NAN_REGION && nan_mode != BSIR_RWI_NAN_FIRST)
+    return fail(BSIR_ERR_ATTR, "reduce_with_index: nan_mode %d", nan_mode);
+  if (rows < 0 || cols < 0) return fail(BSIR_ERR_SHAPE, "reduce_with_index: rows=%lld cols=%lld", (long long)rows, (long long)cols);
+  if (cols > INT_MAX - 64) return fail(BSIR_ERR_SHAPE, "reduce_with_index: cols exceed the int32 index range");
+  if (rows > 65535) {
+    // grid.y limit: fold very tall inputs in slabs
+    for (int64_t r0 = 0; r0 < rows; r0 += 65535) {
+      const int64_t nr = rows - r0 < 65535 ? rows - r0 : 65535;
+      const int eb0 = dtype_bytes(dtype);
+      int32_t rc = bsir_reduce_with_index(kind, dtype, tie_break_left, nan_mode, nr, cols,
+                                          static_cast<const char *>(src) + r0 * src_row_stride * eb0, src_row_stride,
+                                          static_cast<char *>(dst_value) + r0 * eb0, dst_index + r0, workspace,
+                                          workspace_bytes, stream);
+      if (rc) return rc;
+    }
+    return BSIR_OK;
+  }
+  if (rows == 0) return BSIR_OK;
+  if (!dst_value || !dst_index || (!src && cols > 0)) return fail(BSIR_ERR_NULL, "reduce_with_index: null pointer");
+  if (src_row_stride < cols) return fail(BSIR_ERR_STRIDE, "reduce_with_index: row stride < cols");
+  const int eb = dtype_bytes(dtype);
+  if (!aligned_to(src, eb) || !aligned_to(dst_value, eb) || !aligned_to(dst_index, 4))
+    return fail(BSIR_ERR_ALIGN, "reduce_with_index: misaligned");
+  cudaStream_t st = resolve_stream(stream);
+  RwiParams p{};
+  p.rows = rows; p.cols = cols; p.row_stride = src_row_stride;
+  p.tie_left = tie_break_left ? 1 : 0;
+  p.nan_first = nan_mode == BSIR_RWI_NAN_FIRST;
+  const bool is_max = kind == BSIR_RWI_MAX;
+  const int per_vec = 16 / eb;
+  const bool vec_ok = cols > 0 && cols % per_vec == 0 && aligned_to(src, 16) && (src_row_stride * eb) % 16 == 0;
+  if (!vec_ok) {
+    p.nseg = 1;
+#define S(D) \
+  if (is_max) rwi_scalar_kernel<D, true><<<static_cast<unsigned>(rows), 256, 0, st>>>(p, src, dst_value, dst_index); \
+  else rwi_scalar_kernel<D, false><<<static_cast<unsigned>(rows), 256, 0, st>>>(p, src, dst_value, dst_index);
+    if (dtype == BSIR_F32) { S(BSIR_F32) } else if (dtype == BSIR_F16) { S(BSIR_F16) } else { S(BSIR_BF16) }
+#undef S
+    count_launch();
+    return check_launch("reduce_with_index");
+  }
+  p.nvec = cols / per_vec;
+  int vpt = 1;
+  plan_segments(rows, p.nvec, device_info().sm_count, &p.seg_vecs, &p.nseg, &vpt);
+  unsigned *counters = nullptr;
+  Partial *partials = nullptr;
+  if (p.nseg > 1) {
+    const size_t need = rwi_scratch_bytes(rows, p.nseg);
+    char *ws = static_cast<char *>(workspace);
+    if (ws && (static_cast<size_t>(workspace_bytes) < need || !aligned_to(ws, 16))) ws = nullptr;  // too small: use ours
+    if (!ws) ws = static_cast<char *>(device_workspace(need, st));
+    if (!ws) return BSIR_ERR_WORKSPACE;
+    counters = reinterpret_cast<unsigned *>(ws);
+    partials = reinterpret_cast<Partial *>(ws + (static_cast<size_t>(rows) * 4 + 255) / 256 * 256);
+  }
+  const dim3 grid(static_cast<unsigned>(p.nseg), static_cast<unsigned>(rows));
+#define L(D, V)                                                                                             \
+  if (is_max) rwi_kernel<D, V, true><<<grid, 256, 0, st>>>(p, src, dst_value, dst_index, counters, partials); \
+  else rwi_kernel<D, V, false><<<grid, 256, 0, st>>>(p, src, dst_value, dst_index, counters, partials);
+#define LV(D)                      \
+  switch (vpt) {                   \
+    case 1: L(D, 1) break;         \
+    case 2: L(D, 2) break;         \
+    case 4: L(D, 4) break;         \
+    case 8: L(D, 8) break;         \
+    default: L(D, 16) break;       \
+  }
+  if (dtype == BSIR_F32) { LV(BSIR_F32) } else if (dtype == BSIR_F16) { LV(BSIR_F16) } else { LV(BSIR_BF16) }
+#undef LV
+#undef L
+  count_launch();
+  return check_launch("reduce_with_index");
+}
+
+}  // extern "C"

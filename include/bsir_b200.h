@@ -1,0 +1,378 @@
+/*
+ * bsir_b200.h -- C ABI of the B200 (sm_100a) execution backend for the operator
+ * set of BiShengIR's HFusion / HIVM dialects.
+ *
+ * Three layers, all plain C (pointers + sizes, no C++/torch types):
+ *
+ *  B1  op-library ABI: the `_mlir_ciface_<op>_<rank>d_<dtype>` symbols that the
+ *      reference's HIVMToStandard conversion calls, taking pointers to MLIR
+ *      memref descriptors.  Reference declaration macros:
+ *      bishengir/lib/Template/include/Vector/VecUtils.h:971-1023 (elementwise),
+ *      bishengir/lib/Template/include/Vector/Cast/CastUtils.h:229-301 (vcast),
+ *      bishengir/lib/Template/include/Vector/Reduction/ReductionUtils.h:876-1010.
+ *      Descriptor: bishengir/lib/Template/include/Utils.h:72-78.
+ *      Differences from the reference symbols: (1) the buffers are device (HBM)
+ *      pointers, (2) the functions return an int32 status instead of void, and
+ *      (3) they enqueue on the stream set with bsir_set_stream() for the
+ *      calling thread (default: the legacy default stream), exactly as the
+ *      reference enqueues on the ACL stream of its launch.
+ *
+ *  B2  compiled-kernel ABI: bsir_kernel_register() + bsir_launch(), the
+ *      equivalent of `rtFunctionRegister` + `rtKernelLaunch(stub, blockDim,
+ *      args, argsSize, smDesc, stream)` used by
+ *      bishengir/test/Integration/HIVM/VecAdd/main.cpp:96-113,169-171.
+ *      A registered kernel = one op (or fused pattern) + its static shape, the
+ *      thing `bishengir-compile` turns an .mlir file into; args are one bare
+ *      device pointer per memref argument, inputs first, then outputs.
+ *
+ *  B3  typed entry points (bsir_<op>): pointers + sizes/strides + attributes,
+ *      used by B1/B2 internally and callable directly.
+ *
+ * Every function is asynchronous with respect to the host (returns after the
+ * enqueue), allocates nothing per call, and never aborts: errors come back as
+ * a negative bsir_status and bsir_last_error() has the text.
+ */
+#ifndef BSIR_B200_H_
+#define BSIR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BSIR_API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------------ */
+/* status                                                                    */
+/* ------------------------------------------------------------------------ */
+typedef enum {
+  BSIR_OK = 0,
+  BSIR_ERR_NULL = -1,        /* a required pointer is null                   */
+  BSIR_ERR_SHAPE = -2,       /* negative/mismatched sizes                    */
+  BSIR_ERR_STRIDE = -3,      /* layout the kernel cannot address             */
+  BSIR_ERR_DTYPE = -4,       /* dtype not legal for this op                  */
+  BSIR_ERR_ATTR = -5,        /* illegal attribute / attribute-dtype combo    */
+  BSIR_ERR_ALIGN = -6,       /* pointer alignment below the element size     */
+  BSIR_ERR_LAUNCH = -7,      /* CUDA reported an error at enqueue            */
+  BSIR_ERR_UNKNOWN_KERNEL = -8,
+  BSIR_ERR_ARGS = -9,        /* wrong args_size for bsir_launch              */
+  BSIR_ERR_WORKSPACE = -10,  /* scratch too small / could not be set up      */
+  BSIR_ERR_UNSUPPORTED = -11,
+  BSIR_ERR_DEVICE = -12      /* a device-side bounded wait gave up           */
+} bsir_status;
+
+BSIR_API const char *bsir_status_string(int32_t status);
+/* Text of the last error raised on the calling thread ("" if none). */
+BSIR_API const char *bsir_last_error(void);
+BSIR_API const char *bsir_version(void);
+
+/* Stream used by the B1 symbols and by bsir_launch(..., stream == NULL) on the
+ * calling thread.  `stream` is a cudaStream_t; NULL = legacy default stream. */
+BSIR_API int32_t bsir_set_stream(void *stream);
+BSIR_API void *bsir_get_stream(void);
+
+/* ------------------------------------------------------------------------ */
+/* element types (names as spelled in library symbols:                      */
+/* bishengir/lib/Dialect/HIVM/IR/LibraryFunctionOpInterface/                 */
+/* LibraryFunctionOpInterfaceImpl.cpp:45-53)                                 */
+/* ------------------------------------------------------------------------ */
+typedef enum {
+  BSIR_F32 = 0,  /* float       */
+  BSIR_F16 = 1,  /* half        */
+  BSIR_BF16 = 2, /* bfloat16_t  */
+  BSIR_I8 = 3,   /* int8_t      */
+  BSIR_I16 = 4,  /* int16_t     */
+  BSIR_I32 = 5,  /* int32_t     */
+  BSIR_I64 = 6,  /* int64_t     */
+  BSIR_U8 = 7,   /* uint8_t     */
+  BSIR_U16 = 8,  /* uint16_t    */
+  BSIR_U32 = 9,  /* uint32_t    */
+  BSIR_U64 = 10, /* uint64_t    */
+  BSIR_BOOL = 11 /* bool (i1 stored one per byte) */
+} bsir_dtype;
+
+BSIR_API int32_t bsir_dtype_size(int32_t dtype);
+
+/* ------------------------------------------------------------------------ */
+/* attributes (integer values as in                                          */
+/* bishengir/include/bishengir/Dialect/HFusion/IR/HFusionEnums.td)           */
+/* ------------------------------------------------------------------------ */
+typedef enum { /* hfusion.round_mode, HFusionEnums.td:122-141 */
+  BSIR_ROUND_RINT = 0,
+  BSIR_ROUND_ROUND = 1,
+  BSIR_ROUND_FLOOR = 2,
+  BSIR_ROUND_CEIL = 3,
+  BSIR_ROUND_TRUNC = 4,
+  BSIR_ROUND_ODD = 5,
+  BSIR_ROUND_TRUNCWITHOVERFLOW = 6
+} bsir_round_mode;
+
+/* CastMode argument of the vcast library symbols
+ * (bishengir/lib/Template/include/Vector/Cast/CastUtils.h:30-38). */
+typedef enum {
+  BSIR_CASTMODE_R = 0, /* rint  */
+  BSIR_CASTMODE_A = 1, /* round */
+  BSIR_CASTMODE_F = 2, /* floor */
+  BSIR_CASTMODE_C = 3, /* ceil  */
+  BSIR_CASTMODE_Z = 4, /* trunc */
+  BSIR_CASTMODE_O = 5, /* odd   */
+  BSIR_CASTMODE_OVERFLOW = 6
+} bsir_cast_mode;
+
+/* How a float->int (or narrowing int) cast treats out-of-range values. */
+typedef enum {
+  BSIR_OVERFLOW_WRAP = 0,     /* enable_saturate = false: round, then keep the
+                                 low bits (two's complement wrap)            */
+  BSIR_OVERFLOW_SATURATE = 1, /* enable_saturate = true: clamp to the range of
+                                 the destination; NaN -> 0                   */
+  /* Device-path rewrites of the reference for f32 -> i8, kept as named
+   * variants (never the default):                                          */
+  BSIR_OVERFLOW_ASCEND_SATURATE_TRUNC_VIA_F16 = 2, /* Normalize.cpp:3826-3836 */
+  BSIR_OVERFLOW_ASCEND_DOUBLE_ROUND_VIA_F16 = 3    /* HIVMDecomposeOp.cpp:101-190 */
+} bsir_overflow_mode;
+
+typedef enum { /* hfusion.unary_fn 0..26 (HFusionEnums.td:29-57); 100.. = linalg.unary_fn */
+  BSIR_UNARY_RELU = 0, BSIR_UNARY_SQRT = 1, BSIR_UNARY_RSQRT = 2, BSIR_UNARY_REC = 3,
+  BSIR_UNARY_VNOT = 4, BSIR_UNARY_TANH = 5, BSIR_UNARY_SIN = 6, BSIR_UNARY_COS = 7,
+  BSIR_UNARY_ATAN = 8, BSIR_UNARY_TAN = 9, BSIR_UNARY_ABSI = 10, BSIR_UNARY_ERF = 11,
+  BSIR_UNARY_LOG2 = 12, BSIR_UNARY_LOG10 = 13, BSIR_UNARY_LOG1P = 14, BSIR_UNARY_EXP2 = 15,
+  BSIR_UNARY_EXPM1 = 16, BSIR_UNARY_ILOGB = 17, BSIR_UNARY_ASIN = 18, BSIR_UNARY_ACOS = 19,
+  BSIR_UNARY_ASINH = 20, BSIR_UNARY_ACOSH = 21, BSIR_UNARY_ATANH = 22, BSIR_UNARY_SINH = 23,
+  BSIR_UNARY_LGAMMA = 24, BSIR_UNARY_COSH = 25, BSIR_UNARY_NEARBYINT = 26,
+  BSIR_UNARY_EXP = 100, BSIR_UNARY_LOG = 101, BSIR_UNARY_ABS = 102, BSIR_UNARY_CEIL = 103,
+  BSIR_UNARY_FLOOR = 104, BSIR_UNARY_NEGF = 105, BSIR_UNARY_RECIPROCAL = 106,
+  BSIR_UNARY_ROUND = 107, BSIR_UNARY_SQRT_L = 108, BSIR_UNARY_RSQRT_L = 109,
+  BSIR_UNARY_SQUARE = 110, BSIR_UNARY_TANH_L = 111, BSIR_UNARY_ERF_L = 112
+} bsir_unary_fn;
+
+typedef enum { /* hfusion.binary_fn 0..20 (HFusionEnums.td:62-84); 100.. = linalg.binary_fn */
+  BSIR_BINARY_VOR = 0, BSIR_BINARY_VAND = 1, BSIR_BINARY_VXOR = 2, BSIR_BINARY_MINF = 3,
+  BSIR_BINARY_MAXF = 4, BSIR_BINARY_POWF = 5, BSIR_BINARY_MOD = 6, BSIR_BINARY_MODUI = 7,
+  BSIR_BINARY_SHLI = 8, BSIR_BINARY_SHRSI = 9, BSIR_BINARY_SHRUI = 10, BSIR_BINARY_LDEXP = 11,
+  BSIR_BINARY_CEILDIVSI = 12, BSIR_BINARY_CEILDIVUI = 13, BSIR_BINARY_FLOORDIVSI = 14,
+  BSIR_BINARY_POWI = 15, BSIR_BINARY_MINNUMF = 16, BSIR_BINARY_MAXNUMF = 17,
+  BSIR_BINARY_ATAN2 = 18, BSIR_BINARY_DIVFHP = 19, BSIR_BINARY_COPYSIGN = 20,
+  BSIR_BINARY_ADD = 100, BSIR_BINARY_SUB = 101, BSIR_BINARY_MUL = 102, BSIR_BINARY_DIV = 103,
+  BSIR_BINARY_DIV_UNSIGNED = 104, BSIR_BINARY_MAX_SIGNED = 105, BSIR_BINARY_MIN_SIGNED = 106,
+  BSIR_BINARY_MAX_UNSIGNED = 107, BSIR_BINARY_MIN_UNSIGNED = 108, BSIR_BINARY_POWF_L = 109
+} bsir_binary_fn;
+
+typedef enum { /* hfusion.compare_fn */
+  BSIR_CMP_VEQ = 0, BSIR_CMP_VNE = 1, BSIR_CMP_VLE = 2, BSIR_CMP_VLT = 3, BSIR_CMP_VGE = 4,
+  BSIR_CMP_VGT = 5, BSIR_CMP_VULE = 6, BSIR_CMP_VULT = 7, BSIR_CMP_VUGE = 8, BSIR_CMP_VUGT = 9
+} bsir_compare_fn;
+
+typedef enum { /* hivm reduce kinds, HIVMVectorOps.td:1316-1434 */
+  BSIR_REDUCE_SUM = 0, BSIR_REDUCE_PROD = 1, BSIR_REDUCE_MAX = 2, BSIR_REDUCE_MIN = 3,
+  BSIR_REDUCE_ANY = 4, BSIR_REDUCE_ALL = 5, BSIR_REDUCE_XORI = 6, BSIR_REDUCE_ORI = 7,
+  BSIR_REDUCE_ANDI = 8
+} bsir_reduce_kind;
+
+typedef enum { /* hfusion.reduce_with_index_kind, HFusionEnums.td:303-311 */
+  BSIR_RWI_MIN = 0, BSIR_RWI_MAX = 1, BSIR_RWI_MINUI = 2, BSIR_RWI_MAXUI = 3
+} bsir_reduce_with_index_kind;
+
+/* NaN policy of reduce_with_index. */
+typedef enum {
+  /* What the op's region computes when lowered to loops
+   * (HFusionOps.cpp:1506-1523): value = maximumf chain (NaN poisons the value),
+   * index moves only on a strict ordered compare, so it stays at the best
+   * element seen before the first NaN. */
+  BSIR_RWI_NAN_REGION = 0,
+  /* Device/Triton rule: the first NaN wins value and index
+   * (Normalize.cpp:2688-2777, linalg-to-hfusion.mlir:224-241). */
+  BSIR_RWI_NAN_FIRST = 1
+} bsir_rwi_nan_mode;
+
+typedef enum { /* #hivm.descale_mode, HIVMAttrs.td:1061-1071 */
+  BSIR_DESCALE_NULL = 0, BSIR_DESCALE_PER_CHANNEL = 1, BSIR_DESCALE_PER_TENSOR = 2
+} bsir_descale_mode;
+
+/* ------------------------------------------------------------------------ */
+/* memref descriptors (MLIR C interface; Template/include/Utils.h:72-78)     */
+/* base = aligned + offset (elements); strides in elements                   */
+/* ------------------------------------------------------------------------ */
+typedef struct { void *allocated; void *aligned; int64_t offset; int64_t sizes[1]; int64_t strides[1]; } bsir_memref_1d;
+typedef struct { void *allocated; void *aligned; int64_t offset; int64_t sizes[2]; int64_t strides[2]; } bsir_memref_2d;
+typedef struct { void *allocated; void *aligned; int64_t offset; int64_t sizes[3]; int64_t strides[3]; } bsir_memref_3d;
+
+/* ------------------------------------------------------------------------ */
+/* B3: typed entry points                                                    */
+/* ------------------------------------------------------------------------ */
+
+/* A strided operand of rank <= 3.  stride 0 broadcasts that dimension (the
+ * inline `broadcast = [...]` form of HIVM vector ops, HIVMVectorOps.td:55-111).
+ * `data` may be NULL for a scalar operand, in which case `scalar_bits` holds
+ * the value in the op's element type (low bits). */
+typedef struct {
+  const void *data;
+  int64_t strides[3];
+  uint64_t scalar_bits;
+} bsir_operand;
+
+/* out = fn(x); elemwise_unary (HFusionNamedStructuredOps.yaml:72-123,
+ * bodies HFusionOps.cpp:434-535).  rank in 1..3, sizes[rank..] ignored. */
+BSIR_API int32_t bsir_elemwise_unary(int32_t fn, int32_t dtype, int32_t rank, const int64_t *sizes,
+                                     const bsir_operand *x, void *out, const int64_t *out_strides,
+                                     void *stream);
+/* out = fn(a, b); elemwise_binary (yaml:124-190, bodies HFusionOps.cpp:538-639);
+ * hivm.hir.vadd/vsub/vmul/vdiv/vmax/vmin/vand/vor/vxor are this with the
+ * matching fn (HFusionToHIVM.cpp:327-359). */
+BSIR_API int32_t bsir_elemwise_binary(int32_t fn, int32_t dtype, int32_t rank, const int64_t *sizes,
+                                      const bsir_operand *a, const bsir_operand *b, void *out,
+                                      const int64_t *out_strides, void *stream);
+/* out(bool bytes) = a <pred> b; hfusion.compare (HFusionOps.cpp:642-720). */
+BSIR_API int32_t bsir_compare(int32_t fn, int32_t dtype, int32_t rank, const int64_t *sizes,
+                              const bsir_operand *a, const bsir_operand *b, void *out,
+                              const int64_t *out_strides, void *stream);
+/* out = cond ? a : b; hfusion.select (HFusionOps.cpp:723-743); cond is bool bytes. */
+BSIR_API int32_t bsir_select(int32_t dtype, int32_t rank, const int64_t *sizes,
+                             const bsir_operand *cond, const bsir_operand *a, const bsir_operand *b,
+                             void *out, const int64_t *out_strides, void *stream);
+/* hfusion.cast / hivm.hir.vcast (yaml:373-432, HIVMVectorOps.td:542-635). */
+BSIR_API int32_t bsir_cast(int32_t src_dtype, int32_t dst_dtype, int32_t round_mode,
+                           int32_t overflow_mode, int32_t rank, const int64_t *sizes,
+                           const void *src, const int64_t *src_strides, void *dst,
+                           const int64_t *dst_strides, void *stream);
+/* hivm.hir.load/store/copy (HIVMDMAOps.td:62-273): identity copy. */
+BSIR_API int32_t bsir_copy(int32_t dtype, int32_t rank, const int64_t *sizes, const void *src,
+                           const int64_t *src_strides, void *dst, const int64_t *dst_strides,
+                           void *stream);
+
+/* linalg.reduce / hivm.hir.vreduce over the last axis of a [rows, cols] view
+ * (Reduction.cpp:101-148).  dst is write-only: dst[r] = reduce(identity, src[r,:]).
+ * Float sums accumulate in f32 (f16/bf16 inputs are promoted). */
+BSIR_API int32_t bsir_reduce_last_axis(int32_t kind, int32_t dtype, int64_t rows, int64_t cols,
+                                       const void *src, int64_t src_row_stride, void *dst,
+                                       void *stream);
+/* Same over the first axis: dst[c] = reduce(src[:, c]). */
+BSIR_API int32_t bsir_reduce_first_axis(int32_t kind, int32_t dtype, int64_t rows, int64_t cols,
+                                        const void *src, int64_t src_row_stride, void *dst,
+                                        void *stream);
+
+/* Bytes of scratch bsir_reduce_with_index needs for this shape (0 = none). */
+BSIR_API int64_t bsir_reduce_with_index_workspace_bytes(int64_t rows, int64_t cols);
+/* hfusion.reduce_with_index over the last axis (HFusionStructuredOps.td:69-137,
+ * region HFusionOps.cpp:1506-1595).  Ties keep the lowest index when
+ * tie_break_left != 0, the highest otherwise.  dst_index is int32.
+ * `workspace` may be NULL: the library then uses its own per-device scratch
+ * (created on first use).  A caller-provided workspace must be zero-filled
+ * once before its first use; every call leaves it zero-filled again. */
+BSIR_API int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie_break_left,
+                                        int32_t nan_mode, int64_t rows, int64_t cols,
+                                        const void *src, int64_t src_row_stride, void *dst_value,
+                                        int32_t *dst_index, void *workspace,
+                                        int64_t workspace_bytes, void *stream);
+
+/* Fused LAST_AXIS_PBR pattern RMSNorm
+ * (test/bishengir-compile/hfusion/compile-rms-norm-fp16-split-n.mlir:13-71):
+ * y = cast_rint(gamma32 * (rstd * x32)), rstd = 1 / sqrt(sum(x32^2) * (1/cols) + eps);
+ * rstd_out (same dtype as x, may be NULL) = cast_rint(rstd). */
+BSIR_API int32_t bsir_rms_norm(int32_t dtype, int64_t rows, int64_t cols, const void *x,
+                               int64_t x_row_stride, const void *gamma, float eps, void *y,
+                               int64_t y_row_stride, void *rstd_out, void *stream);
+/* Fused softmax over the last axis
+ * (test/Dialect/Analysis/VFFusion/MaxParallelKind/softmax_small_shape.mlir:86-117). */
+BSIR_API int32_t bsir_softmax(int32_t dtype, int64_t rows, int64_t cols, const void *x,
+                              int64_t x_row_stride, void *y, int64_t y_row_stride, void *stream);
+/* Per-token dynamic int8 quantisation: scale[r] = max_j |x32[r,j]| / 127,
+ * q = hfusion.cast{round_mode, enable_saturate}(x32 / scale[r]) -> i8. */
+BSIR_API int32_t bsir_quant_per_token_i8(int32_t dtype, int32_t round_mode, int64_t rows,
+                                         int64_t cols, const void *x, int64_t x_row_stride,
+                                         int8_t *q, int64_t q_row_stride, float *scale,
+                                         void *stream);
+
+/* Bytes of scratch the W8A8 GEMM needs for this problem (0 = none). */
+BSIR_API int64_t bsir_matmul_w8a8_workspace_bytes(int64_t m, int64_t n, int64_t k,
+                                                  int32_t transpose_b);
+/* linalg.matmul i8 x i8 -> i32 (compile-dot-int8-fractal-c.mlir:25) with the
+ * composed dequant suffix: out = bf16_rint( f32(acc) * scale_a[m] * scale_b[n] ).
+ * a: [m,k] row-major int8 (lda elements per row); b: [k,n] row-major (ldb) or,
+ * with transpose_b, [n,k] row-major.  scale_a / scale_b may be NULL (= 1).
+ * acc_out (may be NULL): int32 [m,n] row-major accumulators, for parity checks.
+ * out (may be NULL when acc_out is given): out_dtype is BSIR_BF16 or BSIR_F16.
+ * workspace as for bsir_reduce_with_index (no zero-fill requirement). */
+BSIR_API int32_t bsir_matmul_w8a8(int64_t m, int64_t n, int64_t k, const int8_t *a, int64_t lda,
+                                  const int8_t *b, int64_t ldb, int32_t transpose_b,
+                                  const float *scale_a, const float *scale_b, int32_t out_dtype,
+                                  void *out, int64_t ldo, int32_t *acc_out, void *workspace,
+                                  int64_t workspace_bytes, void *stream);
+
+/* W4A16 group-quantised GEMM: out = bf16_rint( a . bf16_rint((q - z) * s) ), f32
+ * accumulation.  a: [m,k] bf16 row-major (lda); qweight: int32 [k/8, n], nibble i
+ * of word (r, c) (bits 4i..4i+3) is q[8r+i, c]; scales: bf16 [k/group, n];
+ * zeros: int32 [k/group, n/8], nibble i of word (g, c) is z[g, 8c+i].
+ * Requires k % group == 0, group % 32 == 0, n % 8 == 0. */
+BSIR_API int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t group, const void *a,
+                                   int64_t lda, const int32_t *qweight, const void *scales,
+                                   const int32_t *zeros, void *out, int64_t ldo, void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* B2: compiled-kernel ABI                                                   */
+/* ------------------------------------------------------------------------ */
+typedef enum {
+  BSIR_KERNEL_ELEMWISE_BINARY = 0, /* args: a, b, out                          */
+  BSIR_KERNEL_ELEMWISE_UNARY = 1,  /* args: x, out                             */
+  BSIR_KERNEL_CAST = 2,            /* args: src, dst                           */
+  BSIR_KERNEL_RMS_NORM = 3,        /* args: x, gamma, y, rstd (NULL allowed)   */
+  BSIR_KERNEL_SOFTMAX = 4,         /* args: x, y                               */
+  BSIR_KERNEL_QUANT_PER_TOKEN = 5, /* args: x, q, scale                        */
+  BSIR_KERNEL_REDUCE_WITH_INDEX = 6, /* args: src, dst_value, dst_index        */
+  BSIR_KERNEL_REDUCE = 7,          /* args: src, dst                           */
+  BSIR_KERNEL_MATMUL_W8A8 = 8,     /* args: a, scale_a, b, scale_b, out        */
+  BSIR_KERNEL_MATMUL_W4A16 = 9     /* args: a, qweight, scales, zeros, out     */
+} bsir_kernel_kind;
+
+/* What `bishengir-compile` would have baked into a kernel object: the op, its
+ * attributes and the static shape of the arguments (contiguous row-major). */
+typedef struct {
+  int32_t kind;      /* bsir_kernel_kind                                        */
+  int32_t fn;        /* unary/binary fn, reduce kind or reduce_with_index kind  */
+  int32_t dtype;     /* element type of the inputs                              */
+  int32_t dst_dtype; /* cast: destination type; matmul: output type             */
+  int32_t round_mode;
+  int32_t overflow_mode;
+  int32_t flags;     /* reduce_with_index: bit0 tie_break_left, bit1 nan_first;
+                        matmul_w8a8: bit0 transpose_b                          */
+  int32_t rank;
+  int64_t sizes[4];  /* elementwise: tensor shape; row ops: rows, cols;
+                        matmul: m, n, k, group                                  */
+  float eps;         /* rms_norm                                                */
+} bsir_kernel_desc;
+
+/* Register (or replace) a kernel under `name`; thread-safe. */
+BSIR_API int32_t bsir_kernel_register(const char *name, const bsir_kernel_desc *desc);
+BSIR_API int32_t bsir_kernel_unregister(const char *name);
+/* Number of pointer arguments the kernel takes, or a negative status. */
+BSIR_API int32_t bsir_kernel_num_args(const char *name);
+/* rtKernelLaunch analogue: args = array of device pointers, args_size = bytes
+ * of that array.  block_dim is a hint (the reference binds its outer tile loop
+ * to that many cores) and does not change results.  stream NULL = the stream
+ * of bsir_set_stream(). */
+BSIR_API int32_t bsir_launch(const char *name, uint32_t block_dim, void **args, size_t args_size,
+                             void *stream);
+
+/* ------------------------------------------------------------------------ */
+/* device bookkeeping                                                        */
+/* ------------------------------------------------------------------------ */
+/* Reads and clears the device-side error word of the current device (set when a
+ * bounded wait inside a kernel gave up); synchronises the device.  0 = clean. */
+BSIR_API int32_t bsir_device_error(void);
+/* Number of kernel launches this library has enqueued in this process. */
+BSIR_API int64_t bsir_launch_count(void);
+/* Frees the library-owned per-device scratch of the current device. */
+BSIR_API int32_t bsir_release_workspace(void);
+
+/* ------------------------------------------------------------------------ */
+/* B1: op-library symbols                                                    */
+/* ------------------------------------------------------------------------ */
+/* The full list is generated from the same tables as the definitions; see
+ * bsir_b200_ciface.h, included here so that one include declares everything. */
+#include "bsir_b200_ciface.h"
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BSIR_B200_H_ */

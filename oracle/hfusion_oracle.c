@@ -1,0 +1,914 @@
+/*
+ * hfusion_oracle.c -- CPU restatement of the reference's CPU lowering for the
+ * hot-path operator set.  TEST INFRASTRUCTURE ONLY: this file is the checker
+ * for the CUDA kernels (and the timed CPU baseline of the bench); nothing in
+ * the product library links, loads or calls it.
+ *
+ * What it restates.  The reference (BiShengIR) checks numerics by lowering
+ * HFusion/HIVM IR to upstream linalg, then `convert-linalg-to-loops`, then LLVM
+ * (bishengir/lib/ExecutionEngine/ExecutionEnginePipelines.cpp:39-90): scalar,
+ * single-threaded loop nests whose reductions accumulate sequentially in index
+ * order.  Each function below is that loop nest written by hand for one op,
+ * with the scalar body taken from the op's region builder; the citation is on
+ * the function.  Float arithmetic is IEEE binary32 with no contraction (build
+ * with -ffp-contract=off); bf16/f16 inputs are widened to f32, the chain runs
+ * in f32 and the result is rounded once, to nearest even
+ * (bishengir/lib/Dialect/HFusion/Transforms/LegalizeBF16.cpp:243-275 with
+ * SimplifyOps.cpp:105-230 removing the f32->bf16->f32 round trips).
+ *
+ * Parity status.  That pipeline needs the LLVM/MLIR fork in the reference's
+ * empty `third-party/llvm-project` submodule, so it cannot be built or run
+ * next to this file.  Pinned against the reference's own known answers: the
+ * cast constant-folder cases, the saturate example vector, the default
+ * round-mode table, the VecAdd end-to-end vector and the argmax combiner truth
+ * table (tests/test_oracle_pins.py lists file:line for each).  For softmax,
+ * RMSNorm, per-token quantisation and the two GEMMs the reference holds no
+ * numeric test: for those ops PARITY IS UNPINNED and rests on this restatement
+ * of the cited IR.
+ *
+ * OpenMP (`orc_set_threads`) parallelises over rows / independent elements
+ * only, never inside a reduction, so results do not depend on the thread count.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define ORC_API __attribute__((visibility("default")))
+
+enum { ORC_F32 = 0, ORC_F16, ORC_BF16, ORC_I8, ORC_I16, ORC_I32, ORC_I64, ORC_U8, ORC_U16, ORC_U32, ORC_U64, ORC_BOOL };
+
+static int g_threads = 1;
+ORC_API void orc_set_threads(int n) {
+  g_threads = n < 1 ? 1 : n;
+#ifdef _OPENMP
+  omp_set_num_threads(g_threads);
+#endif
+}
+ORC_API int orc_get_max_threads(void) {
+#ifdef _OPENMP
+  return omp_get_num_procs();
+#else
+  return 1;
+#endif
+}
+#define ORC_PAR_FOR _Pragma("omp parallel for schedule(static) if (g_threads > 1)")
+
+/* ---------------------------------------------------------------- scalars */
+static inline uint32_t f2u(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
+static inline float u2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+
+/* arith.extf bf16 -> f32 (exact) */
+static inline float bf16_to_f32(uint16_t h) { return u2f((uint32_t)h << 16); }
+/* arith.truncf f32 -> bf16, round to nearest even */
+static inline uint16_t f32_to_bf16(float f) {
+  uint32_t u = f2u(f);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u); /* quiet NaN */
+  uint32_t lsb = (u >> 16) & 1u;
+  u += 0x7fffu + lsb;
+  return (uint16_t)(u >> 16);
+}
+/* arith.extf f16 -> f32 (exact) */
+static inline float f16_to_f32(uint16_t h) {
+  uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1fu;
+  uint32_t man = h & 0x3ffu;
+  if (exp == 0) {
+    if (man == 0) return u2f(sign);
+    /* subnormal: value = man * 2^-24 */
+    float v = (float)man * 5.9604644775390625e-08f;
+    return (sign ? -v : v);
+  }
+  if (exp == 31) return u2f(sign | 0x7f800000u | (man << 13));
+  return u2f(sign | ((exp + 112u) << 23) | (man << 13));
+}
+/* f32 -> f16 with an explicit rounding direction.
+ * mode: 0 nearest-even, 1 toward zero.  Overflow: nearest -> inf, toward zero -> max finite. */
+static inline uint16_t f32_to_f16_mode(float f, int toward_zero) {
+  uint32_t u = f2u(f);
+  uint16_t sign = (uint16_t)((u >> 16) & 0x8000u);
+  uint32_t a = u & 0x7fffffffu;
+  if (a > 0x7f800000u) return (uint16_t)(sign | 0x7e00u);
+  if (a == 0x7f800000u) return (uint16_t)(sign | 0x7c00u);
+  int32_t e = (int32_t)(a >> 23) - 127;
+  uint32_t m = (a & 0x7fffffu) | 0x800000u; /* 24-bit significand */
+  if (a < 0x00800000u) return sign;          /* f32 subnormal: far below f16 range */
+  if (e > 15) return (uint16_t)(sign | (toward_zero ? 0x7bffu : 0x7c00u));
+  int shift;          /* number of low bits of m dropped */
+  uint32_t base;      /* exponent field of the result */
+  if (e >= -14) { shift = 13; base = (uint32_t)(e + 15); }
+  else { shift = 13 + (-14 - e); base = 0; if (shift > 25) return sign; }
+  uint32_t kept = m >> shift;
+  uint32_t rem = m & ((1u << shift) - 1u);
+  uint32_t half = 1u << (shift - 1);
+  if (!toward_zero && (rem > half || (rem == half && (kept & 1u)))) kept++;
+  /* kept includes the hidden bit for normals; adding base << 10 handles carries */
+  uint32_t r = (base ? ((base - 1u) << 10) : 0u) + kept;
+  if (!base) r = kept; /* subnormal (a carry to 0x400 lands on the smallest normal) */
+  if (r >= 0x7c00u) r = toward_zero ? 0x7bffu : 0x7c00u;
+  return (uint16_t)(sign | r);
+}
+static inline uint16_t f32_to_f16(float f) { return f32_to_f16_mode(f, 0); }
+
+static inline int dtype_size(int dt) {
+  switch (dt) {
+  case ORC_F32: case ORC_I32: case ORC_U32: return 4;
+  case ORC_F16: case ORC_BF16: case ORC_I16: case ORC_U16: return 2;
+  case ORC_I64: case ORC_U64: return 8;
+  default: return 1;
+  }
+}
+static inline int is_float(int dt) { return dt <= ORC_BF16; }
+static inline int is_unsigned(int dt) { return dt >= ORC_U8; }
+
+static inline float load_f(int dt, const void *p, int64_t i) {
+  switch (dt) {
+  case ORC_F32: return ((const float *)p)[i];
+  case ORC_F16: return f16_to_f32(((const uint16_t *)p)[i]);
+  default: return bf16_to_f32(((const uint16_t *)p)[i]);
+  }
+}
+static inline void store_f(int dt, void *p, int64_t i, float v) {
+  switch (dt) {
+  case ORC_F32: ((float *)p)[i] = v; break;
+  case ORC_F16: ((uint16_t *)p)[i] = f32_to_f16(v); break;
+  default: ((uint16_t *)p)[i] = f32_to_bf16(v); break;
+  }
+}
+static inline int64_t load_i(int dt, const void *p, int64_t i) {
+  switch (dt) {
+  case ORC_I8: return ((const int8_t *)p)[i];
+  case ORC_I16: return ((const int16_t *)p)[i];
+  case ORC_I32: return ((const int32_t *)p)[i];
+  case ORC_I64: return ((const int64_t *)p)[i];
+  case ORC_U8: case ORC_BOOL: return ((const uint8_t *)p)[i];
+  case ORC_U16: return ((const uint16_t *)p)[i];
+  case ORC_U32: return ((const uint32_t *)p)[i];
+  default: return (int64_t)((const uint64_t *)p)[i];
+  }
+}
+static inline void store_i(int dt, void *p, int64_t i, int64_t v) {
+  switch (dt) {
+  case ORC_I8: case ORC_U8: ((uint8_t *)p)[i] = (uint8_t)v; break;
+  case ORC_BOOL: ((uint8_t *)p)[i] = (uint8_t)(v & 1); break;
+  case ORC_I16: case ORC_U16: ((uint16_t *)p)[i] = (uint16_t)v; break;
+  case ORC_I32: case ORC_U32: ((uint32_t *)p)[i] = (uint32_t)v; break;
+  default: ((uint64_t *)p)[i] = (uint64_t)v; break;
+  }
+}
+static inline int int_bits(int dt) { return dt == ORC_BOOL ? 1 : 8 * dtype_size(dt); }
+/* wrap a 64-bit value into the value range of integer dtype dt */
+static inline int64_t wrap_int(int dt, int64_t v) {
+  int b = int_bits(dt);
+  if (b == 64) return v;
+  uint64_t m = ((uint64_t)1 << b) - 1u;
+  uint64_t u = (uint64_t)v & m;
+  if (!is_unsigned(dt) && dt != ORC_BOOL && (u >> (b - 1))) u |= ~m;
+  return (int64_t)u;
+}
+
+/* arith.maximumf / minimumf: NaN-propagating, -0 < +0 */
+static inline float maximumf_(float a, float b) {
+  if (a != a) return a;
+  if (b != b) return b;
+  if (a == 0.0f && b == 0.0f) return signbit(a) ? b : a;
+  return a > b ? a : b;
+}
+static inline float minimumf_(float a, float b) {
+  if (a != a) return a;
+  if (b != b) return b;
+  if (a == 0.0f && b == 0.0f) return signbit(a) ? a : b;
+  return a < b ? a : b;
+}
+/* arith.maxnumf / minnumf: the non-NaN operand wins */
+static inline float maxnumf_(float a, float b) { return fmaxf(a, b); }
+static inline float minnumf_(float a, float b) { return fminf(a, b); }
+
+/* ------------------------------------------------------------- elementwise */
+/* unary fn codes: hfusion.unary_fn values 0..26
+ * (bishengir/include/bishengir/Dialect/HFusion/IR/HFusionEnums.td:29-57), 100.. = linalg.unary_fn */
+static int unary_f32(int fn, float x, float *out) {
+  switch (fn) {
+  case 0: *out = maximumf_(0.0f, x); return 0;           /* relu = maximumf(0, x), HFusionOps.cpp:495-510 */
+  case 1: case 108: *out = sqrtf(x); return 0;
+  case 2: case 109: *out = 1.0f / sqrtf(x); return 0;    /* rsqrt is normalised to rec(sqrt): Normalize.cpp:2068 */
+  case 3: case 106: *out = 1.0f / x; return 0;           /* rec = divf(1, x), HFusionOps.cpp:512-519 */
+  case 5: case 111: *out = tanhf(x); return 0;
+  case 6: *out = sinf(x); return 0;
+  case 7: *out = cosf(x); return 0;
+  case 8: *out = atanf(x); return 0;
+  case 9: *out = tanf(x); return 0;
+  case 11: case 112: *out = erff(x); return 0;
+  case 12: *out = log2f(x); return 0;
+  case 13: *out = log10f(x); return 0;
+  case 14: *out = log1pf(x); return 0;
+  case 15: *out = exp2f(x); return 0;
+  case 16: *out = expm1f(x); return 0;
+  case 18: *out = asinf(x); return 0;
+  case 19: *out = acosf(x); return 0;
+  case 20: *out = asinhf(x); return 0;
+  case 21: *out = acoshf(x); return 0;
+  case 22: *out = atanhf(x); return 0;
+  case 23: *out = sinhf(x); return 0;
+  case 24: *out = lgammaf(x); return 0;
+  case 25: *out = coshf(x); return 0;
+  case 26: *out = nearbyintf(x); return 0;               /* math.roundeven */
+  case 100: *out = expf(x); return 0;
+  case 101: *out = logf(x); return 0;
+  case 102: *out = fabsf(x); return 0;
+  case 103: *out = ceilf(x); return 0;
+  case 104: *out = floorf(x); return 0;
+  case 105: *out = -x; return 0;
+  case 107: *out = roundf(x); return 0;
+  case 110: *out = x * x; return 0;
+  default: return -1;
+  }
+}
+static int unary_int(int fn, int dt, int64_t x, int64_t *out) {
+  switch (fn) {
+  case 0: *out = x > 0 ? x : 0; return 0;                 /* relu = maxsi(0, x) */
+  case 4: *out = wrap_int(dt, ~x); return 0;              /* vnot = xori(-1, x), HFusionOps.cpp:526-535 */
+  case 10: case 102: *out = wrap_int(dt, x < 0 ? -x : x); return 0; /* math.absi */
+  case 110: *out = wrap_int(dt, (int64_t)((uint64_t)x * (uint64_t)x)); return 0;
+  default: return -1;
+  }
+}
+
+/* hfusion.elemwise_unary / linalg.elemwise_unary
+ * (HFusionNamedStructuredOps.yaml:72-123; bodies HFusionOps.cpp:434-535).
+ * vnot on a float type acts on the raw bits, as the device library does
+ * (EltWise1D.cpp:1300-1316). */
+ORC_API int orc_elemwise_unary(int fn, int dt, const void *x, void *out, int64_t n) {
+  int rc = 0;
+  if (is_float(dt) && fn == 4) {
+    int sz = dtype_size(dt);
+    for (int64_t i = 0; i < n * sz; i++) ((uint8_t *)out)[i] = (uint8_t)~((const uint8_t *)x)[i];
+    return 0;
+  }
+  ORC_PAR_FOR
+  for (int64_t i = 0; i < n; i++) {
+    if (is_float(dt)) {
+      float r = 0.0f;
+      if (unary_f32(fn, load_f(dt, x, i), &r)) rc = -1;
+      store_f(dt, out, i, r);
+    } else {
+      int64_t r = 0;
+      if (unary_int(fn, dt, load_i(dt, x, i), &r)) rc = -1;
+      store_i(dt, out, i, r);
+    }
+  }
+  return rc;
+}
+
+static int64_t ipowi(int64_t b, int64_t e) { /* math.ipowi */
+  if (e < 0) return b == 1 ? 1 : (b == -1 ? ((e & 1) ? -1 : 1) : 0);
+  uint64_t r = 1, x = (uint64_t)b;
+  while (e) { if (e & 1) r *= x; x *= x; e >>= 1; }
+  return (int64_t)r;
+}
+/* binary fn codes: hfusion.binary_fn 0..20 (HFusionEnums.td:62-84), 100.. = linalg.binary_fn */
+static int binary_f32(int fn, float a, float b, float *out) {
+  switch (fn) {
+  case 3: *out = minimumf_(a, b); return 0;   /* minf  = arith.minimumf, HFusionOps.cpp:558-563 */
+  case 4: *out = maximumf_(a, b); return 0;   /* maxf  = arith.maximumf */
+  case 5: case 109: *out = powf(a, b); return 0;
+  case 6: case 7: *out = fmodf(a, b); return 0; /* arith.remf */
+  case 11: *out = ldexpf(a, (int)b); return 0;
+  case 16: *out = minnumf_(a, b); return 0;
+  case 17: *out = maxnumf_(a, b); return 0;
+  case 18: *out = atan2f(a, b); return 0;
+  case 19: case 103: *out = a / b; return 0;  /* divfhp: IEEE divide */
+  case 20: *out = copysignf(a, b); return 0;
+  case 100: *out = a + b; return 0;
+  case 101: *out = a - b; return 0;
+  case 102: *out = a * b; return 0;
+  case 105: case 107: *out = maximumf_(a, b); return 0; /* linalg max_* on floats = maximumf */
+  case 106: case 108: *out = minimumf_(a, b); return 0;
+  default: return -1;
+  }
+}
+static int binary_int(int fn, int dt, int64_t a, int64_t b, int64_t *out) {
+  int bits = int_bits(dt);
+  uint64_t mask = bits == 64 ? ~(uint64_t)0 : (((uint64_t)1 << bits) - 1u);
+  uint64_t ua = (uint64_t)a & mask, ub = (uint64_t)b & mask;
+  int64_t r;
+  switch (fn) {
+  case 0: r = a | b; break;
+  case 1: r = a & b; break;
+  case 2: r = a ^ b; break;
+  case 6: if (b == 0) return -2; r = (b == -1) ? 0 : a % b; break;             /* remsi */
+  case 7: if (ub == 0) return -2; r = (int64_t)(ua % ub); break;               /* remui */
+  case 8: r = (ub >= (uint64_t)bits) ? 0 : (int64_t)(ua << ub); break;         /* shli  */
+  case 9: r = is_unsigned(dt) ? ((ub >= (uint64_t)bits) ? 0 : (int64_t)(ua >> ub))
+                              : ((ub >= (uint64_t)bits) ? (a < 0 ? -1 : 0) : (a >> ub)); break;
+  case 10: r = (ub >= (uint64_t)bits) ? 0 : (int64_t)(ua >> ub); break;        /* shrui */
+  case 12: if (b == 0) return -2; { int64_t q = a / b; if ((a % b) && ((a < 0) == (b < 0))) q++; r = q; } break;
+  case 13: if (ub == 0) return -2; r = (int64_t)(ua / ub + (ua % ub ? 1 : 0)); break;
+  case 14: if (b == 0) return -2; { int64_t q = a / b; if ((a % b) && ((a < 0) != (b < 0))) q--; r = q; } break;
+  case 15: r = ipowi(a, b); break;
+  case 100: r = (int64_t)((uint64_t)a + (uint64_t)b); break;                   /* addi wraps */
+  case 101: r = (int64_t)((uint64_t)a - (uint64_t)b); break;
+  case 102: r = (int64_t)((uint64_t)a * (uint64_t)b); break;
+  case 103: if (b == 0) return -2; r = (b == -1) ? (int64_t)(0 - (uint64_t)a) : a / b; break; /* divsi */
+  case 104: if (ub == 0) return -2; r = (int64_t)(ua / ub); break;
+  case 105: r = a > b ? a : b; break;
+  case 106: r = a < b ? a : b; break;
+  case 107: r = ua > ub ? a : b; break;
+  case 108: r = ua < ub ? a : b; break;
+  default: return -1;
+  }
+  *out = wrap_int(dt, r);
+  return 0;
+}
+
+/* hfusion.elemwise_binary / linalg.elemwise_binary (yaml:124-190; bodies
+ * HFusionOps.cpp:538-639); hivm.hir.vadd lowers to linalg.add on the CPU path
+ * (bishengir/lib/ExecutionEngine/ConvertHIVMToUpstream.cpp:1704).
+ * a_stride / b_stride are 1 (tensor) or 0 (scalar operand / broadcast).
+ * vand/vor on float types act on raw bits (device library behaviour). */
+ORC_API int orc_elemwise_binary(int fn, int dt, const void *a, int64_t a_stride, const void *b,
+                                int64_t b_stride, void *out, int64_t n) {
+  int rc = 0;
+  if (is_float(dt) && fn <= 2) {
+    int sz = dtype_size(dt);
+    for (int64_t i = 0; i < n; i++)
+      for (int k = 0; k < sz; k++) {
+        uint8_t x = ((const uint8_t *)a)[i * a_stride * sz + k], y = ((const uint8_t *)b)[i * b_stride * sz + k];
+        ((uint8_t *)out)[i * sz + k] = fn == 0 ? (x | y) : fn == 1 ? (x & y) : (x ^ y);
+      }
+    return 0;
+  }
+  ORC_PAR_FOR
+  for (int64_t i = 0; i < n; i++) {
+    if (is_float(dt)) {
+      float r = 0.0f;
+      if (binary_f32(fn, load_f(dt, a, i * a_stride), load_f(dt, b, i * b_stride), &r)) rc = -1;
+      store_f(dt, out, i, r);
+    } else {
+      int64_t r = 0;
+      int e = binary_int(fn, dt, load_i(dt, a, i * a_stride), load_i(dt, b, i * b_stride), &r);
+      if (e == -1) rc = -1;
+      store_i(dt, out, i, r);
+    }
+  }
+  return rc;
+}
+
+/* hfusion.compare (yaml:275-322; HFusionOps.cpp:642-720): float predicates are
+ * ordered (false on NaN) except vne, which is unordered-or-not-equal. */
+ORC_API int orc_compare(int fn, int dt, const void *a, int64_t a_stride, const void *b,
+                        int64_t b_stride, uint8_t *out, int64_t n) {
+  int bits = int_bits(dt);
+  uint64_t mask = bits == 64 ? ~(uint64_t)0 : (((uint64_t)1 << bits) - 1u);
+  for (int64_t i = 0; i < n; i++) {
+    int r;
+    if (is_float(dt)) {
+      float x = load_f(dt, a, i * a_stride), y = load_f(dt, b, i * b_stride);
+      switch (fn) {
+      case 0: r = x == y; break;
+      case 1: r = !(x == y); break;
+      case 2: r = x <= y; break;
+      case 3: r = x < y; break;
+      case 4: r = x >= y; break;
+      case 5: r = x > y; break;
+      default: return -1;
+      }
+    } else {
+      int64_t x = load_i(dt, a, i * a_stride), y = load_i(dt, b, i * b_stride);
+      uint64_t ux = (uint64_t)x & mask, uy = (uint64_t)y & mask;
+      switch (fn) {
+      case 0: r = x == y; break;
+      case 1: r = x != y; break;
+      case 2: r = x <= y; break;
+      case 3: r = x < y; break;
+      case 4: r = x >= y; break;
+      case 5: r = x > y; break;
+      case 6: r = ux <= uy; break;
+      case 7: r = ux < uy; break;
+      case 8: r = ux >= uy; break;
+      case 9: r = ux > uy; break;
+      default: return -1;
+      }
+    }
+    out[i] = (uint8_t)r;
+  }
+  return 0;
+}
+
+/* hfusion.select = arith.select (HFusionOps.cpp:723-743) */
+ORC_API int orc_select(int dt, const uint8_t *cond, int64_t c_stride, const void *a, int64_t a_stride,
+                       const void *b, int64_t b_stride, void *out, int64_t n) {
+  int sz = dtype_size(dt);
+  for (int64_t i = 0; i < n; i++) {
+    const uint8_t *s = cond[i * c_stride] ? (const uint8_t *)a + i * a_stride * sz
+                                          : (const uint8_t *)b + i * b_stride * sz;
+    memcpy((uint8_t *)out + i * sz, s, (size_t)sz);
+  }
+  return 0;
+}
+
+/* -------------------------------------------------------------------- cast */
+/* Round a double to an integral double under hfusion.round_mode
+ * (HFusionEnums.td:122-141; the constant folder does the same through
+ * APFloat::convertToInteger(rm), HFusionOps.cpp:1951-1994). */
+static double round_mode_apply(double x, int mode) {
+  switch (mode) {
+  case 0: return nearbyint(x);                 /* rint : nearest, ties to even (default FP env) */
+  case 1: return round(x);                     /* round: nearest, ties away from zero */
+  case 2: return floor(x);
+  case 3: return ceil(x);
+  case 4: case 6: return trunc(x);
+  case 5: {                                    /* odd (von Neumann): inexact -> the odd neighbour */
+    double t = trunc(x);
+    if (t == x) return x;
+    if (fmod(t, 2.0) == 0.0) return t + (x > 0 ? 1.0 : -1.0);
+    return t;
+  }
+  default: return nearbyint(x);
+  }
+}
+static void int_range(int dt, double *lo, double *hi) {
+  int b = int_bits(dt);
+  if (dt == ORC_BOOL) { *lo = 0; *hi = 1; return; }
+  if (is_unsigned(dt)) { *lo = 0; *hi = ldexp(1.0, b) - 1.0; }
+  else { *lo = -ldexp(1.0, b - 1); *hi = ldexp(1.0, b - 1) - 1.0; }
+}
+/* float -> int for one element.  overflow_mode: 0 wrap, 1 saturate (NaN -> 0). */
+static int64_t float_to_int(double x, int dst, int round_mode, int saturate) {
+  double lo, hi;
+  int_range(dst, &lo, &hi);
+  if (x != x) return 0;
+  double r = round_mode_apply(x, round_mode);
+  if (saturate) {
+    if (r < lo) r = lo;
+    if (r > hi) r = hi;
+    if (r >= 9223372036854775808.0) return INT64_MAX;
+    return (dst == ORC_U64 && r >= 9223372036854775808.0) ? INT64_MAX : (int64_t)r;
+  }
+  /* wrap: exact integer value modulo 2^bits (values beyond the int64 range keep
+   * only multiples of large powers of two, whose low 64 bits are zero) */
+  if (fabs(r) < 9223372036854775808.0) return wrap_int(dst, (int64_t)r);
+  if (!(fabs(r) < 1.0e300)) return 0; /* +-inf */
+  double m = fmod(r, 18446744073709551616.0);
+  if (m < 0) m += 18446744073709551616.0;
+  uint64_t u = (uint64_t)m;
+  return wrap_int(dst, (int64_t)u);
+}
+/* int -> float under a rounding direction (the folder: convertFromAPInt(rm),
+ * HFusionOps.cpp:1996-2004).  Only nearest-even matters for <= 32-bit ints into
+ * f32 when the value fits 24 bits; directed modes are honoured through double. */
+static float int_to_f32_mode(int64_t v, int is_u, int mode) {
+  double d = is_u ? (double)(uint64_t)v : (double)v; /* exact for |v| < 2^53 */
+  float f = (float)d;                                 /* nearest even */
+  if (mode == 0 || (double)f == d) return f;
+  float dn = (double)f > d ? nextafterf(f, -INFINITY) : f;
+  float up = (double)f < d ? nextafterf(f, INFINITY) : f;
+  switch (mode) {
+  case 2: return dn;
+  case 3: return up;
+  case 4: case 6: return d > 0 ? dn : up;
+  case 1: { double a = d - (double)dn, b = (double)up - d; if (a == b) return d > 0 ? up : dn; return a < b ? dn : up; }
+  default: return f;
+  }
+}
+
+/* hfusion.cast / hivm.hir.vcast (yaml:373-432; region HFusionOps.cpp:762-796,
+ * 845-861; meaning of the modes HFusionEnums.td:122-141).
+ * overflow_mode: 0 wrap, 1 saturate,
+ *   2 = f32 -> f16 (toward zero) -> i8 (toward zero, saturating), the rewrite the
+ *       reference applies under overflow_mode="saturate" (Normalize.cpp:3826-3836),
+ *   3 = f32 -> f16 -> i8 with round_mode applied at both steps, saturating
+ *       (lib/Dialect/HIVM/Transforms/HIVMDecomposeOp.cpp:101-127,160-190).
+ * Same-type float casts round to an integral value (folder KAT 2.8 -> 3.0,
+ * test/Dialect/HFusion/canonicalize.mlir:159-166). */
+ORC_API int orc_cast(int src_dt, int dst_dt, int round_mode, int overflow_mode, const void *src,
+                     void *dst, int64_t n) {
+  if (round_mode < 0 || round_mode > 6) return -1;
+  ORC_PAR_FOR
+  for (int64_t i = 0; i < n; i++) {
+    if (is_float(src_dt) && is_float(dst_dt)) {
+      float x = load_f(src_dt, src, i);
+      if (src_dt == dst_dt) { store_f(dst_dt, dst, i, (float)round_mode_apply((double)x, round_mode)); continue; }
+      if (dst_dt == ORC_F32) { ((float *)dst)[i] = x; continue; }   /* extf: exact */
+      if (round_mode == 0) { store_f(dst_dt, dst, i, x); continue; } /* truncf: nearest even */
+      /* directed narrowing: pick between the two neighbours of x in the target type */
+      uint16_t ne = dst_dt == ORC_F16 ? f32_to_f16(x) : f32_to_bf16(x);
+      float fne = dst_dt == ORC_F16 ? f16_to_f32(ne) : bf16_to_f32(ne);
+      if (fne == x || x != x) { ((uint16_t *)dst)[i] = ne; continue; }
+      /* the other neighbour: step one ulp of the target toward x */
+      uint16_t other = ne;
+      int up_needed = fne < x;
+      if ((ne & 0x7fffu) == 0) other = (uint16_t)((up_needed ? 0x0000u : 0x8000u) | 1u);
+      else if (((ne & 0x8000u) == 0) == up_needed) other = (uint16_t)(ne + 1u); else other = (uint16_t)(ne - 1u);
+      float fo = dst_dt == ORC_F16 ? f16_to_f32(other) : bf16_to_f32(other);
+      float lo = fne < fo ? fne : fo, hi = fne < fo ? fo : fne;
+      uint16_t blo = fne < fo ? ne : other, bhi = fne < fo ? other : ne;
+      uint16_t pick;
+      switch (round_mode) {
+      case 2: pick = blo; break;
+      case 3: pick = bhi; break;
+      case 4: case 6: pick = x > 0 ? blo : bhi; break;
+      case 1: { float dl = x - lo, dh = hi - x; pick = dl < dh ? blo : dl > dh ? bhi : (x > 0 ? bhi : blo); break; }
+      case 5: pick = (blo & 1u) ? blo : bhi; break;
+      default: pick = ne; break;
+      }
+      if (isinf(lo) && (round_mode == 3 || ((round_mode == 4 || round_mode == 6) && x < 0))) pick = bhi;
+      if (isinf(hi) && (round_mode == 2 || ((round_mode == 4 || round_mode == 6) && x > 0))) pick = blo;
+      ((uint16_t *)dst)[i] = pick;
+    } else if (is_float(src_dt)) {
+      float x = load_f(src_dt, src, i);
+      int64_t r;
+      if (overflow_mode == 2 || overflow_mode == 3) {
+        int rm = overflow_mode == 2 ? 4 : round_mode;
+        float h;
+        if (src_dt == ORC_F32) {
+          if (rm == 4) h = f16_to_f32(f32_to_f16_mode(x, 1));
+          else { /* round_mode at the f16 step */
+            uint16_t tmp; float xx = x;
+            orc_cast(ORC_F32, ORC_F16, rm, 0, &xx, &tmp, 1);
+            h = f16_to_f32(tmp);
+          }
+        } else h = x;
+        if (isinf(h)) h = h > 0 ? 65504.0f : -65504.0f;
+        r = float_to_int((double)h, dst_dt, rm, 1);
+      } else {
+        r = float_to_int((double)x, dst_dt, round_mode, overflow_mode == 1);
+      }
+      store_i(dst_dt, dst, i, r);
+    } else if (is_float(dst_dt)) {
+      int64_t v = load_i(src_dt, src, i);
+      float f = int_to_f32_mode(v, is_unsigned(src_dt) || src_dt == ORC_BOOL, round_mode);
+      if (dst_dt == ORC_F32) ((float *)dst)[i] = f;
+      else {
+        /* one rounding from the exact integer: go through double (exact for < 2^53) */
+        double d = (is_unsigned(src_dt) || src_dt == ORC_BOOL) ? (double)(uint64_t)v : (double)v;
+        float g = (float)d;
+        if ((double)g != d) { /* avoid double rounding: sticky bit trick (round to odd in f32) */
+          uint32_t u = f2u(g);
+          float toward = (fabs((double)g) > fabs(d)) ? u2f(u - 1u) : g;
+          g = u2f(f2u(toward) | 1u);
+        }
+        store_f(dst_dt, dst, i, g);
+      }
+    } else {
+      int64_t v = load_i(src_dt, src, i);
+      if (overflow_mode == 1) {
+        double lo, hi; int_range(dst_dt, &lo, &hi);
+        if ((double)v < lo) v = (int64_t)lo;
+        if ((double)v > hi) v = (hi >= 9223372036854775807.0) ? INT64_MAX : (int64_t)hi;
+      }
+      store_i(dst_dt, dst, i, wrap_int(dst_dt, v));
+    }
+  }
+  return 0;
+}
+
+/* -------------------------------------------------------------- reductions */
+/* linalg.reduce over the last axis, one row at a time, acc = combiner(in, acc)
+ * in index order (ConvertHIVMToUpstream.cpp:573-753; init values
+ * bishengir/lib/Dialect/HIVM/IR/HIVMVectorOps.cpp:571-640).  kind: 0 sum 1 prod
+ * 2 max 3 min 4 any 5 all 6 xori 7 ori 8 andi.  f16/bf16 accumulate in f32
+ * (Normalize.cpp:7679-7716) and round once at the end.  row_stride in elements. */
+ORC_API int orc_reduce_last_axis(int kind, int dt, const void *src, int64_t rows, int64_t cols,
+                                 int64_t row_stride, void *dst) {
+  if (kind < 0 || kind > 8) return -1;
+  ORC_PAR_FOR
+  for (int64_t r = 0; r < rows; r++) {
+    if (is_float(dt)) {
+      float acc = kind == 0 ? 0.0f : kind == 1 ? 1.0f : (kind == 2 || kind == 4) ? -INFINITY : INFINITY;
+      for (int64_t j = 0; j < cols; j++) {
+        float x = load_f(dt, src, r * row_stride + j);
+        switch (kind) {
+        case 0: acc = x + acc; break;
+        case 1: acc = x * acc; break;
+        case 2: case 4: acc = maximumf_(x, acc); break;
+        default: acc = minimumf_(x, acc); break;
+        }
+      }
+      store_f(dt, dst, r, acc);
+    } else {
+      double lo, hi; int_range(dt, &lo, &hi);
+      int64_t acc;
+      switch (kind) {
+      case 0: case 6: case 7: acc = 0; break;
+      case 1: acc = 1; break;
+      case 2: case 4: acc = is_unsigned(dt) ? 0 : (int64_t)lo; break;
+      case 3: case 5: acc = (dt == ORC_U64) ? -1 : (dt == ORC_I64 ? INT64_MAX : (int64_t)hi); break;
+      default: acc = -1; break; /* andi */
+      }
+      acc = wrap_int(dt, acc);
+      for (int64_t j = 0; j < cols; j++) {
+        int64_t x = load_i(dt, src, r * row_stride + j), t = 0;
+        switch (kind) {
+        case 0: binary_int(100, dt, x, acc, &t); break;
+        case 1: binary_int(102, dt, x, acc, &t); break;
+        case 2: case 4: binary_int(is_unsigned(dt) ? 107 : 105, dt, x, acc, &t); break;
+        case 3: case 5: binary_int(is_unsigned(dt) ? 108 : 106, dt, x, acc, &t); break;
+        case 6: t = x ^ acc; break;
+        case 7: t = x | acc; break;
+        default: t = x & acc; break;
+        }
+        acc = wrap_int(dt, t);
+      }
+      store_i(dt, dst, r, acc);
+    }
+  }
+  return 0;
+}
+
+/* Same over the first axis: dst[c] = reduce_r src[r, c], r ascending. */
+ORC_API int orc_reduce_first_axis(int kind, int dt, const void *src, int64_t rows, int64_t cols,
+                                  int64_t row_stride, void *dst) {
+  int sz = dtype_size(dt);
+  uint8_t *col = (uint8_t *)malloc((size_t)(rows > 0 ? rows : 1) * (size_t)sz);
+  if (!col) return -3;
+  int rc = 0;
+  for (int64_t c = 0; c < cols && !rc; c++) {
+    for (int64_t r = 0; r < rows; r++)
+      memcpy(col + r * sz, (const uint8_t *)src + (r * row_stride + c) * sz, (size_t)sz);
+    rc = orc_reduce_last_axis(kind, dt, col, 1, rows, rows, (uint8_t *)dst + c * sz);
+  }
+  free(col);
+  return rc;
+}
+
+/* hfusion.reduce_with_index over the last axis
+ * (HFusionStructuredOps.td:69-137).  kind: 0 min, 1 max.  dst is write-only:
+ * the accumulator starts at the identity (-inf / +inf, int extrema) with index 0.
+ *
+ * nan_mode 0 -- the op's region as convert-linalg-to-loops runs it
+ *   (HFusionOps.cpp:1506-1523, 1541-1595):
+ *     r = maximumf(in, acc); p = r OGT acc; idx = p ? j : idx; acc = r
+ *   so ties keep the first index and, once acc is NaN, nothing moves.  The region
+ *   has no right-tie form; tie_break_left = 0 is the device library's
+ *   `_right` variant (Reduction.cpp:85-99) and uses OGE, moving on ties.
+ * nan_mode 1 -- the device / Triton combiner: the first NaN wins value and index
+ *   (Normalize.cpp:2688-2777; scalar fallback
+ *   bishengir/lib/Template/lib/Vector/Reduction/ReduceR_With_Index.cpp:83-125;
+ *   truth table test/Conversion/LinalgToHFusion/linalg-to-hfusion.mlir:224-241). */
+ORC_API int orc_reduce_with_index(int kind, int dt, int tie_break_left, int nan_mode, const void *src,
+                                  int64_t rows, int64_t cols, int64_t row_stride, void *dst_value,
+                                  int32_t *dst_index) {
+  if (kind != 0 && kind != 1) return -1;
+  ORC_PAR_FOR
+  for (int64_t r = 0; r < rows; r++) {
+    int32_t idx = 0;
+    if (is_float(dt)) {
+      float acc = kind ? -INFINITY : INFINITY;
+      for (int64_t j = 0; j < cols; j++) {
+        float x = load_f(dt, src, r * row_stride + j);
+        if (nan_mode == 1) {
+          if (acc != acc) break;
+          int take = (x != x) || (kind ? x > acc : x < acc) || (!tie_break_left && x == acc);
+          if (j == 0) take = 1;
+          if (take) { acc = x; idx = (int32_t)j; }
+        } else {
+          float m = kind ? maximumf_(x, acc) : minimumf_(x, acc);
+          int p = kind ? (tie_break_left ? m > acc : x >= acc) : (tie_break_left ? m < acc : x <= acc);
+          if (p) idx = (int32_t)j;
+          acc = m;
+        }
+      }
+      store_f(dt, dst_value, r, acc);
+    } else {
+      double lo, hi; int_range(dt, &lo, &hi);
+      int64_t acc = kind ? (dt == ORC_I64 ? INT64_MIN : (int64_t)lo) : (dt == ORC_I64 ? INT64_MAX : (int64_t)hi);
+      for (int64_t j = 0; j < cols; j++) {
+        int64_t x = load_i(dt, src, r * row_stride + j);
+        int p = kind ? (tie_break_left ? x > acc : x >= acc) : (tie_break_left ? x < acc : x <= acc);
+        if (p) { idx = (int32_t)j; acc = x; }
+      }
+      store_i(dt, dst_value, r, acc);
+    }
+    dst_index[r] = idx;
+  }
+  return 0;
+}
+
+/* ----------------------------------------------------------- fused patterns */
+/* RMSNorm, LAST_AXIS_PBR fusion unit
+ * (test/bishengir-compile/hfusion/compile-rms-norm-fp16-split-n.mlir:13-71):
+ *   x32 = cast(x); sq = x32*x32; ss = reduce addf (sequential); mean = ss * (1/float(cols));
+ *   v = mean + eps; s = sqrt(v); r = 1/s; y = cast_rint(gamma32 * (r * x32)); rstd = cast_rint(r) */
+ORC_API int orc_rms_norm(int dt, const void *x, const void *gamma, float eps, int64_t rows,
+                         int64_t cols, int64_t x_row_stride, void *y, int64_t y_row_stride,
+                         void *rstd_out) {
+  if (!is_float(dt)) return -1;
+  const float avg = 1.0f / (float)(uint32_t)cols;
+  ORC_PAR_FOR
+  for (int64_t r = 0; r < rows; r++) {
+    float ss = 0.0f;
+    for (int64_t j = 0; j < cols; j++) {
+      float v = load_f(dt, x, r * x_row_stride + j);
+      float sq = v * v;
+      ss = sq + ss;
+    }
+    float mean = ss * avg;
+    float s = sqrtf(mean + eps);
+    float rr = 1.0f / s;
+    for (int64_t j = 0; j < cols; j++) {
+      float m0 = rr * load_f(dt, x, r * x_row_stride + j);
+      float m1 = load_f(dt, gamma, j) * m0;
+      store_f(dt, y, r * y_row_stride + j, m1);
+    }
+    if (rstd_out) store_f(dt, rstd_out, r, rr);
+  }
+  return 0;
+}
+
+/* softmax over the last axis
+ * (test/Dialect/Analysis/VFFusion/MaxParallelKind/softmax_small_shape.mlir:86-117):
+ *   x32 = cast(x); masked = isnan(x32) ? -inf : x32; m = reduce maximumf(masked), init -inf;
+ *   e = exp(x32 - m); s = reduce addf(e), init 0; y = cast_rint(e / s) */
+ORC_API int orc_softmax(int dt, const void *x, int64_t rows, int64_t cols, int64_t x_row_stride, void *y,
+                        int64_t y_row_stride) {
+  if (!is_float(dt)) return -1;
+  int rc = 0;
+  ORC_PAR_FOR
+  for (int64_t r = 0; r < rows; r++) {
+    float *e = (float *)malloc(sizeof(float) * (size_t)(cols > 0 ? cols : 1));
+    if (!e) { rc = -3; continue; }
+    float m = -INFINITY;
+    for (int64_t j = 0; j < cols; j++) {
+      float v = load_f(dt, x, r * x_row_stride + j);
+      if (v != v) v = -INFINITY;
+      m = maximumf_(v, m);
+    }
+    float s = 0.0f;
+    for (int64_t j = 0; j < cols; j++) {
+      e[j] = expf(load_f(dt, x, r * x_row_stride + j) - m);
+      s = e[j] + s;
+    }
+    for (int64_t j = 0; j < cols; j++) store_f(dt, y, r * y_row_stride + j, e[j] / s);
+    free(e);
+  }
+  return rc;
+}
+
+/* Per-token dynamic int8 quantisation (composition of elemwise abs, reduce
+ * maximumf, divf and hfusion.cast{round_mode, enable_saturate = true}):
+ *   x32 = cast(x); amax = reduce maximumf(|x32|), init -inf... the |.| makes 0 the floor;
+ *   scale = amax / 127; q = cast(x32 / scale) -> i8 saturating (NaN -> 0).
+ * overflow_mode as in orc_cast (1 = the attribute semantics). */
+ORC_API int orc_quant_per_token_i8(int dt, int round_mode, int overflow_mode, const void *x, int64_t rows,
+                                   int64_t cols, int64_t x_row_stride, int8_t *q, int64_t q_row_stride,
+                                   float *scale) {
+  if (!is_float(dt)) return -1;
+  ORC_PAR_FOR
+  for (int64_t r = 0; r < rows; r++) {
+    float amax = -INFINITY;
+    for (int64_t j = 0; j < cols; j++) amax = maximumf_(fabsf(load_f(dt, x, r * x_row_stride + j)), amax);
+    if (cols == 0) amax = 0.0f;
+    float sc = amax / 127.0f;
+    scale[r] = sc;
+    for (int64_t j = 0; j < cols; j++) {
+      float v = load_f(dt, x, r * x_row_stride + j) / sc;
+      int8_t o;
+      orc_cast(ORC_F32, ORC_I8, round_mode, overflow_mode, &v, &o, 1);
+      q[r * q_row_stride + j] = o;
+    }
+  }
+  return 0;
+}
+
+/* linalg.matmul i8 x i8 -> i32 (test/bishengir-compile/hivm/compile-dot-int8-fractal-c.mlir:25;
+ * body: sext both operands to i32, muli, addi, k ascending) followed by the
+ * composed dequant suffix  out = cast_rint( (sitofp(acc) * sa[m]) * sw[n] ).
+ * b is [k,n] row-major (ldb) or, with transpose_b, [n,k].  acc_out / out / sa / sw may be NULL.
+ * out_dt: ORC_BF16 or ORC_F16 (f16 saturates at +-65504 instead of overflowing to inf, as
+ * the fixpipe S322F16 pre-quant does: bishengir/lib/Dialect/HIVM/Transforms/InlineFixpipe.cpp:876-884). */
+ORC_API int orc_matmul_w8a8(int64_t m, int64_t n, int64_t k, const int8_t *a, int64_t lda, const int8_t *b,
+                            int64_t ldb, int transpose_b, const float *sa, const float *sw, int out_dt,
+                            void *out, int64_t ldo, int32_t *acc_out, int64_t ldacc) {
+  ORC_PAR_FOR
+  for (int64_t i = 0; i < m; i++) {
+    int32_t *acc = (int32_t *)calloc((size_t)(n > 0 ? n : 1), sizeof(int32_t));
+    if (!acc) continue;
+    if (transpose_b) {
+      for (int64_t j = 0; j < n; j++) {
+        int32_t s = 0;
+        for (int64_t p = 0; p < k; p++) s += (int32_t)a[i * lda + p] * (int32_t)b[j * ldb + p];
+        acc[j] = s;
+      }
+    } else {
+      for (int64_t p = 0; p < k; p++) {
+        int32_t av = a[i * lda + p];
+        const int8_t *brow = b + p * ldb;
+        for (int64_t j = 0; j < n; j++) acc[j] += av * (int32_t)brow[j];
+      }
+    }
+    for (int64_t j = 0; j < n; j++) {
+      if (acc_out) acc_out[i * ldacc + j] = acc[j];
+      if (out) {
+        float f = (float)acc[j];
+        if (sa) f = f * sa[i];
+        if (sw) f = f * sw[j];
+        if (out_dt == ORC_F16) {
+          if (f > 65504.0f) f = 65504.0f;
+          if (f < -65504.0f) f = -65504.0f;
+        }
+        store_f(out_dt, out, i * ldo + j, f);
+      }
+    }
+    free(acc);
+  }
+  return 0;
+}
+
+/* W4A16 group-quantised GEMM as the composed prefix + linalg.matmul:
+ *   w[kk, j] = cast_rint_bf16( (sitofp(q) - sitofp(z)) * extf(s) )   (f32 arithmetic)
+ *   acc = sum_kk extf(a[i,kk]) * extf(w[kk,j])  in f32, kk ascending (matmul body: extf, mulf, addf)
+ *   out = cast_rint_bf16(acc)
+ * Packing (defined by this project; the reference defines none): qweight int32 [k/8, n], nibble t
+ * of word (r, j) = q[8r+t, j]; scales bf16 [k/group, n]; zeros int32 [k/group, n/8], nibble t of
+ * word (g, c) = z[g, 8c+t]. */
+ORC_API int orc_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t group, const uint16_t *a, int64_t lda,
+                             const int32_t *qweight, const uint16_t *scales, const int32_t *zeros,
+                             uint16_t *out, int64_t ldo) {
+  if (group <= 0 || k % group || k % 8 || n % 8) return -1;
+  float *w = (float *)malloc(sizeof(float) * (size_t)k * (size_t)n);
+  if (!w) return -3;
+  ORC_PAR_FOR
+  for (int64_t kk = 0; kk < k; kk++) {
+    int64_t g = kk / group;
+    for (int64_t j = 0; j < n; j++) {
+      uint32_t word = (uint32_t)qweight[(kk / 8) * n + j];
+      float qv = (float)(int32_t)((word >> (4 * (kk % 8))) & 0xfu);
+      uint32_t zw = (uint32_t)zeros[g * (n / 8) + j / 8];
+      float zv = (float)(int32_t)((zw >> (4 * (j % 8))) & 0xfu);
+      float d = (qv - zv) * bf16_to_f32(scales[g * n + j]);
+      w[kk * n + j] = bf16_to_f32(f32_to_bf16(d));
+    }
+  }
+  ORC_PAR_FOR
+  for (int64_t j0 = 0; j0 < n; j0 += 64) {
+    int64_t j1 = j0 + 64 < n ? j0 + 64 : n;
+    for (int64_t i = 0; i < m; i++) {
+      float acc[64];
+      for (int64_t j = j0; j < j1; j++) acc[j - j0] = 0.0f;
+      for (int64_t kk = 0; kk < k; kk++) {
+        float av = bf16_to_f32(a[i * lda + kk]);
+        const float *wr = w + kk * n;
+        for (int64_t j = j0; j < j1; j++) { float p = av * wr[j]; acc[j - j0] = acc[j - j0] + p; }
+      }
+      for (int64_t j = j0; j < j1; j++) out[i * ldo + j] = f32_to_bf16(acc[j - j0]);
+    }
+  }
+  free(w);
+  return 0;
+}
+
+/* ----------------------------------------------------------------- helpers */
+/* Conversions exposed so the tests can check them against independent ones. */
+ORC_API float orc_bf16_to_f32(uint16_t h) { return bf16_to_f32(h); }
+ORC_API uint16_t orc_f32_to_bf16(float f) { return f32_to_bf16(f); }
+ORC_API float orc_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
+ORC_API uint16_t orc_f32_to_f16(float f) { return f32_to_f16(f); }
+ORC_API uint16_t orc_f32_to_f16_rz(float f) { return f32_to_f16_mode(f, 1); }
+/* Compares the hand-written f16 conversions with the compiler's _Float16 on `n` pseudo-random
+ * bit patterns plus every f16 value; returns the number of disagreements (NaN payloads ignored). */
+ORC_API int64_t orc_selftest_f16(int64_t n) {
+  int64_t bad = 0;
+  uint32_t s = 12345u;
+  for (uint32_t h = 0; h < 65536u; h++) {
+    _Float16 t; uint16_t hh = (uint16_t)h; memcpy(&t, &hh, 2);
+    float a = f16_to_f32(hh), b = (float)t;
+    if (!((a != a && b != b) || f2u(a) == f2u(b))) bad++;
+  }
+  for (int64_t i = 0; i < n; i++) {
+    s = s * 1664525u + 1013904223u;
+    uint32_t bits = s ^ (s >> 7);
+    if ((i & 3) == 0) bits = (bits & 0x807fffffu) | ((100u + (bits >> 23) % 40u) << 23); /* near the f16 range */
+    float f = u2f(bits);
+    _Float16 t = (_Float16)f; uint16_t want; memcpy(&want, &t, 2);
+    uint16_t got = f32_to_f16(f);
+    if (f != f) { if ((got & 0x7c00u) != 0x7c00u || !(got & 0x3ffu)) bad++; continue; }
+    if (got != want) bad++;
+  }
+  return bad;
+}
+
+/* Check of the reciprocal-based division used by the CUDA per-token quantiser:
+ *   r = RN(1/s); q0 = RN(x*r); e0 = fma(-q0, s, x); q1 = fma(e0, r, q0);
+ *   e1 = fma(-q1, s, x); q2 = fma(e1, r, q1)
+ * For every finite bf16 x with |x| <= amax (amax = 127*s rounded up to bf16 range) it must
+ * hold that nearbyint(q_steps) == nearbyint(x / s).  Returns the number of mismatches for
+ * the given scale using `steps` refinement steps (1 or 2). */
+ORC_API int64_t orc_check_recip_division(float s, int steps) {
+  int64_t bad = 0;
+  float r = 1.0f / s;
+  for (uint32_t h = 0; h < 0x7f80u; h++) {
+    for (int sg = 0; sg < 2; sg++) {
+      float x = bf16_to_f32((uint16_t)(h | (sg ? 0x8000u : 0u)));
+      float t = x / s;
+      if (!(fabsf(t) <= 127.5f)) continue;
+      float q = x * r;
+      for (int it = 0; it < steps; it++) { float e = fmaf(-q, s, x); q = fmaf(e, r, q); }
+      if (nearbyintf(q) != nearbyintf(t)) bad++;
+    }
+  }
+  return bad;
+}

@@ -1,0 +1,266 @@
+"""ctypes front end of the CPU oracle (oracle/hfusion_oracle.c).
+
+TEST INFRASTRUCTURE ONLY.  Importable from tests/, the smoke check and the
+CPU-baseline leg of the bench; the product package never imports it.
+
+Arrays are numpy, C-contiguous.  f16 / bf16 tensors travel as ``np.uint16`` bit
+patterns together with a dtype code (``F16`` / ``BF16``); everything else uses the
+natural numpy dtype.  The functions mirror the reference op they restate; the
+C file carries the reference file:line citations.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liboracle.so")
+
+F32, F16, BF16, I8, I16, I32, I64, U8, U16, U32, U64, BOOL = range(12)
+DTYPE_NAMES = {"f32": F32, "f16": F16, "bf16": BF16, "i8": I8, "i16": I16, "i32": I32, "i64": I64,
+               "u8": U8, "u16": U16, "u32": U32, "u64": U64, "bool": BOOL, "i1": BOOL}
+_NP = {F32: np.float32, F16: np.uint16, BF16: np.uint16, I8: np.int8, I16: np.int16, I32: np.int32,
+       I64: np.int64, U8: np.uint8, U16: np.uint16, U32: np.uint32, U64: np.uint64, BOOL: np.uint8}
+
+ROUND = {"rint": 0, "round": 1, "floor": 2, "ceil": 3, "trunc": 4, "odd": 5, "truncwithoverflow": 6}
+OVERFLOW = {"wrap": 0, "saturate": 1, "ascend_saturate_trunc_via_f16": 2, "ascend_double_round_via_f16": 3}
+UNARY = {"relu": 0, "sqrt": 1, "rsqrt": 2, "rec": 3, "vnot": 4, "tanh": 5, "sin": 6, "cos": 7, "atan": 8,
+         "tan": 9, "absi": 10, "erf": 11, "log2": 12, "log10": 13, "log1p": 14, "exp2": 15, "expm1": 16,
+         "ilogb": 17, "asin": 18, "acos": 19, "asinh": 20, "acosh": 21, "atanh": 22, "sinh": 23,
+         "lgamma": 24, "cosh": 25, "nearbyint": 26, "exp": 100, "log": 101, "abs": 102, "ceil": 103,
+         "floor": 104, "negf": 105, "reciprocal": 106, "round": 107, "square": 110}
+BINARY = {"vor": 0, "vand": 1, "vxor": 2, "minf": 3, "maxf": 4, "powf": 5, "mod": 6, "modui": 7, "shli": 8,
+          "shrsi": 9, "shrui": 10, "ldexp": 11, "ceildivsi": 12, "ceildivui": 13, "floordivsi": 14,
+          "powi": 15, "minnumf": 16, "maxnumf": 17, "atan2": 18, "divfhp": 19, "copysign": 20,
+          "add": 100, "sub": 101, "mul": 102, "div": 103, "div_unsigned": 104, "max_signed": 105,
+          "min_signed": 106, "max_unsigned": 107, "min_unsigned": 108}
+COMPARE = {"veq": 0, "vne": 1, "vle": 2, "vlt": 3, "vge": 4, "vgt": 5, "vule": 6, "vult": 7, "vuge": 8, "vugt": 9}
+REDUCE = {"sum": 0, "prod": 1, "max": 2, "min": 3, "any": 4, "all": 5, "xori": 6, "ori": 7, "andi": 8}
+
+
+def build(force: bool = False) -> str:
+    """Compile liboracle.so with the Makefile beside this file (gcc); returns its path."""
+    if force or not os.path.exists(_LIB_PATH) or \
+            os.path.getmtime(_LIB_PATH) < os.path.getmtime(os.path.join(_HERE, "hfusion_oracle.c")):
+        subprocess.run(["make", "-C", _HERE, "-s"], check=True)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        _lib = C.CDLL(_LIB_PATH)
+        _lib.orc_bf16_to_f32.restype = C.c_float
+        _lib.orc_bf16_to_f32.argtypes = [C.c_uint16]
+        _lib.orc_f16_to_f32.restype = C.c_float
+        _lib.orc_f16_to_f32.argtypes = [C.c_uint16]
+        _lib.orc_f32_to_bf16.restype = C.c_uint16
+        _lib.orc_f32_to_bf16.argtypes = [C.c_float]
+        _lib.orc_f32_to_f16.restype = C.c_uint16
+        _lib.orc_f32_to_f16.argtypes = [C.c_float]
+        _lib.orc_f32_to_f16_rz.restype = C.c_uint16
+        _lib.orc_f32_to_f16_rz.argtypes = [C.c_float]
+        _lib.orc_selftest_f16.restype = C.c_int64
+        _lib.orc_selftest_f16.argtypes = [C.c_int64]
+        _lib.orc_check_recip_division.restype = C.c_int64
+        _lib.orc_check_recip_division.argtypes = [C.c_float, C.c_int]
+    return _lib
+
+
+def set_threads(n: int) -> None:
+    lib().orc_set_threads(C.c_int(int(n)))
+
+
+def max_threads() -> int:
+    return int(lib().orc_get_max_threads())
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt) -> np.ndarray:
+    a = np.ascontiguousarray(a)
+    if a.dtype != _NP[dt]:
+        if a.dtype == np.bool_ and dt == BOOL:
+            a = a.view(np.uint8)
+        else:
+            raise TypeError(f"array dtype {a.dtype} does not match dtype code {dt} ({_NP[dt]})")
+    return a
+
+
+def _i64(v):
+    return C.c_int64(int(v))
+
+
+def _chk(rc, what):
+    if rc != 0:
+        raise RuntimeError(f"oracle {what} failed with code {rc}")
+
+
+# ---------------------------------------------------------------- conversions
+def bf16_to_f32(bits: np.ndarray) -> np.ndarray:
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16(x: np.ndarray) -> np.ndarray:
+    out = np.empty(x.shape, np.uint16)
+    cast(F32, BF16, np.ascontiguousarray(x, np.float32), out=out)
+    return out
+
+
+def f16_to_f32(bits: np.ndarray) -> np.ndarray:
+    return bits.view(np.float16).astype(np.float32)
+
+
+# ------------------------------------------------------------------------ ops
+def elemwise_unary(fn, dt, x):
+    fn = UNARY[fn] if isinstance(fn, str) else fn
+    x = _c(x, dt)
+    out = np.empty_like(x)
+    _chk(lib().orc_elemwise_unary(fn, dt, _p(x), _p(out), _i64(x.size)), "elemwise_unary")
+    return out
+
+
+def elemwise_binary(fn, dt, a, b):
+    """a / b: arrays of the same shape, or 1-element arrays (scalar operand, stride 0)."""
+    fn = BINARY[fn] if isinstance(fn, str) else fn
+    a, b = _c(a, dt), _c(b, dt)
+    n = max(a.size, b.size)
+    shape = a.shape if a.size == n else b.shape
+    sa = 1 if a.size == n else 0
+    sb = 1 if b.size == n else 0
+    out = np.empty(shape, _NP[dt])
+    _chk(lib().orc_elemwise_binary(fn, dt, _p(a), _i64(sa), _p(b), _i64(sb), _p(out), _i64(n)), "elemwise_binary")
+    return out
+
+
+def compare(fn, dt, a, b):
+    fn = COMPARE[fn] if isinstance(fn, str) else fn
+    a, b = _c(a, dt), _c(b, dt)
+    n = max(a.size, b.size)
+    shape = a.shape if a.size == n else b.shape
+    out = np.empty(shape, np.uint8)
+    _chk(lib().orc_compare(fn, dt, _p(a), _i64(1 if a.size == n else 0), _p(b), _i64(1 if b.size == n else 0),
+                           _p(out), _i64(n)), "compare")
+    return out
+
+
+def select(dt, cond, a, b):
+    cond = np.ascontiguousarray(cond).view(np.uint8)
+    a, b = _c(a, dt), _c(b, dt)
+    n = max(cond.size, a.size, b.size)
+    shape = cond.shape if cond.size == n else (a.shape if a.size == n else b.shape)
+    out = np.empty(shape, _NP[dt])
+    _chk(lib().orc_select(dt, _p(cond), _i64(1 if cond.size == n else 0), _p(a), _i64(1 if a.size == n else 0),
+                          _p(b), _i64(1 if b.size == n else 0), _p(out), _i64(n)), "select")
+    return out
+
+
+def cast(src_dt, dst_dt, src, round_mode="rint", overflow="wrap", out=None):
+    rm = ROUND[round_mode] if isinstance(round_mode, str) else round_mode
+    ov = OVERFLOW[overflow] if isinstance(overflow, str) else overflow
+    src = _c(src, src_dt)
+    if out is None:
+        out = np.empty(src.shape, _NP[dst_dt])
+    _chk(lib().orc_cast(src_dt, dst_dt, rm, ov, _p(src), _p(out), _i64(src.size)), "cast")
+    return out
+
+
+def reduce_last_axis(kind, dt, src):
+    kind = REDUCE[kind] if isinstance(kind, str) else kind
+    src = _c(src, dt)
+    rows, cols = src.shape
+    out = np.empty(rows, _NP[dt])
+    _chk(lib().orc_reduce_last_axis(kind, dt, _p(src), _i64(rows), _i64(cols), _i64(cols), _p(out)), "reduce")
+    return out
+
+
+def reduce_first_axis(kind, dt, src):
+    kind = REDUCE[kind] if isinstance(kind, str) else kind
+    src = _c(src, dt)
+    rows, cols = src.shape
+    out = np.empty(cols, _NP[dt])
+    _chk(lib().orc_reduce_first_axis(kind, dt, _p(src), _i64(rows), _i64(cols), _i64(cols), _p(out)), "reduce")
+    return out
+
+
+def reduce_with_index(kind, dt, src, tie_break_left=True, nan_mode="region"):
+    """kind: 'max' | 'min'.  Returns (values, int32 indices)."""
+    k = {"min": 0, "max": 1}[kind]
+    nm = {"region": 0, "nan_first": 1}[nan_mode]
+    src = _c(src, dt)
+    rows, cols = src.shape
+    val = np.empty(rows, _NP[dt])
+    idx = np.empty(rows, np.int32)
+    _chk(lib().orc_reduce_with_index(k, dt, int(bool(tie_break_left)), nm, _p(src), _i64(rows), _i64(cols),
+                                     _i64(cols), _p(val), _p(idx)), "reduce_with_index")
+    return val, idx
+
+
+def rms_norm(dt, x, gamma, eps, want_rstd=False):
+    x, gamma = _c(x, dt), _c(gamma, dt)
+    rows, cols = x.shape
+    y = np.empty_like(x)
+    rstd = np.empty(rows, _NP[dt]) if want_rstd else None
+    _chk(lib().orc_rms_norm(dt, _p(x), _p(gamma), C.c_float(eps), _i64(rows), _i64(cols), _i64(cols), _p(y),
+                            _i64(cols), _p(rstd) if want_rstd else None), "rms_norm")
+    return (y, rstd) if want_rstd else y
+
+
+def softmax(dt, x):
+    x = _c(x, dt)
+    rows, cols = x.shape
+    y = np.empty_like(x)
+    _chk(lib().orc_softmax(dt, _p(x), _i64(rows), _i64(cols), _i64(cols), _p(y), _i64(cols)), "softmax")
+    return y
+
+
+def quant_per_token_i8(dt, x, round_mode="rint", overflow="saturate"):
+    rm = ROUND[round_mode] if isinstance(round_mode, str) else round_mode
+    ov = OVERFLOW[overflow] if isinstance(overflow, str) else overflow
+    x = _c(x, dt)
+    rows, cols = x.shape
+    q = np.empty((rows, cols), np.int8)
+    scale = np.empty(rows, np.float32)
+    _chk(lib().orc_quant_per_token_i8(dt, rm, ov, _p(x), _i64(rows), _i64(cols), _i64(cols), _p(q), _i64(cols),
+                                      _p(scale)), "quant_per_token_i8")
+    return q, scale
+
+
+def matmul_w8a8(a, b, sa=None, sw=None, transpose_b=False, out_dt=BF16, want_acc=False):
+    a = _c(a, I8)
+    b = _c(b, I8)
+    m, k = a.shape
+    n = b.shape[0] if transpose_b else b.shape[1]
+    assert (b.shape[1] if transpose_b else b.shape[0]) == k
+    out = np.empty((m, n), np.uint16)
+    acc = np.empty((m, n), np.int32) if want_acc else None
+    sa_ = _c(sa, F32) if sa is not None else None
+    sw_ = _c(sw, F32) if sw is not None else None
+    _chk(lib().orc_matmul_w8a8(_i64(m), _i64(n), _i64(k), _p(a), _i64(k), _p(b), _i64(b.shape[1]),
+                               int(bool(transpose_b)), _p(sa_) if sa_ is not None else None,
+                               _p(sw_) if sw_ is not None else None, out_dt, _p(out), _i64(n),
+                               _p(acc) if want_acc else None, _i64(n)), "matmul_w8a8")
+    return (out, acc) if want_acc else out
+
+
+def matmul_w4a16(a_bits, qweight, scales_bits, zeros, group=128):
+    a = _c(a_bits, BF16)
+    qw = _c(qweight, I32)
+    sc = _c(scales_bits, BF16)
+    zp = _c(zeros, I32)
+    m, k = a.shape
+    n = qw.shape[1]
+    out = np.empty((m, n), np.uint16)
+    _chk(lib().orc_matmul_w4a16(_i64(m), _i64(n), _i64(k), _i64(group), _p(a), _i64(k), _p(qw), _p(sc), _p(zp),
+                                _p(out), _i64(n)), "matmul_w4a16")
+    return out

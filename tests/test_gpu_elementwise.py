@@ -1,0 +1,220 @@
+"""GPU parity: elementwise / compare / select / cast against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from conftest import assert_bits_equal, assert_close, oracle_dtype, to_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def bsir():
+    import bsir as B
+    B.lib()
+    return B
+
+
+def _rand(shape, dtype, seed, lo=-4.0, hi=4.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    if dtype.is_floating_point:
+        return (torch.rand(shape, generator=g, device="cuda") * (hi - lo) + lo).to(dtype)
+    info = torch.iinfo(dtype)
+    return torch.randint(max(info.min, -1000), min(info.max, 1000) + 1, shape, generator=g, device="cuda", dtype=dtype)
+
+
+# --- config 0: HIVM VecAdd, fp32 and fp16, length 2^24, bit-exact -------------------------------
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_vecadd_full_size_bit_exact(bsir, dtype):
+    from bsir import workloads as W
+    a, b = W.vecadd(1 << 24, dtype, seed=0)
+    out = bsir.vadd(a, b)
+    want = O.elemwise_binary("add", oracle_dtype(a), to_bits(a), to_bits(b))
+    assert_bits_equal(out, want, f"vadd {dtype}")
+
+
+def test_vecadd_reference_e2e_vector(bsir):
+    # bishengir/test/Integration/HIVM/VecAdd/main.cpp:141-158: {0..15} + {1,...} -> {1..16}, i16, N = 16
+    a = torch.arange(16, dtype=torch.int16, device="cuda")
+    b = torch.ones(16, dtype=torch.int16, device="cuda")
+    assert bsir.vadd(a, b).cpu().tolist() == list(range(1, 17))
+
+
+@pytest.mark.parametrize("n", [0, 1, 3, 7, 8, 9, 255, 256, 1023, 4097, 100003])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.int16, torch.int32])
+def test_vadd_ragged_lengths(bsir, n, dtype):
+    a, b = _rand((n,), dtype, 1), _rand((n,), dtype, 2)
+    out = bsir.vadd(a, b)
+    if n == 0:
+        assert out.numel() == 0
+        return
+    want = O.elemwise_binary("add", oracle_dtype(a), to_bits(a), to_bits(b))
+    assert_bits_equal(out, want, f"vadd n={n} {dtype}")
+
+
+EXACT_BINARY = ["add", "sub", "mul", "div", "maxf", "minf", "maxnumf", "minnumf", "copysign"]
+
+
+@pytest.mark.parametrize("fn", EXACT_BINARY)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_binary_float_exact(bsir, fn, dtype):
+    a, b = _rand((257, 129), dtype, 3), _rand((257, 129), dtype, 4)
+    # plant special values
+    a.view(-1)[:8] = torch.tensor([0.0, -0.0, float("nan"), float("inf"), -float("inf"), 1.0, -0.0, 0.0], device="cuda").to(dtype)
+    b.view(-1)[:8] = torch.tensor([-0.0, 0.0, 1.0, float("inf"), 2.0, float("nan"), -0.0, 0.0], device="cuda").to(dtype)
+    out = bsir.elemwise_binary(fn, a, b)
+    want = O.elemwise_binary(fn, oracle_dtype(a), to_bits(a), to_bits(b))
+    assert_bits_equal(out, want, f"{fn} {dtype}")
+
+
+@pytest.mark.parametrize("fn", ["add", "sub", "mul", "div", "max_signed", "min_signed", "vand", "vor", "vxor",
+                                "mod", "shli", "shrsi", "shrui", "floordivsi", "ceildivsi"])
+@pytest.mark.parametrize("dtype", [torch.int8, torch.int16, torch.int32, torch.int64])
+def test_binary_int_exact(bsir, fn, dtype):
+    a, b = _rand((1000,), dtype, 5), _rand((1000,), dtype, 6)
+    if fn in ("shli", "shrsi", "shrui"):
+        b = b.abs() % 9
+    if fn in ("div", "mod", "floordivsi", "ceildivsi"):
+        b = torch.where(b == 0, torch.ones_like(b), b)
+    out = bsir.elemwise_binary(fn, a, b)
+    want = O.elemwise_binary(fn, oracle_dtype(a), to_bits(a), to_bits(b))
+    assert_bits_equal(out, want, f"{fn} {dtype}")
+
+
+@pytest.mark.parametrize("fn,lo,hi", [("exp", -10, 10), ("log", 0.01, 100), ("abs", -4, 4), ("sqrt", 0, 100),
+                                      ("rsqrt", 0.01, 100), ("rec", 0.1, 10), ("relu", -4, 4), ("tanh", -4, 4),
+                                      ("sin", -6, 6), ("cos", -6, 6), ("erf", -3, 3), ("floor", -9, 9),
+                                      ("ceil", -9, 9), ("negf", -4, 4), ("exp2", -8, 8), ("log2", 0.01, 100),
+                                      ("log1p", -0.5, 10), ("square", -4, 4), ("nearbyint", -9, 9), ("sinh", -4, 4)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_unary_float(bsir, fn, lo, hi, dtype):
+    x = _rand((4099,), dtype, 7, lo, hi)
+    out = bsir.elemwise_unary(fn, x)
+    want = O.elemwise_unary(fn, oracle_dtype(x), to_bits(x))
+    if fn in ("abs", "sqrt", "rsqrt", "rec", "relu", "floor", "ceil", "negf", "square", "nearbyint"):
+        assert_bits_equal(out, want, f"{fn} {dtype}")      # correctly rounded ops: bit-exact
+    else:
+        # transcendental: device libm vs host libm; tolerance of the reference's own convention
+        # (docs/source/en/developer_guide/conversion/triton_interface.md:88-99)
+        tol = 1e-4 if dtype == torch.float32 else 1e-2
+        assert_close(out, want, tol, tol, f"{fn} {dtype}")
+
+
+def test_scalar_and_broadcast_operands(bsir):
+    a = _rand((33, 65), torch.float32, 8)
+    out = bsir.elemwise_binary("mul", a, 2.5)
+    want = O.elemwise_binary("mul", O.F32, to_bits(a), np.array([2.5], np.float32))
+    assert_bits_equal(out, want, "mul scalar")
+    out = bsir.elemwise_binary("sub", 1.0, a)
+    want = O.elemwise_binary("sub", O.F32, np.array([1.0], np.float32), to_bits(a))
+    assert_bits_equal(out, want, "scalar sub")
+    row = _rand((1, 65), torch.float32, 9)      # inline broadcast along dim 0
+    out = bsir.elemwise_binary("add", a, row)
+    want = O.elemwise_binary("add", O.F32, to_bits(a), to_bits(row.expand(33, 65).contiguous()))
+    assert_bits_equal(out, want, "add broadcast")
+    col = _rand((33, 1), torch.float32, 10)     # inline broadcast along dim 1
+    out = bsir.elemwise_binary("add", a, col)
+    want = O.elemwise_binary("add", O.F32, to_bits(a), to_bits(col.expand(33, 65).contiguous()))
+    assert_bits_equal(out, want, "add broadcast col")
+
+
+def test_strided_views(bsir):
+    big = _rand((64, 96), torch.float16, 11)
+    a = big[::2, 1:65]           # non-contiguous, misaligned base
+    b = big.t()[1:65, :32].t()   # transposed view
+    out = bsir.elemwise_binary("add", a, b)
+    want = O.elemwise_binary("add", O.F16, to_bits(a.contiguous()), to_bits(b.contiguous()))
+    assert_bits_equal(out, want, "strided add")
+
+
+def test_rank3(bsir):
+    a, b = _rand((5, 7, 24), torch.bfloat16, 12), _rand((5, 7, 24), torch.bfloat16, 13)
+    out = bsir.elemwise_binary("mul", a, b)
+    want = O.elemwise_binary("mul", O.BF16, to_bits(a), to_bits(b))
+    assert_bits_equal(out, want, "rank3 mul")
+
+
+@pytest.mark.parametrize("fn", ["veq", "vne", "vlt", "vle", "vgt", "vge"])
+def test_compare_and_select(bsir, fn):
+    a, b = _rand((1000,), torch.float32, 14), _rand((1000,), torch.float32, 15)
+    a[:4] = torch.tensor([float("nan"), 1.0, 0.0, -0.0], device="cuda")
+    b[:4] = torch.tensor([1.0, float("nan"), -0.0, 0.0], device="cuda")
+    b[10:20] = a[10:20]
+    c = bsir.compare(fn, a, b)
+    want = O.compare(fn, O.F32, to_bits(a), to_bits(b))
+    assert_bits_equal(c, want, f"compare {fn}")
+    s = bsir.select(c, a, b)
+    wants = O.select(O.F32, want, to_bits(a), to_bits(b))
+    assert_bits_equal(s, wants, "select")
+
+
+def test_copy_strided(bsir):
+    x = _rand((40, 50), torch.int32, 16)
+    out = bsir.copy(x.t())
+    assert torch.equal(out, x.t())
+
+
+# --- hfusion.cast ------------------------------------------------------------------------------
+MODES = ["rint", "round", "floor", "ceil", "trunc", "odd"]
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("sat", [False, True])
+@pytest.mark.parametrize("dst", [torch.int8, torch.int16, torch.int32, torch.int64])
+def test_cast_float_to_int(bsir, mode, sat, dst):
+    x = _rand((5003,), torch.float32, 17, -300.0, 300.0)
+    ties = torch.arange(-140, 140, device="cuda", dtype=torch.float32) + 0.5
+    x[:ties.numel()] = ties
+    x[300:306] = torch.tensor([float("nan"), float("inf"), -float("inf"), 3e9, -3e9, 1e20], device="cuda")
+    out = bsir.cast(x, dst, round_mode=mode, enable_saturate=sat)
+    want = O.cast(O.F32, {torch.int8: O.I8, torch.int16: O.I16, torch.int32: O.I32, torch.int64: O.I64}[dst], to_bits(x),
+                  mode, "saturate" if sat else "wrap")
+    assert_bits_equal(out, want, f"cast f32->{dst} {mode} sat={sat}")
+
+
+@pytest.mark.parametrize("mode", MODES)
+@pytest.mark.parametrize("dst", [torch.float16, torch.bfloat16])
+def test_cast_float_narrowing(bsir, mode, dst):
+    x = _rand((8191,), torch.float32, 18, -70000.0, 70000.0)
+    x[:6] = torch.tensor([0.0, -0.0, float("nan"), float("inf"), 1e-8, -1e-8], device="cuda")
+    out = bsir.cast(x, dst, round_mode=mode)
+    want = O.cast(O.F32, O.F16 if dst == torch.float16 else O.BF16, to_bits(x), mode)
+    assert_bits_equal(out, want, f"cast f32->{dst} {mode}")
+
+
+def test_cast_reference_known_answers(bsir):
+    # test/Dialect/HFusion/canonicalize.mlir:149-166: i64 2 -> 2.0f; f32 2.8 -> 3.0 (default rint)
+    assert bsir.cast(torch.full((16,), 2, dtype=torch.int64, device="cuda"), torch.float32).cpu().tolist() == [2.0] * 16
+    assert bsir.cast(torch.full((16,), 2.8, device="cuda"), torch.float32).cpu().tolist() == [3.0] * 16
+    # Normalize.cpp:3806-3811 saturate example
+    x = torch.tensor([128.7, 127.5, 100.3, -129.2, -128.4], device="cuda")
+    got = bsir.cast(x, torch.int8, overflow_mode="ascend_saturate_trunc_via_f16").cpu().tolist()
+    assert got == [127, 127, 100, -128, -128]
+    # double rounding through f16 vs single rounding
+    y = torch.tensor([2.5 + 2.0 ** -20], device="cuda")
+    assert bsir.cast(y, torch.int8, enable_saturate=True).item() == 3
+    assert bsir.cast(y, torch.int8, overflow_mode="ascend_double_round_via_f16").item() == 2
+
+
+@pytest.mark.parametrize("src,dst", [(torch.bfloat16, torch.float32), (torch.float16, torch.float32),
+                                     (torch.int8, torch.float16), (torch.int32, torch.float32),
+                                     (torch.int64, torch.float32), (torch.int32, torch.int8),
+                                     (torch.int64, torch.int32), (torch.int16, torch.int8),
+                                     (torch.bool, torch.float32), (torch.uint8, torch.int32),
+                                     (torch.int32, torch.bfloat16), (torch.bfloat16, torch.int32)])
+def test_cast_other_pairs(bsir, src, dst):
+    if src == torch.bool:
+        x = _rand((1000,), torch.int8, 19) > 0
+    elif src.is_floating_point:
+        x = _rand((1000,), src, 19, -1000, 1000)
+    elif src == torch.uint8:
+        x = _rand((1000,), torch.int16, 19).abs().clamp(max=255).to(torch.uint8)
+    else:
+        x = _rand((1000,), src, 19)
+        if src in (torch.int32, torch.int64):
+            x = x * 70001
+    out = bsir.cast(x, dst, round_mode="trunc" if (src.is_floating_point and not dst.is_floating_point) else "rint")
+    code = lambda d: oracle_dtype(torch.empty(0, dtype=d))
+    want = O.cast(code(src), code(dst), to_bits(x), "trunc" if (src.is_floating_point and not dst.is_floating_point) else "rint", "wrap")
+    assert_bits_equal(out, want, f"cast {src}->{dst}")
