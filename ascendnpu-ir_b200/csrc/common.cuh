@@ -38,6 +38,9 @@ void *device_workspace(size_t bytes, cudaStream_t stream);
 // Device-side error word (one int per device); kernels OR a code into it when a
 // bounded wait gives up.
 int *device_error_word();
+// The first kScratchCounterBytes of any scratch block hold self-resetting counters only (one
+// uint32 per row of a launch, at most 65535 rows); everything else starts after them.
+constexpr size_t kScratchCounterBytes = 256 * 1024;
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

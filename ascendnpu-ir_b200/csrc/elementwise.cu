@@ -561,7 +561,7 @@ extern "C" {
 int32_t bsir_elemwise_unary(int32_t fn, int32_t dtype, int32_t rank, const int64_t *sizes, const bsir_operand *x,
                             void *out, const int64_t *out_strides, void *stream) {
   clear_error();
-  if (!x || !out || !x->data) return fail(BSIR_ERR_NULL, "elemwise_unary: null operand");
+  if (!x) return fail(BSIR_ERR_NULL, "elemwise_unary: null operand");
   if (dtype_bytes(dtype) == 0) return fail(BSIR_ERR_DTYPE, "elemwise_unary: dtype %d", dtype);
   if (fn == BSIR_UNARY_VNOT) dtype = bits_dtype(dtype);
   if (!fn_is_valid(kOpUnary, fn, dtype))
@@ -569,6 +569,8 @@ int32_t bsir_elemwise_unary(int32_t fn, int32_t dtype, int32_t rank, const int64
   if (!check_align(x->data, dtype) || !check_align(out, dtype)) return fail(BSIR_ERR_ALIGN, "elemwise_unary: misaligned");
   Prepared p;
   if (int32_t rc = prepare("elemwise_unary", rank, sizes, out_strides, &p)) return rc;
+  if (p.sh.total == 0) return BSIR_OK;
+  if (!out || !x->data) return fail(BSIR_ERR_NULL, "elemwise_unary: null operand");
   bool ac;
   Operand a = make_operand(x, rank, sizes, &ac), none{nullptr, 0, 0, 0, 0};
   return launch_by_dtype<kOpUnary>("elemwise_unary", fn, dtype, p, a, ac, none, true, none, out, resolve_stream(stream));
@@ -577,7 +579,7 @@ int32_t bsir_elemwise_unary(int32_t fn, int32_t dtype, int32_t rank, const int64
 int32_t bsir_elemwise_binary(int32_t fn, int32_t dtype, int32_t rank, const int64_t *sizes, const bsir_operand *a,
                              const bsir_operand *b, void *out, const int64_t *out_strides, void *stream) {
   clear_error();
-  if (!a || !b || !out) return fail(BSIR_ERR_NULL, "elemwise_binary: null operand");
+  if (!a || !b) return fail(BSIR_ERR_NULL, "elemwise_binary: null operand");
   if (dtype_bytes(dtype) == 0) return fail(BSIR_ERR_DTYPE, "elemwise_binary: dtype %d", dtype);
   if (fn == BSIR_BINARY_VAND || fn == BSIR_BINARY_VOR || fn == BSIR_BINARY_VXOR) dtype = bits_dtype(dtype);
   if (!fn_is_valid(kOpBinary, fn, dtype))
@@ -586,6 +588,8 @@ int32_t bsir_elemwise_binary(int32_t fn, int32_t dtype, int32_t rank, const int6
     return fail(BSIR_ERR_ALIGN, "elemwise_binary: misaligned");
   Prepared p;
   if (int32_t rc = prepare("elemwise_binary", rank, sizes, out_strides, &p)) return rc;
+  if (p.sh.total == 0) return BSIR_OK;
+  if (!out) return fail(BSIR_ERR_NULL, "elemwise_binary: null result");
   bool ac, bc;
   Operand oa = make_operand(a, rank, sizes, &ac), ob = make_operand(b, rank, sizes, &bc), none{nullptr, 0, 0, 0, 0};
   return launch_by_dtype<kOpBinary>("elemwise_binary", fn, dtype, p, oa, ac, ob, bc, none, out, resolve_stream(stream));
@@ -594,12 +598,14 @@ int32_t bsir_elemwise_binary(int32_t fn, int32_t dtype, int32_t rank, const int6
 int32_t bsir_compare(int32_t fn, int32_t dtype, int32_t rank, const int64_t *sizes, const bsir_operand *a,
                      const bsir_operand *b, void *out, const int64_t *out_strides, void *stream) {
   clear_error();
-  if (!a || !b || !out) return fail(BSIR_ERR_NULL, "compare: null operand");
+  if (!a || !b) return fail(BSIR_ERR_NULL, "compare: null operand");
   if (dtype_bytes(dtype) == 0) return fail(BSIR_ERR_DTYPE, "compare: dtype %d", dtype);
   if (!fn_is_valid(kOpCompare, fn, dtype)) return fail(BSIR_ERR_ATTR, "compare: fn %d for dtype %d", fn, dtype);
   if (!check_align(a->data, dtype) || !check_align(b->data, dtype)) return fail(BSIR_ERR_ALIGN, "compare: misaligned");
   Prepared p;
   if (int32_t rc = prepare("compare", rank, sizes, out_strides, &p)) return rc;
+  if (p.sh.total == 0) return BSIR_OK;
+  if (!out) return fail(BSIR_ERR_NULL, "compare: null result");
   bool ac, bc;
   Operand oa = make_operand(a, rank, sizes, &ac), ob = make_operand(b, rank, sizes, &bc), none{nullptr, 0, 0, 0, 0};
   return launch_by_dtype<kOpCompare>("compare", fn, dtype, p, oa, ac, ob, bc, none, out, resolve_stream(stream));
@@ -608,12 +614,14 @@ int32_t bsir_compare(int32_t fn, int32_t dtype, int32_t rank, const int64_t *siz
 int32_t bsir_select(int32_t dtype, int32_t rank, const int64_t *sizes, const bsir_operand *cond, const bsir_operand *a,
                     const bsir_operand *b, void *out, const int64_t *out_strides, void *stream) {
   clear_error();
-  if (!cond || !a || !b || !out) return fail(BSIR_ERR_NULL, "select: null operand");
+  if (!cond || !a || !b) return fail(BSIR_ERR_NULL, "select: null operand");
   if (dtype_bytes(dtype) == 0) return fail(BSIR_ERR_DTYPE, "select: dtype %d", dtype);
   if (!check_align(a->data, dtype) || !check_align(b->data, dtype) || !check_align(out, dtype))
     return fail(BSIR_ERR_ALIGN, "select: misaligned");
   Prepared p;
   if (int32_t rc = prepare("select", rank, sizes, out_strides, &p)) return rc;
+  if (p.sh.total == 0) return BSIR_OK;
+  if (!out || !cond->data) return fail(BSIR_ERR_NULL, "select: null pointer");
   bool cc, ac, bc;
   Operand oc = make_operand(cond, rank, sizes, &cc), oa = make_operand(a, rank, sizes, &ac),
           ob = make_operand(b, rank, sizes, &bc);
@@ -625,11 +633,12 @@ int32_t bsir_select(int32_t dtype, int32_t rank, const int64_t *sizes, const bsi
 int32_t bsir_copy(int32_t dtype, int32_t rank, const int64_t *sizes, const void *src, const int64_t *src_strides,
                   void *dst, const int64_t *dst_strides, void *stream) {
   clear_error();
-  if (!src || !dst) return fail(BSIR_ERR_NULL, "copy: null pointer");
   if (dtype_bytes(dtype) == 0) return fail(BSIR_ERR_DTYPE, "copy: dtype %d", dtype);
   if (!check_align(src, dtype) || !check_align(dst, dtype)) return fail(BSIR_ERR_ALIGN, "copy: misaligned");
   Prepared p;
   if (int32_t rc = prepare("copy", rank, sizes, dst_strides, &p)) return rc;
+  if (p.sh.total == 0) return BSIR_OK;
+  if (!src || !dst) return fail(BSIR_ERR_NULL, "copy: null pointer");
   bsir_operand s{src, {0, 0, 0}, 0};
   int64_t cs = 1;
   for (int i = rank - 1; i >= 0; --i) { s.strides[i] = src_strides ? src_strides[i] : cs; cs *= sizes[i]; }

@@ -1,8 +1,495 @@
+// gemm_w8a8.cu -- linalg.matmul i8 x i8 -> i32 with the fused dequant suffix
+//   out[m, n] = cast_rint( (sitofp(acc[m, n]) * scale_a[m]) * scale_b[n] )
+// (int8 dot: bishengir/test/bishengir-compile/hivm/compile-dot-int8-fractal-c.mlir:25; the global
+// GEMM with a descale epilogue is hivm.hir.matmul, bishengir/include/bishengir/Dialect/HIVM/IR/HIVMMacroOps.td:364-492;
+// device library variants bishengir/lib/Template/lib/Cube/GlobalMmad.cpp:176-187).
+//
+// sm_100a design.  A persistent kernel, one CTA per SM, 192 threads in three roles:
+//   warp 0     TMA producer: cp.async.bulk.tensor loads of the A tile [128 x 128 B] and the B tile
+//              into a ring of shared-memory stages (128-byte swizzle), completion on mbarriers;
+//   warp 1     MMA issuer: one thread issues tcgen05.mma.kind::i8 (M=128, N=BN, K=32) with the int32
+//              accumulator in tensor memory; tcgen05.commit releases stages and publishes tiles;
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp its 32 TMEM lanes), convert to f32,
+//              apply both scales, round to bf16/f16, store.
+// Two accumulator buffers in TMEM (2 x BN columns) let the epilogue of tile i overlap the main
+// loop of tile i + 1.
+//
+// B comes either as [n, k] rows (transpose_b, "K-major" for the tensor core) or, as linalg.matmul has
+// it, as [k, n] rows ("MN-major"): the shared-memory matrix descriptor and the instruction
+// descriptor's b_major bit describe the layout, so no transpose pass is needed.
+//
+// Every wait on an mbarrier is bounded: after ~2 s of cycles a waiter sets the device error word
+// and an abort flag that all roles poll; the CTA then drains and frees its tensor memory.
+//
+// Shapes the TMA path cannot address (row pitches that are not multiples of 16 bytes, unaligned
+// bases) run on a plain CUDA-core kernel instead.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "common.cuh"
+
+namespace bsir {
+namespace {
+
+constexpr int kBM = 128;        // rows of A per tile = TMEM lanes
+constexpr int kBK = 128;        // K bytes per stage (one 128-byte swizzle row)
+constexpr int kUmmaK = 32;      // K per tcgen05.mma for 8-bit operands
+constexpr int kThreads = 192;
+constexpr uint32_t kErrGemmWait = 0x10;
+
+struct GemmParams {
+  int64_t m, n, k;
+  const float *scale_a;
+  const float *scale_b;
+  void *out;
+  int64_t ldo;
+  int32_t out_dtype;
+  int32_t *acc_out;
+  int64_t ldacc;
+  int *err;
+  int m_tiles, n_tiles, k_blocks;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false when it gave up or another role raised the abort flag.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *err) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t spin = 0;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > 4000000000LL) {  // about two seconds
+        *abort_flag = 1;
+        if (err) atomicOr(err, static_cast<int>(kErrGemmWait));
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
+//   K-major operand  (rows of 128 K-bytes):        SBO = 1024 (8 rows), LBO unused
+//   MN-major operand (rows of 128 N-bytes per k):  SBO = 1024 (8 k rows), LBO = pitch between 128-wide N chunks
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr >> 4) & 0x3fffu);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
+  d |= 1ull << 46;  // descriptor version
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+
+template <int BN>
+struct TileCfg {
+  static constexpr int kStageA = kBM * kBK;           // 16 KB
+  static constexpr int kStageB = BN * kBK;            // BN x 128 B
+  static constexpr int kStage = kStageA + kStageB;
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStage + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
+
+// ------------------------------------------------------------------ the kernel
+template <int BN, bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+    w8a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+  using Cfg = TileCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;  // 128-byte swizzle wants 1024-byte aligned tiles
+  uint8_t *gen_base = smem_raw + (base - raw);
+  const uint32_t bars = base + Cfg::kStages * Cfg::kStage;
+  // barrier slots (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (Cfg::kStages + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * Cfg::kStages + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * Cfg::kStages + 2 + a); };
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen_base + Cfg::kStages * Cfg::kStage + 8 * (2 * Cfg::kStages + 4));
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = p.m_tiles * p.n_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.m_tiles) * kBM;
+        const int n0 = (tile / p.m_tiles) * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.err)) { ok = false; break; }
+          const uint32_t sa = base + stage * Cfg::kStage;
+          const uint32_t sb = sa + Cfg::kStageA;
+          mbar_expect_tx(full_bar(stage), Cfg::kStage);
+          tma_load_2d(sa, &tmap_a, kb * kBK, m0, full_bar(stage));
+          if constexpr (B_MN) {
+            // B is [k, n]: one box of [128 k rows x 128 n bytes] per 128-wide column chunk
+#pragma unroll
+            for (int c = 0; c < BN / 128; ++c) tma_load_2d(sb + c * (kBK * 128), &tmap_b, n0 + c * 128, kb * kBK, full_bar(stage));
+          } else {
+            // B is [n, k]: boxes of [128 n rows x 128 k bytes]
+#pragma unroll
+            for (int c = 0; c < (BN + 127) / 128; ++c)
+              tma_load_2d(sb + c * (128 * kBK), &tmap_b, kb * kBK, n0 + c * 128, full_bar(stage));
+          }
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // loads already issued still write this CTA's shared memory: wait (bounded) for them
+        for (int s = 0; s < Cfg::kStages; ++s) {
+          for (int i = 0; i < 200000; ++i)
+            if (mbar_try_wait(full_bar(s), 0) || mbar_try_wait(full_bar(s), 1)) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: D = s32, A = B = signed int8, A K-major, B per layout, N, M
+      const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((B_MN ? 1u : 0u) << 16) |
+                             (static_cast<uint32_t>(BN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase[2] = {0u, 0u};
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.err)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + stage * Cfg::kStage;
+          const uint32_t sb = sa + Cfg::kStageA;
+#pragma unroll
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+            const uint64_t adesc = make_desc(sa + kk * kUmmaK, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_desc(sb + kk * (kUmmaK * 128), kBK * 128, 1024)
+                                        : make_desc(sb + kk * kUmmaK, 16, 1024);
+            mma_i8(d_tmem, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(tfull_bar(acc));      // accumulator complete
+        acc_phase[acc] ^= 1u;
+        acc ^= 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5, TMEM lane quadrant = warp % 4
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase[2] = {0u, 0u};
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int64_t m0 = static_cast<int64_t>(tile % p.m_tiles) * kBM;
+      const int64_t n0 = static_cast<int64_t>(tile / p.m_tiles) * BN;
+      if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, p.err)) { ok = false; break; }
+      tc_fence_after();
+      const int64_t row = m0 + row_in_tile;
+      const bool row_ok = row < p.m;
+      const float sa = (p.scale_a && row_ok) ? p.scale_a[row] : 1.0f;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_row + static_cast<uint32_t>(c0), r);
+        tmem_ld_wait();
+        const int64_t col0 = n0 + c0;
+        if (!row_ok || col0 >= p.n) continue;
+        const bool full = col0 + 32 <= p.n;
+        if (p.acc_out) {
+          int32_t *dst = p.acc_out + row * p.ldacc + col0;
+          if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<int4 *>(dst + j) = make_int4(static_cast<int>(r[j]), static_cast<int>(r[j + 1]),
+                                                             static_cast<int>(r[j + 2]), static_cast<int>(r[j + 3]));
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = static_cast<int32_t>(r[j]);
+          }
+        }
+        if (p.out) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float sw0 = 1.0f, sw1 = 1.0f;
+            if (p.scale_b) {
+              sw0 = (col0 + j < p.n) ? __ldg(p.scale_b + col0 + j) : 1.0f;
+              sw1 = (col0 + j + 1 < p.n) ? __ldg(p.scale_b + col0 + j + 1) : 1.0f;
+            }
+            float f0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j])), sa), sw0);
+            float f1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j + 1])), sa), sw1);
+            if (p.out_dtype == BSIR_F16) {
+              f0 = fminf(fmaxf(f0, -65504.0f), 65504.0f);
+              f1 = fminf(fmaxf(f1, -65504.0f), 65504.0f);
+              packed[j >> 1] = pack_f16x2(f0, f1);
+            } else {
+              packed[j >> 1] = pack_bf16x2(f0, f1);
+            }
+          }
+          uint16_t *dst = static_cast<uint16_t *>(p.out) + row * p.ldo + col0;
+          if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+              *reinterpret_cast<uint4 *>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.n; ++j)
+              dst[j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));  // 4 arrivals (one per epilogue warp) free the buffer
+      acc_phase[acc] ^= 1u;
+      acc ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ plain fallback (any layout)
+__global__ void __launch_bounds__(256) w8a8_simple_kernel(GemmParams p, const int8_t *__restrict__ a, int64_t lda,
+                                                          const int8_t *__restrict__ b, int64_t ldb, int transpose_b) {
+  const int64_t col = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t row = blockIdx.y;
+  if (col >= p.n || row >= p.m) return;
+  int32_t acc = 0;
+  const int8_t *ar = a + row * lda;
+  if (transpose_b) {
+    const int8_t *br = b + col * ldb;
+    for (int64_t kk = 0; kk < p.k; ++kk) acc += static_cast<int32_t>(ar[kk]) * static_cast<int32_t>(br[kk]);
+  } else {
+    for (int64_t kk = 0; kk < p.k; ++kk) acc += static_cast<int32_t>(ar[kk]) * static_cast<int32_t>(b[kk * ldb + col]);
+  }
+  if (p.acc_out) p.acc_out[row * p.ldacc + col] = acc;
+  if (p.out) {
+    float f = static_cast<float>(acc);
+    if (p.scale_a) f = __fmul_rn(f, p.scale_a[row]);
+    if (p.scale_b) f = __fmul_rn(f, p.scale_b[col]);
+    uint16_t *dst = static_cast<uint16_t *>(p.out) + row * p.ldo + col;
+    if (p.out_dtype == BSIR_F16) *dst = __half_as_ushort(__float2half_rn(fminf(fmaxf(f, -65504.0f), 65504.0f)));
+    else *dst = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+  }
+}
+
+// ------------------------------------------------------------------ host side
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+// 2-D uint8 tensor map: `inner` contiguous bytes per row, `outer` rows of pitch `pitch` bytes,
+// box = [box_rows x 128 bytes], 128-byte swizzle, out-of-range bytes read as zero.
+bool make_tmap(CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t outer, uint64_t pitch, uint32_t box_rows) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch};
+  cuuint32_t box[2] = {128u, box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool B_MN>
+int32_t launch_tc(const CUtensorMap &ta, const CUtensorMap &tb, GemmParams p, cudaStream_t st) {
+  using Cfg = TileCfg<BN>;
+  // the attribute is per device and cheap to set
+  cudaFuncSetAttribute(w8a8_tc_kernel<BN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+  p.n_tiles = static_cast<int>(ceil_div(p.n, BN));
+  const int total = p.m_tiles * p.n_tiles;
+  int grid = device_info().sm_count > 0 ? device_info().sm_count : 148;
+  if (grid > total) grid = total;
+  w8a8_tc_kernel<BN, B_MN><<<grid, kThreads, Cfg::kSmemBytes, st>>>(ta, tb, p);
+  count_launch();
+  return check_launch("matmul_w8a8");
+}
+
+// Tile width: the widest N tile whose tile count still covers the SMs reasonably.
+int pick_bn(int64_t m, int64_t n, int sm_count, bool b_mn) {
+  const int64_t m_tiles = ceil_div(m, kBM);
+  const int min_bn = b_mn ? 128 : 64;
+  int best = 256;
+  double best_eff = -1.0;
+  for (int bn = 256; bn >= min_bn; bn >>= 1) {
+    const int64_t tiles = m_tiles * ceil_div(n, bn);
+    const int64_t rounds = ceil_div(tiles, sm_count);
+    double eff = static_cast<double>(tiles) / static_cast<double>(rounds * sm_count);
+    if (bn == 256) eff *= 1.0; else if (bn == 128) eff *= 0.93; else eff *= 0.85;  // narrower tiles re-read A more
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = bn; }
+  }
+  return best;
+}
+
+}  // namespace
+}  // namespace bsir
+
 using namespace bsir;
+
 extern "C" int64_t bsir_matmul_w8a8_workspace_bytes(int64_t, int64_t, int64_t, int32_t) { return 0; }
-extern "C" int32_t bsir_matmul_w8a8(int64_t, int64_t, int64_t, const int8_t *, int64_t, const int8_t *, int64_t,
-                                    int32_t, const float *, const float *, int32_t, void *, int64_t, int32_t *,
-                                    void *, int64_t, void *) {
-  return fail(BSIR_ERR_UNSUPPORTED, "matmul_w8a8: not built yet");
+
+extern "C" int32_t bsir_matmul_w8a8(int64_t m, int64_t n, int64_t k, const int8_t *a, int64_t lda, const int8_t *b,
+                                    int64_t ldb, int32_t transpose_b, const float *scale_a, const float *scale_b,
+                                    int32_t out_dtype, void *out, int64_t ldo, int32_t *acc_out, void *workspace,
+                                    int64_t workspace_bytes, void *stream) {
+  (void)workspace;
+  (void)workspace_bytes;
+  clear_error();
+  if (m < 0 || n < 0 || k < 0) return fail(BSIR_ERR_SHAPE, "matmul_w8a8: m=%lld n=%lld k=%lld", (long long)m, (long long)n, (long long)k);
+  if (m == 0 || n == 0) return BSIR_OK;
+  if (!out && !acc_out) return fail(BSIR_ERR_NULL, "matmul_w8a8: neither out nor acc_out given");
+  if (k > 0 && (!a || !b)) return fail(BSIR_ERR_NULL, "matmul_w8a8: null operand");
+  if (out && out_dtype != BSIR_BF16 && out_dtype != BSIR_F16) return fail(BSIR_ERR_DTYPE, "matmul_w8a8: out dtype %d (bf16 or f16)", out_dtype);
+  if (lda < k || ldb < (transpose_b ? k : n) || (out && ldo < n)) return fail(BSIR_ERR_STRIDE, "matmul_w8a8: leading dimension too small");
+  if (m > 0x7fffffffLL || n > 0x7fffffffLL || k > 0x7fffffffLL) return fail(BSIR_ERR_SHAPE, "matmul_w8a8: dimension exceeds int32");
+  if ((out && !aligned_to(out, 2)) || !aligned_to(acc_out, 4) || !aligned_to(scale_a, 4) || !aligned_to(scale_b, 4))
+    return fail(BSIR_ERR_ALIGN, "matmul_w8a8: misaligned");
+  cudaStream_t st = resolve_stream(stream);
+  GemmParams p{};
+  p.m = m; p.n = n; p.k = k;
+  p.scale_a = scale_a; p.scale_b = scale_b;
+  p.out = out; p.ldo = ldo; p.out_dtype = out_dtype;
+  p.acc_out = acc_out; p.ldacc = n;
+  p.err = device_error_word();
+  p.m_tiles = static_cast<int>(ceil_div(m, kBM));
+  p.k_blocks = static_cast<int>(ceil_div(k, kBK));
+
+  const bool tma_ok = k > 0 && device_info().cc_major >= 10 && aligned_to(a, 16) && aligned_to(b, 16) && lda % 16 == 0 &&
+                      ldb % 16 == 0 && encode_fn() != nullptr;
+  if (tma_ok) {
+    CUtensorMap ta, tb;
+    const bool b_mn = !transpose_b;
+    const int bn = pick_bn(m, n, device_info().sm_count > 0 ? device_info().sm_count : 148, b_mn);
+    bool ok = make_tmap(&ta, a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(lda), kBM);
+    if (b_mn) ok = ok && make_tmap(&tb, b, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(ldb), kBK);
+    else ok = ok && make_tmap(&tb, b, static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(ldb), bn < 128 ? bn : 128);
+    if (ok) {
+      if (b_mn) return bn == 256 ? launch_tc<256, true>(ta, tb, p, st) : launch_tc<128, true>(ta, tb, p, st);
+      return bn == 256 ? launch_tc<256, false>(ta, tb, p, st)
+                       : bn == 128 ? launch_tc<128, false>(ta, tb, p, st) : launch_tc<64, false>(ta, tb, p, st);
+    }
+  }
+  if (k == 0) {
+    // empty contraction: accumulators are zero
+    if (acc_out) cudaMemsetAsync(acc_out, 0, static_cast<size_t>(m) * n * 4, st);
+  }
+  const dim3 grid(static_cast<unsigned>(ceil_div(n, 256)), static_cast<unsigned>(m));
+  if (m > 65535) return fail(BSIR_ERR_UNSUPPORTED, "matmul_w8a8: unaligned operands with m > 65535");
+  w8a8_simple_kernel<<<grid, 256, 0, st>>>(p, a, lda, b, ldb, transpose_b);
+  count_launch();
+  return check_launch("matmul_w8a8 (plain path)");
 }

@@ -282,6 +282,26 @@ __device__ __forceinline__ int cta_reduce_i(int v, int *red, F f) {
   return p;
 }
 
+// Writes one row's result.  Under the first-NaN-wins rule the value is the element at the
+// reported index itself (its sign of zero and NaN payload included), as the device library's
+// scalar loop returns it (bishengir/lib/Template/lib/Vector/Reduction/ReduceR_With_Index.cpp:83-125).
+template <int DT>
+__device__ __forceinline__ void rwi_write(const RwiParams &p, const void *src, int64_t row, float val, int idx,
+                                          void *dst_val, int32_t *dst_idx) {
+  if constexpr (DT == BSIR_F32) {
+    const float *x = static_cast<const float *>(src) + row * p.row_stride;
+    static_cast<float *>(dst_val)[row] = (p.nan_first && p.cols > 0) ? x[idx] : val;
+  } else {
+    const uint16_t *x = static_cast<const uint16_t *>(src) + row * p.row_stride;
+    uint16_t bits;
+    if (p.nan_first && p.cols > 0) bits = x[idx];
+    else if constexpr (DT == BSIR_F16) bits = __half_as_ushort(__float2half_rn(val));
+    else bits = __bfloat16_as_ushort(__float2bfloat16_rn(val));
+    static_cast<uint16_t *>(dst_val)[row] = bits;
+  }
+  dst_idx[row] = idx;
+}
+
 template <int DT, int VPT, bool IS_MAX>
 __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__restrict__ src, void *__restrict__ dst_val,
                                                   int32_t *__restrict__ dst_idx, unsigned *__restrict__ counters,
@@ -388,13 +408,7 @@ __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__res
         val = __int_as_float(0x7fc00000);
         if (p.nan_first) idx = nanpos;
       }
-      float o[kPerWord];
-      o[0] = val;
-      if constexpr (kPerWord == 2) o[1] = 0.0f;
-      const uint32_t packed = FloatTraits<DT>::pack(o);
-      if constexpr (DT == BSIR_F32) static_cast<float *>(dst_val)[row] = val;
-      else static_cast<uint16_t *>(dst_val)[row] = static_cast<uint16_t>(packed & 0xffffu);
-      dst_idx[row] = idx;
+      rwi_write<DT>(p, src, row, val, idx, dst_val, dst_idx);
     }
     return;
   }
@@ -432,13 +446,7 @@ __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__res
     }
   }
   if (saw_nan) val = __int_as_float(0x7fc00000);
-  float o[kPerWord];
-  o[0] = val;
-  if constexpr (kPerWord == 2) o[1] = 0.0f;
-  const uint32_t packed = FloatTraits<DT>::pack(o);
-  if constexpr (DT == BSIR_F32) static_cast<float *>(dst_val)[row] = val;
-  else static_cast<uint16_t *>(dst_val)[row] = static_cast<uint16_t>(packed & 0xffffu);
-  dst_idx[row] = idx;
+  rwi_write<DT>(p, src, row, val, idx, dst_val, dst_idx);
   counters[row] = 0u;  // scratch is zero again for the next call
 }
 
@@ -478,10 +486,7 @@ __global__ void __launch_bounds__(256) rwi_scalar_kernel(RwiParams p, const void
       val = __int_as_float(0x7fc00000);
       if (p.nan_first) idx = nanpos;
     }
-    if constexpr (DT == BSIR_F32) static_cast<float *>(dst_val)[row] = val;
-    else if constexpr (DT == BSIR_F16) static_cast<uint16_t *>(dst_val)[row] = __half_as_ushort(__float2half_rn(val));
-    else static_cast<uint16_t *>(dst_val)[row] = __bfloat16_as_ushort(__float2bfloat16_rn(val));
-    dst_idx[row] = idx;
+    rwi_write<DT>(p, src, row, val, idx, dst_val, dst_idx);
   }
 }
 
@@ -501,9 +506,10 @@ void plan_segments(int64_t rows, int64_t nvec, int sm_count, int64_t *seg_vecs, 
   if (*nseg < 1) *nseg = 1;
 }
 
+// Scratch layout: a fixed region of per-row counters first (so that, whatever shapes follow one
+// another, only counters ever live there and "zero between calls" holds), partial results after it.
 size_t rwi_scratch_bytes(int64_t rows, int nseg) {
-  const size_t counters = (static_cast<size_t>(rows) * 4 + 255) / 256 * 256;
-  return counters + static_cast<size_t>(rows) * static_cast<size_t>(nseg) * sizeof(Partial);
+  return kScratchCounterBytes + static_cast<size_t>(rows) * static_cast<size_t>(nseg) * sizeof(Partial);
 }
 
 }  // namespace
@@ -593,7 +599,7 @@ int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie_break_le
     if (!ws) ws = static_cast<char *>(device_workspace(need, st));
     if (!ws) return BSIR_ERR_WORKSPACE;
     counters = reinterpret_cast<unsigned *>(ws);
-    partials = reinterpret_cast<Partial *>(ws + (static_cast<size_t>(rows) * 4 + 255) / 256 * 256);
+    partials = reinterpret_cast<Partial *>(ws + kScratchCounterBytes);
   }
   const dim3 grid(static_cast<unsigned>(p.nseg), static_cast<unsigned>(rows));
 #define L(D, V)                                                                                             \

@@ -183,9 +183,18 @@ static inline float minimumf_(float a, float b) {
   if (a == 0.0f && b == 0.0f) return signbit(a) ? a : b;
   return a < b ? a : b;
 }
-/* arith.maxnumf / minnumf: the non-NaN operand wins */
-static inline float maxnumf_(float a, float b) { return fmaxf(a, b); }
-static inline float minnumf_(float a, float b) { return fminf(a, b); }
+/* arith.maxnumf / minnumf: the non-NaN operand wins.  IEEE maxNum leaves the sign of max(+0, -0)
+ * open (the x86 lowering depends on operand order); this project fixes -0 < +0, as for maximumf. */
+static inline float maxnumf_(float a, float b) {
+  if (a != a) return b;
+  if (b != b) return a;
+  return maximumf_(a, b);
+}
+static inline float minnumf_(float a, float b) {
+  if (a != a) return b;
+  if (b != b) return a;
+  return minimumf_(a, b);
+}
 
 /* ------------------------------------------------------------- elementwise */
 /* unary fn codes: hfusion.unary_fn values 0..26
@@ -475,6 +484,20 @@ static float int_to_f32_mode(int64_t v, int is_u, int mode) {
   }
 }
 
+static uint16_t f32_to_f16_by_mode(float x, int round_mode);
+
+/* float -> int for one element under an overflow mode (see orc_cast). */
+static int64_t float_to_int_elem(float x, int src_dt, int dst_dt, int round_mode, int overflow_mode) {
+  if (overflow_mode == 2 || overflow_mode == 3) {
+    int rm = overflow_mode == 2 ? 4 : round_mode;
+    float h = x;
+    if (src_dt == ORC_F32) h = f16_to_f32(rm == 4 ? f32_to_f16_mode(x, 1) : f32_to_f16_by_mode(x, rm));
+    if (isinf(h)) h = h > 0 ? 65504.0f : -65504.0f;
+    return float_to_int((double)h, dst_dt, rm, 1);
+  }
+  return float_to_int((double)x, dst_dt, round_mode, overflow_mode == 1);
+}
+
 /* hfusion.cast / hivm.hir.vcast (yaml:373-432; region HFusionOps.cpp:762-796,
  * 845-861; meaning of the modes HFusionEnums.td:122-141).
  * overflow_mode: 0 wrap, 1 saturate,
@@ -511,32 +534,19 @@ ORC_API int orc_cast(int src_dt, int dst_dt, int round_mode, int overflow_mode, 
       case 2: pick = blo; break;
       case 3: pick = bhi; break;
       case 4: case 6: pick = x > 0 ? blo : bhi; break;
-      case 1: { float dl = x - lo, dh = hi - x; pick = dl < dh ? blo : dl > dh ? bhi : (x > 0 ? bhi : blo); break; }
+      case 1:
+        /* next to the overflow threshold the "other neighbour" is infinity: nearest-even already
+         * decides it (the tie at the threshold goes to infinity under both rules) */
+        if (isinf(lo) || isinf(hi)) { pick = ne; break; }
+        { float dl = x - lo, dh = hi - x; pick = dl < dh ? blo : dl > dh ? bhi : (x > 0 ? bhi : blo); break; }
       case 5: pick = (blo & 1u) ? blo : bhi; break;
       default: pick = ne; break;
       }
-      if (isinf(lo) && (round_mode == 3 || ((round_mode == 4 || round_mode == 6) && x < 0))) pick = bhi;
-      if (isinf(hi) && (round_mode == 2 || ((round_mode == 4 || round_mode == 6) && x > 0))) pick = blo;
+      if (round_mode == 5 && isinf(lo)) pick = bhi; /* round-to-odd never produces an infinity */
+      if (round_mode == 5 && isinf(hi)) pick = blo;
       ((uint16_t *)dst)[i] = pick;
     } else if (is_float(src_dt)) {
-      float x = load_f(src_dt, src, i);
-      int64_t r;
-      if (overflow_mode == 2 || overflow_mode == 3) {
-        int rm = overflow_mode == 2 ? 4 : round_mode;
-        float h;
-        if (src_dt == ORC_F32) {
-          if (rm == 4) h = f16_to_f32(f32_to_f16_mode(x, 1));
-          else { /* round_mode at the f16 step */
-            uint16_t tmp; float xx = x;
-            orc_cast(ORC_F32, ORC_F16, rm, 0, &xx, &tmp, 1);
-            h = f16_to_f32(tmp);
-          }
-        } else h = x;
-        if (isinf(h)) h = h > 0 ? 65504.0f : -65504.0f;
-        r = float_to_int((double)h, dst_dt, rm, 1);
-      } else {
-        r = float_to_int((double)x, dst_dt, round_mode, overflow_mode == 1);
-      }
+      int64_t r = float_to_int_elem(load_f(src_dt, src, i), src_dt, dst_dt, round_mode, overflow_mode);
       store_i(dst_dt, dst, i, r);
     } else if (is_float(dst_dt)) {
       int64_t v = load_i(src_dt, src, i);
@@ -564,6 +574,12 @@ ORC_API int orc_cast(int src_dt, int dst_dt, int round_mode, int overflow_mode, 
     }
   }
   return 0;
+}
+
+static uint16_t f32_to_f16_by_mode(float x, int round_mode) {
+  uint16_t tmp;
+  orc_cast(ORC_F32, ORC_F16, round_mode, 0, &x, &tmp, 1);
+  return tmp;
 }
 
 /* -------------------------------------------------------------- reductions */
@@ -766,9 +782,7 @@ ORC_API int orc_quant_per_token_i8(int dt, int round_mode, int overflow_mode, co
     scale[r] = sc;
     for (int64_t j = 0; j < cols; j++) {
       float v = load_f(dt, x, r * x_row_stride + j) / sc;
-      int8_t o;
-      orc_cast(ORC_F32, ORC_I8, round_mode, overflow_mode, &v, &o, 1);
-      q[r * q_row_stride + j] = o;
+      q[r * q_row_stride + j] = (int8_t)float_to_int_elem(v, ORC_F32, ORC_I8, round_mode, overflow_mode);
     }
   }
   return 0;

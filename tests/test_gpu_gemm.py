@@ -1,0 +1,114 @@
+"""GPU parity: W8A8 GEMM (int32 accumulators bit-exact, bf16 output within 1e-2 rel) and the
+W4A16 group-quantised GEMM (within 2e-2 rel), against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from conftest import assert_bits_equal, assert_close, to_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def bsir():
+    import bsir as B
+    B.lib()
+    O.set_threads(O.max_threads())
+    return B
+
+
+def _w8a8_case(bsir, m, n, k, transpose_b, seed=0, out_dtype=torch.bfloat16):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    a = torch.randint(-127, 128, (m, k), generator=g, device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (k, n), generator=g, device="cuda", dtype=torch.int8)
+    sa = torch.rand(m, generator=g, device="cuda") * 9e-3 + 1e-3
+    sw = torch.rand(n, generator=g, device="cuda") * 9e-3 + 1e-3
+    b = w.t().contiguous() if transpose_b else w
+    out, acc = bsir.matmul_w8a8(a, b, sa, sw, transpose_b=transpose_b, want_acc=True, out_dtype=out_dtype)
+    wout, wacc = O.matmul_w8a8(to_bits(a), to_bits(b), to_bits(sa), to_bits(sw), transpose_b=transpose_b,
+                               out_dt=O.BF16 if out_dtype == torch.bfloat16 else O.F16, want_acc=True)
+    assert np.array_equal(acc.cpu().numpy(), wacc), f"int32 accumulators differ ({m},{n},{k}) tb={transpose_b}"
+    assert_bits_equal(out, wout, f"w8a8 out ({m},{n},{k}) tb={transpose_b}")   # same f32 op order: bit-exact
+    assert bsir.device_error() == 0
+
+
+@pytest.mark.parametrize("transpose_b", [True, False])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (128, 128, 512), (16, 256, 4096), (1, 128, 128), (200, 384, 640),
+                                   (130, 320, 208), (256, 512, 1024), (128, 1000, 256), (300, 136, 144)])
+def test_w8a8_small_shapes_exact(bsir, m, n, k, transpose_b):
+    _w8a8_case(bsir, m, n, k, transpose_b, seed=m + n + k)
+
+
+def test_w8a8_f16_output_and_unaligned_fallback(bsir):
+    _w8a8_case(bsir, 64, 256, 256, False, seed=3, out_dtype=torch.float16)
+    # k = 100: the row pitch is not a multiple of 16 bytes -> plain path
+    _w8a8_case(bsir, 33, 72, 100, False, seed=4)
+    _w8a8_case(bsir, 33, 72, 100, True, seed=5)
+
+
+@pytest.mark.parametrize("m", [16, 128])
+def test_w8a8_config_small_m_full_check(bsir, m):
+    from bsir import workloads as W
+    a, sa, w, sw = W.w8a8_input(m, seed=1)
+    out, acc = bsir.matmul_w8a8(a, w, sa, sw, want_acc=True)
+    wout, wacc = O.matmul_w8a8(to_bits(a), to_bits(w), to_bits(sa), to_bits(sw), want_acc=True)
+    assert np.array_equal(acc.cpu().numpy(), wacc), "int32 accumulators differ"
+    assert_close(out, wout, 1e-2, 1e-6, f"w8a8 m={m}")
+    assert_bits_equal(out, wout, f"w8a8 m={m} bits")
+
+
+def test_w8a8_config_m4096(bsir):
+    from bsir import workloads as W
+    a, sa, w, sw = W.w8a8_input(4096, seed=2)
+    out, acc = bsir.matmul_w8a8(a, w, sa, sw, want_acc=True)
+    assert bsir.device_error() == 0
+    # 48 sampled rows (every tile row block is hit) against the oracle, bit-exact accumulators
+    rows = torch.arange(5, 4096, 86, device="cuda")
+    wout, wacc = O.matmul_w8a8(to_bits(a[rows]), to_bits(w), to_bits(sa[rows]), to_bits(sw), want_acc=True)
+    assert np.array_equal(acc[rows].cpu().numpy(), wacc), "sampled int32 accumulators differ"
+    assert_close(out[rows], wout, 1e-2, 1e-6, "w8a8 m=4096 sample")
+    # checksum over every output element: row sums of acc == A . (W . 1) in int64
+    w1 = w.cpu().numpy().astype(np.int64).sum(axis=1)
+    want_rows = a.cpu().numpy().astype(np.int64) @ w1
+    got_rows = acc.sum(dim=1, dtype=torch.int64).cpu().numpy()
+    assert np.array_equal(got_rows, want_rows), "row checksums differ"
+    # and column sums == (1 . A) . W
+    a1 = a.cpu().numpy().astype(np.int64).sum(axis=0)
+    want_cols = a1 @ w.cpu().numpy().astype(np.int64)
+    got_cols = acc.sum(dim=0, dtype=torch.int64).cpu().numpy()
+    assert np.array_equal(got_cols, want_cols), "column checksums differ"
+    # the output is the accumulator times both scales, rounded once
+    ref = (acc.float() * sa[:, None]) * sw[None, :]
+    assert torch.equal(out, ref.to(torch.bfloat16))
+    # transposed-B entry point gives the same bits
+    out_t = bsir.matmul_w8a8(a, w.t().contiguous(), sa, sw, transpose_b=True)
+    assert torch.equal(out_t, out)
+
+
+def test_w8a8_library_symbol(bsir):
+    import ctypes as C
+    L = bsir.lib()
+    L.bsir_set_stream(C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    a = torch.randint(-5, 6, (64, 256), device="cuda", dtype=torch.int8)
+    b = torch.randint(-5, 6, (256, 128), device="cuda", dtype=torch.int8)
+    c = torch.empty(64, 128, device="cuda", dtype=torch.float16)
+    f = L._mlir_ciface_matmul_Xbias_Xdescale_XtransposeA_XtransposeB_TAint8_t_TBint8_t_TChalf
+    assert f(C.byref(bsir.memref(a)), C.byref(bsir.memref(b)), C.byref(bsir.memref(c))) == 0
+    want = (a.cpu().int() @ b.cpu().int()).to(torch.float16)
+    assert torch.equal(c.cpu(), want)
+
+
+# ---------------------------------------------------------------- W4A16 (2e-2 rel, stated by the config)
+@pytest.mark.parametrize("m", [1, 2, 3, 8, 16, 5, 33])
+@pytest.mark.parametrize("n,k", [(256, 256), (14336, 4096), (1024, 1024), (136, 384)])
+def test_w4a16(bsir, m, n, k):
+    from bsir import workloads as W
+    a, qw, s, z = W.w4a16_input(m, n, k, seed=m + n)
+    out = bsir.matmul_w4a16(a, qw, s, z)
+    want = O.matmul_w4a16(to_bits(a), to_bits(qw), to_bits(s), to_bits(z))
+    assert_close(out, want, 2e-2, 2e-2 * 0.05, f"w4a16 m={m} n={n} k={k}")
+    # tighter in practice: same products, only the f32 summation order differs
+    gf = out.float().cpu().numpy()
+    wf = O.bf16_to_f32(want)
+    assert np.abs(gf - wf).max() <= 1.0 / 128 * np.abs(wf).max() + 1e-6

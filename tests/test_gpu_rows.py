@@ -120,7 +120,9 @@ def test_softmax_shapes(bsir, rows, cols, dtype):
     x = W.softmax_input(rows, cols, seed=cols + 1, dtype=dtype)
     y = bsir.softmax(x)
     wy = O.softmax(oracle_dtype(x), to_bits(x))
-    tol = (2e-5, 1e-9) if dtype == torch.float32 else (1e-2, 1e-6)
+    # f32: the oracle adds the row sequentially in f32 (error grows with the row length), the
+    # kernel adds it as a tree; the two sums differ by up to ~cols * 2^-24 relative
+    tol = (max(2e-5, cols * 6e-8 * 0.1), 1e-9) if dtype == torch.float32 else (1e-2, 1e-6)
     assert_close(y, wy, *tol, what=f"softmax {rows}x{cols} {dtype}")
 
 
