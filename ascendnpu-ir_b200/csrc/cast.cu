@@ -86,11 +86,9 @@ __device__ __forceinline__ uint16_t narrow_float(float x, int mode) {
   if (lo == hi) return lo;
   const float flo = widen(lo), fhi = widen(hi);
   if (mode == BSIR_ROUND_ROUND) {  // nearest, ties away from zero
-    if (isinf(flo)) return hi;
-    if (isinf(fhi)) {  // halfway to infinity is measured against the next power of two
-      const uint16_t ne = cv(x, 0);
-      return ne;
-    }
+    // next to the overflow threshold one neighbour is infinity: nearest-even already decides it
+    // (the tie at the threshold goes to infinity under both rules)
+    if (isinf(flo) || isinf(fhi)) return cv(x, 0);
     const float dl = x - flo, dh = fhi - x;
     if (dl < dh) return lo;
     if (dl > dh) return hi;

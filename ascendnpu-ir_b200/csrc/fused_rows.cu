@@ -102,16 +102,27 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
     if (row_ok && vi < g.nvec) v[i] = ld_stream(reinterpret_cast<const Vec16 *>(xrow) + vi);
     else v[i] = Vec16{{0u, 0u, 0u, 0u}};
   }
+  // row maximum of |x|, NaN-propagating.  16-bit types stay packed: clear both sign bits, then one
+  // max.NaN.{bf16x2,f16x2} per word.
   float amax = 0.0f;
+  if constexpr (kPerWord == 2) {
+    uint32_t m2 = 0u;
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
+    for (int i = 0; i < VPT; ++i)
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      float e[kPerWord];
-      FloatTraits<DT>::unpack(v[i].w[w], e);
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t a = v[i].w[w] & 0x7fff7fffu;
+        if constexpr (DT == BSIR_BF16) asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(a));
+        else asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(a));
+      }
+    float e[2];
+    FloatTraits<DT>::unpack(m2, e);
+    amax = maximumf(e[0], e[1]);
+  } else {
 #pragma unroll
-      for (int k = 0; k < kPerWord; ++k) amax = maximumf(amax, fabsf(e[k]));
-    }
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int w = 0; w < 4; ++w) amax = maximumf(amax, fabsf(__uint_as_float(v[i].w[w])));
   }
   amax = row_reduce(amax, g.tpr, red + sub * kMaxWarpsPerRow, 0.0f, 0, warp_red_maxnan);
   const float scale = __fdiv_rn(amax, 127.0f);
@@ -120,9 +131,53 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
 
   const bool degenerate = !(amax > 0.0f && amax < __int_as_float(0x7f800000));
   const bool fast = DT == BSIR_BF16 && round_mode == BSIR_ROUND_RINT && scale > 8.6736174e-19f && scale < 1.1529215e18f;
-  const float rcp = __frcp_rn(scale);
   int8_t *qrow = qp + row * q_stride;
 
+  if (degenerate) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
+      if (vi >= g.nvec) continue;
+      if constexpr (kPerVec == 8) *reinterpret_cast<uint2 *>(qrow + vi * 8) = make_uint2(0u, 0u);
+      else *reinterpret_cast<uint32_t *>(qrow + vi * 4) = 0u;
+    }
+    return;
+  }
+  if constexpr (DT == BSIR_BF16) {
+    if (fast) {
+      // two elements per instruction (f32x2): q0 = x r; q = fma(fma(q0, -scale, x), r, q0); then
+      // q + 1.5 * 2^23 rounds to nearest even and leaves the integer in the low mantissa byte
+      const float rcp = __frcp_rn(scale);
+      unsigned long long rcp2, nscale2, magic2;
+      asm("mov.b64 %0, {%1, %1};" : "=l"(rcp2) : "f"(rcp));
+      asm("mov.b64 %0, {%1, %1};" : "=l"(nscale2) : "f"(-scale));
+      asm("mov.b64 %0, {%1, %1};" : "=l"(magic2) : "f"(12582912.0f));
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
+        if (vi >= g.nvec) continue;
+        uint32_t lo8[8];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const uint32_t word = v[i].w[w];
+          unsigned long long x2, q0, e2, q1, r2;
+          asm("mov.b64 %0, {%1, %2};" : "=l"(x2) : "r"(word << 16), "r"(word & 0xffff0000u));
+          asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(q0) : "l"(x2), "l"(rcp2));
+          asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(e2) : "l"(q0), "l"(nscale2), "l"(x2));
+          asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q1) : "l"(e2), "l"(rcp2), "l"(q0));
+          asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r2) : "l"(q1), "l"(magic2));
+          asm("mov.b64 {%0, %1}, %2;" : "=r"(lo8[2 * w]), "=r"(lo8[2 * w + 1]) : "l"(r2));
+        }
+        // byte 0 of each of the eight results -> two packed words
+        const uint32_t p01 = __byte_perm(lo8[0], lo8[1], 0x0040), p23 = __byte_perm(lo8[2], lo8[3], 0x0040);
+        const uint32_t p45 = __byte_perm(lo8[4], lo8[5], 0x0040), p67 = __byte_perm(lo8[6], lo8[7], 0x0040);
+        *reinterpret_cast<uint2 *>(qrow + vi * 8) =
+            make_uint2(__byte_perm(p01, p23, 0x5410), __byte_perm(p45, p67, 0x5410));
+      }
+      return;
+    }
+  }
+  // general path: IEEE divide per element, any round mode, saturating conversion
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
@@ -130,7 +185,6 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
     uint32_t bytes[kPerVec / 4];
 #pragma unroll
     for (int w4 = 0; w4 < kPerVec / 4; ++w4) {
-      // four consecutive elements -> one packed word of int8
       float e[4];
       if constexpr (kPerWord == 2) {
         FloatTraits<DT>::unpack(v[i].w[2 * w4], e);
@@ -140,20 +194,8 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
         for (int k = 0; k < 4; ++k) e[k] = __uint_as_float(v[i].w[k]);
       }
       uint32_t b[4];
-      if (degenerate) {
-        b[0] = b[1] = b[2] = b[3] = 0u;
-      } else if (fast) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const float q0 = __fmul_rn(e[k], rcp);
-          const float q1 = __fmaf_rn(__fmaf_rn(-q0, scale, e[k]), rcp, q0);
-          // |q1| < 128: adding 1.5 * 2^23 rounds to nearest even and leaves the integer in the low bits
-          b[k] = __float_as_uint(__fadd_rn(q1, 12582912.0f));
-        }
-      } else {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) b[k] = static_cast<uint32_t>(sat_i8(round_by_mode(__fdiv_rn(e[k], scale), round_mode)));
-      }
+      for (int k = 0; k < 4; ++k) b[k] = static_cast<uint32_t>(sat_i8(round_by_mode(__fdiv_rn(e[k], scale), round_mode)));
       bytes[w4] = (b[0] & 0xffu) | ((b[1] & 0xffu) << 8) | ((b[2] & 0xffu) << 16) | (b[3] << 24);
     }
     if constexpr (kPerVec == 8) {
@@ -235,14 +277,46 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) rmsno
 // ------------------------------------------------------------------ softmax
 // m = max over non-NaN x; e = exp(x - m); y = cast_rint(e / sum e)
 // (test/Dialect/Analysis/VFFusion/MaxParallelKind/softmax_small_shape.mlir:86-117).
-// exp runs on the special-function unit (ex2.approx of (x - m) * log2 e, relative error below
-// 3e-6 for the arguments a softmax sees); the division by the row sum is a reciprocal with one
-// correction step.
+// exp runs on the special-function unit: ex2.approx(x log2e - m log2e), relative error below 3e-6
+// for the arguments a softmax sees (results below 2^-126 flush to zero).  The arithmetic around it is
+// two elements per instruction (f32x2).  16-bit outputs multiply by the reciprocal of the row sum
+// (the result is rounded to 8 or 11 bits afterwards); f32 outputs add one correction step so the
+// quotient is the IEEE one.
+__device__ __forceinline__ unsigned long long pack2(float a, float b) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float &a, float &b) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
 template <int DT, int VPT>
 __global__ void __launch_bounds__(VPT * (DT == BSIR_F32 ? 4 : 8) > 32 ? 256 : 1024) softmax_rows_kernel(RowGeom g, const void *__restrict__ xp, int64_t x_stride,
                                                             void *__restrict__ yp, int64_t y_stride) {
   constexpr int kPerWord = FloatTraits<DT>::kPerWord;
   constexpr int kPerVec = 4 * kPerWord;
+  constexpr int kPairs = VPT * kPerVec / 2;   // element pairs held by a thread
   __shared__ float red_max[kMaxWarpsPerRow * 32];
   __shared__ float red_sum[kMaxWarpsPerRow * 32];
   using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
@@ -252,60 +326,93 @@ __global__ void __launch_bounds__(VPT * (DT == BSIR_F32 ? 4 : 8) > 32 ? 256 : 10
   const bool row_ok = row < g.rows;
   const E *xrow = static_cast<const E *>(xp) + (row_ok ? row : 0) * x_stride;
   const float ninf = __int_as_float(0xff800000);
+  // padding is -inf in the storage type: ignored by the max, exp gives 0
+  constexpr uint32_t kPad = DT == BSIR_F32 ? 0xff800000u : DT == BSIR_BF16 ? 0xff80ff80u : 0xfc00fc00u;
 
   Vec16 v[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
     if (row_ok && vi < g.nvec) v[i] = ld_stream(reinterpret_cast<const Vec16 *>(xrow) + vi);
-    else v[i] = Vec16{{0u, 0u, 0u, 0u}};
+    else v[i] = Vec16{{kPad, kPad, kPad, kPad}};
   }
-  float e[VPT * kPerVec];
+  // row maximum, NaN ignored (= the NaN -> -inf mask of the reference IR); 16-bit types stay packed
   float m = ninf;
+  if constexpr (kPerWord == 2) {
+    uint32_t m2 = kPad;
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const bool live = (t + static_cast<int64_t>(i) * g.tpr) < g.nvec;
+    for (int i = 0; i < VPT; ++i)
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      FloatTraits<DT>::unpack(v[i].w[w], e + i * kPerVec + w * kPerWord);
-#pragma unroll
-      for (int k = 0; k < kPerWord; ++k) {
-        if (!live) e[i * kPerVec + w * kPerWord + k] = ninf;  // padding: exp -> 0, ignored by the max
-        m = fmaxf(m, e[i * kPerVec + w * kPerWord + k]);      // fmaxf skips NaN = the NaN -> -inf mask
+      for (int w = 0; w < 4; ++w) {
+        if constexpr (DT == BSIR_BF16) asm("max.bf16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
+        else asm("max.f16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
       }
-    }
+    float e2[2];
+    FloatTraits<DT>::unpack(m2, e2);
+    m = fmaxf(e2[0], e2[1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i)
+#pragma unroll
+      for (int w = 0; w < 4; ++w) m = fmaxf(m, __uint_as_float(v[i].w[w]));
   }
   m = row_reduce(m, g.tpr, red_max + sub * kMaxWarpsPerRow, ninf, 0, warp_red_maxnum);
-  float s = 0.0f;
+
   const float kLog2e = 1.4426950408889634f;
+  const unsigned long long l2e2 = pack2(kLog2e, kLog2e);
+  const float nm = -m * kLog2e;   // -inf * c stays inf of the right sign; NaN cannot occur (m ignores NaN)
+  const unsigned long long nm2 = pack2(nm, nm);
+  unsigned long long e[kPairs];
+  unsigned long long s2 = pack2(0.0f, 0.0f);
 #pragma unroll
-  for (int j = 0; j < VPT * kPerVec; ++j) {
-    const float d = __fmul_rn(__fsub_rn(e[j], m), kLog2e);
-    float ex;
-    asm("ex2.approx.f32 %0, %1;" : "=f"(ex) : "f"(d));
-    e[j] = ex;
-    s += ex;
+  for (int pi = 0; pi < kPairs; ++pi) {
+    float x0, x1;
+    if constexpr (kPerWord == 2) {
+      const uint32_t word = v[pi / 4].w[pi % 4];
+      float xe[2];
+      FloatTraits<DT>::unpack(word, xe);
+      x0 = xe[0];
+      x1 = xe[1];
+    } else {
+      x0 = __uint_as_float(v[pi / 2].w[(pi % 2) * 2]);
+      x1 = __uint_as_float(v[pi / 2].w[(pi % 2) * 2 + 1]);
+    }
+    const unsigned long long d = fma2(pack2(x0, x1), l2e2, nm2);
+    float d0, d1;
+    unpack2(d, d0, d1);
+    e[pi] = pack2(ex2_approx(d0), ex2_approx(d1));
+    s2 = add2(s2, e[pi]);
   }
-  // padding lanes hold exp(-inf - m): 0 for any m except -inf, where the live lanes are NaN too.
-  s = row_reduce(s, g.tpr, red_sum + sub * kMaxWarpsPerRow, 0.0f, 0, warp_red_sum);
+  float s0, s1;
+  unpack2(s2, s0, s1);
+  float s = row_reduce(s0 + s1, g.tpr, red_sum + sub * kMaxWarpsPerRow, 0.0f, 0, warp_red_sum);
   if (!row_ok) return;
   const float rcp = __frcp_rn(s);
+  const unsigned long long rcp2 = pack2(rcp, rcp), ns2 = pack2(-s, -s);
   E *yrow = static_cast<E *>(yp) + row * y_stride;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
     if (vi >= g.nvec) continue;
     Vec16 o;
+    if constexpr (kPerWord == 2) {
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
-      float r[kPerWord];
-#pragma unroll
-      for (int k = 0; k < kPerWord; ++k) {
-        const float ev = e[i * kPerVec + w * kPerWord + k];
-        const float q0 = __fmul_rn(ev, rcp);
-        r[k] = __fmaf_rn(__fmaf_rn(-q0, s, ev), rcp, q0);
+      for (int w = 0; w < 4; ++w) {
+        float y0, y1;
+        unpack2(mul2(e[i * 4 + w], rcp2), y0, y1);
+        const float yy[2] = {y0, y1};
+        o.w[w] = FloatTraits<DT>::pack(yy);
       }
-      o.w[w] = FloatTraits<DT>::pack(r);
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const unsigned long long ev = e[i * 2 + h];
+        const unsigned long long q0 = mul2(ev, rcp2);
+        float y0, y1;
+        unpack2(fma2(fma2(q0, ns2, ev), rcp2, q0), y0, y1);
+        o.w[2 * h] = __float_as_uint(y0);
+        o.w[2 * h + 1] = __float_as_uint(y1);
+      }
     }
     st_stream(reinterpret_cast<Vec16 *>(yrow) + vi, o);
   }
@@ -388,21 +495,28 @@ int env_int(const char *name, int dflt) {
   return s && *s ? std::atoi(s) : dflt;
 }
 
-// Picks threads-per-row and vectors-per-thread: the fewest threads (>= 32, power of two) that
-// keep a thread at or under `max_vpt` vectors.  Returns false when the row does not fit.
-bool pick_geometry(int64_t rows, int64_t cols, int elem_bytes, int max_vpt, int min_tpr, RowGeom *g, int *vpt) {
+// Picks threads-per-row (TPR, a power of two in 32..1024) and vectors-per-thread (VPT).  Measured on
+// B200: rows spread over enough threads that each holds about `want_vpt` vectors run fastest (4 for
+// the 8 KB rows of the benchmark shapes); `max_vpt` is what the kernel's registers can hold.
+// Register budget: 16 vectors per thread only up to 256 threads per CTA, 8 up to 512, 4 at 1024.
+// Returns false when the row does not fit.
+bool pick_geometry(int64_t rows, int64_t cols, int elem_bytes, int max_vpt, int want_vpt, int forced_tpr, RowGeom *g,
+                   int *vpt) {
   const int per_vec = 16 / elem_bytes;
   if (cols <= 0 || cols % per_vec) return false;
   const int64_t nvec = cols / per_vec;
-  int tpr = min_tpr;
-  while (tpr < 1024 && ceil_div(nvec, tpr) > max_vpt) tpr <<= 1;
-  int64_t need = ceil_div(nvec, tpr);
-  // register budget: 16 vectors per thread only up to 256 threads per CTA, 8 up to 512, 4 at 1024
-  while (tpr < 1024 && ((tpr > 256 && need > 8) || (tpr > 128 && need > 16))) { tpr <<= 1; need = ceil_div(nvec, tpr); }
-  if (need > max_vpt || (tpr == 1024 && need > 4) || (tpr == 512 && need > 8)) return false;
+  auto allowed = [&](int tpr) { int a = tpr <= 256 ? 16 : tpr <= 512 ? 8 : 4; return a < max_vpt ? a : max_vpt; };
+  int tpr = 32;
+  if (forced_tpr >= 32 && forced_tpr <= 1024 && (forced_tpr & (forced_tpr - 1)) == 0) {
+    tpr = forced_tpr;
+  } else {
+    while (tpr < 1024 && ceil_div(nvec, tpr) > want_vpt) tpr <<= 1;
+  }
+  while (tpr < 1024 && ceil_div(nvec, tpr) > allowed(tpr)) tpr <<= 1;
+  const int64_t need = ceil_div(nvec, tpr);
+  if (need > allowed(tpr)) return false;
   int v = 1;
   while (v < need) v <<= 1;
-  // prefer more threads over idle vector slots when a thread would hold mostly padding
   g->rows = rows; g->cols = cols; g->nvec = nvec; g->tpr = tpr;
   const int cta = tpr < 128 ? 128 : tpr;
   g->rpc = cta / tpr;
@@ -469,7 +583,7 @@ int32_t bsir_quant_per_token_i8(int32_t dtype, int32_t round_mode, int64_t rows,
   int vpt = 0;
   const int per_vec = 16 / eb;
   const bool vec_ok = cols > 0 && rows_vector_ok(x, x_row_stride, eb) && aligned_to(q, per_vec) && q_row_stride % per_vec == 0 &&
-                      pick_geometry(rows, cols, eb, 16, env_int("BSIR_QUANT_TPR", 32), &g, &vpt);
+                      pick_geometry(rows, cols, eb, 16, 4, env_int("BSIR_QUANT_TPR", 0), &g, &vpt);
   if (vec_ok) {
     const unsigned blocks = static_cast<unsigned>(ceil_div(rows, g.rpc));
     const unsigned threads = static_cast<unsigned>(g.tpr * g.rpc);
@@ -498,7 +612,7 @@ int32_t bsir_rms_norm(int32_t dtype, int64_t rows, int64_t cols, const void *x, 
   RowGeom g;
   int vpt = 0;
   const bool vec_ok = cols > 0 && rows_vector_ok(x, x_row_stride, eb) && rows_vector_ok(y, y_row_stride, eb) &&
-                      aligned_to(gamma, 16) && pick_geometry(rows, cols, eb, 16, env_int("BSIR_RMS_TPR", 32), &g, &vpt);
+                      aligned_to(gamma, 16) && pick_geometry(rows, cols, eb, 16, 4, env_int("BSIR_RMS_TPR", 0), &g, &vpt);
   if (vec_ok) {
     const unsigned blocks = static_cast<unsigned>(ceil_div(rows, g.rpc));
     const unsigned threads = static_cast<unsigned>(g.tpr * g.rpc);
@@ -525,7 +639,7 @@ int32_t bsir_softmax(int32_t dtype, int64_t rows, int64_t cols, const void *x, i
   // exp values live in registers: at most 32 per thread
   const int max_vpt = eb == 4 ? 8 : 4;
   const bool vec_ok = rows_vector_ok(x, x_row_stride, eb) && rows_vector_ok(y, y_row_stride, eb) &&
-                      pick_geometry(rows, cols, eb, max_vpt, env_int("BSIR_SOFTMAX_TPR", 32), &g, &vpt);
+                      pick_geometry(rows, cols, eb, max_vpt, 4, env_int("BSIR_SOFTMAX_TPR", 0), &g, &vpt);
   if (vec_ok) {
     const unsigned blocks = static_cast<unsigned>(ceil_div(rows, g.rpc));
     const unsigned threads = static_cast<unsigned>(g.tpr * g.rpc);

@@ -229,7 +229,7 @@ int32_t reduce_axis(const char *what, bool last, int32_t kind, int32_t dtype, in
 }
 
 // ------------------------------------------------------------------ reduce_with_index
-// A row is cut into segments of up to 256 x VPT 16-byte vectors; one CTA per (segment, row)
+// A row is cut into segments of up to 256 x VPT (VPT <= 8) 16-byte vectors; one CTA per (segment, row)
 // keeps its segment in registers, finds the segment extreme with a NaN-propagating
 // max/min, then looks for the first (or last) element equal to it.  Partial results go to a
 // scratch array; the CTA that finishes a row last (a counter in the same scratch, left at zero
@@ -325,21 +325,41 @@ __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__res
     const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
     if (vi < v1) v[i] = ld_stream(reinterpret_cast<const Vec16 *>(xrow) + vi);
   }
-  // pass 1: NaN-propagating extreme
+  // pass 1: NaN-propagating extreme; 16-bit types stay packed (one max/min.NaN.x2 per word)
   float m = ident;
+  if constexpr (kPerWord == 2) {
+    constexpr uint32_t kIdent2 = DT == BSIR_BF16 ? (IS_MAX ? 0xff80ff80u : 0x7f807f80u) : (IS_MAX ? 0xfc00fc00u : 0x7c007c00u);
+    uint32_t m2 = kIdent2;
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
-    if (vi < v1) {
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
+      if (vi < v1) {
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        float e[kPerWord];
-        FloatTraits<DT>::unpack(v[i].w[w], e);
+        for (int w = 0; w < 4; ++w) {
+          if constexpr (DT == BSIR_BF16) {
+            if constexpr (IS_MAX) asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
+            else asm("min.NaN.bf16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
+          } else {
+            if constexpr (IS_MAX) asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
+            else asm("min.NaN.f16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
+          }
+        }
+      }
+    }
+    float e2[2];
+    FloatTraits<DT>::unpack(m2, e2);
+    m = ext_nan<IS_MAX>(e2[0], e2[1]);
+  } else {
 #pragma unroll
-        for (int k = 0; k < kPerWord; ++k) m = ext_nan<IS_MAX>(m, e[k]);
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
+      if (vi < v1) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = ext_nan<IS_MAX>(m, __uint_as_float(v[i].w[w]));
       }
     }
   }
+  const float tm = m;  // this thread's own extreme
   m = cta_reduce_f(m, redf, [](float a, float b) { return ext_nan<IS_MAX>(a, b); });
 
   int nanpos = INT_MAX;
@@ -378,19 +398,23 @@ __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__res
     m = cta_reduce_f(m, redf, [](float a, float b) { return ext_nan<IS_MAX>(a, b); });
   }
   // pass 2: first (or last) index holding the extreme, among elements before nanpos
+  // Only threads whose own extreme equals the segment's can hold it (all threads rescan in the rare
+  // NaN case, where the extreme was recomputed over a prefix).
   int best = p.tie_left ? INT_MAX : -1;
+  if (nanpos != INT_MAX || tm == m) {
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
-    if (vi < v1) {
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
+      if (vi < v1) {
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        float e[kPerWord];
-        FloatTraits<DT>::unpack(v[i].w[w], e);
+        for (int w = 0; w < 4; ++w) {
+          float e[kPerWord];
+          FloatTraits<DT>::unpack(v[i].w[w], e);
 #pragma unroll
-        for (int k = 0; k < kPerWord; ++k) {
-          const int gi = static_cast<int>(vi * kPerVec + w * kPerWord + k);
-          if (e[k] == m && gi < nanpos) best = p.tie_left ? min(best, gi) : max(best, gi);
+          for (int k = 0; k < kPerWord; ++k) {
+            const int gi = static_cast<int>(vi * kPerVec + w * kPerWord + k);
+            if (e[k] == m && gi < nanpos) best = p.tie_left ? min(best, gi) : max(best, gi);
+          }
         }
       }
     }
@@ -490,13 +514,13 @@ __global__ void __launch_bounds__(256) rwi_scalar_kernel(RwiParams p, const void
   }
 }
 
-// Segment plan: enough CTAs to fill the device, segments of at most 256 x 16 vectors.
+// Segment plan: enough CTAs to fill the device, segments of at most 256 x 8 vectors.
 void plan_segments(int64_t rows, int64_t nvec, int sm_count, int64_t *seg_vecs, int *nseg, int *vpt) {
   const int64_t target_ctas = static_cast<int64_t>(sm_count > 0 ? sm_count : 148) * 4;
   int64_t want_seg = rows > 0 ? ceil_div(target_ctas, rows) : 1;
   if (want_seg < 1) want_seg = 1;
   int64_t sv = ceil_div(nvec, want_seg);
-  if (sv > 4096) sv = 4096;
+  if (sv > 2048) sv = 2048;
   if (sv < 256) sv = 256;
   int v = 1;
   while (v * 256 < sv) v <<= 1;

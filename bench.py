@@ -163,11 +163,13 @@ def time_op(torch, fn, iters: int, warm: int = 3):
     return tot / reps, best
 
 
-def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters):
+def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters, only=None):
     """The remaining configurations, each with inputs larger than L2 or rotated buffers."""
     res = {}
 
     def rec(name, algo_bytes, fn, flops=None, note=None):
+        if only and name != only:
+            return
         try:
             avg, best = time_op(torch, fn, iters)
         except Exception as e:  # an op that is not built yet must not hide the others
@@ -182,35 +184,49 @@ def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters):
             r["note"] = note
         res[name] = r
 
+    def want(name):
+        return not only or name == only
+
     n = 1 << 24
     for dt, nm in ((torch.float32, "vecadd_f32"), (torch.float16, "vecadd_f16")):
+        if not want(nm):
+            continue
         bufs = [W.vecadd(n, dt, seed=s) for s in range(3)]
         outs = [torch.empty_like(b[0]) for b in bufs]
         rec(nm, 3 * n * bufs[0][0].element_size(), lambda i: bsir.vadd(*bufs[i % 3], out=outs[i % 3]))
         del bufs, outs
-    xs = [W.rmsnorm_input(32768, 4096, seed=s) for s in range(2)]
-    ys = [torch.empty_like(x[0]) for x in xs]
-    rec("rmsnorm_bf16_32768x4096", 2 * 32768 * 4096 * 2 + 8192, lambda i: bsir.rms_norm(xs[i % 2][0], xs[i % 2][1], 1e-6, out=ys[i % 2]))
-    del xs, ys
-    xs = [W.softmax_input(4096, 32768, seed=s) for s in range(2)]
-    ys = [torch.empty_like(x) for x in xs]
-    rec("softmax_bf16_4096x32768", 2 * 4096 * 32768 * 2, lambda i: bsir.softmax(xs[i % 2], out=ys[i % 2]))
-    del xs, ys
-    xs = [W.argmax_input(256, 152064, seed=s) for s in range(4)]
-    rec("argmax_bf16_256x152064", 256 * 152064 * 2 + 256 * 6, lambda i: bsir.reduce_with_index("max", xs[i % 4]))
-    del xs
+    if want("rmsnorm_bf16_32768x4096"):
+        xs = [W.rmsnorm_input(32768, 4096, seed=s) for s in range(2)]
+        ys = [torch.empty_like(x[0]) for x in xs]
+        rec("rmsnorm_bf16_32768x4096", 2 * 32768 * 4096 * 2 + 8192,
+            lambda i: bsir.rms_norm(xs[i % 2][0], xs[i % 2][1], 1e-6, out=ys[i % 2]))
+        del xs, ys
+    if want("softmax_bf16_4096x32768"):
+        xs = [W.softmax_input(4096, 32768, seed=s) for s in range(2)]
+        ys = [torch.empty_like(x) for x in xs]
+        rec("softmax_bf16_4096x32768", 2 * 4096 * 32768 * 2, lambda i: bsir.softmax(xs[i % 2], out=ys[i % 2]))
+        del xs, ys
+    if want("argmax_bf16_256x152064"):
+        xs = [W.argmax_input(256, 152064, seed=s) for s in range(4)]
+        rec("argmax_bf16_256x152064", 256 * 152064 * 2 + 256 * 6, lambda i: bsir.reduce_with_index("max", xs[i % 4]))
+        del xs
     for m in (16, 128, 4096):
+        if not want(f"w8a8_m{m}"):
+            continue
         try:
             sets = [W.w8a8_input(m, seed=s) for s in range(3 if m < 4096 else 2)]
             outs = [torch.empty(m, 14336, dtype=torch.bfloat16, device="cuda") for _ in sets]
             k = len(sets)
             byts = m * 4096 + 4096 * 14336 + m * 14336 * 2 + m * 4 + 14336 * 4
-            rec(f"w8a8_m{m}", byts, lambda i: bsir.matmul_w8a8(sets[i % k][0], sets[i % k][2], sets[i % k][1], sets[i % k][3], out=outs[i % k]),
+            rec(f"w8a8_m{m}", byts,
+                lambda i: bsir.matmul_w8a8(sets[i % k][0], sets[i % k][2], sets[i % k][1], sets[i % k][3], out=outs[i % k]),
                 flops=2 * m * 4096 * 14336)
             del sets, outs
         except Exception as e:
             res[f"w8a8_m{m}"] = {"error": str(e)[:200]}
     for m in (1, 8, 16):
+        if not want(f"w4a16_m{m}"):
+            continue
         try:
             sets = [W.w4a16_input(m, seed=s) for s in range(6)]     # 6 x 30 MB of weights > L2
             outs = [torch.empty(m, 14336, dtype=torch.bfloat16, device="cuda") for _ in sets]
@@ -354,7 +370,8 @@ def run_ours(args):
             if not args.no_ops:
                 del xs, qs, ss
                 torch.cuda.empty_cache()
-                line["ops"] = other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters=max(5, min(args.steps, 20)))
+                line["ops"] = other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters=max(3, min(args.steps, 20)),
+                                        only=args.only_op)
         print(json.dumps(line), flush=True)
     if dist:
         dist.barrier()
@@ -368,6 +385,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-ops", action="store_true", help="skip the per-configuration table")
+    ap.add_argument("--only-op", default=None, help="run just this entry of the per-configuration table (for profiling)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
