@@ -9,6 +9,7 @@
 // bishengir/lib/Dialect/HFusion/Transforms/Normalize.cpp:7679-7716) in a tree order, so they
 // match the sequential CPU order only to rounding; everything else is order-independent.
 #include <climits>
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -645,3 +646,132 @@ int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie_break_le
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------ reduce_with_index without allocation
+// Some hosts hand every byte of device memory to their own pool at start-up (an inference server that
+// sizes its cache to whatever is left), or call from places where the CUDA allocator must not be
+// entered; they cannot let a library call cudaMalloc behind their back, and they may have no pool
+// block to spare for a workspace argument either.  For them the scratch of the segmented argmax /
+// argmin lives in the library image itself: a fixed array in device memory that every GPU loading the
+// library carries until the process exits.
+namespace bsir {
+namespace {
+
+constexpr int kStaticMaxRows = 4096;                                   // one counter per row
+constexpr size_t kStaticCounterBytes = kStaticMaxRows * sizeof(unsigned);
+constexpr size_t kStaticScratchBytes = 512 * 1024;                     // counters + partial results
+constexpr size_t kStaticMaxPartials = (kStaticScratchBytes - kStaticCounterBytes) / sizeof(Partial);
+
+static __device__ __align__(256) unsigned char g_rwi_static_scratch[kStaticScratchBytes];
+
+// Device address of the array on each device, looked up once per device.  In host code the array's
+// name is only a handle for the runtime, not a pointer a kernel could use.
+void *g_rwi_static_ptr[64] = {nullptr};
+std::mutex g_rwi_static_mu;
+
+int32_t static_scratch(void **out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return fail(BSIR_ERR_WORKSPACE, "reduce_with_index_static: no current CUDA device");
+  }
+  std::lock_guard<std::mutex> lock(g_rwi_static_mu);
+  if (!g_rwi_static_ptr[dev]) {
+    void *ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_rwi_static_scratch);
+    if (e != cudaSuccess || !ptr) {
+      cudaGetLastError();
+      return fail(BSIR_ERR_WORKSPACE, "reduce_with_index_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    }
+    g_rwi_static_ptr[dev] = ptr;
+  }
+  *out = g_rwi_static_ptr[dev];
+  return BSIR_OK;
+}
+
+}  // namespace
+}  // namespace bsir
+
+// Same result as bsir_reduce_with_index, with the scratch taken from the fixed in-library array:
+// no cudaMalloc, cudaFree or other allocating call, on any path.
+//
+// Limits: rows <= 4096 and rows x segments <= 31744 partial results (the segment count is what
+// bsir_reduce_with_index would choose; the 256 x 152064 benchmark shape needs 2560).  Larger
+// problems are refused with BSIR_ERR_WORKSPACE and nothing is enqueued.
+//
+// The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+// that device current); make that first call before any stream capture begins on the device.
+// All calls share the one array, which keeps whatever the previous call left in it: the row
+// counters the kernel needs at zero are cleared on `stream` ahead of each launch.  Two calls whose
+// kernels may overlap on the GPU (different streams, no ordering between them) race on the array;
+// order them, or give one of them bsir_reduce_with_index with a workspace of its own.
+extern "C" int32_t bsir_reduce_with_index_static(int32_t kind, int32_t dtype, int32_t tie_break_left, int32_t nan_mode,
+                                                 int64_t rows, int64_t cols, const void *src, int64_t src_row_stride,
+                                                 void *dst_value, int32_t *dst_index, void *stream) {
+  clear_error();
+  if (!dtype_is_float(dtype)) return fail(BSIR_ERR_DTYPE, "reduce_with_index_static: dtype %d (f32, f16 or bf16)", dtype);
+  if (kind != BSIR_RWI_MAX && kind != BSIR_RWI_MIN) return fail(BSIR_ERR_ATTR, "reduce_with_index_static: kind %d", kind);
+  if (nan_mode != BSIR_RWI_NAN_REGION && nan_mode != BSIR_RWI_NAN_FIRST)
+    return fail(BSIR_ERR_ATTR, "reduce_with_index_static: nan_mode %d", nan_mode);
+  if (rows < 0 || cols < 0) return fail(BSIR_ERR_SHAPE, "reduce_with_index_static: rows=%lld cols=%lld", (long long)rows, (long long)cols);
+  if (cols > INT_MAX - 64) return fail(BSIR_ERR_SHAPE, "reduce_with_index_static: cols exceed the int32 index range");
+  if (rows > kStaticMaxRows)
+    return fail(BSIR_ERR_WORKSPACE, "reduce_with_index_static: %lld rows exceed the fixed scratch (at most %d rows)",
+                (long long)rows, kStaticMaxRows);
+  if (rows == 0) return BSIR_OK;
+  if (!dst_value || !dst_index || (!src && cols > 0)) return fail(BSIR_ERR_NULL, "reduce_with_index_static: null pointer");
+  if (src_row_stride < cols) return fail(BSIR_ERR_STRIDE, "reduce_with_index_static: row stride < cols");
+  const int eb = dtype_bytes(dtype);
+  if (!aligned_to(src, eb) || !aligned_to(dst_value, eb) || !aligned_to(dst_index, 4))
+    return fail(BSIR_ERR_ALIGN, "reduce_with_index_static: misaligned");
+  void *scratch = nullptr;
+  if (int32_t rc = static_scratch(&scratch)) return rc;
+  cudaStream_t st = resolve_stream(stream);
+  RwiParams p{};
+  p.rows = rows; p.cols = cols; p.row_stride = src_row_stride;
+  p.tie_left = tie_break_left ? 1 : 0;
+  p.nan_first = nan_mode == BSIR_RWI_NAN_FIRST;
+  const bool is_max = kind == BSIR_RWI_MAX;
+  const int per_vec = 16 / eb;
+  const bool vec_ok = cols > 0 && cols % per_vec == 0 && aligned_to(src, 16) && (src_row_stride * eb) % 16 == 0;
+  if (!vec_ok) {
+    p.nseg = 1;  // the one-CTA-per-row kernel needs no scratch at all
+#define S(D) \
+  if (is_max) rwi_scalar_kernel<D, true><<<static_cast<unsigned>(rows), 256, 0, st>>>(p, src, dst_value, dst_index); \
+  else rwi_scalar_kernel<D, false><<<static_cast<unsigned>(rows), 256, 0, st>>>(p, src, dst_value, dst_index);
+    if (dtype == BSIR_F32) { S(BSIR_F32) } else if (dtype == BSIR_F16) { S(BSIR_F16) } else { S(BSIR_BF16) }
+#undef S
+    count_launch();
+    return check_launch("reduce_with_index_static");
+  }
+  p.nvec = cols / per_vec;
+  int vpt = 1;
+  plan_segments(rows, p.nvec, device_info().sm_count, &p.seg_vecs, &p.nseg, &vpt);
+  if (static_cast<size_t>(rows) * static_cast<size_t>(p.nseg) > kStaticMaxPartials)
+    return fail(BSIR_ERR_WORKSPACE,
+                "reduce_with_index_static: %lld rows x %d segments exceed the fixed scratch (at most %zu partial results)",
+                (long long)rows, p.nseg, kStaticMaxPartials);
+  unsigned *counters = reinterpret_cast<unsigned *>(scratch);
+  Partial *partials = reinterpret_cast<Partial *>(static_cast<unsigned char *>(scratch) + kStaticCounterBytes);
+  if (p.nseg > 1) {
+    // the counters must start at zero whatever an earlier (possibly failed) call left behind
+    if (cudaMemsetAsync(counters, 0, static_cast<size_t>(rows) * sizeof(unsigned), st) != cudaSuccess)
+      return check_launch("reduce_with_index_static (clearing the counters)");
+  }
+  const dim3 grid(static_cast<unsigned>(p.nseg), static_cast<unsigned>(rows));
+#define L(D, V)                                                                                             \
+  if (is_max) rwi_kernel<D, V, true><<<grid, 256, 0, st>>>(p, src, dst_value, dst_index, counters, partials); \
+  else rwi_kernel<D, V, false><<<grid, 256, 0, st>>>(p, src, dst_value, dst_index, counters, partials);
+#define LV(D)                      \
+  switch (vpt) {                   \
+    case 1: L(D, 1) break;         \
+    case 2: L(D, 2) break;         \
+    case 4: L(D, 4) break;         \
+    default: L(D, 8) break;        \
+  }
+  if (dtype == BSIR_F32) { LV(BSIR_F32) } else if (dtype == BSIR_F16) { LV(BSIR_F16) } else { LV(BSIR_BF16) }
+#undef LV
+#undef L
+  count_launch();
+  return check_launch("reduce_with_index_static");
+}

@@ -266,6 +266,18 @@ BSIR_API int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie
                                         int32_t *dst_index, void *workspace,
                                         int64_t workspace_bytes, void *stream);
 
+/* bsir_reduce_with_index for hosts that cannot let the library allocate: no counterpart in the
+ * reference (its device library gets `tmp_buf` from the compiler's memory planner).  The scratch is
+ * a fixed 512 KiB array inside the library image, so the call never reaches cudaMalloc or cudaFree.
+ * Limits: rows <= 4096 and rows x segments <= 31744 (the 256 x 152064 benchmark shape uses 2560);
+ * beyond them the call returns BSIR_ERR_WORKSPACE and enqueues nothing.  The first call on a device
+ * looks up the array's device address: make it before any stream capture on that device.  All calls
+ * share the array; calls whose kernels can overlap on the GPU race and must be ordered by the caller. */
+BSIR_API int32_t bsir_reduce_with_index_static(int32_t kind, int32_t dtype, int32_t tie_break_left,
+                                               int32_t nan_mode, int64_t rows, int64_t cols,
+                                               const void *src, int64_t src_row_stride, void *dst_value,
+                                               int32_t *dst_index, void *stream);
+
 /* Fused LAST_AXIS_PBR pattern RMSNorm
  * (test/bishengir-compile/hfusion/compile-rms-norm-fp16-split-n.mlir:13-71):
  * y = cast_rint(gamma32 * (rstd * x32)), rstd = 1 / sqrt(sum(x32^2) * (1/cols) + eps);
