@@ -1,0 +1,80 @@
+"""Multi-GPU partitioning of the operator set: one process per GPU, `torch.distributed` for plumbing.
+
+Row-wise ops (elementwise, cast, per-token quantisation, RMSNorm, softmax, argmax) are independent per
+row, so rank r simply owns rows [lo, hi) and no collective runs on the data path.  GEMMs are sharded
+by output column: rank r holds W[:, lo:hi] (and scale_b[lo:hi], or the matching qweight / scales /
+zeros columns) with A replicated; an all-gather reassembles [M, N] only where a consumer needs it.
+The reference has no counterpart (a single-kernel compiler; its cross-device layer is a thin wrapper
+over aclshmem put/get, bishengir/lib/Template/lib/Shmem/Shmem.cpp:27-120).
+"""
+from __future__ import annotations
+
+from typing import List, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def even_split(total: int, parts: int, multiple: int = 1) -> List[Tuple[int, int]]:
+    """Contiguous [lo, hi) ranges covering [0, total): sizes differ by at most `multiple`, every boundary is
+    a multiple of `multiple` (8 for W4A16 columns, so zero-point words stay whole)."""
+    if parts <= 0 or total < 0 or multiple <= 0:
+        raise ValueError("even_split: bad arguments")
+    if total % multiple:
+        raise ValueError(f"even_split: {total} is not a multiple of {multiple}")
+    units = total // multiple
+    base, extra = divmod(units, parts)
+    out, lo = [], 0
+    for r in range(parts):
+        n = (base + (1 if r < extra else 0)) * multiple
+        out.append((lo, lo + n))
+        lo += n
+    return out
+
+
+def my_rows(rows: int, rank: int, world: int) -> Tuple[int, int]:
+    return even_split(rows, world)[rank]
+
+
+def my_columns(n: int, rank: int, world: int, multiple: int = 8) -> Tuple[int, int]:
+    return even_split(n, world, multiple)[rank]
+
+
+def shard_w8a8_weights(w: torch.Tensor, scale_b: torch.Tensor, rank: int, world: int):
+    """W [K, N], scale_b [N] -> this rank's contiguous column block."""
+    lo, hi = my_columns(w.shape[1], rank, world, 16)
+    return w[:, lo:hi].contiguous(), scale_b[lo:hi].contiguous(), (lo, hi)
+
+
+def shard_w4a16_weights(qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, rank: int, world: int):
+    """qweight [K/8, N], scales [K/g, N], zeros [K/g, N/8] -> this rank's column block (multiple of 8 columns)."""
+    lo, hi = my_columns(qweight.shape[1], rank, world, 8)
+    return (qweight[:, lo:hi].contiguous(), scales[:, lo:hi].contiguous(), zeros[:, lo // 8:hi // 8].contiguous(),
+            (lo, hi))
+
+
+def gather_columns(local: torch.Tensor, n_total: int, group=None) -> torch.Tensor:
+    """All-gather of N-sharded [M, n_r] blocks into [M, n_total] (uneven blocks allowed)."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    ranges = even_split(n_total, world, 8 if n_total % 8 == 0 else 1)
+    if n_total % world == 0 and all(hi - lo == n_total // world for lo, hi in ranges):
+        # equal blocks: one all_gather_into_tensor on a [world, M, n/world] buffer, then a view shuffle
+        m, nr = local.shape
+        buf = torch.empty((world * m, nr), dtype=local.dtype, device=local.device)   # rank blocks stacked on dim 0
+        dist.all_gather_into_tensor(buf, local.contiguous(), group=group)
+        return buf.view(world, m, nr).permute(1, 0, 2).reshape(m, n_total)
+    parts = [torch.empty((local.shape[0], hi - lo), dtype=local.dtype, device=local.device) for lo, hi in ranges]
+    dist.all_gather(parts, local.contiguous(), group=group)
+    assert parts[rank].shape == local.shape
+    return torch.cat(parts, dim=1)
+
+
+def gather_rows(local: torch.Tensor, rows_total: int, group=None) -> torch.Tensor:
+    """All-gather of row-sharded results (only when a consumer wants the whole tensor)."""
+    world = dist.get_world_size(group)
+    ranges = even_split(rows_total, world)
+    parts = [torch.empty((hi - lo,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+             for lo, hi in ranges]
+    dist.all_gather(parts, local.contiguous(), group=group)
+    return torch.cat(parts, dim=0)
