@@ -122,9 +122,9 @@ a = rng.integers(-127, 128, (5, 96), dtype=np.int8); w = rng.integers(-127, 128,
 sa = rng.uniform(1e-3, 1e-2, 5).astype(np.float32); sw = rng.uniform(1e-3, 1e-2, 48).astype(np.float32)
 wl, swl, (c0, c1) = shard.shard_w8a8_weights(torch.from_numpy(w), torch.from_numpy(sw), rank, world)
 out_l = O.matmul_w8a8(a, wl.numpy(), sa, swl.numpy())
-out = shard.gather_columns(torch.from_numpy(out_l.view(np.int16)), 48)
+out = shard.gather_columns(torch.from_numpy(out_l.astype(np.int32)), 48)   # gloo has no 16-bit integer type
 want = O.matmul_w8a8(a, w, sa, sw)
-assert np.array_equal(out.numpy().view(np.uint16), want), "gathered GEMM differs"
+assert np.array_equal(out.numpy().astype(np.uint16), want), "gathered GEMM differs"
 # uneven column blocks (n = 40 over 2 ranks in multiples of 8 -> 24 + 16)
 blocks = shard.even_split(40, 2, 8); mine = blocks[rank]
 loc = torch.arange(40).repeat(3, 1)[:, mine[0]:mine[1]].contiguous()
