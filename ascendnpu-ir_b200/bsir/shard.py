@@ -53,11 +53,12 @@ def shard_w4a16_weights(qweight: torch.Tensor, scales: torch.Tensor, zeros: torc
             (lo, hi))
 
 
-def gather_columns(local: torch.Tensor, n_total: int, group=None) -> torch.Tensor:
-    """All-gather of N-sharded [M, n_r] blocks into [M, n_total] (uneven blocks allowed)."""
+def gather_columns(local: torch.Tensor, n_total: int, group=None, multiple: int = 8) -> torch.Tensor:
+    """All-gather of N-sharded [M, n_r] blocks into [M, n_total] (uneven blocks allowed).  `multiple` must be
+    the one the weights were split with (16 for W8A8, 8 for W4A16)."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
-    ranges = even_split(n_total, world, 8 if n_total % 8 == 0 else 1)
+    ranges = even_split(n_total, world, multiple if n_total % multiple == 0 else 1)
     if n_total % world == 0 and all(hi - lo == n_total // world for lo, hi in ranges):
         # equal blocks: one all_gather_into_tensor on a [world, M, n/world] buffer, then a view shuffle
         m, nr = local.shape

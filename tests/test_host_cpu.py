@@ -122,7 +122,7 @@ a = rng.integers(-127, 128, (5, 96), dtype=np.int8); w = rng.integers(-127, 128,
 sa = rng.uniform(1e-3, 1e-2, 5).astype(np.float32); sw = rng.uniform(1e-3, 1e-2, 48).astype(np.float32)
 wl, swl, (c0, c1) = shard.shard_w8a8_weights(torch.from_numpy(w), torch.from_numpy(sw), rank, world)
 out_l = O.matmul_w8a8(a, wl.numpy(), sa, swl.numpy())
-out = shard.gather_columns(torch.from_numpy(out_l.astype(np.int32)), 48)   # gloo has no 16-bit integer type
+out = shard.gather_columns(torch.from_numpy(out_l.astype(np.int32)), 48, multiple=16)   # gloo has no 16-bit integer type
 want = O.matmul_w8a8(a, w, sa, sw)
 assert np.array_equal(out.numpy().astype(np.uint16), want), "gathered GEMM differs"
 # uneven column blocks (n = 40 over 2 ranks in multiples of 8 -> 24 + 16)
