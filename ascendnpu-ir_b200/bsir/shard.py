@@ -65,17 +65,24 @@ def gather_columns(local: torch.Tensor, n_total: int, group=None, multiple: int 
         buf = torch.empty((world * m, nr), dtype=local.dtype, device=local.device)   # rank blocks stacked on dim 0
         dist.all_gather_into_tensor(buf, local.contiguous(), group=group)
         return buf.view(world, m, nr).permute(1, 0, 2).reshape(m, n_total)
-    parts = [torch.empty((local.shape[0], hi - lo), dtype=local.dtype, device=local.device) for lo, hi in ranges]
-    dist.all_gather(parts, local.contiguous(), group=group)
-    assert parts[rank].shape == local.shape
-    return torch.cat(parts, dim=1)
+    # uneven blocks: collectives want equal sizes, so pad every block to the widest and trim afterwards
+    widest = max(hi - lo for lo, hi in ranges)
+    m = local.shape[0]
+    padded = torch.zeros((m, widest), dtype=local.dtype, device=local.device)
+    padded[:, : local.shape[1]] = local
+    parts = [torch.empty((m, widest), dtype=local.dtype, device=local.device) for _ in ranges]
+    dist.all_gather(parts, padded, group=group)
+    assert ranges[rank][1] - ranges[rank][0] == local.shape[1]
+    return torch.cat([p[:, : hi - lo] for p, (lo, hi) in zip(parts, ranges)], dim=1)
 
 
 def gather_rows(local: torch.Tensor, rows_total: int, group=None) -> torch.Tensor:
     """All-gather of row-sharded results (only when a consumer wants the whole tensor)."""
     world = dist.get_world_size(group)
     ranges = even_split(rows_total, world)
-    parts = [torch.empty((hi - lo,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
-             for lo, hi in ranges]
-    dist.all_gather(parts, local.contiguous(), group=group)
-    return torch.cat(parts, dim=0)
+    tallest = max(hi - lo for lo, hi in ranges)
+    padded = torch.zeros((tallest,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    padded[: local.shape[0]] = local
+    parts = [torch.empty_like(padded) for _ in ranges]
+    dist.all_gather(parts, padded, group=group)
+    return torch.cat([p[: hi - lo] for p, (lo, hi) in zip(parts, ranges)], dim=0)
