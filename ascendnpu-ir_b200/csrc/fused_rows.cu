@@ -418,6 +418,166 @@ __global__ void __launch_bounds__(VPT * (DT == BSIR_F32 ? 4 : 8) > 32 ? 256 : 10
   }
 }
 
+// ------------------------------------------------------------------ softmax, long rows
+// Rows of 32-64 KB leave room for one CTA per SM only, so in the kernel above every thread of the SM
+// is in the same phase and HBM idles while the row is reduced.  Here the CTA is persistent and the
+// rows stream through shared memory: one thread issues a bulk copy (cp.async.bulk, completion on an
+// mbarrier) of the row after next while the 1024 threads work on the current one, so two rows per SM
+// are always in flight.  The arithmetic is the same as above.
+constexpr int kStreamBufs = 3;
+constexpr uint32_t kErrRowWait = 0x20;
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// bounded: gives up after about two seconds and raises the device error word
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, int *err) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t spin = 0;; ++spin) {
+    if (mbar_try(bar, parity)) return true;
+    if ((spin & 1023u) == 1023u && clock64() - t0 > 4000000000LL) {
+      if (err) atomicOr(err, static_cast<int>(kErrRowWait));
+      return false;
+    }
+  }
+}
+
+template <int DT, int VPT>
+__global__ void __launch_bounds__(1024, 1) softmax_stream_kernel(RowGeom g, const void *__restrict__ xp, int64_t x_stride,
+                                                                  void *__restrict__ yp, int64_t y_stride, int *err) {
+  constexpr int kPerWord = FloatTraits<DT>::kPerWord;
+  constexpr int kPerVec = 4 * kPerWord;
+  constexpr int kPairs = VPT * kPerVec / 2;
+  extern __shared__ __align__(128) uint8_t row_smem[];
+  __shared__ float red_max[32];
+  __shared__ float red_sum[32];
+  __shared__ __align__(8) unsigned long long bars[kStreamBufs];
+  using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
+  const int t = threadIdx.x;
+  const uint32_t row_bytes = static_cast<uint32_t>(g.nvec) * 16u;
+  const float ninf = __int_as_float(0xff800000);
+  constexpr uint32_t kPad = DT == BSIR_F32 ? 0xff800000u : DT == BSIR_BF16 ? 0xff80ff80u : 0xfc00fc00u;
+  const int64_t my_rows = (g.rows - blockIdx.x + gridDim.x - 1) / gridDim.x;   // rows blockIdx.x, + gridDim.x, ...
+
+  auto issue = [&](int64_t k) {   // bulk copy of this CTA's k-th row into buffer k % kStreamBufs
+    const int b = static_cast<int>(k % kStreamBufs);
+    const E *src = static_cast<const E *>(xp) + (blockIdx.x + k * gridDim.x) * x_stride;
+    const uint32_t bar = smem_addr(&bars[b]);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_addr(row_smem) + static_cast<uint32_t>(b) * row_bytes),
+                 "l"(src), "r"(row_bytes), "r"(bar)
+                 : "memory");
+  };
+
+  if (t == 0) {
+    for (int b = 0; b < kStreamBufs; ++b)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_addr(&bars[b])) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (t == 0)
+    for (int64_t k = 0; k < kStreamBufs - 1 && k < my_rows; ++k) issue(k);
+
+  bool ok = true;
+  for (int64_t k = 0; k < my_rows; ++k) {
+    const int b = static_cast<int>(k % kStreamBufs);
+    const uint32_t parity = static_cast<uint32_t>((k / kStreamBufs) & 1);
+    if (ok && !mbar_wait_bounded(smem_addr(&bars[b]), parity, err)) ok = false;
+    const Vec16 *buf = reinterpret_cast<const Vec16 *>(row_smem + static_cast<size_t>(b) * row_bytes);
+    Vec16 v[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t vi = t + static_cast<int64_t>(i) * 1024;
+      v[i] = (ok && vi < g.nvec) ? buf[vi] : Vec16{{kPad, kPad, kPad, kPad}};
+    }
+    float m = ninf;
+    if constexpr (kPerWord == 2) {
+      uint32_t m2 = kPad;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          if constexpr (DT == BSIR_BF16) asm("max.bf16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
+          else asm("max.f16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
+        }
+      float e2[2];
+      FloatTraits<DT>::unpack(m2, e2);
+      m = fmaxf(e2[0], e2[1]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, __uint_as_float(v[i].w[w]));
+    }
+    m = row_reduce(m, 1024, red_max, ninf, 0, warp_red_maxnum);
+    // every thread has its part of buffer b in registers (the barrier inside row_reduce is behind us),
+    // and buffer (k + 2) % 3 was released one row ago: start the copy of the row after next
+    if (t == 0 && k + kStreamBufs - 1 < my_rows) issue(k + kStreamBufs - 1);
+
+    const float kLog2e = 1.4426950408889634f;
+    const unsigned long long l2e2 = pack2(kLog2e, kLog2e);
+    const float nm = -m * kLog2e;
+    const unsigned long long nm2 = pack2(nm, nm);
+    unsigned long long e[kPairs];
+    unsigned long long s2 = pack2(0.0f, 0.0f);
+#pragma unroll
+    for (int pi = 0; pi < kPairs; ++pi) {
+      float x0, x1;
+      if constexpr (kPerWord == 2) {
+        float xe[2];
+        FloatTraits<DT>::unpack(v[pi / 4].w[pi % 4], xe);
+        x0 = xe[0];
+        x1 = xe[1];
+      } else {
+        x0 = __uint_as_float(v[pi / 2].w[(pi % 2) * 2]);
+        x1 = __uint_as_float(v[pi / 2].w[(pi % 2) * 2 + 1]);
+      }
+      float d0, d1;
+      unpack2(fma2(pack2(x0, x1), l2e2, nm2), d0, d1);
+      e[pi] = pack2(ex2_approx(d0), ex2_approx(d1));
+      s2 = add2(s2, e[pi]);
+    }
+    float s0, s1;
+    unpack2(s2, s0, s1);
+    const float s = row_reduce(s0 + s1, 1024, red_sum, 0.0f, 0, warp_red_sum);
+    const float rcp = __frcp_rn(s);
+    const unsigned long long rcp2 = pack2(rcp, rcp), ns2 = pack2(-s, -s);
+    E *yrow = static_cast<E *>(yp) + (blockIdx.x + k * gridDim.x) * y_stride;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t vi = t + static_cast<int64_t>(i) * 1024;
+      if (vi >= g.nvec || !ok) continue;
+      Vec16 o;
+      if constexpr (kPerWord == 2) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          float y0, y1;
+          unpack2(mul2(e[i * 4 + w], rcp2), y0, y1);
+          const float yy[2] = {y0, y1};
+          o.w[w] = FloatTraits<DT>::pack(yy);
+        }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const unsigned long long ev = e[i * 2 + h];
+          const unsigned long long q0 = mul2(ev, rcp2);
+          float y0, y1;
+          unpack2(fma2(fma2(q0, ns2, ev), rcp2, q0), y0, y1);
+          o.w[2 * h] = __float_as_uint(y0);
+          o.w[2 * h + 1] = __float_as_uint(y1);
+        }
+      }
+      st_stream(reinterpret_cast<Vec16 *>(yrow) + vi, o);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ multi-pass fallbacks
 // One CTA per row, any cols / stride / alignment; the row is re-read from L2 on each pass.
 template <int DT>
@@ -640,6 +800,20 @@ int32_t bsir_softmax(int32_t dtype, int64_t rows, int64_t cols, const void *x, i
   const int max_vpt = eb == 4 ? 8 : 4;
   const bool vec_ok = rows_vector_ok(x, x_row_stride, eb) && rows_vector_ok(y, y_row_stride, eb) &&
                       pick_geometry(rows, cols, eb, max_vpt, 4, env_int("BSIR_SOFTMAX_TPR", 0), &g, &vpt);
+  // long rows: persistent CTAs with the rows streamed through shared memory by bulk copies
+  const bool want_stream = env_int("BSIR_SOFTMAX_STREAM", 1) != 0;
+  if (vec_ok && want_stream && g.tpr == 1024 && g.nvec >= 2048 && g.nvec * 16 <= 65536 && device_info().cc_major >= 9) {
+    const size_t smem = static_cast<size_t>(kStreamBufs) * static_cast<size_t>(g.nvec) * 16u;
+    int grid = device_info().sm_count > 0 ? device_info().sm_count : 148;
+    if (grid > rows) grid = static_cast<int>(rows);
+    int *err = device_error_word();
+    DISPATCH_FLOAT_DT(dtype, DISPATCH_VPT_LE8(vpt, {
+      cudaFuncSetAttribute(softmax_stream_kernel<D, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      softmax_stream_kernel<D, V><<<grid, 1024, smem, st>>>(g, x, x_row_stride, y, y_row_stride, err);
+    }));
+    count_launch();
+    return check_launch("softmax");
+  }
   if (vec_ok) {
     const unsigned blocks = static_cast<unsigned>(ceil_div(rows, g.rpc));
     const unsigned threads = static_cast<unsigned>(g.tpr * g.rpc);

@@ -18,7 +18,10 @@
 // are taken as they come and A's 8-element pieces are permuted to match with two byte permutes.
 // M up to 16 is one MMA row block; larger M runs the kernel once per 16 rows (decode path; large M
 // belongs on a dense GEMM).
-#include "common.cuh"
+#include <cstdlib>
+#include <mutex>
+
+#include "tc_ptx.cuh"
 
 namespace bsir {
 namespace {
@@ -198,6 +201,289 @@ __global__ void __launch_bounds__(kWarps * 32, 2) w4a16_mma_kernel(W4Params p, i
   }
 }
 
+// ------------------------------------------------------------------ tensor-memory path (tcgen05)
+// out^T[n, m] = W^T[n, k] . a^T[k, m]: the 128 output columns of a CTA are the 128 lanes of tensor
+// memory, the (at most 16) rows of `a` are the MMA's N.  Roles in a CTA of 320 threads:
+//   warp 8      TMA producer: boxes of packed weights [32 word rows x 128 columns] (16 KB) into a ring;
+//   warp 9      MMA issuer: tcgen05.mma.kind::f16, A operand read from tensor memory, B = activations
+//               in shared memory, f32 accumulator in tensor memory;
+//   warps 0-7   dequantisers: thread = one output column.  Each reads its column's words from the
+//               stage, turns every word into four bf16 pairs (k_i, k_i+4) and stores them into its own
+//               TMEM lane (tcgen05.st); warps w and w + 4 share a lane quadrant and alternate 64-k chunks.
+// The activations are staged once per CTA in shared memory in the tensor core's K-major 128-byte
+// swizzled layout, with each group of 8 k permuted to (0,4,1,5,2,6,3,7) so that it matches the pair
+// order the nibble trick produces.  All waits are bounded.
+constexpr int kTcCols = 128;            // output columns per CTA
+constexpr int kTcStageRows = 32;        // word rows per weight stage (= 256 k)
+constexpr int kTcStageBytes = kTcStageRows * kTcCols * 4;
+constexpr int kTcStages = 4;
+constexpr int kTcABufs = 8;             // 64-k chunks of dequantised weights in TMEM (12 x 32 columns)
+constexpr int kTcDqWarps = 16;          // dequantising warps: 4 lane quadrants x 4 chunks of a stage
+constexpr int kTcMmaWarps = 4;          // MMA-issuing warps (one thread each); chunk c belongs to issuer c % 4
+constexpr int kTcThreads = (kTcDqWarps + 1 + kTcMmaWarps) * 32;
+constexpr int kTcMaxK = 4096;
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+    w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, W4Params p, int64_t m0, int *err, long long *dbg) {
+  const long long T0 = clock64();
+#define DBG(i) if (dbg && blockIdx.x == 3 && lane == 0 && (warp == 0 || warp == kTcDqWarps + 1 || warp == kTcDqWarps)) dbg[warp * 16 + (i)] = clock64() - T0;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gen = smem_raw + (base - raw);
+  const int nchunks = static_cast<int>(p.k / 64);
+  const uint32_t act_bytes = static_cast<uint32_t>(nchunks) * 2048u;   // 16 rows x 128 B per 64-k chunk
+  const uint32_t stage0 = base + act_bytes;
+  // per-group scales [ngroups][128] bf16 and zero points [ngroups][16] words of this CTA's columns
+  const int ngroups = static_cast<int>(p.k / p.group);
+  const uint32_t sc_off = act_bytes + kTcStages * kTcStageBytes;
+  const uint32_t zp_off = sc_off + static_cast<uint32_t>(ngroups) * kTcCols * 2u;
+  const uint32_t bar_off = (zp_off + static_cast<uint32_t>(ngroups) * 16u * 4u + 15u) & ~15u;
+  const uint32_t bars = base + bar_off;
+  auto wfull = [&](int s) { return bars + 8u * s; };
+  auto wempty = [&](int s) { return bars + 8u * (kTcStages + s); };
+  auto afull = [&](int b) { return bars + 8u * (2 * kTcStages + b); };
+  auto aempty = [&](int b) { return bars + 8u * (2 * kTcStages + kTcABufs + b); };
+  const uint32_t dfull = bars + 8u * (2 * kTcStages + 2 * kTcABufs);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + bar_off + 8 * (2 * kTcStages + 2 * kTcABufs + 1));
+  uint16_t *sm_scales = reinterpret_cast<uint16_t *>(gen + sc_off);
+  uint32_t *sm_zeros = reinterpret_cast<uint32_t *>(gen + zp_off);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.x) * kTcCols;
+  const int nstages_total = (nchunks + 3) / 4;   // stages of 4 chunks
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTcStages; ++s) { mbar_init(wfull(s), 1); mbar_init(wempty(s), kTcDqWarps); }
+    for (int b = 0; b < kTcABufs; ++b) { mbar_init(afull(b), 4); mbar_init(aempty(b), 1); }
+    mbar_init(dfull, kTcMmaWarps);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tmap_w);
+  }
+  if (warp == kTcDqWarps + 1) tmem_alloc(smem_u32(tmem_slot), 512);
+  tc_fence_before();
+  __syncthreads();   // barriers and the TMEM address are visible; the weight stream can start now
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // One f32 accumulator (16 columns) per issuing warp; the epilogue adds them.  A tcgen05.mma costs its
+  // issuing thread ~70 cycles and a commit ~130 whatever the MMA's size, and these MMAs are tiny
+  // (128 x 16 x 16), so a single issuer would be the bottleneck: four warps issue side by side.
+  const uint32_t tmem_d = tmem_base;            // columns 0..63
+  const uint32_t tmem_a0 = tmem_base + 64;      // kTcABufs x 32 columns of packed bf16 pairs
+
+  // stage the activations (rows m0 .. m0+15, zero beyond m): 16-byte pieces of 8 k, permuted and swizzled
+  if (warp != kTcDqWarps) {   // the producer warp does not wait for this: weights stream in meanwhile
+    const int64_t rows_left = p.m - m0;
+    const int pieces = nchunks * 8 * 16;   // (chunk, 16-B piece, row)
+    const int tix = warp < kTcDqWarps ? static_cast<int>(threadIdx.x) : static_cast<int>(threadIdx.x) - 32;
+    constexpr int kStep = kTcThreads - 32;
+    constexpr int kBatch = 16;
+    DBG(10)
+    for (int i0 = tix; i0 < pieces; i0 += kStep * kBatch) {
+      uint4 v[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {   // all loads of the batch first
+        const int i = i0 + u * kStep;
+        const int piece = i & 7, row = (i >> 3) & 15, chunk = i >> 7;   // 8 threads read one 128-byte run
+        v[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (i < pieces && row < rows_left) v[u] = *reinterpret_cast<const uint4 *>(p.a + (m0 + row) * p.lda + chunk * 64 + piece * 8);
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int i = i0 + u * kStep;
+        if (i >= pieces) break;
+        const int piece = i & 7, row = (i >> 3) & 15, chunk = i >> 7;
+        uint4 o;
+        o.x = __byte_perm(v[u].x, v[u].z, 0x5410);  // (e0, e4)
+        o.y = __byte_perm(v[u].x, v[u].z, 0x7632);  // (e1, e5)
+        o.z = __byte_perm(v[u].y, v[u].w, 0x5410);  // (e2, e6)
+        o.w = __byte_perm(v[u].y, v[u].w, 0x7632);  // (e3, e7)
+        const uint32_t off = static_cast<uint32_t>(chunk) * 2048u + static_cast<uint32_t>(row) * 128u +
+                             static_cast<uint32_t>((piece ^ (row & 7)) * 16);
+        *reinterpret_cast<uint4 *>(gen + off) = o;
+      }
+    }
+    DBG(11)
+    // scales and zero points of all groups, as 16-byte vectors with every load issued before the first
+    // store: one exposed memory latency here instead of one per group in the main loop
+    {
+      const int nvec = ngroups * (kTcCols / 8);                 // 8 bf16 per vector
+      uint4 sv[2];
+      uint32_t zv[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int i = tix + u * kStep;
+        const int gi = i / (kTcCols / 8), c8 = i % (kTcCols / 8);
+        sv[u] = make_uint4(0u, 0u, 0u, 0u);
+        zv[u] = 0u;
+        if (i < nvec && n0 + 8 * c8 < p.n) {
+          sv[u] = *reinterpret_cast<const uint4 *>(p.scales + static_cast<int64_t>(gi) * p.n + n0 + 8 * c8);
+          zv[u] = p.zeros[static_cast<int64_t>(gi) * (p.n / 8) + n0 / 8 + c8];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int i = tix + u * kStep;
+        if (i < nvec) {
+          reinterpret_cast<uint4 *>(sm_scales)[i] = sv[u];
+          sm_zeros[i] = zv[u];
+        }
+      }
+      for (int i = tix + 2 * kStep; i < nvec; i += kStep) {    // only when there are more than 64 groups' worth
+        const int gi = i / (kTcCols / 8), c8 = i % (kTcCols / 8);
+        const bool in = n0 + 8 * c8 < p.n;
+        reinterpret_cast<uint4 *>(sm_scales)[i] = in ? *reinterpret_cast<const uint4 *>(p.scales + static_cast<int64_t>(gi) * p.n + n0 + 8 * c8) : make_uint4(0u, 0u, 0u, 0u);
+        sm_zeros[i] = in ? p.zeros[static_cast<int64_t>(gi) * (p.n / 8) + n0 / 8 + c8] : 0u;
+      }
+    }
+    DBG(12)
+    fence_proxy_async();
+    DBG(13)
+    asm volatile("bar.sync 1, %0;" ::"n"(kTcThreads - 32) : "memory");   // all but the producer warp
+  }
+
+  DBG(0)
+  if (warp == kTcDqWarps) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int s = 0; s < nstages_total; ++s) {
+        if (!mbar_wait(wempty(stage), phase ^ 1u, abort_flag, err)) { ok = false; break; }
+        mbar_expect_tx(wfull(stage), kTcStageBytes);
+        tma_load_2d(stage0 + stage * kTcStageBytes, &tmap_w, static_cast<int>(n0), s * kTcStageRows, wfull(stage));
+        if (++stage == kTcStages) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok)
+        for (int s = 0; s < kTcStages; ++s)
+          for (int i = 0; i < 200000; ++i)
+            if (mbar_try_wait(wfull(s), 0) || mbar_try_wait(wfull(s), 1)) break;
+    }
+  } else if (warp > kTcDqWarps) {
+    if (lane == 0) {
+      // D = f32, A = B = bf16, both K-major, N = 16, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(16 >> 3) << 17) |
+                             (static_cast<uint32_t>(128 >> 4) << 24);
+      const int issuer = warp - kTcDqWarps - 1;
+      uint32_t aphase = 0u;   // one parity bit per buffer
+      bool ok = true;
+      for (int c = issuer; c < nchunks && ok; c += kTcMmaWarps) {
+        const int b = c % kTcABufs;
+        if (!mbar_wait(afull(b), (aphase >> b) & 1u, abort_flag, err)) { ok = false; break; }
+        aphase ^= 1u << b;
+        tc_fence_after();
+        const uint32_t act = base + static_cast<uint32_t>(c) * 2048u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)   // 4 x K=16 per 64-k chunk; 8 TMEM columns and 32 bytes of smem each
+          mma_f16_ts(tmem_d + static_cast<uint32_t>(issuer * 16), tmem_a0 + static_cast<uint32_t>(b * 32 + j * 8),
+                     make_desc(act + j * 32, 16, 1024), idesc, (c >= kTcMmaWarps || j > 0) ? 1u : 0u);
+        tc_commit(aempty(b));
+      }
+      tc_commit(dfull);   // arrives once this issuer's MMAs are done (immediately if it had none)
+    }
+  } else {
+    // ---------------- dequantisers
+    const int quad = warp & 3, sub = warp >> 2;       // sub: which chunk of every stage this warp owns
+    const int tid_n = quad * 32 + lane;                 // TMEM lane = column within the tile
+    const int64_t n = n0 + tid_n;
+    const bool n_ok = n < p.n;
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
+    int stage = 0;
+    uint32_t phase = 0;
+    uint32_t ephase = 0u;   // one parity bit per buffer
+    const int chunks_per_group = static_cast<int>(p.group / 64);
+    bool ok = true;
+    int cur_group = -1;
+    uint32_t zz = 0x43004300u, ss = 0u;
+    for (int s = 0; s < nstages_total && ok; ++s) {
+      if (!mbar_wait(wfull(stage), phase, abort_flag, err)) { ok = false; break; }
+      if (s == 0) { DBG(1) } if (s == 1) { DBG(4) } if (s == 8) { DBG(5) }
+      const uint32_t *st = reinterpret_cast<const uint32_t *>(gen + act_bytes + stage * kTcStageBytes);
+      {
+        const int cs = sub;                             // chunk of the stage this warp owns
+        const int c = s * 4 + cs;                       // global chunk
+        if (c < nchunks) {
+        const int b = c % kTcABufs;
+        const int grp = c / chunks_per_group;
+        if (grp != cur_group) {
+          cur_group = grp;
+          const uint32_t sv = sm_scales[grp * kTcCols + tid_n];
+          const uint32_t z = (sm_zeros[grp * 16 + (tid_n >> 3)] >> (4 * (tid_n & 7))) & 0xfu;
+          ss = sv | (sv << 16);
+          zz = (0x4300u | z) * 0x00010001u;
+        }
+        uint32_t words[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) words[r] = st[(cs * 8 + r) * kTcCols + tid_n];
+        if (c == 0) { DBG(9) }
+        // the buffer must have been drained by the MMAs that read it kTcABufs chunks ago
+        if (c >= kTcABufs) {
+          if (!mbar_wait(aempty(b), (ephase >> b) & 1u, abort_flag, err)) { ok = false; }
+          ephase ^= 1u << b;
+          tc_fence_after();
+        }
+        uint32_t qv[32];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t v = ((words[r] >> (4 * q)) & 0x000f000fu) | 0x43004300u;
+            qv[r * 4 + q] = bf16x2_mul(bf16x2_sub(v, zz), ss);
+          }
+        }
+        if (c == 0) { DBG(8) }
+        tmem_st32(tmem_a0 + lane_addr + static_cast<uint32_t>(b * 32), qv);
+        if (c == 0) { DBG(2) }
+        tmem_st_wait();
+        if (c == 0) { DBG(3) }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(afull(b));
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(wempty(stage));
+      if (++stage == kTcStages) { stage = 0; phase ^= 1u; }
+    }
+    DBG(6)
+    // ---------------- epilogue: the four warps of half 0 read the accumulator
+    if (sub == 0 && ok) {
+      if (mbar_wait(dfull, 0, abort_flag, err)) {
+        tc_fence_after();
+        DBG(7)
+        float accs[16];
+#pragma unroll
+        for (int mm = 0; mm < 16; ++mm) accs[mm] = 0.0f;
+        const int nacc = nchunks < kTcMmaWarps ? nchunks : kTcMmaWarps;   // issuers that had a chunk
+        for (int a8 = 0; a8 < nacc; ++a8) {
+          uint32_t t16[16];
+          tmem_ld16(tmem_d + lane_addr + static_cast<uint32_t>(a8 * 16), t16);
+          tmem_ld_wait();
+#pragma unroll
+          for (int mm = 0; mm < 16; ++mm) accs[mm] += __uint_as_float(t16[mm]);
+        }
+        uint32_t r[16];
+#pragma unroll
+        for (int mm = 0; mm < 16; ++mm) r[mm] = __float_as_uint(accs[mm]);
+        const int64_t rows_left = p.m - m0;
+        if (n_ok) {
+#pragma unroll
+          for (int mm = 0; mm < 16; ++mm)
+            if (mm < rows_left) p.out[(m0 + mm) * p.ldo + n] = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[mm])));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kTcDqWarps + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // Plain path: any alignment; one thread per output column, one row block of up to 4 rows.
 __global__ void __launch_bounds__(128) w4a16_plain_kernel(W4Params p, int64_t m0) {
   const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -215,6 +501,44 @@ __global__ void __launch_bounds__(128) w4a16_plain_kernel(W4Params p, int64_t m0
     acc = __fmaf_rn(av, wv, acc);
   }
   p.out[row * p.ldo + c] = __bfloat16_as_ushort(__float2bfloat16_rn(acc));
+}
+
+// ------------------------------------------------------------------ host helpers for the tcgen05 path
+using EncodeFnW4 = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFnW4 encode_fn_w4() {
+  static EncodeFnW4 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFnW4>(sym);
+    else
+      cudaGetLastError();
+  });
+  return fn;
+}
+
+// qweight as a 2-D int32 tensor [k/8 rows, n columns]; box = [32 rows x 128 columns], no swizzle.
+bool make_weight_tmap(CUtensorMap *map, const uint32_t *qw, int64_t n, int64_t k) {
+  EncodeFnW4 enc = encode_fn_w4();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(k / 8)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(n) * 4u};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kTcCols), static_cast<cuuint32_t>(kTcStageRows)};
+  cuuint32_t estr[2] = {1u, 1u};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<uint32_t *>(qw), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+size_t tc_smem_bytes(int64_t k, int64_t group) {
+  const size_t ngroups = static_cast<size_t>(k / group);
+  return static_cast<size_t>(k / 64) * 2048u + static_cast<size_t>(kTcStages) * kTcStageBytes + ngroups * kTcCols * 2u +
+         ngroups * 64u + 1024u + 512u;
 }
 
 }  // namespace
@@ -239,7 +563,25 @@ extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t gr
   W4Params p{m, n, k, group, static_cast<const uint16_t *>(a), lda, reinterpret_cast<const uint32_t *>(qweight),
              static_cast<const uint16_t *>(scales), reinterpret_cast<const uint32_t *>(zeros),
              static_cast<uint16_t *>(out), ldo};
-  const bool fast = k > 0 && aligned_to(a, 16) && lda % 8 == 0 && aligned_to(qweight, 16) && aligned_to(scales, 8);
+  const bool fast = k > 0 && aligned_to(a, 16) && lda % 8 == 0 && aligned_to(qweight, 16) && aligned_to(scales, 16);
+  // tensor-memory path: needs sm_100, k <= 4096 (activations resident in shared memory), groups that are
+  // whole 64-k chunks and a weight pitch TMA can address
+  const char *force = std::getenv("BSIR_W4A16_PATH");
+  const bool want_tc = !(force && force[0] == 'm');
+  if (fast && want_tc && device_info().cc_major >= 10 && k <= kTcMaxK && group % 64 == 0 && k % 64 == 0) {
+    CUtensorMap tw;
+    if (make_weight_tmap(&tw, p.qw, n, k)) {
+      const size_t smem = tc_smem_bytes(k, group);
+      cudaFuncSetAttribute(w4a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      const unsigned blocks = static_cast<unsigned>(ceil_div(n, kTcCols));
+      int *err = device_error_word();
+      for (int64_t m0 = 0; m0 < m; m0 += 16) {
+        w4a16_tc_kernel<<<blocks, kTcThreads, smem, st>>>(tw, p, m0, err, reinterpret_cast<long long *>(std::getenv("BSIR_DBG_PTR") ? std::strtoull(std::getenv("BSIR_DBG_PTR"), nullptr, 10) : 0ull));
+        count_launch();
+      }
+      return check_launch("matmul_w4a16");
+    }
+  }
   if (fast) {
     const unsigned blocks = static_cast<unsigned>(ceil_div(n, kColsPerCta));
     for (int64_t m0 = 0; m0 < m; m0 += 16) {

@@ -23,11 +23,10 @@
 //
 // Shapes the TMA path cannot address (row pitches that are not multiples of 16 bytes, unaligned
 // bases) run on a plain CUDA-core kernel instead.
-#include <cuda.h>
-
+#include <cstdlib>
 #include <mutex>
 
-#include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace bsir {
 namespace {
@@ -36,7 +35,6 @@ constexpr int kBM = 128;        // rows of A per tile = TMEM lanes
 constexpr int kBK = 128;        // K bytes per stage (one 128-byte swizzle row)
 constexpr int kUmmaK = 32;      // K per tcgen05.mma for 8-bit operands
 constexpr int kThreads = 192;
-constexpr uint32_t kErrGemmWait = 0x10;
 
 struct GemmParams {
   int64_t m, n, k;
@@ -49,104 +47,8 @@ struct GemmParams {
   int64_t ldacc;
   int *err;
   int m_tiles, n_tiles, k_blocks;
+  long long *dbg;
 };
-
-// ------------------------------------------------------------------ PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false when it gave up or another role raised the abort flag.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *err) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (uint32_t spin = 0;; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 255u) == 255u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > 4000000000LL) {  // about two seconds
-        *abort_flag = 1;
-        if (err) atomicOr(err, static_cast<int>(kErrGemmWait));
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
-  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle, version 1 (sm_100).
-//   K-major operand  (rows of 128 K-bytes):        SBO = 1024 (8 rows), LBO unused
-//   MN-major operand (rows of 128 N-bytes per k):  SBO = 1024 (8 k rows), LBO = pitch between 128-wide N chunks
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr >> 4) & 0x3fffu);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
-  d |= 1ull << 46;  // descriptor version
-  d |= 2ull << 61;  // SWIZZLE_128B
-  return d;
-}
 
 template <int BN>
 struct TileCfg {
@@ -240,12 +142,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       int acc = 0;
       uint32_t acc_phase[2] = {0u, 0u};
       bool ok = true;
+      long long t_full = 0, t_issue = 0, t_tempty = 0, t_all = clock64();
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        long long c0 = clock64();
         if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err)) { ok = false; break; }
+        t_tempty += clock64() - c0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
+          long long c1 = clock64();
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.err)) { ok = false; break; }
+          long long c2 = clock64();
+          t_full += c2 - c1;
           tc_fence_after();
           const uint32_t sa = base + stage * Cfg::kStage;
           const uint32_t sb = sa + Cfg::kStageA;
@@ -257,6 +165,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             mma_i8(d_tmem, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
           }
           tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          t_issue += clock64() - c2;
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
@@ -264,6 +173,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         acc_phase[acc] ^= 1u;
         acc ^= 1;
       }
+      if (p.dbg && blockIdx.x == 5) { p.dbg[0] = t_full; p.dbg[1] = t_issue; p.dbg[2] = t_tempty; p.dbg[3] = clock64() - t_all; }
     }
   } else {
     // ---------------- epilogue: warps 2..5, TMEM lane quadrant = warp % 4
@@ -465,6 +375,7 @@ extern "C" int32_t bsir_matmul_w8a8(int64_t m, int64_t n, int64_t k, const int8_
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype;
   p.acc_out = acc_out; p.ldacc = n;
   p.err = device_error_word();
+  p.dbg = reinterpret_cast<long long *>(std::getenv("BSIR_DBG_PTR") ? std::strtoull(std::getenv("BSIR_DBG_PTR"), nullptr, 10) : 0ull);
   p.m_tiles = static_cast<int>(ceil_div(m, kBM));
   p.k_blocks = static_cast<int>(ceil_div(k, kBK));
 

@@ -312,7 +312,6 @@ __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__res
   using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
   __shared__ float redf[8];
   __shared__ int redi[8];
-  __shared__ int is_last;
   const int seg = blockIdx.x;
   const int64_t row = blockIdx.y;
   const E *xrow = static_cast<const E *>(src) + row * p.row_stride;
@@ -361,11 +360,53 @@ __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__res
     }
   }
   const float tm = m;  // this thread's own extreme
-  m = cta_reduce_f(m, redf, [](float a, float b) { return ext_nan<IS_MAX>(a, b); });
-
+  // Common case (no NaN in the segment), one barrier: each warp agrees on its extreme by shuffles, only
+  // the lanes that hold it search their registers for its first (last) position, and the eight warp
+  // results meet in shared memory.
+  __shared__ float warp_val[8];
+  __shared__ int warp_idx[8];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  float wm = tm;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) wm = ext_nan<IS_MAX>(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+  int best = p.tie_left ? INT_MAX : -1;
+  if (wm == wm && tm == wm) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
+      if (vi < v1) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          float e[kPerWord];
+          FloatTraits<DT>::unpack(v[i].w[w], e);
+#pragma unroll
+          for (int k = 0; k < kPerWord; ++k) {
+            const int gi = static_cast<int>(vi * kPerVec + w * kPerWord + k);
+            if (e[k] == wm) best = p.tie_left ? min(best, gi) : max(best, gi);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const int other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = p.tie_left ? min(best, other) : max(best, other);
+  }
+  if (lane == 0) { warp_val[wid] = wm; warp_idx[wid] = best; }
+  __syncthreads();
+  m = warp_val[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) m = ext_nan<IS_MAX>(m, warp_val[k]);
   int nanpos = INT_MAX;
-  if (m != m) {
-    // rare: the segment holds a NaN.  Find the first one, then redo the extreme on the prefix before it.
+  if (m == m) {
+    best = p.tie_left ? INT_MAX : -1;
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (warp_val[k] == m) best = p.tie_left ? min(best, warp_idx[k]) : max(best, warp_idx[k]);
+  } else {
+    // rare: the segment holds a NaN.  Find the first one, redo the extreme on the prefix before it,
+    // then look for that extreme's position inside the prefix (whole-CTA reductions, several barriers).
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
@@ -397,12 +438,7 @@ __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__res
       }
     }
     m = cta_reduce_f(m, redf, [](float a, float b) { return ext_nan<IS_MAX>(a, b); });
-  }
-  // pass 2: first (or last) index holding the extreme, among elements before nanpos
-  // Only threads whose own extreme equals the segment's can hold it (all threads rescan in the rare
-  // NaN case, where the extreme was recomputed over a prefix).
-  int best = p.tie_left ? INT_MAX : -1;
-  if (nanpos != INT_MAX || tm == m) {
+    best = p.tie_left ? INT_MAX : -1;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
@@ -419,9 +455,9 @@ __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__res
         }
       }
     }
+    if (p.tie_left) best = cta_reduce_i(best, redi, [](int a, int b) { return min(a, b); });
+    else best = cta_reduce_i(best, redi, [](int a, int b) { return max(a, b); });
   }
-  if (p.tie_left) best = cta_reduce_i(best, redi, [](int a, int b) { return min(a, b); });
-  else best = cta_reduce_i(best, redi, [](int a, int b) { return max(a, b); });
   // a segment whose prefix is empty or all at the identity reports "nothing better than the start"
   if (best == INT_MAX || best < 0) best = -1;
 
@@ -439,14 +475,11 @@ __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__res
   }
 
   Partial *mine = partials + row * p.nseg;
-  if (threadIdx.x == 0) {
-    mine[seg] = Partial{m, best, nanpos, 0};
-    __threadfence();
-    const unsigned done = atomicAdd(&counters[row], 1u);
-    is_last = (done == static_cast<unsigned>(p.nseg - 1));
-  }
-  __syncthreads();
-  if (!is_last || threadIdx.x != 0) return;
+  if (threadIdx.x != 0) return;
+  mine[seg] = Partial{m, best, nanpos, 0};
+  __threadfence();
+  const unsigned done = atomicAdd(&counters[row], 1u);
+  if (done != static_cast<unsigned>(p.nseg - 1)) return;   // not the last segment of this row to finish
   __threadfence();
   float val = ident;
   int idx = 0;
