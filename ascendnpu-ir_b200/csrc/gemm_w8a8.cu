@@ -256,6 +256,237 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+// ------------------------------------------------------------------ CTA-pair kernel (cta_group::2)
+// Two CTAs of a cluster share one 256 x 256 tile: CTA r owns rows [128 r, 128 r + 128) of A and the
+// accumulator rows that go with them, and loads only columns [128 r, 128 r + 128) of the B tile; the
+// tensor cores of both SMs read both halves of B.  Per SM that is 32 KB of shared-memory fill per
+// 128-deep K block instead of 48 KB, and half as many MMA instructions per flop for the issuing
+// thread -- the two things that bound the single-CTA kernel.  Only the leader (cluster rank 0)
+// issues MMAs; both CTAs' TMA loads complete on the leader's barrier; tcgen05.commit multicasts the
+// "stage free" and "accumulator ready" arrivals to both CTAs (no TMA load is multicast).
+constexpr int kPairStages = 6;
+constexpr int kPairStageA = kBM * kBK;          // 16 KB: this CTA's 128 rows of A
+constexpr int kPairStageB = 128 * kBK;          // 16 KB: this CTA's 128 columns of B
+constexpr int kPairStage = kPairStageA + kPairStageB;
+constexpr int kPairSmem = kPairStages * kPairStage + 1024 + 256;
+constexpr int kPairBN = 256;
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(leader_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {   // arrives on `bar` in both CTAs of the pair
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(static_cast<uint16_t>(3))
+               : "memory");
+}
+__device__ __forceinline__ void mma_i8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+template <bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gen_base = smem_raw + (base - raw);
+  const uint32_t bars = base + kPairStages * kPairStage;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (kPairStages + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * kPairStages + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * kPairStages + 2 + a); };
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen_base + kPairStages * kPairStage + 8 * (2 * kPairStages + 4));
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+  const int m_tiles2 = (p.m_tiles + 1) / 2;            // tiles of 256 rows
+  const int total_tiles = m_tiles2 * p.n_tiles;         // p.n_tiles counts 256-wide tiles
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 8); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tmap_a);
+    prefetch_tmap(&tmap_b);
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();      // both CTAs' barriers are initialised before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs): own half of the operands, completion on the leader's barrier
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += npairs) {
+        const int m0 = (tile % m_tiles2) * 256 + static_cast<int>(rank) * 128;
+        const int n0 = (tile / m_tiles2) * kPairBN + static_cast<int>(rank) * 128;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.err)) { ok = false; break; }
+          const uint32_t sa = base + stage * kPairStage;
+          const uint32_t sb = sa + kPairStageA;
+          const uint32_t leader_full = map_to_cta(full_bar(stage), 0);
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * kPairStage);   // both CTAs' bytes
+          tma_load_2d_pair(sa, &tmap_a, kb * kBK, m0, leader_full);
+          if constexpr (B_MN) tma_load_2d_pair(sb, &tmap_b, n0, kb * kBK, leader_full);
+          else tma_load_2d_pair(sb, &tmap_b, kb * kBK, n0, leader_full);
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer: leader CTA only
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((B_MN ? 1u : 0u) << 16) |
+                             (static_cast<uint32_t>(kPairBN >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase[2] = {0u, 0u};
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += npairs) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPairBN);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.err)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + stage * kPairStage;
+          const uint32_t sb = sa + kPairStageA;
+#pragma unroll
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+            const uint64_t adesc = make_desc(sa + kk * kUmmaK, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_desc(sb + kk * (kUmmaK * 128), kBK * 128, 1024)
+                                        : make_desc(sb + kk * kUmmaK, 16, 1024);
+            mma_i8_pair(d_tmem, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit_pair(empty_bar(stage));
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit_pair(tfull_bar(acc));
+        acc_phase[acc] ^= 1u;
+        acc ^= 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs): own 128 accumulator rows x 256 columns
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase[2] = {0u, 0u};
+    bool ok = true;
+    for (int tile = pair; tile < total_tiles && ok; tile += npairs) {
+      const int64_t m0 = static_cast<int64_t>(tile % m_tiles2) * 256 + static_cast<int64_t>(rank) * 128;
+      const int64_t n0 = static_cast<int64_t>(tile / m_tiles2) * kPairBN;
+      if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, p.err)) { ok = false; break; }
+      tc_fence_after();
+      const int64_t row = m0 + row_in_tile;
+      const bool row_ok = row < p.m;
+      const float sa = (p.scale_a && row_ok) ? p.scale_a[row] : 1.0f;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * kPairBN);
+#pragma unroll 1
+      for (int c0 = 0; c0 < kPairBN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(t_row + static_cast<uint32_t>(c0), r);
+        tmem_ld_wait();
+        const int64_t col0 = n0 + c0;
+        if (!row_ok || col0 >= p.n) continue;
+        const bool full = col0 + 32 <= p.n;
+        if (p.acc_out) {
+          int32_t *dst = p.acc_out + row * p.ldacc + col0;
+          if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<int4 *>(dst + j) = make_int4(static_cast<int>(r[j]), static_cast<int>(r[j + 1]),
+                                                             static_cast<int>(r[j + 2]), static_cast<int>(r[j + 3]));
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = static_cast<int32_t>(r[j]);
+          }
+        }
+        if (p.out) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float sw0 = 1.0f, sw1 = 1.0f;
+            if (p.scale_b) {
+              sw0 = (col0 + j < p.n) ? __ldg(p.scale_b + col0 + j) : 1.0f;
+              sw1 = (col0 + j + 1 < p.n) ? __ldg(p.scale_b + col0 + j + 1) : 1.0f;
+            }
+            float f0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j])), sa), sw0);
+            float f1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j + 1])), sa), sw1);
+            if (p.out_dtype == BSIR_F16) {
+              f0 = fminf(fmaxf(f0, -65504.0f), 65504.0f);
+              f1 = fminf(fmaxf(f1, -65504.0f), 65504.0f);
+              packed[j >> 1] = pack_f16x2(f0, f1);
+            } else {
+              packed[j >> 1] = pack_bf16x2(f0, f1);
+            }
+          }
+          uint16_t *dst = static_cast<uint16_t *>(p.out) + row * p.ldo + col0;
+          if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+            for (int j = 0; j < 16; j += 4)
+              *reinterpret_cast<uint4 *>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.n; ++j)
+              dst[j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));   // 8 arrivals (4 warps x 2 CTAs) at the leader
+      acc_phase[acc] ^= 1u;
+      acc ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();      // the peer may still be signalling into this CTA / reading its shared memory
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------ plain fallback (any layout)
 __global__ void __launch_bounds__(256) w8a8_simple_kernel(GemmParams p, const int8_t *__restrict__ a, int64_t lda,
                                                           const int8_t *__restrict__ b, int64_t ldb, int transpose_b) {
@@ -388,6 +619,32 @@ extern "C" int32_t bsir_matmul_w8a8(int64_t m, int64_t n, int64_t k, const int8_
     bool ok = make_tmap(&ta, a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(lda), kBM);
     if (b_mn) ok = ok && make_tmap(&tb, b, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(ldb), kBK);
     else ok = ok && make_tmap(&tb, b, static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(ldb), bn < 128 ? bn : 128);
+    const char *force = std::getenv("BSIR_W8A8_PATH");
+    // BSIR_W8A8_PATH=1 / 2 forces the single-CTA / CTA-pair kernel (tests use it on small shapes)
+    const bool want_pair = (force && force[0] == '2') ||
+                           (!(force && force[0] == '1') && m >= 512 && ceil_div(m, 256) * ceil_div(n, 256) >= 74);
+    if (ok && want_pair) {
+      // CTA pairs: A boxes of 128 rows as before; B boxes of 128 columns (MN-major) / 128 rows (K-major)
+      CUtensorMap tb2;
+      bool ok2 = b_mn ? make_tmap(&tb2, b, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(ldb), kBK)
+                      : make_tmap(&tb2, b, static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(ldb), 128);
+      if (ok2) {
+        p.n_tiles = static_cast<int>(ceil_div(n, kPairBN));
+        int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
+        int grid = sms & ~1;
+        const int total = static_cast<int>(ceil_div(m, 256)) * p.n_tiles;
+        if (grid > 2 * total) grid = 2 * total;
+        if (b_mn) {
+          cudaFuncSetAttribute(w8a8_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem);
+          w8a8_pair_kernel<true><<<grid, kThreads, kPairSmem, st>>>(ta, tb2, p);
+        } else {
+          cudaFuncSetAttribute(w8a8_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem);
+          w8a8_pair_kernel<false><<<grid, kThreads, kPairSmem, st>>>(ta, tb2, p);
+        }
+        count_launch();
+        return check_launch("matmul_w8a8 (CTA pairs)");
+      }
+    }
     if (ok) {
       if (b_mn) return bn == 256 ? launch_tc<256, true>(ta, tb, p, st) : launch_tc<128, true>(ta, tb, p, st);
       return bn == 256 ? launch_tc<256, false>(ta, tb, p, st)

@@ -40,6 +40,15 @@ def test_w8a8_small_shapes_exact(bsir, m, n, k, transpose_b):
     _w8a8_case(bsir, m, n, k, transpose_b, seed=m + n + k)
 
 
+@pytest.mark.parametrize("transpose_b", [True, False])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 512, 1024), (300, 320, 208), (128, 1000, 256), (1024, 768, 4096)])
+def test_w8a8_cta_pair_kernel_exact(bsir, m, n, k, transpose_b, monkeypatch):
+    monkeypatch.setenv("BSIR_W8A8_PATH", "2")      # force the cta_group::2 kernel on small shapes
+    _w8a8_case(bsir, m, n, k, transpose_b, seed=m + n + k + 7)
+    monkeypatch.setenv("BSIR_W8A8_PATH", "1")      # and the single-CTA kernel gives the same bits
+    _w8a8_case(bsir, m, n, k, transpose_b, seed=m + n + k + 7)
+
+
 def test_w8a8_f16_output_and_unaligned_fallback(bsir):
     _w8a8_case(bsir, 64, 256, 256, False, seed=3, out_dtype=torch.float16)
     # k = 100: the row pitch is not a multiple of 16 bytes -> plain path
