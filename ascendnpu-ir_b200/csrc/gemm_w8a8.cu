@@ -47,23 +47,122 @@ struct GemmParams {
   int64_t ldacc;
   int *err;
   int m_tiles, n_tiles, k_blocks;
-  long long *dbg;
+  int tma_out;   // 1: the output tile goes through shared memory and TMA stores
 };
+
+// ------------------------------------------------------------------ epilogue
+// One accumulator tile, seen by one epilogue warp: its 32 TMEM lanes (rows) x BN columns, 32 columns at
+// a time.  acc -> f32 -> * scale_a[row] -> * scale_b[col] -> bf16/f16.  The per-column scales of the
+// tile sit in shared memory (sw_s); a row's 64 output bytes per chunk are written to a small
+// shared-memory tile with the 64-byte TMA swizzle (conflict-free) and leave through a TMA store, so
+// global memory sees whole sectors and the warp does not wait on the store.  Without TMA (odd output
+// pitch) or for the int32 accumulator dump the lanes store directly.
+constexpr int kEpiStageBytes = 2048;     // 32 rows x 64 bytes, two of them per warp
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y), "r"(src)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+template <int BN>
+__device__ __forceinline__ void epilogue_tile(const GemmParams &p, const CUtensorMap *tmap_out, uint32_t t_row,
+                                              int64_t row, int64_t row_warp0, int64_t n0, int lane, uint8_t *stage_gen,
+                                              uint32_t stage_addr, const float *sw_s, uint32_t &nstores) {
+  const bool row_ok = row < p.m;
+  const float sa = (p.scale_a && row_ok) ? p.scale_a[row] : 1.0f;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    uint32_t r[32];
+    tmem_ld32(t_row + static_cast<uint32_t>(c0), r);
+    tmem_ld_wait();
+    const int64_t col0 = n0 + c0;
+    if (col0 >= p.n) continue;          // uniform over the warp
+    const bool full = col0 + 32 <= p.n;
+    if (p.acc_out && row_ok) {
+      int32_t *dst = p.acc_out + row * p.ldacc + col0;
+      if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<int4 *>(dst + j) = make_int4(static_cast<int>(r[j]), static_cast<int>(r[j + 1]),
+                                                         static_cast<int>(r[j + 2]), static_cast<int>(r[j + 3]));
+      } else {
+        for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = static_cast<int32_t>(r[j]);
+      }
+    }
+    if (!p.out) continue;
+    uint32_t packed[16];
+#pragma unroll
+    for (int j4 = 0; j4 < 32; j4 += 4) {
+      const float4 sw = *reinterpret_cast<const float4 *>(sw_s + c0 + j4);   // same address in every lane: broadcast
+      const float swv[4] = {sw.x, sw.y, sw.z, sw.w};
+#pragma unroll
+      for (int j = 0; j < 4; j += 2) {
+        float f0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j4 + j])), sa), swv[j]);
+        float f1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j4 + j + 1])), sa), swv[j + 1]);
+        if (p.out_dtype == BSIR_F16) {
+          f0 = fminf(fmaxf(f0, -65504.0f), 65504.0f);
+          f1 = fminf(fmaxf(f1, -65504.0f), 65504.0f);
+          packed[(j4 + j) >> 1] = pack_f16x2(f0, f1);
+        } else {
+          packed[(j4 + j) >> 1] = pack_bf16x2(f0, f1);
+        }
+      }
+    }
+    if (p.tma_out) {
+      const uint32_t b = nstores & 1u;
+      // the store that read this buffer two chunks ago must have finished reading it
+      if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      __syncwarp();
+      uint8_t *dstrow = stage_gen + b * kEpiStageBytes + lane * 64;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<uint4 *>(dstrow + ((c ^ ((lane >> 1) & 3)) * 16)) =
+            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) tma_store_2d(tmap_out, static_cast<int>(col0), static_cast<int>(row_warp0), stage_addr + b * kEpiStageBytes);
+      ++nstores;
+    } else if (row_ok) {
+      uint16_t *dst = static_cast<uint16_t *>(p.out) + row * p.ldo + col0;
+      if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+        for (int j = 0; j < 16; j += 4)
+          *reinterpret_cast<uint4 *>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+      } else {
+        for (int j = 0; j < 32 && col0 + j < p.n; ++j)
+          dst[j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu));
+      }
+    }
+  }
+}
+
+// Per-column scales of a tile into this warp's own shared-memory copy (no CTA-wide barrier, so a warp
+// that gives up on a bounded wait can never leave the others stuck).
+template <int BN>
+__device__ __forceinline__ void stage_scales(const GemmParams &p, int64_t n0, float *sw_s, int lane) {
+  for (int i = lane; i < BN; i += 32) sw_s[i] = (p.scale_b && n0 + i < p.n) ? p.scale_b[n0 + i] : 1.0f;
+  __syncwarp();
+}
 
 template <int BN>
 struct TileCfg {
   static constexpr int kStageA = kBM * kBK;           // 16 KB
   static constexpr int kStageB = BN * kBK;            // BN x 128 B
   static constexpr int kStage = kStageA + kStageB;
-  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);   // + 16.5-18 KB of epilogue staging
   static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStage + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr int kEpiOff = kStages * kStage + 1024;                      // after the barriers (1 KB reserved)
+  static constexpr int kEpiBytes = 4 * 2 * kEpiStageBytes + 4 * 2 * BN * 4;     // 4 warps x (2 store buffers + scales of two tiles)
+  static constexpr int kSmemBytes = kEpiOff + kEpiBytes + 1024 /*alignment slack*/;
 };
 
 // ------------------------------------------------------------------ the kernel
 template <int BN, bool B_MN>
 __global__ void __launch_bounds__(kThreads, 1)
-    w8a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+    w8a8_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const __grid_constant__ CUtensorMap tmap_out, GemmParams p) {
   using Cfg = TileCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -142,18 +241,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       int acc = 0;
       uint32_t acc_phase[2] = {0u, 0u};
       bool ok = true;
-      long long t_full = 0, t_issue = 0, t_tempty = 0, t_all = clock64();
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        long long c0 = clock64();
         if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err)) { ok = false; break; }
-        t_tempty += clock64() - c0;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = 0; kb < p.k_blocks; ++kb) {
-          long long c1 = clock64();
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.err)) { ok = false; break; }
-          long long c2 = clock64();
-          t_full += c2 - c1;
           tc_fence_after();
           const uint32_t sa = base + stage * Cfg::kStage;
           const uint32_t sb = sa + Cfg::kStageA;
@@ -165,7 +258,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             mma_i8(d_tmem, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
           }
           tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
-          t_issue += clock64() - c2;
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
@@ -173,79 +265,34 @@ __global__ void __launch_bounds__(kThreads, 1)
         acc_phase[acc] ^= 1u;
         acc ^= 1;
       }
-      if (p.dbg && blockIdx.x == 5) { p.dbg[0] = t_full; p.dbg[1] = t_issue; p.dbg[2] = t_tempty; p.dbg[3] = clock64() - t_all; }
     }
   } else {
     // ---------------- epilogue: warps 2..5, TMEM lane quadrant = warp % 4
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
+    uint8_t *stage_gen = gen_base + Cfg::kEpiOff + (warp - 2) * 2 * kEpiStageBytes;
+    const uint32_t stage_addr = base + Cfg::kEpiOff + (warp - 2) * 2 * kEpiStageBytes;
+    float *sw_all = reinterpret_cast<float *>(gen_base + Cfg::kEpiOff + 4 * 2 * kEpiStageBytes);
+    uint32_t nstores = 0;
     int acc = 0;
     uint32_t acc_phase[2] = {0u, 0u};
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int64_t m0 = static_cast<int64_t>(tile % p.m_tiles) * kBM;
       const int64_t n0 = static_cast<int64_t>(tile / p.m_tiles) * BN;
+      float *sw_s = sw_all + ((warp - 2) * 2 + acc) * BN;
+      stage_scales<BN>(p, n0, sw_s, lane);         // overlaps the tile's main loop
       if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, p.err)) { ok = false; break; }
       tc_fence_after();
-      const int64_t row = m0 + row_in_tile;
-      const bool row_ok = row < p.m;
-      const float sa = (p.scale_a && row_ok) ? p.scale_a[row] : 1.0f;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_row + static_cast<uint32_t>(c0), r);
-        tmem_ld_wait();
-        const int64_t col0 = n0 + c0;
-        if (!row_ok || col0 >= p.n) continue;
-        const bool full = col0 + 32 <= p.n;
-        if (p.acc_out) {
-          int32_t *dst = p.acc_out + row * p.ldacc + col0;
-          if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<int4 *>(dst + j) = make_int4(static_cast<int>(r[j]), static_cast<int>(r[j + 1]),
-                                                             static_cast<int>(r[j + 2]), static_cast<int>(r[j + 3]));
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = static_cast<int32_t>(r[j]);
-          }
-        }
-        if (p.out) {
-          uint32_t packed[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float sw0 = 1.0f, sw1 = 1.0f;
-            if (p.scale_b) {
-              sw0 = (col0 + j < p.n) ? __ldg(p.scale_b + col0 + j) : 1.0f;
-              sw1 = (col0 + j + 1 < p.n) ? __ldg(p.scale_b + col0 + j + 1) : 1.0f;
-            }
-            float f0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j])), sa), sw0);
-            float f1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j + 1])), sa), sw1);
-            if (p.out_dtype == BSIR_F16) {
-              f0 = fminf(fmaxf(f0, -65504.0f), 65504.0f);
-              f1 = fminf(fmaxf(f1, -65504.0f), 65504.0f);
-              packed[j >> 1] = pack_f16x2(f0, f1);
-            } else {
-              packed[j >> 1] = pack_bf16x2(f0, f1);
-            }
-          }
-          uint16_t *dst = static_cast<uint16_t *>(p.out) + row * p.ldo + col0;
-          if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-            for (int j = 0; j < 16; j += 4)
-              *reinterpret_cast<uint4 *>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.n; ++j)
-              dst[j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu));
-          }
-        }
-      }
+      epilogue_tile<BN>(p, &tmap_out, t_row, m0 + row_in_tile, m0 + quad * 32, n0, lane, stage_gen, stage_addr, sw_s, nstores);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));  // 4 arrivals (one per epilogue warp) free the buffer
       acc_phase[acc] ^= 1u;
       acc ^= 1;
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory must outlive the stores
   }
 
   tc_fence_before();
@@ -268,7 +315,8 @@ constexpr int kPairStages = 6;
 constexpr int kPairStageA = kBM * kBK;          // 16 KB: this CTA's 128 rows of A
 constexpr int kPairStageB = 128 * kBK;          // 16 KB: this CTA's 128 columns of B
 constexpr int kPairStage = kPairStageA + kPairStageB;
-constexpr int kPairSmem = kPairStages * kPairStage + 1024 + 256;
+constexpr int kPairEpiOff = kPairStages * kPairStage + 1024;   // barriers get 1 KB
+constexpr int kPairSmem = kPairEpiOff + 4 * 2 * kEpiStageBytes + 4 * 2 * 256 * 4 + 1024;
 constexpr int kPairBN = 256;
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -311,7 +359,8 @@ __device__ __forceinline__ void mma_i8_pair(uint32_t tmem_d, uint64_t adesc, uin
 
 template <bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-    w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmParams p) {
+    w8a8_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                     const __grid_constant__ CUtensorMap tmap_out, GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -409,73 +458,29 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     // ---------------- epilogue (both CTAs): own 128 accumulator rows x 256 columns
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
+    uint8_t *stage_gen = gen_base + kPairEpiOff + (warp - 2) * 2 * kEpiStageBytes;
+    const uint32_t stage_addr = base + kPairEpiOff + (warp - 2) * 2 * kEpiStageBytes;
+    float *sw_all = reinterpret_cast<float *>(gen_base + kPairEpiOff + 4 * 2 * kEpiStageBytes);
+    uint32_t nstores = 0;
     int acc = 0;
     uint32_t acc_phase[2] = {0u, 0u};
     bool ok = true;
     for (int tile = pair; tile < total_tiles && ok; tile += npairs) {
       const int64_t m0 = static_cast<int64_t>(tile % m_tiles2) * 256 + static_cast<int64_t>(rank) * 128;
       const int64_t n0 = static_cast<int64_t>(tile / m_tiles2) * kPairBN;
+      float *sw_s = sw_all + ((warp - 2) * 2 + acc) * kPairBN;
+      stage_scales<kPairBN>(p, n0, sw_s, lane);
       if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, p.err)) { ok = false; break; }
       tc_fence_after();
-      const int64_t row = m0 + row_in_tile;
-      const bool row_ok = row < p.m;
-      const float sa = (p.scale_a && row_ok) ? p.scale_a[row] : 1.0f;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * kPairBN);
-#pragma unroll 1
-      for (int c0 = 0; c0 < kPairBN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(t_row + static_cast<uint32_t>(c0), r);
-        tmem_ld_wait();
-        const int64_t col0 = n0 + c0;
-        if (!row_ok || col0 >= p.n) continue;
-        const bool full = col0 + 32 <= p.n;
-        if (p.acc_out) {
-          int32_t *dst = p.acc_out + row * p.ldacc + col0;
-          if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<int4 *>(dst + j) = make_int4(static_cast<int>(r[j]), static_cast<int>(r[j + 1]),
-                                                             static_cast<int>(r[j + 2]), static_cast<int>(r[j + 3]));
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = static_cast<int32_t>(r[j]);
-          }
-        }
-        if (p.out) {
-          uint32_t packed[16];
-#pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            float sw0 = 1.0f, sw1 = 1.0f;
-            if (p.scale_b) {
-              sw0 = (col0 + j < p.n) ? __ldg(p.scale_b + col0 + j) : 1.0f;
-              sw1 = (col0 + j + 1 < p.n) ? __ldg(p.scale_b + col0 + j + 1) : 1.0f;
-            }
-            float f0 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j])), sa), sw0);
-            float f1 = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j + 1])), sa), sw1);
-            if (p.out_dtype == BSIR_F16) {
-              f0 = fminf(fmaxf(f0, -65504.0f), 65504.0f);
-              f1 = fminf(fmaxf(f1, -65504.0f), 65504.0f);
-              packed[j >> 1] = pack_f16x2(f0, f1);
-            } else {
-              packed[j >> 1] = pack_bf16x2(f0, f1);
-            }
-          }
-          uint16_t *dst = static_cast<uint16_t *>(p.out) + row * p.ldo + col0;
-          if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-            for (int j = 0; j < 16; j += 4)
-              *reinterpret_cast<uint4 *>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.n; ++j)
-              dst[j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu));
-          }
-        }
-      }
+      epilogue_tile<kPairBN>(p, &tmap_out, t_row, m0 + row_in_tile, m0 + quad * 32, n0, lane, stage_gen, stage_addr, sw_s, nstores);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));   // 8 arrivals (4 warps x 2 CTAs) at the leader
       acc_phase[acc] ^= 1u;
       acc ^= 1;
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   }
 
   tc_fence_before();
@@ -534,6 +539,18 @@ EncodeFn encode_fn() {
 
 // 2-D uint8 tensor map: `inner` contiguous bytes per row, `outer` rows of pitch `pitch` bytes,
 // box = [box_rows x 128 bytes], 128-byte swizzle, out-of-range bytes read as zero.
+// Output [m, n] of 2-byte elements: box = [32 rows x 32 columns (64 bytes)], 64-byte swizzle.
+bool make_out_tmap(CUtensorMap *map, void *ptr, uint64_t n, uint64_t m, uint64_t ldo) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {n, m};
+  cuuint64_t strides[1] = {ldo * 2u};
+  cuuint32_t box[2] = {32u, 32u};
+  cuuint32_t estr[2] = {1u, 1u};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool make_tmap(CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t outer, uint64_t pitch, uint32_t box_rows) {
   EncodeFn enc = encode_fn();
   if (!enc) return false;
@@ -547,7 +564,7 @@ bool make_tmap(CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t outer
 }
 
 template <int BN, bool B_MN>
-int32_t launch_tc(const CUtensorMap &ta, const CUtensorMap &tb, GemmParams p, cudaStream_t st) {
+int32_t launch_tc(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tout, GemmParams p, cudaStream_t st) {
   using Cfg = TileCfg<BN>;
   // the attribute is per device and cheap to set
   cudaFuncSetAttribute(w8a8_tc_kernel<BN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
@@ -555,7 +572,7 @@ int32_t launch_tc(const CUtensorMap &ta, const CUtensorMap &tb, GemmParams p, cu
   const int total = p.m_tiles * p.n_tiles;
   int grid = device_info().sm_count > 0 ? device_info().sm_count : 148;
   if (grid > total) grid = total;
-  w8a8_tc_kernel<BN, B_MN><<<grid, kThreads, Cfg::kSmemBytes, st>>>(ta, tb, p);
+  w8a8_tc_kernel<BN, B_MN><<<grid, kThreads, Cfg::kSmemBytes, st>>>(ta, tb, tout, p);
   count_launch();
   return check_launch("matmul_w8a8");
 }
@@ -606,14 +623,15 @@ extern "C" int32_t bsir_matmul_w8a8(int64_t m, int64_t n, int64_t k, const int8_
   p.out = out; p.ldo = ldo; p.out_dtype = out_dtype;
   p.acc_out = acc_out; p.ldacc = n;
   p.err = device_error_word();
-  p.dbg = reinterpret_cast<long long *>(std::getenv("BSIR_DBG_PTR") ? std::strtoull(std::getenv("BSIR_DBG_PTR"), nullptr, 10) : 0ull);
   p.m_tiles = static_cast<int>(ceil_div(m, kBM));
   p.k_blocks = static_cast<int>(ceil_div(k, kBK));
 
   const bool tma_ok = k > 0 && device_info().cc_major >= 10 && aligned_to(a, 16) && aligned_to(b, 16) && lda % 16 == 0 &&
                       ldb % 16 == 0 && encode_fn() != nullptr;
   if (tma_ok) {
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tout;
+    memset(&tout, 0, sizeof(tout));
+    p.tma_out = (out && aligned_to(out, 16) && ldo % 8 == 0 && make_out_tmap(&tout, out, static_cast<uint64_t>(n), static_cast<uint64_t>(m), static_cast<uint64_t>(ldo))) ? 1 : 0;
     const bool b_mn = !transpose_b;
     const int bn = pick_bn(m, n, device_info().sm_count > 0 ? device_info().sm_count : 148, b_mn);
     bool ok = make_tmap(&ta, a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(lda), kBM);
@@ -636,19 +654,19 @@ extern "C" int32_t bsir_matmul_w8a8(int64_t m, int64_t n, int64_t k, const int8_
         if (grid > 2 * total) grid = 2 * total;
         if (b_mn) {
           cudaFuncSetAttribute(w8a8_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem);
-          w8a8_pair_kernel<true><<<grid, kThreads, kPairSmem, st>>>(ta, tb2, p);
+          w8a8_pair_kernel<true><<<grid, kThreads, kPairSmem, st>>>(ta, tb2, tout, p);
         } else {
           cudaFuncSetAttribute(w8a8_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem);
-          w8a8_pair_kernel<false><<<grid, kThreads, kPairSmem, st>>>(ta, tb2, p);
+          w8a8_pair_kernel<false><<<grid, kThreads, kPairSmem, st>>>(ta, tb2, tout, p);
         }
         count_launch();
         return check_launch("matmul_w8a8 (CTA pairs)");
       }
     }
     if (ok) {
-      if (b_mn) return bn == 256 ? launch_tc<256, true>(ta, tb, p, st) : launch_tc<128, true>(ta, tb, p, st);
-      return bn == 256 ? launch_tc<256, false>(ta, tb, p, st)
-                       : bn == 128 ? launch_tc<128, false>(ta, tb, p, st) : launch_tc<64, false>(ta, tb, p, st);
+      if (b_mn) return bn == 256 ? launch_tc<256, true>(ta, tb, tout, p, st) : launch_tc<128, true>(ta, tb, tout, p, st);
+      return bn == 256 ? launch_tc<256, false>(ta, tb, tout, p, st)
+                       : bn == 128 ? launch_tc<128, false>(ta, tb, tout, p, st) : launch_tc<64, false>(ta, tb, tout, p, st);
     }
   }
   if (k == 0) {
