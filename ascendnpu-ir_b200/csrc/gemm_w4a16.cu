@@ -63,11 +63,6 @@ __device__ __forceinline__ uint4 ldg_stream16(const void *p) {
   return v;
 }
 
-// One k32 step of one 32-column piece: 4 weight words (columns 4g..4g+3, 8 k values each).
-struct Piece {
-  uint4 w;
-};
-
 __global__ void __launch_bounds__(kWarps * 32, 2) w4a16_mma_kernel(W4Params p, int64_t m0) {
   __shared__ float red[kWarps][16][kColsPerCta + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -224,9 +219,7 @@ constexpr int kTcThreads = (kTcDqWarps + 1 + kTcMmaWarps) * 32;
 constexpr int kTcMaxK = 4096;
 
 __global__ void __launch_bounds__(kTcThreads, 1)
-    w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, W4Params p, int64_t m0, int *err, long long *dbg) {
-  const long long T0 = clock64();
-#define DBG(i) if (dbg && blockIdx.x == 3 && lane == 0 && (warp == 0 || warp == kTcDqWarps + 1 || warp == kTcDqWarps)) dbg[warp * 16 + (i)] = clock64() - T0;
+    w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, W4Params p, int64_t m0, int *err) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -280,13 +273,14 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     const int tix = warp < kTcDqWarps ? static_cast<int>(threadIdx.x) : static_cast<int>(threadIdx.x) - 32;
     constexpr int kStep = kTcThreads - 32;
     constexpr int kBatch = 16;
-    DBG(10)
     for (int i0 = tix; i0 < pieces; i0 += kStep * kBatch) {
       uint4 v[kBatch];
 #pragma unroll
       for (int u = 0; u < kBatch; ++u) {   // all loads of the batch first
         const int i = i0 + u * kStep;
-        const int piece = i & 7, row = (i >> 3) & 15, chunk = i >> 7;   // 8 threads read one 128-byte run
+        // 8 threads read one 128-byte run; each CTA starts at its own chunk so the CTAs do not all pull
+        // the same L2 lines at the same moment
+        const int piece = i & 7, row = (i >> 3) & 15, chunk = ((i >> 7) + static_cast<int>(blockIdx.x) * 5) % nchunks;
         v[u] = make_uint4(0u, 0u, 0u, 0u);
         if (i < pieces && row < rows_left) v[u] = *reinterpret_cast<const uint4 *>(p.a + (m0 + row) * p.lda + chunk * 64 + piece * 8);
       }
@@ -294,7 +288,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       for (int u = 0; u < kBatch; ++u) {
         const int i = i0 + u * kStep;
         if (i >= pieces) break;
-        const int piece = i & 7, row = (i >> 3) & 15, chunk = i >> 7;
+        const int piece = i & 7, row = (i >> 3) & 15, chunk = ((i >> 7) + static_cast<int>(blockIdx.x) * 5) % nchunks;
         uint4 o;
         o.x = __byte_perm(v[u].x, v[u].z, 0x5410);  // (e0, e4)
         o.y = __byte_perm(v[u].x, v[u].z, 0x7632);  // (e1, e5)
@@ -305,7 +299,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         *reinterpret_cast<uint4 *>(gen + off) = o;
       }
     }
-    DBG(11)
     // scales and zero points of all groups, as 16-byte vectors with every load issued before the first
     // store: one exposed memory latency here instead of one per group in the main loop
     {
@@ -338,13 +331,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         sm_zeros[i] = in ? p.zeros[static_cast<int64_t>(gi) * (p.n / 8) + n0 / 8 + c8] : 0u;
       }
     }
-    DBG(12)
     fence_proxy_async();
-    DBG(13)
     asm volatile("bar.sync 1, %0;" ::"n"(kTcThreads - 32) : "memory");   // all but the producer warp
   }
 
-  DBG(0)
   if (warp == kTcDqWarps) {
     if (lane == 0) {
       int stage = 0;
@@ -399,7 +389,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     uint32_t zz = 0x43004300u, ss = 0u;
     for (int s = 0; s < nstages_total && ok; ++s) {
       if (!mbar_wait(wfull(stage), phase, abort_flag, err)) { ok = false; break; }
-      if (s == 0) { DBG(1) } if (s == 1) { DBG(4) } if (s == 8) { DBG(5) }
       const uint32_t *st = reinterpret_cast<const uint32_t *>(gen + act_bytes + stage * kTcStageBytes);
       {
         const int cs = sub;                             // chunk of the stage this warp owns
@@ -417,7 +406,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         uint32_t words[8];
 #pragma unroll
         for (int r = 0; r < 8; ++r) words[r] = st[(cs * 8 + r) * kTcCols + tid_n];
-        if (c == 0) { DBG(9) }
         // the buffer must have been drained by the MMAs that read it kTcABufs chunks ago
         if (c >= kTcABufs) {
           if (!mbar_wait(aempty(b), (ephase >> b) & 1u, abort_flag, err)) { ok = false; }
@@ -433,11 +421,8 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             qv[r * 4 + q] = bf16x2_mul(bf16x2_sub(v, zz), ss);
           }
         }
-        if (c == 0) { DBG(8) }
         tmem_st32(tmem_a0 + lane_addr + static_cast<uint32_t>(b * 32), qv);
-        if (c == 0) { DBG(2) }
         tmem_st_wait();
-        if (c == 0) { DBG(3) }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(afull(b));
@@ -447,12 +432,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       if (lane == 0) mbar_arrive(wempty(stage));
       if (++stage == kTcStages) { stage = 0; phase ^= 1u; }
     }
-    DBG(6)
     // ---------------- epilogue: the four warps of half 0 read the accumulator
     if (sub == 0 && ok) {
       if (mbar_wait(dfull, 0, abort_flag, err)) {
         tc_fence_after();
-        DBG(7)
         float accs[16];
 #pragma unroll
         for (int mm = 0; mm < 16; ++mm) accs[mm] = 0.0f;
@@ -576,7 +559,7 @@ extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t gr
       const unsigned blocks = static_cast<unsigned>(ceil_div(n, kTcCols));
       int *err = device_error_word();
       for (int64_t m0 = 0; m0 < m; m0 += 16) {
-        w4a16_tc_kernel<<<blocks, kTcThreads, smem, st>>>(tw, p, m0, err, reinterpret_cast<long long *>(std::getenv("BSIR_DBG_PTR") ? std::strtoull(std::getenv("BSIR_DBG_PTR"), nullptr, 10) : 0ull));
+        w4a16_tc_kernel<<<blocks, kTcThreads, smem, st>>>(tw, p, m0, err);
         count_launch();
       }
       return check_launch("matmul_w4a16");
