@@ -111,9 +111,11 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
     for (int i = 0; i < VPT; ++i)
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        const uint32_t a = v[i].w[w] & 0x7fff7fffu;
-        if constexpr (DT == BSIR_BF16) asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(a));
-        else asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(a));
+        // abs + max in one asm block so the assembler can fold |.| into the max as an operand modifier
+        if constexpr (DT == BSIR_BF16)
+          asm("{\n\t.reg .b32 t;\n\tabs.bf16x2 t, %2;\n\tmax.NaN.bf16x2 %0, %1, t;\n\t}" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
+        else
+          asm("{\n\t.reg .b32 t;\n\tabs.f16x2 t, %2;\n\tmax.NaN.f16x2 %0, %1, t;\n\t}" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
       }
     float e[2];
     FloatTraits<DT>::unpack(m2, e);
@@ -657,7 +659,7 @@ int env_int(const char *name, int dflt) {
 
 // Picks threads-per-row (TPR, a power of two in 32..1024) and vectors-per-thread (VPT).  Measured on
 // B200: rows spread over enough threads that each holds about `want_vpt` vectors run fastest (4 for
-// the 8 KB rows of the benchmark shapes); `max_vpt` is what the kernel's registers can hold.
+// the 8 KB rows of the benchmark shapes, 8 for the 16-bit quantiser: 64 threads per 4096-element row); `max_vpt` is what the kernel's registers can hold.
 // Register budget: 16 vectors per thread only up to 256 threads per CTA, 8 up to 512, 4 at 1024.
 // Returns false when the row does not fit.
 bool pick_geometry(int64_t rows, int64_t cols, int elem_bytes, int max_vpt, int want_vpt, int forced_tpr, RowGeom *g,
@@ -743,7 +745,7 @@ int32_t bsir_quant_per_token_i8(int32_t dtype, int32_t round_mode, int64_t rows,
   int vpt = 0;
   const int per_vec = 16 / eb;
   const bool vec_ok = cols > 0 && rows_vector_ok(x, x_row_stride, eb) && aligned_to(q, per_vec) && q_row_stride % per_vec == 0 &&
-                      pick_geometry(rows, cols, eb, 16, 4, env_int("BSIR_QUANT_TPR", 0), &g, &vpt);
+                      pick_geometry(rows, cols, eb, 16, eb == 2 ? 8 : 4, env_int("BSIR_QUANT_TPR", 0), &g, &vpt);
   if (vec_ok) {
     const unsigned blocks = static_cast<unsigned>(ceil_div(rows, g.rpc));
     const unsigned threads = static_cast<unsigned>(g.tpr * g.rpc);
