@@ -30,6 +30,11 @@ for _sub in ("ascendnpu-ir_b200", "oracle"):
 
 ROWS, COLS = 16384, 4096
 ALGO_BYTES = ROWS * COLS * 2 + ROWS * COLS + ROWS * 4   # read bf16 + write int8 + write f32 scales
+# dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of the quantiser on this workload
+# (Nsight Compute, summary in profiles/quant_rows_kernel__bf16_16384x4096.txt): 134,285,568 read + 10,814,976 written.
+NCU_TRAFFIC_BYTES = 145_100_544
+NCU_TRAFFIC_NOTE = ("reads equal the input exactly; 56 MB of the 67 MB output was still dirty in the 126 MB L2 when the "
+                    "captured launch ended, so steady-state traffic per launch is 134.3 + 67.2 = 201.5 MB")
 METRIC = "per_token_int8_quant_hbm_gbps"
 NBUF = 4                                                # input/output sets rotated between steps
 
@@ -351,7 +356,8 @@ def run_ours(args):
                        "l2": f"{NBUF} input/output sets rotated; one set (201 MB) exceeds the 126 MB L2",
                        "parallelism": f"rows sharded over {world} GPU(s), no collective"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                         "frac": achieved / hbm_peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": achieved / hbm_peak, "traffic": NCU_TRAFFIC_BYTES, "traffic_note": NCU_TRAFFIC_NOTE,
+                         "peak_kind": peak_kind,
                          "algorithmic_bytes_per_launch": ALGO_BYTES, "kernel_ms": kernel_ms,
                          "frac_of_nominal_8000": achieved / 8000.0},
             "e2e": {"value": e2e_val, "unit": "GB/s", "h2d_bytes_per_step": ROWS * COLS * 2,
