@@ -8,6 +8,7 @@
 // Float sums are accumulated in f32 (f16 sums are promoted by the reference too:
 // bishengir/lib/Dialect/HFusion/Transforms/Normalize.cpp:7679-7716) in a tree order, so they
 // match the sequential CPU order only to rounding; everything else is order-independent.
+#include <cstdlib>
 #include <climits>
 #include <mutex>
 #include <type_traits>
@@ -303,6 +304,76 @@ __device__ __forceinline__ void rwi_write(const RwiParams &p, const void *src, i
   dst_idx[row] = idx;
 }
 
+// Warp 0 of a (row, segment) CTA publishes the segment's result; the warp that completes the row
+// folds the row's `nseg` partials in segment order and writes the outputs.  Called by all 32 lanes.
+template <int DT, bool IS_MAX>
+__device__ __forceinline__ void rwi_publish_and_fold(const RwiParams &p, const void *src, int64_t row, int seg, int nseg,
+                                                     float m, int best, int nanpos, void *dst_val, int32_t *dst_idx,
+                                                     unsigned *counters, Partial *partials) {
+  const int lane = threadIdx.x & 31;
+  const float ident = IS_MAX ? __int_as_float(0xff800000) : __int_as_float(0x7f800000);
+  Partial *mine = partials + row * nseg;
+  // lane 0 publishes this segment and counts
+  unsigned done = 0u;
+  if (lane == 0) {
+    mine[seg] = Partial{m, best, nanpos, 0};
+    __threadfence();
+    done = atomicAdd(&counters[row], 1u);
+  }
+  done = __shfl_sync(0xffffffffu, done, 0);
+  if (done != static_cast<unsigned>(nseg - 1)) return;   // not the last segment of this row to finish
+  __threadfence();
+  // Ordered fold of the row's partials.  The combine below ("strictly better moves the index; on a
+  // tie the left rule keeps the earlier segment, the right rule takes the later one; nothing after
+  // the first NaN counts") is associative, so each lane folds a contiguous stretch of segments (its
+  // loads independent of one another) and the 32 stretches are joined in order by shuffles.
+  float val = ident;
+  int idx = 0, nan_at = INT_MAX;
+  bool have = false, saw_nan = false;
+  auto join = [&](float sv, int si, bool sh, bool sn, int sa) {   // state (left) <- state (+) right
+    if (saw_nan) return;
+    if (sh) {
+      const bool better = IS_MAX ? (sv > val) : (sv < val);
+      const bool tie = sv == val;
+      if (!have || better || (tie && !p.tie_left)) idx = si;
+      val = have ? ext_nan<IS_MAX>(val, sv) : sv;
+      have = true;
+    }
+    saw_nan = sn;
+    nan_at = sa;
+  };
+  const int per_lane = (nseg + 31) / 32;
+  const int s_begin = min(nseg, lane * per_lane), s_end = min(nseg, s_begin + per_lane);
+  for (int s0 = s_begin; s0 < s_end; s0 += 4) {
+    float pv[4];
+    int pi[4], pn[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      pv[k] = ident; pi[k] = -1; pn[k] = INT_MAX;
+      if (s0 + k < s_end) {
+        const volatile Partial *q = mine + s0 + k;
+        pv[k] = q->val; pi[k] = q->idx; pn[k] = q->nan;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (s0 + k < s_end) join(pv[k], pi[k], pi[k] >= 0, pn[k] != INT_MAX, pn[k]);
+  }
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float sv = __shfl_down_sync(0xffffffffu, val, o);
+    const int si = __shfl_down_sync(0xffffffffu, idx, o);
+    const int sa = __shfl_down_sync(0xffffffffu, nan_at, o);
+    const int flags = __shfl_down_sync(0xffffffffu, (have ? 1 : 0) | (saw_nan ? 2 : 0), o);
+    if ((lane & (2 * o - 1)) == 0 && lane + o < 32) join(sv, si, (flags & 1) != 0, (flags & 2) != 0, sa);
+  }
+  if (saw_nan && p.nan_first) idx = nan_at;
+  if (lane != 0) return;
+  if (saw_nan) val = __int_as_float(0x7fc00000);
+  rwi_write<DT>(p, src, row, val, idx, dst_val, dst_idx);
+  counters[row] = 0u;  // scratch is zero again for the next call
+}
+
 template <int DT, int VPT, bool IS_MAX>
 __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__restrict__ src, void *__restrict__ dst_val,
                                                   int32_t *__restrict__ dst_idx, unsigned *__restrict__ counters,
@@ -360,50 +431,54 @@ __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__res
     }
   }
   const float tm = m;  // this thread's own extreme
-  // Common case (no NaN in the segment), one barrier: each warp agrees on its extreme by shuffles, only
-  // the lanes that hold it search their registers for its first (last) position, and the eight warp
-  // results meet in shared memory.
+  // Common case (no NaN in the segment): the warps agree on the segment extreme through shared
+  // memory, then only the warps that hold it (normally one of eight) search their registers for
+  // its first (last) position.  Searching in every warp costs ten times the instructions of the
+  // reduction itself, which made the kernel issue-bound.
   __shared__ float warp_val[8];
   __shared__ int warp_idx[8];
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   float wm = tm;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) wm = ext_nan<IS_MAX>(wm, __shfl_xor_sync(0xffffffffu, wm, o));
-  int best = p.tie_left ? INT_MAX : -1;
-  if (wm == wm && tm == wm) {
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-      const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
-      if (vi < v1) {
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          float e[kPerWord];
-          FloatTraits<DT>::unpack(v[i].w[w], e);
-#pragma unroll
-          for (int k = 0; k < kPerWord; ++k) {
-            const int gi = static_cast<int>(vi * kPerVec + w * kPerWord + k);
-            if (e[k] == wm) best = p.tie_left ? min(best, gi) : max(best, gi);
-          }
-        }
-      }
-    }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const int other = __shfl_xor_sync(0xffffffffu, best, o);
-    best = p.tie_left ? min(best, other) : max(best, other);
-  }
-  if (lane == 0) { warp_val[wid] = wm; warp_idx[wid] = best; }
+  if (lane == 0) warp_val[wid] = wm;
   __syncthreads();
   m = warp_val[0];
 #pragma unroll
   for (int k = 1; k < 8; ++k) m = ext_nan<IS_MAX>(m, warp_val[k]);
   int nanpos = INT_MAX;
+  int best = p.tie_left ? INT_MAX : -1;
   if (m == m) {
-    best = p.tie_left ? INT_MAX : -1;
+    if (wm == m) {  // warp-uniform
+      if (tm == m) {
 #pragma unroll
-    for (int k = 0; k < 8; ++k)
-      if (warp_val[k] == m) best = p.tie_left ? min(best, warp_idx[k]) : max(best, warp_idx[k]);
+        for (int i = 0; i < VPT; ++i) {
+          const int64_t vi = v0 + threadIdx.x + static_cast<int64_t>(i) * 256;
+          if (vi < v1) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              float e[kPerWord];
+              FloatTraits<DT>::unpack(v[i].w[w], e);
+#pragma unroll
+              for (int k = 0; k < kPerWord; ++k) {
+                const int gi = static_cast<int>(vi * kPerVec + w * kPerWord + k);
+                if (e[k] == m) best = p.tie_left ? min(best, gi) : max(best, gi);
+              }
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const int other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = p.tie_left ? min(best, other) : max(best, other);
+      }
+    }
+    if (lane == 0) warp_idx[wid] = best;
+    __syncthreads();
+    best = warp_idx[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) best = p.tie_left ? min(best, warp_idx[k]) : max(best, warp_idx[k]);
   } else {
     // rare: the segment holds a NaN.  Find the first one, redo the extreme on the prefix before it,
     // then look for that extreme's position inside the prefix (whole-CTA reductions, several barriers).
@@ -474,38 +549,173 @@ __global__ void __launch_bounds__(256) rwi_kernel(RwiParams p, const void *__res
     return;
   }
 
-  Partial *mine = partials + row * p.nseg;
-  if (threadIdx.x != 0) return;
-  mine[seg] = Partial{m, best, nanpos, 0};
-  __threadfence();
-  const unsigned done = atomicAdd(&counters[row], 1u);
-  if (done != static_cast<unsigned>(p.nseg - 1)) return;   // not the last segment of this row to finish
-  __threadfence();
-  float val = ident;
-  int idx = 0;
-  bool have = false, saw_nan = false;
-  for (int s = 0; s < p.nseg; ++s) {
-    const volatile Partial *q = mine + s;
-    const float sv = q->val;
-    const int si = q->idx, sn = q->nan;
-    if (si >= 0) {
-      // sequential-order combine: strictly better moves the index; on a tie the left rule keeps
-      // the earlier segment and the right rule takes the later one
-      const bool better = IS_MAX ? (sv > val) : (sv < val);
-      const bool tie = sv == val;
-      if (!have || better || (tie && !p.tie_left)) idx = si;
-      val = have ? ext_nan<IS_MAX>(val, sv) : sv;
-      have = true;
-    }
-    if (sn != INT_MAX) {
-      saw_nan = true;
-      if (p.nan_first) idx = sn;
-      break;
-    }
+  if (threadIdx.x >= 32) return;
+  rwi_publish_and_fold<DT, IS_MAX>(p, src, row, seg, p.nseg, m, best, nanpos, dst_val, dst_idx, counters, partials);
+}
+
+// Long rows: each row is cut into `nseg` equal parts of `p.seg_vecs` vectors and one CTA streams a
+// part through two register buffers of 256 x 4 vectors, so that the loads of tile t+1 are in flight
+// while tile t is reduced (a 12 us launch cannot afford CTAs that load, wait, reduce and leave).
+// A thread keeps only its running extreme and the tile where it first (last) rose to it; at the end
+// the warps that hold the part's extreme fetch that one tile again (four vectors per thread, from
+// L2) and look for the position.  A part that holds a NaN is redone by three scalar sweeps.
+template <int DT, bool IS_MAX>
+__device__ __noinline__ void rwi_part_with_nan(const RwiParams &p, const void *src, int64_t row, int64_t e0, int64_t e1,
+                                               float *redf, int *redi, float *out_val, int *out_idx, int *out_nan) {
+  const int64_t base = row * p.row_stride;
+  const float ident = IS_MAX ? __int_as_float(0xff800000) : __int_as_float(0x7f800000);
+  auto at = [&](int64_t j) -> float {
+    if constexpr (DT == BSIR_F32) return static_cast<const float *>(src)[base + j];
+    else if constexpr (DT == BSIR_F16) return __half2float(__ushort_as_half(static_cast<const uint16_t *>(src)[base + j]));
+    else return __uint_as_float(static_cast<uint32_t>(static_cast<const uint16_t *>(src)[base + j]) << 16);
+  };
+  int nanpos = INT_MAX;
+  for (int64_t j = e0 + threadIdx.x; j < e1; j += 256) {
+    const float e = at(j);
+    if (e != e) { nanpos = static_cast<int>(j); break; }
   }
-  if (saw_nan) val = __int_as_float(0x7fc00000);
-  rwi_write<DT>(p, src, row, val, idx, dst_val, dst_idx);
-  counters[row] = 0u;  // scratch is zero again for the next call
+  nanpos = cta_reduce_i(nanpos, redi, [](int a, int b) { return min(a, b); });
+  const int64_t lim = nanpos == INT_MAX ? e1 : nanpos;
+  float m = ident;
+  for (int64_t j = e0 + threadIdx.x; j < lim; j += 256) m = ext_nan<IS_MAX>(m, at(j));
+  m = cta_reduce_f(m, redf, [](float a, float b) { return ext_nan<IS_MAX>(a, b); });
+  int best = p.tie_left ? INT_MAX : -1;
+  for (int64_t j = e0 + threadIdx.x; j < lim; j += 256)
+    if (at(j) == m) best = p.tie_left ? min(best, static_cast<int>(j)) : max(best, static_cast<int>(j));
+  if (p.tie_left) best = cta_reduce_i(best, redi, [](int a, int b) { return min(a, b); });
+  else best = cta_reduce_i(best, redi, [](int a, int b) { return max(a, b); });
+  *out_val = m;
+  *out_idx = (best == INT_MAX || best < 0) ? -1 : best;
+  *out_nan = nanpos;
+}
+
+template <int DT, bool IS_MAX>
+__global__ void __launch_bounds__(256, 4) rwi_stream_kernel(RwiParams p, const void *__restrict__ src,
+                                                            void *__restrict__ dst_val, int32_t *__restrict__ dst_idx,
+                                                            unsigned *__restrict__ counters, Partial *__restrict__ partials) {
+  constexpr int VPT = 4;
+  constexpr int kTileVecs = 256 * VPT;
+  constexpr int kPerWord = FloatTraits<DT>::kPerWord;
+  constexpr int kPerVec = 4 * kPerWord;
+  constexpr uint32_t kIdentWord =
+      DT == BSIR_F32 ? (IS_MAX ? 0xff800000u : 0x7f800000u)
+                     : DT == BSIR_BF16 ? (IS_MAX ? 0xff80ff80u : 0x7f807f80u) : (IS_MAX ? 0xfc00fc00u : 0x7c007c00u);
+  using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
+  __shared__ float redf[8];
+  __shared__ int redi[8];
+  __shared__ float warp_val[8];
+  __shared__ int warp_idx[8];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const float ident = IS_MAX ? __int_as_float(0xff800000) : __int_as_float(0x7f800000);
+  const int seg = blockIdx.x;
+  const int64_t row = blockIdx.y;
+  const int64_t a = static_cast<int64_t>(seg) * p.seg_vecs;   // first vector of the part within the row
+  const int64_t b = min(p.nvec, a + p.seg_vecs);              // one past its last vector
+  const Vec16 *xv = reinterpret_cast<const Vec16 *>(static_cast<const E *>(src) + row * p.row_stride);
+  const int ntiles = static_cast<int>((b - a + kTileVecs - 1) / kTileVecs);
+
+  auto load_tile = [&](Vec16 (&buf)[VPT], int t) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t vi = a + static_cast<int64_t>(t) * kTileVecs + i * 256 + threadIdx.x;
+      if (vi < b) buf[i] = ld_stream(xv + vi);
+      else buf[i] = Vec16{{kIdentWord, kIdentWord, kIdentWord, kIdentWord}};
+    }
+  };
+  float rm = ident;   // this thread's running extreme
+  int tbest = 0;      // tile in which it was first (tie_left) or last reached
+  auto reduce_tile = [&](const Vec16 (&buf)[VPT], int t) {
+    float tm;
+    if constexpr (kPerWord == 2) {
+      uint32_t m2 = kIdentWord;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          if constexpr (DT == BSIR_BF16) {
+            if constexpr (IS_MAX) asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(buf[i].w[w]));
+            else asm("min.NaN.bf16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(buf[i].w[w]));
+          } else {
+            if constexpr (IS_MAX) asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(buf[i].w[w]));
+            else asm("min.NaN.f16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(buf[i].w[w]));
+          }
+        }
+      float e2[2];
+      FloatTraits<DT>::unpack(m2, e2);
+      tm = ext_nan<IS_MAX>(e2[0], e2[1]);
+    } else {
+      tm = ident;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i)
+#pragma unroll
+        for (int w = 0; w < 4; ++w) tm = ext_nan<IS_MAX>(tm, __uint_as_float(buf[i].w[w]));
+    }
+    // a tile in which this thread holds no element must not claim the position
+    const bool has = a + static_cast<int64_t>(t) * kTileVecs + threadIdx.x < b;
+    const bool rises = p.tie_left ? (IS_MAX ? tm > rm : tm < rm) : (IS_MAX ? tm >= rm : tm <= rm);
+    if (has && rises) tbest = t;
+    rm = ext_nan<IS_MAX>(rm, tm);
+  };
+
+  Vec16 bufa[VPT], bufb[VPT];
+  load_tile(bufa, 0);
+  for (int t = 0; t < ntiles; t += 2) {
+    if (t + 1 < ntiles) load_tile(bufb, t + 1);
+    reduce_tile(bufa, t);
+    if (t + 1 >= ntiles) break;
+    if (t + 2 < ntiles) load_tile(bufa, t + 2);
+    reduce_tile(bufb, t + 1);
+  }
+
+  // the part's extreme over the CTA, then its position from the warps that hold it
+  float wm = rm;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) wm = ext_nan<IS_MAX>(wm, __shfl_xor_sync(0xffffffffu, wm, o));
+  if (lane == 0) warp_val[wid] = wm;
+  __syncthreads();
+  float m = warp_val[0];
+#pragma unroll
+  for (int k = 1; k < 8; ++k) m = ext_nan<IS_MAX>(m, warp_val[k]);
+  int best = p.tie_left ? INT_MAX : -1;
+  int nanpos = INT_MAX;
+  if (m == m) {
+    if (wm == m) {  // warp-uniform: normally one warp in eight
+      if (rm == m) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+          const int64_t vi = a + static_cast<int64_t>(tbest) * kTileVecs + i * 256 + threadIdx.x;
+          if (vi < b) {
+            const Vec16 v = ld_stream(xv + vi);
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              float e[kPerWord];
+              FloatTraits<DT>::unpack(v.w[w], e);
+#pragma unroll
+              for (int k = 0; k < kPerWord; ++k) {
+                const int gi = static_cast<int>(vi * kPerVec + w * kPerWord + k);
+                if (e[k] == m) best = p.tie_left ? min(best, gi) : max(best, gi);
+              }
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const int other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = p.tie_left ? min(best, other) : max(best, other);
+      }
+    }
+    if (lane == 0) warp_idx[wid] = best;
+    __syncthreads();
+    best = warp_idx[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) best = p.tie_left ? min(best, warp_idx[k]) : max(best, warp_idx[k]);
+    if (best == INT_MAX || best < 0) best = -1;
+  } else {
+    rwi_part_with_nan<DT, IS_MAX>(p, src, row, a * kPerVec, b * kPerVec, redf, redi, &m, &best, &nanpos);
+  }
+  if (threadIdx.x >= 32) return;
+  rwi_publish_and_fold<DT, IS_MAX>(p, src, row, seg, p.nseg, m, best, nanpos, dst_val, dst_idx, counters, partials);
 }
 
 // Scalar fallback: one CTA per row, any stride / alignment / length.
@@ -554,7 +764,9 @@ void plan_segments(int64_t rows, int64_t nvec, int sm_count, int64_t *seg_vecs, 
   int64_t want_seg = rows > 0 ? ceil_div(target_ctas, rows) : 1;
   if (want_seg < 1) want_seg = 1;
   int64_t sv = ceil_div(nvec, want_seg);
-  if (sv > 2048) sv = 2048;
+  int64_t cap = 2048;
+  if (const char *e = std::getenv("BSIR_RWI_SEGVECS")) { const long c = std::atol(e); if (c >= 256 && c <= 2048) cap = c; }
+  if (sv > cap) sv = cap;
   if (sv < 256) sv = 256;
   int v = 1;
   while (v * 256 < sv) v <<= 1;
@@ -562,6 +774,20 @@ void plan_segments(int64_t rows, int64_t nvec, int sm_count, int64_t *seg_vecs, 
   *seg_vecs = static_cast<int64_t>(v) * 256;
   *nseg = static_cast<int>(ceil_div(nvec, *seg_vecs));
   if (*nseg < 1) *nseg = 1;
+}
+
+// Streaming plan for long rows: as many equal parts per row as keep the CTA count within what is
+// resident at once (4 CTAs of 256 threads per SM), each part at least 2048 vectors (two tiles).
+bool plan_stream(int64_t rows, int64_t nvec, int sm_count, int64_t *seg_vecs, int *nseg) {
+  const int64_t ctas = static_cast<int64_t>(sm_count > 0 ? sm_count : 148) * 4;
+  if (nvec < 4096 || rows > ctas) return false;
+  int64_t parts = ctas / rows;
+  if (parts > nvec / 2048) parts = nvec / 2048;
+  if (parts < 1) return false;
+  const int64_t per = ceil_div(nvec, parts);
+  *seg_vecs = per;
+  *nseg = static_cast<int>(ceil_div(nvec, per));
+  return true;
 }
 
 // Scratch layout: a fixed region of per-row counters first (so that, whatever shapes follow one
@@ -593,6 +819,12 @@ int64_t bsir_reduce_with_index_workspace_bytes(int64_t rows, int64_t cols) {
     int64_t sv; int ns, v;
     plan_segments(rows, ceil_div(cols * eb, 16), device_info().sm_count, &sv, &ns, &v);
     if (ns > 1) { const size_t b = rwi_scratch_bytes(rows, ns); if (b > worst) worst = b; }
+    // the streaming kernel for long rows
+    int64_t sv2; int ns2;
+    if (plan_stream(rows < 65535 ? rows : 65535, ceil_div(cols * eb, 16), device_info().sm_count, &sv2, &ns2)) {
+      const size_t b = rwi_scratch_bytes(rows < 65535 ? rows : 65535, ns2);
+      if (b > worst) worst = b;
+    }
   }
   return static_cast<int64_t>(worst);
 }
@@ -646,6 +878,25 @@ int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie_break_le
     return check_launch("reduce_with_index");
   }
   p.nvec = cols / per_vec;
+  // long rows, no more of them than CTAs fit on the device: rows cut into equal parts, streamed
+  if (plan_stream(rows, p.nvec, device_info().sm_count, &p.seg_vecs, &p.nseg) &&
+      std::getenv("BSIR_RWI_NO_STREAM") == nullptr) {
+    const size_t need = rwi_scratch_bytes(rows, p.nseg);
+    char *ws = static_cast<char *>(workspace);
+    if (ws && (static_cast<size_t>(workspace_bytes) < need || !aligned_to(ws, 16))) ws = nullptr;
+    if (!ws) ws = static_cast<char *>(device_workspace(need, st));
+    if (!ws) return BSIR_ERR_WORKSPACE;
+    unsigned *cnt = reinterpret_cast<unsigned *>(ws);
+    Partial *parts = reinterpret_cast<Partial *>(ws + kScratchCounterBytes);
+    const dim3 grid1(static_cast<unsigned>(p.nseg), static_cast<unsigned>(rows));
+#define LS(D)                                                                                         \
+  if (is_max) rwi_stream_kernel<D, true><<<grid1, 256, 0, st>>>(p, src, dst_value, dst_index, cnt, parts); \
+  else rwi_stream_kernel<D, false><<<grid1, 256, 0, st>>>(p, src, dst_value, dst_index, cnt, parts);
+    if (dtype == BSIR_F32) { LS(BSIR_F32) } else if (dtype == BSIR_F16) { LS(BSIR_F16) } else { LS(BSIR_BF16) }
+#undef LS
+    count_launch();
+    return check_launch("reduce_with_index");
+  }
   int vpt = 1;
   plan_segments(rows, p.nvec, device_info().sm_count, &p.seg_vecs, &p.nseg, &vpt);
   unsigned *counters = nullptr;

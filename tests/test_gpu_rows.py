@@ -240,6 +240,59 @@ def test_argmax_ties_and_specials(bsir):
     _check_rwi(bsir, -x, "min")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_argmax_long_rows_streaming_path(bsir, dtype):
+    """Enough long rows that the persistent streaming kernel runs (each CTA's share starts and ends
+    inside rows): duplicates, signed zeros, -inf rows, NaNs before/after the extreme, extremes at
+    both ends of a row and at share boundaries."""
+    cols = 152064 if dtype == torch.bfloat16 else 76032
+    rows = 80
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn(rows, cols, device="cuda", generator=g).clamp(-3, 3).to(dtype)
+    x[0, [5, cols // 2, cols - 1]] = 9.0
+    x[1, :] = 1.0
+    x[2, :] = -float("inf")
+    x[3, :] = 0.0
+    x[3, 100] = -0.0
+    x[4, :] = -0.0
+    x[4, cols // 2 + 1] = 0.0
+    x[5, 40000] = float("nan")
+    x[5, 100] = 8.0
+    x[6, 0] = float("nan")
+    x[7, cols - 1] = float("nan")
+    x[8, cols - 1] = 9.0
+    x[9, 0] = 9.0
+    x[10, [30000, 70000]] = float("nan")
+    x[10, 60000] = 9.0
+    x[11, :] = float("inf")
+    x[12, 12345] = float("inf")
+    for r in range(13, rows):                      # an extreme every few thousand elements: hits share edges
+        x[r, (r * 7919) % cols] = 7.0
+        x[r, (r * 104729) % cols] = 7.0
+    for left in (True, False):
+        for nm in ("region", "nan_first"):
+            _check_rwi(bsir, x, "max", left, nm)
+    _check_rwi(bsir, -x, "min")
+    _check_rwi(bsir, -x, "min", False, "nan_first")
+
+
+def test_argmax_few_very_long_rows_many_partials(bsir):
+    """Two rows cut into hundreds of parts: the ordered fold of the partials runs lane-parallel."""
+    cols = 4_800_000
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(2, cols, device="cuda", generator=g).clamp(-3, 3).to(torch.bfloat16)
+    x[0, [1_234_567, 3_000_001, 4_799_999]] = 9.0       # ties far apart
+    x[1, 2_000_000] = 9.0
+    x[1, 2_500_000] = float("nan")                      # NaN after the extreme
+    x[1, 4_000_000] = 10.0                              # larger value after the NaN must not count
+    for left in (True, False):
+        for nm in ("region", "nan_first"):
+            _check_rwi(bsir, x, "max", left, nm)
+    x[1, 100] = float("nan")                            # and a NaN before everything of interest
+    _check_rwi(bsir, x, "max", True, "nan_first")
+    _check_rwi(bsir, -x, "min", False, "region")
+
+
 def test_argmax_caller_workspace_is_left_zeroed(bsir):
     from bsir import workloads as W
     import ctypes as C
