@@ -8,16 +8,17 @@
 // project's: qweight int32 [k/8, n], nibble t of word (r, c) = q[8r + t, c]; scales bf16 [k/group, n];
 // zeros int32 [k/group, n/8], nibble t of word (g, c) = z[g, 8c + t].
 //
-// Kernel.  One CTA owns 64 output columns and all of K; its 8 warps take contiguous K slices and
-// meet in shared memory at the end.  A thread streams 16-byte pieces of qweight (4 columns x 8 k
-// values), dequantises in registers with packed bf16 arithmetic and feeds mma.sync.m16n8k16:
+// Streaming kernel (w4a16_mma_kernel).  One CTA owns 64 output columns and all of K; its 8 warps take
+// contiguous K slices and meet in shared memory at the end.  A thread streams 16-byte pieces of
+// qweight (4 columns x 8 k values), dequantises in registers with packed bf16 arithmetic and feeds
+// mma.sync.m16n8k16 with the weights as the A operand (see the kernel's comment):
 //   (word >> 4i) & 0x000F000F | 0x43004300 is the bf16 pair (128 + q[k_i], 128 + q[k_i+4]);
 //   subtracting (128 + z) is exact and the product with s rounds once, exactly like the f32
 //   computation it restates ((q - z) * s needs 13 bits).
-// The k order inside an MMA is free as long as A uses the same one, so the nibble pairs (i, i + 4)
-// are taken as they come and A's 8-element pieces are permuted to match with two byte permutes.
-// M up to 16 is one MMA row block; larger M runs the kernel once per 16 rows (decode path; large M
-// belongs on a dense GEMM).
+// The k order inside an MMA is free as long as both operands use the same one, so the nibble pairs
+// (i, i + 4) are taken as they come and the activations' 8-element pieces are permuted to match with
+// two byte permutes.  Row blocks of 9..16 rows run the tensor-memory kernel further down; larger M
+// runs once per 16 rows (decode path; large M belongs on a dense GEMM).
 #include <cstdlib>
 #include <mutex>
 
@@ -26,9 +27,8 @@
 namespace bsir {
 namespace {
 
-constexpr int kColsPerCta = 64;
 constexpr int kWarps = 8;
-constexpr int kPrefetch = 3;  // k32 steps of weights in flight per warp
+constexpr int kPrefetch = 4;  // k32 steps of weights in flight per warp
 
 struct W4Params {
   int64_t m, n, k, group;
@@ -57,137 +57,222 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
   return r;
 }
+// (w >> shift) & 0x000f000f | 0x43004300 as one lop3: written as separate and / or the assembler
+// keeps two instructions (measured: one more instruction per nibble pair).
+__device__ __forceinline__ uint32_t nibble_pair_bf16(uint32_t w, int shift) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(w >> shift), "r"(0x000f000fu), "r"(0x43004300u));
+  return r;
+}
 __device__ __forceinline__ uint4 ldg_stream16(const void *p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
 
-__global__ void __launch_bounds__(kWarps * 32, 2) w4a16_mma_kernel(W4Params p, int64_t m0) {
-  __shared__ float red[kWarps][16][kColsPerCta + 1];
+// out^T = W^T . a^T on mma.sync.m16n8k16: the dequantised weights are the MMA's A operand (16 output
+// columns x 16 k), the activations its B operand (16 k x 8 rows of `a`).  A lane holds weight words of
+// four adjacent columns (one 16-byte piece = 4 columns x 8 k); columns (c0, c1) and (c2, c3) are the
+// tile rows (g, g + 8) of two MMA tiles, and the two nibble-pair halves of a word are two k blocks.
+// Lane (g, t) supplies k = 8 t + {0,4,1,5} (first MMA) and 8 t + {2,6,3,7} (second) of the 32-k step,
+// and reads the activation row g at exactly those k (one 16-byte load, two byte permutes per MMA).
+// MT = number of 8-row blocks of `a` (1 for m <= 8: the decode case needs half the MMAs and accumulators).
+template <int NP, int MT>
+__global__ void __launch_bounds__(kWarps * 32, NP == 1 ? 3 : 2) w4a16_mma_kernel(W4Params p, int64_t m0) {
+  constexpr int kCols = 32 * NP;   // output columns per CTA
+  __shared__ float red[kWarps][8 * MT][kCols + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int64_t col_base = static_cast<int64_t>(blockIdx.x) * kColsPerCta;
-  const int64_t steps = p.k / 32;
-  const int64_t per_warp = (steps + kWarps - 1) / kWarps;
-  const int64_t s_begin = warp * per_warp;
-  const int64_t s_end = s_begin + per_warp < steps ? s_begin + per_warp : steps;
+  const int64_t col_base = static_cast<int64_t>(blockIdx.x) * kCols;
+  const int steps = static_cast<int>(p.k / 32);
+  const int per_warp = (steps + kWarps - 1) / kWarps;
+  const int s_begin = min(steps, warp * per_warp);
+  const int s_end = min(steps, s_begin + per_warp);
   const int64_t rows_left = p.m - m0;
-  const bool row_lo_ok = g < rows_left, row_hi_ok = g + 8 < rows_left;
-  const uint16_t *a_lo = p.a + (m0 + g) * p.lda;
-  const uint16_t *a_hi = p.a + (m0 + g + 8) * p.lda;
 
-  // this thread's columns: piece j (0, 1) covers col_base + 32 j + 4 g + {0..3}
-  int64_t col[2];
-  bool col_ok[2];
+  // this thread's columns: piece j covers col_base + 32 j + 4 g + {0..3}; n is a multiple of 8, so a
+  // piece is all in or all out.  Everything is addressed through pointers that advance by a fixed
+  // stride (weights: one step = 4 word rows; scales / zeros: one group), counters are 32-bit.
+  bool col_ok[NP];
+  const uint32_t *wp[NP];       // weights of the step kPrefetch ahead
+  const uint16_t *sp[NP];       // scales of the next group
+  const uint32_t *zp[NP];       // zero words of the next group
+  int zshift[NP];
+  const int64_t wstride = 4 * p.n;
+  const int steps_per_group = static_cast<int>(p.group / 32);
+  const int first_group = s_begin / steps_per_group;
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    col[j] = col_base + 32 * j + 4 * g;
-    col_ok[j] = col[j] < p.n;  // n is a multiple of 8, so a piece is all in or all out
+  for (int j = 0; j < NP; ++j) {
+    const int64_t c = col_base + 32 * j + 4 * g;
+    col_ok[j] = c < p.n;
+    const int64_t cc = col_ok[j] ? c : 0;
+    wp[j] = p.qw + (static_cast<int64_t>(s_begin) * 4 + t) * p.n + cc;
+    sp[j] = p.scales + static_cast<int64_t>(first_group) * p.n + cc;
+    zp[j] = p.zeros + static_cast<int64_t>(first_group) * (p.n / 8) + cc / 8;
+    zshift[j] = 4 * static_cast<int>(cc % 8);
+  }
+  bool row_ok[MT];
+  const uint16_t *ap[MT];
+#pragma unroll
+  for (int r = 0; r < MT; ++r) {
+    row_ok[r] = g + 8 * r < rows_left;
+    ap[r] = p.a + (m0 + (row_ok[r] ? g + 8 * r : 0)) * p.lda + static_cast<int64_t>(s_begin) * 32 + 8 * t;
   }
 
-  float acc[2][4][4];
+  float acc[NP][2][MT][4];   // [piece][column pair][row block][d0..d3]
 #pragma unroll
-  for (int j = 0; j < 2; ++j)
+  for (int j = 0; j < NP; ++j)
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
+    for (int c2 = 0; c2 < 2; ++c2)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) acc[j][i][e] = 0.0f;
+      for (int r = 0; r < MT; ++r)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][c2][r][e] = 0.0f;
 
-  auto load_piece = [&](int64_t step, int j) -> uint4 {
-    if (step < s_end && col_ok[j]) return ldg_stream16(p.qw + (step * 4 + t) * p.n + col[j]);
-    return make_uint4(0u, 0u, 0u, 0u);
+  // Everything a step needs is requested ahead of its use: weights kPrefetch steps ahead, the
+  // activations one step ahead, the scales and zero points one group ahead.  A warp runs only
+  // k / (32 * kWarps) steps, so a single exposed round trip per step or per group would dominate.
+  int loads_left = s_end - s_begin;     // weight steps not yet requested
+  auto load_pieces = [&](uint4 (&dst)[NP]) {
+#pragma unroll
+    for (int j = 0; j < NP; ++j) {
+      dst[j] = make_uint4(0u, 0u, 0u, 0u);
+      if (loads_left > 0 && col_ok[j]) dst[j] = ldg_stream16(wp[j]);
+      wp[j] += wstride;
+    }
+    --loads_left;
   };
+  uint4 pre[kPrefetch][NP];
+#pragma unroll
+  for (int d = 0; d < kPrefetch; ++d) load_pieces(pre[d]);
 
-  uint4 pre[kPrefetch][2];
+  int groups_left = s_begin < s_end ? (s_end - 1) / steps_per_group - first_group + 1 : 0;
+  uint2 next_sc[NP];
+  uint32_t next_zw[NP];
+  auto load_group = [&]() {
 #pragma unroll
-  for (int d = 0; d < kPrefetch; ++d)
-#pragma unroll
-    for (int j = 0; j < 2; ++j) pre[d][j] = load_piece(s_begin + d, j);
-
-  uint32_t zz[2][4], ss[2][4];  // per column: bf16x2 (128 + z, 128 + z) and (s, s)
-  int64_t cur_group = -1;
-
-  for (int64_t step = s_begin; step < s_end; ++step) {
-    // weights of this step; refill the slot with the step kPrefetch ahead
-    uint4 w[2];
-    {
-      const int slot = static_cast<int>((step - s_begin) % kPrefetch);
-#pragma unroll
-      for (int d = 0; d < kPrefetch; ++d)
-        if (d == slot) {
-#pragma unroll
-          for (int j = 0; j < 2; ++j) { w[j] = pre[d][j]; pre[d][j] = load_piece(step + kPrefetch, j); }
-        }
-    }
-    // this thread's k values of the step: 32 step + 8 t + {0..7}
-    const int64_t k0 = step * 32 + 8 * t;
-    const int64_t grp = k0 / p.group;
-    if (grp != cur_group) {
-      cur_group = grp;
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        uint2 sc = make_uint2(0u, 0u);
-        uint32_t zw = 0u;
-        if (col_ok[j]) {
-          sc = *reinterpret_cast<const uint2 *>(p.scales + grp * p.n + col[j]);
-          zw = p.zeros[grp * (p.n / 8) + col[j] / 8] >> (4 * (col[j] % 8));
-        }
-        const uint32_t s01[4] = {sc.x & 0xffffu, sc.x >> 16, sc.y & 0xffffu, sc.y >> 16};
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          ss[j][i] = s01[i] | (s01[i] << 16);
-          const uint32_t z = (zw >> (4 * i)) & 0xfu;
-          zz[j][i] = (0x4300u | z) * 0x00010001u;
-        }
+    for (int j = 0; j < NP; ++j) {
+      next_sc[j] = make_uint2(0u, 0u);
+      next_zw[j] = 0u;
+      if (groups_left > 0 && col_ok[j]) {
+        next_sc[j] = __ldg(reinterpret_cast<const uint2 *>(sp[j]));
+        next_zw[j] = __ldg(zp[j]) >> zshift[j];
       }
+      sp[j] += p.n;
+      zp[j] += p.n / 8;
     }
-    // A pieces (8 consecutive k) permuted to the pair order (e0,e4) (e1,e5) (e2,e6) (e3,e7)
-    uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = make_uint4(0u, 0u, 0u, 0u);
-    if (row_lo_ok) ra = *reinterpret_cast<const uint4 *>(a_lo + k0);
-    if (row_hi_ok) rb = *reinterpret_cast<const uint4 *>(a_hi + k0);
-    uint32_t fa[2][4];  // [mma][a0..a3]
-    fa[0][0] = __byte_perm(ra.x, ra.z, 0x5410);  // row g   : (e0, e4)
-    fa[0][2] = __byte_perm(ra.x, ra.z, 0x7632);  // row g   : (e1, e5)
-    fa[1][0] = __byte_perm(ra.y, ra.w, 0x5410);  //           (e2, e6)
-    fa[1][2] = __byte_perm(ra.y, ra.w, 0x7632);  //           (e3, e7)
-    fa[0][1] = __byte_perm(rb.x, rb.z, 0x5410);  // row g+8
-    fa[0][3] = __byte_perm(rb.x, rb.z, 0x7632);
-    fa[1][1] = __byte_perm(rb.y, rb.w, 0x5410);
-    fa[1][3] = __byte_perm(rb.y, rb.w, 0x7632);
+    --groups_left;
+  };
+  int a_left = s_end - s_begin;
+  uint4 next_a[MT];
+  auto load_a = [&]() {
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const uint32_t words[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
+    for (int r = 0; r < MT; ++r) {
+      next_a[r] = make_uint4(0u, 0u, 0u, 0u);
+      if (a_left > 0 && row_ok[r]) next_a[r] = __ldg(reinterpret_cast<const uint4 *>(ap[r]));
+      ap[r] += 32;
+    }
+    --a_left;
+  };
+  // The activation and scale loads further down are only one step / one group ahead of their use,
+  // far less than an L2 round trip: ask for all of this warp's lines now, so that they hit in L1.
+  for (int sidx = 1; sidx < s_end - s_begin; ++sidx) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t wd = words[i];
-        uint32_t b[4];
+    for (int r = 0; r < MT; ++r)
+      if (row_ok[r]) asm volatile("prefetch.global.L1 [%0];" ::"l"(ap[r] + 32 * sidx));
+  }
+  for (int gi = 1; gi < groups_left; ++gi) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const uint32_t v = ((wd >> (4 * q)) & 0x000f000fu) | 0x43004300u;  // (128 + q_k, 128 + q_{k+4})
-          b[q] = bf16x2_mul(bf16x2_sub(v, zz[j][i]), ss[j][i]);
+    for (int j = 0; j < NP; ++j)
+      if (col_ok[j]) {
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(sp[j] + gi * p.n));
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(zp[j] + gi * (p.n / 8)));
+      }
+  }
+  load_group();
+  load_a();
+
+  uint32_t zz[NP][4], ss[NP][4];  // per column: bf16x2 (128 + z, 128 + z) and (s, s)
+  int to_group_end = 0;           // steps left in the current group
+
+  for (int base = s_begin; base < s_end; base += kPrefetch) {
+#pragma unroll
+    for (int d = 0; d < kPrefetch; ++d) {
+      const int step = base + d;
+      if (step >= s_end) break;
+      // weights of this step; refill the slot with the step kPrefetch ahead
+      uint4 w[NP];
+#pragma unroll
+      for (int j = 0; j < NP; ++j) w[j] = pre[d][j];
+      load_pieces(pre[d]);
+      if (to_group_end == 0) {
+        to_group_end = steps_per_group - step % steps_per_group;
+#pragma unroll
+        for (int j = 0; j < NP; ++j) {
+          const uint32_t s01[4] = {next_sc[j].x & 0xffffu, next_sc[j].x >> 16, next_sc[j].y & 0xffffu, next_sc[j].y >> 16};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            ss[j][i] = s01[i] | (s01[i] << 16);
+            const uint32_t z = (next_zw[j] >> (4 * i)) & 0xfu;
+            zz[j][i] = (0x4300u | z) * 0x00010001u;
+          }
         }
-        mma_bf16_16816(acc[j][i], fa[0], b[0], b[1]);  // k pairs (0,4) and (1,5)
-        mma_bf16_16816(acc[j][i], fa[1], b[2], b[3]);  // k pairs (2,6) and (3,7)
+        load_group();
+      }
+      --to_group_end;
+      // activations of row g (+8): 8 consecutive k as the pairs (e0,e4) (e1,e5) | (e2,e6) (e3,e7)
+      uint32_t fb[MT][2][2];   // [row block][k block][b0, b1]
+#pragma unroll
+      for (int r = 0; r < MT; ++r) {
+        const uint4 ra = next_a[r];
+        fb[r][0][0] = __byte_perm(ra.x, ra.z, 0x5410);
+        fb[r][0][1] = __byte_perm(ra.x, ra.z, 0x7632);
+        fb[r][1][0] = __byte_perm(ra.y, ra.w, 0x5410);
+        fb[r][1][1] = __byte_perm(ra.y, ra.w, 0x7632);
+      }
+      load_a();
+#pragma unroll
+      for (int j = 0; j < NP; ++j) {
+        const uint32_t words[4] = {w[j].x, w[j].y, w[j].z, w[j].w};
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
+          uint32_t dq[2][4];   // [column of the pair][nibble pair q]: (k_q, k_{q+4})
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint32_t v = nibble_pair_bf16(words[2 * c2 + i], 4 * q);  // (128 + q_k, 128 + q_{k+4})
+              dq[i][q] = bf16x2_mul(bf16x2_sub(v, zz[j][2 * c2 + i]), ss[j][2 * c2 + i]);
+            }
+#pragma unroll
+          for (int kb = 0; kb < 2; ++kb) {
+            // A fragment: a0 (row g, k 2t..) a1 (row g+8, k 2t..) a2 (row g, k 2t+8..) a3 (row g+8, k 2t+8..)
+            const uint32_t fa[4] = {dq[0][2 * kb], dq[1][2 * kb], dq[0][2 * kb + 1], dq[1][2 * kb + 1]};
+#pragma unroll
+            for (int r = 0; r < MT; ++r) mma_bf16_16816(acc[j][c2][r], fa, fb[r][kb][0], fb[r][kb][1]);
+          }
+        }
       }
     }
   }
 
-  // C fragment: c0,c1 -> row g, tile columns 2t, 2t+1; c2,c3 -> row g+8.  Tile column nn of piece j,
-  // word i is CTA column 32 j + 4 nn + i.
+  // D fragment: d0,d1 -> tile row g (column word 2 c2), rows 2t, 2t+1 of `a`; d2,d3 -> tile row g+8
+  // (column word 2 c2 + 1).  CTA column of (piece j, word i) = 32 j + 4 g + i.
 #pragma unroll
-  for (int j = 0; j < 2; ++j)
+  for (int j = 0; j < NP; ++j)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c0 = 32 * j + 4 * (2 * t) + i, c1 = 32 * j + 4 * (2 * t + 1) + i;
-      red[warp][g][c0] = acc[j][i][0];
-      red[warp][g][c1] = acc[j][i][1];
-      red[warp][g + 8][c0] = acc[j][i][2];
-      red[warp][g + 8][c1] = acc[j][i][3];
-    }
+    for (int c2 = 0; c2 < 2; ++c2)
+#pragma unroll
+      for (int r = 0; r < MT; ++r) {
+        const int c0 = 32 * j + 4 * g + 2 * c2, mr = 8 * r + 2 * t;
+        red[warp][mr][c0] = acc[j][c2][r][0];
+        red[warp][mr + 1][c0] = acc[j][c2][r][1];
+        red[warp][mr][c0 + 1] = acc[j][c2][r][2];
+        red[warp][mr + 1][c0 + 1] = acc[j][c2][r][3];
+      }
   __syncthreads();
-  for (int o = threadIdx.x; o < 16 * kColsPerCta; o += kWarps * 32) {
-    const int r = o / kColsPerCta, c = o % kColsPerCta;
+  for (int o = threadIdx.x; o < 8 * MT * kCols; o += kWarps * 32) {
+    const int r = o / kCols, c = o % kCols;
     if (r >= rows_left || col_base + c >= p.n) continue;
     float s = 0.0f;
 #pragma unroll
@@ -417,7 +502,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         for (int r = 0; r < 8; ++r) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const uint32_t v = ((words[r] >> (4 * q)) & 0x000f000fu) | 0x43004300u;
+            const uint32_t v = nibble_pair_bf16(words[r], 4 * q);
             qv[r * 4 + q] = bf16x2_mul(bf16x2_sub(v, zz), ss);
           }
         }
@@ -549,35 +634,42 @@ extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t gr
   const bool fast = k > 0 && aligned_to(a, 16) && lda % 8 == 0 && aligned_to(qweight, 16) && aligned_to(scales, 16);
   // tensor-memory path: needs sm_100, k <= 4096 (activations resident in shared memory), groups that are
   // whole 64-k chunks and a weight pitch TMA can address
+  // Two kernels stream the packed weights.  Blocks of up to 8 rows (decode) run the register
+  // dequantisation + mma.sync kernel, whose MMA count halves for 8 rows; taller blocks run the
+  // tensor-memory kernel (tcgen05), where the MMA cost does not depend on the rows: legacy mma.sync
+  // tiles cost about 32 cycles per SM sub-core on this GPU.  BSIR_W4A16_PATH=m / t forces one of them.
   const char *force = std::getenv("BSIR_W4A16_PATH");
-  const bool want_tc = !(force && force[0] == 'm');
-  if (fast && want_tc && device_info().cc_major >= 10 && k <= kTcMaxK && group % 64 == 0 && k % 64 == 0) {
-    CUtensorMap tw;
-    if (make_weight_tmap(&tw, p.qw, n, k)) {
-      const size_t smem = tc_smem_bytes(k, group);
-      cudaFuncSetAttribute(w4a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-      const unsigned blocks = static_cast<unsigned>(ceil_div(n, kTcCols));
-      int *err = device_error_word();
-      for (int64_t m0 = 0; m0 < m; m0 += 16) {
-        w4a16_tc_kernel<<<blocks, kTcThreads, smem, st>>>(tw, p, m0, err);
-        count_launch();
-      }
-      return check_launch("matmul_w4a16");
-    }
-  }
-  if (fast) {
-    const unsigned blocks = static_cast<unsigned>(ceil_div(n, kColsPerCta));
-    for (int64_t m0 = 0; m0 < m; m0 += 16) {
-      w4a16_mma_kernel<<<blocks, kWarps * 32, 0, st>>>(p, m0);
-      count_launch();
-    }
-  } else {
+  const bool tc_ok = fast && device_info().cc_major >= 10 && k <= kTcMaxK && group % 64 == 0 && k % 64 == 0;
+  if (!fast) {
     for (int64_t m0 = 0; m0 < m; m0 += 65535) {
       const int64_t mr = m - m0 < 65535 ? m - m0 : 65535;
       const dim3 grid(static_cast<unsigned>(ceil_div(n, 128)), static_cast<unsigned>(mr));
       w4a16_plain_kernel<<<grid, 128, 0, st>>>(p, m0);
       count_launch();
     }
+    return check_launch("matmul_w4a16");
+  }
+  CUtensorMap tw;
+  bool have_map = false;
+  for (int64_t m0 = 0; m0 < m; m0 += 16) {
+    const bool one_block = m - m0 <= 8;
+    bool use_tc = tc_ok && !one_block;
+    if (force && force[0] == 'm') use_tc = false;
+    if (force && force[0] == 't') use_tc = tc_ok;
+    if (use_tc && !have_map) {
+      have_map = make_weight_tmap(&tw, p.qw, n, k);
+      if (!have_map) use_tc = false;
+    }
+    if (use_tc) {
+      const size_t smem = tc_smem_bytes(k, group);
+      cudaFuncSetAttribute(w4a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      w4a16_tc_kernel<<<static_cast<unsigned>(ceil_div(n, kTcCols)), kTcThreads, smem, st>>>(tw, p, m0, device_error_word());
+    } else {
+      const unsigned blocks = static_cast<unsigned>(ceil_div(n, 64));
+      if (one_block) w4a16_mma_kernel<2, 1><<<blocks, kWarps * 32, 0, st>>>(p, m0);
+      else w4a16_mma_kernel<2, 2><<<blocks, kWarps * 32, 0, st>>>(p, m0);
+    }
+    count_launch();
   }
   return check_launch("matmul_w4a16");
 }

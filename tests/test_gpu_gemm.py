@@ -121,3 +121,17 @@ def test_w4a16(bsir, m, n, k):
     gf = out.float().cpu().numpy()
     wf = O.bf16_to_f32(want)
     assert np.abs(gf - wf).max() <= 1.0 / 128 * np.abs(wf).max() + 1e-6
+
+
+@pytest.mark.parametrize("path", ["m", "t"])
+@pytest.mark.parametrize("m,n,k", [(1, 14336, 4096), (16, 14336, 4096), (7, 1024, 1024), (16, 256, 8192), (3, 136, 384), (9, 128, 2048), (33, 192, 4096)])
+def test_w4a16_each_kernel(bsir, m, n, k, path, monkeypatch):
+    """Both weight-streaming kernels (register dequantisation + mma.sync, tensor-memory + tcgen05) on the
+    same inputs; shapes a kernel does not take fall through to the other one."""
+    from bsir import workloads as W
+    monkeypatch.setenv("BSIR_W4A16_PATH", path)
+    a, qw, s, z = W.w4a16_input(m, n, k, seed=3 * m + n)
+    out = bsir.matmul_w4a16(a, qw, s, z)
+    want = O.matmul_w4a16(to_bits(a), to_bits(qw), to_bits(s), to_bits(z))
+    wf = O.bf16_to_f32(want)
+    assert np.abs(out.float().cpu().numpy() - wf).max() <= 1.0 / 128 * np.abs(wf).max() + 1e-6
