@@ -472,13 +472,32 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     bool ok = true;
     int cur_group = -1;
     uint32_t zz = 0x43004300u, ss = 0u;
+    // The tensor-memory store of a chunk completes while the next chunk is read and dequantised: the
+    // wait for it, and the arrival that hands the chunk to the MMA issuers, come just before the
+    // next store.  The stage is released as soon as its words are in registers.
+    int pending_buf = -1;
+    auto hand_over = [&]() {
+      if (pending_buf < 0) return;
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(afull(pending_buf));
+      pending_buf = -1;
+    };
     for (int s = 0; s < nstages_total && ok; ++s) {
       if (!mbar_wait(wfull(stage), phase, abort_flag, err)) { ok = false; break; }
       const uint32_t *st = reinterpret_cast<const uint32_t *>(gen + act_bytes + stage * kTcStageBytes);
-      {
-        const int cs = sub;                             // chunk of the stage this warp owns
-        const int c = s * 4 + cs;                       // global chunk
-        if (c < nchunks) {
+      const int cs = sub;                             // chunk of the stage this warp owns
+      const int c = s * 4 + cs;                       // global chunk
+      uint32_t words[8];
+      if (c < nchunks) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) words[r] = st[(cs * 8 + r) * kTcCols + tid_n];
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(wempty(stage));
+      if (++stage == kTcStages) { stage = 0; phase ^= 1u; }
+      if (c < nchunks) {
         const int b = c % kTcABufs;
         const int grp = c / chunks_per_group;
         if (grp != cur_group) {
@@ -487,15 +506,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           const uint32_t z = (sm_zeros[grp * 16 + (tid_n >> 3)] >> (4 * (tid_n & 7))) & 0xfu;
           ss = sv | (sv << 16);
           zz = (0x4300u | z) * 0x00010001u;
-        }
-        uint32_t words[8];
-#pragma unroll
-        for (int r = 0; r < 8; ++r) words[r] = st[(cs * 8 + r) * kTcCols + tid_n];
-        // the buffer must have been drained by the MMAs that read it kTcABufs chunks ago
-        if (c >= kTcABufs) {
-          if (!mbar_wait(aempty(b), (ephase >> b) & 1u, abort_flag, err)) { ok = false; }
-          ephase ^= 1u << b;
-          tc_fence_after();
         }
         uint32_t qv[32];
 #pragma unroll
@@ -506,17 +516,18 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             qv[r * 4 + q] = bf16x2_mul(bf16x2_sub(v, zz), ss);
           }
         }
-        tmem_st32(tmem_a0 + lane_addr + static_cast<uint32_t>(b * 32), qv);
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(afull(b));
+        hand_over();   // the previous chunk's store
+        // the buffer must have been drained by the MMAs that read it kTcABufs chunks ago
+        if (c >= kTcABufs) {
+          if (!mbar_wait(aempty(b), (ephase >> b) & 1u, abort_flag, err)) { ok = false; }
+          ephase ^= 1u << b;
+          tc_fence_after();
         }
+        tmem_st32(tmem_a0 + lane_addr + static_cast<uint32_t>(b * 32), qv);
+        pending_buf = b;
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(wempty(stage));
-      if (++stage == kTcStages) { stage = 0; phase ^= 1u; }
     }
+    hand_over();
     // ---------------- epilogue: the four warps of half 0 read the accumulator
     if (sub == 0 && ok) {
       if (mbar_wait(dfull, 0, abort_flag, err)) {

@@ -303,6 +303,189 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
+// ------------------------------------------------------------------ decode kernel (few rows of A)
+// For m <= 128 the roles of the operands are swapped: out^T[n, m] = W^T[n, k] . a^T[k, m].  The 128
+// output columns of a tile are the MMA's M (the TMEM lanes), the rows of `a`, padded to a multiple
+// of 16, are its N.  A stage then holds a 16 KB weight tile and only NB x 128 bytes of activations
+// instead of a 128-row activation tile that is mostly padding, so the ring is up to 11 stages deep
+// and a CTA keeps ~180 KB of weight loads in flight -- this shape is bound by HBM latency x
+// bandwidth per SM, not by the tensor core.  Roles and barriers as in the kernel above; the
+// epilogue reads the accumulator with lanes = output columns and writes 64-byte runs per row.
+constexpr int kDecStageW = kBM * kBK;             // weight tile: 128 columns x 128 k
+constexpr int kDecMaxStages = 12;
+constexpr int kDecSmemBudget = 200 * 1024;
+
+struct DecodeCfg {
+  int nb;          // rows of `a` per MMA (multiple of 16, <= 128)
+  int stage;       // bytes per stage
+  int stages;
+  uint32_t smem;   // dynamic shared memory to request
+};
+inline DecodeCfg decode_cfg(int64_t m) {
+  DecodeCfg c;
+  c.nb = static_cast<int>((m + 15) / 16 * 16);
+  c.stage = kDecStageW + c.nb * kBK;
+  c.stages = kDecSmemBudget / c.stage;
+  if (c.stages > kDecMaxStages) c.stages = kDecMaxStages;
+  c.smem = static_cast<uint32_t>(c.stages * c.stage + 1024 /*barriers*/ + 1024 /*alignment slack*/);
+  return c;
+}
+
+template <bool W_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+    w8a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, GemmParams p,
+                       int nb, int stage_bytes, int nstages) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *gen_base = smem_raw + (base - raw);
+  const uint32_t bars = base + static_cast<uint32_t>(nstages * stage_bytes);
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (kDecMaxStages + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * kDecMaxStages + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * kDecMaxStages + 2 + a); };
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen_base + nstages * stage_bytes + 8 * (2 * kDecMaxStages + 4));
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = p.n_tiles;
+  const uint32_t tmem_cols = 2 * nb < 32 ? 32u : (2 * nb <= 64 ? 64u : (2 * nb <= 128 ? 128u : 256u));
+
+  // (tile, k block) pairs of this CTA in issue order; pair `it` uses stage it % nstages
+  const int my_tiles = (total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int total_its = my_tiles * p.k_blocks;
+  auto issue = [&](int it) {
+    const int tile = static_cast<int>(blockIdx.x) + (it / p.k_blocks) * static_cast<int>(gridDim.x);
+    const int kb = it % p.k_blocks, stage = it % nstages;
+    const int n0 = tile * kBM;
+    const uint32_t sw = base + stage * stage_bytes;
+    mbar_expect_tx(full_bar(stage), static_cast<uint32_t>(stage_bytes));
+    if constexpr (W_MN) tma_load_2d(sw, &tmap_w, n0, kb * kBK, full_bar(stage));   // [128 k rows x 128 n bytes]
+    else tma_load_2d(sw, &tmap_w, kb * kBK, n0, full_bar(stage));                 // [128 n rows x 128 k bytes]
+    tma_load_2d(sw + kDecStageW, &tmap_a, kb * kBK, 0, full_bar(stage));          // [nb rows x 128 k bytes]
+  };
+  const int preissued = total_its < nstages ? total_its : nstages;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < nstages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // the first ring of loads goes out before the CTA meets: a launch this short (about 9 us of
+    // transfer) cannot afford to wait for the tensor-memory allocation first
+    for (int it = 0; it < preissued; ++it) issue(it);
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      for (int it = preissued; it < total_its; ++it) {
+        const int stage = it % nstages;
+        const uint32_t phase = static_cast<uint32_t>(it / nstages) & 1u;
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.err)) { ok = false; break; }
+        issue(it);
+      }
+      if (!ok) {
+        for (int s = 0; s < nstages; ++s)
+          for (int i = 0; i < 200000; ++i)
+            if (mbar_try_wait(full_bar(s), 0) || mbar_try_wait(full_bar(s), 1)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      // D = s32, A (weights) and B (activations) signed int8; A's major per the weight layout; N = nb, M = 128
+      const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((W_MN ? 1u : 0u) << 15) |
+                             (static_cast<uint32_t>(nb >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase[2] = {0u, 0u};
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * nb);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.err)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sw = base + stage * stage_bytes;
+          const uint32_t sa = sw + kDecStageW;
+#pragma unroll
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+            const uint64_t wdesc = W_MN ? make_desc(sw + kk * (kUmmaK * 128), kBK * 128, 1024) : make_desc(sw + kk * kUmmaK, 16, 1024);
+            const uint64_t adesc = make_desc(sa + kk * kUmmaK, 16, 1024);
+            mma_i8(d_tmem, wdesc, adesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));
+          if (++stage == nstages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(tfull_bar(acc));
+        acc_phase[acc] ^= 1u;
+        acc ^= 1;
+      }
+    }
+  } else {
+    // ---------------- epilogue: warps 2..5, TMEM lane quadrant = warp % 4; lane = output column
+    const int quad = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase[2] = {0u, 0u};
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int64_t col = static_cast<int64_t>(tile) * kBM + quad * 32 + lane;
+      const bool col_ok = col < p.n;
+      const float sw = (p.scale_b && col_ok) ? p.scale_b[col] : 1.0f;
+      const float sa_lane = (p.scale_a && lane < p.m) ? p.scale_a[lane] : 1.0f;   // rows 0..31, one per lane
+      if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, p.err)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * nb);
+      for (int c0 = 0; c0 < nb; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(t_row + static_cast<uint32_t>(c0), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int64_t row = c0 + j;
+          if (row >= p.m) break;               // uniform over the warp
+          const int32_t v = static_cast<int32_t>(r[j]);
+          // all lanes take part in the shuffle (row is uniform over the warp)
+          const float sa = row < 32 ? __shfl_sync(0xffffffffu, sa_lane, static_cast<int>(row)) : (p.scale_a ? __ldg(p.scale_a + row) : 1.0f);
+          if (p.acc_out && col_ok) p.acc_out[row * p.ldacc + col] = v;
+          if (p.out && col_ok) {
+            float f = __fmul_rn(__fmul_rn(static_cast<float>(v), sa), sw);
+            uint16_t bits;
+            if (p.out_dtype == BSIR_F16) {
+              f = fminf(fmaxf(f, -65504.0f), 65504.0f);
+              bits = static_cast<uint16_t>(pack_f16x2(f, 0.0f) & 0xffffu);
+            } else {
+              bits = static_cast<uint16_t>(pack_bf16x2(f, 0.0f) & 0xffffu);
+            }
+            static_cast<uint16_t *>(p.out)[row * p.ldo + col] = bits;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      acc_phase[acc] ^= 1u;
+      acc ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
 // ------------------------------------------------------------------ CTA-pair kernel (cta_group::2)
 // Two CTAs of a cluster share one 256 x 256 tile: CTA r owns rows [128 r, 128 r + 128) of A and the
 // accumulator rows that go with them, and loads only columns [128 r, 128 r + 128) of the B tile; the
@@ -661,6 +844,30 @@ extern "C" int32_t bsir_matmul_w8a8(int64_t m, int64_t n, int64_t k, const int8_
         }
         count_launch();
         return check_launch("matmul_w8a8 (CTA pairs)");
+      }
+    }
+    // few rows: operands swapped, deep ring of weight tiles (BSIR_W8A8_PATH=3 forces it for m <= 128, =1 avoids it)
+    // measured on B200 (k 4096, n 14336): 13.5-16 us against 19-20 us for m <= 24, slower from m = 32 on
+    const bool want_decode = (force && force[0] == '3') ? m <= 128 : (!force && m <= 24);
+    if (ok && want_decode) {
+      const DecodeCfg dc = decode_cfg(m);
+      CUtensorMap tw, tact;
+      bool ok3 = b_mn ? make_tmap(&tw, b, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(ldb), kBK)
+                      : make_tmap(&tw, b, static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(ldb), kBM);
+      ok3 = ok3 && make_tmap(&tact, a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(lda), static_cast<uint32_t>(dc.nb));
+      if (ok3) {
+        p.n_tiles = static_cast<int>(ceil_div(n, kBM));
+        int grid = device_info().sm_count > 0 ? device_info().sm_count : 148;
+        if (grid > p.n_tiles) grid = p.n_tiles;
+        if (b_mn) {
+          cudaFuncSetAttribute(w8a8_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dc.smem));
+          w8a8_decode_kernel<true><<<grid, kThreads, dc.smem, st>>>(tw, tact, p, dc.nb, dc.stage, dc.stages);
+        } else {
+          cudaFuncSetAttribute(w8a8_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dc.smem));
+          w8a8_decode_kernel<false><<<grid, kThreads, dc.smem, st>>>(tw, tact, p, dc.nb, dc.stage, dc.stages);
+        }
+        count_launch();
+        return check_launch("matmul_w8a8 (decode)");
       }
     }
     if (ok) {

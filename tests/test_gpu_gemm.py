@@ -49,6 +49,17 @@ def test_w8a8_cta_pair_kernel_exact(bsir, m, n, k, transpose_b, monkeypatch):
     _w8a8_case(bsir, m, n, k, transpose_b, seed=m + n + k + 7)
 
 
+@pytest.mark.parametrize("transpose_b", [True, False])
+@pytest.mark.parametrize("m,n,k", [(1, 128, 128), (16, 256, 4096), (7, 1000, 640), (33, 384, 208), (64, 14336, 512),
+                                   (100, 320, 1024), (128, 256, 256)])
+def test_w8a8_decode_kernel_exact(bsir, m, n, k, transpose_b, monkeypatch):
+    monkeypatch.setenv("BSIR_W8A8_PATH", "3")      # operands swapped: weights on the TMEM lanes, rows of a as MMA N
+    _w8a8_case(bsir, m, n, k, transpose_b, seed=m + n + k + 11)
+    _w8a8_case(bsir, m, n, k, transpose_b, seed=m + n + k + 12, out_dtype=torch.float16)
+    monkeypatch.setenv("BSIR_W8A8_PATH", "1")      # the 128-row-tile kernel gives the same bits
+    _w8a8_case(bsir, m, n, k, transpose_b, seed=m + n + k + 11)
+
+
 def test_w8a8_f16_output_and_unaligned_fallback(bsir):
     _w8a8_case(bsir, 64, 256, 256, False, seed=3, out_dtype=torch.float16)
     # k = 100: the row pitch is not a multiple of 16 bytes -> plain path
