@@ -283,116 +283,109 @@ __global__ void __launch_bounds__(kWarps * 32, NP == 1 ? 3 : 2) w4a16_mma_kernel
 
 // ------------------------------------------------------------------ tensor-memory path (tcgen05)
 // out^T[n, m] = W^T[n, k] . a^T[k, m]: the 128 output columns of a CTA are the 128 lanes of tensor
-// memory, the (at most 16) rows of `a` are the MMA's N.  Roles in a CTA of 320 threads:
-//   warp 8      TMA producer: boxes of packed weights [32 word rows x 128 columns] (16 KB) into a ring;
-//   warp 9      MMA issuer: tcgen05.mma.kind::f16, A operand read from tensor memory, B = activations
-//               in shared memory, f32 accumulator in tensor memory;
-//   warps 0-7   dequantisers: thread = one output column.  Each reads its column's words from the
+// memory, the (at most 16) rows of `a` are the MMA's N.  Roles in a CTA of 672 threads:
+//   warp 16     TMA producer.  A stage of the ring holds 256 k: one box of packed weights
+//               [32 word rows x 128 columns] (16 KB) and four boxes of activations [16 rows x 64 k]
+//               (2 KB each, 128-byte swizzle: the tensor core's K-major layout as TMA writes it);
+//   warps 0-15  dequantisers: thread = one output column.  Each reads its column's words from the
 //               stage, turns every word into four bf16 pairs (k_i, k_i+4) and stores them into its own
-//               TMEM lane (tcgen05.st); warps w and w + 4 share a lane quadrant and alternate 64-k chunks.
-// The activations are staged once per CTA in shared memory in the tensor core's K-major 128-byte
-// swizzled layout, with each group of 8 k permuted to (0,4,1,5,2,6,3,7) so that it matches the pair
-// order the nibble trick produces.  All waits are bounded.
+//               TMEM lane (tcgen05.st); warp w owns lane quadrant w % 4 and chunk w / 4 of every stage;
+//   warps 17-20 first put every 16-byte piece of the stage's activations into the pair order the nibble
+//               trick produces (k 0,4,1,5,2,6,3,7; in place, the swizzle only moves whole pieces), then
+//               one thread per warp issues tcgen05.mma.kind::f16 for its chunk: A operand from tensor
+//               memory, B = the activations in the stage, f32 accumulator in tensor memory.
+// Nothing is staged up front except the scales and zero points, so the ring is as deep as shared
+// memory allows (8 stages = 128 KB of weight loads in flight per SM): the shape is bound by HBM
+// latency x bandwidth per SM.  All waits are bounded.
 constexpr int kTcCols = 128;            // output columns per CTA
 constexpr int kTcStageRows = 32;        // word rows per weight stage (= 256 k)
-constexpr int kTcStageBytes = kTcStageRows * kTcCols * 4;
-constexpr int kTcStages = 4;
-constexpr int kTcABufs = 8;             // 64-k chunks of dequantised weights in TMEM (12 x 32 columns)
+constexpr int kTcWeightBytes = kTcStageRows * kTcCols * 4;   // 16 KB
+constexpr int kTcActBytes = 4 * 2048;                        // four chunks of 16 rows x 128 B
+constexpr int kTcStageBytes = kTcWeightBytes + kTcActBytes;  // 24 KB
+constexpr int kTcMaxStages = 8;
+constexpr int kTcABufs = 8;             // 64-k chunks of dequantised weights in TMEM (8 x 32 columns)
 constexpr int kTcDqWarps = 16;          // dequantising warps: 4 lane quadrants x 4 chunks of a stage
-constexpr int kTcMmaWarps = 4;          // MMA-issuing warps (one thread each); chunk c belongs to issuer c % 4
+constexpr int kTcMmaWarps = 4;          // fix-up + MMA-issuing warps; chunk c belongs to issuer c % 4
 constexpr int kTcThreads = (kTcDqWarps + 1 + kTcMmaWarps) * 32;
-constexpr int kTcMaxK = 4096;
+constexpr int kTcSmemBudget = 222 * 1024;
+
+struct TcLayout {
+  int stages;
+  uint32_t sc_off, zp_off, bar_off, bytes;
+};
+__host__ __device__ inline TcLayout tc_layout(int64_t k, int64_t group) {
+  TcLayout L;
+  const uint32_t ngroups = static_cast<uint32_t>(k / group);
+  const uint32_t tail = ngroups * kTcCols * 2u + ngroups * 64u + 512u;   // scales, zero words, barriers
+  int st = static_cast<int>((kTcSmemBudget - 1024 - static_cast<int>(tail)) / kTcStageBytes);
+  L.stages = st > kTcMaxStages ? kTcMaxStages : st;
+  L.sc_off = static_cast<uint32_t>(L.stages > 0 ? L.stages : 0) * kTcStageBytes;
+  L.zp_off = L.sc_off + ngroups * kTcCols * 2u;
+  L.bar_off = (L.zp_off + ngroups * 64u + 15u) & ~15u;
+  L.bytes = L.bar_off + 512u + 1024u;
+  return L;
+}
 
 __global__ void __launch_bounds__(kTcThreads, 1)
-    w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, W4Params p, int64_t m0, int *err) {
+    w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, W4Params p,
+                    int64_t m0, int *err) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t *gen = smem_raw + (base - raw);
+  const TcLayout L = tc_layout(p.k, p.group);
+  const int nstages = L.stages;
   const int nchunks = static_cast<int>(p.k / 64);
-  const uint32_t act_bytes = static_cast<uint32_t>(nchunks) * 2048u;   // 16 rows x 128 B per 64-k chunk
-  const uint32_t stage0 = base + act_bytes;
-  // per-group scales [ngroups][128] bf16 and zero points [ngroups][16] words of this CTA's columns
   const int ngroups = static_cast<int>(p.k / p.group);
-  const uint32_t sc_off = act_bytes + kTcStages * kTcStageBytes;
-  const uint32_t zp_off = sc_off + static_cast<uint32_t>(ngroups) * kTcCols * 2u;
-  const uint32_t bar_off = (zp_off + static_cast<uint32_t>(ngroups) * 16u * 4u + 15u) & ~15u;
-  const uint32_t bars = base + bar_off;
+  const uint32_t bars = base + L.bar_off;
   auto wfull = [&](int s) { return bars + 8u * s; };
-  auto wempty = [&](int s) { return bars + 8u * (kTcStages + s); };
-  auto afull = [&](int b) { return bars + 8u * (2 * kTcStages + b); };
-  auto aempty = [&](int b) { return bars + 8u * (2 * kTcStages + kTcABufs + b); };
-  const uint32_t dfull = bars + 8u * (2 * kTcStages + 2 * kTcABufs);
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + bar_off + 8 * (2 * kTcStages + 2 * kTcABufs + 1));
-  uint16_t *sm_scales = reinterpret_cast<uint16_t *>(gen + sc_off);
-  uint32_t *sm_zeros = reinterpret_cast<uint32_t *>(gen + zp_off);
+  auto wempty = [&](int s) { return bars + 8u * (kTcMaxStages + s); };
+  auto aready = [&](int s) { return bars + 8u * (2 * kTcMaxStages + s); };
+  auto afull = [&](int b) { return bars + 8u * (3 * kTcMaxStages + b); };
+  auto aempty = [&](int b) { return bars + 8u * (3 * kTcMaxStages + kTcABufs + b); };
+  const uint32_t dfull = bars + 8u * (3 * kTcMaxStages + 2 * kTcABufs);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + L.bar_off + 8 * (3 * kTcMaxStages + 2 * kTcABufs + 1));
+  uint16_t *sm_scales = reinterpret_cast<uint16_t *>(gen + L.sc_off);
+  uint32_t *sm_zeros = reinterpret_cast<uint32_t *>(gen + L.zp_off);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t n0 = static_cast<int64_t>(blockIdx.x) * kTcCols;
   const int nstages_total = (nchunks + 3) / 4;   // stages of 4 chunks
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kTcStages; ++s) { mbar_init(wfull(s), 1); mbar_init(wempty(s), kTcDqWarps); }
+  auto issue_stage = [&](int s) {
+    const int slot = s % nstages;
+    const uint32_t dst = base + slot * kTcStageBytes;
+    mbar_expect_tx(wfull(slot), kTcStageBytes);
+    tma_load_2d(dst, &tmap_w, static_cast<int>(n0), s * kTcStageRows, wfull(slot));
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+      tma_load_2d(dst + kTcWeightBytes + c * 2048, &tmap_a, (s * 4 + c) * 64, static_cast<int>(m0), wfull(slot));
+  };
+  const int preissued = nstages_total < nstages ? nstages_total : nstages;
+  if (warp == kTcDqWarps && lane == 0) {
+    for (int s = 0; s < nstages; ++s) {
+      mbar_init(wfull(s), 1);
+      mbar_init(wempty(s), kTcDqWarps + kTcMmaWarps);
+      mbar_init(aready(s), kTcMmaWarps * 32);
+    }
     for (int b = 0; b < kTcABufs; ++b) { mbar_init(afull(b), 4); mbar_init(aempty(b), 1); }
     mbar_init(dfull, kTcMmaWarps);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    prefetch_tmap(&tmap_w);
+    // the first ring of loads goes out before the CTA meets
+    for (int s = 0; s < preissued; ++s) issue_stage(s);
   }
   if (warp == kTcDqWarps + 1) tmem_alloc(smem_u32(tmem_slot), 512);
-  tc_fence_before();
-  __syncthreads();   // barriers and the TMEM address are visible; the weight stream can start now
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  // One f32 accumulator (16 columns) per issuing warp; the epilogue adds them.  A tcgen05.mma costs its
-  // issuing thread ~70 cycles and a commit ~130 whatever the MMA's size, and these MMAs are tiny
-  // (128 x 16 x 16), so a single issuer would be the bottleneck: four warps issue side by side.
-  const uint32_t tmem_d = tmem_base;            // columns 0..63
-  const uint32_t tmem_a0 = tmem_base + 64;      // kTcABufs x 32 columns of packed bf16 pairs
-
-  // stage the activations (rows m0 .. m0+15, zero beyond m): 16-byte pieces of 8 k, permuted and swizzled
-  if (warp != kTcDqWarps) {   // the producer warp does not wait for this: weights stream in meanwhile
-    const int64_t rows_left = p.m - m0;
-    const int pieces = nchunks * 8 * 16;   // (chunk, 16-B piece, row)
-    const int tix = warp < kTcDqWarps ? static_cast<int>(threadIdx.x) : static_cast<int>(threadIdx.x) - 32;
-    constexpr int kStep = kTcThreads - 32;
-    constexpr int kBatch = 16;
-    for (int i0 = tix; i0 < pieces; i0 += kStep * kBatch) {
-      uint4 v[kBatch];
-#pragma unroll
-      for (int u = 0; u < kBatch; ++u) {   // all loads of the batch first
-        const int i = i0 + u * kStep;
-        // 8 threads read one 128-byte run; each CTA starts at its own chunk so the CTAs do not all pull
-        // the same L2 lines at the same moment
-        const int piece = i & 7, row = (i >> 3) & 15, chunk = ((i >> 7) + static_cast<int>(blockIdx.x) * 5) % nchunks;
-        v[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (i < pieces && row < rows_left) v[u] = *reinterpret_cast<const uint4 *>(p.a + (m0 + row) * p.lda + chunk * 64 + piece * 8);
-      }
-#pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
-        const int i = i0 + u * kStep;
-        if (i >= pieces) break;
-        const int piece = i & 7, row = (i >> 3) & 15, chunk = ((i >> 7) + static_cast<int>(blockIdx.x) * 5) % nchunks;
-        uint4 o;
-        o.x = __byte_perm(v[u].x, v[u].z, 0x5410);  // (e0, e4)
-        o.y = __byte_perm(v[u].x, v[u].z, 0x7632);  // (e1, e5)
-        o.z = __byte_perm(v[u].y, v[u].w, 0x5410);  // (e2, e6)
-        o.w = __byte_perm(v[u].y, v[u].w, 0x7632);  // (e3, e7)
-        const uint32_t off = static_cast<uint32_t>(chunk) * 2048u + static_cast<uint32_t>(row) * 128u +
-                             static_cast<uint32_t>((piece ^ (row & 7)) * 16);
-        *reinterpret_cast<uint4 *>(gen + off) = o;
-      }
-    }
-    // scales and zero points of all groups, as 16-byte vectors with every load issued before the first
-    // store: one exposed memory latency here instead of one per group in the main loop
-    {
-      const int nvec = ngroups * (kTcCols / 8);                 // 8 bf16 per vector
+  // scales and zero points of all groups of this CTA's columns, every load issued before the first store
+  {
+    const int nvec = ngroups * (kTcCols / 8);                 // 8 bf16 per vector
+    for (int i0 = threadIdx.x; i0 < nvec; i0 += 2 * kTcThreads) {
       uint4 sv[2];
       uint32_t zv[2];
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
-        const int i = tix + u * kStep;
+        const int i = i0 + u * kTcThreads;
         const int gi = i / (kTcCols / 8), c8 = i % (kTcCols / 8);
         sv[u] = make_uint4(0u, 0u, 0u, 0u);
         zv[u] = 0u;
@@ -403,61 +396,85 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       }
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
-        const int i = tix + u * kStep;
+        const int i = i0 + u * kTcThreads;
         if (i < nvec) {
           reinterpret_cast<uint4 *>(sm_scales)[i] = sv[u];
           sm_zeros[i] = zv[u];
         }
       }
-      for (int i = tix + 2 * kStep; i < nvec; i += kStep) {    // only when there are more than 64 groups' worth
-        const int gi = i / (kTcCols / 8), c8 = i % (kTcCols / 8);
-        const bool in = n0 + 8 * c8 < p.n;
-        reinterpret_cast<uint4 *>(sm_scales)[i] = in ? *reinterpret_cast<const uint4 *>(p.scales + static_cast<int64_t>(gi) * p.n + n0 + 8 * c8) : make_uint4(0u, 0u, 0u, 0u);
-        sm_zeros[i] = in ? p.zeros[static_cast<int64_t>(gi) * (p.n / 8) + n0 / 8 + c8] : 0u;
-      }
     }
-    fence_proxy_async();
-    asm volatile("bar.sync 1, %0;" ::"n"(kTcThreads - 32) : "memory");   // all but the producer warp
   }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // One f32 accumulator (16 columns) per issuing warp; the epilogue adds them.  A tcgen05.mma costs its
+  // issuing thread ~70 cycles and a commit ~130 whatever the MMA's size, and these MMAs are tiny
+  // (128 x 16 x 16), so a single issuer would be the bottleneck: four warps issue side by side.
+  const uint32_t tmem_d = tmem_base;            // columns 0..63
+  const uint32_t tmem_a0 = tmem_base + 64;      // kTcABufs x 32 columns of packed bf16 pairs
 
   if (warp == kTcDqWarps) {
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
       bool ok = true;
-      for (int s = 0; s < nstages_total; ++s) {
-        if (!mbar_wait(wempty(stage), phase ^ 1u, abort_flag, err)) { ok = false; break; }
-        mbar_expect_tx(wfull(stage), kTcStageBytes);
-        tma_load_2d(stage0 + stage * kTcStageBytes, &tmap_w, static_cast<int>(n0), s * kTcStageRows, wfull(stage));
-        if (++stage == kTcStages) { stage = 0; phase ^= 1u; }
+      for (int s = preissued; s < nstages_total; ++s) {
+        const int slot = s % nstages;
+        const uint32_t phase = static_cast<uint32_t>(s / nstages) & 1u;
+        if (!mbar_wait_relaxed(wempty(slot), phase ^ 1u, abort_flag, err)) { ok = false; break; }
+        issue_stage(s);
       }
       if (!ok)
-        for (int s = 0; s < kTcStages; ++s)
+        for (int s = 0; s < nstages; ++s)
           for (int i = 0; i < 200000; ++i)
             if (mbar_try_wait(wfull(s), 0) || mbar_try_wait(wfull(s), 1)) break;
     }
   } else if (warp > kTcDqWarps) {
-    if (lane == 0) {
-      // D = f32, A = B = bf16, both K-major, N = 16, M = 128
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(16 >> 3) << 17) |
-                             (static_cast<uint32_t>(128 >> 4) << 24);
-      const int issuer = warp - kTcDqWarps - 1;
-      uint32_t aphase = 0u;   // one parity bit per buffer
-      bool ok = true;
-      for (int c = issuer; c < nchunks && ok; c += kTcMmaWarps) {
+    // ---------------- activation fix-up (all lanes) and MMA issue (lane 0)
+    // D = f32, A = B = bf16, both K-major, N = 16, M = 128
+    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(16 >> 3) << 17) |
+                           (static_cast<uint32_t>(128 >> 4) << 24);
+    const int issuer = warp - kTcDqWarps - 1;
+    const int tix = issuer * 32 + lane;
+    uint32_t aphase = 0u;   // one parity bit per TMEM buffer
+    bool ok = true;
+    for (int s = 0; s < nstages_total && ok; ++s) {
+      const int slot = s % nstages;
+      const uint32_t phase = static_cast<uint32_t>(s / nstages) & 1u;
+      if (!mbar_wait_relaxed(wfull(slot), phase, abort_flag, err)) { ok = false; break; }
+      uint8_t *act = gen + slot * kTcStageBytes + kTcWeightBytes;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        uint4 *piece = reinterpret_cast<uint4 *>(act) + tix + u * 128;
+        const uint4 v = *piece;
+        uint4 o;
+        o.x = __byte_perm(v.x, v.z, 0x5410);  // (e0, e4)
+        o.y = __byte_perm(v.x, v.z, 0x7632);  // (e1, e5)
+        o.z = __byte_perm(v.y, v.w, 0x5410);  // (e2, e6)
+        o.w = __byte_perm(v.y, v.w, 0x7632);  // (e3, e7)
+        *piece = o;
+      }
+      fence_proxy_async();
+      mbar_arrive(aready(slot));
+      if (lane != 0) continue;
+      const int c = s * 4 + issuer;
+      if (c < nchunks) {
         const int b = c % kTcABufs;
+        if (!mbar_wait(aready(slot), phase, abort_flag, err)) { ok = false; break; }
         if (!mbar_wait(afull(b), (aphase >> b) & 1u, abort_flag, err)) { ok = false; break; }
         aphase ^= 1u << b;
         tc_fence_after();
-        const uint32_t act = base + static_cast<uint32_t>(c) * 2048u;
+        const uint32_t act_addr = base + slot * kTcStageBytes + kTcWeightBytes + static_cast<uint32_t>(issuer) * 2048u;
 #pragma unroll
         for (int j = 0; j < 4; ++j)   // 4 x K=16 per 64-k chunk; 8 TMEM columns and 32 bytes of smem each
           mma_f16_ts(tmem_d + static_cast<uint32_t>(issuer * 16), tmem_a0 + static_cast<uint32_t>(b * 32 + j * 8),
-                     make_desc(act + j * 32, 16, 1024), idesc, (c >= kTcMmaWarps || j > 0) ? 1u : 0u);
+                     make_desc(act_addr + j * 32, 16, 1024), idesc, (c >= kTcMmaWarps || j > 0) ? 1u : 0u);
         tc_commit(aempty(b));
+        tc_commit(wempty(slot));    // the stage's activations are free once these MMAs have read them
+      } else {
+        mbar_arrive(wempty(slot));
       }
-      tc_commit(dfull);   // arrives once this issuer's MMAs are done (immediately if it had none)
     }
+    if (lane == 0) tc_commit(dfull);   // arrives once this issuer's MMAs are done (immediately if it had none)
   } else {
     // ---------------- dequantisers
     const int quad = warp & 3, sub = warp >> 2;       // sub: which chunk of every stage this warp owns
@@ -465,8 +482,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     const int64_t n = n0 + tid_n;
     const bool n_ok = n < p.n;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    int stage = 0;
-    uint32_t phase = 0;
     uint32_t ephase = 0u;   // one parity bit per buffer
     const int chunks_per_group = static_cast<int>(p.group / 64);
     bool ok = true;
@@ -474,7 +489,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     uint32_t zz = 0x43004300u, ss = 0u;
     // The tensor-memory store of a chunk completes while the next chunk is read and dequantised: the
     // wait for it, and the arrival that hands the chunk to the MMA issuers, come just before the
-    // next store.  The stage is released as soon as its words are in registers.
+    // next store.  The stage's weights are released as soon as its words are in registers.
     int pending_buf = -1;
     auto hand_over = [&]() {
       if (pending_buf < 0) return;
@@ -485,8 +500,10 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       pending_buf = -1;
     };
     for (int s = 0; s < nstages_total && ok; ++s) {
-      if (!mbar_wait(wfull(stage), phase, abort_flag, err)) { ok = false; break; }
-      const uint32_t *st = reinterpret_cast<const uint32_t *>(gen + act_bytes + stage * kTcStageBytes);
+      const int slot = s % nstages;
+      const uint32_t phase = static_cast<uint32_t>(s / nstages) & 1u;
+      if (!mbar_wait_relaxed(wfull(slot), phase, abort_flag, err)) { ok = false; break; }
+      const uint32_t *st = reinterpret_cast<const uint32_t *>(gen + slot * kTcStageBytes);
       const int cs = sub;                             // chunk of the stage this warp owns
       const int c = s * 4 + cs;                       // global chunk
       uint32_t words[8];
@@ -495,8 +512,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         for (int r = 0; r < 8; ++r) words[r] = st[(cs * 8 + r) * kTcCols + tid_n];
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(wempty(stage));
-      if (++stage == kTcStages) { stage = 0; phase ^= 1u; }
+      if (lane == 0) mbar_arrive(wempty(slot));
       if (c < nchunks) {
         const int b = c % kTcABufs;
         const int grp = c / chunks_per_group;
@@ -519,7 +535,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         hand_over();   // the previous chunk's store
         // the buffer must have been drained by the MMAs that read it kTcABufs chunks ago
         if (c >= kTcABufs) {
-          if (!mbar_wait(aempty(b), (ephase >> b) & 1u, abort_flag, err)) { ok = false; }
+          if (!mbar_wait_relaxed(aempty(b), (ephase >> b) & 1u, abort_flag, err)) { ok = false; }
           ephase ^= 1u << b;
           tc_fence_after();
         }
@@ -614,10 +630,18 @@ bool make_weight_tmap(CUtensorMap *map, const uint32_t *qw, int64_t n, int64_t k
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-size_t tc_smem_bytes(int64_t k, int64_t group) {
-  const size_t ngroups = static_cast<size_t>(k / group);
-  return static_cast<size_t>(k / 64) * 2048u + static_cast<size_t>(kTcStages) * kTcStageBytes + ngroups * kTcCols * 2u +
-         ngroups * 64u + 1024u + 512u;
+// activations as a 2-D bf16 tensor [m rows, k]; box = [16 rows x 64 k] (128 bytes per row), 128-byte
+// swizzle: a box lands in the tensor core's K-major layout; rows beyond m read as zeros
+bool make_act_tmap(CUtensorMap *map, const uint16_t *a, int64_t m, int64_t k, int64_t lda) {
+  EncodeFnW4 enc = encode_fn_w4();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(m)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(lda) * 2u};
+  cuuint32_t box[2] = {64u, 16u};
+  cuuint32_t estr[2] = {1u, 1u};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(a), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace
@@ -650,7 +674,7 @@ extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t gr
   // tensor-memory kernel (tcgen05), where the MMA cost does not depend on the rows: legacy mma.sync
   // tiles cost about 32 cycles per SM sub-core on this GPU.  BSIR_W4A16_PATH=m / t forces one of them.
   const char *force = std::getenv("BSIR_W4A16_PATH");
-  const bool tc_ok = fast && device_info().cc_major >= 10 && k <= kTcMaxK && group % 64 == 0 && k % 64 == 0;
+  const bool tc_ok = fast && device_info().cc_major >= 10 && group % 64 == 0 && k % 64 == 0 && tc_layout(k, group).stages >= 2;
   if (!fast) {
     for (int64_t m0 = 0; m0 < m; m0 += 65535) {
       const int64_t mr = m - m0 < 65535 ? m - m0 : 65535;
@@ -660,7 +684,7 @@ extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t gr
     }
     return check_launch("matmul_w4a16");
   }
-  CUtensorMap tw;
+  CUtensorMap tw, ta;
   bool have_map = false;
   for (int64_t m0 = 0; m0 < m; m0 += 16) {
     const bool one_block = m - m0 <= 8;
@@ -668,13 +692,13 @@ extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t gr
     if (force && force[0] == 'm') use_tc = false;
     if (force && force[0] == 't') use_tc = tc_ok;
     if (use_tc && !have_map) {
-      have_map = make_weight_tmap(&tw, p.qw, n, k);
+      have_map = make_weight_tmap(&tw, p.qw, n, k) && make_act_tmap(&ta, p.a, m, k, lda);
       if (!have_map) use_tc = false;
     }
     if (use_tc) {
-      const size_t smem = tc_smem_bytes(k, group);
+      const size_t smem = tc_layout(k, group).bytes;
       cudaFuncSetAttribute(w4a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-      w4a16_tc_kernel<<<static_cast<unsigned>(ceil_div(n, kTcCols)), kTcThreads, smem, st>>>(tw, p, m0, device_error_word());
+      w4a16_tc_kernel<<<static_cast<unsigned>(ceil_div(n, kTcCols)), kTcThreads, smem, st>>>(tw, ta, p, m0, device_error_word());
     } else {
       const unsigned blocks = static_cast<unsigned>(ceil_div(n, 64));
       if (one_block) w4a16_mma_kernel<2, 1><<<blocks, kWarps * 32, 0, st>>>(p, m0);

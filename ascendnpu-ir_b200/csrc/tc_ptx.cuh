@@ -50,6 +50,25 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// The same bounded wait for roles that are not on the critical path: between polls the warp sleeps,
+// so that its spinning does not take issue slots from the warps that compute.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *err) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t spin = 0;; ++spin) {
+    __nanosleep(80);
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 63u) == 63u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > 4000000000LL) {  // about two seconds
+        *abort_flag = 1;
+        if (err) atomicOr(err, static_cast<int>(kErrGemmWait));
+        return false;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
