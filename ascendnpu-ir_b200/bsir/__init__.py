@@ -256,6 +256,34 @@ def copy(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     return out
 
 
+PAD_MODE = {"null": 0, "first_elem": 1, "value": 2}
+ATOMIC_KIND = {"none": 0, "add": 1, "max": 2, "min": 3, "and": 4, "or": 5, "xor": 6, "cas": 7, "xchg": 8, "umax": 9,
+               "umin": 10}
+
+
+def load(x: torch.Tensor, out: torch.Tensor, pad_mode: str = "null", pad_value=None, left_padding_num: int = -1,
+         right_padding_num: int = -1) -> torch.Tensor:
+    """``hivm.hir.load`` with ``pad_mode`` / ``pad_value`` / ``left_padding_num`` / ``right_padding_num``:
+    pads the last dimension of ``x`` into ``out`` (same leading shape, wider last dimension)."""
+    shape = list(x.shape)
+    pv = None
+    if pad_value is not None:
+        pv = torch.tensor([pad_value], dtype=x.dtype).contiguous()     # one element of the dtype, host memory
+    _check(lib().bsir_load(_dt(x), len(shape), _i64arr(shape), _ptr(x), _i64arr(x.stride()), _ptr(out),
+                           _i64arr(out.stride()), C.c_int64(out.shape[-1]), PAD_MODE[pad_mode],
+                           C.c_void_p(pv.data_ptr() if pv is not None else None), C.c_int64(left_padding_num),
+                           C.c_int64(right_padding_num), _stream()))
+    return out
+
+
+def store(x: torch.Tensor, out: torch.Tensor, atomic: str = "none") -> torch.Tensor:
+    """``hivm.hir.store`` with ``atomic = <kind>``: out = out <kind> x (a copy for "none")."""
+    shape = list(x.shape)
+    _check(lib().bsir_store(_dt(x), len(shape), _i64arr(shape), _ptr(x), _i64arr(x.stride()), _ptr(out),
+                            _i64arr(out.stride()), ATOMIC_KIND[atomic], _stream()))
+    return out
+
+
 # ---------------------------------------------------------------------------- reductions
 def _rows(x: torch.Tensor):
     if x.dim() != 2:

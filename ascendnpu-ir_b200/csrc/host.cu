@@ -19,17 +19,19 @@
 namespace bsir {
 
 static thread_local char tl_error[512] = {0};
+static thread_local int32_t tl_status = 0;
 static thread_local cudaStream_t tl_stream = nullptr;
 static std::atomic<long long> g_launches{0};
 
 int32_t fail(int32_t status, const char *fmt, ...) {
+  tl_status = status;
   va_list ap;
   va_start(ap, fmt);
   vsnprintf(tl_error, sizeof(tl_error), fmt, ap);
   va_end(ap);
   return status;
 }
-void clear_error() { tl_error[0] = 0; }
+void clear_error() { tl_error[0] = 0; tl_status = 0; }
 cudaStream_t resolve_stream(void *stream) { return stream ? static_cast<cudaStream_t>(stream) : tl_stream; }
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
@@ -166,6 +168,7 @@ const char *bsir_status_string(int32_t s) {
   }
 }
 const char *bsir_last_error(void) { return tl_error; }
+int32_t bsir_last_status(void) { return tl_status; }
 const char *bsir_version(void) { return "bsir_b200 0.1 (sm_100a)"; }
 
 int32_t bsir_set_stream(void *stream) {

@@ -66,6 +66,9 @@ typedef enum {
 BSIR_API const char *bsir_status_string(int32_t status);
 /* Text of the last error raised on the calling thread ("" if none). */
 BSIR_API const char *bsir_last_error(void);
+/* Status of the calling thread's most recent library call (0 = ok): for callers that use the void
+ * prototypes of BSIR_VOID_ABI and cannot see the return value. */
+BSIR_API int32_t bsir_last_status(void);
 BSIR_API const char *bsir_version(void);
 
 /* Stream used by the B1 symbols and by bsir_launch(..., stream == NULL) on the
@@ -240,6 +243,30 @@ BSIR_API int32_t bsir_cast(int32_t src_dtype, int32_t dst_dtype, int32_t round_m
 BSIR_API int32_t bsir_copy(int32_t dtype, int32_t rank, const int64_t *sizes, const void *src,
                            const int64_t *src_strides, void *dst, const int64_t *dst_strides,
                            void *stream);
+
+/* hivm.hir.load with last-dimension padding (HIVMDMAOps.td:62-155; PadMode values HIVMAttrs.td:388-401).
+ * `src_sizes` are the source's extents (rank 1..3); the destination has the same leading extents and
+ * `dst_last` elements in the last one.  dst[..., 0:left] = pad, then the source row, then `right` pads;
+ * pad = *pad_value (one element of `dtype`, host memory) or the row's first source element.  A padding
+ * given as -1 is deduced from dst_last the way the CPU lowering does (ConvertHIVMToUpstream.cpp:1140-1166);
+ * destination elements beyond left + n + right keep their contents.  BSIR_PAD_NULL is a plain copy. */
+typedef enum bsir_pad_mode { BSIR_PAD_NULL = 0, BSIR_PAD_FIRST_ELEM = 1, BSIR_PAD_VALUE = 2 } bsir_pad_mode;
+BSIR_API int32_t bsir_load(int32_t dtype, int32_t rank, const int64_t *src_sizes, const void *src,
+                           const int64_t *src_strides, void *dst, const int64_t *dst_strides,
+                           int64_t dst_last, int32_t pad_mode, const void *pad_value, int64_t left_pad,
+                           int64_t right_pad, void *stream);
+/* hivm.hir.store (HIVMDMAOps.td:157-200; AtomicKind values HIVMAttrs.td:792-803).  BSIR_ATOMIC_NONE copies
+ * (as the CPU lowering always does, ConvertHIVMToUpstream.cpp:1715); the other kinds combine the
+ * destination with the source through device-wide atomics: f32 add/max/min (max/min propagate NaN),
+ * f16/bf16 add, 32- and 64-bit integers every kind but CAS/XCHG; other combinations are refused. */
+typedef enum bsir_atomic_kind {
+  BSIR_ATOMIC_NONE = 0, BSIR_ATOMIC_ADD = 1, BSIR_ATOMIC_MAX = 2, BSIR_ATOMIC_MIN = 3, BSIR_ATOMIC_AND = 4,
+  BSIR_ATOMIC_OR = 5, BSIR_ATOMIC_XOR = 6, BSIR_ATOMIC_CAS = 7, BSIR_ATOMIC_XCHG = 8, BSIR_ATOMIC_UMAX = 9,
+  BSIR_ATOMIC_UMIN = 10
+} bsir_atomic_kind;
+BSIR_API int32_t bsir_store(int32_t dtype, int32_t rank, const int64_t *sizes, const void *src,
+                            const int64_t *src_strides, void *dst, const int64_t *dst_strides,
+                            int32_t atomic_kind, void *stream);
 
 /* linalg.reduce / hivm.hir.vreduce over the last axis of a [rows, cols] view
  * (Reduction.cpp:101-148).  dst is write-only: dst[r] = reduce(identity, src[r,:]).

@@ -19,6 +19,17 @@
 #ifndef BSIR_B200_CIFACE_H_
 #define BSIR_B200_CIFACE_H_
 
+/* The reference's library functions return void; these return a bsir_status in the integer return
+ * register, which a caller that declared them void simply does not read (the C calling conventions
+ * of x86-64 and AArch64 pass no hidden argument for an int32_t result).  Define BSIR_VOID_ABI before
+ * including bsir_b200.h to get the reference's exact prototypes -- the declarations MLIR emits for
+ * `llvm.emit_c_interface` callees -- and read failures through bsir_last_status() instead. */
+#ifdef BSIR_VOID_ABI
+#define BSIR_CIFACE_RET void
+#else
+#define BSIR_CIFACE_RET int32_t
+#endif
+
 /* C type of a scalar argument of element type <tok>. */
 #define BSIR_SCALAR_float float
 #define BSIR_SCALAR_half uint16_t
@@ -145,44 +156,44 @@
 #define BSIR_MEMREF_T(rank) bsir_memref_##rank##d
 
 #define BSIR_DECL_VV(op, fn, rank, tok)                                                   \
-  BSIR_API int32_t _mlir_ciface_##op##_##rank##d_##tok(BSIR_MEMREF_T(rank) *src0,         \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##op##_##rank##d_##tok(BSIR_MEMREF_T(rank) *src0,         \
       BSIR_MEMREF_T(rank) *src1, BSIR_MEMREF_T(rank) *dst, bsir_memref_1d *tmp_buf);
 #define BSIR_DECL_VS(op, fn, rank, tok)                                                   \
-  BSIR_API int32_t _mlir_ciface_##op##_vs_##rank##d_##tok(BSIR_MEMREF_T(rank) *src0,      \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##op##_vs_##rank##d_##tok(BSIR_MEMREF_T(rank) *src0,      \
       BSIR_SCALAR_##tok scalar, BSIR_MEMREF_T(rank) *dst, bsir_memref_1d *tmp_buf);
 #define BSIR_DECL_SV(op, fn, rank, tok)                                                   \
-  BSIR_API int32_t _mlir_ciface_##op##_sv_##rank##d_##tok(BSIR_SCALAR_##tok scalar,       \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##op##_sv_##rank##d_##tok(BSIR_SCALAR_##tok scalar,       \
       BSIR_MEMREF_T(rank) *src1, BSIR_MEMREF_T(rank) *dst, bsir_memref_1d *tmp_buf);
 #define BSIR_DECL_V(op, fn, rank, tok)                                                    \
-  BSIR_API int32_t _mlir_ciface_##op##_##rank##d_##tok(BSIR_MEMREF_T(rank) *src0,         \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##op##_##rank##d_##tok(BSIR_MEMREF_T(rank) *src0,         \
       BSIR_MEMREF_T(rank) *dst, bsir_memref_1d *tmp_buf);
 #define BSIR_DECL_CAST_MODE(s, d, rank)                                                   \
-  BSIR_API int32_t _mlir_ciface_vcast_##s##_to_##d##_##rank##d_with_mode(                 \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_vcast_##s##_to_##d##_##rank##d_with_mode(                 \
       BSIR_MEMREF_T(rank) *src, BSIR_MEMREF_T(rank) *dst, uint32_t cast_mode);
 #define BSIR_DECL_CAST_OVERFLOW(s, d, rank)                                               \
-  BSIR_API int32_t _mlir_ciface_vcast_##s##_to_##d##_##rank##d_with_overflow(             \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_vcast_##s##_to_##d##_##rank##d_with_overflow(             \
       BSIR_MEMREF_T(rank) *src, BSIR_MEMREF_T(rank) *dst, bsir_memref_1d *tmp,            \
       uint32_t cast_mode);                                                                \
-  BSIR_API int32_t _mlir_ciface_vcast_##s##_to_##d##_##rank##d_with_overflow_no_size_align( \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_vcast_##s##_to_##d##_##rank##d_with_overflow_no_size_align( \
       BSIR_MEMREF_T(rank) *src, BSIR_MEMREF_T(rank) *dst, bsir_memref_1d *tmp,            \
       uint32_t cast_mode);
 #define BSIR_DECL_CAST_TEMP(s, d, rank)                                                   \
-  BSIR_API int32_t _mlir_ciface_vcast_##s##_to_##d##_##rank##d_with_temp(                 \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_vcast_##s##_to_##d##_##rank##d_with_temp(                 \
       BSIR_MEMREF_T(rank) *src, BSIR_MEMREF_T(rank) *dst, bsir_memref_1d *temp,           \
       uint32_t cast_mode);
 /* (a, r) -> (a, 1): src/dst 2-D; (r) -> (1): 1-D; (r, a) -> (1, a): 2-D */
 #define BSIR_DECL_REDUCE(name, kind, tok)                                                 \
-  BSIR_API int32_t _mlir_ciface_##name##_ar_##tok(bsir_memref_2d *src0, bsir_memref_2d *dst, \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##name##_ar_##tok(bsir_memref_2d *src0, bsir_memref_2d *dst, \
       bsir_memref_1d *tmp_buf, BSIR_SCALAR_##tok initvalue);                              \
-  BSIR_API int32_t _mlir_ciface_##name##_r_##tok(bsir_memref_1d *src0, bsir_memref_1d *dst, \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##name##_r_##tok(bsir_memref_1d *src0, bsir_memref_1d *dst, \
       bsir_memref_1d *tmp_buf, BSIR_SCALAR_##tok initvalue);                              \
-  BSIR_API int32_t _mlir_ciface_##name##_ra_##tok(bsir_memref_2d *src0, bsir_memref_2d *dst, \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##name##_ra_##tok(bsir_memref_2d *src0, bsir_memref_2d *dst, \
       bsir_memref_1d *tmp_buf, BSIR_SCALAR_##tok initvalue);
 #define BSIR_DECL_REDUCE_WITH_INDEX(name, kind, left, tok)                                \
-  BSIR_API int32_t _mlir_ciface_##name##_ar_##tok(bsir_memref_2d *src0,                   \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##name##_ar_##tok(bsir_memref_2d *src0,                   \
       bsir_memref_2d *dst_value, bsir_memref_2d *dst_index, bsir_memref_1d *tmp_buf,      \
       BSIR_SCALAR_##tok initvalue);                                                       \
-  BSIR_API int32_t _mlir_ciface_##name##_r_##tok(bsir_memref_1d *src0,                    \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##name##_r_##tok(bsir_memref_1d *src0,                    \
       bsir_memref_1d *dst_value, bsir_memref_1d *dst_index, bsir_memref_1d *tmp_buf,      \
       BSIR_SCALAR_##tok initvalue);
 
@@ -212,9 +223,9 @@ BSIR_FOREACH_REDUCE_WITH_INDEX(BSIR_DECL_REDUCE_WITH_INDEX)
  * variants bishengir/lib/Template/lib/Cube/GlobalMmad.cpp:176-187).  C = A x B, int8 inputs
  * accumulate in int32 and are converted to half with round-to-nearest-even, saturating
  * at the half range. */
-BSIR_API int32_t _mlir_ciface_matmul_Xbias_Xdescale_XtransposeA_XtransposeB_TAint8_t_TBint8_t_TChalf(
+BSIR_API BSIR_CIFACE_RET _mlir_ciface_matmul_Xbias_Xdescale_XtransposeA_XtransposeB_TAint8_t_TBint8_t_TChalf(
     bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_2d *C);
-BSIR_API int32_t _mlir_ciface_matmul_Xbias_Xdescale_XtransposeA_transposeB_TAint8_t_TBint8_t_TChalf(
+BSIR_API BSIR_CIFACE_RET _mlir_ciface_matmul_Xbias_Xdescale_XtransposeA_transposeB_TAint8_t_TBint8_t_TChalf(
     bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_2d *C);
 
 #endif /* BSIR_B200_CIFACE_H_ */

@@ -419,6 +419,64 @@ ORC_API int orc_select(int dt, const uint8_t *cond, int64_t c_stride, const void
   return 0;
 }
 
+/* hivm.hir.load with last-dimension padding, rows x n -> rows x dst_last, contiguous rows
+ * (CPU lowering: bishengir/lib/ExecutionEngine/ConvertHIVMToUpstream.cpp:1102-1269: left padding,
+ * data, right padding, each a subview of the destination; the pad is the given value or the row's
+ * first element; a padding that is not given (-1) is what the destination leaves over).  pad_mode:
+ * 1 = first element, 2 = value.  Elements beyond left + n + right are left as they are. */
+ORC_API int orc_load_pad(int dt, const void *src, int64_t rows, int64_t n, void *dst, int64_t dst_last,
+                         int pad_mode, const void *pad_value, int64_t left, int64_t right) {
+  int sz = dtype_size(dt);
+  if (sz == 0 || (pad_mode != 1 && pad_mode != 2)) return -1;
+  if (right < 0) { if (left < 0) left = 0; right = dst_last - (n + left); }
+  else if (left < 0) left = dst_last - (n + right);
+  if (left < 0 || right < 0 || left + n + right > dst_last) return -2;
+  for (int64_t r = 0; r < rows; r++) {
+    const uint8_t *srow = (const uint8_t *)src + r * n * sz;
+    uint8_t *drow = (uint8_t *)dst + r * dst_last * sz;
+    const uint8_t *pad = (pad_mode == 1 && n > 0) ? srow : (const uint8_t *)pad_value;
+    for (int64_t c = 0; c < left; c++) memcpy(drow + c * sz, pad, (size_t)sz);
+    memcpy(drow + left * sz, srow, (size_t)(n * sz));
+    for (int64_t c = left + n; c < left + n + right; c++) memcpy(drow + c * sz, pad, (size_t)sz);
+  }
+  return 0;
+}
+
+/* hivm.hir.store with an atomic kind (HIVMDMAOps.td:157-200, kinds HIVMAttrs.td:792-803): what the
+ * destination holds after one store, dst = dst <kind> src element by element (a single store has no
+ * contention, so the atomic result is the sequential one).  add on floats rounds once in the element
+ * type; max / min on floats propagate NaN; UMAX / UMIN compare as unsigned. */
+ORC_API int orc_store_atomic(int dt, int kind, const void *src, void *dst, int64_t n) {
+  for (int64_t i = 0; i < n; i++) {
+    if (is_float(dt)) {
+      float a = load_f(dt, dst, i), b = load_f(dt, src, i), r;
+      if (kind == 1) r = a + b;
+      else if (kind == 2) r = maximumf_(a, b);
+      else if (kind == 3) r = minimumf_(a, b);
+      else return -1;
+      store_f(dt, dst, i, r);
+    } else {
+      int64_t a = load_i(dt, dst, i), b = load_i(dt, src, i), r;
+      uint64_t ua = (uint64_t)a, ub = (uint64_t)b;
+      if (int_bits(dt) < 64) { ua &= ((1ull << int_bits(dt)) - 1); ub &= ((1ull << int_bits(dt)) - 1); }
+      int uns = is_unsigned(dt);
+      switch (kind) {
+      case 1: r = (int64_t)((uint64_t)a + (uint64_t)b); break;
+      case 2: r = uns ? (int64_t)(ua > ub ? ua : ub) : (a > b ? a : b); break;
+      case 3: r = uns ? (int64_t)(ua < ub ? ua : ub) : (a < b ? a : b); break;
+      case 4: r = a & b; break;
+      case 5: r = a | b; break;
+      case 6: r = a ^ b; break;
+      case 9: r = (int64_t)(ua > ub ? ua : ub); break;
+      case 10: r = (int64_t)(ua < ub ? ua : ub); break;
+      default: return -1;
+      }
+      store_i(dt, dst, i, wrap_int(dt, r));
+    }
+  }
+  return 0;
+}
+
 /* -------------------------------------------------------------------- cast */
 /* Round a double to an integral double under hfusion.round_mode
  * (HFusionEnums.td:122-141; the constant folder does the same through

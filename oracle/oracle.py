@@ -165,6 +165,25 @@ def select(dt, cond, a, b):
     return out
 
 
+def load_pad(dt, src, dst, pad_mode, pad_value=None, left=-1, right=-1):
+    """hivm.hir.load with padding; ``src`` [rows, n], ``dst`` [rows, dst_last] (initial contents, returned updated)."""
+    src, dst = _c(src, dt), _c(dst, dt).copy()
+    rows, n = (1, src.shape[0]) if src.ndim == 1 else (int(np.prod(src.shape[:-1])), src.shape[-1])
+    pv = _c(np.asarray([0 if pad_value is None else pad_value]).astype(_NP[dt]) if not isinstance(pad_value, np.ndarray) else pad_value, dt)
+    mode = {"first_elem": 1, "value": 2}[pad_mode]
+    _chk(lib().orc_load_pad(dt, _p(src), _i64(rows), _i64(n), _p(dst), _i64(dst.shape[-1]), mode, _p(pv), _i64(left),
+                            _i64(right)), "load_pad")
+    return dst
+
+
+def store_atomic(dt, kind, src, dst):
+    """hivm.hir.store atomic = <kind>: the destination after one store."""
+    kinds = {"add": 1, "max": 2, "min": 3, "and": 4, "or": 5, "xor": 6, "umax": 9, "umin": 10}
+    src, dst = _c(src, dt), _c(dst, dt).copy()
+    _chk(lib().orc_store_atomic(dt, kinds[kind], _p(src), _p(dst), _i64(src.size)), "store_atomic")
+    return dst
+
+
 def cast(src_dt, dst_dt, src, round_mode="rint", overflow="wrap", out=None):
     rm = ROUND[round_mode] if isinstance(round_mode, str) else round_mode
     ov = OVERFLOW[overflow] if isinstance(overflow, str) else overflow

@@ -218,3 +218,63 @@ def test_cast_other_pairs(bsir, src, dst):
     code = lambda d: oracle_dtype(torch.empty(0, dtype=d))
     want = O.cast(code(src), code(dst), to_bits(x), "trunc" if (src.is_floating_point and not dst.is_floating_point) else "rint", "wrap")
     assert_bits_equal(out, want, f"cast {src}->{dst}")
+
+
+# ---------------------------------------------------------------- hivm.hir.load (padding) / hivm.hir.store (atomic)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int8, torch.int64])
+@pytest.mark.parametrize("shape,dst_last,left,right", [((5, 37), 64, -1, -1), ((5, 37), 64, 3, -1), ((5, 37), 64, -1, 7),
+                                                      ((5, 37), 64, 3, 7), ((1000,), 1024, 8, 16), ((3, 4, 100), 128, 28, 0),
+                                                      ((70000, 3), 8, 2, 3)])
+@pytest.mark.parametrize("pad_mode", ["value", "first_elem"])
+def test_load_with_padding(bsir, dtype, shape, dst_last, left, right, pad_mode):
+    """Left / right padding with the paddings given or deduced (reference CPU lowering:
+    ConvertHIVMToUpstream.cpp:1140-1166), value or first-element pad, untouched tail."""
+    x = _rand(shape, dtype, seed=sum(shape) + dst_last)
+    out = _rand(shape[:-1] + (dst_last,), dtype, seed=1)          # recognisable initial contents
+    before = out.clone()
+    pv = 3 if not dtype.is_floating_point else 2.5
+    bsir.load(x, out, pad_mode=pad_mode, pad_value=pv, left_padding_num=left, right_padding_num=right)
+    want = O.load_pad(oracle_dtype(x), to_bits(x), to_bits(before), pad_mode, to_bits(torch.tensor([pv], dtype=dtype)),
+                      left, right)
+    assert_bits_equal(out, want.reshape(out.shape), f"load {pad_mode} {shape}->{dst_last} l={left} r={right}")
+
+
+def test_load_plain_and_errors(bsir):
+    x = _rand((7, 33), torch.float16, seed=2)
+    out = torch.empty_like(x)
+    bsir.load(x, out)                                            # no pad_mode: shapes must match, plain copy
+    assert torch.equal(out, x)
+    with pytest.raises(bsir.BsirError):
+        bsir.load(x, torch.empty(7, 40, dtype=torch.float16, device="cuda"))            # pad needed but no pad_mode
+    with pytest.raises(bsir.BsirError):
+        bsir.load(x, torch.empty(7, 40, dtype=torch.float16, device="cuda"), pad_mode="value", pad_value=0.0,
+                  left_padding_num=5, right_padding_num=5)                               # 5 + 33 + 5 > 40
+
+
+@pytest.mark.parametrize("dtype,kinds", [(torch.float32, ["add", "max", "min"]), (torch.float16, ["add"]), (torch.bfloat16, ["add"]),
+                                         (torch.int32, ["add", "max", "min", "and", "or", "xor", "umax", "umin"]),
+                                         (torch.int64, ["add", "max", "min", "and", "or", "xor", "umax", "umin"])])
+def test_store_atomic_kinds(bsir, dtype, kinds):
+    for kind in kinds:
+        src = _rand((9, 1000), dtype, seed=3)
+        dst = _rand((9, 1000), dtype, seed=4)
+        if dtype == torch.float32:
+            src[0, 5] = float("nan")
+            dst[1, 6] = float("nan")
+        before = dst.clone()
+        bsir.store(src, dst, atomic=kind)
+        want = O.store_atomic(oracle_dtype(src), kind, to_bits(src), to_bits(before))
+        assert_bits_equal(dst, want.reshape(dst.shape), f"store atomic={kind} {dtype}")
+    out = torch.zeros(9, 1000, dtype=dtype, device="cuda")
+    bsir.store(src, out)                                         # atomic none: a copy
+    assert torch.equal(out.view(torch.uint8), src.view(torch.uint8))
+    with pytest.raises(bsir.BsirError):
+        bsir.store(src, out, atomic="cas")
+
+
+def test_store_atomic_adds_up_over_calls(bsir):
+    acc = torch.zeros(4, 257, dtype=torch.int32, device="cuda")
+    parts = [torch.randint(-100, 100, (4, 257), dtype=torch.int32, device="cuda") for _ in range(5)]
+    for p in parts:
+        bsir.store(p, acc, atomic="add")
+    assert torch.equal(acc, sum(parts))
