@@ -236,6 +236,15 @@ def select(cond: torch.Tensor, a, b) -> torch.Tensor:
     return out
 
 
+def default_round_mode(src: torch.dtype, dst: torch.dtype) -> str:
+    """The round mode the reference picks for a conversion that names none (``selectRoundMode``,
+    bishengir/include/bishengir/Dialect/Utils/Util.h:180-213): float -> integer truncates, everything else rounds
+    to nearest even."""
+    if src.is_floating_point and not dst.is_floating_point:
+        return "trunc"
+    return "rint"
+
+
 def cast(x: torch.Tensor, dtype: torch.dtype, round_mode: str = "rint", enable_saturate: bool = False,
          overflow_mode: Optional[str] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``hfusion.cast`` {round_mode, enable_saturate}; ``overflow_mode`` selects a named variant."""
