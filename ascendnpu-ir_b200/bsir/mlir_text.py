@@ -1,0 +1,372 @@
+"""A small front end for the MLIR assembly of the hot-path ops: it reads a `func.func` written the way the
+reference's tests write them (HFusion / linalg named ops on tensors, HIVM ops on memrefs, the scalar `arith`
+ops around them) and runs it op by op through the CUDA library.
+
+    fn = parse(open("rms_norm.mlir").read())["rms_norm_f16"]
+    y, rstd = fn(x, gamma, out0, out1)            # torch CUDA tensors in the order of the signature
+
+Covered (attribute spellings as in the reference):
+  hfusion.cast {round_mode | mode = #hfusion.round_mode<..>, enable_saturate, overflow_mode}      HFusionNamedStructuredOps.yaml:373-432
+  hfusion.elemwise_unary / elemwise_binary {fun = #hfusion.unary_fn<..>}, linalg.elemwise_unary / elemwise_binary
+  hfusion.compare {compare_fn = #hfusion.compare_fn<..>}, hfusion.select, hfusion.isnan
+  hfusion.reduce_with_index {tie_break_left} <max|min>
+  linalg.fill, linalg.broadcast dimensions = [..], linalg.reduce {arith.<combiner>} dimensions = [k] (short form and a
+  region with one combiner op), linalg.matmul (i8 x i8 -> i32), linalg.copy
+  hivm.hir.load (pad_mode / pad_value / left_padding_num / right_padding_num), hivm.hir.store (atomic = <kind>),
+  hivm.hir.copy, hivm.hir.vadd / vsub / vmul / vdiv / vmax / vmin, hivm.hir.vcast, hivm.hir.vreduce <kind>
+  tensor.empty, tensor.dim, memref.alloc, arith.constant (scalars, splat `dense<..>`), arith.{addf,subf,mulf,divf,addi,subi,muli},
+  arith.{index_cast,index_castui,uitofp,sitofp,extf,truncf}, return
+Scalar arithmetic is done in the scalar's own type (f32 ops round to f32).  Anything else raises MlirTextError
+with the op's name, so an unsupported file fails loudly instead of computing something different.
+"""
+import re
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+__all__ = ["parse", "Function", "MlirTextError"]
+
+
+class MlirTextError(ValueError):
+    pass
+
+
+_TORCH_NAMES = {"f32": "float32", "f16": "float16", "bf16": "bfloat16", "i8": "int8", "i16": "int16", "i32": "int32",
+                "i64": "int64", "i1": "bool", "ui8": "uint8", "index": "int64"}
+_REDUCE_COMBINERS = {"arith.addf": "sum", "arith.addi": "sum", "arith.mulf": "prod", "arith.muli": "prod",
+                     "arith.maximumf": "max", "arith.maxsi": "max", "arith.minimumf": "min", "arith.minsi": "min",
+                     "arith.ori": "ori", "arith.andi": "andi", "arith.xori": "xori"}
+_HIVM_BINARY = {"vadd": "add", "vsub": "sub", "vmul": "mul", "vdiv": "div", "vmax": "maxf", "vmin": "minf"}
+_LINALG_UNARY = {"exp", "log", "abs", "ceil", "floor", "negf", "reciprocal", "round", "sqrt", "rsqrt", "square", "tanh", "erf"}
+
+
+class ShapedType:
+    def __init__(self, text: str):
+        m = re.match(r"(tensor|memref)<(.*)>$", text.strip(), re.S)
+        if not m:
+            raise MlirTextError(f"not a tensor/memref type: {text}")
+        inner = m.group(2).split(",")[0].strip()          # drops the memory space of a memref
+        parts = inner.split("x")
+        self.elem = parts[-1]
+        self.shape = []
+        for p in parts[:-1]:
+            if p == "?":
+                raise MlirTextError("dynamic shapes are not supported by this front end")
+            self.shape.append(int(p))
+        if self.elem not in _TORCH_NAMES:
+            raise MlirTextError(f"element type {self.elem}")
+
+
+class Scalar:
+    """An SSA scalar: a value and its MLIR type (f32 / i32 / index ...)."""
+
+    def __init__(self, value, ty: str):
+        self.ty = ty
+        if ty == "f32":
+            self.value = float(np.float32(value))
+        elif ty in ("f16", "bf16", "f64"):
+            self.value = float(value)
+        else:
+            self.value = int(value)
+
+
+def _strip_comments(text: str) -> str:
+    return "\n".join(line.split("//", 1)[0] for line in text.split("\n"))
+
+
+def _split_top(text: str, sep: str = ",") -> List[str]:
+    """Splits at `sep` outside any brackets."""
+    out, depth, cur = [], 0, ""
+    for ch in text:
+        if ch in "([{<":
+            depth += 1
+        elif ch in ")]}>":
+            depth -= 1
+        if ch == sep and depth == 0:
+            out.append(cur.strip())
+            cur = ""
+        else:
+            cur += ch
+    if cur.strip():
+        out.append(cur.strip())
+    return out
+
+
+def _balanced(text: str, start: int, open_ch: str, close_ch: str) -> int:
+    """Index just past the bracket group that opens at `start`."""
+    depth = 0
+    for i in range(start, len(text)):
+        if text[i] == open_ch:
+            depth += 1
+        elif text[i] == close_ch:
+            depth -= 1
+            if depth == 0:
+                return i + 1
+    raise MlirTextError("unbalanced brackets")
+
+
+class Op:
+    def __init__(self, results: List[str], name: str, text: str):
+        self.results, self.name, self.text = results, name, text
+
+    # ins(%a, %b : t1, t2)  ->  (["%a", "%b"], ["t1", "t2"])
+    def group(self, key: str):
+        m = re.search(rf"\b{key}\s*\(", self.text)
+        if not m:
+            return [], []
+        end = _balanced(self.text, m.end() - 1, "(", ")")
+        inner = self.text[m.end():end - 1]
+        if ":" not in inner:
+            return [], []
+        names, types = inner.split(":", 1)
+        return [n.strip() for n in _split_top(names)], _split_top(types)
+
+    def attr(self, key: str, default=None):
+        m = re.search(rf"\b{key}\s*=\s*(#[\w.]+<(\w+)>|true|false|-?[\d.eE+-]+|\"[^\"]*\")", self.text)
+        if not m:
+            return default
+        if m.group(2):
+            return m.group(2)
+        v = m.group(1)
+        return {"true": True, "false": False}.get(v, v.strip('"'))
+
+    def int_list(self, key: str) -> Optional[List[int]]:
+        m = re.search(rf"\b{key}\s*=\s*\[([^\]]*)\]", self.text)
+        if not m:
+            m = re.search(rf"\b{key}\s*=\s*array<i64(?::\s*([^>]*))?>", self.text)
+            if not m:
+                return None
+        body = (m.group(1) or "").strip()
+        return [int(v) for v in body.split(",")] if body else []
+
+
+_OP_START = re.compile(r"(?:(?P<res>%[\w.#:]+(?:\s*,\s*%[\w.#:]+)*)\s*=\s*)?(?P<name>(?:[a-z_][\w]*\.)+[a-z_][\w]*|return)\b")
+
+
+def _statements(body: str) -> List[Op]:
+    """Cuts a function body into ops.  An op starts at `[%r =] dialect.name` at bracket depth 0."""
+    ops, depth, i, starts = [], 0, 0, []
+    n = len(body)
+    while i < n:
+        ch = body[i]
+        if ch in "([{":
+            depth += 1
+        elif ch in ")]}":
+            depth -= 1
+        elif ch == "<" and i > 0 and (body[i - 1].isalnum() or body[i - 1] in "_."):
+            end = _balanced(body, i, "<", ">")             # a type or attribute parameter list: skip as a whole
+            i = end
+            continue
+        if depth == 0 and (i == 0 or body[i - 1] in " \n\t"):
+            m = _OP_START.match(body, i)
+            if m and (m.group("res") or "." in m.group("name") or m.group("name") == "return"):
+                # names inside `ins(... : ...)` never match here because depth > 0 there
+                starts.append((i, m))
+                i = m.end()
+                continue
+        i += 1
+    for k, (pos, m) in enumerate(starts):
+        end = starts[k + 1][0] if k + 1 < len(starts) else n
+        res = [r.strip().split(":")[0] for r in m.group("res").split(",")] if m.group("res") else []
+        ops.append(Op(res, m.group("name"), body[m.end():end].strip()))
+    return ops
+
+
+class Function:
+    def __init__(self, name: str, args: List[tuple], ops: List[Op]):
+        self.name, self.args, self.ops = name, args, ops
+
+    def op_names(self) -> List[str]:
+        return [o.name for o in self.ops]
+
+    # ------------------------------------------------------------------ execution
+    def __call__(self, *tensors):
+        import torch
+        from . import (cast, compare, copy, elemwise_binary, elemwise_unary, load, matmul_w8a8, reduce, reduce_with_index,
+                       select, store)
+        if len(tensors) != len(self.args):
+            raise MlirTextError(f"@{self.name} takes {len(self.args)} arguments, got {len(tensors)}")
+        env: Dict[str, object] = {}
+        for (name, ty), t in zip(self.args, tensors):
+            if ty.startswith(("tensor", "memref")):
+                st = ShapedType(ty)
+                if list(t.shape) != st.shape or str(t.dtype) != "torch." + _TORCH_NAMES[st.elem]:
+                    raise MlirTextError(f"argument {name}: expected {ty}, got {tuple(t.shape)} {t.dtype}")
+                env[name] = t
+            else:
+                env[name] = Scalar(t, ty)
+        dev = next((t.device for t in tensors if isinstance(t, torch.Tensor)), torch.device("cuda"))
+
+        def tdtype(elem):
+            return getattr(torch, _TORCH_NAMES[elem])
+
+        def val(name):
+            if name not in env:
+                raise MlirTextError(f"use of undefined value {name}")
+            return env[name]
+
+        def operand(name):
+            v = val(name)
+            return v.value if isinstance(v, Scalar) else v
+
+        def define(op, values):
+            if len(op.results) > len(values):
+                raise MlirTextError(f"{op.name}: {len(op.results)} results, {len(values)} produced")
+            for r, v in zip(op.results, values):
+                env[r] = v
+
+        def write_out(dst, src):
+            """Destination-style result: the value lands in the outs buffer."""
+            if dst.data_ptr() != src.data_ptr():
+                copy(src, out=dst)
+            return dst
+
+        for op in self.ops:
+            name = op.name
+            ins, in_types = op.group("ins")
+            outs, out_types = op.group("outs")
+            if name == "return" or name == "func.return":
+                names = [n.strip() for n in _split_top(op.text.split(":")[0])] if op.text.strip() else []
+                res = tuple(operand(n) for n in names)
+                return res[0] if len(res) == 1 else (res if res else None)
+            if name == "arith.constant":
+                m = re.match(r"\s*dense<([^>]+)>\s*:\s*(.+)$", op.text, re.S)
+                if m:
+                    st = ShapedType(m.group(2))
+                    define(op, [torch.full(st.shape, float(m.group(1)), dtype=tdtype(st.elem), device=dev)])
+                else:
+                    v, ty = op.text.rsplit(":", 1)
+                    v = v.strip()
+                    define(op, [Scalar({"true": 1, "false": 0}.get(v, v) if ty.strip() in ("i1",) else float(v) if ty.strip().startswith("f") else int(float(v)), ty.strip())])
+            elif name in ("arith.addf", "arith.subf", "arith.mulf", "arith.divf", "arith.addi", "arith.subi", "arith.muli"):
+                a, b = [val(n.strip()) for n in _split_top(op.text.split(":")[0])]
+                ty = op.text.rsplit(":", 1)[1].strip()
+                f = {"add": lambda x, y: x + y, "sub": lambda x, y: x - y, "mul": lambda x, y: x * y, "div": lambda x, y: x / y}[name[6:9]]
+                if ty == "f32":
+                    define(op, [Scalar(f(np.float32(a.value), np.float32(b.value)), ty)])
+                else:
+                    define(op, [Scalar(f(a.value, b.value), ty)])
+            elif name in ("arith.index_cast", "arith.index_castui", "arith.uitofp", "arith.sitofp", "arith.extf", "arith.truncf",
+                          "arith.extsi", "arith.extui", "arith.trunci"):
+                src = val(op.text.split(":")[0].strip())
+                ty = op.text.rsplit(" to ", 1)[1].strip()
+                define(op, [Scalar(src.value, ty)])
+            elif name in ("tensor.empty", "memref.alloc"):
+                st = ShapedType(op.text.split(":", 1)[1])
+                define(op, [torch.empty(st.shape, dtype=tdtype(st.elem), device=dev)])
+            elif name == "tensor.dim":
+                t_name, i_name = [n.strip() for n in _split_top(op.text.split(":")[0])]
+                define(op, [Scalar(val(t_name).shape[val(i_name).value], "index")])
+            elif name == "hfusion.cast" or name == "hivm.hir.vcast":
+                dst = val(outs[0])
+                mode = op.attr("round_mode") or op.attr("mode") or "rint"
+                ov = op.attr("overflow_mode")
+                y = cast(val(ins[0]), dst.dtype, round_mode=mode, enable_saturate=bool(op.attr("enable_saturate", False)),
+                         overflow_mode=ov if isinstance(ov, str) and ov in ("saturate", "wrap") else None, out=dst)
+                define(op, [y])
+            elif name in ("linalg.elemwise_unary", "hfusion.elemwise_unary"):
+                fun = op.attr("fun") or "exp"
+                if name.startswith("linalg") and fun not in _LINALG_UNARY:
+                    raise MlirTextError(f"linalg.elemwise_unary fun {fun}")
+                define(op, [elemwise_unary(fun, val(ins[0]), out=val(outs[0]))])
+            elif name in ("linalg.elemwise_binary", "hfusion.elemwise_binary"):
+                fun = op.attr("fun") or "add"
+                define(op, [elemwise_binary(fun, operand(ins[0]), operand(ins[1]), out=val(outs[0]))])
+            elif name.startswith("hivm.hir.") and name[9:] in _HIVM_BINARY:
+                define(op, [elemwise_binary(_HIVM_BINARY[name[9:]], operand(ins[0]), operand(ins[1]), out=val(outs[0]))])
+            elif name == "hfusion.compare":
+                define(op, [write_out(val(outs[0]), compare(op.attr("compare_fn") or "veq", operand(ins[0]), operand(ins[1])))])
+            elif name == "hfusion.isnan":
+                x = val(op.text.split(":")[0].strip())
+                define(op, [compare("vne", x, x)])
+            elif name == "hfusion.select":
+                define(op, [write_out(val(outs[0]), select(val(ins[0]), operand(ins[1]), operand(ins[2])))])
+            elif name == "linalg.fill":
+                dst = val(outs[0])
+                define(op, [elemwise_binary("add", torch.zeros_like(dst), operand(ins[0]), out=dst)
+                            if dst.dtype.is_floating_point or dst.dtype != torch.bool else dst.fill_(bool(operand(ins[0])))])
+            elif name == "linalg.broadcast":
+                src, dst = val(ins[0]), val(outs[0])
+                dims = op.int_list("dimensions") or []
+                view = src
+                for d in sorted(dims):
+                    view = view.unsqueeze(d)
+                define(op, [copy(view.expand(dst.shape), out=dst)])
+            elif name in ("linalg.copy", "hivm.hir.copy"):
+                define(op, [copy(val(ins[0]), out=val(outs[0]))])
+            elif name == "hivm.hir.load":
+                pm = op.attr("pad_mode")
+                if pm is None:
+                    define(op, [copy(val(ins[0]), out=val(outs[0]))])
+                else:
+                    pv = re.search(r"pad_value\s*=\s*(%[\w.]+)", op.text)
+                    lp = re.search(r"left_padding_num\s*=\s*(%[\w.]+)", op.text)
+                    rp = re.search(r"right_padding_num\s*=\s*(%[\w.]+)", op.text)
+                    define(op, [load(val(ins[0]), val(outs[0]), pad_mode={"PadValue": "value", "PadFirstElem": "first_elem", "PadNull": "null"}[pm],
+                                     pad_value=operand(pv.group(1)) if pv else None,
+                                     left_padding_num=operand(lp.group(1)) if lp else -1,
+                                     right_padding_num=operand(rp.group(1)) if rp else -1)])
+            elif name == "hivm.hir.store":
+                m = re.search(r"atomic\s*=\s*<(\w+)>", op.text)
+                define(op, [store(val(ins[0]), val(outs[0]), atomic=m.group(1) if m else "none")])
+            elif name == "linalg.reduce" or name == "hivm.hir.vreduce":
+                src, dst = val(ins[0]), val(outs[0])
+                if name == "linalg.reduce":
+                    comb = next((c for c in _REDUCE_COMBINERS if re.search(rf"\b{re.escape(c)}\b", op.text)), None)
+                    if comb is None:
+                        raise MlirTextError("linalg.reduce: combiner not recognised")
+                    kind = _REDUCE_COMBINERS[comb]
+                    dims = op.int_list("dimensions")
+                else:
+                    kind = re.search(r"<(\w+)>", op.text).group(1)
+                    dims = op.int_list("reduce_dims")
+                if src.dim() != 2 or dims not in ([0], [1]):
+                    raise MlirTextError(f"{name}: a 2-D source reduced over one axis is supported, got rank {src.dim()} dims {dims}")
+                define(op, [write_out(dst.view(-1) if dst.dim() != 1 else dst, reduce(kind, src, dim=dims[0])).view(dst.shape)])
+            elif name == "hfusion.reduce_with_index":
+                kind = re.search(r"<(max|min)>", op.text).group(1)
+                v, i = reduce_with_index(kind, val(ins[0]), tie_break_left=bool(op.attr("tie_break_left", True)))
+                define(op, [write_out(val(outs[0]), v), write_out(val(outs[1]), i)])
+            elif name == "linalg.matmul":
+                a, b, c = val(ins[0]), val(ins[1]), val(outs[0])
+                if a.dtype != torch.int8 or c.dtype != torch.int32:
+                    raise MlirTextError("linalg.matmul: i8 x i8 -> i32 is supported")
+                _, acc = matmul_w8a8(a, b, want_acc=True)
+                define(op, [write_out(c, acc)])
+            else:
+                raise MlirTextError(f"op {name} is not supported by this front end")
+        return None
+
+
+def parse(text: str) -> Dict[str, Function]:
+    """All `func.func`s of a module, by name."""
+    text = _strip_comments(text)
+    fns: Dict[str, Function] = {}
+    for m in re.finditer(r"func\.func\s+(?:private\s+)?@([\w.]+)\s*\(", text):
+        args_end = _balanced(text, m.end() - 1, "(", ")")
+        arg_text = text[m.end():args_end - 1]
+        args = []
+        for a in _split_top(arg_text):
+            if not a:
+                continue
+            nm, ty = a.split(":", 1)
+            args.append((nm.strip(), re.sub(r"\{[^}]*\}\s*$", "", ty).strip()))
+        brace = text.find("{", args_end)
+        # skip `attributes {...}` dictionaries: the body is the last brace group that follows the signature
+        while True:
+            head = text[args_end:brace]
+            end = _balanced(text, brace, "{", "}")
+            if re.search(r"attributes\s*$", head):
+                args_end = end
+                brace = text.find("{", end)
+                if brace < 0:
+                    break
+                continue
+            break
+        if brace < 0:
+            continue                                   # a declaration
+        body = text[brace + 1:end - 1]
+        fns[m.group(1)] = Function(m.group(1), args, _statements(body))
+    if not fns:
+        raise MlirTextError("no func.func found")
+    return fns

@@ -1,0 +1,225 @@
+"""The MLIR-assembly front end (bsir/mlir_text.py): parsing on CPU, execution through the CUDA library on GPU.
+The IR below is written for these tests in the reference's syntax (generic `ins(...) outs(...)` form, attribute
+spellings of HFusionNamedStructuredOps.yaml / HIVMDMAOps.td)."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle as O
+
+QUANT_IR = """
+// per-token int8 quantisation as the composition of hot-path ops
+module {
+func.func @quant(%x: tensor<64x512xbf16>, %q_out: tensor<64x512xi8>, %scale_out: tensor<64xf32>)
+    -> (tensor<64x512xi8>, tensor<64xf32>) attributes {hacc.entry} {
+  %e0 = tensor.empty() : tensor<64x512xf32>
+  %x32 = hfusion.cast {round_mode = #hfusion.round_mode<rint>} ins(%x : tensor<64x512xbf16>) outs(%e0 : tensor<64x512xf32>) -> tensor<64x512xf32>
+  %e1 = tensor.empty() : tensor<64x512xf32>
+  %ax = linalg.elemwise_unary {fun = #linalg.unary_fn<abs>} ins(%x32 : tensor<64x512xf32>) outs(%e1 : tensor<64x512xf32>) -> tensor<64x512xf32>
+  %amax = linalg.reduce { arith.maximumf } ins(%ax : tensor<64x512xf32>) outs(%scale_out : tensor<64xf32>) dimensions = [1]
+  %c127 = arith.constant 1.270000e+02 : f32
+  %e2 = tensor.empty() : tensor<64xf32>
+  %scale = linalg.elemwise_binary {fun = #linalg.binary_fn<div>} ins(%amax, %c127 : tensor<64xf32>, f32) outs(%e2 : tensor<64xf32>) -> tensor<64xf32>
+  %e3 = tensor.empty() : tensor<64x512xf32>
+  %brc = linalg.broadcast ins(%scale : tensor<64xf32>) outs(%e3 : tensor<64x512xf32>) dimensions = [1]
+  %e4 = tensor.empty() : tensor<64x512xf32>
+  %y = linalg.elemwise_binary {fun = #linalg.binary_fn<div>} ins(%x32, %brc : tensor<64x512xf32>, tensor<64x512xf32>)
+         outs(%e4 : tensor<64x512xf32>) -> tensor<64x512xf32>
+  %q = hfusion.cast {round_mode = #hfusion.round_mode<rint>, enable_saturate = true}
+         ins(%y : tensor<64x512xf32>) outs(%q_out : tensor<64x512xi8>) -> tensor<64x512xi8>
+  return %q, %scale : tensor<64x512xi8>, tensor<64xf32>
+}
+}
+"""
+
+VEC_IR = """
+func.func @axpy(%a: memref<1000xf32, #hivm.address_space<gm>>, %b: memref<1000xf32, #hivm.address_space<gm>>,
+                %out: memref<1024xf32, #hivm.address_space<gm>>) attributes {hacc.entry, hacc.function_kind = #hacc.function_kind<DEVICE>} {
+  %ua = memref.alloc() : memref<1000xf32, #hivm.address_space<ub>>
+  hivm.hir.load ins(%a : memref<1000xf32, #hivm.address_space<gm>>) outs(%ua : memref<1000xf32, #hivm.address_space<ub>>)
+  %ub = memref.alloc() : memref<1000xf32, #hivm.address_space<ub>>
+  hivm.hir.load ins(%b : memref<1000xf32, #hivm.address_space<gm>>) outs(%ub : memref<1000xf32, #hivm.address_space<ub>>)
+  %t = memref.alloc() : memref<1000xf32, #hivm.address_space<ub>>
+  hivm.hir.vmul ins(%ua, %ub : memref<1000xf32, #hivm.address_space<ub>>, memref<1000xf32, #hivm.address_space<ub>>) outs(%t : memref<1000xf32, #hivm.address_space<ub>>)
+  %s = memref.alloc() : memref<1000xf32, #hivm.address_space<ub>>
+  hivm.hir.vadd ins(%t, %ua : memref<1000xf32, #hivm.address_space<ub>>, memref<1000xf32, #hivm.address_space<ub>>) outs(%s : memref<1000xf32, #hivm.address_space<ub>>)
+  %pad = arith.constant 7.500000e+00 : f32
+  %c8 = arith.constant 8 : index
+  %p = memref.alloc() : memref<1024xf32, #hivm.address_space<ub>>
+  hivm.hir.load ins(%s : memref<1000xf32, #hivm.address_space<ub>>) outs(%p : memref<1024xf32, #hivm.address_space<ub>>)
+      pad_mode = #hivm.padmode<PadValue> pad_value = %pad : f32 left_padding_num = %c8 : index
+  hivm.hir.store ins(%p : memref<1024xf32, #hivm.address_space<ub>>) outs(%out : memref<1024xf32, #hivm.address_space<gm>>) atomic = <add>
+  return
+}
+"""
+
+ARGMAX_IR = """
+func.func @pick(%x: tensor<8x4096xf32>, %v0: tensor<8xf32>, %i0: tensor<8xi32>, %lo: tensor<8x4096xf32>) -> (tensor<8xf32>, tensor<8xi32>, tensor<8x4096xf32>) {
+  %v, %i = hfusion.reduce_with_index {tie_break_left = true} <max> ins(%x : tensor<8x4096xf32>) outs(%v0, %i0 : tensor<8xf32>, tensor<8xi32>) dimensions = [1] -> tensor<8xf32>, tensor<8xi32>
+  %zero = arith.constant 0.000000e+00 : f32
+  %m0 = tensor.empty() : tensor<8x4096xi1>
+  %mask = hfusion.compare {compare_fn = #hfusion.compare_fn<vlt>} ins(%x, %zero : tensor<8x4096xf32>, f32) outs(%m0 : tensor<8x4096xi1>) -> tensor<8x4096xi1>
+  %r = hfusion.select ins(%mask, %zero, %x : tensor<8x4096xi1>, f32, tensor<8x4096xf32>) outs(%lo : tensor<8x4096xf32>) -> tensor<8x4096xf32>
+  return %v, %i, %r : tensor<8xf32>, tensor<8xi32>, tensor<8x4096xf32>
+}
+"""
+
+
+RMS_IR = """
+func.func @rms(%x: tensor<40x512xf16>, %gamma: tensor<512xf16>, %out0: tensor<40x512xf16>, %out1: tensor<40xf16>)
+      -> (tensor<40x512xf16>, tensor<40xf16>) attributes {hfusion.fusion_kind = #hfusion.fusion_kind<LAST_AXIS_PBR>} {
+  %c1 = arith.constant 1 : index
+  %t0 = tensor.empty() : tensor<40x512xf32>
+  %x32 = hfusion.cast {round_mode = #hfusion.round_mode<rint>} ins(%x : tensor<40x512xf16>) outs(%t0 : tensor<40x512xf32>) -> tensor<40x512xf32>
+  %t1 = tensor.empty() : tensor<512xf32>
+  %g32 = hfusion.cast {round_mode = #hfusion.round_mode<rint>} ins(%gamma : tensor<512xf16>) outs(%t1 : tensor<512xf32>) -> tensor<512xf32>
+  %d = tensor.dim %x32, %c1 : tensor<40x512xf32>
+  %eps = arith.constant 1.000000e-06 : f32
+  %t2 = tensor.empty() : tensor<40x512xf32>
+  %sq = linalg.elemwise_binary {fun = #linalg.binary_fn<mul>} ins(%x32, %x32 : tensor<40x512xf32>, tensor<40x512xf32>) outs(%t2 : tensor<40x512xf32>) -> tensor<40x512xf32>
+  %t3 = tensor.empty() : tensor<40xf32>
+  %ss = linalg.reduce { arith.addf } ins(%sq : tensor<40x512xf32>) outs(%t3 : tensor<40xf32>) dimensions = [1]
+  %one = arith.constant 1.0 : f32
+  %di = arith.index_castui %d : index to i32
+  %df = arith.uitofp %di : i32 to f32
+  %inv = arith.divf %one, %df : f32
+  %t4 = tensor.empty() : tensor<40xf32>
+  %mean = linalg.elemwise_binary {fun = #linalg.binary_fn<mul>} ins(%ss, %inv : tensor<40xf32>, f32) outs(%t4 : tensor<40xf32>) -> tensor<40xf32>
+  %t5 = tensor.empty() : tensor<40xf32>
+  %v = linalg.elemwise_binary {fun = #linalg.binary_fn<add>} ins(%mean, %eps : tensor<40xf32>, f32) outs(%t5 : tensor<40xf32>) -> tensor<40xf32>
+  %t6 = tensor.empty() : tensor<40xf32>
+  %sd = hfusion.elemwise_unary {fun = #hfusion.unary_fn<sqrt>} ins(%v : tensor<40xf32>) outs(%t6 : tensor<40xf32>) -> tensor<40xf32>
+  %t7 = tensor.empty() : tensor<40xf32>
+  %r = hfusion.elemwise_unary {fun = #hfusion.unary_fn<rec>} ins(%sd : tensor<40xf32>) outs(%t7 : tensor<40xf32>) -> tensor<40xf32>
+  %t8 = tensor.empty() : tensor<40x512xf32>
+  %rb = linalg.broadcast ins(%r : tensor<40xf32>) outs(%t8 : tensor<40x512xf32>) dimensions = [1]
+  %t9 = tensor.empty() : tensor<40x512xf32>
+  %xn = linalg.elemwise_binary {fun = #linalg.binary_fn<mul>} ins(%rb, %x32 : tensor<40x512xf32>, tensor<40x512xf32>) outs(%t9 : tensor<40x512xf32>) -> tensor<40x512xf32>
+  %t10 = tensor.empty() : tensor<40x512xf32>
+  %gb = linalg.broadcast ins(%g32 : tensor<512xf32>) outs(%t10 : tensor<40x512xf32>) dimensions = [0]
+  %t11 = tensor.empty() : tensor<40x512xf32>
+  %y32 = linalg.elemwise_binary {fun = #linalg.binary_fn<mul>} ins(%gb, %xn : tensor<40x512xf32>, tensor<40x512xf32>) outs(%t11 : tensor<40x512xf32>) -> tensor<40x512xf32>
+  %y = hfusion.cast {round_mode = #hfusion.round_mode<rint>} ins(%y32 : tensor<40x512xf32>) outs(%out0 : tensor<40x512xf16>) -> tensor<40x512xf16>
+  %rs = hfusion.cast {round_mode = #hfusion.round_mode<rint>} ins(%r : tensor<40xf32>) outs(%out1 : tensor<40xf16>) -> tensor<40xf16>
+  return %y, %rs : tensor<40x512xf16>, tensor<40xf16>
+}
+"""
+
+
+def _mlir_text():
+    import importlib.util
+    here = os.path.dirname(os.path.abspath(__file__))
+    path = os.path.join(here, "..", "ascendnpu-ir_b200", "bsir", "mlir_text.py")
+    spec = importlib.util.spec_from_file_location("bsir_mlir_text_standalone", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_parser_splits_ops_and_attributes():
+    M = _mlir_text()
+    fn = M.parse(QUANT_IR)["quant"]
+    assert [a[0] for a in fn.args] == ["%x", "%q_out", "%scale_out"]
+    assert fn.op_names() == ["tensor.empty", "hfusion.cast", "tensor.empty", "linalg.elemwise_unary", "linalg.reduce",
+                             "arith.constant", "tensor.empty", "linalg.elemwise_binary", "tensor.empty", "linalg.broadcast",
+                             "tensor.empty", "linalg.elemwise_binary", "hfusion.cast", "return"]
+    last_cast = fn.ops[-2]
+    assert last_cast.attr("round_mode") == "rint" and last_cast.attr("enable_saturate") is True
+    assert fn.ops[4].int_list("dimensions") == [1]
+    ins, types = fn.ops[7].group("ins")
+    assert ins == ["%amax", "%c127"] and types == ["tensor<64xf32>", "f32"]
+    vec = M.parse(VEC_IR)["axpy"]
+    assert vec.op_names().count("hivm.hir.load") == 3 and vec.ops[-2].name == "hivm.hir.store"
+    assert vec.ops[-3].attr("pad_mode") == "PadValue"
+    with pytest.raises(M.MlirTextError):
+        M.parse("module {}")
+
+
+@pytest.mark.skipif(not os.environ.get("BSIR_REFERENCE_DIR"), reason="needs a checkout of the reference (BSIR_REFERENCE_DIR)")
+def test_reference_files_parse_unchanged():
+    M = _mlir_text()
+    ref = os.environ["BSIR_REFERENCE_DIR"]
+    for rel, fn_name in (("bishengir/test/Integration/HIVM/VecAdd/add.mlir", "add"),
+                         ("bishengir/test/bishengir-compile/hfusion/compile-rms-norm-fp16-split-n.mlir", "rms_norm_f16")):
+        with open(os.path.join(ref, rel), encoding="utf-8") as f:
+            fn = M.parse(f.read())[fn_name]
+        assert fn.op_names()[-1] == "return" and len(fn.ops) >= 8
+
+
+# ------------------------------------------------------------------------------------------------ GPU
+@pytest.fixture(scope="module")
+def bsir():
+    import bsir as B
+    B.lib()
+    return B
+
+
+@pytest.mark.gpu
+def test_quant_chain_equals_fused_kernel_and_oracle(bsir):
+    import torch
+    from bsir import mlir_text
+    from conftest import to_bits
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = (torch.randn(64, 512, generator=g, device="cuda") * 3).to(torch.bfloat16)
+    x[3] = 0                                                         # an all-zero row: 0/0 -> NaN -> 0
+    fn = mlir_text.parse(QUANT_IR)["quant"]
+    q, scale = fn(x, torch.empty(64, 512, dtype=torch.int8, device="cuda"), torch.empty(64, device="cuda"))
+    fq, fs = bsir.quant_per_token_i8(x)
+    assert torch.equal(q, fq) and torch.equal(scale.view(torch.int32), fs.view(torch.int32))
+    wq, ws = O.quant_per_token_i8(O.BF16, to_bits(x))
+    assert np.array_equal(q.cpu().numpy(), wq) and np.array_equal(scale.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+
+
+@pytest.mark.gpu
+def test_hivm_vector_program_with_padding_and_atomic_store(bsir):
+    import torch
+    from bsir import mlir_text
+    g = torch.Generator(device="cuda").manual_seed(1)
+    a = torch.randn(1000, generator=g, device="cuda")
+    b = torch.randn(1000, generator=g, device="cuda")
+    out = torch.ones(1024, device="cuda")
+    mlir_text.parse(VEC_IR)["axpy"](a, b, out)
+    want = torch.full((1024,), 7.5, device="cuda")
+    want[8:1008] = a * b + a
+    assert torch.equal(out, want + 1.0)                              # atomic add onto the ones
+
+
+@pytest.mark.gpu
+def test_reduce_with_index_compare_select_program(bsir):
+    import torch
+    from bsir import mlir_text
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn(8, 4096, generator=g, device="cuda")
+    x[2, [7, 900]] = 9.0
+    v, i, r = mlir_text.parse(ARGMAX_IR)["pick"](x, torch.empty(8, device="cuda"), torch.empty(8, dtype=torch.int32, device="cuda"),
+                                                 torch.empty(8, 4096, device="cuda"))
+    assert torch.equal(v, x.max(dim=1).values) and i[2].item() == 7
+    assert torch.equal(r, torch.where(x < 0, torch.zeros_like(x), x))
+
+
+@pytest.mark.gpu
+def test_unsupported_op_fails_loudly(bsir):
+    import torch
+    from bsir import mlir_text
+    fn = mlir_text.parse("func.func @f(%x: tensor<4xf32>) -> tensor<4xf32> {\n  %y = hfusion.cumsum %x : tensor<4xf32>\n  return %y : tensor<4xf32>\n}")["f"]
+    with pytest.raises(mlir_text.MlirTextError):
+        fn(torch.zeros(4, device="cuda"))
+
+
+@pytest.mark.gpu
+def test_rms_norm_program_against_oracle_and_fused_kernel(bsir):
+    """The RMSNorm op chain in the order the reference writes it; the fused kernel computes the same ops, only the
+    row sums associate differently (tolerance 1e-2 relative, as for the fused kernel)."""
+    import torch
+    from bsir import mlir_text
+    from conftest import assert_close, to_bits
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x = torch.randn(40, 512, generator=g, device="cuda").to(torch.float16)
+    gamma = (1 + 0.02 * torch.randn(512, generator=g, device="cuda")).to(torch.float16)
+    y, rstd = mlir_text.parse(RMS_IR)["rms"](x, gamma, torch.empty_like(x), torch.empty(40, dtype=torch.float16, device="cuda"))
+    wy, wr = O.rms_norm(O.F16, to_bits(x), to_bits(gamma), 1e-6, want_rstd=True)
+    assert_close(y, wy, 1e-2, 1e-3, "rms-norm program vs oracle")
+    assert_close(rstd, wr, 1e-2, 1e-3, "rstd vs oracle")
+    fy, fr = bsir.rms_norm(x, gamma, 1e-6, want_rstd=True)
+    assert (y.float() - fy.float()).abs().max().item() <= 1e-2 * fy.float().abs().max().item()
