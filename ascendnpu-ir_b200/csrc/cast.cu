@@ -111,6 +111,7 @@ __device__ __forceinline__ float src_to_f32(typename CT<SRC>::type v) {
 __device__ __forceinline__ unsigned long long f32_integral_to_bits(float r) {
   const float a = fabsf(r);
   if (!(a < 3.4028235e38f)) return 0ull;  // inf / NaN
+  if (a < 2.1474836e9f) return static_cast<unsigned long long>(static_cast<long long>(__float2int_rz(r)));  // the common case: one 32-bit convert
   if (a < 9.2233720e18f) return static_cast<unsigned long long>(__float2ll_rz(r));
   const uint32_t u = __float_as_uint(a);
   const int sh = static_cast<int>(u >> 23) - 150;  // value = mant << sh, sh >= 40 here
@@ -137,7 +138,16 @@ __device__ __forceinline__ typename CT<DST>::type float_to_int(float x, int mode
     if constexpr (DST == BSIR_BOOL) return r >= 1.0f ? T(1) : T(0);
     else if constexpr (DST == BSIR_U64) return r <= 0.0f ? T(0) : static_cast<T>(__float2ull_rz(r));
     else if constexpr (DST == BSIR_I64) return static_cast<T>(__float2ll_rz(r));
-    else if constexpr (is_u<DST>()) {
+    else if constexpr (kBits <= 32 && !is_u<DST>()) {
+      // cvt.rzi.s32.f32 saturates at the int32 range, which contains every narrower range
+      const int v = __float2int_rz(r);
+      constexpr int lo = kBits == 32 ? INT_MIN : -(1 << (kBits - 1)), hi = kBits == 32 ? INT_MAX : (1 << (kBits - 1)) - 1;
+      return static_cast<T>(v < lo ? lo : v > hi ? hi : v);
+    } else if constexpr (kBits <= 32) {
+      const unsigned v = __float2uint_rz(r);   // saturates at [0, 2^32 - 1]; negatives give 0
+      constexpr unsigned hi = kBits == 32 ? 0xffffffffu : (1u << kBits) - 1u;
+      return static_cast<T>(v > hi ? hi : v);
+    } else if constexpr (is_u<DST>()) {
       const unsigned long long v = r <= 0.0f ? 0ull : __float2ull_rz(r);
       const unsigned long long hi = (1ull << kBits) - 1ull;
       return static_cast<T>(v > hi ? hi : v);
@@ -265,15 +275,40 @@ __global__ void __launch_bounds__(256) cast_stream_kernel(int64_t n, const void 
     const int64_t gidx = base + static_cast<int64_t>(u) * 256;
     if (gidx < ngroups) in[u] = static_cast<const SV *>(src)[gidx];
   }
+  // With the attributes known at compile time the conversion folds to a few instructions; the usual
+  // float -> integer combinations get their own copy of the loop, the rest share the general one.
+  auto body = [&](auto mode_c, auto overflow_c) {
 #pragma unroll
-  for (int u = 0; u < kUnroll; ++u) {
-    const int64_t gidx = base + static_cast<int64_t>(u) * 256;
-    if (gidx >= ngroups) continue;
-    DV out;
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t gidx = base + static_cast<int64_t>(u) * 256;
+      if (gidx >= ngroups) continue;
+      DV out;
 #pragma unroll
-    for (int e = 0; e < kElems; ++e) out.e[e] = convert<SRC, DST>(in[u].e[e], mode, overflow);
-    static_cast<DV *>(dst)[gidx] = out;
+      for (int e = 0; e < kElems; ++e) out.e[e] = convert<SRC, DST>(in[u].e[e], mode_c(), overflow_c());
+      static_cast<DV *>(dst)[gidx] = out;
+    }
+  };
+  constexpr bool kFloatToInt = (SRC == BSIR_F32 || SRC == BSIR_F16 || SRC == BSIR_BF16) &&
+                               !(DST == BSIR_F32 || DST == BSIR_F16 || DST == BSIR_BF16);
+  auto fixed = [](auto v) { return [v]() { return decltype(v)::value; }; };
+  using std::integral_constant;
+  bool done = false;
+  if constexpr (kFloatToInt) {
+    if (mode == BSIR_ROUND_RINT && overflow == BSIR_OVERFLOW_SATURATE) {
+      body(fixed(integral_constant<int, BSIR_ROUND_RINT>{}), fixed(integral_constant<int, BSIR_OVERFLOW_SATURATE>{}));
+      done = true;
+    } else if (mode == BSIR_ROUND_RINT && overflow == BSIR_OVERFLOW_WRAP) {
+      body(fixed(integral_constant<int, BSIR_ROUND_RINT>{}), fixed(integral_constant<int, BSIR_OVERFLOW_WRAP>{}));
+      done = true;
+    } else if (mode == BSIR_ROUND_TRUNC && overflow == BSIR_OVERFLOW_SATURATE) {
+      body(fixed(integral_constant<int, BSIR_ROUND_TRUNC>{}), fixed(integral_constant<int, BSIR_OVERFLOW_SATURATE>{}));
+      done = true;
+    } else if (mode == BSIR_ROUND_TRUNC && overflow == BSIR_OVERFLOW_WRAP) {
+      body(fixed(integral_constant<int, BSIR_ROUND_TRUNC>{}), fixed(integral_constant<int, BSIR_OVERFLOW_WRAP>{}));
+      done = true;
+    }
   }
+  if (!done) body([mode]() { return mode; }, [overflow]() { return overflow; });
   const int64_t tail0 = ngroups * kElems;
   if (blockIdx.x == 0 && tail0 + threadIdx.x < n)
     static_cast<D *>(dst)[tail0 + threadIdx.x] = convert<SRC, DST>(static_cast<const S *>(src)[tail0 + threadIdx.x], mode, overflow);

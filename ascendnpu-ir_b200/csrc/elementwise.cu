@@ -416,6 +416,100 @@ __global__ void __launch_bounds__(kStreamThreads)
   }
 }
 
+// ------------------------------------------------------------------ streaming compare / select
+template <int DT>
+__device__ __forceinline__ bool compare_elem(int fn, typename CType<DT>::type xa, typename CType<DT>::type ya) {
+  using T = typename CType<DT>::type;
+  if constexpr (IsFloat<DT>::value) {
+    const float x = widen<DT>(xa), y = widen<DT>(ya);
+    switch (fn) {
+      case BSIR_CMP_VEQ: return x == y;
+      case BSIR_CMP_VNE: return !(x == y);  // unordered-or-not-equal
+      case BSIR_CMP_VLE: return x <= y;
+      case BSIR_CMP_VLT: return x < y;
+      case BSIR_CMP_VGE: return x >= y;
+      default: return x > y;
+    }
+  } else {
+    using UT = typename Unsigned<T>::type;
+    const UT ux = static_cast<UT>(xa), uy = static_cast<UT>(ya);
+    switch (fn) {
+      case BSIR_CMP_VEQ: return xa == ya;
+      case BSIR_CMP_VNE: return xa != ya;
+      case BSIR_CMP_VLE: return xa <= ya;
+      case BSIR_CMP_VLT: return xa < ya;
+      case BSIR_CMP_VGE: return xa >= ya;
+      case BSIR_CMP_VGT: return xa > ya;
+      case BSIR_CMP_VULE: return ux <= uy;
+      case BSIR_CMP_VULT: return ux < uy;
+      case BSIR_CMP_VUGE: return ux >= uy;
+      default: return ux > uy;
+    }
+  }
+}
+
+// Contiguous, aligned operands: a thread handles 16-byte vectors of the value type; compare writes the
+// vector's results as one store of 16 / sizeof(T) bool bytes, select reads its condition bytes the same way.
+// KIND = kOpCompare: out(bool) = a <fn> b.  KIND = kOpSelect: out = cond ? a : b (cond in `cp`).
+template <int DT, int KIND>
+__global__ void __launch_bounds__(kStreamThreads)
+    cmpsel_stream_kernel(int fn, int64_t n, const void *__restrict__ ap, const void *__restrict__ bp,
+                         const void *__restrict__ cp, unsigned long long a_scalar, unsigned long long b_scalar,
+                         void *__restrict__ outp) {
+  using T = typename CType<DT>::type;
+  constexpr int kPerVec = 16 / sizeof(T);
+  struct alignas(kPerVec) Flags { uint8_t f[kPerVec]; };
+  const int64_t nvec = n / kPerVec;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * (kStreamThreads * kStreamUnroll) + threadIdx.x;
+  T sa, sb;
+  memcpy(&sa, &a_scalar, sizeof(T));
+  memcpy(&sb, &b_scalar, sizeof(T));
+  Vec16 va[kStreamUnroll], vb[kStreamUnroll];
+  Flags fc[kStreamUnroll];
+#pragma unroll
+  for (int u = 0; u < kStreamUnroll; ++u) {
+    const int64_t v = base + static_cast<int64_t>(u) * kStreamThreads;
+    if (v < nvec) {
+      if (ap) va[u] = ld_stream(static_cast<const Vec16 *>(ap) + v);
+      if (bp) vb[u] = ld_stream(static_cast<const Vec16 *>(bp) + v);
+      if constexpr (KIND == kOpSelect) fc[u] = static_cast<const Flags *>(cp)[v];
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kStreamUnroll; ++u) {
+    const int64_t v = base + static_cast<int64_t>(u) * kStreamThreads;
+    if (v >= nvec) continue;
+    T x[kPerVec], y[kPerVec];
+    if (ap) memcpy(x, &va[u], 16);
+    else
+      for (int e = 0; e < kPerVec; ++e) x[e] = sa;
+    if (bp) memcpy(y, &vb[u], 16);
+    else
+      for (int e = 0; e < kPerVec; ++e) y[e] = sb;
+    if constexpr (KIND == kOpCompare) {
+      Flags r;
+#pragma unroll
+      for (int e = 0; e < kPerVec; ++e) r.f[e] = compare_elem<DT>(fn, x[e], y[e]) ? 1 : 0;
+      static_cast<Flags *>(outp)[v] = r;
+    } else {
+      T r[kPerVec];
+#pragma unroll
+      for (int e = 0; e < kPerVec; ++e) r[e] = fc[u].f[e] ? x[e] : y[e];
+      Vec16 vo;
+      memcpy(&vo, r, 16);
+      st_stream(static_cast<Vec16 *>(outp) + v, vo);
+    }
+  }
+  // ragged tail (< one vector): the first threads of block 0, one element each
+  const int64_t i = nvec * kPerVec + threadIdx.x;
+  if (blockIdx.x == 0 && i < n) {
+    const T xa = ap ? static_cast<const T *>(ap)[i] : sa;
+    const T ya = bp ? static_cast<const T *>(bp)[i] : sb;
+    if constexpr (KIND == kOpCompare) static_cast<uint8_t *>(outp)[i] = compare_elem<DT>(fn, xa, ya) ? 1 : 0;
+    else static_cast<T *>(outp)[i] = static_cast<const uint8_t *>(cp)[i] ? xa : ya;
+  }
+}
+
 // ------------------------------------------------------------------ host dispatch
 bool fn_is_valid(int kind, int fn, int dt) {
   const bool f = dtype_is_float(dt);
@@ -520,6 +614,28 @@ int32_t launch_typed(const char *what, int fn, const Prepared &p, const Operand 
       if (blocks < 1) blocks = 1;
       stream_kernel<DT, KIND><<<static_cast<unsigned>(blocks), kStreamThreads, 0, st>>>(
           fn, n, a.p, KIND == kOpBinary ? b.p : nullptr, a.scalar, b.scalar, out);
+      count_launch();
+      return check_launch(what);
+    }
+  }
+  if constexpr (KIND == kOpCompare || KIND == kOpSelect) {
+    // compare: a, b are the values; select: a is the condition (bool bytes), b and c the values
+    constexpr int kPerVec = 16 / sizeof(T);
+    auto dense = [&](const Operand &o) {
+      if (!o.p) return true;
+      return (p.sh.n2 == 1 || o.s2 == 1) && (p.sh.n1 == 1 || o.s1 == p.sh.n2) && (p.sh.n0 == 1 || o.s0 == p.sh.n1 * p.sh.n2);
+    };
+    const Operand &x = KIND == kOpCompare ? a : b;
+    const Operand &y = KIND == kOpCompare ? b : c;
+    const bool ok = p.out_contig && dense(x) && dense(y) && (x.p || y.p) && (!x.p || aligned_to(x.p, 16)) &&
+                    (!y.p || aligned_to(y.p, 16)) &&
+                    (KIND == kOpCompare ? aligned_to(out, kPerVec)
+                                        : (a.p && dense(a) && aligned_to(a.p, kPerVec) && aligned_to(out, 16)));
+    if (ok) {
+      int64_t blocks = ceil_div(n / kPerVec, kStreamThreads * kStreamUnroll);
+      if (blocks < 1) blocks = 1;
+      cmpsel_stream_kernel<DT, KIND><<<static_cast<unsigned>(blocks), kStreamThreads, 0, st>>>(
+          fn, n, x.p, y.p, KIND == kOpSelect ? a.p : nullptr, x.scalar, y.scalar, out);
       count_launch();
       return check_launch(what);
     }

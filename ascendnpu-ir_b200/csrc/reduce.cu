@@ -167,6 +167,171 @@ __global__ void __launch_bounds__(256) reduce_first_kernel(int64_t rows, int64_t
   }
 }
 
+// ------------------------------------------------------------------ vectorised paths
+// Rows (or columns) whose base and pitch are 16-byte aligned are read as 16-byte vectors, several per
+// thread in flight.  When a single pass would leave most SMs idle (few long rows; a tall matrix
+// reduced over its first axis) the work is cut into parts, every part leaves one partial per output
+// in a scratch array, and a second, tiny launch combines the partials in part order -- no atomics, the
+// result does not depend on timing.
+template <int DT>
+__device__ __forceinline__ typename Acc<DT>::type acc_from_vec(const Vec16 &v, int k) {
+  using A = typename Acc<DT>::type;
+  using E = typename Acc<DT>::elem;
+  if constexpr (sizeof(E) == 4) {
+    const uint32_t w = v.w[k];
+    if constexpr (std::is_same<A, float>::value) return __uint_as_float(w);
+    else return static_cast<A>(static_cast<E>(w));
+  } else if constexpr (sizeof(E) == 8) {
+    const unsigned long long u = static_cast<unsigned long long>(v.w[2 * k]) | (static_cast<unsigned long long>(v.w[2 * k + 1]) << 32);
+    return static_cast<A>(static_cast<E>(u));
+  } else if constexpr (sizeof(E) == 2) {
+    const uint16_t h = static_cast<uint16_t>(v.w[k >> 1] >> (16 * (k & 1)));
+    if constexpr (DT == BSIR_F16) return __half2float(__ushort_as_half(h));
+    else if constexpr (DT == BSIR_BF16) return __uint_as_float(static_cast<uint32_t>(h) << 16);
+    else return static_cast<A>(static_cast<E>(h));
+  } else {
+    const uint8_t b = static_cast<uint8_t>(v.w[k >> 2] >> (8 * (k & 3)));
+    return static_cast<A>(static_cast<E>(b));
+  }
+}
+
+template <typename A>
+__device__ __forceinline__ unsigned long long acc_bits(A a) {
+  unsigned long long u = 0;
+  memcpy(&u, &a, sizeof(A));
+  return u;
+}
+template <typename A>
+__device__ __forceinline__ A acc_of_bits(unsigned long long u) {
+  A a;
+  memcpy(&a, &u, sizeof(A));
+  return a;
+}
+
+// Last axis.  grid = (row groups, parts); `tpr` threads (4..256, a power of two) share a row part.
+template <int DT, int KIND>
+__global__ void __launch_bounds__(256) reduce_last_vec_kernel(int64_t rows, int64_t nvec, int64_t row_stride,
+                                                              const void *__restrict__ src, int64_t part_vecs, int nparts,
+                                                              int tpr, void *__restrict__ dst, unsigned long long *partials) {
+  using A = typename Acc<DT>::type;
+  using E = typename Acc<DT>::elem;
+  constexpr int kPerVec = 16 / sizeof(E);
+  __shared__ unsigned long long red[4][8];     // used only when a row has more than one warp (tpr >= 64)
+  const int rpc = 256 / tpr;
+  const int sub = threadIdx.x / tpr, t = threadIdx.x % tpr;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * rpc + sub;
+  const int part = blockIdx.y;
+  const int64_t v0 = static_cast<int64_t>(part) * part_vecs;
+  const int64_t v1 = min(nvec, v0 + part_vecs);
+  A acc[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) acc[u] = identity<DT, KIND>();
+  if (row < rows) {
+    const Vec16 *xv = reinterpret_cast<const Vec16 *>(static_cast<const E *>(src) + row * row_stride);
+    for (int64_t j = v0 + t; j < v1; j += 4 * tpr) {
+      Vec16 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (j + u * tpr < v1) v[u] = ld_stream(xv + j + u * tpr);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (j + u * tpr < v1) {
+#pragma unroll
+          for (int k = 0; k < kPerVec; ++k) acc[u] = combine<KIND, A>(acc_from_vec<DT>(v[u], k), acc[u]);
+        }
+    }
+  }
+  A a = combine<KIND, A>(combine<KIND, A>(acc[0], acc[1]), combine<KIND, A>(acc[2], acc[3]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    if (o < tpr) a = combine<KIND, A>(a, shfl_xor_any(a, o));
+  if (tpr > 32) {
+    const int lane = threadIdx.x & 31, w = t >> 5, nw = tpr >> 5;
+    if (lane == 0) red[sub][w] = acc_bits(a);
+    __syncthreads();
+    A p = identity<DT, KIND>();
+    if (lane < nw) p = acc_of_bits<A>(red[sub][lane]);
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) p = combine<KIND, A>(p, shfl_xor_any(p, o));
+    a = p;
+  }
+  if (row < rows && t == 0) {
+    if (nparts == 1) store_acc<DT>(dst, row, a);
+    else partials[row * nparts + part] = acc_bits(a);
+  }
+}
+
+// First axis.  A thread owns one 16-byte column vector; block = 32 column vectors x 8 row slices;
+// grid = (column groups, row slabs).
+template <int DT, int KIND>
+__global__ void __launch_bounds__(256) reduce_first_vec_kernel(int64_t rows, int64_t cvecs, int64_t row_stride,
+                                                               const void *__restrict__ src, int64_t slab_rows, int nslabs,
+                                                               void *__restrict__ dst, unsigned long long *partials) {
+  using A = typename Acc<DT>::type;
+  using E = typename Acc<DT>::elem;
+  constexpr int kPerVec = 16 / sizeof(E);
+  __shared__ unsigned long long red[7][32][kPerVec < 8 ? kPerVec : 8];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int64_t cv = static_cast<int64_t>(blockIdx.x) * 32 + cx;
+  const int slab = blockIdx.y;
+  const int64_t r0 = static_cast<int64_t>(slab) * slab_rows, r1 = min(rows, r0 + slab_rows);
+  A acc[kPerVec];
+#pragma unroll
+  for (int k = 0; k < kPerVec; ++k) acc[k] = identity<DT, KIND>();
+  if (cv < cvecs) {
+    const E *base = static_cast<const E *>(src) + cv * kPerVec;
+    for (int64_t r = r0 + ry; r < r1; r += 32) {
+      Vec16 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (r + 8 * u < r1) v[u] = ld_stream(reinterpret_cast<const Vec16 *>(base + (r + 8 * u) * row_stride));
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (r + 8 * u < r1) {
+#pragma unroll
+          for (int k = 0; k < kPerVec; ++k) acc[k] = combine<KIND, A>(acc_from_vec<DT>(v[u], k), acc[k]);
+        }
+    }
+  }
+  // the eight row slices meet in shared memory, 8 elements of the vector at a time
+  constexpr int kChunk = kPerVec < 8 ? kPerVec : 8;
+#pragma unroll
+  for (int c0 = 0; c0 < kPerVec; c0 += kChunk) {
+    if (ry > 0) {
+#pragma unroll
+      for (int k = 0; k < kChunk; ++k) red[ry - 1][cx][k] = acc_bits(acc[c0 + k]);
+    }
+    __syncthreads();
+    if (ry == 0 && cv < cvecs) {
+#pragma unroll
+      for (int s = 0; s < 7; ++s)
+#pragma unroll
+        for (int k = 0; k < kChunk; ++k) acc[c0 + k] = combine<KIND, A>(acc[c0 + k], acc_of_bits<A>(red[s][cx][k]));
+    }
+    __syncthreads();
+  }
+  if (ry == 0 && cv < cvecs) {
+#pragma unroll
+    for (int k = 0; k < kPerVec; ++k) {
+      const int64_t c = cv * kPerVec + k;
+      if (nslabs == 1) store_acc<DT>(dst, c, acc[k]);
+      else partials[static_cast<int64_t>(slab) * (cvecs * kPerVec) + c] = acc_bits(acc[k]);
+    }
+  }
+}
+
+// out[o] = combine over p of partials[o * out_stride + p * part_stride], in part order
+template <int DT, int KIND>
+__global__ void __launch_bounds__(256) reduce_finish_kernel(int64_t nout, int nparts, int64_t out_stride, int64_t part_stride,
+                                                            const unsigned long long *__restrict__ partials, void *__restrict__ dst) {
+  using A = typename Acc<DT>::type;
+  const int64_t o = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+  if (o >= nout) return;
+  A a = identity<DT, KIND>();
+  for (int p = 0; p < nparts; ++p) a = combine<KIND, A>(a, acc_of_bits<A>(partials[o * out_stride + p * part_stride]));
+  store_acc<DT>(dst, o, a);
+}
+
 bool reduce_kind_valid(int kind, int dt) {
   if (kind < BSIR_REDUCE_SUM || kind > BSIR_REDUCE_ANDI) return false;
   if (dtype_is_float(dt)) return kind <= BSIR_REDUCE_MIN;
@@ -175,6 +340,71 @@ bool reduce_kind_valid(int kind, int dt) {
 
 template <int DT, int KIND>
 void launch_reduce(bool last, int64_t rows, int64_t cols, const void *src, int64_t rs, void *dst, cudaStream_t st) {
+  using E = typename Acc<DT>::elem;
+  constexpr int kPerVec = 16 / sizeof(E);
+  const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
+  const bool vec_ok = rows > 0 && cols > 0 && cols % kPerVec == 0 && rs % kPerVec == 0 && aligned_to(src, 16) &&
+                      std::getenv("BSIR_REDUCE_SCALAR") == nullptr;
+  if (last && vec_ok) {
+    const int64_t nvec = cols / kPerVec;
+    int tpr = 4;
+    while (tpr < 256 && nvec > tpr * 4) tpr <<= 1;          // about 4 vectors per thread before a row gets more threads
+    const int rpc = 256 / tpr;
+    const int64_t row_groups = ceil_div(rows, rpc);
+    // few long rows: cut them so that about 4 CTAs per SM have work, parts of at least 1024 vectors
+    int64_t parts = 1;
+    if (tpr == 256 && row_groups < 4 * sms) {
+      parts = ceil_div(4 * sms, row_groups);
+      if (parts > nvec / 1024) parts = nvec / 1024;
+      if (parts > 1024) parts = 1024;
+      if (parts < 1) parts = 1;
+    }
+    const int64_t part_vecs = ceil_div(nvec, parts);
+    parts = ceil_div(nvec, part_vecs);
+    unsigned long long *partials = nullptr;
+    if (parts > 1) {
+      char *ws = static_cast<char *>(device_workspace(kScratchCounterBytes + static_cast<size_t>(rows) * parts * 8, st));
+      if (ws) partials = reinterpret_cast<unsigned long long *>(ws + kScratchCounterBytes);
+      else parts = 1;
+    }
+    const dim3 grid(static_cast<unsigned>(row_groups), static_cast<unsigned>(parts));
+    reduce_last_vec_kernel<DT, KIND><<<grid, 256, 0, st>>>(rows, nvec, rs, src, parts > 1 ? part_vecs : nvec,
+                                                          static_cast<int>(parts), tpr, dst, partials);
+    if (parts > 1) {
+      reduce_finish_kernel<DT, KIND><<<static_cast<unsigned>(ceil_div(rows, 256)), 256, 0, st>>>(rows, static_cast<int>(parts), parts, 1,
+                                                                                                  partials, dst);
+      count_launch();
+    }
+    return;
+  }
+  if (!last && vec_ok) {
+    const int64_t cvecs = cols / kPerVec;
+    const int64_t col_groups = ceil_div(cvecs, 32);
+    int64_t slabs = 1;
+    if (col_groups < 4 * sms) {
+      slabs = ceil_div(4 * sms, col_groups);
+      if (slabs > rows / 64) slabs = rows / 64;
+      if (slabs > 1024) slabs = 1024;
+      if (slabs < 1) slabs = 1;
+    }
+    const int64_t slab_rows = ceil_div(rows, slabs);
+    slabs = ceil_div(rows, slab_rows);
+    unsigned long long *partials = nullptr;
+    if (slabs > 1) {
+      char *ws = static_cast<char *>(device_workspace(kScratchCounterBytes + static_cast<size_t>(cols) * slabs * 8, st));
+      if (ws) partials = reinterpret_cast<unsigned long long *>(ws + kScratchCounterBytes);
+      else slabs = 1;
+    }
+    const dim3 grid(static_cast<unsigned>(col_groups), static_cast<unsigned>(slabs));
+    reduce_first_vec_kernel<DT, KIND><<<grid, 256, 0, st>>>(rows, cvecs, rs, src, slabs > 1 ? slab_rows : rows,
+                                                           static_cast<int>(slabs), dst, partials);
+    if (slabs > 1) {
+      reduce_finish_kernel<DT, KIND><<<static_cast<unsigned>(ceil_div(cols, 256)), 256, 0, st>>>(cols, static_cast<int>(slabs), 1, cols,
+                                                                                                  partials, dst);
+      count_launch();
+    }
+    return;
+  }
   if (last) {
     int tpr = 32;
     while (tpr < 256 && cols > tpr * 8) tpr <<= 1;
