@@ -948,6 +948,94 @@ __global__ void __launch_bounds__(256, 4) rwi_stream_kernel(RwiParams p, const v
   rwi_publish_and_fold<DT, IS_MAX>(p, src, row, seg, p.nseg, m, best, nanpos, dst_val, dst_idx, counters, partials);
 }
 
+// Short rows (at most 64 vectors): `gs` lanes (4, 8, 16 or 32) share a row, so a warp holds 32 / gs rows and
+// every lane has a load in flight; no shared memory, no barrier; a lane holds up to two vectors.  Same
+// result as the kernels above.
+template <int DT, bool IS_MAX>
+__global__ void __launch_bounds__(256) rwi_warp_kernel(RwiParams p, int gs, const void *__restrict__ src,
+                                                       void *__restrict__ dst_val, int32_t *__restrict__ dst_idx) {
+  constexpr int kPerWord = FloatTraits<DT>::kPerWord;
+  constexpr int kPerVec = 4 * kPerWord;
+  using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
+  const int lane = threadIdx.x & 31, sl = lane & (gs - 1);
+  const int rows_per_warp = 32 / gs;
+  const int64_t warp_id = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int64_t row = warp_id * rows_per_warp + lane / gs;
+  const bool row_ok = row < p.rows;                           // lanes of missing rows still take part in the shuffles
+  const float ident = IS_MAX ? __int_as_float(0xff800000) : __int_as_float(0x7f800000);
+  const Vec16 *xv = reinterpret_cast<const Vec16 *>(static_cast<const E *>(src) + (row_ok ? row : 0) * p.row_stride);
+  Vec16 v[2];
+  bool have[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    have[i] = row_ok && sl + gs * i < p.nvec;
+    if (have[i]) v[i] = ld_stream(xv + sl + gs * i);
+  }
+  auto for_each = [&](auto f) {   // f(row index of the element, its value)
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if (have[i]) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          float e[kPerWord];
+          FloatTraits<DT>::unpack(v[i].w[w], e);
+#pragma unroll
+          for (int k = 0; k < kPerWord; ++k) f((sl + gs * i) * kPerVec + w * kPerWord + k, e[k]);
+        }
+      }
+  };
+  auto group_ext = [&](float x) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, x, o);
+      if (o < gs) x = ext_nan<IS_MAX>(x, other);
+    }
+    return x;
+  };
+  auto group_pick = [&](int b) {   // lowest (tie_left) or highest index over the row's lanes
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const int other = __shfl_xor_sync(0xffffffffu, b, o);
+      if (o < gs) b = p.tie_left ? min(b, other) : max(b, other);
+    }
+    return b;
+  };
+  float tm = ident;
+  for_each([&](int, float e) { tm = ext_nan<IS_MAX>(tm, e); });
+  float m = group_ext(tm);
+  // rows of one warp may differ in whether they hold a NaN: both searches run for all lanes, each row
+  // keeps the one that applies to it
+  int best = p.tie_left ? INT_MAX : -1;
+  if (m == m && tm == m) for_each([&](int gi, float e) { if (e == m) best = p.tie_left ? min(best, gi) : max(best, gi); });
+  best = group_pick(best);
+  int nanpos = INT_MAX;
+  for_each([&](int gi, float e) { if (e != e) nanpos = min(nanpos, gi); });
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const int other = __shfl_xor_sync(0xffffffffu, nanpos, o);
+    if (o < gs) nanpos = min(nanpos, other);
+  }
+  if (__any_sync(0xffffffffu, nanpos != INT_MAX)) {
+    // some row holds a NaN: the extreme of its prefix before the first NaN and that extreme's position
+    float tm2 = ident;
+    for_each([&](int gi, float e) { if (gi < nanpos) tm2 = ext_nan<IS_MAX>(tm2, e); });
+    const float m2 = group_ext(tm2);
+    int best2 = p.tie_left ? INT_MAX : -1;
+    for_each([&](int gi, float e) { if (gi < nanpos && e == m2) best2 = p.tie_left ? min(best2, gi) : max(best2, gi); });
+    best2 = group_pick(best2);
+    if (nanpos != INT_MAX) { m = m2; best = best2; }
+  }
+  if (row_ok && sl == 0) {
+    float val = m;
+    int idx = (best == INT_MAX || best < 0) ? 0 : best;
+    if (nanpos != INT_MAX) {
+      val = __int_as_float(0x7fc00000);
+      if (p.nan_first) idx = nanpos;
+    }
+    rwi_write<DT>(p, src, row, val, idx, dst_val, dst_idx);
+  }
+}
+
 // Scalar fallback: one CTA per row, any stride / alignment / length.
 template <int DT, bool IS_MAX>
 __global__ void __launch_bounds__(256) rwi_scalar_kernel(RwiParams p, const void *__restrict__ src,
@@ -1070,6 +1158,29 @@ int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie_break_le
     return fail(BSIR_ERR_ATTR, "reduce_with_index: nan_mode %d", nan_mode);
   if (rows < 0 || cols < 0) return fail(BSIR_ERR_SHAPE, "reduce_with_index: rows=%lld cols=%lld", (long long)rows, (long long)cols);
   if (cols > INT_MAX - 64) return fail(BSIR_ERR_SHAPE, "reduce_with_index: cols exceed the int32 index range");
+  // short rows: one warp per row, any number of rows in one launch
+  if (rows > 0 && cols > 0 && src && dst_value && dst_index) {
+    const int eb0 = dtype_bytes(dtype), pv0 = 16 / eb0;
+    if (cols % pv0 == 0 && cols / pv0 <= 64 && src_row_stride >= cols && aligned_to(src, 16) && (src_row_stride * eb0) % 16 == 0 &&
+        aligned_to(dst_value, eb0) && aligned_to(dst_index, 4) && rows <= 0x7fffffffLL * 8) {
+      RwiParams q{};
+      q.rows = rows; q.cols = cols; q.row_stride = src_row_stride; q.nvec = cols / pv0; q.nseg = 1;
+      q.tie_left = tie_break_left ? 1 : 0;
+      q.nan_first = nan_mode == BSIR_RWI_NAN_FIRST;
+      cudaStream_t st0 = resolve_stream(stream);
+      int gs = 4;                                           // lanes per row: each lane holds up to two vectors
+      while (gs < 32 && q.nvec > 2 * gs) gs <<= 1;
+      const unsigned blocks = static_cast<unsigned>(ceil_div(rows, 8 * (32 / gs)));
+      const bool mx = kind == BSIR_RWI_MAX;
+#define W(D)                                                                                        \
+  if (mx) rwi_warp_kernel<D, true><<<blocks, 256, 0, st0>>>(q, gs, src, dst_value, dst_index);        \
+  else rwi_warp_kernel<D, false><<<blocks, 256, 0, st0>>>(q, gs, src, dst_value, dst_index);
+      if (dtype == BSIR_F32) { W(BSIR_F32) } else if (dtype == BSIR_F16) { W(BSIR_F16) } else { W(BSIR_BF16) }
+#undef W
+      count_launch();
+      return check_launch("reduce_with_index");
+    }
+  }
   if (rows > 65535) {
     // grid.y limit: fold very tall inputs in slabs
     for (int64_t r0 = 0; r0 < rows; r0 += 65535) {

@@ -276,6 +276,31 @@ def test_argmax_long_rows_streaming_path(bsir, dtype):
     _check_rwi(bsir, -x, "min", False, "nan_first")
 
 
+@pytest.mark.parametrize("dtype,cols", [(torch.bfloat16, 64), (torch.bfloat16, 256), (torch.bfloat16, 512), (torch.float16, 8),
+                                        (torch.float32, 256), (torch.float32, 4)])
+def test_argmax_short_rows_warp_per_row(bsir, dtype, cols):
+    """Rows of at most 64 vectors take the warp-per-row kernel: many rows, planted ties, zeros, -inf, NaNs."""
+    rows = 70001                                   # more rows than a grid dimension of 65535
+    g = torch.Generator(device="cuda").manual_seed(cols)
+    x = torch.randn(rows, cols, device="cuda", generator=g).clamp(-3, 3).to(dtype)
+    x[0, [0, cols - 1]] = 9.0
+    x[1, :] = 1.0
+    x[2, :] = -float("inf")
+    x[3, :] = -0.0
+    x[3, cols // 2] = 0.0
+    x[4, cols // 2] = float("nan")
+    x[4, 0] = 8.0
+    x[5, 0] = float("nan")
+    x[6, cols - 1] = float("nan")
+    x[7, [cols // 4, 3 * cols // 4]] = float("nan")
+    x[7, cols // 2] = 9.0
+    x[rows - 1, cols - 1] = 9.0
+    for left in (True, False):
+        for nm in ("region", "nan_first"):
+            _check_rwi(bsir, x, "max", left, nm)
+    _check_rwi(bsir, -x, "min")
+
+
 def test_argmax_few_very_long_rows_many_partials(bsir):
     """Two rows cut into hundreds of parts: the ordered fold of the partials runs lane-parallel."""
     cols = 4_800_000
