@@ -77,10 +77,10 @@ __device__ __forceinline__ int sat_i8(float r) {
 // Rows whose max|x| is 0, inf or NaN quantise to all zeros: every quotient is then 0/0, x/inf
 // or involves a NaN, and NaN saturates to 0.
 //
-// For bf16 rows with a scale in [2^-60, 2^60] the per-element divide is replaced by the
+// For bf16 and f16 rows with a scale in [2^-60, 2^60] the per-element divide is replaced by the
 // reciprocal r = RN(1/scale) and one correction step, q0 = x r, q = fma(fma(-q0, scale, x), r, q0):
-// for every bf16 x with |x / scale| <= 127.5 this rounds to the same integer as the IEEE
-// quotient (checked exhaustively over all bf16 x for thousands of scales by the CPU tests).
+// for every bf16 / f16 x with |x / scale| <= 127.5 this rounds to the same integer as the IEEE
+// quotient (checked exhaustively over all bf16 and all f16 x for thousands of scales by the CPU tests).
 template <int DT, int VPT>
 __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant_rows_kernel(RowGeom g, const void *__restrict__ xp, int64_t x_stride,
                                                           int8_t *__restrict__ qp, int64_t q_stride,
@@ -132,7 +132,7 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
   if (!row_ok) return;
 
   const bool degenerate = !(amax > 0.0f && amax < __int_as_float(0x7f800000));
-  const bool fast = DT == BSIR_BF16 && round_mode == BSIR_ROUND_RINT && scale > 8.6736174e-19f && scale < 1.1529215e18f;
+  const bool fast = (DT == BSIR_BF16 || DT == BSIR_F16) && round_mode == BSIR_ROUND_RINT && scale > 8.6736174e-19f && scale < 1.1529215e18f;
   int8_t *qrow = qp + row * q_stride;
 
   if (degenerate) {
@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
     }
     return;
   }
-  if constexpr (DT == BSIR_BF16) {
+  if constexpr (DT == BSIR_BF16 || DT == BSIR_F16) {
     if (fast) {
       // two elements per instruction (f32x2): q0 = x r; q = fma(fma(q0, -scale, x), r, q0); then
       // q + 1.5 * 2^23 rounds to nearest even and leaves the integer in the low mantissa byte
@@ -163,7 +163,13 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
         for (int w = 0; w < 4; ++w) {
           const uint32_t word = v[i].w[w];
           unsigned long long x2, q0, e2, q1, r2;
-          asm("mov.b64 %0, {%1, %2};" : "=l"(x2) : "r"(word << 16), "r"(word & 0xffff0000u));
+          if constexpr (DT == BSIR_BF16) {
+            asm("mov.b64 %0, {%1, %2};" : "=l"(x2) : "r"(word << 16), "r"(word & 0xffff0000u));
+          } else {
+            float e2[2];
+            FloatTraits<DT>::unpack(word, e2);
+            asm("mov.b64 %0, {%1, %2};" : "=l"(x2) : "f"(e2[0]), "f"(e2[1]));
+          }
           asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(q0) : "l"(x2), "l"(rcp2));
           asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(e2) : "l"(q0), "l"(nscale2), "l"(x2));
           asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(q1) : "l"(e2), "l"(rcp2), "l"(q0));

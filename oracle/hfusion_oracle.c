@@ -969,6 +969,23 @@ ORC_API int64_t orc_selftest_f16(int64_t n) {
  * For every finite bf16 x with |x| <= amax (amax = 127*s rounded up to bf16 range) it must
  * hold that nearbyint(q_steps) == nearbyint(x / s).  Returns the number of mismatches for
  * the given scale using `steps` refinement steps (1 or 2). */
+/* The same check over every finite f16 x (11 significant bits instead of 8). */
+ORC_API int64_t orc_check_recip_division_f16(float s, int steps) {
+  int64_t bad = 0;
+  float r = 1.0f / s;
+  for (uint32_t h = 0; h < 0x7c00u; h++) {
+    for (int sg = 0; sg < 2; sg++) {
+      float x = f16_to_f32((uint16_t)(h | (sg ? 0x8000u : 0u)));
+      float t = x / s;
+      if (!(fabsf(t) <= 127.5f)) continue;
+      float q = x * r;
+      for (int it = 0; it < steps; it++) { float e = fmaf(-q, s, x); q = fmaf(e, r, q); }
+      if (nearbyintf(q) != nearbyintf(t)) bad++;
+    }
+  }
+  return bad;
+}
+
 ORC_API int64_t orc_check_recip_division(float s, int steps) {
   int64_t bad = 0;
   float r = 1.0f / s;

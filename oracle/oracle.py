@@ -72,6 +72,8 @@ def lib() -> C.CDLL:
         _lib.orc_selftest_f16.argtypes = [C.c_int64]
         _lib.orc_check_recip_division.restype = C.c_int64
         _lib.orc_check_recip_division.argtypes = [C.c_float, C.c_int]
+        _lib.orc_check_recip_division_f16.restype = C.c_int64
+        _lib.orc_check_recip_division_f16.argtypes = [C.c_float, C.c_int]
     return _lib
 
 

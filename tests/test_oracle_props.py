@@ -66,6 +66,10 @@ def test_reciprocal_division_identity(seed):
     scales = np.concatenate([scales, rng.uniform(1e-3, 1.0, 300).astype(np.float32)])
     bad = sum(O.lib().orc_check_recip_division(float(s), 1) for s in scales)
     assert bad == 0
+    # f16 rows: scales are (an f16 row maximum) / 127; every finite f16 x
+    am = rng.integers(1, 0x7c00, 400).astype(np.uint16).view(np.float16).astype(np.float32)
+    bad = sum(O.lib().orc_check_recip_division_f16(float(s), 1) for s in (am / np.float32(127)).astype(np.float32))
+    assert bad == 0
 
 
 def test_w8a8_against_int64():
