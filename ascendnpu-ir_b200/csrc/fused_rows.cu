@@ -31,25 +31,48 @@ struct RowGeom {
 
 // Cross-thread reduction inside a row group.  `red` points at this row group's slice
 // (kMaxWarpsPerRow floats) of a shared array used by this reduction only.
+// Rows shorter than a warp's worth of vectors get 4, 8 or 16 lanes (an aligned group of the warp): the
+// shuffle steps that would cross into a neighbouring row's lanes are skipped.
 template <class Combine, class Shuffle>
 __device__ __forceinline__ float row_reduce(float v, int tpr, float *red, float identity, Combine combine,
                                             Shuffle warp_red) {
-  v = warp_red(v);
-  if (tpr == 32) return v;
+  v = warp_red(v, tpr < 32 ? tpr : 32);
+  if (tpr <= 32) return v;
   const int lane = threadIdx.x & 31;
   const int warp_in_row = (threadIdx.x % tpr) >> 5;
   const int nwarps = tpr >> 5;
   if (lane == 0) red[warp_in_row] = v;
   __syncthreads();
   float p = lane < nwarps ? red[lane] : identity;
-  p = warp_red(p);
+  p = warp_red(p, 32);
   (void)combine;
   return p;
 }
 
-__device__ __forceinline__ float warp_red_sum(float v) { return warp_sum(v); }
-__device__ __forceinline__ float warp_red_maxnan(float v) { return warp_max_nan(v); }
-__device__ __forceinline__ float warp_red_maxnum(float v) { return warp_max_num(v); }
+__device__ __forceinline__ float warp_red_sum(float v, int width = 32) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, o);
+    if (o < width) v += other;
+  }
+  return v;
+}
+__device__ __forceinline__ float warp_red_maxnan(float v, int width = 32) {  // maximumf
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, o);
+    if (o < width) v = maximumf(v, other);
+  }
+  return v;
+}
+__device__ __forceinline__ float warp_red_maxnum(float v, int width = 32) {  // fmaxf: NaN ignored
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, o);
+    if (o < width) v = fmaxf(v, other);
+  }
+  return v;
+}
 
 // hfusion.round_mode applied to an f32 value (result integral, still f32).
 __device__ __forceinline__ float round_by_mode(float x, int mode) {
@@ -603,13 +626,13 @@ __device__ __forceinline__ void store_elem(void *p, int64_t i, float v) {
 
 template <class WarpRed>
 __device__ __forceinline__ float block_reduce(float v, float *red, float identity, WarpRed warp_red) {
-  v = warp_red(v);
+  v = warp_red(v, 32);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   __syncthreads();  // red may still be read from the previous reduction
   if (lane == 0) red[warp] = v;
   __syncthreads();
   float p = lane < nw ? red[lane] : identity;
-  return warp_red(p);
+  return warp_red(p, 32);
 }
 
 enum { kRowQuant = 0, kRowRms = 1, kRowSoftmax = 2 };
@@ -663,7 +686,7 @@ int env_int(const char *name, int dflt) {
   return s && *s ? std::atoi(s) : dflt;
 }
 
-// Picks threads-per-row (TPR, a power of two in 32..1024) and vectors-per-thread (VPT).  Measured on
+// Picks threads-per-row (TPR, a power of two in 4..1024) and vectors-per-thread (VPT).  Measured on
 // B200: rows spread over enough threads that each holds about `want_vpt` vectors run fastest (4 for
 // the 8 KB rows of the benchmark shapes, 8 for the 16-bit quantiser: 64 threads per 4096-element row); `max_vpt` is what the kernel's registers can hold.
 // Register budget: 16 vectors per thread only up to 256 threads per CTA, 8 up to 512, 4 at 1024.
@@ -674,8 +697,8 @@ bool pick_geometry(int64_t rows, int64_t cols, int elem_bytes, int max_vpt, int 
   if (cols <= 0 || cols % per_vec) return false;
   const int64_t nvec = cols / per_vec;
   auto allowed = [&](int tpr) { int a = tpr <= 256 ? 16 : tpr <= 512 ? 8 : 4; return a < max_vpt ? a : max_vpt; };
-  int tpr = 32;
-  if (forced_tpr >= 32 && forced_tpr <= 1024 && (forced_tpr & (forced_tpr - 1)) == 0) {
+  int tpr = 4;
+  if (forced_tpr >= 4 && forced_tpr <= 1024 && (forced_tpr & (forced_tpr - 1)) == 0) {
     tpr = forced_tpr;
   } else {
     while (tpr < 1024 && ceil_div(nvec, tpr) > want_vpt) tpr <<= 1;

@@ -19,7 +19,7 @@ def bsir():
 
 
 # ---------------------------------------------------------------- per-token int8 quantisation
-@pytest.mark.parametrize("rows,cols", [(1, 8), (3, 64), (17, 4096), (64, 1000), (5, 8192), (2, 40000), (7, 1), (9, 33)])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (3, 64), (17, 4096), (64, 1000), (5, 8192), (2, 40000), (7, 1), (9, 33), (1001, 64), (333, 128), (77, 16), (50, 256)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 def test_quant_small_shapes_bit_exact(bsir, rows, cols, dtype):
     from bsir import workloads as W
@@ -84,7 +84,7 @@ def test_quant_strided_rows(bsir):
 RMS_RTOL, RMS_ATOL = 1e-2, 1e-3
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 8), (5, 128), (33, 4096), (4, 1000), (3, 8192), (2, 65536), (2, 70000)])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (5, 128), (33, 4096), (4, 1000), (3, 8192), (2, 65536), (2, 70000), (1001, 64), (333, 128), (77, 16), (50, 256)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 def test_rms_norm_shapes(bsir, rows, cols, dtype):
     from bsir import workloads as W
@@ -113,7 +113,7 @@ def test_rms_norm_config_shape(bsir):
 
 
 # ---------------------------------------------------------------- softmax (1e-2 rel)
-@pytest.mark.parametrize("rows,cols", [(1, 8), (4, 384), (9, 4096), (3, 1000), (2, 32768), (2, 40000), (3, 16384)])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (4, 384), (9, 4096), (3, 1000), (2, 32768), (2, 40000), (3, 16384), (1001, 64), (333, 128), (77, 16), (50, 256)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 def test_softmax_shapes(bsir, rows, cols, dtype):
     from bsir import workloads as W
