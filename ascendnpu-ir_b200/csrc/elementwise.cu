@@ -240,74 +240,118 @@ __device__ __forceinline__ typename CType<DT>::type fetch(const Operand &o, int6
 enum { kOpUnary = 0, kOpBinary = 1, kOpCompare = 2, kOpSelect = 3, kOpCopy = 4 };
 
 // ------------------------------------------------------------------ indexed (generic) path
+// Any strides (views, broadcast operands with stride 0, rank 3).  block = (columns, rows): threadIdx.x
+// runs along the innermost dimension, threadIdx.y over the collapsed outer ones, so there is one
+// division per row instead of two per element; a thread takes kIdxUnroll columns (a block apart, so
+// that a warp's accesses stay together) through one evaluation of the function switch.
+constexpr int kIdxUnroll = 4;
+
+template <int DT>
+__device__ __forceinline__ bool compare_elem_idx(int fn, typename CType<DT>::type xa, typename CType<DT>::type ya, bool *ok) {
+  using T = typename CType<DT>::type;
+  if constexpr (IsFloat<DT>::value) {
+    const float x = widen<DT>(xa), y = widen<DT>(ya);
+    switch (fn) {
+      case BSIR_CMP_VEQ: return x == y;
+      case BSIR_CMP_VNE: return !(x == y);  // unordered-or-not-equal
+      case BSIR_CMP_VLE: return x <= y;
+      case BSIR_CMP_VLT: return x < y;
+      case BSIR_CMP_VGE: return x >= y;
+      case BSIR_CMP_VGT: return x > y;
+      default: *ok = false; return false;
+    }
+  } else {
+    using UT = typename Unsigned<T>::type;
+    const UT ux = static_cast<UT>(xa), uy = static_cast<UT>(ya);
+    switch (fn) {
+      case BSIR_CMP_VEQ: return xa == ya;
+      case BSIR_CMP_VNE: return xa != ya;
+      case BSIR_CMP_VLE: return xa <= ya;
+      case BSIR_CMP_VLT: return xa < ya;
+      case BSIR_CMP_VGE: return xa >= ya;
+      case BSIR_CMP_VGT: return xa > ya;
+      case BSIR_CMP_VULE: return ux <= uy;
+      case BSIR_CMP_VULT: return ux < uy;
+      case BSIR_CMP_VUGE: return ux >= uy;
+      case BSIR_CMP_VUGT: return ux > uy;
+      default: *ok = false; return false;
+    }
+  }
+}
+
 template <int DT, int KIND>
 __global__ void __launch_bounds__(256) indexed_kernel(int fn, Shape sh, Operand a, Operand b, Operand c, void *out,
                                                       int64_t os0, int64_t os1, int64_t os2, int *bad_fn) {
   using T = typename CType<DT>::type;
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= sh.total) return;
-  const int64_t i2 = idx % sh.n2;
-  const int64_t t = idx / sh.n2;
-  const int64_t i1 = t % sh.n1;
-  const int64_t i0 = t / sh.n1;
-  const int64_t o = i0 * os0 + i1 * os1 + i2 * os2;
   bool ok = true;
-  if constexpr (KIND == kOpCopy) {
-    static_cast<T *>(out)[o] = fetch<DT>(a, i0, i1, i2);
-  } else if constexpr (KIND == kOpSelect) {
-    const uint8_t cnd = fetch<BSIR_BOOL>(a, i0, i1, i2);
-    static_cast<T *>(out)[o] = cnd ? fetch<DT>(b, i0, i1, i2) : fetch<DT>(c, i0, i1, i2);
-  } else if constexpr (KIND == kOpCompare) {
-    bool r = false;
-    if constexpr (IsFloat<DT>::value) {
-      const float x = widen<DT>(fetch<DT>(a, i0, i1, i2)), y = widen<DT>(fetch<DT>(b, i0, i1, i2));
-      switch (fn) {
-        case BSIR_CMP_VEQ: r = x == y; break;
-        case BSIR_CMP_VNE: r = !(x == y); break;  // unordered-or-not-equal
-        case BSIR_CMP_VLE: r = x <= y; break;
-        case BSIR_CMP_VLT: r = x < y; break;
-        case BSIR_CMP_VGE: r = x >= y; break;
-        case BSIR_CMP_VGT: r = x > y; break;
-        default: ok = false;
+  const int64_t nrows = sh.n0 * sh.n1;
+  const int64_t col_step = static_cast<int64_t>(gridDim.x) * blockDim.x * kIdxUnroll;
+  for (int64_t row = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; row < nrows;
+       row += static_cast<int64_t>(gridDim.y) * blockDim.y) {
+    const int64_t i0 = row / sh.n1, i1 = row - i0 * sh.n1;
+    const int64_t obase = i0 * os0 + i1 * os1;
+    for (int64_t c0 = static_cast<int64_t>(blockIdx.x) * blockDim.x * kIdxUnroll + threadIdx.x; c0 < sh.n2; c0 += col_step) {
+      int64_t i2[kIdxUnroll];
+      bool in[kIdxUnroll];
+#pragma unroll
+      for (int u = 0; u < kIdxUnroll; ++u) {
+        i2[u] = c0 + static_cast<int64_t>(u) * blockDim.x;
+        in[u] = i2[u] < sh.n2;
+        if (!in[u]) i2[u] = c0;                    // a valid address; the result is not stored
       }
-    } else {
-      using UT = typename Unsigned<T>::type;
-      const T x = fetch<DT>(a, i0, i1, i2), y = fetch<DT>(b, i0, i1, i2);
-      const UT ux = static_cast<UT>(x), uy = static_cast<UT>(y);
-      switch (fn) {
-        case BSIR_CMP_VEQ: r = x == y; break;
-        case BSIR_CMP_VNE: r = x != y; break;
-        case BSIR_CMP_VLE: r = x <= y; break;
-        case BSIR_CMP_VLT: r = x < y; break;
-        case BSIR_CMP_VGE: r = x >= y; break;
-        case BSIR_CMP_VGT: r = x > y; break;
-        case BSIR_CMP_VULE: r = ux <= uy; break;
-        case BSIR_CMP_VULT: r = ux < uy; break;
-        case BSIR_CMP_VUGE: r = ux >= uy; break;
-        case BSIR_CMP_VUGT: r = ux > uy; break;
-        default: ok = false;
+      if constexpr (KIND == kOpCopy) {
+        T v[kIdxUnroll];
+#pragma unroll
+        for (int u = 0; u < kIdxUnroll; ++u) v[u] = fetch<DT>(a, i0, i1, i2[u]);
+#pragma unroll
+        for (int u = 0; u < kIdxUnroll; ++u)
+          if (in[u]) static_cast<T *>(out)[obase + i2[u] * os2] = v[u];
+      } else if constexpr (KIND == kOpSelect) {
+#pragma unroll
+        for (int u = 0; u < kIdxUnroll; ++u) {
+          const uint8_t cnd = fetch<BSIR_BOOL>(a, i0, i1, i2[u]);
+          const T v = cnd ? fetch<DT>(b, i0, i1, i2[u]) : fetch<DT>(c, i0, i1, i2[u]);
+          if (in[u]) static_cast<T *>(out)[obase + i2[u] * os2] = v;
+        }
+      } else if constexpr (KIND == kOpCompare) {
+        T x[kIdxUnroll], y[kIdxUnroll];
+#pragma unroll
+        for (int u = 0; u < kIdxUnroll; ++u) { x[u] = fetch<DT>(a, i0, i1, i2[u]); y[u] = fetch<DT>(b, i0, i1, i2[u]); }
+#pragma unroll
+        for (int u = 0; u < kIdxUnroll; ++u) {
+          const bool r = compare_elem_idx<DT>(fn, x[u], y[u], &ok);
+          if (in[u]) static_cast<uint8_t *>(out)[obase + i2[u] * os2] = r ? 1 : 0;
+        }
+      } else if constexpr (IsFloat<DT>::value) {
+        float x[kIdxUnroll], y[kIdxUnroll], r[kIdxUnroll];
+#pragma unroll
+        for (int u = 0; u < kIdxUnroll; ++u) {
+          x[u] = widen<DT>(fetch<DT>(a, i0, i1, i2[u]));
+          if constexpr (KIND == kOpBinary) y[u] = widen<DT>(fetch<DT>(b, i0, i1, i2[u]));
+          r[u] = 0.0f;
+        }
+        if constexpr (KIND == kOpUnary) ok = unary_f32<kIdxUnroll>(fn, x, r) && ok;
+        else ok = binary_f32<kIdxUnroll>(fn, x, y, r) && ok;
+#pragma unroll
+        for (int u = 0; u < kIdxUnroll; ++u)
+          if (in[u]) static_cast<T *>(out)[obase + i2[u] * os2] = narrow<DT>(r[u]);
+      } else {
+        T x[kIdxUnroll], y[kIdxUnroll], r[kIdxUnroll];
+#pragma unroll
+        for (int u = 0; u < kIdxUnroll; ++u) {
+          x[u] = fetch<DT>(a, i0, i1, i2[u]);
+          if constexpr (KIND == kOpBinary) y[u] = fetch<DT>(b, i0, i1, i2[u]);
+          r[u] = 0;
+        }
+        if constexpr (KIND == kOpUnary) ok = unary_int<T, kIdxUnroll>(fn, x, r) && ok;
+        else ok = binary_int<T, kIdxUnroll>(fn, x, y, r) && ok;
+#pragma unroll
+        for (int u = 0; u < kIdxUnroll; ++u) {
+          if constexpr (DT == BSIR_BOOL) r[u] &= 1;
+          if (in[u]) static_cast<T *>(out)[obase + i2[u] * os2] = r[u];
+        }
       }
     }
-    static_cast<uint8_t *>(out)[o] = r ? 1 : 0;
-  } else if constexpr (IsFloat<DT>::value) {
-    float x = widen<DT>(fetch<DT>(a, i0, i1, i2)), r = 0.0f;
-    if constexpr (KIND == kOpUnary) {
-      ok = unary_f32<1>(fn, &x, &r);
-    } else {
-      float y = widen<DT>(fetch<DT>(b, i0, i1, i2));
-      ok = binary_f32<1>(fn, &x, &y, &r);
-    }
-    static_cast<T *>(out)[o] = narrow<DT>(r);
-  } else {
-    T x = fetch<DT>(a, i0, i1, i2), r = 0;
-    if constexpr (KIND == kOpUnary) {
-      ok = unary_int<T, 1>(fn, &x, &r);
-    } else {
-      T y = fetch<DT>(b, i0, i1, i2);
-      ok = binary_int<T, 1>(fn, &x, &y, &r);
-    }
-    if constexpr (DT == BSIR_BOOL) r &= 1;
-    static_cast<T *>(out)[o] = r;
   }
   if (!ok && bad_fn) *bad_fn = 1;
 }
@@ -640,10 +684,14 @@ int32_t launch_typed(const char *what, int fn, const Prepared &p, const Operand 
       return check_launch(what);
     }
   }
-  const int64_t blocks = ceil_div(n, 256);
-  if (blocks > 0x7fffffffLL) return fail(BSIR_ERR_SHAPE, "%s: %lld elements exceed the indexed path", what, (long long)n);
-  indexed_kernel<DT, KIND><<<static_cast<unsigned>(blocks), 256, 0, st>>>(fn, p.sh, a, b, c, out, p.os[0], p.os[1],
-                                                                         p.os[2], nullptr);
+  int bx = 256;                                  // threads along the innermost dimension
+  while (bx > 1 && bx / 2 >= p.sh.n2) bx >>= 1;
+  const int by = 256 / bx;
+  int64_t gx = ceil_div(p.sh.n2, static_cast<int64_t>(bx) * kIdxUnroll), gy = ceil_div(p.sh.n0 * p.sh.n1, by);
+  if (gx > 0x7fffffffLL) gx = 0x7fffffffLL;     // the kernel loops over what the grid does not cover
+  if (gy > 65535) gy = 65535;
+  indexed_kernel<DT, KIND><<<dim3(static_cast<unsigned>(gx), static_cast<unsigned>(gy)), dim3(bx, by), 0, st>>>(
+      fn, p.sh, a, b, c, out, p.os[0], p.os[1], p.os[2], nullptr);
   count_launch();
   return check_launch(what);
 }

@@ -208,33 +208,38 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
       return;
     }
   }
-  // general path: IEEE divide per element, any round mode, saturating conversion
+  // general path: IEEE divide per element, any round mode, saturating conversion.  The round mode is
+  // decided once: rint (the default) is one cvt.rni, which saturates at the int32 range and maps NaN to 0.
+  auto run = [&](auto conv) {
 #pragma unroll
-  for (int i = 0; i < VPT; ++i) {
-    const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
-    if (vi >= g.nvec) continue;
-    uint32_t bytes[kPerVec / 4];
+    for (int i = 0; i < VPT; ++i) {
+      const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
+      if (vi >= g.nvec) continue;
+      uint32_t bytes[kPerVec / 4];
 #pragma unroll
-    for (int w4 = 0; w4 < kPerVec / 4; ++w4) {
-      float e[4];
-      if constexpr (kPerWord == 2) {
-        FloatTraits<DT>::unpack(v[i].w[2 * w4], e);
-        FloatTraits<DT>::unpack(v[i].w[2 * w4 + 1], e + 2);
-      } else {
+      for (int w4 = 0; w4 < kPerVec / 4; ++w4) {
+        float e[4];
+        if constexpr (kPerWord == 2) {
+          FloatTraits<DT>::unpack(v[i].w[2 * w4], e);
+          FloatTraits<DT>::unpack(v[i].w[2 * w4 + 1], e + 2);
+        } else {
 #pragma unroll
-        for (int k = 0; k < 4; ++k) e[k] = __uint_as_float(v[i].w[k]);
+          for (int k = 0; k < 4; ++k) e[k] = __uint_as_float(v[i].w[k]);
+        }
+        uint32_t b[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) b[k] = static_cast<uint32_t>(conv(__fdiv_rn(e[k], scale)));
+        bytes[w4] = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
       }
-      uint32_t b[4];
-#pragma unroll
-      for (int k = 0; k < 4; ++k) b[k] = static_cast<uint32_t>(sat_i8(round_by_mode(__fdiv_rn(e[k], scale), round_mode)));
-      bytes[w4] = (b[0] & 0xffu) | ((b[1] & 0xffu) << 8) | ((b[2] & 0xffu) << 16) | (b[3] << 24);
+      if constexpr (kPerVec == 8) {
+        *reinterpret_cast<uint2 *>(qrow + vi * 8) = make_uint2(bytes[0], bytes[1]);
+      } else {
+        *reinterpret_cast<uint32_t *>(qrow + vi * 4) = bytes[0];
+      }
     }
-    if constexpr (kPerVec == 8) {
-      *reinterpret_cast<uint2 *>(qrow + vi * 8) = make_uint2(bytes[0], bytes[1]);
-    } else {
-      *reinterpret_cast<uint32_t *>(qrow + vi * 4) = bytes[0];
-    }
-  }
+  };
+  if (round_mode == BSIR_ROUND_RINT) run([](float d) { return max(-128, min(127, __float2int_rn(d))); });
+  else run([&](float d) { return sat_i8(round_by_mode(d, round_mode)); });
 }
 
 // ------------------------------------------------------------------ RMSNorm
@@ -680,6 +685,196 @@ __global__ void __launch_bounds__(256) rows_multipass_kernel(int64_t rows, int64
   }
 }
 
+// ------------------------------------------------------------------ rows longer than the on-chip kernels hold
+// A row of more than 64 KB (a softmax over a 150k-entry vocabulary, say) does not fit the registers or the
+// shared memory of one CTA.  It is cut into parts of 2048 vectors (32 KB, eight vectors per thread of a
+// 256-thread CTA).  Pass one leaves one statistic per (row, part) in a scratch array: the part's
+// max|x| (quantiser), its sum of squares (RMSNorm), or its maximum and the sum of exp(x - that maximum)
+// (softmax).  Pass two combines a row's statistics in part order -- every CTA of the row does it for
+// itself, the numbers are few -- and streams its part again, now mostly from L2, to produce the output.
+// Element arithmetic is that of the kernels above.
+constexpr int kLongPartVecs = 2048;
+struct LongStat { float a, b; };
+
+template <int DT>
+__device__ __forceinline__ void long_load(const void *xp, int64_t x_stride, int64_t row, int64_t v0, int64_t nvec,
+                                          Vec16 (&v)[8], bool (&have)[8]) {
+  using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
+  const Vec16 *xv = reinterpret_cast<const Vec16 *>(static_cast<const E *>(xp) + row * x_stride);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int64_t vi = v0 + threadIdx.x + i * 256;
+    have[i] = vi < nvec;
+    if (have[i]) v[i] = ld_stream(xv + vi);
+  }
+}
+
+template <int DT, int OP>
+__global__ void __launch_bounds__(256) rows_long_stat_kernel(int64_t row0, int64_t nvec, const void *__restrict__ xp,
+                                                             int64_t x_stride, LongStat *__restrict__ stats, int nparts) {
+  constexpr int kPerWord = FloatTraits<DT>::kPerWord;
+  __shared__ float red[32];
+  const int64_t row = row0 + blockIdx.y;
+  const int part = blockIdx.x;
+  Vec16 v[8];
+  bool have[8];
+  long_load<DT>(xp, x_stride, row, static_cast<int64_t>(part) * kLongPartVecs, nvec, v, have);
+  auto for_each = [&](auto f) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (have[i]) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          float e[kPerWord];
+          FloatTraits<DT>::unpack(v[i].w[w], e);
+#pragma unroll
+          for (int k = 0; k < kPerWord; ++k) f(e[k]);
+        }
+      }
+  };
+  LongStat st{0.0f, 0.0f};
+  if constexpr (OP == kRowQuant) {
+    float amax = 0.0f;
+    for_each([&](float x) { amax = maximumf(amax, fabsf(x)); });
+    st.a = block_reduce(amax, red, 0.0f, warp_red_maxnan);
+  } else if constexpr (OP == kRowRms) {
+    float ss = 0.0f;
+    for_each([&](float x) { ss = __fmaf_rn(x, x, ss); });
+    st.a = block_reduce(ss, red, 0.0f, warp_red_sum);
+  } else {
+    const float ninf = __int_as_float(0xff800000);
+    float m = ninf, nans = 0.0f;
+    for_each([&](float x) { m = fmaxf(m, x); if (x != x) nans = 1.0f; });
+    m = block_reduce(m, red, ninf, warp_red_maxnum);
+    nans = block_reduce(nans, red, 0.0f, warp_red_sum);
+    const float l2e = 1.4426950408889634f, nm = -m * l2e;
+    float s = 0.0f;
+    for_each([&](float x) { s += ex2_approx(__fmaf_rn(x, l2e, nm)); });
+    s = block_reduce(s, red, 0.0f, warp_red_sum);
+    // a part whose maximum is -inf holds no finite value: it adds nothing, unless it holds a NaN
+    if (m == ninf) s = nans > 0.0f ? __int_as_float(0x7fc00000) : 0.0f;
+    st.a = m;
+    st.b = s;
+  }
+  if (threadIdx.x == 0) stats[static_cast<int64_t>(blockIdx.y) * nparts + part] = st;
+}
+
+template <int DT, int OP>
+__global__ void __launch_bounds__(256) rows_long_apply_kernel(int64_t row0, int64_t nvec, const void *__restrict__ xp,
+                                                              int64_t x_stride, const void *__restrict__ gammap, float eps,
+                                                              float avg, void *__restrict__ yp, int64_t y_stride,
+                                                              void *__restrict__ aux, int round_mode,
+                                                              const LongStat *__restrict__ stats, int nparts) {
+  constexpr int kPerWord = FloatTraits<DT>::kPerWord;
+  constexpr int kPerVec = 4 * kPerWord;
+  using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
+  const int64_t row = row0 + blockIdx.y;
+  const int part = blockIdx.x;
+  const int64_t v0 = static_cast<int64_t>(part) * kLongPartVecs;
+  Vec16 v[8];
+  bool have[8];
+  long_load<DT>(xp, x_stride, row, v0, nvec, v, have);       // in flight while the statistics are combined
+  const LongStat *rs = stats + static_cast<int64_t>(blockIdx.y) * nparts;
+  if constexpr (OP == kRowQuant) {
+    float amax = 0.0f;
+    for (int p = 0; p < nparts; ++p) amax = maximumf(amax, rs[p].a);
+    const float scale = __fdiv_rn(amax, 127.0f);
+    if (part == 0 && threadIdx.x == 0) static_cast<float *>(aux)[row] = scale;
+    const bool degenerate = !(amax > 0.0f && amax < __int_as_float(0x7f800000));
+    const bool fast = (DT == BSIR_BF16 || DT == BSIR_F16) && round_mode == BSIR_ROUND_RINT && scale > 8.6736174e-19f &&
+                      scale < 1.1529215e18f;
+    const float rcp = __frcp_rn(scale);
+    int8_t *qrow = static_cast<int8_t *>(yp) + row * y_stride;
+    // one loop per case, so that the case is decided once and not per element
+    auto run = [&](auto conv) {   // conv(x) -> a word whose low byte is the int8 result
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (!have[i]) continue;
+        const int64_t vi = v0 + threadIdx.x + i * 256;
+        uint32_t b[kPerVec];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          float e[kPerWord];
+          FloatTraits<DT>::unpack(v[i].w[w], e);
+#pragma unroll
+          for (int k = 0; k < kPerWord; ++k) b[w * kPerWord + k] = conv(e[k]);
+        }
+        // byte 0 of each result -> packed words
+        const uint32_t p01 = __byte_perm(b[0], b[1], 0x0040), p23 = __byte_perm(b[2], b[3], 0x0040);
+        if constexpr (kPerVec == 8) {
+          const uint32_t p45 = __byte_perm(b[4], b[5], 0x0040), p67 = __byte_perm(b[6], b[7], 0x0040);
+          *reinterpret_cast<uint2 *>(qrow + vi * 8) = make_uint2(__byte_perm(p01, p23, 0x5410), __byte_perm(p45, p67, 0x5410));
+        } else {
+          *reinterpret_cast<uint32_t *>(qrow + vi * 4) = __byte_perm(p01, p23, 0x5410);
+        }
+      }
+    };
+    if (degenerate) {
+      run([](float) { return 0u; });
+    } else if (fast) {
+      // the reciprocal form of the register kernel: same operations, one element at a time
+      const float nscale = -scale;
+      run([&](float x) {
+        const float q0 = __fmul_rn(x, rcp);
+        return __float_as_uint(__fadd_rn(__fmaf_rn(__fmaf_rn(q0, nscale, x), rcp, q0), 12582912.0f));
+      });
+    } else {
+      run([&](float x) { return static_cast<uint32_t>(sat_i8(round_by_mode(__fdiv_rn(x, scale), round_mode))); });
+    }
+  } else if constexpr (OP == kRowRms) {
+    float ss = 0.0f;
+    for (int p = 0; p < nparts; ++p) ss += rs[p].a;
+    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fmul_rn(ss, avg), eps)));
+    if (aux && part == 0 && threadIdx.x == 0) store_elem<DT>(aux, row, rstd);
+    E *yrow = static_cast<E *>(yp) + row * y_stride;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (!have[i]) continue;
+      const int64_t vi = v0 + threadIdx.x + i * 256;
+      const Vec16 gv = *(reinterpret_cast<const Vec16 *>(gammap) + vi);
+      Vec16 o;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        float e[kPerWord], ge[kPerWord], r[kPerWord];
+        FloatTraits<DT>::unpack(v[i].w[w], e);
+        FloatTraits<DT>::unpack(gv.w[w], ge);
+#pragma unroll
+        for (int k = 0; k < kPerWord; ++k) r[k] = __fmul_rn(ge[k], __fmul_rn(rstd, e[k]));
+        o.w[w] = FloatTraits<DT>::pack(r);
+      }
+      st_stream(reinterpret_cast<Vec16 *>(yrow) + vi, o);
+    }
+  } else {
+    const float ninf = __int_as_float(0xff800000);
+    const float l2e = 1.4426950408889634f;
+    float m = ninf;
+    for (int p = 0; p < nparts; ++p) m = fmaxf(m, rs[p].a);
+    float s = 0.0f;
+    for (int p = 0; p < nparts; ++p) s += rs[p].b * ex2_approx((rs[p].a - m) * l2e);   // weight 1 for the part that holds m
+    const float nm = -m * l2e, rcp = __frcp_rn(s);
+    E *yrow = static_cast<E *>(yp) + row * y_stride;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (!have[i]) continue;
+      const int64_t vi = v0 + threadIdx.x + i * 256;
+      Vec16 o;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        float e[kPerWord], r[kPerWord];
+        FloatTraits<DT>::unpack(v[i].w[w], e);
+#pragma unroll
+        for (int k = 0; k < kPerWord; ++k) {
+          const float ex = ex2_approx(__fmaf_rn(e[k], l2e, nm));
+          const float q0 = __fmul_rn(ex, rcp);
+          r[k] = DT == BSIR_F32 ? __fmaf_rn(__fmaf_rn(q0, -s, ex), rcp, q0) : q0;
+        }
+        o.w[w] = FloatTraits<DT>::pack(r);
+      }
+      st_stream(reinterpret_cast<Vec16 *>(yrow) + vi, o);
+    }
+  }
+}
+
 // ------------------------------------------------------------------ host side
 int env_int(const char *name, int dflt) {
   const char *s = std::getenv(name);
@@ -741,6 +936,30 @@ bool rows_vector_ok(const void *p, int64_t stride_elems, int elem_bytes) {
     default: { constexpr int D = BSIR_BF16; __VA_ARGS__; break; }        \
   }
 
+// Both passes of the long-row path; rows beyond a grid dimension go in slabs.
+template <int OP>
+int32_t launch_long_rows(const char *what, int32_t dtype, int64_t rows, int64_t cols, const void *x, int64_t xs,
+                         const void *gamma, float eps, float avg, void *y, int64_t ys, void *aux, int round_mode,
+                         cudaStream_t st) {
+  const int eb = dtype_bytes(dtype);
+  const int64_t nvec = cols / (16 / eb);
+  const int nparts = static_cast<int>(ceil_div(nvec, kLongPartVecs));
+  const int64_t slab = rows < 65535 ? rows : 65535;
+  char *ws = static_cast<char *>(device_workspace(kScratchCounterBytes + static_cast<size_t>(slab) * nparts * sizeof(LongStat), st));
+  if (!ws) return BSIR_ERR_WORKSPACE;
+  LongStat *stats = reinterpret_cast<LongStat *>(ws + kScratchCounterBytes);
+  for (int64_t r0 = 0; r0 < rows; r0 += slab) {
+    const int64_t nr = rows - r0 < slab ? rows - r0 : slab;
+    const dim3 grid(static_cast<unsigned>(nparts), static_cast<unsigned>(nr));
+    DISPATCH_FLOAT_DT(dtype, {
+      rows_long_stat_kernel<D, OP><<<grid, 256, 0, st>>>(r0, nvec, x, xs, stats, nparts);
+      rows_long_apply_kernel<D, OP><<<grid, 256, 0, st>>>(r0, nvec, x, xs, gamma, eps, avg, y, ys, aux, round_mode, stats, nparts);
+    });
+    count_launch(2);
+  }
+  return check_launch(what);
+}
+
 int32_t check_rows_args(const char *what, int32_t dtype, int64_t rows, int64_t cols, const void *x, int64_t xs,
                         const void *y, int64_t ys) {
   if (!dtype_is_float(dtype)) return fail(BSIR_ERR_DTYPE, "%s: dtype %d (f32, f16 or bf16 required)", what, dtype);
@@ -773,8 +992,12 @@ int32_t bsir_quant_per_token_i8(int32_t dtype, int32_t round_mode, int64_t rows,
   RowGeom g;
   int vpt = 0;
   const int per_vec = 16 / eb;
-  const bool vec_ok = cols > 0 && rows_vector_ok(x, x_row_stride, eb) && aligned_to(q, per_vec) && q_row_stride % per_vec == 0 &&
-                      pick_geometry(rows, cols, eb, 16, eb == 2 ? 8 : 4, env_int("BSIR_QUANT_TPR", 0), &g, &vpt);
+  const bool aligned_ok = cols > 0 && cols % per_vec == 0 && rows_vector_ok(x, x_row_stride, eb) && aligned_to(q, per_vec) &&
+                          q_row_stride % per_vec == 0;
+  const bool vec_ok = aligned_ok && pick_geometry(rows, cols, eb, 16, eb == 2 ? 8 : 4, env_int("BSIR_QUANT_TPR", 0), &g, &vpt);
+  if (aligned_ok && !vec_ok)   // the row does not fit one CTA's registers
+    return launch_long_rows<kRowQuant>("quant_per_token_i8", dtype, rows, cols, x, x_row_stride, nullptr, 0.0f, 0.0f, q,
+                                       q_row_stride, scale, round_mode, st);
   if (vec_ok) {
     const unsigned blocks = static_cast<unsigned>(ceil_div(rows, g.rpc));
     const unsigned threads = static_cast<unsigned>(g.tpr * g.rpc);
@@ -802,8 +1025,11 @@ int32_t bsir_rms_norm(int32_t dtype, int64_t rows, int64_t cols, const void *x, 
   const float avg = 1.0f / static_cast<float>(static_cast<uint32_t>(cols));
   RowGeom g;
   int vpt = 0;
-  const bool vec_ok = cols > 0 && rows_vector_ok(x, x_row_stride, eb) && rows_vector_ok(y, y_row_stride, eb) &&
-                      aligned_to(gamma, 16) && pick_geometry(rows, cols, eb, 16, 4, env_int("BSIR_RMS_TPR", 0), &g, &vpt);
+  const bool aligned_ok = cols > 0 && cols % (16 / eb) == 0 && rows_vector_ok(x, x_row_stride, eb) &&
+                          rows_vector_ok(y, y_row_stride, eb) && aligned_to(gamma, 16);
+  const bool vec_ok = aligned_ok && pick_geometry(rows, cols, eb, 16, 4, env_int("BSIR_RMS_TPR", 0), &g, &vpt);
+  if (aligned_ok && !vec_ok)
+    return launch_long_rows<kRowRms>("rms_norm", dtype, rows, cols, x, x_row_stride, gamma, eps, avg, y, y_row_stride, rstd_out, 0, st);
   if (vec_ok) {
     const unsigned blocks = static_cast<unsigned>(ceil_div(rows, g.rpc));
     const unsigned threads = static_cast<unsigned>(g.tpr * g.rpc);
@@ -829,8 +1055,10 @@ int32_t bsir_softmax(int32_t dtype, int64_t rows, int64_t cols, const void *x, i
   int vpt = 0;
   // exp values live in registers: at most 32 per thread
   const int max_vpt = eb == 4 ? 8 : 4;
-  const bool vec_ok = rows_vector_ok(x, x_row_stride, eb) && rows_vector_ok(y, y_row_stride, eb) &&
-                      pick_geometry(rows, cols, eb, max_vpt, 4, env_int("BSIR_SOFTMAX_TPR", 0), &g, &vpt);
+  const bool aligned_ok = cols % (16 / eb) == 0 && rows_vector_ok(x, x_row_stride, eb) && rows_vector_ok(y, y_row_stride, eb);
+  const bool vec_ok = aligned_ok && pick_geometry(rows, cols, eb, max_vpt, 4, env_int("BSIR_SOFTMAX_TPR", 0), &g, &vpt);
+  if (aligned_ok && !vec_ok)
+    return launch_long_rows<kRowSoftmax>("softmax", dtype, rows, cols, x, x_row_stride, nullptr, 0.0f, 0.0f, y, y_row_stride, nullptr, 0, st);
   // long rows: persistent CTAs with the rows streamed through shared memory by bulk copies
   const bool want_stream = env_int("BSIR_SOFTMAX_STREAM", 1) != 0;
   if (vec_ok && want_stream && g.tpr == 1024 && g.nvec >= 2048 && g.nvec * 16 <= 65536 && device_info().cc_major >= 9) {

@@ -152,6 +152,40 @@ def test_softmax_special_rows(bsir):
     assert_close(y, wy, 1e-2, 1e-7, what="softmax special")
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_long_rows_two_pass_path(bsir, dtype):
+    """Rows of more than 64 KB are cut into 32 KB parts (statistics pass, then apply pass): the three fused row ops
+    on a vocabulary-sized row, with parts that are all -inf, a NaN inside such a part, +inf, an all -inf row."""
+    cols = 152064 if dtype == torch.bfloat16 else 50048
+    g = torch.Generator(device="cuda").manual_seed(21)
+    x = (3 * torch.randn(9, cols, device="cuda", generator=g)).to(dtype)
+    part = 2048 * (8 if dtype == torch.bfloat16 else 4)          # elements per part
+    x[1, part:2 * part] = -float("inf")                           # a whole part adds nothing
+    x[2, part:2 * part] = -float("inf")
+    x[2, part + 17] = float("nan")                                # ... unless it hides a NaN
+    x[3] = -float("inf")                                          # (-inf) - (-inf) = NaN everywhere
+    x[4, 5 * part + 3] = float("inf")
+    x[5, 7] = float("nan")
+    x[6, :] = 2.0
+    x[7, 1:] = -float("inf")
+    y = bsir.softmax(x)
+    wy = O.softmax(oracle_dtype(x), to_bits(x))
+    assert_close(y, wy, 1e-2 if dtype == torch.bfloat16 else cols * 6e-9 + 1e-5, 1e-7, what="softmax long rows")
+    # quantiser: bit-exact as for short rows
+    xq = x.clone()
+    xq[[2, 3, 4, 5, 7]] = (3 * torch.randn(5, cols, device="cuda", generator=g)).to(dtype)
+    xq[3] = 0
+    q, sc = bsir.quant_per_token_i8(xq)
+    wq, ws = O.quant_per_token_i8(oracle_dtype(xq), to_bits(xq))
+    assert np.array_equal(q.cpu().numpy(), wq) and np.array_equal(sc.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+    # RMSNorm
+    gamma = (1 + 0.02 * torch.randn(cols, device="cuda", generator=g)).to(dtype)
+    yn, rstd = bsir.rms_norm(xq, gamma, 1e-6, want_rstd=True)
+    wn, wr = O.rms_norm(oracle_dtype(xq), to_bits(xq), to_bits(gamma), 1e-6, want_rstd=True)
+    assert_close(yn, wn, 1e-2 if dtype == torch.bfloat16 else 1e-4, 1e-3, what="rms_norm long rows")
+    assert_close(rstd, wr, 1e-2 if dtype == torch.bfloat16 else 1e-4, 1e-6, what="rstd long rows")
+
+
 # ---------------------------------------------------------------- generic reductions
 @pytest.mark.parametrize("kind", ["sum", "prod", "max", "min"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
