@@ -14,7 +14,7 @@ Covered (attribute spellings as in the reference):
   region with one combiner op), linalg.matmul (i8 x i8 -> i32), linalg.copy
   hivm.hir.load (pad_mode / pad_value / left_padding_num / right_padding_num), hivm.hir.store (atomic = <kind>),
   hivm.hir.copy, hivm.hir.vadd / vsub / vmul / vdiv / vmax / vmin, hivm.hir.vcast, hivm.hir.vreduce <kind>
-  tensor.empty, tensor.dim, memref.alloc, arith.constant (scalars, splat `dense<..>`), arith.{addf,subf,mulf,divf,addi,subi,muli},
+  tensor.empty, tensor.dim, tensor.collapse_shape / expand_shape / reshape, tensor.extract_slice (static), linalg.transpose, memref.alloc, arith.constant (scalars, splat `dense<..>`), arith.{addf,subf,mulf,divf,addi,subi,muli},
   arith.{index_cast,index_castui,uitofp,sitofp,extf,truncf}, return
 Scalar arithmetic is done in the scalar's own type (f32 ops round to f32).  Anything else raises MlirTextError
 with the op's name, so an unsupported file fails loudly instead of computing something different.
@@ -257,6 +257,23 @@ class Function:
             elif name == "tensor.dim":
                 t_name, i_name = [n.strip() for n in _split_top(op.text.split(":")[0])]
                 define(op, [Scalar(val(t_name).shape[val(i_name).value], "index")])
+            elif name in ("tensor.collapse_shape", "tensor.expand_shape", "tensor.reshape"):
+                # `%r = tensor.collapse_shape %x [[0, 1], [2]] : tensor<AxBxCxf32> into tensor<ABxCxf32>`: a view
+                src = val(re.match(r"\s*(%[\w.]+)", op.text).group(1))
+                st = ShapedType(re.split(r"\binto\b|->", op.text)[-1])
+                define(op, [src.reshape(st.shape)])
+            elif name == "tensor.extract_slice":
+                m = re.match(r"\s*(%[\w.]+)\s*\[([^\]]*)\]\s*\[([^\]]*)\]\s*\[([^\]]*)\]", op.text)
+                if not m or "%" in m.group(2) + m.group(3) + m.group(4):
+                    raise MlirTextError("tensor.extract_slice: static offsets / sizes / strides are supported")
+                src = val(m.group(1))
+                offs, sizes, strides = ([int(v) for v in m.group(i).split(",")] for i in (2, 3, 4))
+                view = src[tuple(slice(o, o + n * st_, st_) for o, n, st_ in zip(offs, sizes, strides))]
+                st = ShapedType(op.text.rsplit(" to ", 1)[1])
+                define(op, [view.reshape(st.shape)])
+            elif name == "linalg.transpose":
+                perm = op.int_list("permutation")
+                define(op, [copy(val(ins[0]).permute(perm), out=val(outs[0]))])
             elif name == "hfusion.cast" or name == "hivm.hir.vcast":
                 dst = val(outs[0])
                 mode = op.attr("round_mode") or op.attr("mode") or "rint"

@@ -306,7 +306,8 @@ constexpr int kTcMaxStages = 8;
 constexpr int kTcABufs = 8;             // 64-k chunks of dequantised weights in TMEM (8 x 32 columns)
 constexpr int kTcDqWarps = 16;          // dequantising warps: 4 lane quadrants x 4 chunks of a stage
 constexpr int kTcMmaWarps = 4;          // fix-up + MMA-issuing warps; chunk c belongs to issuer c % 4
-constexpr int kTcThreads = (kTcDqWarps + 1 + kTcMmaWarps) * 32;
+constexpr int kTcFixWarps = 4;          // warps that put the activations into the nibble-pair order
+constexpr int kTcThreads = (kTcDqWarps + 1 + kTcMmaWarps + kTcFixWarps) * 32;
 constexpr int kTcSmemBudget = 222 * 1024;
 
 struct TcLayout {
@@ -367,7 +368,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     for (int s = 0; s < nstages; ++s) {
       mbar_init(wfull(s), 1);
       mbar_init(wempty(s), kTcDqWarps + kTcMmaWarps);
-      mbar_init(aready(s), kTcMmaWarps * 32);
+      mbar_init(aready(s), kTcFixWarps * 32);
     }
     for (int b = 0; b < kTcABufs; ++b) { mbar_init(afull(b), 4); mbar_init(aempty(b), 1); }
     mbar_init(dfull, kTcMmaWarps);
@@ -417,30 +418,25 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   if (warp == kTcDqWarps) {
     if (lane == 0) {
       bool ok = true;
+      int slot = preissued % nstages;
+      uint32_t phase = static_cast<uint32_t>(preissued / nstages) & 1u;
       for (int s = preissued; s < nstages_total; ++s) {
-        const int slot = s % nstages;
-        const uint32_t phase = static_cast<uint32_t>(s / nstages) & 1u;
         if (!mbar_wait_relaxed(wempty(slot), phase ^ 1u, abort_flag, err)) { ok = false; break; }
         issue_stage(s);
+        if (++slot == nstages) { slot = 0; phase ^= 1u; }
       }
       if (!ok)
         for (int s = 0; s < nstages; ++s)
           for (int i = 0; i < 200000; ++i)
             if (mbar_try_wait(wfull(s), 0) || mbar_try_wait(wfull(s), 1)) break;
     }
-  } else if (warp > kTcDqWarps) {
-    // ---------------- activation fix-up (all lanes) and MMA issue (lane 0)
-    // D = f32, A = B = bf16, both K-major, N = 16, M = 128
-    const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(16 >> 3) << 17) |
-                           (static_cast<uint32_t>(128 >> 4) << 24);
-    const int issuer = warp - kTcDqWarps - 1;
-    const int tix = issuer * 32 + lane;
-    uint32_t aphase = 0u;   // one parity bit per TMEM buffer
-    bool ok = true;
-    for (int s = 0; s < nstages_total && ok; ++s) {
-      const int slot = s % nstages;
-      const uint32_t phase = static_cast<uint32_t>(s / nstages) & 1u;
-      if (!mbar_wait_relaxed(wfull(slot), phase, abort_flag, err)) { ok = false; break; }
+  } else if (warp > kTcDqWarps + kTcMmaWarps) {
+    // ---------------- activation fix-up: every 16-byte piece of the stage into the nibble-pair k order
+    const int tix = (warp - kTcDqWarps - kTcMmaWarps - 1) * 32 + lane;
+    int slot = 0;
+    uint32_t phase = 0u;
+    for (int s = 0; s < nstages_total; ++s) {
+      if (!mbar_wait_relaxed(wfull(slot), phase, abort_flag, err)) break;
       uint8_t *act = gen + slot * kTcStageBytes + kTcWeightBytes;
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -455,26 +451,40 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       }
       fence_proxy_async();
       mbar_arrive(aready(slot));
-      if (lane != 0) continue;
-      const int c = s * 4 + issuer;
-      if (c < nchunks) {
-        const int b = c % kTcABufs;
-        if (!mbar_wait(aready(slot), phase, abort_flag, err)) { ok = false; break; }
-        if (!mbar_wait(afull(b), (aphase >> b) & 1u, abort_flag, err)) { ok = false; break; }
-        aphase ^= 1u << b;
-        tc_fence_after();
-        const uint32_t act_addr = base + slot * kTcStageBytes + kTcWeightBytes + static_cast<uint32_t>(issuer) * 2048u;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)   // 4 x K=16 per 64-k chunk; 8 TMEM columns and 32 bytes of smem each
-          mma_f16_ts(tmem_d + static_cast<uint32_t>(issuer * 16), tmem_a0 + static_cast<uint32_t>(b * 32 + j * 8),
-                     make_desc(act_addr + j * 32, 16, 1024), idesc, (c >= kTcMmaWarps || j > 0) ? 1u : 0u);
-        tc_commit(aempty(b));
-        tc_commit(wempty(slot));    // the stage's activations are free once these MMAs have read them
-      } else {
-        mbar_arrive(wempty(slot));
-      }
+      if (++slot == nstages) { slot = 0; phase ^= 1u; }
     }
-    if (lane == 0) tc_commit(dfull);   // arrives once this issuer's MMAs are done (immediately if it had none)
+  } else if (warp > kTcDqWarps) {
+    // ---------------- MMA issue: one thread per warp, chunk c of a stage belongs to issuer c
+    // D = f32, A = B = bf16, both K-major, N = 16, M = 128
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(16 >> 3) << 17) |
+                             (static_cast<uint32_t>(128 >> 4) << 24);
+      const int issuer = warp - kTcDqWarps - 1;
+      uint32_t aphase = 0u;   // one parity bit per TMEM buffer
+      int slot = 0;
+      uint32_t phase = 0u;
+      for (int s = 0; s < nstages_total; ++s) {
+        const int c = s * 4 + issuer;
+        if (c < nchunks) {
+          const int b = c % kTcABufs;
+          if (!mbar_wait(aready(slot), phase, abort_flag, err) || !mbar_wait(afull(b), (aphase >> b) & 1u, abort_flag, err)) break;
+          aphase ^= 1u << b;
+          tc_fence_after();
+          const uint32_t act_addr = base + slot * kTcStageBytes + kTcWeightBytes + static_cast<uint32_t>(issuer) * 2048u;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)   // 4 x K=16 per 64-k chunk; 8 TMEM columns and 32 bytes of smem each
+            mma_f16_ts(tmem_d + static_cast<uint32_t>(issuer * 16), tmem_a0 + static_cast<uint32_t>(b * 32 + j * 8),
+                       make_desc(act_addr + j * 32, 16, 1024), idesc, (c >= kTcMmaWarps || j > 0) ? 1u : 0u);
+          // one commit per chunk: when the stage's four commits and its sixteen reader arrivals are in, the
+          // stage can be refilled, and the unpackers know the tensor-memory buffers of that stage are drained
+          tc_commit(wempty(slot));
+        } else {
+          mbar_arrive(wempty(slot));
+        }
+        if (++slot == nstages) { slot = 0; phase ^= 1u; }
+      }
+      tc_commit(dfull);   // arrives once this issuer's MMAs are done (immediately if it had none)
+    }
   } else {
     // ---------------- dequantisers
     const int quad = warp & 3, sub = warp >> 2;       // sub: which chunk of every stage this warp owns
@@ -482,7 +492,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     const int64_t n = n0 + tid_n;
     const bool n_ok = n < p.n;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    uint32_t ephase = 0u;   // one parity bit per buffer
     const int chunks_per_group = static_cast<int>(p.group / 64);
     bool ok = true;
     int cur_group = -1;
@@ -499,9 +508,11 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       if (lane == 0) mbar_arrive(afull(pending_buf));
       pending_buf = -1;
     };
+    int slot = 0;
+    uint32_t phase = 0u;
+    int slot2 = 0;            // slot and phase of the stage two before this one: its MMAs read the
+    uint32_t phase2 = 0u;     // tensor-memory buffer this stage's chunk is about to overwrite
     for (int s = 0; s < nstages_total && ok; ++s) {
-      const int slot = s % nstages;
-      const uint32_t phase = static_cast<uint32_t>(s / nstages) & 1u;
       if (!mbar_wait_relaxed(wfull(slot), phase, abort_flag, err)) { ok = false; break; }
       const uint32_t *st = reinterpret_cast<const uint32_t *>(gen + slot * kTcStageBytes);
       const int cs = sub;                             // chunk of the stage this warp owns
@@ -533,15 +544,17 @@ __global__ void __launch_bounds__(kTcThreads, 1)
           }
         }
         hand_over();   // the previous chunk's store
-        // the buffer must have been drained by the MMAs that read it kTcABufs chunks ago
-        if (c >= kTcABufs) {
-          if (!mbar_wait_relaxed(aempty(b), (ephase >> b) & 1u, abort_flag, err)) { ok = false; }
-          ephase ^= 1u << b;
+        // the buffer must have been drained by the MMAs that read it kTcABufs chunks (two stages) ago:
+        // the "stage empty" barrier of that stage completes only after its four MMA commits
+        if (s >= 2) {
+          if (!mbar_wait_relaxed(wempty(slot2), phase2, abort_flag, err)) { ok = false; }
           tc_fence_after();
         }
         tmem_st32(tmem_a0 + lane_addr + static_cast<uint32_t>(b * 32), qv);
         pending_buf = b;
       }
+      if (s >= 2 && ++slot2 == nstages) { slot2 = 0; phase2 ^= 1u; }
+      if (++slot == nstages) { slot = 0; phase ^= 1u; }
     }
     hand_over();
     // ---------------- epilogue: the four warps of half 0 read the accumulator

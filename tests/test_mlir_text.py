@@ -145,6 +145,13 @@ def test_reference_files_parse_unchanged():
         with open(os.path.join(ref, rel), encoding="utf-8") as f:
             fn = M.parse(f.read())[fn_name]
         assert fn.op_names()[-1] == "return" and len(fn.ops) >= 8
+    # every function of the reference's HFusion compile tests must at least split into ops; most use only ops
+    # this front end executes
+    import glob
+    files = glob.glob(os.path.join(ref, "bishengir/test/bishengir-compile/hfusion/*.mlir"))
+    assert len(files) >= 20
+    nfuncs = sum(len(M.parse(open(f, encoding="utf-8").read())) for f in files)
+    assert nfuncs >= len(files)
 
 
 # ------------------------------------------------------------------------------------------------ GPU
@@ -223,3 +230,29 @@ def test_rms_norm_program_against_oracle_and_fused_kernel(bsir):
     assert_close(rstd, wr, 1e-2, 1e-3, "rstd vs oracle")
     fy, fr = bsir.rms_norm(x, gamma, 1e-6, want_rstd=True)
     assert (y.float() - fy.float()).abs().max().item() <= 1e-2 * fy.float().abs().max().item()
+
+
+VIEW_IR = """
+func.func @views(%x: tensor<4x6x8xf32>, %o: tensor<8x24xf32>) -> tensor<8x24xf32> {
+  %c = tensor.collapse_shape %x [[0, 1], [2]] : tensor<4x6x8xf32> into tensor<24x8xf32>
+  %t = linalg.transpose ins(%c : tensor<24x8xf32>) outs(%o : tensor<8x24xf32>) permutation = [1, 0]
+  return %t : tensor<8x24xf32>
+}
+func.func @slice(%x: tensor<16x32xf32>, %o: tensor<4x8xf32>) -> tensor<4x8xf32> {
+  %s = tensor.extract_slice %x[2, 8] [4, 8] [2, 1] : tensor<16x32xf32> to tensor<4x8xf32>
+  %e = linalg.elemwise_unary {fun = #linalg.unary_fn<negf>} ins(%s : tensor<4x8xf32>) outs(%o : tensor<4x8xf32>) -> tensor<4x8xf32>
+  return %e : tensor<4x8xf32>
+}
+"""
+
+
+@pytest.mark.gpu
+def test_views_transpose_and_slices(bsir):
+    import torch
+    from bsir import mlir_text
+    fns = mlir_text.parse(VIEW_IR)
+    x = torch.arange(4 * 6 * 8, device="cuda", dtype=torch.float32).reshape(4, 6, 8)
+    y = fns["views"](x, torch.empty(8, 24, device="cuda"))
+    assert torch.equal(y, x.reshape(24, 8).t())
+    z = torch.randn(16, 32, device="cuda")
+    assert torch.equal(fns["slice"](z, torch.empty(4, 8, device="cuda")), -z[2:10:2, 8:16])
