@@ -293,6 +293,121 @@ def store(x: torch.Tensor, out: torch.Tensor, atomic: str = "none") -> torch.Ten
     return out
 
 
+# ---------------------------------------------------------------------------- fused elementwise chains
+class _ChainOperand(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("row_stride", C.c_int64), ("dtype", C.c_int32), ("kind", C.c_int32)]
+
+
+class _ChainInstr(C.Structure):
+    _fields_ = [("op", C.c_int32), ("fn", C.c_int32), ("src_kind", C.c_int32), ("src", C.c_int32), ("imm", C.c_float)]
+
+
+class _ChainOutput(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("row_stride", C.c_int64), ("dtype", C.c_int32), ("tmp", C.c_int32)]
+
+
+class FusedChain:
+    """A chain of elementwise ops over a [rows, cols] problem, run as ONE kernel (``bsir_fused_elementwise``): what
+    HFusion's op fusion outlines as a PURE_ELEMWISE / ANY_PB function.  f32 arithmetic, one rounding per output.
+
+        ch = FusedChain()
+        x, g, r = ch.operand(x_t), ch.operand(gamma_t), ch.operand(rstd_t)   # [rows,cols], [cols], [rows]
+        ch.load(r); ch.binary("mul", x); ch.rbinary("mul", g)               # gamma * (rstd * x)
+        y = ch.run(out_dtype=torch.bfloat16)
+
+    An operand's shape decides how it is broadcast: [rows, cols] full, [cols] or [1, cols] the same for every row,
+    [rows] (when rows != cols) or [rows, 1] one value per row, a 0-d / 1-element tensor a scalar.  ``src`` of an
+    instruction is an operand handle, ``("tmp", k)`` or a Python number (immediate)."""
+
+    def __init__(self):
+        self._ops, self._tape, self._shape = [], [], None
+
+    def operand(self, t: torch.Tensor, kind: Optional[str] = None) -> int:
+        self._ops.append((t, kind))
+        return len(self._ops) - 1
+
+    def _src(self, src):
+        if isinstance(src, tuple):
+            return 1, int(src[1]), 0.0
+        if isinstance(src, (float, int)) and not isinstance(src, bool):
+            return 2, 0, float(src)
+        raise BsirError(-5, "source must be an operand handle (use .op(handle)), ('tmp', k) or a number")
+
+    def op(self, handle: int):
+        """Marks an operand handle as a source (plain ints are immediates)."""
+        return ("operand", handle)
+
+    def _emit(self, op, fn, src):
+        if isinstance(src, tuple) and src[0] == "operand":
+            kind, idx, imm = 0, int(src[1]), 0.0
+        elif src is None:
+            kind, idx, imm = 0, 0, 0.0
+        else:
+            kind, idx, imm = self._src(src)
+        self._tape.append((op, fn, kind, idx, imm))
+        return self
+
+    def load(self, src):
+        return self._emit(0, 0, src)
+
+    def unary(self, fun: str):
+        return self._emit(1, UNARY_FN[fun], None)
+
+    def binary(self, fun: str, src):
+        """acc = fun(acc, src)"""
+        return self._emit(2, BINARY_FN[fun], src)
+
+    def rbinary(self, fun: str, src):
+        """acc = fun(src, acc)"""
+        return self._emit(3, BINARY_FN[fun], src)
+
+    def save(self, tmp: int):
+        self._tape.append((4, 0, 1, int(tmp), 0.0))
+        return self
+
+    def run(self, rows: Optional[int] = None, cols: Optional[int] = None, out_dtype: Optional[torch.dtype] = None,
+            outs: Optional[Sequence] = None):
+        """Runs the tape.  ``outs``: list of (tensor-or-dtype, tmp) with tmp = -1 for the accumulator; default one
+        output taking the accumulator.  Returns the output tensor(s)."""
+        full = next((t for t, k in self._ops if t.dim() == 2 and (k in (None, "full")) and t.shape[0] > 1 and t.shape[1] > 1), None)
+        if rows is None or cols is None:
+            if full is None:
+                raise BsirError(-2, "rows / cols are needed when no operand is a full [rows, cols] tensor")
+            rows, cols = full.shape
+        dev = self._ops[0][0].device if self._ops else torch.device("cuda")
+        ins = (_ChainOperand * max(1, len(self._ops)))()
+        for i, (t, kind) in enumerate(self._ops):
+            if kind is None:
+                if t.numel() == 1:
+                    kind = "scalar"
+                elif t.dim() == 2 and tuple(t.shape) == (rows, cols):
+                    kind = "full"
+                elif (t.dim() == 1 and t.shape[0] == cols and cols != rows) or (t.dim() == 2 and tuple(t.shape) == (1, cols)):
+                    kind = "row_vector"
+                elif (t.dim() == 1 and t.shape[0] == rows) or (t.dim() == 2 and tuple(t.shape) == (rows, 1)):
+                    kind = "col_vector"
+                else:
+                    raise BsirError(-2, f"operand {i} of shape {tuple(t.shape)} does not broadcast to [{rows}, {cols}]")
+            k = {"full": 0, "row_vector": 1, "col_vector": 2, "scalar": 3}[kind]
+            if k == 0 and t.stride(1) != 1 and cols > 1:
+                raise BsirError(-3, "innermost dimension must be unit-stride")
+            if k in (1, 2) and not t.is_contiguous():
+                t = t.contiguous()
+                self._ops[i] = (t, kind)
+            ins[i] = _ChainOperand(t.data_ptr(), t.stride(0) if k == 0 and rows > 1 else cols, _dt(t), k)
+        tape = (_ChainInstr * len(self._tape))(*[_ChainInstr(*t) for t in self._tape])
+        spec = outs if outs is not None else [(out_dtype or (full.dtype if full is not None else torch.float32), -1)]
+        tensors = []
+        carr = (_ChainOutput * len(spec))()
+        for i, (o, tmp) in enumerate(spec):
+            t = o if isinstance(o, torch.Tensor) else torch.empty((rows, cols), dtype=o, device=dev)
+            tensors.append(t)
+            carr[i] = _ChainOutput(t.data_ptr(), t.stride(0) if rows > 1 else cols, _dt(t), int(tmp))
+        _check(lib().bsir_fused_elementwise(C.c_int64(rows), C.c_int64(cols), len(self._ops), ins, len(self._tape), tape,
+                                            len(spec), carr, _stream()))
+        return tensors[0] if len(tensors) == 1 else tuple(tensors)
+
+
 # ---------------------------------------------------------------------------- reductions
 def _rows(x: torch.Tensor):
     if x.dim() != 2:

@@ -312,6 +312,32 @@ BSIR_API int32_t bsir_reduce_with_index_static(int32_t kind, int32_t dtype, int3
 BSIR_API int32_t bsir_rms_norm(int32_t dtype, int64_t rows, int64_t cols, const void *x,
                                int64_t x_row_stride, const void *gamma, float eps, void *y,
                                int64_t y_row_stride, void *rstd_out, void *stream);
+/* A chain of elementwise ops with broadcast operands as ONE kernel: what HFusion's op fusion outlines as a
+ * PURE_ELEMWISE / ANY_PB function (FusibleHelper.cpp:52-72).  All arithmetic is f32 with a single
+ * rounding at each output (the bf16 policy of LegalizeBF16.cpp:243-275 + SimplifyOps.cpp:105-230).
+ * The chain is a tape for an accumulator machine with four temporaries:
+ *   LOAD    acc = src                 UNARY   acc = fn(acc)            SAVE  tmp[src] = acc
+ *   BINARY  acc = fn(acc, src)        RBINARY acc = fn(src, acc)
+ * src is an input operand, a temporary or the immediate.  fn is a bsir_unary_fn / bsir_binary_fn that
+ * has an f32 form.  Operands and outputs are f32 / f16 / bf16; an output takes the accumulator
+ * (tmp = -1) or a temporary.  At most 8 operands, 24 instructions, 4 outputs. */
+typedef enum bsir_chain_operand_kind {
+  BSIR_CHAIN_FULL = 0,        /* [rows, cols], row_stride in elements             */
+  BSIR_CHAIN_ROW_VECTOR = 1,  /* [cols], the same for every row (linalg.broadcast dimensions = [0]) */
+  BSIR_CHAIN_COL_VECTOR = 2,  /* [rows], one value per row (linalg.broadcast dimensions = [1])      */
+  BSIR_CHAIN_SCALAR = 3       /* one element in device memory                     */
+} bsir_chain_operand_kind;
+typedef enum bsir_chain_op {
+  BSIR_CHAIN_LOAD = 0, BSIR_CHAIN_UNARY = 1, BSIR_CHAIN_BINARY = 2, BSIR_CHAIN_RBINARY = 3, BSIR_CHAIN_SAVE = 4
+} bsir_chain_op;
+typedef enum bsir_chain_src { BSIR_CHAIN_SRC_OPERAND = 0, BSIR_CHAIN_SRC_TMP = 1, BSIR_CHAIN_SRC_IMM = 2 } bsir_chain_src;
+typedef struct bsir_chain_operand { const void *data; int64_t row_stride; int32_t dtype; int32_t kind; } bsir_chain_operand;
+typedef struct bsir_chain_instr { int32_t op; int32_t fn; int32_t src_kind; int32_t src; float imm; } bsir_chain_instr;
+typedef struct bsir_chain_output { void *data; int64_t row_stride; int32_t dtype; int32_t tmp; } bsir_chain_output;
+BSIR_API int32_t bsir_fused_elementwise(int64_t rows, int64_t cols, int32_t n_in, const bsir_chain_operand *ins,
+                                        int32_t n_instr, const bsir_chain_instr *tape, int32_t n_out,
+                                        const bsir_chain_output *outs, void *stream);
+
 /* Fused softmax over the last axis
  * (test/Dialect/Analysis/VFFusion/MaxParallelKind/softmax_small_shape.mlir:86-117). */
 BSIR_API int32_t bsir_softmax(int32_t dtype, int64_t rows, int64_t cols, const void *x,

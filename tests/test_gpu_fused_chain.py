@@ -1,0 +1,96 @@
+"""GPU: chains of elementwise ops run as one kernel (bsir_fused_elementwise) against the oracle's op-by-op f32
+evaluation with a single final rounding -- the numerics HFusion's bf16 legalisation gives a fused chain
+(LegalizeBF16.cpp:243-275 + SimplifyOps.cpp:105-230)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from conftest import assert_bits_equal, oracle_dtype, to_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def bsir():
+    import bsir as B
+    B.lib()
+    return B
+
+
+def _f32(t):
+    return t.float().cpu().numpy().astype(np.float32)
+
+
+def _round_to(x32, dtype):
+    """f32 numpy -> storage bits of dtype (one RNE)."""
+    if dtype == torch.float32:
+        return x32.astype(np.float32)
+    return O.cast(O.F32, oracle_dtype(torch.empty(0, dtype=dtype)), np.ascontiguousarray(x32), "rint")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,cols", [(64, 4096), (7, 40), (1, 8), (333, 1000), (5, 17)])
+def test_rms_norm_tail_chain(bsir, dtype, rows, cols):
+    """y = gamma * (rstd * x): full tensor, per-row vector, per-column vector -- bit-exact against the f32 evaluation."""
+    g = torch.Generator(device="cuda").manual_seed(rows + cols)
+    x = torch.randn(rows, cols, device="cuda", generator=g).to(dtype)
+    gamma = (1 + 0.1 * torch.randn(cols, device="cuda", generator=g)).to(dtype)
+    rstd = (0.5 + torch.rand(rows, 1, device="cuda", generator=g)).to(torch.float32)
+    ch = bsir.FusedChain()
+    hx, hg, hr = ch.operand(x), ch.operand(gamma, "row_vector"), ch.operand(rstd, "col_vector")
+    ch.load(ch.op(hr)).binary("mul", ch.op(hx)).rbinary("mul", ch.op(hg))
+    y = ch.run(rows, cols, out_dtype=dtype)
+    want32 = O.elemwise_binary("mul", O.F32, np.broadcast_to(_f32(gamma)[None, :], (rows, cols)).copy(),
+                               O.elemwise_binary("mul", O.F32, np.broadcast_to(_f32(rstd), (rows, cols)).copy(), _f32(x)))
+    assert_bits_equal(y, _round_to(want32, dtype).reshape(rows, cols), f"chain {dtype} {rows}x{cols}")
+
+
+def test_gelu_like_chain_with_temporaries_and_two_outputs(bsir):
+    """0.5 x (1 + tanh(0.79788456 (x + 0.044715 x^3))) with a saved temporary, plus a second output (x^2)."""
+    rows, cols = 48, 2048
+    x = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    ch = bsir.FusedChain()
+    hx = ch.operand(x)
+    (ch.load(ch.op(hx)).unary("square").save(1)                      # t1 = x^2
+       .binary("mul", ch.op(hx)).binary("mul", 0.044715).binary("add", ch.op(hx)).binary("mul", 0.7978845608)
+       .unary("tanh").binary("add", 1.0).binary("mul", ch.op(hx)).binary("mul", 0.5))
+    y, sq = ch.run(outs=[(torch.bfloat16, -1), (torch.float32, 1)])
+    x32 = _f32(x)
+    f = lambda fn, a, b: O.elemwise_binary(fn, O.F32, a, b)
+    c = lambda v: np.full_like(x32, np.float32(v))
+    x2 = O.elemwise_unary("square", O.F32, x32)
+    t = f("mul", f("add", f("mul", f("mul", x2, x32), c(0.044715)), x32), c(0.7978845608))
+    want = f("mul", f("mul", f("add", O.elemwise_unary("tanh", O.F32, t), c(1.0)), x32), c(0.5))
+    assert np.array_equal(sq.cpu().numpy(), x2)
+    got = _f32(y)
+    ref = O.bf16_to_f32(O.f32_to_bf16(want))
+    assert np.abs(got - ref).max() <= 2 ** -7 * np.abs(ref).max()      # tanh: device libm vs host libm, then bf16
+
+
+def test_chain_equals_separate_launches_in_f32(bsir):
+    """For f32 data the fused chain and the op-by-op library calls give the same bits."""
+    a = torch.randn(100, 513, device="cuda")
+    b = torch.rand(100, 513, device="cuda") + 0.5
+    s = torch.tensor([1.5], device="cuda")
+    ch = bsir.FusedChain()
+    ha, hb, hs = ch.operand(a), ch.operand(b), ch.operand(s)
+    ch.load(ch.op(ha)).binary("div", ch.op(hb)).unary("abs").unary("sqrt").rbinary("sub", ch.op(hs)).binary("maxf", 0.25)
+    y = ch.run()
+    w = bsir.elemwise_binary("maxf", bsir.elemwise_binary("sub", 1.5, bsir.elemwise_unary(
+        "sqrt", bsir.elemwise_unary("abs", bsir.elemwise_binary("div", a, b)))), 0.25)
+    assert torch.equal(y, w)
+
+
+def test_chain_validation(bsir):
+    x = torch.randn(4, 8, device="cuda")
+    ch = bsir.FusedChain()
+    h = ch.operand(x)
+    ch.load(ch.op(h)).unary("vnot")                                   # no f32 form
+    with pytest.raises(bsir.BsirError):
+        ch.run()
+    ch2 = bsir.FusedChain()
+    ch2.operand(x)
+    ch2.load(("operand", 3))                                          # operand out of range
+    with pytest.raises(bsir.BsirError):
+        ch2.run()
