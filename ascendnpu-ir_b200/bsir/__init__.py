@@ -104,6 +104,7 @@ def lib() -> C.CDLL:
         L.bsir_launch_count.restype = C.c_int64
         L.bsir_reduce_with_index_workspace_bytes.restype = C.c_int64
         L.bsir_matmul_w8a8_workspace_bytes.restype = C.c_int64
+        L.bsir_fused_elementwise_source.restype = C.c_int64
         _lib = L
     return _lib
 
@@ -406,6 +407,46 @@ class FusedChain:
         _check(lib().bsir_fused_elementwise(C.c_int64(rows), C.c_int64(cols), len(self._ops), ins, len(self._tape), tape,
                                             len(spec), carr, _stream()))
         return tensors[0] if len(tensors) == 1 else tuple(tensors)
+
+    @staticmethod
+    def last_path() -> str:
+        """How this thread's last chain ran: "compiled" (a kernel built for the chain with NVRTC), "interpreted"
+        (the tape interpreter kernel) or "none"."""
+        return {0: "none", 1: "interpreted", 2: "compiled"}[int(lib().bsir_fused_elementwise_path())]
+
+    def _tables_without_data(self, outs):
+        """Operand / tape / output tables carrying dtypes and kinds only (for source() and compile())."""
+        ins = (_ChainOperand * max(1, len(self._ops)))()
+        for i, (t, kind) in enumerate(self._ops):
+            if kind is None:
+                kind = "scalar" if t.numel() == 1 else "full" if t.dim() == 2 and min(t.shape) > 1 else None
+            if kind is None:
+                raise BsirError(-2, f"operand {i}: say kind='row_vector' or 'col_vector' for a vector")
+            ins[i] = _ChainOperand(None, 0, _dt(t), {"full": 0, "row_vector": 1, "col_vector": 2, "scalar": 3}[kind])
+        tape = (_ChainInstr * len(self._tape))(*[_ChainInstr(*t) for t in self._tape])
+        spec = outs if outs is not None else [(torch.float32, -1)]
+        carr = (_ChainOutput * len(spec))()
+        for i, (o, tmp) in enumerate(spec):
+            carr[i] = _ChainOutput(None, 0, _dt(o) if isinstance(o, torch.Tensor) else _TORCH2DT[o], int(tmp))
+        return ins, tape, carr, len(spec)
+
+    def source(self, outs: Optional[Sequence] = None, contiguous: bool = True, in_place: bool = False) -> str:
+        """The CUDA C++ of the kernel that is compiled for this chain (no device needed)."""
+        ins, tape, carr, n_out = self._tables_without_data(outs)
+        flags = (1 if contiguous else 0) | (2 if in_place else 0)
+        need = lib().bsir_fused_elementwise_source(len(self._ops), ins, len(self._tape), tape, n_out, carr, flags, None, C.c_int64(0))
+        _check(min(int(need), 0))
+        buf = C.create_string_buffer(int(need))
+        lib().bsir_fused_elementwise_source(len(self._ops), ins, len(self._tape), tape, n_out, carr, flags, buf, C.c_int64(int(need)))
+        return buf.value.decode()
+
+    def compile(self, outs: Optional[Sequence] = None, contiguous: bool = True, in_place: bool = False) -> int:
+        """Compiles the chain's kernel for sm_100a with NVRTC (no device needed); returns the size of the image."""
+        ins, tape, carr, n_out = self._tables_without_data(outs)
+        size = C.c_int64(0)
+        _check(lib().bsir_fused_elementwise_compile(len(self._ops), ins, len(self._tape), tape, n_out, carr,
+                                                    (1 if contiguous else 0) | (2 if in_place else 0), C.byref(size)))
+        return int(size.value)
 
 
 # ---------------------------------------------------------------------------- reductions

@@ -1,0 +1,418 @@
+// chain_jit.cu -- a chain of elementwise ops compiled into its own sm_100a kernel at run time.
+//
+// The reference compiles every fused function into one device kernel ahead of time
+// (HFusion outlining: bishengir/lib/Dialect/HFusion/Transforms/OpFusion/FusibleHelper.cpp:52-72).  The
+// equivalent here: the tape of bsir_fused_elementwise is turned into CUDA C++ (straight-line code,
+// every operand a 16-byte streaming load issued before the arithmetic), compiled once with NVRTC for
+// sm_100a, loaded through the runtime's library API and cached by its source text.  The arithmetic is
+// spelled with the same expressions as the tape interpreter of fused_chain.cu (and --fmad=false), so
+// both paths give the same bits.
+//
+// NVRTC is looked up with dlopen when the first chain arrives, so that the library itself does not
+// depend on it; where it is missing the caller falls back to the interpreter kernel.
+#include <dlfcn.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "chain_jit.h"
+#include "common.cuh"
+
+namespace bsir {
+namespace {
+
+// ---------------------------------------------------------------- NVRTC through dlopen
+typedef struct _nvrtcProgram *nvrtcProgramT;
+struct Nvrtc {
+  void *lib = nullptr;
+  int (*CreateProgram)(nvrtcProgramT *, const char *, const char *, int, const char *const *, const char *const *) = nullptr;
+  int (*CompileProgram)(nvrtcProgramT, int, const char *const *) = nullptr;
+  int (*GetCUBINSize)(nvrtcProgramT, size_t *) = nullptr;
+  int (*GetCUBIN)(nvrtcProgramT, char *) = nullptr;
+  int (*GetProgramLogSize)(nvrtcProgramT, size_t *) = nullptr;
+  int (*GetProgramLog)(nvrtcProgramT, char *) = nullptr;
+  int (*DestroyProgram)(nvrtcProgramT *) = nullptr;
+  std::string why;   // non-empty: not usable
+};
+
+const Nvrtc &nvrtc() {
+  static Nvrtc n;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    // the toolkit the library itself was built with first, then whatever the process can find
+    const char *names[] = {"/usr/local/cuda/lib64/libnvrtc.so.12", "libnvrtc.so.12", "libnvrtc.so", "libnvrtc.so.13"};
+    if (const char *e = std::getenv("BSIR_NVRTC_PATH")) n.lib = dlopen(e, RTLD_NOW | RTLD_LOCAL);
+    for (const char *nm : names) {
+      if (n.lib) break;
+      n.lib = dlopen(nm, RTLD_NOW | RTLD_LOCAL);
+    }
+    if (!n.lib) {
+      n.why = "libnvrtc not found (set BSIR_NVRTC_PATH)";
+      return;
+    }
+    auto sym = [&](const char *s) { return dlsym(n.lib, s); };
+    n.CreateProgram = reinterpret_cast<decltype(n.CreateProgram)>(sym("nvrtcCreateProgram"));
+    n.CompileProgram = reinterpret_cast<decltype(n.CompileProgram)>(sym("nvrtcCompileProgram"));
+    n.GetCUBINSize = reinterpret_cast<decltype(n.GetCUBINSize)>(sym("nvrtcGetCUBINSize"));
+    n.GetCUBIN = reinterpret_cast<decltype(n.GetCUBIN)>(sym("nvrtcGetCUBIN"));
+    n.GetProgramLogSize = reinterpret_cast<decltype(n.GetProgramLogSize)>(sym("nvrtcGetProgramLogSize"));
+    n.GetProgramLog = reinterpret_cast<decltype(n.GetProgramLog)>(sym("nvrtcGetProgramLog"));
+    n.DestroyProgram = reinterpret_cast<decltype(n.DestroyProgram)>(sym("nvrtcDestroyProgram"));
+    if (!n.CreateProgram || !n.CompileProgram || !n.GetCUBINSize || !n.GetCUBIN || !n.GetProgramLogSize || !n.GetProgramLog ||
+        !n.DestroyProgram)
+      n.why = "libnvrtc lacks the cubin entry points";
+  });
+  return n;
+}
+
+// ---------------------------------------------------------------- code generation
+const char *kPrelude = R"SRC(
+typedef unsigned int u32;
+typedef unsigned short u16;
+typedef long long i64;
+struct V4 { u32 x, y, z, w; };
+struct Args {
+  i64 gpr, total;
+  const void *in[8];
+  i64 in_stride[8];
+  void *out[4];
+  i64 out_stride[4];
+};
+__device__ __forceinline__ V4 ld_stream(const void *p) {
+  V4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ V4 ld_keep(const void *p) {
+  V4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ V4 ld_plain(const void *p) {
+  V4 v;
+  asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_stream(void *p, u32 a, u32 b, u32 c, u32 d) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ float f16_bits(u16 h) {
+  float r;
+  asm("cvt.f32.f16 %0, %1;" : "=f"(r) : "h"(h));
+  return r;
+}
+__device__ __forceinline__ void un_bf16(const V4 &v, float *o) {
+  const u32 w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { o[2 * k] = __uint_as_float(w[k] << 16); o[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u); }
+}
+__device__ __forceinline__ void un_f16(const V4 &v, float *o) {
+  const u32 w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { o[2 * k] = f16_bits((u16)(w[k] & 0xffffu)); o[2 * k + 1] = f16_bits((u16)(w[k] >> 16)); }
+}
+__device__ __forceinline__ void un_f32(const V4 &a, const V4 &b, float *o) {
+  o[0] = __uint_as_float(a.x); o[1] = __uint_as_float(a.y); o[2] = __uint_as_float(a.z); o[3] = __uint_as_float(a.w);
+  o[4] = __uint_as_float(b.x); o[5] = __uint_as_float(b.y); o[6] = __uint_as_float(b.z); o[7] = __uint_as_float(b.w);
+}
+__device__ __forceinline__ u32 pk_bf16(float a, float b) {
+  u32 r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+__device__ __forceinline__ u32 pk_f16(float a, float b) {
+  u32 r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+__device__ __forceinline__ float one_f32(const void *p, i64 i) { return ((const float *)p)[i]; }
+__device__ __forceinline__ float one_bf16(const void *p, i64 i) { return __uint_as_float((u32)((const u16 *)p)[i] << 16); }
+__device__ __forceinline__ float one_f16(const void *p, i64 i) { return f16_bits(((const u16 *)p)[i]); }
+__device__ __forceinline__ float maximumf(float a, float b) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ float minimumf(float a, float b) {
+  float r;
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+  return r;
+}
+)SRC";
+
+const char *dtype_tag(int dt) { return dt == BSIR_F32 ? "f32" : dt == BSIR_BF16 ? "bf16" : "f16"; }
+
+// v = the accumulator's element
+const char *unary_expr(int fn) {
+  switch (fn) {
+    case BSIR_UNARY_RELU: return "maximumf(0.0f, v)";
+    case BSIR_UNARY_SQRT: case BSIR_UNARY_SQRT_L: return "__fsqrt_rn(v)";
+    case BSIR_UNARY_RSQRT: case BSIR_UNARY_RSQRT_L: return "__fdiv_rn(1.0f, __fsqrt_rn(v))";
+    case BSIR_UNARY_REC: case BSIR_UNARY_RECIPROCAL: return "__fdiv_rn(1.0f, v)";
+    case BSIR_UNARY_TANH: case BSIR_UNARY_TANH_L: return "tanhf(v)";
+    case BSIR_UNARY_EXP: return "expf(v)";
+    case BSIR_UNARY_LOG: return "logf(v)";
+    case BSIR_UNARY_ABS: return "fabsf(v)";
+    case BSIR_UNARY_CEIL: return "ceilf(v)";
+    case BSIR_UNARY_FLOOR: return "floorf(v)";
+    case BSIR_UNARY_NEGF: return "-v";
+    case BSIR_UNARY_ROUND: return "roundf(v)";
+    case BSIR_UNARY_SQUARE: return "__fmul_rn(v, v)";
+    case BSIR_UNARY_ERF: case BSIR_UNARY_ERF_L: return "erff(v)";
+    case BSIR_UNARY_SIN: return "sinf(v)";
+    case BSIR_UNARY_COS: return "cosf(v)";
+    case BSIR_UNARY_EXP2: return "exp2f(v)";
+    case BSIR_UNARY_LOG2: return "log2f(v)";
+    default: return nullptr;
+  }
+}
+// x = left, y = right
+const char *binary_expr(int fn) {
+  switch (fn) {
+    case BSIR_BINARY_ADD: return "__fadd_rn(x, y)";
+    case BSIR_BINARY_SUB: return "__fsub_rn(x, y)";
+    case BSIR_BINARY_MUL: return "__fmul_rn(x, y)";
+    case BSIR_BINARY_DIV: case BSIR_BINARY_DIVFHP: return "__fdiv_rn(x, y)";
+    case BSIR_BINARY_MAXF: return "maximumf(x, y)";
+    case BSIR_BINARY_MINF: return "minimumf(x, y)";
+    case BSIR_BINARY_MAXNUMF: return "fmaxf(x, y)";
+    case BSIR_BINARY_MINNUMF: return "fminf(x, y)";
+    case BSIR_BINARY_POWF: return "powf(x, y)";
+    default: return nullptr;
+  }
+}
+
+void appendf(std::string &s, const char *fmt, ...) __attribute__((format(printf, 2, 3)));
+void appendf(std::string &s, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  s += buf;
+}
+
+struct Compiled {
+  cudaKernel_t kernel = nullptr;
+  std::string why;   // non-empty: this chain cannot be compiled (remembered, so that it is not retried)
+};
+std::mutex g_mu;
+std::unordered_map<std::string, Compiled> g_cache;
+
+// compiles src to a cubin; empty result + why on failure
+std::vector<char> compile_cubin(const std::string &src, std::string *why) {
+  std::vector<char> cubin;
+  const Nvrtc &n = nvrtc();
+  if (!n.why.empty()) {
+    *why = n.why;
+    return cubin;
+  }
+  nvrtcProgramT prog = nullptr;
+  if (n.CreateProgram(&prog, src.c_str(), "bsir_chain.cu", 0, nullptr, nullptr) != 0) {
+    *why = "nvrtcCreateProgram failed";
+    return cubin;
+  }
+  const char *opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "--fmad=false"};
+  const int rc = n.CompileProgram(prog, 3, opts);
+  if (rc != 0) {
+    size_t ls = 0;
+    n.GetProgramLogSize(prog, &ls);
+    std::string log(ls, '\0');
+    if (ls) n.GetProgramLog(prog, log.data());
+    *why = "nvrtc: " + log.substr(0, 600);
+  } else {
+    size_t sz = 0;
+    if (n.GetCUBINSize(prog, &sz) == 0 && sz > 0) {
+      cubin.resize(sz);
+      if (n.GetCUBIN(prog, cubin.data()) != 0) cubin.clear();
+    }
+    if (cubin.empty()) *why = "nvrtc produced no cubin";
+  }
+  n.DestroyProgram(&prog);
+  return cubin;
+}
+
+}  // namespace
+
+int chain_jit_unroll(const ChainJitSpec &s) {
+  // 16-byte loads a group issues; keep about eight in flight per thread
+  int vecs = 0;
+  for (int i = 0; i < s.n_in; ++i)
+    if (s.in_kind[i] == BSIR_CHAIN_FULL) vecs += s.in_dtype[i] == BSIR_F32 ? 2 : 1;
+  if (vecs <= 2) return 4;
+  if (vecs <= 4) return 2;
+  return 1;
+}
+
+std::string chain_jit_source(const ChainJitSpec &s) {
+  const int U = chain_jit_unroll(s);
+  bool need_rc = !s.flat;
+  for (int i = 0; i < s.n_in; ++i)
+    if (s.in_kind[i] == BSIR_CHAIN_ROW_VECTOR || s.in_kind[i] == BSIR_CHAIN_COL_VECTOR) need_rc = true;
+  std::string c = kPrelude;
+  appendf(c, "#define U %d\n", U);
+  c += "extern \"C\" __global__ void __launch_bounds__(256) bsir_chain(const __grid_constant__ Args a) {\n";
+  c += "  const i64 base = (i64)blockIdx.x * (256 * U) + threadIdx.x;\n";
+  // per-operand registers
+  for (int i = 0; i < s.n_in; ++i) {
+    switch (s.in_kind[i]) {
+      case BSIR_CHAIN_FULL:
+      case BSIR_CHAIN_ROW_VECTOR:
+        if (s.in_dtype[i] == BSIR_F32) appendf(c, "  V4 r%da[U], r%db[U];\n", i, i);
+        else appendf(c, "  V4 r%d[U];\n", i);
+        break;
+      case BSIR_CHAIN_COL_VECTOR: appendf(c, "  float b%d[U];\n", i); break;
+      default: appendf(c, "  const float b%d = one_%s(a.in[%d], 0);\n", i, dtype_tag(s.in_dtype[i]), i); break;
+    }
+  }
+  const char *pos = need_rc ? "    const i64 row = a.total <= 0x7fffffffLL ? (i64)((u32)u / (u32)a.gpr) : u / a.gpr;\n"
+                              "    const i64 c0 = (u - row * a.gpr) * 8;\n"
+                            : "    const i64 row = 0, c0 = u * 8;\n";
+  // ---- loads, all issued before any arithmetic
+  c += "#pragma unroll\n  for (int j = 0; j < U; ++j) {\n    const i64 u = base + j * 256;\n    if (u >= a.total) continue;\n";
+  c += pos;
+  for (int i = 0; i < s.n_in; ++i) {
+    const int k = s.in_kind[i];
+    if (k == BSIR_CHAIN_FULL || k == BSIR_CHAIN_ROW_VECTOR) {
+      const char *ld = k == BSIR_CHAIN_ROW_VECTOR ? "ld_keep" : s.alias ? "ld_plain" : "ld_stream";
+      std::string off = k == BSIR_CHAIN_ROW_VECTOR ? "c0" : std::string("(row * a.in_stride[") + std::to_string(i) + "] + c0)";
+      if (s.in_dtype[i] == BSIR_F32) {
+        appendf(c, "    r%da[j] = %s((const float *)a.in[%d] + %s);\n", i, ld, i, off.c_str());
+        appendf(c, "    r%db[j] = %s((const float *)a.in[%d] + %s + 4);\n", i, ld, i, off.c_str());
+      } else {
+        appendf(c, "    r%d[j] = %s((const u16 *)a.in[%d] + %s);\n", i, ld, i, off.c_str());
+      }
+    } else if (k == BSIR_CHAIN_COL_VECTOR) {
+      appendf(c, "    b%d[j] = one_%s(a.in[%d], row);\n", i, dtype_tag(s.in_dtype[i]), i);
+    }
+  }
+  c += "  }\n";
+  // ---- arithmetic and stores
+  c += "#pragma unroll\n  for (int j = 0; j < U; ++j) {\n    const i64 u = base + j * 256;\n    if (u >= a.total) continue;\n";
+  c += pos;
+  bool tmp_used[4] = {false, false, false, false};
+  for (int i = 0; i < s.n_instr; ++i)
+    if (s.tape[i].op == BSIR_CHAIN_SAVE) tmp_used[s.tape[i].src] = true;
+  c += "    float acc[8];\n";
+  if (s.tape[0].op != BSIR_CHAIN_LOAD) c += "#pragma unroll\n    for (int e = 0; e < 8; ++e) acc[e] = 0.0f;\n";
+  for (int t = 0; t < 4; ++t)
+    if (tmp_used[t]) appendf(c, "    float t%d[8];\n", t);
+  bool unpacked[8] = {false, false, false, false, false, false, false, false};
+  for (int ip = 0; ip < s.n_instr; ++ip) {
+    const bsir_chain_instr &t = s.tape[ip];
+    if (t.op == BSIR_CHAIN_SAVE) {
+      appendf(c, "#pragma unroll\n    for (int e = 0; e < 8; ++e) t%d[e] = acc[e];\n", t.src);
+      continue;
+    }
+    if (t.op == BSIR_CHAIN_UNARY) {
+      appendf(c, "#pragma unroll\n    for (int e = 0; e < 8; ++e) { const float v = acc[e]; acc[e] = %s; }\n", unary_expr(t.fn));
+      continue;
+    }
+    // the source, as an expression of e
+    std::string src;
+    if (t.src_kind == BSIR_CHAIN_SRC_IMM) {
+      uint32_t bits;
+      memcpy(&bits, &t.imm, 4);
+      char lit[48];
+      snprintf(lit, sizeof lit, "__uint_as_float(0x%08xu)", bits);
+      src = lit;
+    } else if (t.src_kind == BSIR_CHAIN_SRC_TMP) {
+      src = "t" + std::to_string(t.src) + "[e]";
+    } else {
+      const int i = t.src, k = s.in_kind[i];
+      if (k == BSIR_CHAIN_COL_VECTOR) src = "b" + std::to_string(i) + "[j]";
+      else if (k == BSIR_CHAIN_SCALAR) src = "b" + std::to_string(i);
+      else {
+        if (!unpacked[i]) {
+          appendf(c, "    float x%d[8];\n", i);
+          if (s.in_dtype[i] == BSIR_F32) appendf(c, "    un_f32(r%da[j], r%db[j], x%d);\n", i, i, i);
+          else appendf(c, "    un_%s(r%d[j], x%d);\n", dtype_tag(s.in_dtype[i]), i, i);
+          unpacked[i] = true;
+        }
+        src = "x" + std::to_string(i) + "[e]";
+      }
+    }
+    if (t.op == BSIR_CHAIN_LOAD) {
+      appendf(c, "#pragma unroll\n    for (int e = 0; e < 8; ++e) acc[e] = %s;\n", src.c_str());
+    } else {
+      const bool rev = t.op == BSIR_CHAIN_RBINARY;
+      appendf(c, "#pragma unroll\n    for (int e = 0; e < 8; ++e) { const float x = %s, y = %s; acc[e] = %s; }\n",
+              rev ? src.c_str() : "acc[e]", rev ? "acc[e]" : src.c_str(), binary_expr(t.fn));
+    }
+  }
+  for (int io = 0; io < s.n_out; ++io) {
+    std::string v = s.out_tmp[io] < 0 ? "acc" : "t" + std::to_string(s.out_tmp[io]);
+    const char *vn = v.c_str();
+    if (s.out_dtype[io] == BSIR_F32) {
+      appendf(c, "    { float *d = (float *)a.out[%d] + (row * a.out_stride[%d] + c0);\n", io, io);
+      appendf(c, "      st_stream(d, __float_as_uint(%s[0]), __float_as_uint(%s[1]), __float_as_uint(%s[2]), __float_as_uint(%s[3]));\n", vn, vn, vn, vn);
+      appendf(c, "      st_stream(d + 4, __float_as_uint(%s[4]), __float_as_uint(%s[5]), __float_as_uint(%s[6]), __float_as_uint(%s[7])); }\n", vn, vn, vn, vn);
+    } else {
+      const char *pk = s.out_dtype[io] == BSIR_BF16 ? "pk_bf16" : "pk_f16";
+      appendf(c, "    st_stream((u16 *)a.out[%d] + (row * a.out_stride[%d] + c0), %s(%s[0], %s[1]), %s(%s[2], %s[3]), %s(%s[4], %s[5]), %s(%s[6], %s[7]));\n",
+              io, io, pk, vn, vn, pk, vn, vn, pk, vn, vn, pk, vn, vn);
+    }
+  }
+  c += "  }\n}\n";
+  return c;
+}
+
+int chain_jit_compile_only(const ChainJitSpec &s, size_t *cubin_bytes, std::string *why) {
+  const std::vector<char> cubin = compile_cubin(chain_jit_source(s), why);
+  if (cubin.empty()) return -1;
+  if (cubin_bytes) *cubin_bytes = cubin.size();
+  return 0;
+}
+
+int chain_jit_launch(const ChainJitSpec &s, const ChainJitArgs &args, cudaStream_t st, std::string *why) {
+  const std::string src = chain_jit_source(s);
+  cudaKernel_t kernel = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mu);
+    auto it = g_cache.find(src);
+    if (it == g_cache.end()) {
+      Compiled cpl;
+      const std::vector<char> cubin = compile_cubin(src, &cpl.why);
+      if (!cubin.empty()) {
+        cudaLibrary_t lib = nullptr;
+        cudaError_t e = cudaLibraryLoadData(&lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+        if (e == cudaSuccess) e = cudaLibraryGetKernel(&cpl.kernel, lib, "bsir_chain");
+        if (e != cudaSuccess) {
+          cpl.kernel = nullptr;
+          cpl.why = std::string("loading the compiled chain: ") + cudaGetErrorString(e);
+          (void)cudaGetLastError();
+        }
+      }
+      it = g_cache.emplace(src, std::move(cpl)).first;
+    }
+    if (!it->second.kernel) {
+      *why = it->second.why;
+      return -1;
+    }
+    kernel = it->second.kernel;
+  }
+  const int U = chain_jit_unroll(s);
+  const int64_t blocks = (args.total + 256 * U - 1) / (256 * U);
+  if (blocks > 0x7fffffffLL) {
+    *why = "grid too large";
+    return -1;
+  }
+  ChainJitArgs copy = args;
+  void *params[] = {&copy};
+  const cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void *>(kernel), dim3(static_cast<unsigned>(blocks)), dim3(256), params, 0, st);
+  if (e != cudaSuccess) {
+    *why = std::string("launching the compiled chain: ") + cudaGetErrorString(e);
+    (void)cudaGetLastError();
+    return -1;
+  }
+  return 0;
+}
+
+}  // namespace bsir

@@ -337,6 +337,22 @@ typedef struct bsir_chain_output { void *data; int64_t row_stride; int32_t dtype
 BSIR_API int32_t bsir_fused_elementwise(int64_t rows, int64_t cols, int32_t n_in, const bsir_chain_operand *ins,
                                         int32_t n_instr, const bsir_chain_instr *tape, int32_t n_out,
                                         const bsir_chain_output *outs, void *stream);
+/* How the last bsir_fused_elementwise of this thread ran: 0 nothing was enqueued, 1 the tape interpreter kernel,
+ * 2 a kernel compiled for this chain.  By default a chain whose rows are 16-byte aligned multiples of 8 columns
+ * is compiled on first use (NVRTC, sm_100a; cached by its source for the life of the process) and everything
+ * else is interpreted; both give the same bits.  BSIR_CHAIN_JIT=0 always interprets, =1 returns
+ * BSIR_ERR_UNSUPPORTED instead of interpreting (no NVRTC in the process, ragged rows). */
+BSIR_API int32_t bsir_fused_elementwise_path(void);
+/* The CUDA C++ that would be compiled for a chain (data pointers and strides are not read).  flags: bit 0 every
+ * tensor is contiguous (flat addressing), bit 1 an output overlaps an operand.  Writes at most cap bytes
+ * (NUL-terminated) and returns the bytes needed, or a negative bsir_status. */
+BSIR_API int64_t bsir_fused_elementwise_source(int32_t n_in, const bsir_chain_operand *ins, int32_t n_instr,
+                                               const bsir_chain_instr *tape, int32_t n_out, const bsir_chain_output *outs,
+                                               int32_t flags, char *buf, int64_t cap);
+/* Compiles that source for sm_100a without touching a device; *cubin_bytes receives the size of the image. */
+BSIR_API int32_t bsir_fused_elementwise_compile(int32_t n_in, const bsir_chain_operand *ins, int32_t n_instr,
+                                                const bsir_chain_instr *tape, int32_t n_out, const bsir_chain_output *outs,
+                                                int32_t flags, int64_t *cubin_bytes);
 
 /* Fused softmax over the last axis
  * (test/Dialect/Analysis/VFFusion/MaxParallelKind/softmax_small_shape.mlir:86-117). */

@@ -1,6 +1,7 @@
 """GPU: chains of elementwise ops run as one kernel (bsir_fused_elementwise) against the oracle's op-by-op f32
 evaluation with a single final rounding -- the numerics HFusion's bf16 legalisation gives a fused chain
-(LegalizeBF16.cpp:243-275 + SimplifyOps.cpp:105-230)."""
+(LegalizeBF16.cpp:243-275 + SimplifyOps.cpp:105-230).  Every case runs on both execution paths: the kernel
+compiled for the chain (NVRTC) and the tape interpreter kernel."""
 import numpy as np
 import pytest
 import torch
@@ -18,6 +19,18 @@ def bsir():
     return B
 
 
+@pytest.fixture(params=["compiled", "interpreted"])
+def path(request, monkeypatch):
+    """Selects the execution path through BSIR_CHAIN_JIT; 'compiled' falls back to the interpreter only where the
+    compiled path does not apply (ragged rows), which the tests check through FusedChain.last_path()."""
+    monkeypatch.setenv("BSIR_CHAIN_JIT", "0" if request.param == "interpreted" else "2")
+    return request.param
+
+
+def _expect_path(bsir, path, vector_ok):
+    assert bsir.FusedChain.last_path() == ("compiled" if path == "compiled" and vector_ok else "interpreted")
+
+
 def _f32(t):
     return t.float().cpu().numpy().astype(np.float32)
 
@@ -31,7 +44,7 @@ def _round_to(x32, dtype):
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("rows,cols", [(64, 4096), (7, 40), (1, 8), (333, 1000), (5, 17)])
-def test_rms_norm_tail_chain(bsir, dtype, rows, cols):
+def test_rms_norm_tail_chain(bsir, path, dtype, rows, cols):
     """y = gamma * (rstd * x): full tensor, per-row vector, per-column vector -- bit-exact against the f32 evaluation."""
     g = torch.Generator(device="cuda").manual_seed(rows + cols)
     x = torch.randn(rows, cols, device="cuda", generator=g).to(dtype)
@@ -41,12 +54,13 @@ def test_rms_norm_tail_chain(bsir, dtype, rows, cols):
     hx, hg, hr = ch.operand(x), ch.operand(gamma, "row_vector"), ch.operand(rstd, "col_vector")
     ch.load(ch.op(hr)).binary("mul", ch.op(hx)).rbinary("mul", ch.op(hg))
     y = ch.run(rows, cols, out_dtype=dtype)
+    _expect_path(bsir, path, cols % 8 == 0)
     want32 = O.elemwise_binary("mul", O.F32, np.broadcast_to(_f32(gamma)[None, :], (rows, cols)).copy(),
                                O.elemwise_binary("mul", O.F32, np.broadcast_to(_f32(rstd), (rows, cols)).copy(), _f32(x)))
     assert_bits_equal(y, _round_to(want32, dtype).reshape(rows, cols), f"chain {dtype} {rows}x{cols}")
 
 
-def test_gelu_like_chain_with_temporaries_and_two_outputs(bsir):
+def test_gelu_like_chain_with_temporaries_and_two_outputs(bsir, path):
     """0.5 x (1 + tanh(0.79788456 (x + 0.044715 x^3))) with a saved temporary, plus a second output (x^2)."""
     rows, cols = 48, 2048
     x = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
@@ -56,6 +70,7 @@ def test_gelu_like_chain_with_temporaries_and_two_outputs(bsir):
        .binary("mul", ch.op(hx)).binary("mul", 0.044715).binary("add", ch.op(hx)).binary("mul", 0.7978845608)
        .unary("tanh").binary("add", 1.0).binary("mul", ch.op(hx)).binary("mul", 0.5))
     y, sq = ch.run(outs=[(torch.bfloat16, -1), (torch.float32, 1)])
+    _expect_path(bsir, path, True)
     x32 = _f32(x)
     f = lambda fn, a, b: O.elemwise_binary(fn, O.F32, a, b)
     c = lambda v: np.full_like(x32, np.float32(v))
@@ -68,7 +83,7 @@ def test_gelu_like_chain_with_temporaries_and_two_outputs(bsir):
     assert np.abs(got - ref).max() <= 2 ** -7 * np.abs(ref).max()      # tanh: device libm vs host libm, then bf16
 
 
-def test_chain_equals_separate_launches_in_f32(bsir):
+def test_chain_equals_separate_launches_in_f32(bsir, path):
     """For f32 data the fused chain and the op-by-op library calls give the same bits."""
     a = torch.randn(100, 513, device="cuda")
     b = torch.rand(100, 513, device="cuda") + 0.5
@@ -94,3 +109,48 @@ def test_chain_validation(bsir):
     ch2.load(("operand", 3))                                          # operand out of range
     with pytest.raises(bsir.BsirError):
         ch2.run()
+
+
+def test_both_paths_give_the_same_bits(bsir, monkeypatch):
+    """Transcendentals included: the compiled kernel and the interpreter spell the arithmetic alike."""
+    rows, cols = 96, 1024
+    x = torch.randn(rows, cols, device="cuda").to(torch.float16)
+    w = torch.rand(rows, cols, device="cuda") + 0.25
+    bias = torch.randn(cols, device="cuda").to(torch.bfloat16)
+    res = {}
+    for mode in ("2", "0"):
+        monkeypatch.setenv("BSIR_CHAIN_JIT", mode)
+        ch = bsir.FusedChain()
+        hx, hw, hb = ch.operand(x), ch.operand(w), ch.operand(bias, "row_vector")
+        (ch.load(ch.op(hx)).binary("add", ch.op(hb)).save(0).unary("exp").binary("div", ch.op(hw)).unary("log")
+           .rbinary("sub", ("tmp", 0)).unary("erf").binary("powf", 2.0).unary("sin").binary("minnumf", ch.op(hw)).save(2)
+           .unary("rsqrt").binary("maxf", ("tmp", 2)))
+        res[mode] = ch.run(outs=[(torch.float16, -1), (torch.float32, 0), (torch.bfloat16, 2)])
+        assert bsir.FusedChain.last_path() == ("compiled" if mode == "2" else "interpreted")
+    for a, b in zip(res["2"], res["0"]):
+        assert np.array_equal(to_bits(a), to_bits(b))
+
+
+def test_compiled_chain_in_place_and_strided(bsir, monkeypatch):
+    """An output that is also an operand, and row strides wider than the row."""
+    monkeypatch.setenv("BSIR_CHAIN_JIT", "1")           # the compiled path or an error
+    big = torch.randn(50, 96, device="cuda")
+    before = big.clone()
+    x = big[:, 16:80]                                    # 64 columns, row stride 96, 16-byte aligned
+    keep = x.clone()
+    ch = bsir.FusedChain()
+    h = ch.operand(x)
+    ch.load(ch.op(h)).binary("mul", 2.0).binary("add", ch.op(h))
+    ch.run(50, 64, outs=[(x, -1)])
+    assert bsir.FusedChain.last_path() == "compiled"
+    assert torch.equal(x, keep * 2.0 + keep)
+    assert torch.equal(big[:, :16], before[:, :16]) and torch.equal(big[:, 80:], before[:, 80:])
+
+
+def test_compiled_path_refuses_ragged_rows_when_required(bsir, monkeypatch):
+    monkeypatch.setenv("BSIR_CHAIN_JIT", "1")
+    x = torch.randn(5, 17, device="cuda")
+    ch = bsir.FusedChain()
+    ch.load(ch.op(ch.operand(x)))
+    with pytest.raises(bsir.BsirError):
+        ch.run()
