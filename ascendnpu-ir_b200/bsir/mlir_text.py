@@ -175,6 +175,11 @@ def _statements(body: str) -> List[Op]:
 class Function:
     def __init__(self, name: str, args: List[tuple], ops: List[Op]):
         self.name, self.args, self.ops = name, args, ops
+        self.fuse = True          # f32 elementwise ops are deferred and run as fused chains (see fusion.py)
+        self.uses: Dict[str, int] = {}
+        for o in ops:
+            for m in re.finditer(r"%[\w.]+", o.text):
+                self.uses[m.group(0)] = self.uses.get(m.group(0), 0) + 1
 
     def op_names(self) -> List[str]:
         return [o.name for o in self.ops]
@@ -200,10 +205,57 @@ class Function:
         def tdtype(elem):
             return getattr(torch, _TORCH_NAMES[elem])
 
+        from . import fusion
+        pending: List[str] = []                                # deferred values the op being looked at would consume
+        arg_ptrs = {t.data_ptr() for t in tensors if isinstance(t, torch.Tensor)}
+
         def val(name):
             if name not in env:
                 raise MlirTextError(f"use of undefined value {name}")
+            if isinstance(env[name], fusion.Lazy):            # needed in memory: the expression runs now, as one kernel
+                env[name] = fusion.materialise(env[name])
             return env[name]
+
+        def node_of(name, shape):
+            """The chain node for an operand of an f32 elementwise op of this result shape, or None."""
+            v = env.get(name)
+            if isinstance(v, Scalar):
+                return ("imm", float(v.value))
+            if isinstance(v, fusion.Lazy):
+                if v.shape != list(shape):
+                    return None
+                if v.node[0] not in ("leaf", "imm"):           # a leaf costs nothing to share; an expression has one user
+                    pending.append(name)
+                return v.node
+            if isinstance(v, torch.Tensor) and list(v.shape) == list(shape) and v.dtype == torch.float32 and v.is_contiguous():
+                return ("leaf", v.view(*fusion.problem(list(shape))), "full")
+            return None
+
+        def defer(op, node, dst):
+            """Defines the op's result as a deferred expression; a value with several uses is computed once, now."""
+            shape = list(dst.shape)
+            if not fusion.fits(node):
+                return False
+            for n in pending:                                  # folded into this expression: never launched on their own
+                env[n] = None
+            lazy = fusion.Lazy(node, shape, dst)
+            env[op.results[0]] = lazy
+            if self.uses.get(op.results[0], 0) != 1 and node[0] not in ("leaf", "imm"):
+                env[op.results[0]] = fusion.materialise(lazy)
+            return True
+
+        def vector_leaf(name):
+            """A contiguous float vector, or a widening cast of one, as the tensor a chain reads."""
+            v = env.get(name)
+            if isinstance(v, fusion.Lazy) and v.node[0] == "leaf" and v.node[2] == "full" and len(v.shape) == 1:
+                return v.node[1].reshape(-1)
+            if isinstance(v, torch.Tensor) and v.dim() == 1 and v.is_contiguous() and v.dtype == torch.float32:
+                return v
+            return None
+
+        def fusible(dst):
+            return (self.fuse and isinstance(dst, torch.Tensor) and dst.dtype == torch.float32 and dst.dim() in (1, 2)
+                    and dst.is_contiguous() and dst.numel() > 0 and len(op.results) == 1)
 
         def operand(name):
             v = val(name)
@@ -223,11 +275,15 @@ class Function:
 
         for op in self.ops:
             name = op.name
+            pending.clear()
             ins, in_types = op.group("ins")
             outs, out_types = op.group("outs")
             if name == "return" or name == "func.return":
                 names = [n.strip() for n in _split_top(op.text.split(":")[0])] if op.text.strip() else []
                 res = tuple(operand(n) for n in names)
+                for k in list(env):                            # a deferred value whose destination is an argument is still written
+                    if isinstance(env[k], fusion.Lazy) and env[k].dst is not None and env[k].dst.data_ptr() in arg_ptrs:
+                        val(k)
                 return res[0] if len(res) == 1 else (res if res else None)
             if name == "arith.constant":
                 m = re.match(r"\s*dense<([^>]+)>\s*:\s*(.+)$", op.text, re.S)
@@ -256,7 +312,9 @@ class Function:
                 define(op, [torch.empty(st.shape, dtype=tdtype(st.elem), device=dev)])
             elif name == "tensor.dim":
                 t_name, i_name = [n.strip() for n in _split_top(op.text.split(":")[0])]
-                define(op, [Scalar(val(t_name).shape[val(i_name).value], "index")])
+                src = env.get(t_name)
+                shape = src.shape if isinstance(src, fusion.Lazy) else val(t_name).shape
+                define(op, [Scalar(shape[val(i_name).value], "index")])
             elif name in ("tensor.collapse_shape", "tensor.expand_shape", "tensor.reshape"):
                 # `%r = tensor.collapse_shape %x [[0, 1], [2]] : tensor<AxBxCxf32> into tensor<ABxCxf32>`: a view
                 src = val(re.match(r"\s*(%[\w.]+)", op.text).group(1))
@@ -274,6 +332,37 @@ class Function:
             elif name == "linalg.transpose":
                 perm = op.int_list("permutation")
                 define(op, [copy(val(ins[0]).permute(perm), out=val(outs[0]))])
+            elif name in ("linalg.elemwise_unary", "hfusion.elemwise_unary") and fusible(env.get(outs[0])) and \
+                    (op.attr("fun") or "exp") in fusion.UNARY and \
+                    (name.startswith("hfusion") or (op.attr("fun") or "exp") in _LINALG_UNARY) and \
+                    node_of(ins[0], env[outs[0]].shape) is not None and \
+                    defer(op, ("un", op.attr("fun") or "exp", node_of(ins[0], env[outs[0]].shape)), env[outs[0]]):
+                pass
+            elif name in ("linalg.elemwise_binary", "hfusion.elemwise_binary") and fusible(env.get(outs[0])) and \
+                    (op.attr("fun") or "add") in fusion.BINARY and \
+                    all(node_of(n, env[outs[0]].shape) is not None for n in ins[:2]) and \
+                    defer(op, ("bin", op.attr("fun") or "add", node_of(ins[0], env[outs[0]].shape),
+                               node_of(ins[1], env[outs[0]].shape)), env[outs[0]]):
+                pass
+            elif name == "linalg.fill" and fusible(env.get(outs[0])) and isinstance(env.get(ins[0]), Scalar) and \
+                    defer(op, ("imm", float(env[ins[0]].value)), env[outs[0]]):
+                pass
+            elif name == "linalg.broadcast" and fusible(env.get(outs[0])) and env[outs[0]].dim() == 2 and \
+                    vector_leaf(ins[0]) is not None and (op.int_list("dimensions") or []) in ([0], [1]) and \
+                    vector_leaf(ins[0]).shape[0] == env[outs[0]].shape[1 - op.int_list("dimensions")[0]] and \
+                    defer(op, ("leaf", vector_leaf(ins[0]), "row_vector" if op.int_list("dimensions") == [0] else "col_vector"), env[outs[0]]):
+                pass
+            elif name == "hfusion.cast" and self.fuse and isinstance(env.get(ins[0]), torch.Tensor) and \
+                    env[ins[0]].dtype in (torch.float16, torch.bfloat16) and fusible(env.get(outs[0])) and \
+                    list(env[ins[0]].shape) == list(env[outs[0]].shape) and env[ins[0]].is_contiguous() and \
+                    defer(op, ("leaf", env[ins[0]].view(*fusion.problem(list(env[ins[0]].shape))), "full"), env[outs[0]]):
+                pass                                           # a widening cast is exact: the chain reads the 16-bit storage
+            elif name == "hfusion.cast" and isinstance(env.get(ins[0]), fusion.Lazy) and isinstance(env.get(outs[0]), torch.Tensor) and \
+                    env[outs[0]].dtype in (torch.float16, torch.bfloat16) and env[outs[0]].is_contiguous() and \
+                    (op.attr("round_mode") or op.attr("mode") or "rint") == "rint" and not op.attr("enable_saturate", False) and \
+                    op.attr("overflow_mode") is None and list(env[outs[0]].shape) == env[ins[0]].shape:
+                define(op, [fusion.materialise(env[ins[0]], out=env[outs[0]])])   # the chain's single rounding
+                env[ins[0]] = None
             elif name == "hfusion.cast" or name == "hivm.hir.vcast":
                 dst = val(outs[0])
                 mode = op.attr("round_mode") or op.attr("mode") or "rint"

@@ -256,3 +256,74 @@ def test_views_transpose_and_slices(bsir):
     assert torch.equal(y, x.reshape(24, 8).t())
     z = torch.randn(16, 32, device="cuda")
     assert torch.equal(fns["slice"](z, torch.empty(4, 8, device="cuda")), -z[2:10:2, 8:16])
+
+
+GELU_IR = """
+func.func @gelu(%x: tensor<64x1024xbf16>, %out: tensor<64x1024xbf16>) -> tensor<64x1024xbf16> {
+  %e0 = tensor.empty() : tensor<64x1024xf32>
+  %x32 = hfusion.cast {round_mode = #hfusion.round_mode<rint>} ins(%x : tensor<64x1024xbf16>) outs(%e0 : tensor<64x1024xf32>) -> tensor<64x1024xf32>
+  %c0 = arith.constant 4.471500e-02 : f32
+  %c1 = arith.constant 0.797884583 : f32
+  %one = arith.constant 1.000000e+00 : f32
+  %half = arith.constant 5.000000e-01 : f32
+  %e1 = tensor.empty() : tensor<64x1024xf32>
+  %x2 = linalg.elemwise_unary {fun = #linalg.unary_fn<square>} ins(%x32 : tensor<64x1024xf32>) outs(%e1 : tensor<64x1024xf32>) -> tensor<64x1024xf32>
+  %x3 = linalg.elemwise_binary {fun = #linalg.binary_fn<mul>} ins(%x2, %x32 : tensor<64x1024xf32>, tensor<64x1024xf32>) outs(%e1 : tensor<64x1024xf32>) -> tensor<64x1024xf32>
+  %a = linalg.elemwise_binary {fun = #linalg.binary_fn<mul>} ins(%x3, %c0 : tensor<64x1024xf32>, f32) outs(%e1 : tensor<64x1024xf32>) -> tensor<64x1024xf32>
+  %b = linalg.elemwise_binary {fun = #linalg.binary_fn<add>} ins(%a, %x32 : tensor<64x1024xf32>, tensor<64x1024xf32>) outs(%e1 : tensor<64x1024xf32>) -> tensor<64x1024xf32>
+  %c = linalg.elemwise_binary {fun = #linalg.binary_fn<mul>} ins(%b, %c1 : tensor<64x1024xf32>, f32) outs(%e1 : tensor<64x1024xf32>) -> tensor<64x1024xf32>
+  %t = linalg.elemwise_unary {fun = #linalg.unary_fn<tanh>} ins(%c : tensor<64x1024xf32>) outs(%e1 : tensor<64x1024xf32>) -> tensor<64x1024xf32>
+  %u = linalg.elemwise_binary {fun = #linalg.binary_fn<add>} ins(%t, %one : tensor<64x1024xf32>, f32) outs(%e1 : tensor<64x1024xf32>) -> tensor<64x1024xf32>
+  %e2 = tensor.empty() : tensor<64x1024xf32>
+  %hx = linalg.elemwise_binary {fun = #linalg.binary_fn<mul>} ins(%x32, %half : tensor<64x1024xf32>, f32) outs(%e2 : tensor<64x1024xf32>) -> tensor<64x1024xf32>
+  %y32 = linalg.elemwise_binary {fun = #linalg.binary_fn<mul>} ins(%hx, %u : tensor<64x1024xf32>, tensor<64x1024xf32>) outs(%e1 : tensor<64x1024xf32>) -> tensor<64x1024xf32>
+  %y = hfusion.cast {round_mode = #hfusion.round_mode<rint>} ins(%y32 : tensor<64x1024xf32>) outs(%out : tensor<64x1024xbf16>) -> tensor<64x1024xbf16>
+  return %y : tensor<64x1024xbf16>
+}
+"""
+
+
+def _launches(bsir):
+    return int(bsir.lib().bsir_launch_count())
+
+
+@pytest.mark.gpu
+def test_f32_elementwise_region_runs_as_one_kernel(bsir):
+    """bf16 -> f32, nine elementwise ops (two sub-expressions meet in the last one), -> bf16: one launch instead of
+    eleven, and the same bits as running the ops one by one."""
+    import torch
+    from bsir import mlir_text
+    from conftest import to_bits
+    fn = mlir_text.parse(GELU_IR)["gelu"]
+    x = torch.randn(64, 1024, device="cuda").to(torch.bfloat16)
+    n0 = _launches(bsir)
+    y = fn(x, torch.empty_like(x))
+    assert _launches(bsir) - n0 == 1
+    assert bsir.FusedChain.last_path() == "compiled"
+    fn.fuse = False
+    n0 = _launches(bsir)
+    w = fn(x, torch.empty_like(x))
+    assert _launches(bsir) - n0 == 11
+    assert np.array_equal(to_bits(y), to_bits(w))
+
+
+@pytest.mark.gpu
+def test_rms_norm_program_fused_equals_op_by_op(bsir):
+    """Fusion stops at the reduction and at values with several users; what is fused keeps the bits."""
+    import torch
+    from bsir import mlir_text
+    from conftest import to_bits
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn(40, 512, generator=g, device="cuda").to(torch.float16)
+    gamma = (1 + 0.02 * torch.randn(512, generator=g, device="cuda")).to(torch.float16)
+    fn = mlir_text.parse(RMS_IR)["rms"]
+    out = lambda: (torch.empty_like(x), torch.empty(40, dtype=torch.float16, device="cuda"))
+    n0 = _launches(bsir)
+    y, r = fn(x, gamma, *out())
+    fused = _launches(bsir) - n0
+    fn.fuse = False
+    n0 = _launches(bsir)
+    wy, wr = fn(x, gamma, *out())
+    eager = _launches(bsir) - n0
+    assert np.array_equal(to_bits(y), to_bits(wy)) and np.array_equal(to_bits(r), to_bits(wr))
+    assert fused <= 6 < eager
