@@ -430,22 +430,25 @@ class FusedChain:
             carr[i] = _ChainOutput(None, 0, _dt(o) if isinstance(o, torch.Tensor) else _TORCH2DT[o], int(tmp))
         return ins, tape, carr, len(spec)
 
-    def source(self, outs: Optional[Sequence] = None, contiguous: bool = True, in_place: bool = False) -> str:
+    def source(self, outs: Optional[Sequence] = None, contiguous: bool = True, in_place: bool = False,
+               row_grid: bool = False) -> str:
         """The CUDA C++ of the kernel that is compiled for this chain (no device needed)."""
         ins, tape, carr, n_out = self._tables_without_data(outs)
-        flags = (1 if contiguous else 0) | (2 if in_place else 0)
+        flags = (1 if contiguous else 0) | (2 if in_place else 0) | (4 if row_grid else 0)
         need = lib().bsir_fused_elementwise_source(len(self._ops), ins, len(self._tape), tape, n_out, carr, flags, None, C.c_int64(0))
         _check(min(int(need), 0))
         buf = C.create_string_buffer(int(need))
         lib().bsir_fused_elementwise_source(len(self._ops), ins, len(self._tape), tape, n_out, carr, flags, buf, C.c_int64(int(need)))
         return buf.value.decode()
 
-    def compile(self, outs: Optional[Sequence] = None, contiguous: bool = True, in_place: bool = False) -> int:
+    def compile(self, outs: Optional[Sequence] = None, contiguous: bool = True, in_place: bool = False,
+                row_grid: bool = False) -> int:
         """Compiles the chain's kernel for sm_100a with NVRTC (no device needed); returns the size of the image."""
         ins, tape, carr, n_out = self._tables_without_data(outs)
         size = C.c_int64(0)
         _check(lib().bsir_fused_elementwise_compile(len(self._ops), ins, len(self._tape), tape, n_out, carr,
-                                                    (1 if contiguous else 0) | (2 if in_place else 0), C.byref(size)))
+                                                    (1 if contiguous else 0) | (2 if in_place else 0) | (4 if row_grid else 0),
+                                                    C.byref(size)))
         return int(size.value)
 
 

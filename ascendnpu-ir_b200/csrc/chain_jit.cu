@@ -242,6 +242,7 @@ std::vector<char> compile_cubin(const std::string &src, std::string *why) {
 }  // namespace
 
 int chain_jit_unroll(const ChainJitSpec &s) {
+  if (s.unroll == 1 || s.unroll == 2 || s.unroll == 4) return s.unroll;
   // 16-byte loads a group issues; keep about eight in flight per thread
   int vecs = 0;
   for (int i = 0; i < s.n_in; ++i)
@@ -249,6 +250,22 @@ int chain_jit_unroll(const ChainJitSpec &s) {
   if (vecs <= 2) return 4;
   if (vecs <= 4) return 2;
   return 1;
+}
+
+void chain_jit_plan(ChainJitSpec *s, long long gpr) {
+  // One block per stretch of a row needs no division at all; it is used when a row fills whole blocks with at
+  // most an eighth of the threads idle.  Fewer groups per thread are tried before giving the mapping up.
+  s->row_grid = false;
+  s->unroll = 0;
+  if (s->flat) return;
+  for (int u = chain_jit_unroll(*s); u >= 1; u >>= 1) {
+    const long long span = 256LL * u, covered = (gpr + span - 1) / span * span;
+    if ((covered - gpr) * 8 <= gpr && covered / span <= 65535) {
+      s->row_grid = true;
+      s->unroll = u;
+      return;
+    }
+  }
 }
 
 std::string chain_jit_source(const ChainJitSpec &s) {
@@ -272,11 +289,23 @@ std::string chain_jit_source(const ChainJitSpec &s) {
       default: appendf(c, "  const float b%d = one_%s(a.in[%d], 0);\n", i, dtype_tag(s.in_dtype[i]), i); break;
     }
   }
-  const char *pos = need_rc ? "    const i64 row = a.total <= 0x7fffffffLL ? (i64)((u32)u / (u32)a.gpr) : u / a.gpr;\n"
-                              "    const i64 c0 = (u - row * a.gpr) * 8;\n"
-                            : "    const i64 row = 0, c0 = u * 8;\n";
+  // ---- positions of the thread's groups: flat (contiguous tensors only: no rows at all), one block per stretch
+  // of a row (no division), or a 32-bit division per group.
+  c += "  i64 rowv[U], c0v[U];\n  bool live[U];\n#pragma unroll\n  for (int j = 0; j < U; ++j) {\n";
+  if (!need_rc) {
+    c += "    const i64 u = base + j * 256;\n    live[j] = u < a.total;\n    rowv[j] = 0;\n    c0v[j] = u * 8;\n";
+  } else if (s.row_grid) {
+    c += "    const i64 g = (i64)blockIdx.y * (256 * U) + threadIdx.x + j * 256;\n"
+         "    live[j] = g < a.gpr;\n    rowv[j] = blockIdx.x;\n    c0v[j] = g * 8;\n";
+  } else {
+    c += "    const i64 u = base + j * 256;\n    live[j] = u < a.total;\n"
+         "    rowv[j] = a.total <= 0x7fffffffLL ? (i64)((u32)u / (u32)a.gpr) : u / a.gpr;\n"
+         "    c0v[j] = (u - rowv[j] * a.gpr) * 8;\n";
+  }
+  c += "  }\n";
+  const char *pos = "    const i64 row = rowv[j], c0 = c0v[j];\n";
   // ---- loads, all issued before any arithmetic
-  c += "#pragma unroll\n  for (int j = 0; j < U; ++j) {\n    const i64 u = base + j * 256;\n    if (u >= a.total) continue;\n";
+  c += "#pragma unroll\n  for (int j = 0; j < U; ++j) {\n    if (!live[j]) continue;\n";
   c += pos;
   for (int i = 0; i < s.n_in; ++i) {
     const int k = s.in_kind[i];
@@ -295,7 +324,7 @@ std::string chain_jit_source(const ChainJitSpec &s) {
   }
   c += "  }\n";
   // ---- arithmetic and stores
-  c += "#pragma unroll\n  for (int j = 0; j < U; ++j) {\n    const i64 u = base + j * 256;\n    if (u >= a.total) continue;\n";
+  c += "#pragma unroll\n  for (int j = 0; j < U; ++j) {\n    if (!live[j]) continue;\n";
   c += pos;
   bool tmp_used[4] = {false, false, false, false};
   for (int i = 0; i < s.n_instr; ++i)
@@ -399,14 +428,16 @@ int chain_jit_launch(const ChainJitSpec &s, const ChainJitArgs &args, cudaStream
     kernel = it->second.kernel;
   }
   const int U = chain_jit_unroll(s);
-  const int64_t blocks = (args.total + 256 * U - 1) / (256 * U);
-  if (blocks > 0x7fffffffLL) {
+  const bool rows_on_x = s.row_grid && !s.flat;
+  const int64_t blocks = rows_on_x ? args.total / args.gpr : (args.total + 256 * U - 1) / (256 * U);
+  const int64_t blocks_y = rows_on_x ? (args.gpr + 256 * U - 1) / (256 * U) : 1;
+  if (blocks > 0x7fffffffLL || blocks_y > 65535) {
     *why = "grid too large";
     return -1;
   }
   ChainJitArgs copy = args;
   void *params[] = {&copy};
-  const cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void *>(kernel), dim3(static_cast<unsigned>(blocks)), dim3(256), params, 0, st);
+  const cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void *>(kernel), dim3(static_cast<unsigned>(blocks), static_cast<unsigned>(blocks_y)), dim3(256), params, 0, st);
   if (e != cudaSuccess) {
     *why = std::string("launching the compiled chain: ") + cudaGetErrorString(e);
     (void)cudaGetLastError();

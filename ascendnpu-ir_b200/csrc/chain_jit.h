@@ -18,6 +18,8 @@ struct ChainJitSpec {
   int out_dtype[4] = {}, out_tmp[4] = {};
   bool flat = false;    // every tensor is contiguous and nothing is broadcast along an axis: no row / column arithmetic
   bool alias = false;   // an output overlaps an operand: operands are read with coherent loads
+  bool row_grid = false;   // blockIdx.x is the row, blockIdx.y a stretch of it (no division); set by chain_jit_plan
+  int unroll = 0;          // groups per thread; 0: chosen from the operands
 };
 
 // The kernel's parameter block (the generated source declares the same layout).
@@ -30,6 +32,7 @@ struct ChainJitArgs {
 };
 
 int chain_jit_unroll(const ChainJitSpec &s);          // groups per thread
+void chain_jit_plan(ChainJitSpec *s, long long groups_per_row);   // picks the thread mapping for rows of this length
 std::string chain_jit_source(const ChainJitSpec &s);   // CUDA C++ of the chain's kernel
 // NVRTC only (no device needed): 0 and the cubin's size, or -1 and the reason.
 int chain_jit_compile_only(const ChainJitSpec &s, size_t *cubin_bytes, std::string *why);

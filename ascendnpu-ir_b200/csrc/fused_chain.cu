@@ -540,7 +540,8 @@ extern "C" int32_t bsir_fused_elementwise(int64_t rows, int64_t cols, int32_t n_
         if (a0 < b1 && b0 < a1) alias = true;
       }
     }
-    const ChainJitSpec spec = make_spec(n_in, ins, n_instr, tape, n_out, outs, flat, alias);
+    ChainJitSpec spec = make_spec(n_in, ins, n_instr, tape, n_out, outs, flat, alias);
+    chain_jit_plan(&spec, cols / kGroup);
     ChainJitArgs args{};
     args.gpr = cols / kGroup;
     args.total = rows * args.gpr;
@@ -638,7 +639,9 @@ extern "C" int64_t bsir_fused_elementwise_source(int32_t n_in, const bsir_chain_
   clear_error();
   bool tmp_used[kChainTemps];
   if (const int32_t rc = validate_tape(n_in, ins, n_instr, tape, n_out, outs, tmp_used)) return rc;
-  const std::string src = chain_jit_source(make_spec(n_in, ins, n_instr, tape, n_out, outs, (flags & 1) != 0, (flags & 2) != 0));
+  ChainJitSpec spec = make_spec(n_in, ins, n_instr, tape, n_out, outs, (flags & 1) != 0, (flags & 2) != 0);
+  spec.row_grid = (flags & 4) != 0 && !spec.flat;
+  const std::string src = chain_jit_source(spec);
   if (buf && cap > 0) {
     const size_t n = src.size() < static_cast<size_t>(cap - 1) ? src.size() : static_cast<size_t>(cap - 1);
     memcpy(buf, src.data(), n);
@@ -655,7 +658,9 @@ extern "C" int32_t bsir_fused_elementwise_compile(int32_t n_in, const bsir_chain
   if (const int32_t rc = validate_tape(n_in, ins, n_instr, tape, n_out, outs, tmp_used)) return rc;
   size_t sz = 0;
   std::string why;
-  if (chain_jit_compile_only(make_spec(n_in, ins, n_instr, tape, n_out, outs, (flags & 1) != 0, (flags & 2) != 0), &sz, &why) != 0)
+  ChainJitSpec spec = make_spec(n_in, ins, n_instr, tape, n_out, outs, (flags & 1) != 0, (flags & 2) != 0);
+  spec.row_grid = (flags & 4) != 0 && !spec.flat;
+  if (chain_jit_compile_only(spec, &sz, &why) != 0)
     return fail(BSIR_ERR_UNSUPPORTED, "fused_elementwise_compile: %s", why.c_str());
   if (cubin_bytes) *cubin_bytes = static_cast<int64_t>(sz);
   return BSIR_OK;

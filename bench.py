@@ -215,6 +215,29 @@ def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters, only=None):
         xs = [W.argmax_input(256, 152064, seed=s) for s in range(4)]
         rec("argmax_bf16_256x152064", 256 * 152064 * 2 + 256 * 6, lambda i: bsir.reduce_with_index("max", xs[i % 4]))
         del xs
+    if want("chain_rmstail_bf16_32768x4096") or want("chain_gelu_bf16_32768x4096"):
+        # fused elementwise chains (one kernel compiled per chain): gamma * (rstd * x), and tanh-GELU in ten ops
+        rows, cols = 32768, 4096
+        xs = [W.rmsnorm_input(rows, cols, seed=s) for s in range(2)]
+        ys = [torch.empty_like(x[0]) for x in xs]
+        rstd = torch.rand(rows, 1, device="cuda") + 0.5
+
+        def rms_tail(i):
+            ch = bsir.FusedChain()
+            hx, hg, hr = ch.operand(xs[i % 2][0]), ch.operand(xs[i % 2][1], "row_vector"), ch.operand(rstd, "col_vector")
+            ch.load(ch.op(hr)).binary("mul", ch.op(hx)).rbinary("mul", ch.op(hg))
+            ch.run(rows, cols, outs=[(ys[i % 2], -1)])
+
+        def gelu(i):
+            ch = bsir.FusedChain()
+            hx = ch.op(ch.operand(xs[i % 2][0]))
+            (ch.load(hx).unary("square").binary("mul", hx).binary("mul", 0.044715).binary("add", hx).binary("mul", 0.7978845608)
+               .unary("tanh").binary("add", 1.0).binary("mul", hx).binary("mul", 0.5))
+            ch.run(rows, cols, outs=[(ys[i % 2], -1)])
+
+        rec("chain_rmstail_bf16_32768x4096", 2 * rows * cols * 2 + cols * 2 + rows * 4, rms_tail)
+        rec("chain_gelu_bf16_32768x4096", 2 * rows * cols * 2, gelu)
+        del xs, ys, rstd
     for m in (16, 128, 4096):
         if not want(f"w8a8_m{m}"):
             continue

@@ -344,7 +344,8 @@ BSIR_API int32_t bsir_fused_elementwise(int64_t rows, int64_t cols, int32_t n_in
  * BSIR_ERR_UNSUPPORTED instead of interpreting (no NVRTC in the process, ragged rows). */
 BSIR_API int32_t bsir_fused_elementwise_path(void);
 /* The CUDA C++ that would be compiled for a chain (data pointers and strides are not read).  flags: bit 0 every
- * tensor is contiguous (flat addressing), bit 1 an output overlaps an operand.  Writes at most cap bytes
+ * tensor is contiguous (flat addressing), bit 1 an output overlaps an operand, bit 2 one block per stretch of a
+ * row (the mapping chosen for rows that fill whole blocks) instead of a division per group.  Writes at most cap bytes
  * (NUL-terminated) and returns the bytes needed, or a negative bsir_status. */
 BSIR_API int64_t bsir_fused_elementwise_source(int32_t n_in, const bsir_chain_operand *ins, int32_t n_instr,
                                                const bsir_chain_instr *tape, int32_t n_out, const bsir_chain_output *outs,
