@@ -366,6 +366,13 @@ class FusedChain:
         self._tape.append((4, 0, 1, int(tmp), 0.0))
         return self
 
+    def reduce(self, kind: str):
+        """acc = reduce of acc over the row (sum / prod / max / min), broadcast back to every element of the row.
+        A chain with reductions is a LAST_AXIS_PBR function: it runs only as a compiled kernel that keeps the row in
+        registers.  An output given as a [rows] (or [rows, 1]) tensor takes the row's value."""
+        self._tape.append((5, REDUCE_KIND[kind], 0, 0, 0.0))
+        return self
+
     def run(self, rows: Optional[int] = None, cols: Optional[int] = None, out_dtype: Optional[torch.dtype] = None,
             outs: Optional[Sequence] = None):
         """Runs the tape.  ``outs``: list of (tensor-or-dtype, tmp) with tmp = -1 for the accumulator; default one
@@ -403,7 +410,10 @@ class FusedChain:
         for i, (o, tmp) in enumerate(spec):
             t = o if isinstance(o, torch.Tensor) else torch.empty((rows, cols), dtype=o, device=dev)
             tensors.append(t)
-            carr[i] = _ChainOutput(t.data_ptr(), t.stride(0) if rows > 1 else cols, _dt(t), int(tmp))
+            per_row = cols != 1 and (t.dim() == 1 and t.shape[0] == rows or t.dim() == 2 and tuple(t.shape) == (rows, 1))
+            if per_row and not t.is_contiguous():
+                raise BsirError(-3, "a per-row output must be contiguous")
+            carr[i] = _ChainOutput(t.data_ptr(), 0 if per_row else t.stride(0) if rows > 1 else cols, _dt(t), int(tmp))
         _check(lib().bsir_fused_elementwise(C.c_int64(rows), C.c_int64(cols), len(self._ops), ins, len(self._tape), tape,
                                             len(spec), carr, _stream()))
         return tensors[0] if len(tensors) == 1 else tuple(tensors)
@@ -427,14 +437,16 @@ class FusedChain:
         spec = outs if outs is not None else [(torch.float32, -1)]
         carr = (_ChainOutput * len(spec))()
         for i, (o, tmp) in enumerate(spec):
-            carr[i] = _ChainOutput(None, 0, _dt(o) if isinstance(o, torch.Tensor) else _TORCH2DT[o], int(tmp))
+            per_row = isinstance(o, torch.Tensor) and o.dim() == 1          # a [rows] tensor stands for a per-row output
+            carr[i] = _ChainOutput(None, 0 if per_row else 1, _dt(o) if isinstance(o, torch.Tensor) else _TORCH2DT[o], int(tmp))
         return ins, tape, carr, len(spec)
 
     def source(self, outs: Optional[Sequence] = None, contiguous: bool = True, in_place: bool = False,
-               row_grid: bool = False) -> str:
-        """The CUDA C++ of the kernel that is compiled for this chain (no device needed)."""
+               row_grid: bool = False, cols: int = 4096) -> str:
+        """The CUDA C++ of the kernel that is compiled for this chain (no device needed).  ``cols`` matters for chains
+        with reductions only: their thread geometry follows the row length."""
         ins, tape, carr, n_out = self._tables_without_data(outs)
-        flags = (1 if contiguous else 0) | (2 if in_place else 0) | (4 if row_grid else 0)
+        flags = (1 if contiguous else 0) | (2 if in_place else 0) | (4 if row_grid else 0) | ((cols // 8) << 8)
         need = lib().bsir_fused_elementwise_source(len(self._ops), ins, len(self._tape), tape, n_out, carr, flags, None, C.c_int64(0))
         _check(min(int(need), 0))
         buf = C.create_string_buffer(int(need))
@@ -442,13 +454,13 @@ class FusedChain:
         return buf.value.decode()
 
     def compile(self, outs: Optional[Sequence] = None, contiguous: bool = True, in_place: bool = False,
-                row_grid: bool = False) -> int:
+                row_grid: bool = False, cols: int = 4096) -> int:
         """Compiles the chain's kernel for sm_100a with NVRTC (no device needed); returns the size of the image."""
         ins, tape, carr, n_out = self._tables_without_data(outs)
         size = C.c_int64(0)
         _check(lib().bsir_fused_elementwise_compile(len(self._ops), ins, len(self._tape), tape, n_out, carr,
-                                                    (1 if contiguous else 0) | (2 if in_place else 0) | (4 if row_grid else 0),
-                                                    C.byref(size)))
+                                                    (1 if contiguous else 0) | (2 if in_place else 0) | (4 if row_grid else 0)
+                                                    | ((cols // 8) << 8), C.byref(size)))
         return int(size.value)
 
 

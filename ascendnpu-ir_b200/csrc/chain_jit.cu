@@ -79,7 +79,7 @@ typedef unsigned short u16;
 typedef long long i64;
 struct V4 { u32 x, y, z, w; };
 struct Args {
-  i64 gpr, total;
+  i64 gpr, total, rows;
   const void *in[8];
   i64 in_stride[8];
   void *out[4];
@@ -145,6 +145,33 @@ __device__ __forceinline__ float minimumf(float a, float b) {
   asm("min.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
   return r;
 }
+__device__ __forceinline__ float red_sum(float a, float b) { return __fadd_rn(a, b); }
+__device__ __forceinline__ float red_prod(float a, float b) { return __fmul_rn(a, b); }
+__device__ __forceinline__ float red_max(float a, float b) { return maximumf(a, b); }
+__device__ __forceinline__ float red_min(float a, float b) { return minimumf(a, b); }
+)SRC";
+
+// Reduction of one value per thread over the TPR threads of a row (TPR a power of two; rows of a block are
+// aligned groups of threads): shuffles inside a warp, then one shared-memory word per warp.
+const char *kRowReduce = R"SRC(
+#define ROW_REDUCE(NAME, COMB)                                                                  \
+  __device__ __forceinline__ float NAME(float p, float *red) {                                  \
+    _Pragma("unroll") for (int o = (TPR < 32 ? TPR : 32) / 2; o > 0; o >>= 1)                   \
+      p = COMB(p, __shfl_xor_sync(0xffffffffu, p, o));                                          \
+    if (TPR > 32) {                                                                             \
+      const int warp = threadIdx.x >> 5, first = (threadIdx.x / TPR) * (TPR / 32);              \
+      __syncthreads();                                                                          \
+      if ((threadIdx.x & 31) == 0) red[warp] = p;                                               \
+      __syncthreads();                                                                          \
+      p = red[first];                                                                           \
+      for (int k = 1; k < TPR / 32; ++k) p = COMB(p, red[first + k]);                           \
+    }                                                                                           \
+    return p;                                                                                   \
+  }
+ROW_REDUCE(row_sum, red_sum)
+ROW_REDUCE(row_prod, red_prod)
+ROW_REDUCE(row_max, red_max)
+ROW_REDUCE(row_min, red_min)
 )SRC";
 
 const char *dtype_tag(int dt) { return dt == BSIR_F32 ? "f32" : dt == BSIR_BF16 ? "bf16" : "f16"; }
@@ -268,7 +295,12 @@ void chain_jit_plan(ChainJitSpec *s, long long gpr) {
   }
 }
 
+namespace {
+std::string row_source(const ChainJitSpec &s);
+}
+
 std::string chain_jit_source(const ChainJitSpec &s) {
+  if (s.tpr > 0) return row_source(s);
   const int U = chain_jit_unroll(s);
   bool need_rc = !s.flat;
   for (int i = 0; i < s.n_in; ++i)
@@ -393,6 +425,157 @@ std::string chain_jit_source(const ChainJitSpec &s) {
   return c;
 }
 
+namespace {
+
+const char *reduce_tag(int kind) {
+  switch (kind) {
+    case BSIR_REDUCE_SUM: return "sum";
+    case BSIR_REDUCE_PROD: return "prod";
+    case BSIR_REDUCE_MAX: return "max";
+    case BSIR_REDUCE_MIN: return "min";
+    default: return nullptr;
+  }
+}
+const char *reduce_identity(int kind) {
+  switch (kind) {
+    case BSIR_REDUCE_SUM: return "0.0f";
+    case BSIR_REDUCE_PROD: return "1.0f";
+    case BSIR_REDUCE_MAX: return "__uint_as_float(0xff800000u)";   // -inf
+    default: return "__uint_as_float(0x7f800000u)";                // +inf
+  }
+}
+
+// A chain with last-axis reductions: TPR threads hold a row in registers (VPT groups of 8 elements each, group
+// g of the row with thread g % TPR), so every operand is read once however many reductions the row needs.
+std::string row_source(const ChainJitSpec &s) {
+  const int tpr = s.tpr, vpt = s.vpt, bt = tpr > 128 ? tpr : 128;
+  std::string c = kPrelude;
+  appendf(c, "#define TPR %d\n#define VPT %d\n#define BT %d\n", tpr, vpt, bt);
+  c += kRowReduce;
+  c += "extern \"C\" __global__ void __launch_bounds__(BT) bsir_chain(const __grid_constant__ Args a) {\n"
+       "  __shared__ float red[BT / 32];\n"
+       "  const int lane = threadIdx.x % TPR;\n"
+       "  const i64 row_id = (i64)blockIdx.x * (BT / TPR) + threadIdx.x / TPR;\n"
+       "  const bool row_ok = row_id < a.rows;\n"
+       "  const i64 row = row_ok ? row_id : 0;          // threads past the last row redo row 0 and store nothing\n"
+       "  bool live[VPT];\n  i64 c0v[VPT];\n"
+       "#pragma unroll\n  for (int q = 0; q < VPT; ++q) { const i64 g = lane + q * TPR; live[q] = g < a.gpr; c0v[q] = g * 8; }\n";
+  for (int i = 0; i < s.n_in; ++i) {
+    const char *tag = dtype_tag(s.in_dtype[i]);
+    switch (s.in_kind[i]) {
+      case BSIR_CHAIN_FULL:
+      case BSIR_CHAIN_ROW_VECTOR:
+        if (s.in_dtype[i] == BSIR_F32) appendf(c, "  V4 r%da[VPT], r%db[VPT];\n", i, i);
+        else appendf(c, "  V4 r%d[VPT];\n", i);
+        break;
+      case BSIR_CHAIN_COL_VECTOR: appendf(c, "  const float b%d = one_%s(a.in[%d], row);\n", i, tag, i); break;
+      default: appendf(c, "  const float b%d = one_%s(a.in[%d], 0);\n", i, tag, i); break;
+    }
+  }
+  c += "#pragma unroll\n  for (int q = 0; q < VPT; ++q) {\n    const i64 c0 = c0v[q];\n";
+  for (int i = 0; i < s.n_in; ++i) {
+    const int k = s.in_kind[i];
+    if (k != BSIR_CHAIN_FULL && k != BSIR_CHAIN_ROW_VECTOR) continue;
+    const char *ld = k == BSIR_CHAIN_ROW_VECTOR ? "ld_keep" : s.alias ? "ld_plain" : "ld_stream";
+    std::string off = k == BSIR_CHAIN_ROW_VECTOR ? "c0" : std::string("(row * a.in_stride[") + std::to_string(i) + "] + c0)";
+    if (s.in_dtype[i] == BSIR_F32) {
+      appendf(c, "    r%da[q] = r%db[q] = V4{0, 0, 0, 0};\n", i, i);
+      appendf(c, "    if (live[q]) { r%da[q] = %s((const float *)a.in[%d] + %s); r%db[q] = %s((const float *)a.in[%d] + %s + 4); }\n", i,
+              ld, i, off.c_str(), i, ld, i, off.c_str());
+    } else {
+      appendf(c, "    r%d[q] = V4{0, 0, 0, 0};\n    if (live[q]) r%d[q] = %s((const u16 *)a.in[%d] + %s);\n", i, i, ld, i, off.c_str());
+    }
+  }
+  c += "  }\n";
+  bool tmp_used[4] = {false, false, false, false};
+  for (int i = 0; i < s.n_instr; ++i)
+    if (s.tape[i].op == BSIR_CHAIN_SAVE) tmp_used[s.tape[i].src] = true;
+  c += "  float acc[VPT][8];\n";
+  if (s.tape[0].op != BSIR_CHAIN_LOAD) c += "#pragma unroll\n  for (int q = 0; q < VPT; ++q)\n#pragma unroll\n    for (int e = 0; e < 8; ++e) acc[q][e] = 0.0f;\n";
+  for (int t = 0; t < 4; ++t)
+    if (tmp_used[t]) appendf(c, "  float t%d[VPT][8];\n", t);
+  const char *loop = "#pragma unroll\n  for (int q = 0; q < VPT; ++q)\n#pragma unroll\n    for (int e = 0; e < 8; ++e) ";
+  bool unpacked[8] = {false, false, false, false, false, false, false, false};
+  for (int ip = 0; ip < s.n_instr; ++ip) {
+    const bsir_chain_instr &t = s.tape[ip];
+    if (t.op == BSIR_CHAIN_SAVE) {
+      c += loop;
+      appendf(c, "t%d[q][e] = acc[q][e];\n", t.src);
+      continue;
+    }
+    if (t.op == BSIR_CHAIN_UNARY) {
+      c += loop;
+      appendf(c, "{ const float v = acc[q][e]; acc[q][e] = %s; }\n", unary_expr(t.fn));
+      continue;
+    }
+    if (t.op == BSIR_CHAIN_REDUCE) {
+      // elements past the row's end take the identity; every thread of the row ends with the row's value
+      appendf(c, "  {\n    float p = %s;\n", reduce_identity(t.fn));
+      appendf(c, "#pragma unroll\n    for (int q = 0; q < VPT; ++q)\n#pragma unroll\n      for (int e = 0; e < 8; ++e) if (live[q]) p = red_%s(p, acc[q][e]);\n",
+              reduce_tag(t.fn));
+      appendf(c, "    p = row_%s(p, red);\n", reduce_tag(t.fn));
+      c += "#pragma unroll\n    for (int q = 0; q < VPT; ++q)\n#pragma unroll\n      for (int e = 0; e < 8; ++e) acc[q][e] = p;\n  }\n";
+      continue;
+    }
+    std::string src;
+    if (t.src_kind == BSIR_CHAIN_SRC_IMM) {
+      uint32_t bits;
+      memcpy(&bits, &t.imm, 4);
+      char lit[48];
+      snprintf(lit, sizeof lit, "__uint_as_float(0x%08xu)", bits);
+      src = lit;
+    } else if (t.src_kind == BSIR_CHAIN_SRC_TMP) {
+      src = "t" + std::to_string(t.src) + "[q][e]";
+    } else {
+      const int i = t.src, k = s.in_kind[i];
+      if (k == BSIR_CHAIN_COL_VECTOR || k == BSIR_CHAIN_SCALAR) src = "b" + std::to_string(i);
+      else {
+        if (!unpacked[i]) {
+          appendf(c, "  float x%d[VPT][8];\n#pragma unroll\n  for (int q = 0; q < VPT; ++q) ", i);
+          if (s.in_dtype[i] == BSIR_F32) appendf(c, "un_f32(r%da[q], r%db[q], x%d[q]);\n", i, i, i);
+          else appendf(c, "un_%s(r%d[q], x%d[q]);\n", dtype_tag(s.in_dtype[i]), i, i);
+          unpacked[i] = true;
+        }
+        src = "x" + std::to_string(i) + "[q][e]";
+      }
+    }
+    c += loop;
+    if (t.op == BSIR_CHAIN_LOAD) {
+      appendf(c, "acc[q][e] = %s;\n", src.c_str());
+    } else {
+      const bool rev = t.op == BSIR_CHAIN_RBINARY;
+      appendf(c, "{ const float x = %s, y = %s; acc[q][e] = %s; }\n", rev ? src.c_str() : "acc[q][e]", rev ? "acc[q][e]" : src.c_str(),
+              binary_expr(t.fn));
+    }
+  }
+  for (int io = 0; io < s.n_out; ++io) {
+    std::string v = s.out_tmp[io] < 0 ? "acc" : "t" + std::to_string(s.out_tmp[io]);
+    const char *vn = v.c_str();
+    if (s.out_per_row[io]) {
+      // one value per row: the row's threads all hold it; the first one stores it
+      const char *val = s.out_dtype[io] == BSIR_F32 ? "" : s.out_dtype[io] == BSIR_BF16 ? "pk_bf16" : "pk_f16";
+      if (s.out_dtype[io] == BSIR_F32) appendf(c, "  if (row_ok && lane == 0) ((float *)a.out[%d])[row] = %s[0][0];\n", io, vn);
+      else appendf(c, "  if (row_ok && lane == 0) ((u16 *)a.out[%d])[row] = (u16)%s(%s[0][0], 0.0f);\n", io, val, vn);
+      continue;
+    }
+    c += "#pragma unroll\n  for (int q = 0; q < VPT; ++q) {\n    if (!row_ok || !live[q]) continue;\n";
+    if (s.out_dtype[io] == BSIR_F32) {
+      appendf(c, "    float *d = (float *)a.out[%d] + (row * a.out_stride[%d] + c0v[q]);\n", io, io);
+      appendf(c, "    st_stream(d, __float_as_uint(%s[q][0]), __float_as_uint(%s[q][1]), __float_as_uint(%s[q][2]), __float_as_uint(%s[q][3]));\n", vn, vn, vn, vn);
+      appendf(c, "    st_stream(d + 4, __float_as_uint(%s[q][4]), __float_as_uint(%s[q][5]), __float_as_uint(%s[q][6]), __float_as_uint(%s[q][7]));\n", vn, vn, vn, vn);
+    } else {
+      const char *pk = s.out_dtype[io] == BSIR_BF16 ? "pk_bf16" : "pk_f16";
+      appendf(c, "    st_stream((u16 *)a.out[%d] + (row * a.out_stride[%d] + c0v[q]), %s(%s[q][0], %s[q][1]), %s(%s[q][2], %s[q][3]), %s(%s[q][4], %s[q][5]), %s(%s[q][6], %s[q][7]));\n",
+              io, io, pk, vn, vn, pk, vn, vn, pk, vn, vn, pk, vn, vn);
+    }
+    c += "  }\n";
+  }
+  c += "}\n";
+  return c;
+}
+
+}  // namespace
+
 int chain_jit_compile_only(const ChainJitSpec &s, size_t *cubin_bytes, std::string *why) {
   const std::vector<char> cubin = compile_cubin(chain_jit_source(s), why);
   if (cubin.empty()) return -1;
@@ -426,6 +609,23 @@ int chain_jit_launch(const ChainJitSpec &s, const ChainJitArgs &args, cudaStream
       return -1;
     }
     kernel = it->second.kernel;
+  }
+  if (s.tpr > 0) {
+    const int bt = s.tpr > 128 ? s.tpr : 128;
+    const int64_t nblocks = (args.rows + bt / s.tpr - 1) / (bt / s.tpr);
+    if (nblocks > 0x7fffffffLL) {
+      *why = "grid too large";
+      return -1;
+    }
+    ChainJitArgs copy = args;
+    void *params[] = {&copy};
+    const cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void *>(kernel), dim3(static_cast<unsigned>(nblocks)), dim3(bt), params, 0, st);
+    if (e != cudaSuccess) {
+      *why = std::string("launching the compiled chain: ") + cudaGetErrorString(e);
+      (void)cudaGetLastError();
+      return -1;
+    }
+    return 0;
   }
   const int U = chain_jit_unroll(s);
   const bool rows_on_x = s.row_grid && !s.flat;

@@ -20,11 +20,14 @@ struct ChainJitSpec {
   bool alias = false;   // an output overlaps an operand: operands are read with coherent loads
   bool row_grid = false;   // blockIdx.x is the row, blockIdx.y a stretch of it (no division); set by chain_jit_plan
   int unroll = 0;          // groups per thread; 0: chosen from the operands
+  // a chain with last-axis reductions (a row program): threads per row and groups per thread; 0: no reductions
+  int tpr = 0, vpt = 0;
+  bool out_per_row[4] = {};   // the output is a [rows] vector (its value is the same along the row)
 };
 
 // The kernel's parameter block (the generated source declares the same layout).
 struct ChainJitArgs {
-  long long gpr, total;   // 8-element groups per row, and in all
+  long long gpr, total, rows;   // 8-element groups per row, groups in all, rows
   const void *in[8];
   long long in_stride[8];
   void *out[4];

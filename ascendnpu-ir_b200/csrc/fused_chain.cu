@@ -426,6 +426,7 @@ ChainJitSpec make_spec(int32_t n_in, const bsir_chain_operand *ins, int32_t n_in
   for (int i = 0; i < n_instr; ++i) {
     s.tape[i] = tape[i];
     // fields an instruction does not read must not split the cache
+    if (tape[i].op == BSIR_CHAIN_REDUCE) { s.tape[i].src_kind = 0; s.tape[i].src = 0; s.tape[i].imm = 0.0f; continue; }
     if (tape[i].op == BSIR_CHAIN_UNARY || tape[i].op == BSIR_CHAIN_SAVE) { s.tape[i].src_kind = 0; s.tape[i].imm = 0.0f; }
     if (tape[i].op == BSIR_CHAIN_UNARY) s.tape[i].src = 0;
     if (tape[i].op == BSIR_CHAIN_SAVE || tape[i].op == BSIR_CHAIN_LOAD) s.tape[i].fn = 0;
@@ -438,7 +439,7 @@ ChainJitSpec make_spec(int32_t n_in, const bsir_chain_operand *ins, int32_t n_in
 
 // Checks of a chain that need no sizes (shared by the launch and by the source / compile entry points).
 int32_t validate_tape(int32_t n_in, const bsir_chain_operand *ins, int32_t n_instr, const bsir_chain_instr *tape, int32_t n_out,
-                      const bsir_chain_output *outs, bool (&tmp_used)[kChainTemps]) {
+                      const bsir_chain_output *outs, bool (&tmp_used)[kChainTemps], bool *has_reduce = nullptr) {
   if (n_in < 0 || n_in > kChainMaxOperands || n_instr < 1 || n_instr > kChainMaxInstr || n_out < 1 || n_out > kChainMaxOutputs)
     return fail(BSIR_ERR_SHAPE, "fused_elementwise: %d operands (max %d), %d instructions (1..%d), %d outputs (1..%d)", n_in,
                 kChainMaxOperands, n_instr, kChainMaxInstr, n_out, kChainMaxOutputs);
@@ -451,8 +452,12 @@ int32_t validate_tape(int32_t n_in, const bsir_chain_operand *ins, int32_t n_ins
   for (int t = 0; t < kChainTemps; ++t) tmp_used[t] = false;
   for (int i = 0; i < n_instr; ++i) {
     const bsir_chain_instr &t = tape[i];
-    if (t.op < BSIR_CHAIN_LOAD || t.op > BSIR_CHAIN_SAVE) return fail(BSIR_ERR_ATTR, "fused_elementwise: instruction %d op %d", i, t.op);
-    if (t.op == BSIR_CHAIN_SAVE) {
+    if (t.op < BSIR_CHAIN_LOAD || t.op > BSIR_CHAIN_REDUCE) return fail(BSIR_ERR_ATTR, "fused_elementwise: instruction %d op %d", i, t.op);
+    if (t.op == BSIR_CHAIN_REDUCE) {
+      if (t.fn != BSIR_REDUCE_SUM && t.fn != BSIR_REDUCE_PROD && t.fn != BSIR_REDUCE_MAX && t.fn != BSIR_REDUCE_MIN)
+        return fail(BSIR_ERR_ATTR, "fused_elementwise: instruction %d reduce kind %d (sum, prod, max, min)", i, t.fn);
+      if (has_reduce) *has_reduce = true;
+    } else if (t.op == BSIR_CHAIN_SAVE) {
       if (t.src < 0 || t.src >= kChainTemps) return fail(BSIR_ERR_ATTR, "fused_elementwise: instruction %d saves to temporary %d", i, t.src);
       tmp_used[t.src] = tmp_saved[t.src] = true;
     } else if (t.op == BSIR_CHAIN_UNARY) {
@@ -479,6 +484,24 @@ int32_t validate_tape(int32_t n_in, const bsir_chain_operand *ins, int32_t n_ins
   return BSIR_OK;
 }
 
+// Threads per row and groups per thread of a chain with reductions: the row stays in registers, so the groups a
+// thread holds are bounded by what one group costs in registers.  false: one block cannot hold a row.
+bool plan_rows(ChainJitSpec *s, int64_t gpr, const bool (&tmp_used)[kChainTemps]) {
+  int regs = 16;   // the accumulator and one unpacked operand
+  for (int t = 0; t < kChainTemps; ++t) regs += tmp_used[t] ? 8 : 0;
+  for (int i = 0; i < s->n_in; ++i)
+    if (s->in_kind[i] == BSIR_CHAIN_FULL || s->in_kind[i] == BSIR_CHAIN_ROW_VECTOR) regs += s->in_dtype[i] == BSIR_F32 ? 8 : 4;
+  const int fit = 112 / regs, vmax = fit >= 8 ? 8 : fit >= 4 ? 4 : fit >= 2 ? 2 : 1;
+  const int64_t need = ceil_div(gpr, vmax);
+  int tpr = 4;
+  while (tpr < need && tpr < 1024) tpr *= 2;
+  const int64_t vpt = ceil_div(gpr, tpr);
+  if (vpt > 8) return false;
+  s->tpr = tpr;
+  s->vpt = static_cast<int>(vpt);
+  return true;
+}
+
 // 0: interpreter only; 1: the compiled kernel or an error; 2 (default): compiled when it can be, else the interpreter
 int jit_mode() {
   const char *e = std::getenv("BSIR_CHAIN_JIT");
@@ -497,8 +520,8 @@ extern "C" int32_t bsir_fused_elementwise(int64_t rows, int64_t cols, int32_t n_
   clear_error();
   tl_chain_path = 0;
   if (rows < 0 || cols < 0) return fail(BSIR_ERR_SHAPE, "fused_elementwise: rows=%lld cols=%lld", (long long)rows, (long long)cols);
-  bool tmp_used[kChainTemps];
-  if (const int32_t rc = validate_tape(n_in, ins, n_instr, tape, n_out, outs, tmp_used)) return rc;
+  bool tmp_used[kChainTemps], has_reduce = false;
+  if (const int32_t rc = validate_tape(n_in, ins, n_instr, tape, n_out, outs, tmp_used, &has_reduce)) return rc;
 
   // ---- sizes and addresses; decides whether the 16-byte paths apply ----
   bool vec = cols % kGroup == 0, flat = true;
@@ -515,9 +538,13 @@ extern "C" int32_t bsir_fused_elementwise(int64_t rows, int64_t cols, int32_t n_
   for (int i = 0; i < n_out; ++i) {
     const bsir_chain_output &o = outs[i];
     if (!o.data && rows * cols > 0) return fail(BSIR_ERR_NULL, "fused_elementwise: output %d is null", i);
-    if (o.row_stride < cols) return fail(BSIR_ERR_STRIDE, "fused_elementwise: output %d row stride", i);
     const int eb = dtype_bytes(o.dtype);
     if (!aligned_to(o.data, eb)) return fail(BSIR_ERR_ALIGN, "fused_elementwise: output %d misaligned", i);
+    if (o.row_stride == 0) {   // a [rows] vector
+      if (!has_reduce) return fail(BSIR_ERR_ATTR, "fused_elementwise: output %d is per row, but the chain has no reduction", i);
+      continue;
+    }
+    if (o.row_stride < cols) return fail(BSIR_ERR_STRIDE, "fused_elementwise: output %d row stride", i);
     vec = vec && aligned_to(o.data, 16) && (o.row_stride * eb) % 16 == 0;
     flat = flat && o.row_stride == cols;
   }
@@ -526,6 +553,9 @@ extern "C" int32_t bsir_fused_elementwise(int64_t rows, int64_t cols, int32_t n_
 
   // ---- the compiled kernel: one per distinct chain, built on first use ----
   const int mode = jit_mode();
+  if (has_reduce && (mode == 0 || !vec))
+    return fail(BSIR_ERR_UNSUPPORTED, "fused_elementwise: a chain with reductions runs only as a compiled kernel over 16-byte aligned "
+                                      "rows of a multiple of 8 columns");
   if (mode != 0 && !vec && mode == 1) return fail(BSIR_ERR_UNSUPPORTED, "fused_elementwise: the compiled path needs 16-byte aligned rows of a multiple of 8 columns");
   if (mode != 0 && vec) {
     // an output that overlaps an operand (in-place use) makes the operands' loads coherent ones
@@ -536,15 +566,23 @@ extern "C" int32_t bsir_fused_elementwise(int64_t rows, int64_t cols, int32_t n_
       const char *a0 = static_cast<const char *>(ins[i].data), *a1 = a0 + n_el * dtype_bytes(ins[i].dtype);
       for (int k = 0; k < n_out; ++k) {
         const char *b0 = static_cast<const char *>(outs[k].data);
-        const char *b1 = b0 + ((rows - 1) * outs[k].row_stride + cols) * dtype_bytes(outs[k].dtype);
+        const int64_t m_el = outs[k].row_stride == 0 ? rows : (rows - 1) * outs[k].row_stride + cols;
+        const char *b1 = b0 + m_el * dtype_bytes(outs[k].dtype);
         if (a0 < b1 && b0 < a1) alias = true;
       }
     }
     ChainJitSpec spec = make_spec(n_in, ins, n_instr, tape, n_out, outs, flat, alias);
-    chain_jit_plan(&spec, cols / kGroup);
+    if (has_reduce) {
+      for (int i = 0; i < n_out; ++i) spec.out_per_row[i] = outs[i].row_stride == 0;
+      if (!plan_rows(&spec, cols / kGroup, tmp_used))
+        return fail(BSIR_ERR_UNSUPPORTED, "fused_elementwise: rows of %lld columns do not fit the registers of one block for this chain", (long long)cols);
+    } else {
+      chain_jit_plan(&spec, cols / kGroup);
+    }
     ChainJitArgs args{};
     args.gpr = cols / kGroup;
     args.total = rows * args.gpr;
+    args.rows = rows;
     for (int i = 0; i < n_in; ++i) { args.in[i] = ins[i].data; args.in_stride[i] = ins[i].row_stride; }
     for (int i = 0; i < n_out; ++i) { args.out[i] = outs[i].data; args.out_stride[i] = outs[i].row_stride; }
     std::string why;
@@ -553,7 +591,7 @@ extern "C" int32_t bsir_fused_elementwise(int64_t rows, int64_t cols, int32_t n_
       count_launch();
       return check_launch("fused_elementwise");
     }
-    if (mode == 1) return fail(BSIR_ERR_UNSUPPORTED, "fused_elementwise: %s", why.c_str());
+    if (mode == 1 || has_reduce) return fail(BSIR_ERR_UNSUPPORTED, "fused_elementwise: %s", why.c_str());
   }
   tl_chain_path = 1;
 
@@ -638,9 +676,15 @@ extern "C" int64_t bsir_fused_elementwise_source(int32_t n_in, const bsir_chain_
                                                  int32_t flags, char *buf, int64_t cap) {
   clear_error();
   bool tmp_used[kChainTemps];
-  if (const int32_t rc = validate_tape(n_in, ins, n_instr, tape, n_out, outs, tmp_used)) return rc;
+  bool has_reduce = false;
+  if (const int32_t rc = validate_tape(n_in, ins, n_instr, tape, n_out, outs, tmp_used, &has_reduce)) return rc;
   ChainJitSpec spec = make_spec(n_in, ins, n_instr, tape, n_out, outs, (flags & 1) != 0, (flags & 2) != 0);
   spec.row_grid = (flags & 4) != 0 && !spec.flat;
+  if (has_reduce) {
+    for (int i = 0; i < n_out; ++i) spec.out_per_row[i] = outs[i].row_stride == 0;
+    const int64_t gpr = (flags >> 8) > 0 ? (flags >> 8) : 512;
+    if (!plan_rows(&spec, gpr, tmp_used)) return fail(BSIR_ERR_UNSUPPORTED, "fused_elementwise_source: rows of %lld groups do not fit one block", (long long)gpr);
+  }
   const std::string src = chain_jit_source(spec);
   if (buf && cap > 0) {
     const size_t n = src.size() < static_cast<size_t>(cap - 1) ? src.size() : static_cast<size_t>(cap - 1);
@@ -655,11 +699,17 @@ extern "C" int32_t bsir_fused_elementwise_compile(int32_t n_in, const bsir_chain
                                                   int32_t flags, int64_t *cubin_bytes) {
   clear_error();
   bool tmp_used[kChainTemps];
-  if (const int32_t rc = validate_tape(n_in, ins, n_instr, tape, n_out, outs, tmp_used)) return rc;
+  bool has_reduce = false;
+  if (const int32_t rc = validate_tape(n_in, ins, n_instr, tape, n_out, outs, tmp_used, &has_reduce)) return rc;
   size_t sz = 0;
   std::string why;
   ChainJitSpec spec = make_spec(n_in, ins, n_instr, tape, n_out, outs, (flags & 1) != 0, (flags & 2) != 0);
   spec.row_grid = (flags & 4) != 0 && !spec.flat;
+  if (has_reduce) {
+    for (int i = 0; i < n_out; ++i) spec.out_per_row[i] = outs[i].row_stride == 0;
+    const int64_t gpr = (flags >> 8) > 0 ? (flags >> 8) : 512;
+    if (!plan_rows(&spec, gpr, tmp_used)) return fail(BSIR_ERR_UNSUPPORTED, "fused_elementwise_compile: rows of %lld groups do not fit one block", (long long)gpr);
+  }
   if (chain_jit_compile_only(spec, &sz, &why) != 0)
     return fail(BSIR_ERR_UNSUPPORTED, "fused_elementwise_compile: %s", why.c_str());
   if (cubin_bytes) *cubin_bytes = static_cast<int64_t>(sz);

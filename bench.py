@@ -238,6 +238,35 @@ def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters, only=None):
         rec("chain_rmstail_bf16_32768x4096", 2 * rows * cols * 2 + cols * 2 + rows * 4, rms_tail)
         rec("chain_gelu_bf16_32768x4096", 2 * rows * cols * 2, gelu)
         del xs, ys, rstd
+    if want("chain_rmsnorm_bf16_32768x4096"):
+        # the same RMSNorm as rmsnorm_bf16_32768x4096, written as a chain with one row reduction (compiled per chain)
+        rows, cols = 32768, 4096
+        xs = [W.rmsnorm_input(rows, cols, seed=s) for s in range(2)]
+        ys = [torch.empty_like(x[0]) for x in xs]
+
+        def rms_chain(i):
+            ch = bsir.FusedChain()
+            hx, hg = ch.op(ch.operand(xs[i % 2][0])), ch.op(ch.operand(xs[i % 2][1], "row_vector"))
+            (ch.load(hx).unary("square").reduce("sum").binary("div", float(cols)).binary("add", 1e-6).unary("sqrt").unary("rec")
+               .binary("mul", hx).rbinary("mul", hg))
+            ch.run(rows, cols, outs=[(ys[i % 2], -1)])
+
+        rec("chain_rmsnorm_bf16_32768x4096", 2 * rows * cols * 2 + cols * 2, rms_chain)
+        del xs, ys
+    if want("chain_softmax_bf16_4096x32768"):
+        rows, cols = 4096, 32768
+        xs = [W.softmax_input(rows, cols, seed=s) for s in range(2)]
+        ys = [torch.empty_like(x) for x in xs]
+
+        def softmax_chain(i):
+            ch = bsir.FusedChain()
+            hx = ch.op(ch.operand(xs[i % 2]))
+            (ch.load(hx).reduce("max").save(0).load(hx).binary("sub", ("tmp", 0)).unary("exp").save(1).reduce("sum")
+               .rbinary("div", ("tmp", 1)))
+            ch.run(rows, cols, outs=[(ys[i % 2], -1)])
+
+        rec("chain_softmax_bf16_4096x32768", 2 * rows * cols * 2, softmax_chain)
+        del xs, ys
     for m in (16, 128, 4096):
         if not want(f"w8a8_m{m}"):
             continue

@@ -320,7 +320,15 @@ BSIR_API int32_t bsir_rms_norm(int32_t dtype, int64_t rows, int64_t cols, const 
  *   BINARY  acc = fn(acc, src)        RBINARY acc = fn(src, acc)
  * src is an input operand, a temporary or the immediate.  fn is a bsir_unary_fn / bsir_binary_fn that
  * has an f32 form.  Operands and outputs are f32 / f16 / bf16; an output takes the accumulator
- * (tmp = -1) or a temporary.  At most 8 operands, 24 instructions, 4 outputs. */
+ * (tmp = -1) or a temporary.  At most 8 operands, 24 instructions, 4 outputs.
+ *   REDUCE  acc = reduce over the row of acc (fn = BSIR_REDUCE_SUM / PROD / MAX / MIN), broadcast back to the row
+ * turns the chain into a LAST_AXIS_PBR function (elementwise + broadcast + last-axis reductions, e.g. a whole
+ * RMSNorm, softmax or LayerNorm): the threads of a row keep it in registers across the reductions, so every
+ * operand is still read once.  Sums associate as a tree, not left to right.  An output with row_stride = 0 is a
+ * [rows] vector and takes a value that is uniform along the row (a reduction result and what is computed from
+ * it).  Chains with REDUCE exist only as compiled kernels: 16-byte aligned rows of a multiple of 8 columns, at
+ * most 8192 columns per temporary-free bf16 chain (less with f32 operands or temporaries: the row must fit the
+ * registers of 1024 threads); otherwise BSIR_ERR_UNSUPPORTED. */
 typedef enum bsir_chain_operand_kind {
   BSIR_CHAIN_FULL = 0,        /* [rows, cols], row_stride in elements             */
   BSIR_CHAIN_ROW_VECTOR = 1,  /* [cols], the same for every row (linalg.broadcast dimensions = [0]) */
@@ -328,7 +336,8 @@ typedef enum bsir_chain_operand_kind {
   BSIR_CHAIN_SCALAR = 3       /* one element in device memory                     */
 } bsir_chain_operand_kind;
 typedef enum bsir_chain_op {
-  BSIR_CHAIN_LOAD = 0, BSIR_CHAIN_UNARY = 1, BSIR_CHAIN_BINARY = 2, BSIR_CHAIN_RBINARY = 3, BSIR_CHAIN_SAVE = 4
+  BSIR_CHAIN_LOAD = 0, BSIR_CHAIN_UNARY = 1, BSIR_CHAIN_BINARY = 2, BSIR_CHAIN_RBINARY = 3, BSIR_CHAIN_SAVE = 4,
+  BSIR_CHAIN_REDUCE = 5
 } bsir_chain_op;
 typedef enum bsir_chain_src { BSIR_CHAIN_SRC_OPERAND = 0, BSIR_CHAIN_SRC_TMP = 1, BSIR_CHAIN_SRC_IMM = 2 } bsir_chain_src;
 typedef struct bsir_chain_operand { const void *data; int64_t row_stride; int32_t dtype; int32_t kind; } bsir_chain_operand;
@@ -345,7 +354,8 @@ BSIR_API int32_t bsir_fused_elementwise(int64_t rows, int64_t cols, int32_t n_in
 BSIR_API int32_t bsir_fused_elementwise_path(void);
 /* The CUDA C++ that would be compiled for a chain (data pointers and strides are not read).  flags: bit 0 every
  * tensor is contiguous (flat addressing), bit 1 an output overlaps an operand, bit 2 one block per stretch of a
- * row (the mapping chosen for rows that fill whole blocks) instead of a division per group.  Writes at most cap bytes
+ * row (the mapping chosen for rows that fill whole blocks) instead of a division per group; for a chain with
+ * REDUCE bits 8.. give cols / 8 (the thread geometry depends on the row length; default 512).  Writes at most cap bytes
  * (NUL-terminated) and returns the bytes needed, or a negative bsir_status. */
 BSIR_API int64_t bsir_fused_elementwise_source(int32_t n_in, const bsir_chain_operand *ins, int32_t n_instr,
                                                const bsir_chain_instr *tape, int32_t n_out, const bsir_chain_output *outs,

@@ -92,3 +92,27 @@ def test_every_function_compiles_for_sm_100a():
         ch2.binary(fn, 1.25)
     assert ch2.compile(outs=[(torch.bfloat16, -1)]) > 1000
     assert _rms_tail().compile(outs=[(torch.bfloat16, -1)], contiguous=False) > 1000
+
+
+@pytest.mark.skipif(not _nvrtc_available(), reason="no NVRTC library in this environment")
+def test_chains_with_reductions_compile_for_short_and_long_rows():
+    """A LAST_AXIS_PBR chain: the generated kernel keeps the row in registers (threads per row and groups per thread
+    follow the row length)."""
+    x = torch.zeros(4, 64, dtype=torch.bfloat16)
+    ch = bsir.FusedChain()
+    hx, hg = ch.op(ch.operand(x)), ch.op(ch.operand(torch.zeros(64, dtype=torch.bfloat16), "row_vector"))
+    (ch.load(hx).unary("square").reduce("sum").binary("div", 64.0).binary("add", 1e-6).unary("sqrt").unary("rec").save(0)
+       .binary("mul", hx).rbinary("mul", hg))
+    outs = [(torch.bfloat16, -1), (torch.zeros(4), 0)]
+    short, mid = ch.source(outs=outs, cols=64), ch.source(outs=outs, cols=4096)
+    assert "#define TPR 4\n" in short and "#define VPT 2\n" in short
+    assert "#define TPR 256\n" in mid and "#define VPT 2\n" in mid       # one temporary: two groups per thread
+    assert "row_sum(p, red)" in mid and "((float *)a.out[1])[row] = t0[0][0]" in mid
+    for cols in (64, 4096, 32768):
+        assert ch.compile(outs=outs, cols=cols) > 1000
+    with pytest.raises(bsir.BsirError):
+        ch.source(outs=outs, cols=1 << 20)                       # a row that no block can hold
+    ch2 = bsir.FusedChain()
+    ch2.load(ch2.op(ch2.operand(x))).reduce("any")               # not a float reduction
+    with pytest.raises(bsir.BsirError):
+        ch2.source()

@@ -154,3 +154,78 @@ def test_compiled_path_refuses_ragged_rows_when_required(bsir, monkeypatch):
     ch.load(ch.op(ch.operand(x)))
     with pytest.raises(bsir.BsirError):
         ch.run()
+
+
+# ---------------------------------------------------------------------------- chains with last-axis reductions
+def _rms_chain(bsir, x, gamma, eps):
+    ch = bsir.FusedChain()
+    hx, hg = ch.op(ch.operand(x)), ch.op(ch.operand(gamma, "row_vector"))
+    (ch.load(hx).unary("square").reduce("sum").binary("div", float(x.shape[1])).binary("add", eps).unary("sqrt").unary("rec")
+       .save(0).binary("mul", hx).rbinary("mul", hg))
+    return ch
+
+
+@pytest.mark.parametrize("dtype,rows,cols", [(torch.bfloat16, 64, 4096), (torch.float16, 40, 512), (torch.float32, 1001, 64),
+                                             (torch.bfloat16, 7, 8192), (torch.bfloat16, 3, 32768), (torch.float16, 300, 8)])
+def test_rms_norm_as_a_chain_with_a_reduction(bsir, dtype, rows, cols):
+    """A whole RMSNorm (LAST_AXIS_PBR): square, row sum, scalar tail, two multiplies, the per-row rstd as a second
+    output -- one kernel, against the oracle's RMSNorm (the row sum associates differently: tolerance as for the
+    hand-written kernel)."""
+    g = torch.Generator(device="cuda").manual_seed(cols)
+    x = torch.randn(rows, cols, device="cuda", generator=g).to(dtype)
+    gamma = (1 + 0.1 * torch.randn(cols, device="cuda", generator=g)).to(dtype)
+    n0 = bsir.launch_count()
+    y, rstd = _rms_chain(bsir, x, gamma, 1e-6).run(outs=[(dtype, -1), (torch.empty(rows, dtype=dtype, device="cuda"), 0)])
+    assert bsir.launch_count() - n0 == 1 and bsir.FusedChain.last_path() == "compiled"
+    dt = oracle_dtype(x)
+    wy, wr = O.rms_norm(dt, to_bits(x), to_bits(gamma), 1e-6, want_rstd=True)
+    from conftest import assert_close
+    assert_close(y, wy, 1e-2, 1e-3, "rms-norm chain")
+    assert_close(rstd, wr, 1e-2, 1e-3, "rstd of the chain")
+
+
+@pytest.mark.parametrize("dtype,rows,cols", [(torch.bfloat16, 33, 4096), (torch.float32, 257, 1000), (torch.float16, 5, 32768)])
+def test_softmax_as_a_chain_with_two_reductions(bsir, dtype, rows, cols):
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    x = (4 * torch.randn(rows, cols, device="cuda", generator=g)).to(dtype)
+    ch = bsir.FusedChain()
+    hx = ch.op(ch.operand(x))
+    ch.load(hx).reduce("max").save(0).load(hx).binary("sub", ("tmp", 0)).unary("exp").save(1).reduce("sum").rbinary("div", ("tmp", 1))
+    y = ch.run(out_dtype=dtype)
+    assert bsir.FusedChain.last_path() == "compiled"
+    from conftest import assert_close
+    assert_close(y, O.softmax(oracle_dtype(x), to_bits(x)), 2e-2, 1e-6, "softmax chain")
+    assert abs(y.float().sum(dim=1) - 1).max().item() < 2e-2
+
+
+def test_row_maximum_of_absolute_values_is_exact(bsir):
+    """max is associative: the per-row output equals the op-by-op result exactly (a NaN row gives NaN in both; the
+    payload of a NaN that went through max.NaN is not compared)."""
+    x = torch.randn(500, 2048, device="cuda").to(torch.bfloat16)
+    x[7, 100] = float("nan")
+    x[9, :] = float("-inf")
+    ch = bsir.FusedChain()
+    ch.load(ch.op(ch.operand(x))).unary("abs").reduce("max")
+    amax = ch.run(outs=[(torch.empty(500, dtype=torch.float32, device="cuda"), -1)])
+    want = bsir.reduce("max", bsir.elemwise_unary("abs", x.float()), dim=1)
+    assert np.array_equal(to_bits(amax), to_bits(want), equal_nan=True)
+    assert torch.isnan(amax[7]) and amax[9] == float("inf")
+
+
+def test_chains_with_reductions_need_the_compiled_path(bsir, monkeypatch):
+    x = torch.randn(4, 20, device="cuda")                 # 20 columns: not a multiple of 8
+    ch = bsir.FusedChain()
+    ch.load(ch.op(ch.operand(x))).reduce("sum")
+    with pytest.raises(bsir.BsirError):
+        ch.run()
+    monkeypatch.setenv("BSIR_CHAIN_JIT", "0")
+    x = torch.randn(4, 64, device="cuda")
+    ch = bsir.FusedChain()
+    ch.load(ch.op(ch.operand(x))).reduce("sum")
+    with pytest.raises(bsir.BsirError):
+        ch.run()
+    ch = bsir.FusedChain()                                 # a per-row output without a reduction
+    ch.load(ch.op(ch.operand(x)))
+    monkeypatch.setenv("BSIR_CHAIN_JIT", "2")
+    with pytest.raises(bsir.BsirError):
+        ch.run(outs=[(torch.empty(4, device="cuda"), -1)])
