@@ -18,6 +18,12 @@ Covered (attribute spellings as in the reference):
   arith.{index_cast,index_castui,uitofp,sitofp,extf,truncf}, return
 Scalar arithmetic is done in the scalar's own type (f32 ops round to f32).  Anything else raises MlirTextError
 with the op's name, so an unsupported file fails loudly instead of computing something different.
+
+Fusion (``Function.fuse``, on by default): elementwise ops, fills, broadcasts and last-axis reductions on f32 tensors,
+with the casts at the edges of such a region, are not launched one by one; they are recorded (fusion.py) and every
+value the function needs in memory is produced by one fused kernel per [rows, cols] problem -- an outlined
+LAST_AXIS_PBR function such as RMSNorm or softmax is one launch.  Elementwise regions keep the bits of op-by-op
+execution; a fused row sum associates as a tree.
 """
 import re
 from typing import Dict, List, Optional, Sequence
@@ -68,6 +74,20 @@ class Scalar:
             self.value = float(value)
         else:
             self.value = int(value)
+
+
+def _float_literal(text: str, ty: str) -> float:
+    """A float constant as MLIR prints it: decimal, or the bit pattern in hex (`0xFF800000 : f32` is -inf)."""
+    if text.lower().startswith("0x"):
+        bits = int(text, 16)
+        if ty == "f32":
+            return float(np.array([bits], dtype=np.uint32).view(np.float32)[0])
+        if ty == "f16":
+            return float(np.array([bits], dtype=np.uint16).view(np.float16)[0])
+        if ty == "bf16":
+            return float(np.array([bits << 16], dtype=np.uint32).view(np.float32)[0])
+        return float(np.array([bits], dtype=np.uint64).view(np.float64)[0])
+    return float(text)
 
 
 def _strip_comments(text: str) -> str:
@@ -206,56 +226,148 @@ class Function:
             return getattr(torch, _TORCH_NAMES[elem])
 
         from . import fusion
-        pending: List[str] = []                                # deferred values the op being looked at would consume
         arg_ptrs = {t.data_ptr() for t in tensors if isinstance(t, torch.Tensor)}
+        requests: List[tuple] = []                             # (Lazy, destination) pairs waiting to run together
+        consumed = set()                                       # deferred values folded into another expression
+
+        def flush():
+            """Runs what is waiting: all requests over one [rows, cols] problem as one kernel (four outputs at most)."""
+            groups: Dict[tuple, list] = {}
+            for lz, dst in requests:
+                groups.setdefault(lz.prob, []).append((lz, dst))
+            requests.clear()
+            for prob, group in groups.items():
+                for i in range(0, len(group), fusion.MAX_OUTPUTS):
+                    fusion.run(group[i:i + fusion.MAX_OUTPUTS], prob)
+
+        def request(lz, dst=None):
+            """Asks for a deferred value in memory (in dst, in the op's own destination, or in a new f32 tensor)."""
+            if dst is None:
+                dst = lz.dst if lz.dst is not None else torch.empty(lz.shape, dtype=torch.float32, device=dev)
+            requests.append((lz, dst))
+            return dst
 
         def val(name):
             if name not in env:
                 raise MlirTextError(f"use of undefined value {name}")
-            if isinstance(env[name], fusion.Lazy):            # needed in memory: the expression runs now, as one kernel
-                env[name] = fusion.materialise(env[name])
+            if isinstance(env[name], fusion.Lazy):            # needed in memory now
+                env[name] = request(env[name])
+            if requests and isinstance(env[name], torch.Tensor):
+                flush()
             return env[name]
 
-        def node_of(name, shape):
-            """The chain node for an operand of an f32 elementwise op of this result shape, or None."""
+        def node_of(name, shape, prob, per_row, touched):
+            """The chain node for an operand of a fusible op whose result has this shape in this problem, or None."""
             v = env.get(name)
             if isinstance(v, Scalar):
                 return ("imm", float(v.value))
             if isinstance(v, fusion.Lazy):
                 if v.shape != list(shape):
                     return None
-                if v.node[0] not in ("leaf", "imm"):           # a leaf costs nothing to share; an expression has one user
-                    pending.append(name)
+                if per_row and not v.per_row and v.node[0] == "leaf" and v.node[2] == "full":
+                    return ("leaf", v.node[1].reshape(-1), "col_vector")      # a widened [rows] vector
+                if v.prob != tuple(prob) or v.per_row != per_row:
+                    return None
+                touched.append(name)
                 return v.node
             if isinstance(v, torch.Tensor) and list(v.shape) == list(shape) and v.dtype == torch.float32 and v.is_contiguous():
-                return ("leaf", v.view(*fusion.problem(list(shape))), "full")
+                if requests and any(d.data_ptr() == v.data_ptr() for _, d in requests):
+                    flush()                                    # it is about to be written
+                return ("leaf", v, "col_vector") if per_row else ("leaf", v.view(*prob), "full")
             return None
 
-        def defer(op, node, dst):
-            """Defines the op's result as a deferred expression; a value with several uses is computed once, now."""
-            shape = list(dst.shape)
+        def defer(op, node, shape, prob, per_row, touched):
+            """Defines the op's result as a deferred expression (nothing is launched)."""
             if not fusion.fits(node):
                 return False
-            for n in pending:                                  # folded into this expression: never launched on their own
-                env[n] = None
-            lazy = fusion.Lazy(node, shape, dst)
-            env[op.results[0]] = lazy
-            if self.uses.get(op.results[0], 0) != 1 and node[0] not in ("leaf", "imm"):
-                env[op.results[0]] = fusion.materialise(lazy)
+            consumed.update(touched)
+            dst = None
+            outs_names = op.group("outs")[0]
+            if outs_names and self.uses.get(outs_names[0], 0) == 1 and isinstance(env.get(outs_names[0]), torch.Tensor):
+                cand = env[outs_names[0]]                      # the op's own destination, when no other op writes it
+                if cand.dtype == torch.float32 and list(cand.shape) == list(shape) and cand.is_contiguous():
+                    dst = cand
+            env[op.results[0]] = fusion.Lazy(node, list(shape), prob, per_row, dst)
             return True
 
-        def vector_leaf(name):
-            """A contiguous float vector, or a widening cast of one, as the tensor a chain reads."""
-            v = env.get(name)
-            if isinstance(v, fusion.Lazy) and v.node[0] == "leaf" and v.node[2] == "full" and len(v.shape) == 1:
-                return v.node[1].reshape(-1)
-            if isinstance(v, torch.Tensor) and v.dim() == 1 and v.is_contiguous() and v.dtype == torch.float32:
-                return v
-            return None
-
-        def fusible(dst):
-            return (self.fuse and isinstance(dst, torch.Tensor) and dst.dtype == torch.float32 and dst.dim() in (1, 2)
-                    and dst.is_contiguous() and dst.numel() > 0 and len(op.results) == 1)
+        def try_fuse(op, name, ins, outs) -> bool:
+            """f32 elementwise ops, fills, broadcasts, last-axis reductions and the casts at the edges of an f32 region
+            are deferred; True when the op was taken care of."""
+            if len(op.results) != 1 or not outs:
+                return False
+            init = env.get(outs[0])
+            if name == "linalg.reduce" and isinstance(init, fusion.Lazy) and init.node[0] == "imm" and len(init.shape) == 1:
+                # the accumulator was filled with a constant: the reduction starts from it
+                src = env.get(ins[0]) if ins else None
+                comb = next((c for c in _REDUCE_COMBINERS if re.search(rf"\b{re.escape(c)}\b", op.text)), None)
+                kind = _REDUCE_COMBINERS.get(comb)
+                if kind in fusion.REDUCE and isinstance(src, fusion.Lazy) and not src.per_row and len(src.shape) == 2 and \
+                        src.shape[0] == init.shape[0] and op.int_list("dimensions") == [1]:
+                    fold = {"sum": "add", "prod": "mul", "max": "maxf", "min": "minf"}[kind]
+                    return defer(op, ("bin", fold, ("red", kind, src.node), init.node), init.shape, src.prob, True, [ins[0]])
+                return False
+            if not isinstance(init, torch.Tensor):
+                return False
+            dst = init
+            if not dst.is_contiguous() or dst.numel() == 0 or dst.dim() not in (1, 2):
+                return False
+            shape, touched = list(dst.shape), []
+            if name == "hfusion.cast":
+                src = env.get(ins[0])
+                if isinstance(src, fusion.Lazy) and dst.dtype in (torch.float16, torch.bfloat16) and src.shape == shape and \
+                        (op.attr("round_mode") or op.attr("mode") or "rint") == "rint" and not op.attr("enable_saturate", False) and \
+                        op.attr("overflow_mode") is None:
+                    consumed.add(ins[0])
+                    env[op.results[0]] = request(src, dst)     # the chain's single rounding
+                    return True
+                if isinstance(src, torch.Tensor) and src.dtype in (torch.float16, torch.bfloat16) and dst.dtype == torch.float32 and \
+                        list(src.shape) == shape and src.is_contiguous():
+                    if requests and any(d.data_ptr() == src.data_ptr() for _, d in requests):
+                        flush()
+                    prob = fusion.problem(shape)               # a widening cast is exact: the chain reads the 16-bit storage
+                    return defer(op, ("leaf", src.view(*prob), "full"), shape, prob, False, touched)
+                return False
+            if dst.dtype != torch.float32:
+                return False
+            # the problem the op lives in: that of a per-row operand, else the result's own shape
+            per_row_src = next((env[n] for n in ins if isinstance(env.get(n), fusion.Lazy) and env[n].per_row and env[n].shape == shape), None)
+            prob, per_row = (per_row_src.prob, True) if per_row_src is not None else (fusion.problem(shape), False)
+            if name in ("linalg.elemwise_unary", "hfusion.elemwise_unary"):
+                fun = op.attr("fun") or "exp"
+                if fun not in fusion.UNARY or (name.startswith("linalg") and fun not in _LINALG_UNARY):
+                    return False
+                a = node_of(ins[0], shape, prob, per_row, touched)
+                return a is not None and defer(op, ("un", fun, a), shape, prob, per_row, touched)
+            if name in ("linalg.elemwise_binary", "hfusion.elemwise_binary"):
+                fun = op.attr("fun") or "add"
+                if fun not in fusion.BINARY or len(ins) < 2:
+                    return False
+                a, b = node_of(ins[0], shape, prob, per_row, touched), node_of(ins[1], shape, prob, per_row, touched)
+                return a is not None and b is not None and defer(op, ("bin", fun, a, b), shape, prob, per_row, touched)
+            if name == "linalg.fill" and isinstance(env.get(ins[0]), Scalar):
+                return defer(op, ("imm", float(env[ins[0]].value)), shape, prob, False, touched)
+            if name == "linalg.broadcast" and dst.dim() == 2:
+                dims = op.int_list("dimensions") or []
+                src = env.get(ins[0])
+                if dims == [1] and isinstance(src, fusion.Lazy) and src.per_row and src.prob == tuple(shape):
+                    touched.append(ins[0])
+                    return defer(op, src.node, shape, tuple(shape), False, touched)   # already uniform along the row
+                vec = src.node[1].reshape(-1) if isinstance(src, fusion.Lazy) and src.node[0] == "leaf" and src.node[2] == "full" \
+                    and len(src.shape) == 1 else src if isinstance(src, torch.Tensor) and src.dim() == 1 and src.is_contiguous() \
+                    and src.dtype == torch.float32 else None
+                if vec is not None and dims in ([0], [1]) and vec.shape[0] == shape[1 - dims[0]]:
+                    return defer(op, ("leaf", vec, "row_vector" if dims == [0] else "col_vector"), shape, tuple(shape), False, touched)
+                return False
+            if name == "linalg.reduce" and dst.dim() == 1 and op.int_list("dimensions") == [1]:
+                comb = next((c for c in _REDUCE_COMBINERS if re.search(rf"\b{re.escape(c)}\b", op.text)), None)
+                kind = _REDUCE_COMBINERS.get(comb)
+                src = env.get(ins[0])
+                if kind not in fusion.REDUCE or not isinstance(src, fusion.Lazy) or src.per_row or len(src.shape) != 2 or \
+                        src.shape[0] != shape[0]:
+                    return False                               # a reduction of a tensor in memory stays a plain reduce
+                touched.append(ins[0])
+                return defer(op, ("red", kind, src.node), shape, src.prob, True, touched)
+            return False
 
         def operand(name):
             v = val(name)
@@ -275,15 +387,18 @@ class Function:
 
         for op in self.ops:
             name = op.name
-            pending.clear()
             ins, in_types = op.group("ins")
             outs, out_types = op.group("outs")
+            if self.fuse and try_fuse(op, name, ins, outs):
+                continue
             if name == "return" or name == "func.return":
                 names = [n.strip() for n in _split_top(op.text.split(":")[0])] if op.text.strip() else []
+                for k in list(env):                            # results, and deferred values whose destination is an argument
+                    if isinstance(env[k], fusion.Lazy) and (k in names or (k not in consumed and env[k].dst is not None and
+                                                                            env[k].dst.data_ptr() in arg_ptrs)):
+                        env[k] = request(env[k])
+                flush()                                        # everything that is still waiting, together
                 res = tuple(operand(n) for n in names)
-                for k in list(env):                            # a deferred value whose destination is an argument is still written
-                    if isinstance(env[k], fusion.Lazy) and env[k].dst is not None and env[k].dst.data_ptr() in arg_ptrs:
-                        val(k)
                 return res[0] if len(res) == 1 else (res if res else None)
             if name == "arith.constant":
                 m = re.match(r"\s*dense<([^>]+)>\s*:\s*(.+)$", op.text, re.S)
@@ -293,7 +408,7 @@ class Function:
                 else:
                     v, ty = op.text.rsplit(":", 1)
                     v = v.strip()
-                    define(op, [Scalar({"true": 1, "false": 0}.get(v, v) if ty.strip() in ("i1",) else float(v) if ty.strip().startswith("f") else int(float(v)), ty.strip())])
+                    define(op, [Scalar({"true": 1, "false": 0}.get(v, v) if ty.strip() in ("i1",) else _float_literal(v, ty.strip()) if ty.strip().startswith("f") else int(float(v)), ty.strip())])
             elif name in ("arith.addf", "arith.subf", "arith.mulf", "arith.divf", "arith.addi", "arith.subi", "arith.muli"):
                 a, b = [val(n.strip()) for n in _split_top(op.text.split(":")[0])]
                 ty = op.text.rsplit(":", 1)[1].strip()
@@ -332,37 +447,6 @@ class Function:
             elif name == "linalg.transpose":
                 perm = op.int_list("permutation")
                 define(op, [copy(val(ins[0]).permute(perm), out=val(outs[0]))])
-            elif name in ("linalg.elemwise_unary", "hfusion.elemwise_unary") and fusible(env.get(outs[0])) and \
-                    (op.attr("fun") or "exp") in fusion.UNARY and \
-                    (name.startswith("hfusion") or (op.attr("fun") or "exp") in _LINALG_UNARY) and \
-                    node_of(ins[0], env[outs[0]].shape) is not None and \
-                    defer(op, ("un", op.attr("fun") or "exp", node_of(ins[0], env[outs[0]].shape)), env[outs[0]]):
-                pass
-            elif name in ("linalg.elemwise_binary", "hfusion.elemwise_binary") and fusible(env.get(outs[0])) and \
-                    (op.attr("fun") or "add") in fusion.BINARY and \
-                    all(node_of(n, env[outs[0]].shape) is not None for n in ins[:2]) and \
-                    defer(op, ("bin", op.attr("fun") or "add", node_of(ins[0], env[outs[0]].shape),
-                               node_of(ins[1], env[outs[0]].shape)), env[outs[0]]):
-                pass
-            elif name == "linalg.fill" and fusible(env.get(outs[0])) and isinstance(env.get(ins[0]), Scalar) and \
-                    defer(op, ("imm", float(env[ins[0]].value)), env[outs[0]]):
-                pass
-            elif name == "linalg.broadcast" and fusible(env.get(outs[0])) and env[outs[0]].dim() == 2 and \
-                    vector_leaf(ins[0]) is not None and (op.int_list("dimensions") or []) in ([0], [1]) and \
-                    vector_leaf(ins[0]).shape[0] == env[outs[0]].shape[1 - op.int_list("dimensions")[0]] and \
-                    defer(op, ("leaf", vector_leaf(ins[0]), "row_vector" if op.int_list("dimensions") == [0] else "col_vector"), env[outs[0]]):
-                pass
-            elif name == "hfusion.cast" and self.fuse and isinstance(env.get(ins[0]), torch.Tensor) and \
-                    env[ins[0]].dtype in (torch.float16, torch.bfloat16) and fusible(env.get(outs[0])) and \
-                    list(env[ins[0]].shape) == list(env[outs[0]].shape) and env[ins[0]].is_contiguous() and \
-                    defer(op, ("leaf", env[ins[0]].view(*fusion.problem(list(env[ins[0]].shape))), "full"), env[outs[0]]):
-                pass                                           # a widening cast is exact: the chain reads the 16-bit storage
-            elif name == "hfusion.cast" and isinstance(env.get(ins[0]), fusion.Lazy) and isinstance(env.get(outs[0]), torch.Tensor) and \
-                    env[outs[0]].dtype in (torch.float16, torch.bfloat16) and env[outs[0]].is_contiguous() and \
-                    (op.attr("round_mode") or op.attr("mode") or "rint") == "rint" and not op.attr("enable_saturate", False) and \
-                    op.attr("overflow_mode") is None and list(env[outs[0]].shape) == env[ins[0]].shape:
-                define(op, [fusion.materialise(env[ins[0]], out=env[outs[0]])])   # the chain's single rounding
-                env[ins[0]] = None
             elif name == "hfusion.cast" or name == "hivm.hir.vcast":
                 dst = val(outs[0])
                 mode = op.attr("round_mode") or op.attr("mode") or "rint"
