@@ -266,6 +266,14 @@ def copy(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     return out
 
 
+def transpose(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hivm.hir.vtranspose`` / ``linalg.transpose`` of the last two axes of a 2-D or 3-D tensor (a copy whose source
+    is the transposed view: the library runs it with its tiled transposition kernel)."""
+    if x.dim() not in (2, 3):
+        raise BsirError(-2, "transpose: a 2-D or 3-D tensor")
+    return copy(x.transpose(-1, -2), out=out)
+
+
 PAD_MODE = {"null": 0, "first_elem": 1, "value": 2}
 ATOMIC_KIND = {"none": 0, "add": 1, "max": 2, "min": 3, "and": 4, "or": 5, "xor": 6, "cas": 7, "xchg": 8, "umax": 9,
                "umin": 10}

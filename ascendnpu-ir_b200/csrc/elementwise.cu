@@ -718,6 +718,10 @@ bool check_align(const void *p, int dt) { return p == nullptr || aligned_to(p, s
 }  // namespace
 }  // namespace bsir
 
+namespace bsir {
+bool launch_transpose(int elem_bytes, const void *src, void *dst, int64_t batch, int64_t rows, int64_t cols, int64_t src_row,
+                      int64_t dst_row, int64_t src_batch, int64_t dst_batch, cudaStream_t st);
+}
 using namespace bsir;
 
 extern "C" {
@@ -806,6 +810,18 @@ int32_t bsir_copy(int32_t dtype, int32_t rank, const int64_t *sizes, const void 
   bsir_operand s{src, {0, 0, 0}, 0};
   int64_t cs = 1;
   for (int i = rank - 1; i >= 0; --i) { s.strides[i] = src_strides ? src_strides[i] : cs; cs *= sizes[i]; }
+  if (rank >= 2) {
+    // A source that is a transposed view of the last two axes (hivm.hir.vtranspose / linalg.transpose arrive
+    // like this): the tiled kernel instead of an element-wise strided copy.
+    const int64_t ni = sizes[rank - 2], nj = sizes[rank - 1], nb = rank == 3 ? sizes[0] : 1;
+    const int64_t dj = p.os[2], di = p.os[1], db = rank == 3 ? p.os[0] : 0;
+    const int64_t si = s.strides[rank - 2], sj = s.strides[rank - 1], sb = rank == 3 ? s.strides[0] : 0;
+    if (ni > 1 && nj > 1 && dj == 1 && si == 1 && sj >= ni && di >= nj &&
+        launch_transpose(dtype_bytes(dtype), src, dst, nb, /*rows=*/nj, /*cols=*/ni, sj, di, sb, db, resolve_stream(stream))) {
+      count_launch();
+      return check_launch("copy");
+    }
+  }
   bool ac;
   Operand oa = make_operand(&s, rank, sizes, &ac), none{nullptr, 0, 0, 0, 0};
   const int dt = dtype_bytes(dtype) == 8 ? BSIR_U64 : dtype_bytes(dtype) == 4 ? BSIR_U32 : dtype_bytes(dtype) == 2 ? BSIR_U16 : BSIR_U8;

@@ -278,3 +278,28 @@ def test_store_atomic_adds_up_over_calls(bsir):
     for p in parts:
         bsir.store(p, acc, atomic="add")
     assert torch.equal(acc, sum(parts))
+
+
+# ---------------------------------------------------------------- transposition (a copy from a transposed view)
+@pytest.mark.parametrize("dtype", [torch.int8, torch.bfloat16, torch.float32, torch.int64])
+@pytest.mark.parametrize("shape", [(64, 128), (256, 512), (1000, 72), (65, 33), (3, 200, 136), (2, 64, 64), (1, 7), (513, 1024)])
+def test_transpose_of_the_last_two_axes(bsir, dtype, shape):
+    """Bit-exact against the permutation itself: full tiles, ragged edges, batches, every element size."""
+    g = torch.Generator(device="cuda").manual_seed(sum(shape))
+    x = torch.randint(-2 ** 15, 2 ** 15, shape, device="cuda", generator=g).to(dtype) if not dtype.is_floating_point \
+        else torch.randn(shape, device="cuda", generator=g).to(dtype)
+    y = bsir.transpose(x)
+    assert y.shape == x.transpose(-1, -2).shape and y.is_contiguous()
+    assert torch.equal(y, x.transpose(-1, -2))
+
+
+def test_transpose_with_row_strides_and_unaligned_views(bsir):
+    big = torch.randn(300, 700, device="cuda").to(torch.float16)
+    x = big[4:260, 8:520]                                       # 256 x 512, row stride 700 (16-byte aligned rows)
+    out_big = torch.zeros(600, 400, device="cuda", dtype=torch.float16)
+    out = out_big[:512, 16:272]
+    bsir.transpose(x, out=out)
+    assert torch.equal(out, x.t())
+    assert out_big[:, :16].abs().sum().item() == 0 and out_big[:, 272:].abs().sum().item() == 0 and out_big[512:].abs().sum().item() == 0
+    odd = big[1:258, 3:200]                                     # unaligned start, odd sizes: the element path
+    assert torch.equal(bsir.transpose(odd), odd.t())
