@@ -495,6 +495,20 @@ def reduce(kind: str, x: torch.Tensor, dim: int = 1) -> torch.Tensor:
     return out
 
 
+CUM_KIND = {"sum": 0, "prod": 1, "max": 2, "min": 3}
+
+
+def cumulative(kind: str, x: torch.Tensor, dim: int = 1, reverse: bool = False, propagate_nan: bool = True,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hivm.hir.vcumsum`` / ``vcumprod`` / ``vcummax`` / ``vcummin`` {cum_dims = [dim], reverse} of a 2-D tensor."""
+    rows, cols, rs = _rows(x)
+    out = torch.empty((rows, cols), dtype=x.dtype, device=x.device) if out is None else out
+    _check(lib().bsir_cumulative(CUM_KIND[kind], _dt(x), int(dim % 2), int(bool(reverse)), int(bool(propagate_nan)),
+                                 C.c_int64(rows), C.c_int64(cols), _ptr(x), C.c_int64(rs), _ptr(out),
+                                 C.c_int64(out.stride(0) if rows > 1 else max(cols, 1)), _stream()))
+    return out
+
+
 def reduce_with_index(kind: str, x: torch.Tensor, tie_break_left: bool = True, nan_mode: str = "region",
                       workspace: Optional[torch.Tensor] = None):
     """``hfusion.reduce_with_index <max|min> {tie_break_left}`` over the last axis -> (values, int32 indices)."""

@@ -13,7 +13,8 @@ Covered (attribute spellings as in the reference):
   linalg.fill, linalg.broadcast dimensions = [..], linalg.reduce {arith.<combiner>} dimensions = [k] (short form and a
   region with one combiner op), linalg.matmul (i8 x i8 -> i32), linalg.copy
   hivm.hir.load (pad_mode / pad_value / left_padding_num / right_padding_num), hivm.hir.store (atomic = <kind>),
-  hivm.hir.copy, hivm.hir.vadd / vsub / vmul / vdiv / vmax / vmin, hivm.hir.vcast, hivm.hir.vreduce <kind>
+  hivm.hir.copy, hivm.hir.vadd / vsub / vmul / vdiv / vmax / vmin, hivm.hir.vcast, hivm.hir.vreduce <kind>,
+  hivm.hir.vcumsum / vcumprod / vcummax / vcummin (and hfusion.cumsum ...) cum_dims = [k] reverse = <bool>
   tensor.empty, tensor.dim, tensor.collapse_shape / expand_shape / reshape, tensor.extract_slice (static), linalg.transpose, memref.alloc, arith.constant (scalars, splat `dense<..>`), arith.{addf,subf,mulf,divf,addi,subi,muli},
   arith.{index_cast,index_castui,uitofp,sitofp,extf,truncf}, return
 Scalar arithmetic is done in the scalar's own type (f32 ops round to f32).  Anything else raises MlirTextError
@@ -207,8 +208,8 @@ class Function:
     # ------------------------------------------------------------------ execution
     def __call__(self, *tensors):
         import torch
-        from . import (cast, compare, copy, elemwise_binary, elemwise_unary, load, matmul_w8a8, reduce, reduce_with_index,
-                       select, store)
+        from . import (cast, compare, copy, cumulative, elemwise_binary, elemwise_unary, load, matmul_w8a8, reduce,
+                       reduce_with_index, select, store)
         if len(tensors) != len(self.args):
             raise MlirTextError(f"@{self.name} takes {len(self.args)} arguments, got {len(tensors)}")
         env: Dict[str, object] = {}
@@ -513,6 +514,21 @@ class Function:
                 if src.dim() != 2 or dims not in ([0], [1]):
                     raise MlirTextError(f"{name}: a 2-D source reduced over one axis is supported, got rank {src.dim()} dims {dims}")
                 define(op, [write_out(dst.view(-1) if dst.dim() != 1 else dst, reduce(kind, src, dim=dims[0])).view(dst.shape)])
+            elif name in ("hivm.hir.vcumsum", "hivm.hir.vcumprod", "hivm.hir.vcummax", "hivm.hir.vcummin",
+                          "hfusion.cumsum", "hfusion.cumprod", "hfusion.cummax", "hfusion.cummin"):
+                # `hivm.hir.vcumsum ins(%s : T) outs(%d : T) cum_dims = [k] reverse = false`, or the value form
+                # `hfusion.cumsum %s : T cum_dims = [k] reverse = false -> T`
+                src = val(ins[0]) if ins else val(re.match(r"\s*(%[\w.]+)", op.text).group(1))
+                dims = op.int_list("cum_dims")
+                if src.dim() not in (1, 2) or dims is None or len(dims) != 1 or dims[0] >= src.dim():
+                    raise MlirTextError(f"{name}: one cumulative axis of a 1-D or 2-D operand is supported")
+                two_d = src if src.dim() == 2 else src.view(1, -1)
+                axis = dims[0] if src.dim() == 2 else 1
+                dst = val(outs[0]) if outs else torch.empty_like(src)
+                pn = op.attr("propagate_nan", True)
+                y = cumulative(name.rsplit("cum", 1)[1], two_d, dim=axis, reverse=bool(op.attr("reverse", False)),
+                               propagate_nan=bool(pn), out=dst if dst.dim() == 2 else dst.view(1, -1))
+                define(op, [y.view(src.shape)])
             elif name == "hfusion.reduce_with_index":
                 kind = re.search(r"<(max|min)>", op.text).group(1)
                 v, i = reduce_with_index(kind, val(ins[0]), tie_break_left=bool(op.attr("tie_break_left", True)))

@@ -365,6 +365,17 @@ BSIR_API int32_t bsir_fused_elementwise_compile(int32_t n_in, const bsir_chain_o
                                                 const bsir_chain_instr *tape, int32_t n_out, const bsir_chain_output *outs,
                                                 int32_t flags, int64_t *cubin_bytes);
 
+/* hivm.hir.vcumsum / vcumprod / vcummax / vcummin (HIVMVectorOps.td:1937-2220) over axis 0 or 1 of a [rows, cols]
+ * problem: dst[0] = src[0], dst[i] = src[i] (op) dst[i-1] in index order (hivm-lower-to-loops-op.mlir:1558-1599),
+ * from the last index backwards with reverse.  f16 / bf16 run in f32 and round once per output; integers wrap
+ * in their own width.  propagate_nan (cummax / cummin on floats): NaN poisons what follows (maximumf), else a NaN
+ * operand is ignored (maxnumf).  dtype: f32, f16, bf16, i8, i16, i32, i64.  The scan is sequential along its axis
+ * (float sums do not associate), so it is fast when the other axis is long. */
+typedef enum { BSIR_CUM_SUM = 0, BSIR_CUM_PROD = 1, BSIR_CUM_MAX = 2, BSIR_CUM_MIN = 3 } bsir_cum_kind;
+BSIR_API int32_t bsir_cumulative(int32_t kind, int32_t dtype, int32_t axis, int32_t reverse, int32_t propagate_nan,
+                                 int64_t rows, int64_t cols, const void *src, int64_t src_row_stride, void *dst,
+                                 int64_t dst_row_stride, void *stream);
+
 /* Fused softmax over the last axis
  * (test/Dialect/Analysis/VFFusion/MaxParallelKind/softmax_small_shape.mlir:86-117). */
 BSIR_API int32_t bsir_softmax(int32_t dtype, int64_t rows, int64_t cols, const void *x,

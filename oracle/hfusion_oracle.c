@@ -693,6 +693,53 @@ ORC_API int orc_reduce_last_axis(int kind, int dt, const void *src, int64_t rows
   return 0;
 }
 
+/* hivm.hir.vcumsum / vcumprod / vcummax / vcummin along axis 0 or 1 of [rows, cols]
+ * (HIVMVectorOps.td:1937-2220): dst[0] = src[0]; dst[i] = src[i] (op) dst[i-1], i ascending
+ * (descending from the last index with reverse) -- the loop nest of
+ * test/Dialect/HIVM/hivm-lower-to-loops-op.mlir:1558-1599.  f16/bf16: the running value is f32 and
+ * every output is one rounding of it (the f16->f32 normalisation of cumulative ops,
+ * lib/Dialect/HIVM/Transforms/regbase/Normalize/NormalizeTypeConversion.cpp:714-745,818-822).
+ * kind 0 sum 1 prod 2 max 3 min; propagate_nan picks maximumf/minimumf over maxnumf/minnumf. */
+ORC_API int orc_cumulative(int kind, int dt, int axis, int reverse, int propagate_nan, const void *src,
+                           int64_t rows, int64_t cols, int64_t src_stride, void *dst, int64_t dst_stride) {
+  if (kind < 0 || kind > 3 || (axis != 0 && axis != 1)) return -1;
+  int64_t lines = axis == 1 ? rows : cols, n = axis == 1 ? cols : rows;
+  for (int64_t l = 0; l < lines; l++) {
+    float facc = 0.0f;
+    int64_t iacc = 0;
+    for (int64_t e = 0; e < n; e++) {
+      int64_t j = reverse ? n - 1 - e : e;
+      int64_t si = axis == 1 ? l * src_stride + j : j * src_stride + l;
+      int64_t di = axis == 1 ? l * dst_stride + j : j * dst_stride + l;
+      if (is_float(dt)) {
+        float x = load_f(dt, src, si);
+        if (e == 0) facc = x;
+        else switch (kind) {
+          case 0: facc = x + facc; break;
+          case 1: facc = x * facc; break;
+          case 2: facc = propagate_nan ? maximumf_(x, facc) : maxnumf_(x, facc); break;
+          default: facc = propagate_nan ? minimumf_(x, facc) : minnumf_(x, facc); break;
+        }
+        store_f(dt, dst, di, facc);
+      } else {
+        int64_t x = load_i(dt, src, si), t = 0;
+        if (e == 0) iacc = x;
+        else {
+          switch (kind) {
+            case 0: binary_int(100, dt, x, iacc, &t); break;
+            case 1: binary_int(102, dt, x, iacc, &t); break;
+            case 2: t = x > iacc ? x : iacc; break;
+            default: t = x < iacc ? x : iacc; break;
+          }
+          iacc = wrap_int(dt, t);
+        }
+        store_i(dt, dst, di, iacc);
+      }
+    }
+  }
+  return 0;
+}
+
 /* Same over the first axis: dst[c] = reduce_r src[r, c], r ascending. */
 ORC_API int orc_reduce_first_axis(int kind, int dt, const void *src, int64_t rows, int64_t cols,
                                   int64_t row_stride, void *dst) {

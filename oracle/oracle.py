@@ -214,6 +214,17 @@ def reduce_first_axis(kind, dt, src):
     return out
 
 
+def cumulative(kind, dt, src, axis=1, reverse=False, propagate_nan=True):
+    """kind: 'sum' | 'prod' | 'max' | 'min' along axis 0 or 1 of a 2-D array."""
+    k = {"sum": 0, "prod": 1, "max": 2, "min": 3}[kind]
+    src = _c(src, dt)
+    rows, cols = src.shape
+    out = np.empty_like(src)
+    _chk(lib().orc_cumulative(k, dt, int(axis), int(bool(reverse)), int(bool(propagate_nan)), _p(src), _i64(rows), _i64(cols),
+                              _i64(cols), _p(out), _i64(cols)), "cumulative")
+    return out
+
+
 def reduce_with_index(kind, dt, src, tie_break_left=True, nan_mode="region"):
     """kind: 'max' | 'min'.  Returns (values, int32 indices)."""
     k = {"min": 0, "max": 1}[kind]

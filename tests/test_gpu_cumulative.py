@@ -1,0 +1,66 @@
+"""GPU parity: hivm.hir.vcumsum / vcumprod / vcummax / vcummin through the C ABI against the oracle, bit for bit
+(the scan is sequential along its axis on both sides, so float sums agree exactly too)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle as O
+from conftest import assert_bits_equal, oracle_dtype, to_bits
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def bsir():
+    import bsir as B
+    B.lib()
+    return B
+
+
+def _data(shape, dtype, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    if dtype.is_floating_point:
+        return (torch.randn(shape, device="cuda", generator=g) * 0.5 + 0.05).to(dtype)
+    hi = {torch.int8: 5, torch.int16: 300, torch.int32: 2 ** 20, torch.int64: 2 ** 40}[dtype]
+    return torch.randint(-hi, hi, shape, device="cuda", generator=g, dtype=torch.int64).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.int8, torch.int16, torch.int32, torch.int64])
+@pytest.mark.parametrize("kind", ["sum", "prod", "max", "min"])
+@pytest.mark.parametrize("rows,cols", [(64, 16), (70, 256), (33, 1000), (5, 17), (1, 640), (300, 1)])
+def test_cumulative_ops_both_axes(bsir, dtype, kind, rows, cols):
+    x = _data((rows, cols), dtype, rows * 7 + cols)
+    if kind == "prod" and dtype.is_floating_point:
+        x = (1 + 0.01 * x.float()).to(dtype)                     # keeps the products finite
+    dt = oracle_dtype(x)
+    for axis in (0, 1):
+        for reverse in (False, True):
+            y = bsir.cumulative(kind, x, dim=axis, reverse=reverse)
+            assert_bits_equal(y, O.cumulative(kind, dt, to_bits(x), axis=axis, reverse=reverse),
+                              f"cum{kind} {dtype} [{rows},{cols}] axis {axis} reverse {reverse}")
+
+
+def test_cumulative_nan_modes_and_strided_rows(bsir):
+    x = torch.randn(40, 128, device="cuda")
+    x[3, 5] = float("nan")
+    for nanp in (True, False):
+        y = bsir.cumulative("max", x, propagate_nan=nanp)
+        w = O.cumulative("max", O.F32, to_bits(x), propagate_nan=nanp)
+        assert np.array_equal(to_bits(y), w, equal_nan=True)
+        assert bool(torch.isnan(y[3, 5:]).all()) == nanp
+    big = torch.randn(50, 400, device="cuda").to(torch.bfloat16)
+    view = big[:, 8:264]                                         # 256 columns, row stride 400: the tiled path
+    out_big = torch.zeros(50, 300, device="cuda", dtype=torch.bfloat16)
+    bsir.cumulative("sum", view, out=out_big[:, :256])
+    assert_bits_equal(out_big[:, :256].contiguous(), O.cumulative("sum", O.BF16, to_bits(view.contiguous())), "strided cumsum")
+    assert out_big[:, 256:].abs().sum().item() == 0
+
+
+def test_cumulative_config_shape_and_validation(bsir):
+    """A decode-time top-p shape: many rows, sorted probabilities along the row."""
+    p = torch.softmax(torch.randn(2048, 4096, device="cuda"), dim=1).sort(dim=1, descending=True).values.contiguous()
+    c = bsir.cumulative("sum", p)
+    assert_bits_equal(c[:64].contiguous(), O.cumulative("sum", O.F32, to_bits(p[:64].contiguous())), "top-p cumsum")
+    assert (c[:, -1] - 1).abs().max().item() < 1e-4
+    with pytest.raises(bsir.BsirError):
+        bsir.cumulative("sum", torch.zeros(4, 4, device="cuda", dtype=torch.bool))

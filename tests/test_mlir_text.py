@@ -209,7 +209,7 @@ def test_reduce_with_index_compare_select_program(bsir):
 def test_unsupported_op_fails_loudly(bsir):
     import torch
     from bsir import mlir_text
-    fn = mlir_text.parse("func.func @f(%x: tensor<4xf32>) -> tensor<4xf32> {\n  %y = hfusion.cumsum %x : tensor<4xf32>\n  return %y : tensor<4xf32>\n}")["f"]
+    fn = mlir_text.parse("func.func @f(%x: tensor<4xf32>) -> tensor<4xf32> {\n  %y = hfusion.sort %x : tensor<4xf32>\n  return %y : tensor<4xf32>\n}")["f"]
     with pytest.raises(mlir_text.MlirTextError):
         fn(torch.zeros(4, device="cuda"))
 
@@ -373,3 +373,29 @@ def test_softmax_program_with_two_reductions_runs_as_one_kernel(bsir):
     fn.fuse = False
     w = fn(x, torch.empty_like(x))
     assert (y - w).abs().max().item() < 1e-6
+
+
+CUM_IR = """
+func.func @vcumsum(%arg0: tensor<64x16xf32>) -> tensor<64x16xf32> {
+  %0 = tensor.empty() : tensor<64x16xf32>
+  %1 = hivm.hir.vcumsum ins(%arg0 : tensor<64x16xf32>) outs(%0 : tensor<64x16xf32>) cum_dims = [0] reverse = false -> tensor<64x16xf32>
+  return %1 : tensor<64x16xf32>
+}
+func.func @rev(%arg0: tensor<100xi32>) -> tensor<100xi32> {
+  %1 = hfusion.cumsum %arg0 : tensor<100xi32> cum_dims = [0] reverse = true -> tensor<100xi32>
+  return %1 : tensor<100xi32>
+}
+"""
+
+
+@pytest.mark.gpu
+def test_cumulative_ops_in_both_spellings(bsir):
+    """The vcumsum function of test/ExecutionEngine/convert-hivm-to-upstream.mlir:417-423, and the value form."""
+    import torch
+    from bsir import mlir_text
+    from conftest import to_bits
+    fns = mlir_text.parse(CUM_IR)
+    x = torch.randn(64, 16, device="cuda")
+    assert np.array_equal(to_bits(fns["vcumsum"](x)), O.cumulative("sum", O.F32, to_bits(x), axis=0))
+    v = torch.arange(100, device="cuda", dtype=torch.int32)
+    assert torch.equal(fns["rev"](v), torch.flip(torch.cumsum(torch.flip(v, [0]), 0), [0]).to(torch.int32))
