@@ -495,6 +495,26 @@ def reduce(kind: str, x: torch.Tensor, dim: int = 1) -> torch.Tensor:
     return out
 
 
+def gather(x: torch.Tensor, index: torch.Tensor, dim: int = -1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hivm.hir.vgather`` {gather_axis = dim}: out[.., j, ..] = x[.., index[.., j, ..], ..] (torch.gather's rule;
+    index and out have x's shape but for the gather axis).  index: int16 / int32 / int64."""
+    dim = dim % x.dim()
+    x, index = x.contiguous(), index.contiguous()
+    if index.dim() != x.dim() or any(index.shape[d] != x.shape[d] for d in range(x.dim()) if d != dim):
+        raise BsirError(-2, f"gather: index {tuple(index.shape)} does not match {tuple(x.shape)} outside axis {dim}")
+    out = torch.empty(index.shape, dtype=x.dtype, device=x.device) if out is None else out
+    if not out.is_contiguous() or out.shape != index.shape or out.dtype != x.dtype:
+        raise BsirError(-3, "gather: out must be a contiguous tensor of the index's shape and the source's type")
+    outer = inner = 1
+    for d in range(dim):
+        outer *= x.shape[d]
+    for d in range(dim + 1, x.dim()):
+        inner *= x.shape[d]
+    _check(lib().bsir_gather(_dt(x), _dt(index), C.c_int64(outer), C.c_int64(x.shape[dim]), C.c_int64(index.shape[dim]),
+                             C.c_int64(inner), _ptr(x), _ptr(index), _ptr(out), _stream()))
+    return out
+
+
 CUM_KIND = {"sum": 0, "prod": 1, "max": 2, "min": 3}
 
 

@@ -14,7 +14,8 @@ Covered (attribute spellings as in the reference):
   region with one combiner op), linalg.matmul (i8 x i8 -> i32), linalg.copy
   hivm.hir.load (pad_mode / pad_value / left_padding_num / right_padding_num), hivm.hir.store (atomic = <kind>),
   hivm.hir.copy, hivm.hir.vadd / vsub / vmul / vdiv / vmax / vmin, hivm.hir.vcast, hivm.hir.vreduce <kind>,
-  hivm.hir.vcumsum / vcumprod / vcummax / vcummin (and hfusion.cumsum ...) cum_dims = [k] reverse = <bool>
+  hivm.hir.vcumsum / vcumprod / vcummax / vcummin (and hfusion.cumsum ...) cum_dims = [k] reverse = <bool>,
+  hivm.hir.vgather ins(..) indices(..) outs(..) gather_axis = k
   tensor.empty, tensor.dim, tensor.collapse_shape / expand_shape / reshape, tensor.extract_slice (static), linalg.transpose, memref.alloc, arith.constant (scalars, splat `dense<..>`), arith.{addf,subf,mulf,divf,addi,subi,muli},
   arith.{index_cast,index_castui,uitofp,sitofp,extf,truncf}, return
 Scalar arithmetic is done in the scalar's own type (f32 ops round to f32).  Anything else raises MlirTextError
@@ -208,7 +209,7 @@ class Function:
     # ------------------------------------------------------------------ execution
     def __call__(self, *tensors):
         import torch
-        from . import (cast, compare, copy, cumulative, elemwise_binary, elemwise_unary, load, matmul_w8a8, reduce,
+        from . import (cast, compare, copy, cumulative, elemwise_binary, elemwise_unary, gather, load, matmul_w8a8, reduce,
                        reduce_with_index, select, store)
         if len(tensors) != len(self.args):
             raise MlirTextError(f"@{self.name} takes {len(self.args)} arguments, got {len(tensors)}")
@@ -529,6 +530,14 @@ class Function:
                 y = cumulative(name.rsplit("cum", 1)[1], two_d, dim=axis, reverse=bool(op.attr("reverse", False)),
                                propagate_nan=bool(pn), out=dst if dst.dim() == 2 else dst.view(1, -1))
                 define(op, [y.view(src.shape)])
+            elif name == "hivm.hir.vgather":
+                # `hivm.hir.vgather ins(%s : T) indices(%i : Ti) outs(%d : T) [gather_axis = k]` (-1 / absent: the last axis)
+                idx_names, _ = op.group("indices")
+                if not idx_names:
+                    raise MlirTextError("hivm.hir.vgather: indices(...) expected")
+                src = val(ins[0])
+                m = re.search(r"gather_axis\s*=\s*(-?\d+)", op.text)
+                define(op, [gather(src, val(idx_names[0]), dim=int(m.group(1)) if m else -1, out=val(outs[0]))])
             elif name == "hfusion.reduce_with_index":
                 kind = re.search(r"<(max|min)>", op.text).group(1)
                 v, i = reduce_with_index(kind, val(ins[0]), tie_break_left=bool(op.attr("tie_break_left", True)))

@@ -1,0 +1,71 @@
+// gather.cu -- hivm.hir.vgather (bishengir/include/bishengir/Dialect/HIVM/IR/HIVMVectorOps.td:1834-1883):
+// dst[o][j][k] = src[o][indices[o][j][k]][k] along one axis of contiguous [outer, axis, inner] tensors
+// (source, indices and destination have the same rank; the gather axis of the source may have another length,
+// test/Dialect/HIVM/hivm-flatten-ops.mlir:1036-1045).  A thread per output element: the index and destination
+// streams are coalesced, the source reads go where the indices send them.  An index outside the source axis
+// leaves its element untouched and raises BSIR_DEVERR_GATHER_INDEX in the device error word.
+#include <cstdint>
+
+#include "common.cuh"
+
+namespace bsir {
+namespace {
+
+template <typename T, typename I>
+__global__ void __launch_bounds__(256) gather_kernel(const T *__restrict__ src, const I *__restrict__ idx, T *__restrict__ dst,
+                                                     int64_t total, int64_t src_axis, int64_t dst_axis, int64_t inner, int *err) {
+  const int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (e >= total) return;
+  const int64_t k = inner == 1 ? 0 : e % inner;
+  const int64_t o = e / (dst_axis * inner);
+  const int64_t i = static_cast<int64_t>(idx[e]);
+  if (i < 0 || i >= src_axis) {
+    atomicOr(err, BSIR_DEVERR_GATHER_INDEX);
+    return;
+  }
+  dst[e] = src[(o * src_axis + i) * inner + k];
+}
+
+template <typename T>
+void launch_gather(int index_dtype, const void *src, const void *idx, void *dst, int64_t total, int64_t src_axis, int64_t dst_axis,
+                   int64_t inner, int *err, cudaStream_t st) {
+  const unsigned blocks = static_cast<unsigned>(ceil_div(total, 256));
+  const T *s = static_cast<const T *>(src);
+  T *d = static_cast<T *>(dst);
+  if (index_dtype == BSIR_I16) gather_kernel<T, int16_t><<<blocks, 256, 0, st>>>(s, static_cast<const int16_t *>(idx), d, total, src_axis, dst_axis, inner, err);
+  else if (index_dtype == BSIR_I32) gather_kernel<T, int32_t><<<blocks, 256, 0, st>>>(s, static_cast<const int32_t *>(idx), d, total, src_axis, dst_axis, inner, err);
+  else gather_kernel<T, int64_t><<<blocks, 256, 0, st>>>(s, static_cast<const int64_t *>(idx), d, total, src_axis, dst_axis, inner, err);
+}
+
+}  // namespace
+}  // namespace bsir
+
+using namespace bsir;
+
+extern "C" int32_t bsir_gather(int32_t dtype, int32_t index_dtype, int64_t outer, int64_t src_axis, int64_t dst_axis, int64_t inner,
+                               const void *src, const void *indices, void *dst, void *stream) {
+  clear_error();
+  const int eb = dtype_bytes(dtype);
+  if (eb == 0) return fail(BSIR_ERR_DTYPE, "gather: dtype %d", dtype);
+  if (index_dtype != BSIR_I16 && index_dtype != BSIR_I32 && index_dtype != BSIR_I64)
+    return fail(BSIR_ERR_DTYPE, "gather: index dtype %d (i16, i32, i64)", index_dtype);
+  if (outer < 0 || src_axis < 0 || dst_axis < 0 || inner < 0)
+    return fail(BSIR_ERR_SHAPE, "gather: [%lld, %lld -> %lld, %lld]", (long long)outer, (long long)src_axis, (long long)dst_axis, (long long)inner);
+  const int64_t total = outer * dst_axis * inner;
+  if (total == 0) return BSIR_OK;
+  if (!src || !indices || !dst) return fail(BSIR_ERR_NULL, "gather: null pointer");
+  if (src_axis == 0) return fail(BSIR_ERR_SHAPE, "gather: the source axis is empty");
+  if (!aligned_to(src, eb) || !aligned_to(dst, eb) || !aligned_to(indices, dtype_bytes(index_dtype))) return fail(BSIR_ERR_ALIGN, "gather: misaligned");
+  if (ceil_div(total, 256) > 0x7fffffffLL) return fail(BSIR_ERR_SHAPE, "gather: %lld elements", (long long)total);
+  int *err = device_error_word();
+  if (!err) return fail(BSIR_ERR_WORKSPACE, "gather: no device error word");
+  cudaStream_t st = resolve_stream(stream);
+  switch (eb) {
+    case 1: launch_gather<uint8_t>(index_dtype, src, indices, dst, total, src_axis, dst_axis, inner, err, st); break;
+    case 2: launch_gather<uint16_t>(index_dtype, src, indices, dst, total, src_axis, dst_axis, inner, err, st); break;
+    case 4: launch_gather<uint32_t>(index_dtype, src, indices, dst, total, src_axis, dst_axis, inner, err, st); break;
+    default: launch_gather<uint64_t>(index_dtype, src, indices, dst, total, src_axis, dst_axis, inner, err, st); break;
+  }
+  count_launch();
+  return check_launch("gather");
+}

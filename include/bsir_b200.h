@@ -376,6 +376,14 @@ BSIR_API int32_t bsir_cumulative(int32_t kind, int32_t dtype, int32_t axis, int3
                                  int64_t rows, int64_t cols, const void *src, int64_t src_row_stride, void *dst,
                                  int64_t dst_row_stride, void *stream);
 
+/* hivm.hir.vgather (HIVMVectorOps.td:1834-1883) on contiguous [outer, axis, inner] tensors:
+ * dst[o][j][k] = src[o][indices[o][j][k]][k]; src is [outer, src_axis, inner], indices and dst are
+ * [outer, dst_axis, inner].  index_dtype: BSIR_I16 / I32 (the op's types) or I64.  An index outside
+ * [0, src_axis) leaves its element untouched and sets BSIR_DEVERR_GATHER_INDEX in the device error word
+ * (bsir_device_error). */
+BSIR_API int32_t bsir_gather(int32_t dtype, int32_t index_dtype, int64_t outer, int64_t src_axis, int64_t dst_axis,
+                             int64_t inner, const void *src, const void *indices, void *dst, void *stream);
+
 /* Fused softmax over the last axis
  * (test/Dialect/Analysis/VFFusion/MaxParallelKind/softmax_small_shape.mlir:86-117). */
 BSIR_API int32_t bsir_softmax(int32_t dtype, int64_t rows, int64_t cols, const void *x,
@@ -460,8 +468,10 @@ BSIR_API int32_t bsir_launch(const char *name, uint32_t block_dim, void **args, 
 /* ------------------------------------------------------------------------ */
 /* device bookkeeping                                                        */
 /* ------------------------------------------------------------------------ */
-/* Reads and clears the device-side error word of the current device (set when a
- * bounded wait inside a kernel gave up); synchronises the device.  0 = clean. */
+/* Reads and clears the device-side error word of the current device (bits set by kernels: a bounded wait
+ * that gave up, BSIR_DEVERR_GATHER_INDEX for a gather index outside its axis); synchronises the device.
+ * 0 = clean. */
+#define BSIR_DEVERR_GATHER_INDEX 0x100
 BSIR_API int32_t bsir_device_error(void);
 /* Number of kernel launches this library has enqueued in this process. */
 BSIR_API int64_t bsir_launch_count(void);

@@ -303,3 +303,30 @@ def test_transpose_with_row_strides_and_unaligned_views(bsir):
     assert out_big[:, :16].abs().sum().item() == 0 and out_big[:, 272:].abs().sum().item() == 0 and out_big[512:].abs().sum().item() == 0
     odd = big[1:258, 3:200]                                     # unaligned start, odd sizes: the element path
     assert torch.equal(bsir.transpose(odd), odd.t())
+
+
+# ---------------------------------------------------------------- gather along an axis
+@pytest.mark.parametrize("dtype", [torch.int8, torch.float16, torch.float32, torch.int64])
+@pytest.mark.parametrize("idx_dtype", [torch.int16, torch.int32, torch.int64])
+@pytest.mark.parametrize("shape,dim,n", [((100, 7, 4), 1, 6), ((512,), 0, 300), ((33, 1000), 1, 17), ((50, 9), 0, 64), ((2, 3, 5, 8), 2, 11)])
+def test_gather_along_an_axis(bsir, dtype, idx_dtype, shape, dim, n):
+    """hivm.hir.vgather: bit-exact against the indexing rule itself (the [100,7,4] -> [100,6,4] case is the one of
+    test/Dialect/HIVM/hivm-flatten-ops.mlir:1036-1045)."""
+    g = torch.Generator(device="cuda").manual_seed(n)
+    x = torch.randint(-100, 100, shape, device="cuda", generator=g).to(dtype)
+    ishape = list(shape)
+    ishape[dim] = n
+    idx = torch.randint(0, shape[dim], ishape, device="cuda", generator=g).to(idx_dtype)
+    y = bsir.gather(x, idx, dim=dim)
+    assert torch.equal(y, torch.gather(x, dim, idx.long()))
+    assert bsir.device_error() == 0
+
+
+def test_gather_reports_indices_outside_the_axis(bsir):
+    x = torch.arange(10, device="cuda", dtype=torch.float32)
+    idx = torch.tensor([0, 9, 10, -1, 3], device="cuda", dtype=torch.int32)
+    out = torch.full((5,), -7.0, device="cuda")
+    bsir.gather(x, idx, out=out)
+    assert bsir.device_error() == 0x100                          # BSIR_DEVERR_GATHER_INDEX
+    assert out.tolist() == [0.0, 9.0, -7.0, -7.0, 3.0]           # the bad ones are left untouched
+    assert bsir.device_error() == 0                              # reading clears it

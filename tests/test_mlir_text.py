@@ -381,6 +381,10 @@ func.func @vcumsum(%arg0: tensor<64x16xf32>) -> tensor<64x16xf32> {
   %1 = hivm.hir.vcumsum ins(%arg0 : tensor<64x16xf32>) outs(%0 : tensor<64x16xf32>) cum_dims = [0] reverse = false -> tensor<64x16xf32>
   return %1 : tensor<64x16xf32>
 }
+func.func @gather(%src: memref<100x7x4xf16>, %idx: memref<100x6x4xi32>, %dst: memref<100x6x4xf16>) {
+  hivm.hir.vgather ins(%src : memref<100x7x4xf16>) indices(%idx : memref<100x6x4xi32>) outs(%dst : memref<100x6x4xf16>) gather_axis = 1
+  return
+}
 func.func @rev(%arg0: tensor<100xi32>) -> tensor<100xi32> {
   %1 = hfusion.cumsum %arg0 : tensor<100xi32> cum_dims = [0] reverse = true -> tensor<100xi32>
   return %1 : tensor<100xi32>
@@ -399,3 +403,8 @@ def test_cumulative_ops_in_both_spellings(bsir):
     assert np.array_equal(to_bits(fns["vcumsum"](x)), O.cumulative("sum", O.F32, to_bits(x), axis=0))
     v = torch.arange(100, device="cuda", dtype=torch.int32)
     assert torch.equal(fns["rev"](v), torch.flip(torch.cumsum(torch.flip(v, [0]), 0), [0]).to(torch.int32))
+    src = torch.randn(100, 7, 4, device="cuda").to(torch.float16)
+    idx = torch.randint(0, 7, (100, 6, 4), device="cuda", dtype=torch.int32)
+    dst = torch.empty(100, 6, 4, device="cuda", dtype=torch.float16)
+    fns["gather"](src, idx, dst)
+    assert torch.equal(dst, torch.gather(src, 1, idx.long()))
