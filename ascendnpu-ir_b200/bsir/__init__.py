@@ -515,6 +515,46 @@ def gather(x: torch.Tensor, index: torch.Tensor, dim: int = -1, out: Optional[to
     return out
 
 
+def arange(shape: Sequence[int], strides: Sequence[int], offset: int = 0, dtype: torch.dtype = torch.int32,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hivm.hir.varange offset[o] strides[s..]``: out[i0, i1, ..] = o + sum_d i_d * s_d."""
+    shape = list(shape)
+    out = torch.empty(shape, dtype=dtype, device="cuda") if out is None else out
+    _check(lib().bsir_arange(_dt(out), len(shape), _i64arr(shape), C.c_int64(int(offset)), _i64arr(list(strides)), _ptr(out),
+                             _i64arr(out.stride()), _stream()))
+    return out
+
+
+def interleave(srcs: Sequence[torch.Tensor], out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hivm.hir.vinterleave`` of N tensors of one shape along their last axis: out[.., N * i + ch] = srcs[ch][.., i]."""
+    srcs = [s.contiguous() for s in srcs]
+    n, cols = len(srcs), srcs[0].shape[-1]
+    rows = srcs[0].numel() // max(cols, 1)
+    if any(s.shape != srcs[0].shape or s.dtype != srcs[0].dtype for s in srcs):
+        raise BsirError(-2, "interleave: the sources must have one shape and type")
+    out = torch.empty(list(srcs[0].shape[:-1]) + [n * cols], dtype=srcs[0].dtype, device=srcs[0].device) if out is None else out
+    if not out.is_contiguous():
+        raise BsirError(-3, "interleave: out must be contiguous")
+    arr = (C.c_void_p * n)(*[s.data_ptr() for s in srcs])
+    _check(lib().bsir_interleave(_dt(srcs[0]), n, C.c_int64(rows), C.c_int64(cols), arr, _ptr(out), _stream()))
+    return out
+
+
+def deinterleave(x: torch.Tensor, channels: int = 2, keep: Optional[Sequence[int]] = None):
+    """``hivm.hir.vdeinterleave {channel_num}``: N tensors with out[ch][.., i] = x[.., N * i + ch]; ``keep`` lists the
+    channels wanted (the others are not written and come back as None)."""
+    x = x.contiguous()
+    if x.shape[-1] % channels:
+        raise BsirError(-2, "deinterleave: the last axis must be a multiple of the channel count")
+    cols = x.shape[-1] // channels
+    rows = x.numel() // max(x.shape[-1], 1)
+    outs = [torch.empty(list(x.shape[:-1]) + [cols], dtype=x.dtype, device=x.device) if keep is None or ch in keep else None
+            for ch in range(channels)]
+    arr = (C.c_void_p * channels)(*[(o.data_ptr() if o is not None else None) for o in outs])
+    _check(lib().bsir_deinterleave(_dt(x), channels, C.c_int64(rows), C.c_int64(cols), _ptr(x), arr, _stream()))
+    return outs
+
+
 CUM_KIND = {"sum": 0, "prod": 1, "max": 2, "min": 3}
 
 

@@ -384,6 +384,19 @@ BSIR_API int32_t bsir_cumulative(int32_t kind, int32_t dtype, int32_t axis, int3
 BSIR_API int32_t bsir_gather(int32_t dtype, int32_t index_dtype, int64_t outer, int64_t src_axis, int64_t dst_axis,
                              int64_t inner, const void *src, const void *indices, void *dst, void *stream);
 
+/* hivm.hir.varange (HIVMVectorOps.td:1503-1560): dst[i0, i1, i2] = offset + sum_d i_d * strides[d], converted to
+ * dtype (i16, i32, i64, f16, f32); rank 1..3; dst_strides NULL = contiguous. */
+BSIR_API int32_t bsir_arange(int32_t dtype, int32_t rank, const int64_t *sizes, int64_t offset, const int64_t *strides,
+                             void *dst, const int64_t *dst_strides, void *stream);
+/* hivm.hir.vinterleave {interleave_channel_nums = channels} (HIVMVectorOps.td:1562-1606):
+ * dst[r, channels * i + ch] = srcs[ch][r, i]; sources contiguous [rows, cols], dst contiguous [rows, channels * cols].
+ * hivm.hir.vdeinterleave {channel_num} (1612-1660) is the inverse; a NULL destination skips its channel (the
+ * op's CHANNEL_0 / CHANNEL_1 index modes).  At most 8 channels; any element type (moved as bits). */
+BSIR_API int32_t bsir_interleave(int32_t dtype, int32_t channels, int64_t rows, int64_t cols, const void *const *srcs,
+                                 void *dst, void *stream);
+BSIR_API int32_t bsir_deinterleave(int32_t dtype, int32_t channels, int64_t rows, int64_t cols, const void *src,
+                                   void *const *dsts, void *stream);
+
 /* Fused softmax over the last axis
  * (test/Dialect/Analysis/VFFusion/MaxParallelKind/softmax_small_shape.mlir:86-117). */
 BSIR_API int32_t bsir_softmax(int32_t dtype, int64_t rows, int64_t cols, const void *x,

@@ -330,3 +330,36 @@ def test_gather_reports_indices_outside_the_axis(bsir):
     assert bsir.device_error() == 0x100                          # BSIR_DEVERR_GATHER_INDEX
     assert out.tolist() == [0.0, 9.0, -7.0, -7.0, 3.0]           # the bad ones are left untouched
     assert bsir.device_error() == 0                              # reading clears it
+
+
+# ---------------------------------------------------------------- varange, vinterleave, vdeinterleave
+def test_arange_example_of_the_op_definition(bsir):
+    """HIVMVectorOps.td:1518-1522: offset 1, strides [1, 2], shape 2x4 -> [[1, 3, 5, 7], [2, 4, 6, 8]]."""
+    y = bsir.arange([2, 4], [1, 2], offset=1, dtype=torch.int32)
+    assert y.tolist() == [[1, 3, 5, 7], [2, 4, 6, 8]]
+
+
+@pytest.mark.parametrize("dtype", [torch.int16, torch.int32, torch.int64, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape,strides,offset", [((1000,), (3,), -7), ((17, 33), (100, 1), 5), ((4, 5, 6), (30, 6, 1), 0)])
+def test_arange_shapes_and_types(bsir, dtype, shape, strides, offset):
+    y = bsir.arange(shape, strides, offset=offset, dtype=dtype)
+    want = torch.full(shape, offset, dtype=torch.int64, device="cuda")
+    for d, (n, s) in enumerate(zip(shape, strides)):
+        view = [1] * len(shape)
+        view[d] = n
+        want = want + (torch.arange(n, device="cuda") * s).view(view)
+    assert torch.equal(y, want.to(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.int8, torch.bfloat16, torch.float32, torch.int64])
+@pytest.mark.parametrize("channels", [1, 2, 3, 8])
+@pytest.mark.parametrize("shape", [(64, 128), (7, 33), (1, 1000), (2, 5, 16)])
+def test_interleave_and_deinterleave_are_inverse_bit_moves(bsir, dtype, channels, shape):
+    g = torch.Generator(device="cuda").manual_seed(channels)
+    srcs = [torch.randint(-100, 100, shape, device="cuda", generator=g).to(dtype) for _ in range(channels)]
+    y = bsir.interleave(srcs)
+    assert torch.equal(y, torch.stack(srcs, dim=-1).reshape(*shape[:-1], shape[-1] * channels))
+    back = bsir.deinterleave(y, channels)
+    assert all(torch.equal(b, s) for b, s in zip(back, srcs))
+    only = bsir.deinterleave(y, channels, keep=[channels - 1])
+    assert torch.equal(only[channels - 1], srcs[-1]) and all(o is None for o in only[:-1])
