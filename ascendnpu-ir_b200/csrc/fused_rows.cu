@@ -104,15 +104,19 @@ __device__ __forceinline__ int sat_i8(float r) {
 // reciprocal r = RN(1/scale) and one correction step, q0 = x r, q = fma(fma(-q0, scale, x), r, q0):
 // for every bf16 / f16 x with |x / scale| <= 127.5 this rounds to the same integer as the IEEE
 // quotient (checked exhaustively over all bf16 and all f16 x for thousands of scales by the CPU tests).
-template <int DT, int VPT>
+// TPR_C != 0: the threads per row are a compile-time constant and the row is exactly TPR_C * VPT vectors, so
+// the vector offsets are immediates and no bounds are checked (the usual power-of-two hidden sizes).
+template <int DT, int VPT, int TPR_C = 0>
 __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant_rows_kernel(RowGeom g, const void *__restrict__ xp, int64_t x_stride,
                                                           int8_t *__restrict__ qp, int64_t q_stride,
                                                           float *__restrict__ scale_out, int round_mode) {
   constexpr int kPerWord = FloatTraits<DT>::kPerWord;
   constexpr int kPerVec = 4 * kPerWord;
   __shared__ float red[kMaxWarpsPerRow * 32];
-  const int sub = threadIdx.x / g.tpr;
-  const int t = threadIdx.x % g.tpr;
+  const int tpr = TPR_C ? TPR_C : g.tpr;
+  constexpr bool kExact = TPR_C != 0;
+  const int sub = threadIdx.x / tpr;
+  const int t = threadIdx.x % tpr;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * g.rpc + sub;
   const bool row_ok = row < g.rows;
   using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
@@ -121,8 +125,8 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
   Vec16 v[VPT];
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
-    const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
-    if (row_ok && vi < g.nvec) v[i] = ld_stream(reinterpret_cast<const Vec16 *>(xrow) + vi);
+    const int64_t vi = t + static_cast<int64_t>(i) * tpr;
+    if (row_ok && (kExact || vi < g.nvec)) v[i] = ld_stream(reinterpret_cast<const Vec16 *>(xrow) + vi);
     else v[i] = Vec16{{0u, 0u, 0u, 0u}};
   }
   // row maximum of |x|, NaN-propagating.  16-bit types stay packed: clear both sign bits, then one
@@ -149,7 +153,7 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
 #pragma unroll
       for (int w = 0; w < 4; ++w) amax = maximumf(amax, fabsf(__uint_as_float(v[i].w[w])));
   }
-  amax = row_reduce(amax, g.tpr, red + sub * kMaxWarpsPerRow, 0.0f, 0, warp_red_maxnan);
+  amax = row_reduce(amax, tpr, red + sub * kMaxWarpsPerRow, 0.0f, 0, warp_red_maxnan);
   const float scale = __fdiv_rn(amax, 127.0f);
   if (row_ok && t == 0) scale_out[row] = scale;
   if (!row_ok) return;
@@ -161,8 +165,8 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
   if (degenerate) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
-      if (vi >= g.nvec) continue;
+      const int64_t vi = t + static_cast<int64_t>(i) * tpr;
+      if (!kExact && vi >= g.nvec) continue;
       if constexpr (kPerVec == 8) *reinterpret_cast<uint2 *>(qrow + vi * 8) = make_uint2(0u, 0u);
       else *reinterpret_cast<uint32_t *>(qrow + vi * 4) = 0u;
     }
@@ -179,8 +183,8 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
       asm("mov.b64 %0, {%1, %1};" : "=l"(magic2) : "f"(12582912.0f));
 #pragma unroll
       for (int i = 0; i < VPT; ++i) {
-        const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
-        if (vi >= g.nvec) continue;
+        const int64_t vi = t + static_cast<int64_t>(i) * tpr;
+        if (!kExact && vi >= g.nvec) continue;
         uint32_t lo8[8];
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
@@ -213,8 +217,8 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
   auto run = [&](auto conv) {
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
-      const int64_t vi = t + static_cast<int64_t>(i) * g.tpr;
-      if (vi >= g.nvec) continue;
+      const int64_t vi = t + static_cast<int64_t>(i) * tpr;
+      if (!kExact && vi >= g.nvec) continue;
       uint32_t bytes[kPerVec / 4];
 #pragma unroll
       for (int w4 = 0; w4 < kPerVec / 4; ++w4) {
@@ -1001,8 +1005,20 @@ int32_t bsir_quant_per_token_i8(int32_t dtype, int32_t round_mode, int64_t rows,
   if (vec_ok) {
     const unsigned blocks = static_cast<unsigned>(ceil_div(rows, g.rpc));
     const unsigned threads = static_cast<unsigned>(g.tpr * g.rpc);
-    DISPATCH_FLOAT_DT(dtype, DISPATCH_VPT(vpt, (quant_rows_kernel<D, V><<<blocks, threads, 0, st>>>(
-                                                    g, x, x_row_stride, q, q_row_stride, scale, round_mode))));
+    const bool exact = vpt == 8 && g.nvec == static_cast<int64_t>(g.tpr) * 8 && (dtype == BSIR_BF16 || dtype == BSIR_F16) &&
+                       (g.tpr == 32 || g.tpr == 64 || g.tpr == 128) && !env_int("BSIR_QUANT_GENERIC", 0);
+    if (exact) {
+#define QUANT_EXACT(D, T) quant_rows_kernel<D, 8, T><<<blocks, threads, 0, st>>>(g, x, x_row_stride, q, q_row_stride, scale, round_mode)
+      if (dtype == BSIR_BF16) {
+        if (g.tpr == 32) QUANT_EXACT(BSIR_BF16, 32); else if (g.tpr == 64) QUANT_EXACT(BSIR_BF16, 64); else QUANT_EXACT(BSIR_BF16, 128);
+      } else {
+        if (g.tpr == 32) QUANT_EXACT(BSIR_F16, 32); else if (g.tpr == 64) QUANT_EXACT(BSIR_F16, 64); else QUANT_EXACT(BSIR_F16, 128);
+      }
+#undef QUANT_EXACT
+    } else {
+      DISPATCH_FLOAT_DT(dtype, DISPATCH_VPT(vpt, (quant_rows_kernel<D, V><<<blocks, threads, 0, st>>>(
+                                                      g, x, x_row_stride, q, q_row_stride, scale, round_mode))));
+    }
   } else {
     DISPATCH_FLOAT_DT(dtype, (rows_multipass_kernel<D, kRowQuant><<<static_cast<unsigned>(rows), 256, 0, st>>>(
                                  rows, cols, x, x_row_stride, nullptr, 0.0f, 0.0f, q, q_row_stride, scale, round_mode)));
