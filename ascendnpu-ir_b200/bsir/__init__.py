@@ -555,6 +555,17 @@ def deinterleave(x: torch.Tensor, channels: int = 2, keep: Optional[Sequence[int
     return outs
 
 
+def sort(x: torch.Tensor, descending: bool = False):
+    """``hivm.hir.vsort {descending}`` over the last axis of a 1-D or 2-D tensor -> (values, int32 indices); stable."""
+    two_d = x if x.dim() == 2 else x.reshape(1, -1)
+    rows, cols, rs = _rows(two_d)
+    val = torch.empty((rows, cols), dtype=x.dtype, device=x.device)
+    idx = torch.empty((rows, cols), dtype=torch.int32, device=x.device)
+    _check(lib().bsir_sort(_dt(x), int(bool(descending)), C.c_int64(rows), C.c_int64(cols), _ptr(two_d), C.c_int64(rs), _ptr(val),
+                           C.c_int64(max(cols, 1)), _ptr(idx), C.c_int64(max(cols, 1)), _stream()))
+    return val.reshape(x.shape), idx.reshape(x.shape)
+
+
 CUM_KIND = {"sum": 0, "prod": 1, "max": 2, "min": 3}
 
 

@@ -225,6 +225,25 @@ def cumulative(kind, dt, src, axis=1, reverse=False, propagate_nan=True):
     return out
 
 
+def sort_last_axis(dt, src, descending=False):
+    """hivm.hir.vsort over the last axis (HIVMVectorOps.td:2222-2283): (sorted values in src's storage type, int32
+    source indices).  Stable; -0 = +0; NaN after every number ascending, before every number descending."""
+    src = _c(src, dt)
+    if dt in (F32, F16, BF16):
+        f = src.astype(np.float32) if dt == F32 else (f16_to_f32(src) if dt == F16 else bf16_to_f32(src))
+        bits = f.view(np.uint32).copy()
+        bits[bits == 0x80000000] = 0
+        order = np.where(bits & 0x80000000, ~bits, bits | np.uint32(0x80000000)).astype(np.uint32)
+        order[np.isnan(f)] = 0xFFFFFFFF
+    else:
+        order = (src.astype(np.int64) + 2 ** 31).astype(np.uint32)
+    if descending:
+        order = ~order
+    key = (order.astype(np.uint64) << np.uint64(32)) | np.arange(src.shape[-1], dtype=np.uint64)
+    idx = np.argsort(key, axis=-1, kind="stable").astype(np.int32)
+    return np.take_along_axis(src, idx.astype(np.int64), axis=-1), idx
+
+
 def reduce_with_index(kind, dt, src, tie_break_left=True, nan_mode="region"):
     """kind: 'max' | 'min'.  Returns (values, int32 indices)."""
     k = {"min": 0, "max": 1}[kind]
