@@ -15,7 +15,7 @@ Covered (attribute spellings as in the reference):
   hivm.hir.load (pad_mode / pad_value / left_padding_num / right_padding_num), hivm.hir.store (atomic = <kind>),
   hivm.hir.copy, hivm.hir.vadd / vsub / vmul / vdiv / vmax / vmin, hivm.hir.vcast, hivm.hir.vreduce <kind>,
   hivm.hir.vcumsum / vcumprod / vcummax / vcummin (and hfusion.cumsum ...) cum_dims = [k] reverse = <bool>,
-  hivm.hir.vgather ins(..) indices(..) outs(..) gather_axis = k
+  hivm.hir.vgather ins(..) indices(..) outs(..) gather_axis = k, hivm.hir.vsort ins(..) outs(%v, %i) descending = <bool>
   tensor.empty, tensor.dim, tensor.collapse_shape / expand_shape / reshape, tensor.extract_slice (static), linalg.transpose, memref.alloc, arith.constant (scalars, splat `dense<..>`), arith.{addf,subf,mulf,divf,addi,subi,muli},
   arith.{index_cast,index_castui,uitofp,sitofp,extf,truncf}, return
 Scalar arithmetic is done in the scalar's own type (f32 ops round to f32).  Anything else raises MlirTextError
@@ -210,7 +210,7 @@ class Function:
     def __call__(self, *tensors):
         import torch
         from . import (cast, compare, copy, cumulative, elemwise_binary, elemwise_unary, gather, load, matmul_w8a8, reduce,
-                       reduce_with_index, select, store)
+                       reduce_with_index, select, sort, store)
         if len(tensors) != len(self.args):
             raise MlirTextError(f"@{self.name} takes {len(self.args)} arguments, got {len(tensors)}")
         env: Dict[str, object] = {}
@@ -530,6 +530,18 @@ class Function:
                 y = cumulative(name.rsplit("cum", 1)[1], two_d, dim=axis, reverse=bool(op.attr("reverse", False)),
                                propagate_nan=bool(pn), out=dst if dst.dim() == 2 else dst.view(1, -1))
                 define(op, [y.view(src.shape)])
+            elif name == "hivm.hir.vsort":
+                # `hivm.hir.vsort ins(%s : T) outs(%v, %i : T, Ti) descending = <bool> sort_axis = k` (the last axis)
+                src = val(ins[0])
+                axis = re.search(r"sort_axis\s*=\s*(-?\d+)", op.text)
+                if axis and int(axis.group(1)) not in (-1, src.dim() - 1):
+                    raise MlirTextError("hivm.hir.vsort: only the last axis is sorted")
+                v, i = sort(src, descending=bool(op.attr("descending", False)))
+                res = [write_out(val(outs[0]), v)]
+                if len(outs) > 1:
+                    dst_i = val(outs[1])
+                    res.append(write_out(dst_i, i if dst_i.dtype == torch.int32 else cast(i, dst_i.dtype)))
+                define(op, res[:max(len(op.results), 0)] if op.results else [])
             elif name == "hivm.hir.vgather":
                 # `hivm.hir.vgather ins(%s : T) indices(%i : Ti) outs(%d : T) [gather_axis = k]` (-1 / absent: the last axis)
                 idx_names, _ = op.group("indices")

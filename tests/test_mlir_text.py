@@ -385,6 +385,10 @@ func.func @gather(%src: memref<100x7x4xf16>, %idx: memref<100x6x4xi32>, %dst: me
   hivm.hir.vgather ins(%src : memref<100x7x4xf16>) indices(%idx : memref<100x6x4xi32>) outs(%dst : memref<100x6x4xf16>) gather_axis = 1
   return
 }
+func.func @sort(%src: memref<8x100xf32>, %v: memref<8x100xf32>, %i: memref<8x100xi32>) {
+  hivm.hir.vsort ins(%src : memref<8x100xf32>) outs(%v, %i : memref<8x100xf32>, memref<8x100xi32>) descending = true sort_axis = 1
+  return
+}
 func.func @rev(%arg0: tensor<100xi32>) -> tensor<100xi32> {
   %1 = hfusion.cumsum %arg0 : tensor<100xi32> cum_dims = [0] reverse = true -> tensor<100xi32>
   return %1 : tensor<100xi32>
@@ -408,3 +412,8 @@ def test_cumulative_ops_in_both_spellings(bsir):
     dst = torch.empty(100, 6, 4, device="cuda", dtype=torch.float16)
     fns["gather"](src, idx, dst)
     assert torch.equal(dst, torch.gather(src, 1, idx.long()))
+    s = torch.randn(8, 100, device="cuda")
+    sv, si = torch.empty_like(s), torch.empty(8, 100, device="cuda", dtype=torch.int32)
+    fns["sort"](s, sv, si)
+    want = torch.sort(s, dim=1, descending=True, stable=True)
+    assert torch.equal(sv, want.values) and torch.equal(si.long(), want.indices)
