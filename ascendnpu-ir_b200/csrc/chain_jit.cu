@@ -4,7 +4,8 @@
 // (HFusion outlining: bishengir/lib/Dialect/HFusion/Transforms/OpFusion/FusibleHelper.cpp:52-72).  The
 // equivalent here: the tape of bsir_fused_elementwise is turned into CUDA C++ (straight-line code,
 // every operand a 16-byte streaming load issued before the arithmetic), compiled once with NVRTC for
-// sm_100a, loaded through the runtime's library API and cached by its source text.  The arithmetic is
+// sm_100a, loaded through the runtime's library API and cached by what its text depends on (the tape, the
+// operand and output types, the thread mapping).  The arithmetic is
 // spelled with the same expressions as the tape interpreter of fused_chain.cu (and --fmad=false), so
 // both paths give the same bits.
 //
@@ -583,14 +584,34 @@ int chain_jit_compile_only(const ChainJitSpec &s, size_t *cubin_bytes, std::stri
   return 0;
 }
 
+namespace {
+// Everything the generated source depends on, as bytes: the cache key (the source itself is only built on a miss).
+std::string spec_key(const ChainJitSpec &s) {
+  std::string k;
+  auto put = [&](int32_t v) { k.append(reinterpret_cast<const char *>(&v), sizeof v); };
+  put(s.n_in); put(s.n_instr); put(s.n_out);
+  put(s.flat); put(s.alias); put(s.row_grid); put(chain_jit_unroll(s)); put(s.tpr); put(s.vpt);
+  for (int i = 0; i < s.n_in; ++i) { put(s.in_dtype[i]); put(s.in_kind[i]); }
+  for (int i = 0; i < s.n_instr; ++i) {
+    const bsir_chain_instr &t = s.tape[i];
+    int32_t imm;
+    memcpy(&imm, &t.imm, 4);
+    put(t.op); put(t.fn); put(t.src_kind); put(t.src); put(imm);
+  }
+  for (int i = 0; i < s.n_out; ++i) { put(s.out_dtype[i]); put(s.out_tmp[i]); put(s.out_per_row[i]); }
+  return k;
+}
+}  // namespace
+
 int chain_jit_launch(const ChainJitSpec &s, const ChainJitArgs &args, cudaStream_t st, std::string *why) {
-  const std::string src = chain_jit_source(s);
+  const std::string key = spec_key(s);
   cudaKernel_t kernel = nullptr;
   {
     std::lock_guard<std::mutex> lock(g_mu);
-    auto it = g_cache.find(src);
+    auto it = g_cache.find(key);
     if (it == g_cache.end()) {
       Compiled cpl;
+      const std::string src = chain_jit_source(s);
       const std::vector<char> cubin = compile_cubin(src, &cpl.why);
       if (!cubin.empty()) {
         cudaLibrary_t lib = nullptr;
@@ -602,7 +623,7 @@ int chain_jit_launch(const ChainJitSpec &s, const ChainJitArgs &args, cudaStream
           (void)cudaGetLastError();
         }
       }
-      it = g_cache.emplace(src, std::move(cpl)).first;
+      it = g_cache.emplace(key, std::move(cpl)).first;
     }
     if (!it->second.kernel) {
       *why = it->second.why;

@@ -348,7 +348,7 @@ BSIR_API int32_t bsir_fused_elementwise(int64_t rows, int64_t cols, int32_t n_in
                                         const bsir_chain_output *outs, void *stream);
 /* How the last bsir_fused_elementwise of this thread ran: 0 nothing was enqueued, 1 the tape interpreter kernel,
  * 2 a kernel compiled for this chain.  By default a chain whose rows are 16-byte aligned multiples of 8 columns
- * is compiled on first use (NVRTC, sm_100a; cached by its source for the life of the process) and everything
+ * is compiled on first use (NVRTC, sm_100a; cached for the life of the process; the first call with a new chain must not sit inside a stream capture) and everything
  * else is interpreted; both give the same bits.  BSIR_CHAIN_JIT=0 always interprets, =1 returns
  * BSIR_ERR_UNSUPPORTED instead of interpreting (no NVRTC in the process, ragged rows). */
 BSIR_API int32_t bsir_fused_elementwise_path(void);
