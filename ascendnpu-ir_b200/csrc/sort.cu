@@ -6,8 +6,9 @@
 // 64-bit keys  order(value) << 32 | index  (order() maps the element type to unsigned integers that compare
 // like the values; descending complements it), so one integer comparison decides value and tie at once and the
 // bitonic network -- not stable by itself -- gives a stable result.  A CTA sorts one row in shared memory
-// (rows of up to 8192 elements: 64 KB of keys); the values are read back from the source by index, so their
-// bits (the sign of a zero, the payload of a NaN) are the source's.
+// (rows of up to 8192 elements: 64 KB of keys); longer rows keep their keys in device scratch and run the wide
+// steps of the network on global memory.  The values are read back from the source by index, so their bits
+// (the sign of a zero, the payload of a NaN) are the source's.
 #include <cstdint>
 
 #include "common.cuh"
@@ -82,6 +83,125 @@ __global__ void __launch_bounds__(kSortThreads) sort_rows_kernel(const typename 
   }
 }
 
+// ------------------------------------------------------------------ rows longer than one CTA's shared memory
+// The same network over keys kept in device scratch ([rows][npow2] 64-bit words): one launch sorts every 8192-key
+// chunk in shared memory (all steps with k <= 8192, directions taken from the position in the whole row), then
+// for k = 16384, 32768, ...: the steps whose partners are 8192 or more apart run on global memory, one launch
+// each, and the steps below that again in shared memory, one launch per k.
+template <int DT>
+__global__ void __launch_bounds__(kSortThreads) sort_chunks_kernel(const typename SortElem<DT>::type *__restrict__ src, int64_t src_stride,
+                                                                   unsigned long long *__restrict__ keys_g, int64_t cols, int npow2,
+                                                                   int descending, int k_first, int k_last) {
+  // k_first == 2: build the keys from the source and run k = 2 .. k_last; otherwise k = k_first only, with the
+  // steps j < kSortMaxLen (the wider ones were done on global memory)
+  extern __shared__ unsigned long long keys[];
+  const int64_t row = blockIdx.y;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kSortMaxLen;      // position of this chunk in the row
+  unsigned long long *g = keys_g + row * npow2 + base;
+  if (k_first == 2) {
+    const auto *s = src + row * src_stride;
+    for (int i = threadIdx.x; i < kSortMaxLen; i += kSortThreads) {
+      const int64_t pos = base + i;
+      unsigned long long k = ~0ull;
+      if (pos < cols) {
+        uint32_t o = sort_order<DT>(s[pos]);
+        if (descending) o = ~o;
+        k = (static_cast<unsigned long long>(o) << 32) | static_cast<uint32_t>(pos);
+      }
+      keys[i] = k;
+    }
+  } else {
+    for (int i = threadIdx.x; i < kSortMaxLen; i += kSortThreads) keys[i] = g[i];
+  }
+  __syncthreads();
+  for (int64_t k = k_first; k <= k_last; k <<= 1) {
+    for (int j = static_cast<int>(k >> 1 < kSortMaxLen ? k >> 1 : kSortMaxLen >> 1); j > 0; j >>= 1) {
+      for (int t = threadIdx.x; t < kSortMaxLen / 2; t += kSortThreads) {
+        const int lo = ((t & ~(j - 1)) << 1) | (t & (j - 1)), hi = lo | j;
+        const bool up = ((base + lo) & k) == 0;
+        const unsigned long long a = keys[lo], b = keys[hi];
+        if ((a > b) == up) {
+          keys[lo] = b;
+          keys[hi] = a;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int i = threadIdx.x; i < kSortMaxLen; i += kSortThreads) g[i] = keys[i];
+}
+
+// one compare-exchange step (partners j apart, j >= kSortMaxLen) of stage k on global memory
+__global__ void __launch_bounds__(256) sort_global_step_kernel(unsigned long long *__restrict__ keys_g, int npow2, int64_t k, int64_t j) {
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= npow2 / 2) return;
+  unsigned long long *g = keys_g + static_cast<int64_t>(blockIdx.y) * npow2;
+  const int64_t lo = ((t & ~(j - 1)) << 1) | (t & (j - 1)), hi = lo | j;
+  const bool up = (lo & k) == 0;
+  const unsigned long long a = g[lo], b = g[hi];
+  if ((a > b) == up) {
+    g[lo] = b;
+    g[hi] = a;
+  }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(256) sort_emit_kernel(const typename SortElem<DT>::type *__restrict__ src, int64_t src_stride,
+                                                        const unsigned long long *__restrict__ keys_g, int npow2,
+                                                        typename SortElem<DT>::type *__restrict__ dst_value, int64_t val_stride,
+                                                        int32_t *__restrict__ dst_index, int64_t idx_stride, int64_t cols) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= cols) return;
+  const int64_t row = blockIdx.y;
+  const uint32_t idx = static_cast<uint32_t>(keys_g[row * npow2 + i]);
+  if (dst_value) dst_value[row * val_stride + i] = src[row * src_stride + idx];
+  if (dst_index) dst_index[row * idx_stride + i] = static_cast<int32_t>(idx);
+}
+
+// rows per pass such that the keys fit `budget` bytes of scratch
+template <int DT>
+int32_t launch_sort_long(const void *src, int64_t ss, void *dv, int64_t vs, int32_t *di, int64_t is, int64_t rows, int64_t cols,
+                         int descending, cudaStream_t st) {
+  using T = typename SortElem<DT>::type;
+  int64_t npow2 = kSortMaxLen;
+  while (npow2 < cols) npow2 <<= 1;
+  if (npow2 > (int64_t(1) << 30)) return fail(BSIR_ERR_UNSUPPORTED, "sort: rows of %lld elements", (long long)cols);
+  const int64_t row_bytes = npow2 * 8;
+  const int64_t budget = int64_t(1) << 30;                       // at most 1 GiB of keys at a time
+  int64_t rows_per_pass = budget / row_bytes;
+  if (rows_per_pass < 1) rows_per_pass = 1;
+  if (rows_per_pass > rows) rows_per_pass = rows;
+  if (rows_per_pass > 65535) rows_per_pass = 65535;
+  char *ws = static_cast<char *>(device_workspace(kScratchCounterBytes + static_cast<size_t>(rows_per_pass * row_bytes), st));
+  if (!ws) return BSIR_ERR_WORKSPACE;
+  unsigned long long *keys = reinterpret_cast<unsigned long long *>(ws + kScratchCounterBytes);
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaFuncSetAttribute(sort_chunks_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSortMaxLen * 8);
+    attr_done = true;
+  }
+  const T *s = static_cast<const T *>(src);
+  T *d = static_cast<T *>(dv);
+  const int n = static_cast<int>(npow2);
+  for (int64_t r0 = 0; r0 < rows; r0 += rows_per_pass) {
+    const unsigned nr = static_cast<unsigned>(rows - r0 < rows_per_pass ? rows - r0 : rows_per_pass);
+    const dim3 chunks(static_cast<unsigned>(npow2 / kSortMaxLen), nr);
+    sort_chunks_kernel<DT><<<chunks, kSortThreads, kSortMaxLen * 8, st>>>(s + r0 * ss, ss, keys, cols, n, descending, 2, kSortMaxLen);
+    count_launch();
+    for (int64_t k = 2 * kSortMaxLen; k <= npow2; k <<= 1) {
+      for (int64_t j = k >> 1; j >= kSortMaxLen; j >>= 1) {
+        sort_global_step_kernel<<<dim3(static_cast<unsigned>(ceil_div(npow2 / 2, 256)), nr), 256, 0, st>>>(keys, n, k, j);
+        count_launch();
+      }
+      sort_chunks_kernel<DT><<<chunks, kSortThreads, kSortMaxLen * 8, st>>>(s, ss, keys, cols, n, descending, static_cast<int>(k), static_cast<int>(k));
+      count_launch();
+    }
+    sort_emit_kernel<DT><<<dim3(static_cast<unsigned>(ceil_div(cols, 256)), nr), 256, 0, st>>>(
+        s + r0 * ss, ss, keys, n, d ? d + r0 * vs : nullptr, vs, di ? di + r0 * is : nullptr, is, cols);
+  }
+  return BSIR_OK;
+}
+
 template <int DT>
 void launch_sort(const void *src, int64_t ss, void *dv, int64_t vs, int32_t *di, int64_t is, int64_t rows, int64_t cols, int descending,
                  cudaStream_t st) {
@@ -111,7 +231,6 @@ extern "C" int32_t bsir_sort(int32_t dtype, int32_t descending, int64_t rows, in
   if (rows < 0 || cols < 0) return fail(BSIR_ERR_SHAPE, "sort: rows=%lld cols=%lld", (long long)rows, (long long)cols);
   if (rows == 0 || cols == 0) return BSIR_OK;
   if (!src || (!dst_value && !dst_index)) return fail(BSIR_ERR_NULL, "sort: null pointer");
-  if (cols > kSortMaxLen) return fail(BSIR_ERR_UNSUPPORTED, "sort: rows of %lld elements (at most %d are sorted in shared memory)", (long long)cols, kSortMaxLen);
   if (rows > 0x7fffffffLL) return fail(BSIR_ERR_SHAPE, "sort: %lld rows", (long long)rows);
   if (src_row_stride < cols || (dst_value && value_row_stride < cols) || (dst_index && index_row_stride < cols))
     return fail(BSIR_ERR_STRIDE, "sort: row stride below the row length");
@@ -119,6 +238,20 @@ extern "C" int32_t bsir_sort(int32_t dtype, int32_t descending, int64_t rows, in
   if (!aligned_to(src, eb) || !aligned_to(dst_value, eb) || !aligned_to(dst_index, 4)) return fail(BSIR_ERR_ALIGN, "sort: misaligned");
   cudaStream_t st = resolve_stream(stream);
   const int desc = descending != 0;
+  if (cols > kSortMaxLen) {   // keys in device scratch, the wide steps of the network on global memory
+    int32_t rc;
+    switch (dtype) {
+      case BSIR_F32: rc = launch_sort_long<BSIR_F32>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
+      case BSIR_F16: rc = launch_sort_long<BSIR_F16>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
+      case BSIR_BF16: rc = launch_sort_long<BSIR_BF16>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
+      case BSIR_I8: rc = launch_sort_long<BSIR_I8>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
+      case BSIR_I16: rc = launch_sort_long<BSIR_I16>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
+      default: rc = launch_sort_long<BSIR_I32>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
+    }
+    if (rc != BSIR_OK) return rc;
+    count_launch();
+    return check_launch("sort");
+  }
   switch (dtype) {
     case BSIR_F32: launch_sort<BSIR_F32>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
     case BSIR_F16: launch_sort<BSIR_F16>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;

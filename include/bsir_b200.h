@@ -400,8 +400,8 @@ BSIR_API int32_t bsir_deinterleave(int32_t dtype, int32_t channels, int64_t rows
 /* hivm.hir.vsort {descending, sort_axis = last} (HIVMVectorOps.td:2222-2283): every row sorted by value, with the
  * source index of each sorted element (int32).  Equal values keep their source order; -0 = +0; NaN comes after
  * every number when ascending, before every number when descending.  dst_value or dst_index may be NULL.
- * dtype: f32, f16, bf16, i8, i16, i32.  Rows of up to 8192 elements (sorted in shared memory); longer rows
- * return BSIR_ERR_UNSUPPORTED. */
+ * dtype: f32, f16, bf16, i8, i16, i32.  Rows of up to 8192 elements are sorted in shared memory by one CTA; longer
+ * rows (up to 2^30 elements) keep 8 bytes per padded element in the library's device scratch. */
 BSIR_API int32_t bsir_sort(int32_t dtype, int32_t descending, int64_t rows, int64_t cols, const void *src,
                            int64_t src_row_stride, void *dst_value, int64_t value_row_stride, int32_t *dst_index,
                            int64_t index_row_stride, void *stream);

@@ -47,10 +47,24 @@ def test_sort_special_values(bsir):
 
 
 def test_sort_limits_and_strides(bsir):
-    with pytest.raises(bsir.BsirError):
-        bsir.sort(torch.zeros(2, 8193, device="cuda"))
     big = torch.randn(10, 300, device="cuda")
     view = big[:, 10:210]                                      # row stride 300
     val, idx = bsir.sort(view)
     assert torch.equal(val, torch.sort(view, dim=1, stable=True).values)
     assert torch.equal(idx.long(), torch.sort(view, dim=1, stable=True).indices)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32])
+@pytest.mark.parametrize("rows,cols", [(2, 8193), (3, 20000), (5, 65536), (2, 152064)])
+@pytest.mark.parametrize("descending", [False, True])
+def test_sort_rows_longer_than_shared_memory(bsir, dtype, rows, cols, descending):
+    """Keys in device scratch, the wide steps of the network on global memory: the same rule, the same bits."""
+    g = torch.Generator(device="cuda").manual_seed(cols)
+    if dtype.is_floating_point:
+        x = (torch.randn(rows, cols, device="cuda", generator=g) * 8).round().div(4).to(dtype)
+    else:
+        x = torch.randint(-3000, 3000, (rows, cols), device="cuda", generator=g).to(dtype)
+    val, idx = bsir.sort(x, descending=descending)
+    wv, wi = O.sort_last_axis(oracle_dtype(x), to_bits(x), descending=descending)
+    assert np.array_equal(idx.cpu().numpy(), wi)
+    assert np.array_equal(to_bits(val), wv)
