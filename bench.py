@@ -377,8 +377,9 @@ def run_ours(args):
                 bsir.quant_per_token_i8(xs[1][r0:r1], q=qs[1][r0:r1], scale=ss[1][r0:r1])
                 hq[r0:r1].copy_(qs[1][r0:r1], non_blocking=True)
                 hs[r0:r1].copy_(ss[1][r0:r1], non_blocking=True)
-        for st in streams:
-            st.synchronize()
+        # no host wait here: a chunk always uses the same stream, so step i+1's copies of a chunk queue behind
+        # step i's, and the device-to-host tail of one step overlaps the host-to-device head of the next; the
+        # timed region ends with a device synchronise, when every step's results are in host memory
 
     e2e_step()
     torch.cuda.synchronize()
