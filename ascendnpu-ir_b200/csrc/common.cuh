@@ -8,7 +8,9 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <utility>
 
 #include "bsir_b200.h"
 
@@ -57,6 +59,32 @@ inline int dtype_bytes(int32_t dt) {
 inline bool dtype_is_float(int32_t dt) { return dt == BSIR_F32 || dt == BSIR_F16 || dt == BSIR_BF16; }
 inline bool dtype_is_unsigned(int32_t dt) { return dt >= BSIR_U8 && dt <= BSIR_BOOL; }
 inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+// ----------------------------------------------------------------------------
+// programmatic dependent launch
+// ----------------------------------------------------------------------------
+// A kernel launched with launch_pdl may be scheduled before the kernel ahead of it in the stream has finished, if
+// that one called pdl_launch_dependents(); it must call pdl_wait() before its first access to global memory
+// (the wait returns when the kernel ahead has completed and its writes are visible).  Kernels ahead that never
+// call pdl_launch_dependents() serialise as usual.  BSIR_NO_PDL=1 launches plainly.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+  static const bool off = [] { const char *e = std::getenv("BSIR_NO_PDL"); return e && e[0] == '1'; }();
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = off ? 0 : 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // ----------------------------------------------------------------------------
 // device: element types and conversions

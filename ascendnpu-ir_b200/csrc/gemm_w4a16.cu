@@ -89,6 +89,8 @@ __global__ void __launch_bounds__(kWarps * 32, NP == 1 ? 3 : 2) w4a16_mma_kernel
   const int s_begin = min(steps, warp * per_warp);
   const int s_end = min(steps, s_begin + per_warp);
   const int64_t rows_left = p.m - m0;
+  pdl_launch_dependents();   // the next launch may be scheduled while this one runs (launch_pdl) ...
+  pdl_wait();                // ... and this one reads global memory only after the kernel ahead has completed
 
   // this thread's columns: piece j covers col_base + 32 j + 4 g + {0..3}; n is a multiple of 8, so a
   // piece is all in or all out.  Everything is addressed through pointers that advance by a fixed
@@ -364,6 +366,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       tma_load_2d(dst + kTcWeightBytes + c * 2048, &tmap_a, (s * 4 + c) * 64, static_cast<int>(m0), wfull(slot));
   };
   const int preissued = nstages_total < nstages ? nstages_total : nstages;
+  pdl_launch_dependents();   // barrier set-up and the tensor-memory allocation overlap the kernel ahead (launch_pdl)
   if (warp == kTcDqWarps && lane == 0) {
     for (int s = 0; s < nstages; ++s) {
       mbar_init(wfull(s), 1);
@@ -374,10 +377,13 @@ __global__ void __launch_bounds__(kTcThreads, 1)
     mbar_init(dfull, kTcMmaWarps);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    pdl_wait();
     // the first ring of loads goes out before the CTA meets
     for (int s = 0; s < preissued; ++s) issue_stage(s);
+  } else {
+    if (warp == kTcDqWarps + 1) tmem_alloc(smem_u32(tmem_slot), 512);
+    pdl_wait();              // global memory is read from here on
   }
-  if (warp == kTcDqWarps + 1) tmem_alloc(smem_u32(tmem_slot), 512);
   // scales and zero points of all groups of this CTA's columns, every load issued before the first store
   {
     const int nvec = ngroups * (kTcCols / 8);                 // 8 bf16 per vector
@@ -711,11 +717,12 @@ extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t gr
     if (use_tc) {
       const size_t smem = tc_layout(k, group).bytes;
       cudaFuncSetAttribute(w4a16_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-      w4a16_tc_kernel<<<static_cast<unsigned>(ceil_div(n, kTcCols)), kTcThreads, smem, st>>>(tw, ta, p, m0, device_error_word());
+      launch_pdl(w4a16_tc_kernel, dim3(static_cast<unsigned>(ceil_div(n, kTcCols))), dim3(kTcThreads), smem, st, tw, ta, p, m0,
+                 device_error_word());
     } else {
       const unsigned blocks = static_cast<unsigned>(ceil_div(n, 64));
-      if (one_block) w4a16_mma_kernel<2, 1><<<blocks, kWarps * 32, 0, st>>>(p, m0);
-      else w4a16_mma_kernel<2, 2><<<blocks, kWarps * 32, 0, st>>>(p, m0);
+      if (one_block) launch_pdl(w4a16_mma_kernel<2, 1>, dim3(blocks), dim3(kWarps * 32), 0, st, p, m0);
+      else launch_pdl(w4a16_mma_kernel<2, 2>, dim3(blocks), dim3(kWarps * 32), 0, st, p, m0);
     }
     count_launch();
   }

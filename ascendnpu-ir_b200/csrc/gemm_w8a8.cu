@@ -180,6 +180,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = p.m_tiles * p.n_tiles;
 
+  pdl_launch_dependents();   // the set-up below overlaps the tail of the kernel ahead (see launch_pdl)
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
@@ -189,6 +190,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     prefetch_tmap(&tmap_b);
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+  pdl_wait();                // no global memory is touched before this
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -365,16 +367,22 @@ __global__ void __launch_bounds__(kThreads, 1)
     tma_load_2d(sw + kDecStageW, &tmap_a, kb * kBK, 0, full_bar(stage));          // [nb rows x 128 k bytes]
   };
   const int preissued = total_its < nstages ? total_its : nstages;
+  // Programmatic dependent launch: the next kernel of the stream may be scheduled while this one runs (its
+  // blocks take SMs as ours leave them), and this kernel touches global memory only after the one before it
+  // has completed -- so launch latency and the barrier / tensor-memory set-up overlap the predecessor's tail.
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < nstages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    pdl_wait();
     // the first ring of loads goes out before the CTA meets: a launch this short (about 9 us of
     // transfer) cannot afford to wait for the tensor-memory allocation first
     for (int it = 0; it < preissued; ++it) issue(it);
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), tmem_cols);
+  if (threadIdx.x != 0) pdl_wait();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -755,7 +763,7 @@ int32_t launch_tc(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMa
   const int total = p.m_tiles * p.n_tiles;
   int grid = device_info().sm_count > 0 ? device_info().sm_count : 148;
   if (grid > total) grid = total;
-  w8a8_tc_kernel<BN, B_MN><<<grid, kThreads, Cfg::kSmemBytes, st>>>(ta, tb, tout, p);
+  launch_pdl(w8a8_tc_kernel<BN, B_MN>, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, ta, tb, tout, p);
   count_launch();
   return check_launch("matmul_w8a8");
 }
@@ -861,10 +869,10 @@ extern "C" int32_t bsir_matmul_w8a8(int64_t m, int64_t n, int64_t k, const int8_
         if (grid > p.n_tiles) grid = p.n_tiles;
         if (b_mn) {
           cudaFuncSetAttribute(w8a8_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dc.smem));
-          w8a8_decode_kernel<true><<<grid, kThreads, dc.smem, st>>>(tw, tact, p, dc.nb, dc.stage, dc.stages);
+          launch_pdl(w8a8_decode_kernel<true>, dim3(grid), dim3(kThreads), dc.smem, st, tw, tact, p, dc.nb, dc.stage, dc.stages);
         } else {
           cudaFuncSetAttribute(w8a8_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dc.smem));
-          w8a8_decode_kernel<false><<<grid, kThreads, dc.smem, st>>>(tw, tact, p, dc.nb, dc.stage, dc.stages);
+          launch_pdl(w8a8_decode_kernel<false>, dim3(grid), dim3(kThreads), dc.smem, st, tw, tact, p, dc.nb, dc.stage, dc.stages);
         }
         count_launch();
         return check_launch("matmul_w8a8 (decode)");

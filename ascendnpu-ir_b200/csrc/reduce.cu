@@ -834,6 +834,8 @@ __global__ void __launch_bounds__(256, 4) rwi_stream_kernel(RwiParams p, const v
   __shared__ float redf[8];
   __shared__ int redi[8];
   __shared__ float warp_val[8];
+  pdl_launch_dependents();   // the next launch may be scheduled while this one runs (launch_pdl) ...
+  pdl_wait();                // ... and this one touches global memory only after the kernel ahead has completed
   __shared__ int warp_idx[8];
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const float ident = IS_MAX ? __int_as_float(0xff800000) : __int_as_float(0x7f800000);
@@ -1231,8 +1233,8 @@ int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie_break_le
     Partial *parts = reinterpret_cast<Partial *>(ws + kScratchCounterBytes);
     const dim3 grid1(static_cast<unsigned>(p.nseg), static_cast<unsigned>(rows));
 #define LS(D)                                                                                         \
-  if (is_max) rwi_stream_kernel<D, true><<<grid1, 256, 0, st>>>(p, src, dst_value, dst_index, cnt, parts); \
-  else rwi_stream_kernel<D, false><<<grid1, 256, 0, st>>>(p, src, dst_value, dst_index, cnt, parts);
+  if (is_max) launch_pdl(rwi_stream_kernel<D, true>, grid1, dim3(256), 0, st, p, src, dst_value, dst_index, cnt, parts); \
+  else launch_pdl(rwi_stream_kernel<D, false>, grid1, dim3(256), 0, st, p, src, dst_value, dst_index, cnt, parts);
     if (dtype == BSIR_F32) { LS(BSIR_F32) } else if (dtype == BSIR_F16) { LS(BSIR_F16) } else { LS(BSIR_BF16) }
 #undef LS
     count_launch();
