@@ -369,6 +369,8 @@ __global__ void __launch_bounds__(kStreamThreads)
   constexpr int kPerVec = 16 / sizeof(T);
   const int64_t nvec = n / kPerVec;
   const int64_t base = static_cast<int64_t>(blockIdx.x) * (kStreamThreads * kStreamUnroll) + threadIdx.x;
+  pdl_launch_dependents();   // the next launch may be scheduled while this one runs (launch_pdl) ...
+  pdl_wait();                // ... and this one touches global memory only after the kernel ahead has completed
 
   Vec16 va[kStreamUnroll], vb[kStreamUnroll];
   T sa, sb;
@@ -656,8 +658,8 @@ int32_t launch_typed(const char *what, int fn, const Prepared &p, const Operand 
       const int64_t nvec = n / kPerVec;
       int64_t blocks = ceil_div(nvec, kStreamThreads * kStreamUnroll);
       if (blocks < 1) blocks = 1;
-      stream_kernel<DT, KIND><<<static_cast<unsigned>(blocks), kStreamThreads, 0, st>>>(
-          fn, n, a.p, KIND == kOpBinary ? b.p : nullptr, a.scalar, b.scalar, out);
+      launch_pdl(stream_kernel<DT, KIND>, dim3(static_cast<unsigned>(blocks)), dim3(kStreamThreads), 0, st, fn, n, a.p,
+                 KIND == kOpBinary ? b.p : nullptr, a.scalar, b.scalar, out);
       count_launch();
       return check_launch(what);
     }

@@ -115,6 +115,8 @@ __global__ void __launch_bounds__(VPT >= 16 ? 256 : VPT >= 8 ? 512 : 1024) quant
   __shared__ float red[kMaxWarpsPerRow * 32];
   const int tpr = TPR_C ? TPR_C : g.tpr;
   constexpr bool kExact = TPR_C != 0;
+  pdl_launch_dependents();   // the next launch may be scheduled while this one runs (launch_pdl) ...
+  pdl_wait();                // ... and this one touches global memory only after the kernel ahead has completed
   const int sub = threadIdx.x / tpr;
   const int t = threadIdx.x % tpr;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * g.rpc + sub;
@@ -1008,7 +1010,7 @@ int32_t bsir_quant_per_token_i8(int32_t dtype, int32_t round_mode, int64_t rows,
     const bool exact = vpt == 8 && g.nvec == static_cast<int64_t>(g.tpr) * 8 && (dtype == BSIR_BF16 || dtype == BSIR_F16) &&
                        (g.tpr == 32 || g.tpr == 64 || g.tpr == 128) && !env_int("BSIR_QUANT_GENERIC", 0);
     if (exact) {
-#define QUANT_EXACT(D, T) quant_rows_kernel<D, 8, T><<<blocks, threads, 0, st>>>(g, x, x_row_stride, q, q_row_stride, scale, round_mode)
+#define QUANT_EXACT(D, T) launch_pdl(quant_rows_kernel<D, 8, T>, dim3(blocks), dim3(threads), 0, st, g, x, x_row_stride, q, q_row_stride, scale, round_mode)
       if (dtype == BSIR_BF16) {
         if (g.tpr == 32) QUANT_EXACT(BSIR_BF16, 32); else if (g.tpr == 64) QUANT_EXACT(BSIR_BF16, 64); else QUANT_EXACT(BSIR_BF16, 128);
       } else {
@@ -1016,8 +1018,8 @@ int32_t bsir_quant_per_token_i8(int32_t dtype, int32_t round_mode, int64_t rows,
       }
 #undef QUANT_EXACT
     } else {
-      DISPATCH_FLOAT_DT(dtype, DISPATCH_VPT(vpt, (quant_rows_kernel<D, V><<<blocks, threads, 0, st>>>(
-                                                      g, x, x_row_stride, q, q_row_stride, scale, round_mode))));
+      DISPATCH_FLOAT_DT(dtype, DISPATCH_VPT(vpt, (launch_pdl(quant_rows_kernel<D, V, 0>, dim3(blocks), dim3(threads), 0, st, g, x,
+                                                             x_row_stride, q, q_row_stride, scale, round_mode))));
     }
   } else {
     DISPATCH_FLOAT_DT(dtype, (rows_multipass_kernel<D, kRowQuant><<<static_cast<unsigned>(rows), 256, 0, st>>>(
