@@ -363,3 +363,21 @@ def test_interleave_and_deinterleave_are_inverse_bit_moves(bsir, dtype, channels
     assert all(torch.equal(b, s) for b, s in zip(back, srcs))
     only = bsir.deinterleave(y, channels, keep=[channels - 1])
     assert torch.equal(only[channels - 1], srcs[-1]) and all(o is None for o in only[:-1])
+
+
+def test_broadcast_binary_ops_run_as_compiled_chains(bsir):
+    """A float binary op with a per-column or per-row operand takes the fused-chain kernel (16-byte accesses); the
+    bits are those of the indexed kernel, which still serves ragged rows."""
+    x = torch.randn(300, 1024, device="cuda").to(torch.bfloat16)
+    bias = torch.randn(1024, device="cuda").to(torch.bfloat16)
+    scale = (torch.rand(300, 1, device="cuda") + 0.5).to(torch.bfloat16)
+    for fn, other in (("add", bias.view(1, -1).expand(300, 1024)), ("mul", scale.expand(300, 1024)), ("sub", bias.view(1, -1).expand(300, 1024))):
+        y = bsir.elemwise_binary(fn, x, other)
+        assert bsir.FusedChain.last_path() == "compiled"
+        want = O.elemwise_binary(fn, O.BF16, to_bits(x), to_bits(other.contiguous()))
+        assert_bits_equal(y, want, f"broadcast {fn}")
+        z = bsir.elemwise_binary(fn, other, x)                     # the broadcast operand on the left
+        assert_bits_equal(z, O.elemwise_binary(fn, O.BF16, to_bits(other.contiguous()), to_bits(x)), f"broadcast r{fn}")
+    ragged = torch.randn(50, 1001, device="cuda")
+    y = bsir.elemwise_binary("add", ragged, torch.randn(1001, device="cuda").view(1, -1).expand(50, 1001))
+    assert y.shape == ragged.shape
