@@ -728,6 +728,11 @@ using namespace bsir;
 
 extern "C" {
 
+namespace {
+bool try_chain_route(bool binary, int fn, int dtype, const Prepared &p, const Operand &a, const Operand &b, void *out, void *stream,
+                     int32_t *rc);
+}
+
 int32_t bsir_elemwise_unary(int32_t fn, int32_t dtype, int32_t rank, const int64_t *sizes, const bsir_operand *x,
                             void *out, const int64_t *out_strides, void *stream) {
   clear_error();
@@ -743,41 +748,66 @@ int32_t bsir_elemwise_unary(int32_t fn, int32_t dtype, int32_t rank, const int64
   if (!out || !x->data) return fail(BSIR_ERR_NULL, "elemwise_unary: null operand");
   bool ac;
   Operand a = make_operand(x, rank, sizes, &ac), none{nullptr, 0, 0, 0, 0};
+  int32_t rc = BSIR_OK;
+  if (!(ac && p.out_contig) && try_chain_route(false, fn, dtype, p, a, none, out, stream, &rc)) return rc;
   return launch_by_dtype<kOpUnary>("elemwise_unary", fn, dtype, p, a, ac, none, true, none, out, resolve_stream(stream));
 }
 
 namespace {
 
-// A float binary op with one operand broadcast along rows or columns (bias add, per-row scale ...): run it as a
-// two-instruction fused chain -- the kernel compiled for it reads 16-byte vectors where the indexed kernel reads
-// elements.  Same arithmetic (f32, one rounding), so the bits do not change.  false: not this pattern.
-bool try_broadcast_chain(int fn, int dtype, const Prepared &p, const Operand &a, const Operand &b, void *out, void *stream,
-                         int32_t *rc) {
+// Float unary / binary ops whose operands are row-strided views, or per-column / per-row vectors (bias add,
+// per-row scale, slices of a wider tensor): run them as a one- or two-instruction fused chain -- the kernel
+// compiled for it reads 16-byte vectors where the indexed kernel moves elements.  Same arithmetic (f32, one
+// rounding), so the bits do not change.  false: not such a pattern (the caller goes on as before).
+bool try_chain_route(bool binary, int fn, int dtype, const Prepared &p, const Operand &a, const Operand &b, void *out, void *stream,
+                     int32_t *rc) {
   if (dtype != BSIR_F32 && dtype != BSIR_F16 && dtype != BSIR_BF16) return false;
-  switch (fn) {
-    case BSIR_BINARY_ADD: case BSIR_BINARY_SUB: case BSIR_BINARY_MUL: case BSIR_BINARY_DIV: case BSIR_BINARY_DIVFHP:
-    case BSIR_BINARY_MAXF: case BSIR_BINARY_MINF: case BSIR_BINARY_MAXNUMF: case BSIR_BINARY_MINNUMF: case BSIR_BINARY_POWF: break;
-    default: return false;
+  if (binary) {
+    switch (fn) {
+      case BSIR_BINARY_ADD: case BSIR_BINARY_SUB: case BSIR_BINARY_MUL: case BSIR_BINARY_DIV: case BSIR_BINARY_DIVFHP:
+      case BSIR_BINARY_MAXF: case BSIR_BINARY_MINF: case BSIR_BINARY_MAXNUMF: case BSIR_BINARY_MINNUMF: case BSIR_BINARY_POWF: break;
+      default: return false;
+    }
+  } else {
+    switch (fn) {
+      case BSIR_UNARY_RELU: case BSIR_UNARY_SQRT: case BSIR_UNARY_RSQRT: case BSIR_UNARY_REC: case BSIR_UNARY_RECIPROCAL:
+      case BSIR_UNARY_TANH: case BSIR_UNARY_EXP: case BSIR_UNARY_LOG: case BSIR_UNARY_ABS: case BSIR_UNARY_CEIL: case BSIR_UNARY_FLOOR:
+      case BSIR_UNARY_NEGF: case BSIR_UNARY_ROUND: case BSIR_UNARY_SQUARE: case BSIR_UNARY_ERF: case BSIR_UNARY_SIN: case BSIR_UNARY_COS:
+      case BSIR_UNARY_EXP2: case BSIR_UNARY_LOG2: break;
+      default: return false;
+    }
   }
-  if (!p.out_contig) return false;
   const int64_t n0 = p.sh.n0, n1 = p.sh.n1, n2 = p.sh.n2, rows = n0 * n1, cols = n2;
+  const int eb = dtype_bytes(dtype);
   if (rows < 2 || cols < 8 || cols % 8) return false;   // ragged rows keep the indexed kernel
-  // 0 full, 1 row vector, 2 column vector, 3 scalar in memory, 4 immediate, -1 none of these
-  auto classify = [&](const Operand &o) {
-    if (!o.p) return 4;
+  // a [rows, cols] view with one row stride (in elements), 16-byte aligned rows; 0: not one
+  auto row_stride = [&](const void *ptr, int64_t s0, int64_t s1, int64_t s2) -> int64_t {
+    if (s2 != 1) return 0;
+    const int64_t rs = n1 == 1 ? (n0 == 1 ? cols : s0) : s1;
+    if (n0 != 1 && n1 != 1 && s0 != n1 * s1) return 0;
+    if (rs < cols || (rs * eb) % 16 != 0 || !aligned_to(ptr, 16)) return 0;
+    return rs;
+  };
+  // 0 full (stride in *rs), 1 row vector, 2 column vector, 3 scalar in memory, -1 none of these
+  auto classify = [&](const Operand &o, int64_t *rs) {
+    if (!o.p) return -1;
     const bool z0 = n0 == 1 || o.s0 == 0, z1 = n1 == 1 || o.s1 == 0, z2 = o.s2 == 0;
     if (z0 && z1 && z2) return 3;
-    if (o.s2 == 1 && (n1 == 1 || o.s1 == n2) && (n0 == 1 || o.s0 == n1 * n2)) return 0;
-    if (o.s2 == 1 && z0 && z1) return 1;
+    if (o.s2 == 1 && z0 && z1) return aligned_to(o.p, 16) ? 1 : -1;
     if (z2 && (n1 == 1 || o.s1 == 1) && (n0 == 1 || o.s0 == n1)) return 2;
-    return -1;
+    *rs = row_stride(o.p, o.s0, o.s1, o.s2);
+    return *rs ? 0 : -1;
   };
-  const int ka = classify(a), kb = classify(b);
-  if (ka < 0 || kb < 0 || (ka != 0 && kb != 0) || (ka == 0 && kb == 0) || ka == 4 || kb == 4) return false;
-  bsir_chain_operand ops[2] = {{a.p, cols, dtype, ka}, {b.p, cols, dtype, kb}};
-  bsir_chain_instr tape[2] = {{BSIR_CHAIN_LOAD, 0, BSIR_CHAIN_SRC_OPERAND, 0, 0.0f}, {BSIR_CHAIN_BINARY, fn, BSIR_CHAIN_SRC_OPERAND, 1, 0.0f}};
-  bsir_chain_output o{out, cols, dtype, -1};
-  *rc = bsir_fused_elementwise(rows, cols, 2, ops, 2, tape, 1, &o, stream);
+  const int64_t out_rs = row_stride(out, p.os[0], p.os[1], p.os[2]);
+  if (!out_rs) return false;
+  int64_t ra = cols, rb = cols;
+  const int ka = classify(a, &ra), kb = binary ? classify(b, &rb) : 0;
+  if (ka < 0 || kb < 0 || (ka != 0 && (!binary || kb != 0))) return false;
+  bsir_chain_operand ops[2] = {{a.p, ra, dtype, ka}, {b.p, rb, dtype, kb}};
+  bsir_chain_instr tape[2] = {{BSIR_CHAIN_LOAD, 0, BSIR_CHAIN_SRC_OPERAND, 0, 0.0f},
+                              {binary ? BSIR_CHAIN_BINARY : BSIR_CHAIN_UNARY, fn, BSIR_CHAIN_SRC_OPERAND, 1, 0.0f}};
+  bsir_chain_output o{out, out_rs, dtype, -1};
+  *rc = bsir_fused_elementwise(rows, cols, binary ? 2 : 1, ops, 2, tape, 1, &o, stream);
   return true;
 }
 
@@ -800,7 +830,7 @@ int32_t bsir_elemwise_binary(int32_t fn, int32_t dtype, int32_t rank, const int6
   bool ac, bc;
   Operand oa = make_operand(a, rank, sizes, &ac), ob = make_operand(b, rank, sizes, &bc), none{nullptr, 0, 0, 0, 0};
   int32_t rc = BSIR_OK;
-  if (!(ac && bc) && try_broadcast_chain(fn, dtype, p, oa, ob, out, stream, &rc)) return rc;
+  if (!(ac && bc && p.out_contig) && try_chain_route(true, fn, dtype, p, oa, ob, out, stream, &rc)) return rc;
   return launch_by_dtype<kOpBinary>("elemwise_binary", fn, dtype, p, oa, ac, ob, bc, none, out, resolve_stream(stream));
 }
 

@@ -381,3 +381,21 @@ def test_broadcast_binary_ops_run_as_compiled_chains(bsir):
     ragged = torch.randn(50, 1001, device="cuda")
     y = bsir.elemwise_binary("add", ragged, torch.randn(1001, device="cuda").view(1, -1).expand(50, 1001))
     assert y.shape == ragged.shape
+
+
+def test_row_strided_views_run_as_compiled_chains(bsir):
+    """Slices of wider tensors (row stride > row length, 16-byte aligned rows) as operands and as the result."""
+    big_a = torch.randn(200, 512, device="cuda").to(torch.float16)
+    big_b = torch.randn(200, 640, device="cuda").to(torch.float16)
+    a, b = big_a[:, 64:320], big_b[:, 128:384]                     # 256 columns each
+    out_big = torch.zeros(200, 400, device="cuda", dtype=torch.float16)
+    out = out_big[:, 8:264]
+    bsir.elemwise_binary("mul", a, b, out=out)
+    assert bsir.FusedChain.last_path() == "compiled"
+    assert_bits_equal(out.contiguous(), O.elemwise_binary("mul", O.F16, to_bits(a.contiguous()), to_bits(b.contiguous())), "strided mul")
+    assert out_big[:, :8].abs().sum().item() == 0 and out_big[:, 264:].abs().sum().item() == 0
+    y = bsir.elemwise_unary("exp", a)
+    assert bsir.FusedChain.last_path() == "compiled"
+    assert_bits_equal(y, O.elemwise_unary("exp", O.F16, to_bits(a.contiguous())), "strided exp")
+    odd = big_a[:, 3:259]                                          # rows not 16-byte aligned: the indexed kernel
+    assert_bits_equal(bsir.elemwise_unary("abs", odd), O.elemwise_unary("abs", O.F16, to_bits(odd.contiguous())), "unaligned abs")
