@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_rows_kernel(const typename 
   extern __shared__ unsigned long long keys[];
   const int64_t row = blockIdx.x;
   const auto *s = src + row * src_stride;
-  for (int i = threadIdx.x; i < npow2; i += kSortThreads) {
+  for (int i = threadIdx.x; i < npow2; i += blockDim.x) {
     unsigned long long k = ~0ull;                   // padding sorts last
     if (i < cols) {
       uint32_t o = sort_order<DT>(s[i]);
@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_rows_kernel(const typename 
   __syncthreads();
   for (int k = 2; k <= npow2; k <<= 1) {
     for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int t = threadIdx.x; t < npow2 / 2; t += kSortThreads) {
+      for (int t = threadIdx.x; t < npow2 / 2; t += blockDim.x) {
         const int lo = ((t & ~(j - 1)) << 1) | (t & (j - 1)), hi = lo | j;   // the pair this step compares
         const bool up = (lo & k) == 0;
         const unsigned long long a = keys[lo], b = keys[hi];
@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_rows_kernel(const typename 
       __syncthreads();
     }
   }
-  for (int i = threadIdx.x; i < cols; i += kSortThreads) {
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
     const uint32_t idx = static_cast<uint32_t>(keys[i]);
     if (dst_value) dst_value[row * val_stride + i] = s[idx];
     if (dst_index) dst_index[row * idx_stride + i] = static_cast<int32_t>(idx);
@@ -214,7 +214,10 @@ void launch_sort(const void *src, int64_t ss, void *dv, int64_t vs, int32_t *di,
     cudaFuncSetAttribute(sort_rows_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSortMaxLen * 8);
     attr_done = true;
   }
-  sort_rows_kernel<DT><<<static_cast<unsigned>(rows), kSortThreads, smem, st>>>(static_cast<const T *>(src), ss, static_cast<T *>(dv), vs, di, is,
+  // half a thread per padded element (each step compares pairs), within [32, 512]: short rows do not pay for
+  // idle warps at every barrier
+  int threads = npow2 / 2 < 32 ? 32 : npow2 / 2 > kSortThreads ? kSortThreads : npow2 / 2;
+  sort_rows_kernel<DT><<<static_cast<unsigned>(rows), threads, smem, st>>>(static_cast<const T *>(src), ss, static_cast<T *>(dv), vs, di, is,
                                                                                cols, npow2, descending);
 }
 
