@@ -217,6 +217,8 @@ __global__ void __launch_bounds__(256) reduce_last_vec_kernel(int64_t rows, int6
   using E = typename Acc<DT>::elem;
   constexpr int kPerVec = 16 / sizeof(E);
   __shared__ unsigned long long red[4][8];     // used only when a row has more than one warp (tpr >= 64)
+  pdl_launch_dependents();   // the finishing launch (or the next op) is scheduled while this one runs (launch_pdl) ...
+  pdl_wait();                // ... and global memory is touched only after the kernel ahead has completed
   const int rpc = 256 / tpr;
   const int sub = threadIdx.x / tpr, t = threadIdx.x % tpr;
   const int64_t row = static_cast<int64_t>(blockIdx.x) * rpc + sub;
@@ -271,6 +273,8 @@ __global__ void __launch_bounds__(256) reduce_first_vec_kernel(int64_t rows, int
   using E = typename Acc<DT>::elem;
   constexpr int kPerVec = 16 / sizeof(E);
   __shared__ unsigned long long red[7][32][kPerVec < 8 ? kPerVec : 8];
+  pdl_launch_dependents();   // the finishing launch (or the next op) is scheduled while this one runs (launch_pdl) ...
+  pdl_wait();                // ... and global memory is touched only after the kernel ahead has completed
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
   const int64_t cv = static_cast<int64_t>(blockIdx.x) * 32 + cx;
   const int slab = blockIdx.y;
@@ -325,6 +329,8 @@ template <int DT, int KIND>
 __global__ void __launch_bounds__(256) reduce_finish_kernel(int64_t nout, int nparts, int64_t out_stride, int64_t part_stride,
                                                             const unsigned long long *__restrict__ partials, void *__restrict__ dst) {
   using A = typename Acc<DT>::type;
+  pdl_launch_dependents();
+  pdl_wait();                // the partials of the launch ahead are complete from here on
   const int64_t o = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
   if (o >= nout) return;
   A a = identity<DT, KIND>();
@@ -368,11 +374,11 @@ void launch_reduce(bool last, int64_t rows, int64_t cols, const void *src, int64
       else parts = 1;
     }
     const dim3 grid(static_cast<unsigned>(row_groups), static_cast<unsigned>(parts));
-    reduce_last_vec_kernel<DT, KIND><<<grid, 256, 0, st>>>(rows, nvec, rs, src, parts > 1 ? part_vecs : nvec,
-                                                          static_cast<int>(parts), tpr, dst, partials);
+    launch_pdl(reduce_last_vec_kernel<DT, KIND>, grid, dim3(256), 0, st, rows, nvec, rs, src, parts > 1 ? part_vecs : nvec,
+               static_cast<int>(parts), tpr, dst, partials);
     if (parts > 1) {
-      reduce_finish_kernel<DT, KIND><<<static_cast<unsigned>(ceil_div(rows, 256)), 256, 0, st>>>(rows, static_cast<int>(parts), parts, 1,
-                                                                                                  partials, dst);
+      launch_pdl(reduce_finish_kernel<DT, KIND>, dim3(static_cast<unsigned>(ceil_div(rows, 256))), dim3(256), 0, st, rows,
+                 static_cast<int>(parts), static_cast<int64_t>(parts), static_cast<int64_t>(1), partials, dst);
       count_launch();
     }
     return;
@@ -396,11 +402,11 @@ void launch_reduce(bool last, int64_t rows, int64_t cols, const void *src, int64
       else slabs = 1;
     }
     const dim3 grid(static_cast<unsigned>(col_groups), static_cast<unsigned>(slabs));
-    reduce_first_vec_kernel<DT, KIND><<<grid, 256, 0, st>>>(rows, cvecs, rs, src, slabs > 1 ? slab_rows : rows,
-                                                           static_cast<int>(slabs), dst, partials);
+    launch_pdl(reduce_first_vec_kernel<DT, KIND>, grid, dim3(256), 0, st, rows, cvecs, rs, src, slabs > 1 ? slab_rows : rows,
+               static_cast<int>(slabs), dst, partials);
     if (slabs > 1) {
-      reduce_finish_kernel<DT, KIND><<<static_cast<unsigned>(ceil_div(cols, 256)), 256, 0, st>>>(cols, static_cast<int>(slabs), 1, cols,
-                                                                                                  partials, dst);
+      launch_pdl(reduce_finish_kernel<DT, KIND>, dim3(static_cast<unsigned>(ceil_div(cols, 256))), dim3(256), 0, st, cols,
+                 static_cast<int>(slabs), static_cast<int64_t>(1), cols, partials, dst);
       count_launch();
     }
     return;
