@@ -1007,15 +1007,18 @@ int32_t bsir_quant_per_token_i8(int32_t dtype, int32_t round_mode, int64_t rows,
   if (vec_ok) {
     const unsigned blocks = static_cast<unsigned>(ceil_div(rows, g.rpc));
     const unsigned threads = static_cast<unsigned>(g.tpr * g.rpc);
-    const bool exact = vpt == 8 && g.nvec == static_cast<int64_t>(g.tpr) * 8 && (dtype == BSIR_BF16 || dtype == BSIR_F16) &&
+    const bool exact = (vpt == 8 || vpt == 4) && g.nvec == static_cast<int64_t>(g.tpr) * vpt && (dtype == BSIR_BF16 || dtype == BSIR_F16) &&
                        (g.tpr == 32 || g.tpr == 64 || g.tpr == 128) && !env_int("BSIR_QUANT_GENERIC", 0);
     if (exact) {
-#define QUANT_EXACT(D, T) launch_pdl(quant_rows_kernel<D, 8, T>, dim3(blocks), dim3(threads), 0, st, g, x, x_row_stride, q, q_row_stride, scale, round_mode)
+#define QUANT_EXACT(D, V, T) launch_pdl(quant_rows_kernel<D, V, T>, dim3(blocks), dim3(threads), 0, st, g, x, x_row_stride, q, q_row_stride, scale, round_mode)
+#define QUANT_EXACT_T(D, V)                                                                        \
+  if (g.tpr == 32) QUANT_EXACT(D, V, 32); else if (g.tpr == 64) QUANT_EXACT(D, V, 64); else QUANT_EXACT(D, V, 128)
       if (dtype == BSIR_BF16) {
-        if (g.tpr == 32) QUANT_EXACT(BSIR_BF16, 32); else if (g.tpr == 64) QUANT_EXACT(BSIR_BF16, 64); else QUANT_EXACT(BSIR_BF16, 128);
+        if (vpt == 8) { QUANT_EXACT_T(BSIR_BF16, 8); } else { QUANT_EXACT_T(BSIR_BF16, 4); }
       } else {
-        if (g.tpr == 32) QUANT_EXACT(BSIR_F16, 32); else if (g.tpr == 64) QUANT_EXACT(BSIR_F16, 64); else QUANT_EXACT(BSIR_F16, 128);
+        if (vpt == 8) { QUANT_EXACT_T(BSIR_F16, 8); } else { QUANT_EXACT_T(BSIR_F16, 4); }
       }
+#undef QUANT_EXACT_T
 #undef QUANT_EXACT
     } else {
       DISPATCH_FLOAT_DT(dtype, DISPATCH_VPT(vpt, (launch_pdl(quant_rows_kernel<D, V, 0>, dim3(blocks), dim3(threads), 0, st, g, x,
