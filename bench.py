@@ -31,8 +31,8 @@ for _sub in ("ascendnpu-ir_b200", "oracle"):
 ROWS, COLS = 16384, 4096
 ALGO_BYTES = ROWS * COLS * 2 + ROWS * COLS + ROWS * 4   # read bf16 + write int8 + write f32 scales
 # dram__bytes_read.sum + dram__bytes_write.sum of one captured launch of the quantiser on this workload
-# (Nsight Compute, summary in profiles/quant_rows_kernel__bf16_16384x4096.txt): 134,285,568 read + 10,814,976 written.
-NCU_TRAFFIC_BYTES = 145_100_544
+# (Nsight Compute, summary in profiles/quant_rows_kernel__bf16_16384x4096.txt): 134,288,896 read + 10,988,288 written.
+NCU_TRAFFIC_BYTES = 145_277_184
 NCU_TRAFFIC_NOTE = ("reads equal the input exactly; 56 MB of the 67 MB output was still dirty in the 126 MB L2 when the "
                     "captured launch ended, so steady-state traffic per launch is 134.3 + 67.2 = 201.5 MB")
 METRIC = "per_token_int8_quant_hbm_gbps"
