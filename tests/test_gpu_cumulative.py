@@ -64,3 +64,14 @@ def test_cumulative_config_shape_and_validation(bsir):
     assert (c[:, -1] - 1).abs().max().item() < 1e-4
     with pytest.raises(bsir.BsirError):
         bsir.cumulative("sum", torch.zeros(4, 4, device="cuda", dtype=torch.bool))
+
+
+@pytest.mark.parametrize("dtype,cols", [(torch.bfloat16, 16384), (torch.float32, 8192), (torch.int8, 32768), (torch.int16, 16384)])
+@pytest.mark.parametrize("kind", ["sum", "max"])
+def test_first_axis_scan_of_wide_problems(bsir, dtype, cols, kind):
+    """Wide problems scanned down the rows (a thread per column; 16 bytes of columns per thread measured slower: fewer
+    loads in flight)."""
+    x = _data((37, cols), dtype, cols)
+    for reverse in (False, True):
+        y = bsir.cumulative(kind, x, dim=0, reverse=reverse)
+        assert_bits_equal(y, O.cumulative(kind, oracle_dtype(x), to_bits(x), axis=0, reverse=reverse), f"cum{kind} axis 0 {dtype} reverse {reverse}")
