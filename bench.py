@@ -267,6 +267,23 @@ def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters, only=None):
 
         rec("chain_softmax_bf16_4096x32768", 2 * rows * cols * 2, softmax_chain)
         del xs, ys
+    # the data-movement / scan ops beside the hot path, same measurement (algorithmic bytes = read + written once)
+    if want("transpose_bf16_8192x8192"):
+        xs = [torch.randn(8192, 8192, device="cuda").to(torch.bfloat16) for _ in range(2)]
+        ys = [torch.empty_like(x) for x in xs]
+        rec("transpose_bf16_8192x8192", 2 * 8192 * 8192 * 2, lambda i: bsir.transpose(xs[i % 2], out=ys[i % 2]))
+        del xs, ys
+    if want("cumsum_f32_32768x4096"):
+        xs = [torch.randn(32768, 4096, device="cuda") for _ in range(2)]
+        ys = [torch.empty_like(x) for x in xs]
+        rec("cumsum_f32_32768x4096", 2 * 32768 * 4096 * 4, lambda i: bsir.cumulative("sum", xs[i % 2], dim=1, out=ys[i % 2]),
+            note="sequential along the row, as the reference's loop: exact float sums")
+        del xs, ys
+    if want("sort_f32_1024x8192"):
+        xs = [torch.randn(1024, 8192, device="cuda") for _ in range(2)]
+        rec("sort_f32_1024x8192", 1024 * 8192 * (4 + 4 + 4), lambda i: bsir.sort(xs[i % 2], descending=True),
+            note="values + int32 indices; shared-memory bitonic network, not bandwidth-bound")
+        del xs
     for m in (16, 128, 4096):
         if not want(f"w8a8_m{m}"):
             continue
