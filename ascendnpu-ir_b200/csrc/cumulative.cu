@@ -10,9 +10,10 @@
 //   * axis 0: a thread owns a column (or the 16 bytes of columns of one vector) and walks down the rows,
 //     loads of the next rows in flight while it adds;
 //   * axis 1: a warp owns 32 rows; it brings a 32 x 128-byte tile into shared memory with coalesced
-//     16-byte loads (the next tile already requested), every lane scans its own row of the tile (row
-//     pitch 33 words: conflict-free), and the tile goes back with coalesced 16-byte stores.
+//     16-byte cp.async copies (a ring of four tiles in flight per warp), every lane scans its own row of the tile 16 bytes
+//     at a time (row pitch 36 words: conflict-free 16-byte accesses), and the tile goes back with coalesced 16-byte stores.
 #include <cstdint>
+#include <cstring>
 #include <type_traits>
 
 #include "common.cuh"
@@ -88,67 +89,85 @@ __global__ void __launch_bounds__(64) cum_first_seq_kernel(const T *__restrict__
 }
 
 // ------------------------------------------------------------------ axis 1: a warp per 32 rows, tiles of 128 bytes
-constexpr int kCumWarps = 4;
-// words per tile row in shared memory: odd for conflict-free row scans; even for 8-byte elements, which must
-// stay 8-byte aligned in every row
-template <typename T> constexpr int cum_pitch() { return sizeof(T) == 8 ? 34 : 33; }
+constexpr int kCumWarps = 2;   // two warps x four tiles of 4.5 KB: 36 KB of static shared memory
+// words per tile row in shared memory: 36, so that every row starts on a 16-byte boundary and the rows of the
+// eight lanes that share a 16-byte access phase start in different banks (lane * 36 mod 32 = 4 * lane)
+constexpr int kCumPitch = 36;
 
 template <typename T, int KIND, bool NANP>
 __global__ void __launch_bounds__(kCumWarps * 32) cum_last_kernel(const T *__restrict__ src, T *__restrict__ dst, int64_t rows,
                                                                    int64_t cols, int64_t ss, int64_t ds, int reverse) {
   using A = typename CumAcc<T>::type;
   constexpr int EPT = 128 / sizeof(T);              // elements of a tile row
-  constexpr int kCumPitch = cum_pitch<T>();
-  __shared__ __align__(16) uint32_t sm[kCumWarps][32 * kCumPitch];
+  constexpr int EPV = 16 / sizeof(T);               // elements of a 16-byte chunk
+  constexpr int kDepth = 4;                          // tiles in flight per warp (cp.async ring)
+  __shared__ __align__(16) uint32_t sm[kCumWarps][kDepth][32 * kCumPitch];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  uint32_t *tile = sm[warp];
   const int64_t row0 = (static_cast<int64_t>(blockIdx.x) * kCumWarps + warp) * 32;
   if (row0 >= rows) return;
   const int64_t ntiles = cols / EPT;                // the host sends only whole tiles here
   const char *sb = reinterpret_cast<const char *>(src);
   char *db = reinterpret_cast<char *>(dst);
 
-  auto fetch = [&](int64_t t, Vec16 (&buf)[8]) {    // lane -> (row i*4 + lane/8, vector lane%8) of tile t
+  // lane -> (row i*4 + lane/8, 16-byte chunk lane%8) of a tile; one commit group per tile, empty past the end
+  auto fetch = [&](int64_t it) {
+    if (it < ntiles) {
+      const int64_t t = reverse ? ntiles - 1 - it : it;
+      uint32_t *tile = sm[warp][it % kDepth];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int64_t r = row0 + i * 4 + lane / 8;
-      if (r < rows) buf[i] = ld_stream(sb + (r * ss + t * EPT) * sizeof(T) + (lane % 8) * 16);
+      for (int i = 0; i < 8; ++i) {
+        const int64_t r = row0 + i * 4 + lane / 8;
+        if (r < rows) {
+          const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(tile + (i * 4 + lane / 8) * kCumPitch + (lane % 8) * 4));
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(sb + (r * ss + t * EPT) * sizeof(T) + (lane % 8) * 16) : "memory");
+        }
+      }
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  Vec16 cur[8], nxt[8];
-  fetch(reverse ? ntiles - 1 : 0, cur);
+  for (int64_t it = 0; it < kDepth - 1; ++it) fetch(it);
   A acc{};
   for (int64_t it = 0; it < ntiles; ++it) {
     const int64_t t = reverse ? ntiles - 1 - it : it;
-    if (it + 1 < ntiles) fetch(reverse ? t - 1 : t + 1, nxt);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      uint32_t *w = tile + (i * 4 + lane / 8) * kCumPitch + (lane % 8) * 4;
-      w[0] = cur[i].w[0]; w[1] = cur[i].w[1]; w[2] = cur[i].w[2]; w[3] = cur[i].w[3];
-    }
+    uint32_t *tile = sm[warp][it % kDepth];
+    fetch(it + kDepth - 1);                           // its buffer was drained in the previous iteration
+    asm volatile("cp.async.wait_group %0;" ::"n"(kDepth - 1) : "memory");
     __syncwarp();
-    // lane = row: scan the 128 bytes of this row, in place
-    T *mine = reinterpret_cast<T *>(tile + lane * kCumPitch);
+    // lane = row: scan the 128 bytes of this row in place, 16 bytes at a time
     if (row0 + lane < rows) {
-#pragma unroll 8
-      for (int e = 0; e < EPT; ++e) {
-        const int j = reverse ? EPT - 1 - e : e;
-        acc = cum_step<T, KIND, NANP>(acc, mine[j], it == 0 && e == 0);
-        mine[j] = cum_narrow<T>(acc);
-      }
+      uint4 *mine = reinterpret_cast<uint4 *>(tile + lane * kCumPitch);
+      auto scan = [&](auto rev_tag) {                 // the direction is a compile-time constant inside
+        constexpr bool REV = decltype(rev_tag)::value;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int cc = REV ? 7 - c : c;
+          const uint4 raw = mine[cc];
+          T x[EPV];
+          memcpy(x, &raw, 16);
+#pragma unroll
+          for (int e = 0; e < EPV; ++e) {
+            const int j = REV ? EPV - 1 - e : e;
+            acc = cum_step<T, KIND, NANP>(acc, x[j], it == 0 && c == 0 && e == 0);
+            x[j] = cum_narrow<T>(acc);
+          }
+          uint4 res;
+          memcpy(&res, x, 16);
+          mine[cc] = res;
+        }
+      };
+      if (reverse) scan(std::true_type{});
+      else scan(std::false_type{});
     }
     __syncwarp();
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int64_t r = row0 + i * 4 + lane / 8;
-      const uint32_t *w = tile + (i * 4 + lane / 8) * kCumPitch + (lane % 8) * 4;
+      const uint4 w = *reinterpret_cast<const uint4 *>(tile + (i * 4 + lane / 8) * kCumPitch + (lane % 8) * 4);
       Vec16 o;
-      o.w[0] = w[0]; o.w[1] = w[1]; o.w[2] = w[2]; o.w[3] = w[3];
+      o.w[0] = w.x; o.w[1] = w.y; o.w[2] = w.z; o.w[3] = w.w;
       if (r < rows) st_stream(db + (r * ds + t * EPT) * sizeof(T) + (lane % 8) * 16, o);
     }
-    __syncwarp();
-#pragma unroll
-    for (int i = 0; i < 8; ++i) cur[i] = nxt[i];
+    __syncwarp();                                     // the buffer may be refilled from the next iteration on
   }
 }
 
