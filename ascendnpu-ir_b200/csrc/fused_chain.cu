@@ -406,11 +406,8 @@ uint32_t binary_code(int fn) {
 
 template <bool VEC, int G>
 void launch_chain(const ChainParams &p, unsigned blocks, size_t smem, cudaStream_t st) {
-  static bool attr_done = false;   // one flag per instantiation
-  if (!attr_done) {
+  if (smem > 48 * 1024)   // the attribute is per device: set whenever it is needed, not once per process
     cudaFuncSetAttribute(fused_chain_kernel<VEC, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    attr_done = true;
-  }
   fused_chain_kernel<VEC, G><<<blocks, kChainThreads, smem, st>>>(p);
 }
 

@@ -13,6 +13,7 @@
 #include <map>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "common.cuh"
 
@@ -42,12 +43,19 @@ int32_t check_launch(const char *what) {
 }
 
 static constexpr int kMaxDevices = 64;
+struct ScratchBlock {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+};
 struct PerDevice {
   std::once_flag once;
   DeviceInfo info;
   std::mutex mu;
-  void *workspace = nullptr;
-  size_t workspace_bytes = 0;
+  // Library-owned scratch: one block per stream that ever asked for one, so that calls on different streams never
+  // share counters or partial results.  A block that became too small is replaced and kept in `retired` until
+  // bsir_release_workspace(): a launch already enqueued may still be using it, and nothing here waits for the GPU.
+  std::map<cudaStream_t, ScratchBlock> scratch;
+  std::vector<void *> retired;
   int *error_word = nullptr;
 };
 static PerDevice g_dev[kMaxDevices];
@@ -71,30 +79,33 @@ const DeviceInfo &device_info() {
   return p ? p->info : none;
 }
 
+// Scratch of at least `bytes` for work enqueued on `stream`.  Steady state: a map lookup, no CUDA call.  When the
+// stream has no block yet, or one too small, a new one is allocated (cudaMalloc: not allowed while a stream capture
+// is under way -- size the block beforehand with bsir_reserve_workspace or a warm-up call) and cleared on `stream`,
+// which orders the clearing before the caller's kernels without the host waiting.
 void *device_workspace(size_t bytes, cudaStream_t stream) {
   PerDevice *p = current();
   if (!p) { fail(BSIR_ERR_WORKSPACE, "no current CUDA device"); return nullptr; }
   std::lock_guard<std::mutex> lock(p->mu);
-  if (p->workspace_bytes >= bytes && p->workspace) return p->workspace;
-  size_t want = bytes < (size_t(1) << 20) ? (size_t(1) << 20) : bytes;
-  // Growing: earlier launches may still use the old block, so drain before freeing it.
-  if (p->workspace) {
-    cudaDeviceSynchronize();
-    cudaFree(p->workspace);
-    p->workspace = nullptr;
-    p->workspace_bytes = 0;
-  }
+  ScratchBlock &b = p->scratch[stream];
+  if (b.ptr && b.bytes >= bytes) return b.ptr;
+  size_t want = size_t(1) << 20;
+  while (want < bytes) want <<= 1;
   void *q = nullptr;
   if (cudaMalloc(&q, want) != cudaSuccess) {
     cudaGetLastError();
     fail(BSIR_ERR_WORKSPACE, "cannot allocate %zu bytes of device scratch", want);
     return nullptr;
   }
-  cudaMemsetAsync(q, 0, want, stream);
-  if (stream != nullptr) cudaStreamSynchronize(stream);  // other streams may use it next
-  else cudaDeviceSynchronize();
-  p->workspace = q;
-  p->workspace_bytes = want;
+  if (cudaMemsetAsync(q, 0, want, stream) != cudaSuccess) {
+    cudaGetLastError();
+    cudaFree(q);
+    fail(BSIR_ERR_WORKSPACE, "cannot clear %zu bytes of device scratch", want);
+    return nullptr;
+  }
+  if (b.ptr) p->retired.push_back(b.ptr);
+  b.ptr = q;
+  b.bytes = want;
   return q;
 }
 
@@ -193,12 +204,20 @@ int32_t bsir_release_workspace(void) {
   PerDevice *p = current();
   if (!p) return fail(BSIR_ERR_WORKSPACE, "no current CUDA device");
   std::lock_guard<std::mutex> lock(p->mu);
-  if (p->workspace) {
-    cudaDeviceSynchronize();
-    cudaFree(p->workspace);
-    p->workspace = nullptr;
-    p->workspace_bytes = 0;
-  }
+  if (!p->scratch.empty() || !p->retired.empty()) cudaDeviceSynchronize();   // nothing enqueued may still use a block
+  for (auto &kv : p->scratch)
+    if (kv.second.ptr) cudaFree(kv.second.ptr);
+  for (void *q : p->retired) cudaFree(q);
+  p->scratch.clear();
+  p->retired.clear();
+  return BSIR_OK;
+}
+
+int32_t bsir_reserve_workspace(int64_t bytes, void *stream) {
+  clear_error();
+  if (bytes < 0) return fail(BSIR_ERR_SHAPE, "bsir_reserve_workspace: %lld bytes", (long long)bytes);
+  if (!device_workspace(static_cast<size_t>(bytes), resolve_stream(stream))) return BSIR_ERR_WORKSPACE;
+  if (!device_error_word()) return fail(BSIR_ERR_WORKSPACE, "bsir_reserve_workspace: no device error word");
   return BSIR_OK;
 }
 

@@ -1232,7 +1232,9 @@ int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie_break_le
       std::getenv("BSIR_RWI_NO_STREAM") == nullptr) {
     const size_t need = rwi_scratch_bytes(rows, p.nseg);
     char *ws = static_cast<char *>(workspace);
-    if (ws && (static_cast<size_t>(workspace_bytes) < need || !aligned_to(ws, 16))) ws = nullptr;
+    if (ws && (static_cast<size_t>(workspace_bytes) < need || !aligned_to(ws, 16)))
+      return fail(BSIR_ERR_WORKSPACE, "reduce_with_index: the workspace given is %s (need %zu bytes, 16-byte aligned; "
+                  "bsir_reduce_with_index_workspace_bytes gives the size)", aligned_to(ws, 16) ? "too small" : "misaligned", need);
     if (!ws) ws = static_cast<char *>(device_workspace(need, st));
     if (!ws) return BSIR_ERR_WORKSPACE;
     unsigned *cnt = reinterpret_cast<unsigned *>(ws);
@@ -1253,7 +1255,9 @@ int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie_break_le
   if (p.nseg > 1) {
     const size_t need = rwi_scratch_bytes(rows, p.nseg);
     char *ws = static_cast<char *>(workspace);
-    if (ws && (static_cast<size_t>(workspace_bytes) < need || !aligned_to(ws, 16))) ws = nullptr;  // too small: use ours
+    if (ws && (static_cast<size_t>(workspace_bytes) < need || !aligned_to(ws, 16)))
+      return fail(BSIR_ERR_WORKSPACE, "reduce_with_index: the workspace given is %s (need %zu bytes, 16-byte aligned; "
+                  "bsir_reduce_with_index_workspace_bytes gives the size)", aligned_to(ws, 16) ? "too small" : "misaligned", need);
     if (!ws) ws = static_cast<char *>(device_workspace(need, st));
     if (!ws) return BSIR_ERR_WORKSPACE;
     counters = reinterpret_cast<unsigned *>(ws);
@@ -1329,8 +1333,11 @@ int32_t static_scratch(void **out) {
 // no cudaMalloc, cudaFree or other allocating call, on any path.
 //
 // Limits: rows <= 4096 and rows x segments <= 31744 partial results (the segment count is what
-// bsir_reduce_with_index would choose; the 256 x 152064 benchmark shape needs 2560).  Larger
-// problems are refused with BSIR_ERR_WORKSPACE and nothing is enqueued.
+// bsir_reduce_with_index would choose).  Larger problems are refused with BSIR_ERR_WORKSPACE and
+// nothing is enqueued.  Kernels: the same ones bsir_reduce_with_index picks -- the streaming kernel
+// for long rows (the 256 x 152064 shape: 2 parts per row), the segmented kernel otherwise, the
+// one-CTA-per-row kernel for unaligned rows -- except that rows of at most 64 vectors also take the
+// segmented kernel; one small memset ahead of the launch clears the row counters.
 //
 // The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
 // that device current); make that first call before any stream capture begins on the device.
@@ -1378,14 +1385,28 @@ extern "C" int32_t bsir_reduce_with_index_static(int32_t kind, int32_t dtype, in
     return check_launch("reduce_with_index_static");
   }
   p.nvec = cols / per_vec;
+  unsigned *counters = reinterpret_cast<unsigned *>(scratch);
+  Partial *partials = reinterpret_cast<Partial *>(static_cast<unsigned char *>(scratch) + kStaticCounterBytes);
+  // long rows: the streaming kernel bsir_reduce_with_index uses for them, whenever its partial results fit the array
+  if (plan_stream(rows, p.nvec, device_info().sm_count, &p.seg_vecs, &p.nseg) && std::getenv("BSIR_RWI_NO_STREAM") == nullptr &&
+      static_cast<size_t>(rows) * static_cast<size_t>(p.nseg) <= kStaticMaxPartials) {
+    if (cudaMemsetAsync(counters, 0, static_cast<size_t>(rows) * sizeof(unsigned), st) != cudaSuccess)
+      return check_launch("reduce_with_index_static (clearing the counters)");
+    const dim3 grid1(static_cast<unsigned>(p.nseg), static_cast<unsigned>(rows));
+#define LS(D)                                                                                                    \
+  if (is_max) rwi_stream_kernel<D, true><<<grid1, 256, 0, st>>>(p, src, dst_value, dst_index, counters, partials); \
+  else rwi_stream_kernel<D, false><<<grid1, 256, 0, st>>>(p, src, dst_value, dst_index, counters, partials);
+    if (dtype == BSIR_F32) { LS(BSIR_F32) } else if (dtype == BSIR_F16) { LS(BSIR_F16) } else { LS(BSIR_BF16) }
+#undef LS
+    count_launch();
+    return check_launch("reduce_with_index_static");
+  }
   int vpt = 1;
   plan_segments(rows, p.nvec, device_info().sm_count, &p.seg_vecs, &p.nseg, &vpt);
   if (static_cast<size_t>(rows) * static_cast<size_t>(p.nseg) > kStaticMaxPartials)
     return fail(BSIR_ERR_WORKSPACE,
                 "reduce_with_index_static: %lld rows x %d segments exceed the fixed scratch (at most %zu partial results)",
                 (long long)rows, p.nseg, kStaticMaxPartials);
-  unsigned *counters = reinterpret_cast<unsigned *>(scratch);
-  Partial *partials = reinterpret_cast<Partial *>(static_cast<unsigned char *>(scratch) + kStaticCounterBytes);
   if (p.nseg > 1) {
     // the counters must start at zero whatever an earlier (possibly failed) call left behind
     if (cudaMemsetAsync(counters, 0, static_cast<size_t>(rows) * sizeof(unsigned), st) != cudaSuccess)

@@ -1,11 +1,17 @@
 // sort.cu -- hivm.hir.vsort over the last axis: sorted values and the source index of each
 // (bishengir/include/bishengir/Dialect/HIVM/IR/HIVMVectorOps.td:2222-2283).
 //
-// Order: ascending (or descending) by value; equal values keep their source order (stable), -0 and +0 compare
-// equal, NaN sorts after every number when ascending and before every number when descending.  A row becomes
-// 64-bit keys  order(value) << 32 | index  (order() maps the element type to unsigned integers that compare
-// like the values; descending complements it), so one integer comparison decides value and tie at once and the
-// bitonic network -- not stable by itself -- gives a stable result.  A CTA sorts one row in shared memory
+// The result is the one the reference's lowering of hfusion.sort produces: n-1 bubble passes of n-1 adjacent
+// compare-and-swaps on `cmpf ugt` (ascending) / `cmpf ult` (descending), `cmpi sgt` / `slt` for integers
+// (bishengir/lib/Dialect/HFusion/Transforms/DecomposeOpInterfaceImpl.cpp:742-838).  In closed form: equal values
+// keep their source order (stable; -0 and +0 are equal); a pair holding a NaN always swaps, which moves every NaN
+// one place to the left per pass and carries the one at the front to the end, so a NaN that starts at position p
+// ends at (p + 1) mod n whatever the direction; the numbers fill the other places in order.
+//
+// A row becomes 64-bit keys  order(value) << 32 | index  (order() maps the element type to unsigned integers
+// that compare like the values; descending complements it; NaN is the largest key in both directions), so one
+// integer comparison decides value and tie at once and the bitonic network -- not stable by itself -- gives a
+// stable result with the NaNs at the end in source order; the write-out then moves them to their places.  A CTA sorts one row in shared memory
 // (rows of up to 8192 elements: 64 KB of keys); longer rows keep their keys in device scratch and run the wide
 // steps of the network on global memory.  The values are read back from the source by index, so their bits
 // (the sign of a zero, the payload of a NaN) are the source's.
@@ -37,11 +43,53 @@ __device__ __forceinline__ uint32_t sort_order(typename SortElem<DT>::type v) {
     if constexpr (DT == BSIR_F32) f = v;
     else if constexpr (DT == BSIR_F16) f = __half2float(__ushort_as_half(v));
     else f = __uint_as_float(static_cast<uint32_t>(v) << 16);
-    if (f != f) return 0xffffffffu;                 // NaN: after every number
+    if (f != f) return 0xffffffffu;                 // NaN: no number maps here (+inf is 0xff800000)
     uint32_t b = __float_as_uint(f);
     if (b == 0x80000000u) b = 0u;                   // -0 ties with +0
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
   }
+}
+
+template <int DT> constexpr bool kSortFloat = DT == BSIR_F32 || DT == BSIR_F16 || DT == BSIR_BF16;
+
+template <int DT>
+__device__ __forceinline__ unsigned long long sort_key(typename SortElem<DT>::type v, int64_t pos, int descending) {
+  uint32_t o = sort_order<DT>(v);
+  if (descending && !(kSortFloat<DT> && o == 0xffffffffu)) o = ~o;      // a NaN key stays the largest
+  return (static_cast<unsigned long long>(o) << 32) | static_cast<uint32_t>(pos);
+}
+
+__device__ __forceinline__ bool sort_key_is_nan(unsigned long long k) { return (k >> 32) == 0xffffffffull && k != ~0ull; }
+
+// Where element i of the sorted keys (numbers first, then the row's `nan` NaNs in source order) goes in a row of
+// `cols`.  The NaN from source position p goes to (p + 1) mod cols; number r takes the r-th place no NaN took:
+// with the NaN places T[0] < T[1] < ... ascending, that is r + #{j : T[j] - j <= r}.
+__device__ __forceinline__ int64_t sort_place(const unsigned long long *keys, int64_t i, int64_t cols, int64_t nan) {
+  const int64_t numbers = cols - nan;
+  if (i >= numbers) {
+    const int64_t p = static_cast<uint32_t>(keys[i]);
+    return p + 1 == cols ? 0 : p + 1;
+  }
+  const bool wrap = static_cast<uint32_t>(keys[cols - 1]) == cols - 1;   // the last NaN sits at the row's end
+  int64_t lo = 0, hi = nan;                                             // first j with T[j] - j > i
+  while (lo < hi) {
+    const int64_t j = (lo + hi) >> 1;
+    const int64_t t = wrap ? (j == 0 ? 0 : static_cast<int64_t>(static_cast<uint32_t>(keys[numbers + j - 1])) + 1)
+                           : static_cast<int64_t>(static_cast<uint32_t>(keys[numbers + j])) + 1;
+    if (t - j <= i) lo = j + 1; else hi = j;
+  }
+  return i + lo;
+}
+
+// number of NaN keys at the end of a sorted row (keys[0 .. cols))
+__device__ __forceinline__ int64_t sort_count_nan(const unsigned long long *keys, int64_t cols) {
+  if (!sort_key_is_nan(keys[cols - 1])) return 0;
+  int64_t lo = 0, hi = cols - 1;                                        // first NaN key
+  while (lo < hi) {
+    const int64_t m = (lo + hi) >> 1;
+    if (sort_key_is_nan(keys[m])) hi = m; else lo = m + 1;
+  }
+  return cols - lo;
 }
 
 template <int DT>
@@ -54,11 +102,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_rows_kernel(const typename 
   const auto *s = src + row * src_stride;
   for (int i = threadIdx.x; i < npow2; i += blockDim.x) {
     unsigned long long k = ~0ull;                   // padding sorts last
-    if (i < cols) {
-      uint32_t o = sort_order<DT>(s[i]);
-      if (descending) o = ~o;
-      k = (static_cast<unsigned long long>(o) << 32) | static_cast<uint32_t>(i);
-    }
+    if (i < cols) k = sort_key<DT>(s[i], i, descending);
     keys[i] = k;
   }
   __syncthreads();
@@ -76,10 +120,13 @@ __global__ void __launch_bounds__(kSortThreads) sort_rows_kernel(const typename 
       __syncthreads();
     }
   }
+  int64_t nan = 0;
+  if constexpr (kSortFloat<DT>) nan = sort_count_nan(keys, cols);
   for (int i = threadIdx.x; i < cols; i += blockDim.x) {
     const uint32_t idx = static_cast<uint32_t>(keys[i]);
-    if (dst_value) dst_value[row * val_stride + i] = s[idx];
-    if (dst_index) dst_index[row * idx_stride + i] = static_cast<int32_t>(idx);
+    const int64_t at = nan ? sort_place(keys, i, cols, nan) : i;
+    if (dst_value) dst_value[row * val_stride + at] = s[idx];
+    if (dst_index) dst_index[row * idx_stride + at] = static_cast<int32_t>(idx);
   }
 }
 
@@ -103,11 +150,7 @@ __global__ void __launch_bounds__(kSortThreads) sort_chunks_kernel(const typenam
     for (int i = threadIdx.x; i < kSortMaxLen; i += kSortThreads) {
       const int64_t pos = base + i;
       unsigned long long k = ~0ull;
-      if (pos < cols) {
-        uint32_t o = sort_order<DT>(s[pos]);
-        if (descending) o = ~o;
-        k = (static_cast<unsigned long long>(o) << 32) | static_cast<uint32_t>(pos);
-      }
+      if (pos < cols) k = sort_key<DT>(s[pos], pos, descending);
       keys[i] = k;
     }
   } else {
@@ -153,9 +196,15 @@ __global__ void __launch_bounds__(256) sort_emit_kernel(const typename SortElem<
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= cols) return;
   const int64_t row = blockIdx.y;
-  const uint32_t idx = static_cast<uint32_t>(keys_g[row * npow2 + i]);
-  if (dst_value) dst_value[row * val_stride + i] = src[row * src_stride + idx];
-  if (dst_index) dst_index[row * idx_stride + i] = static_cast<int32_t>(idx);
+  const unsigned long long *keys = keys_g + row * npow2;
+  const uint32_t idx = static_cast<uint32_t>(keys[i]);
+  int64_t at = i;
+  if constexpr (kSortFloat<DT>) {
+    const int64_t nan = sort_count_nan(keys, cols);          // one load when the row has no NaN
+    if (nan) at = sort_place(keys, i, cols, nan);
+  }
+  if (dst_value) dst_value[row * val_stride + at] = src[row * src_stride + idx];
+  if (dst_index) dst_index[row * idx_stride + at] = static_cast<int32_t>(idx);
 }
 
 // rows per pass such that the keys fit `budget` bytes of scratch
@@ -175,11 +224,8 @@ int32_t launch_sort_long(const void *src, int64_t ss, void *dv, int64_t vs, int3
   char *ws = static_cast<char *>(device_workspace(kScratchCounterBytes + static_cast<size_t>(rows_per_pass * row_bytes), st));
   if (!ws) return BSIR_ERR_WORKSPACE;
   unsigned long long *keys = reinterpret_cast<unsigned long long *>(ws + kScratchCounterBytes);
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaFuncSetAttribute(sort_chunks_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSortMaxLen * 8);
-    attr_done = true;
-  }
+  // the attribute belongs to the current device's copy of the kernel: set it on every call, not once per process
+  cudaFuncSetAttribute(sort_chunks_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSortMaxLen * 8);
   const T *s = static_cast<const T *>(src);
   T *d = static_cast<T *>(dv);
   const int n = static_cast<int>(npow2);
@@ -209,11 +255,8 @@ void launch_sort(const void *src, int64_t ss, void *dv, int64_t vs, int32_t *di,
   int npow2 = 2;
   while (npow2 < cols) npow2 <<= 1;
   const size_t smem = static_cast<size_t>(npow2) * sizeof(unsigned long long);
-  static bool attr_done = false;   // per instantiation
-  if (!attr_done) {
+  if (smem > 48 * 1024)   // per device, so on every such call rather than once per process
     cudaFuncSetAttribute(sort_rows_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSortMaxLen * 8);
-    attr_done = true;
-  }
   // half a thread per padded element (each step compares pairs), within [32, 512]: short rows do not pay for
   // idle warps at every barrier
   int threads = npow2 / 2 < 32 ? 32 : npow2 / 2 > kSortThreads ? kSortThreads : npow2 / 2;

@@ -284,9 +284,12 @@ BSIR_API int64_t bsir_reduce_with_index_workspace_bytes(int64_t rows, int64_t co
 /* hfusion.reduce_with_index over the last axis (HFusionStructuredOps.td:69-137,
  * region HFusionOps.cpp:1506-1595).  Ties keep the lowest index when
  * tie_break_left != 0, the highest otherwise.  dst_index is int32.
- * `workspace` may be NULL: the library then uses its own per-device scratch
- * (created on first use).  A caller-provided workspace must be zero-filled
- * once before its first use; every call leaves it zero-filled again. */
+ * `workspace` may be NULL: the library then uses its own scratch (see "library-owned
+ * scratch" below).  A caller-provided workspace must be 16-byte aligned, at least
+ * bsir_reduce_with_index_workspace_bytes() long and zero-filled once before its first use;
+ * every call leaves it zero-filled again.  One that is too small or misaligned is refused
+ * with BSIR_ERR_WORKSPACE (the library never swaps in its own scratch behind the caller's
+ * back), and two calls that may overlap on the GPU need a workspace each. */
 BSIR_API int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie_break_left,
                                         int32_t nan_mode, int64_t rows, int64_t cols,
                                         const void *src, int64_t src_row_stride, void *dst_value,
@@ -497,7 +500,21 @@ BSIR_API int32_t bsir_launch(const char *name, uint32_t block_dim, void **args, 
 BSIR_API int32_t bsir_device_error(void);
 /* Number of kernel launches this library has enqueued in this process. */
 BSIR_API int64_t bsir_launch_count(void);
-/* Frees the library-owned per-device scratch of the current device. */
+/* Library-owned scratch.  Ops that need global memory beyond their operands (argmax over several
+ * CTAs per row, split reductions, rows too long for one CTA, long sorts) and were given no workspace
+ * take it from a block the library keeps PER (device, stream): calls on different streams never share
+ * counters or partial results; calls on one stream are ordered by the stream.  A stream's block is
+ * created, or replaced by a larger one, inside the first call that needs it (cudaMalloc + a clearing
+ * memset enqueued on that stream; no host-side wait, and an outgrown block is kept, not freed, because
+ * enqueued work may still use it).  That allocation is not allowed during stream capture: before
+ * capturing, run the ops once on the capturing stream or call bsir_reserve_workspace.  The per-row
+ * counters in a block are reset by the kernels themselves; they stay non-zero only if a kernel died,
+ * which also ends the CUDA context.
+ *
+ * bsir_reserve_workspace: makes the block of `stream` (NULL = the thread's stream) at least `bytes`
+ * long and creates the device error word, so that later calls allocate nothing.
+ * bsir_release_workspace: waits for the device, then frees every block of the current device. */
+BSIR_API int32_t bsir_reserve_workspace(int64_t bytes, void *stream);
 BSIR_API int32_t bsir_release_workspace(void);
 
 /* ------------------------------------------------------------------------ */

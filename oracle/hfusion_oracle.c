@@ -809,6 +809,58 @@ ORC_API int orc_reduce_with_index(int kind, int dt, int tie_break_left, int nan_
   return 0;
 }
 
+/* hfusion.sort / hivm.hir.vsort over the last axis, as hfusion-decompose lowers it
+ * (bishengir/lib/Dialect/HFusion/Transforms/DecomposeOpInterfaceImpl.cpp:742-838; the IR the lit test
+ * test/Dialect/HFusion/test_sort.mlir:28-60 checks; runner goldens test_sort_2d_asc.mlir:16-19,
+ * test_sort_3d_des.mlir:14-15): a bubble sort of exactly n-1 passes of n-1 adjacent compare-and-swaps, the
+ * swap taken when  cmpf ugt lhs, rhs  (ascending) or  cmpf ult  (descending) -- unordered predicates, so a pair
+ * that holds a NaN always swaps -- and  cmpi sgt / slt  for integers.  f16 / bf16 compare as f32
+ * (LegalizeBF16.cpp:321).  This function runs those loops literally (O(n^2) per row); dst_index carries the
+ * source position of every element along.  Consequences, used by the closed form in oracle.py and by the CUDA
+ * kernel: equal keys never swap (stable, -0 = +0); every NaN moves one place to the left per pass, the one at
+ * position 0 being carried to the end, so a NaN that starts at p ends at (p + 1) mod n in either direction, and
+ * the other elements end up stably sorted in the remaining places. */
+ORC_API int orc_sort_last_axis(int dt, int descending, const void *src, int64_t rows, int64_t cols,
+                               void *dst_value, int32_t *dst_index) {
+  if (dt == ORC_I64 || dt >= ORC_U8) return -1;
+  ORC_PAR_FOR
+  for (int64_t r = 0; r < rows; r++) {
+    int32_t *ix = dst_index + r * cols;
+    for (int64_t j = 0; j < cols; j++) ix[j] = (int32_t)j;
+    if (is_float(dt)) {
+      float *v = (float *)malloc(sizeof(float) * (size_t)(cols ? cols : 1));
+      for (int64_t j = 0; j < cols; j++) v[j] = load_f(dt, src, r * cols + j);
+      for (int64_t pass = 0; pass + 1 < cols; pass++)
+        for (int64_t j = 0; j + 1 < cols; j++) {
+          float a = v[j], b = v[j + 1];
+          int swap = descending ? !(a >= b) : !(a <= b);   /* ult / ugt: true when unordered */
+          if (swap) {
+            v[j] = b; v[j + 1] = a;
+            int32_t t = ix[j]; ix[j] = ix[j + 1]; ix[j + 1] = t;
+          }
+        }
+      free(v);
+    } else {
+      int64_t *v = (int64_t *)malloc(sizeof(int64_t) * (size_t)(cols ? cols : 1));
+      for (int64_t j = 0; j < cols; j++) v[j] = load_i(dt, src, r * cols + j);
+      for (int64_t pass = 0; pass + 1 < cols; pass++)
+        for (int64_t j = 0; j + 1 < cols; j++) {
+          int64_t a = v[j], b = v[j + 1];
+          if (descending ? a < b : a > b) {
+            v[j] = b; v[j + 1] = a;
+            int32_t t = ix[j]; ix[j] = ix[j + 1]; ix[j + 1] = t;
+          }
+        }
+      free(v);
+    }
+    /* the values travel as their own bits (sign of a zero, NaN payload): tensor.insert moves the element */
+    int es = dtype_size(dt);
+    for (int64_t j = 0; j < cols; j++)
+      memcpy((char *)dst_value + (r * cols + j) * es, (const char *)src + (r * cols + ix[j]) * es, (size_t)es);
+  }
+  return 0;
+}
+
 /* ----------------------------------------------------------- fused patterns */
 /* RMSNorm, LAST_AXIS_PBR fusion unit
  * (test/bishengir-compile/hfusion/compile-rms-norm-fp16-split-n.mlir:13-71):
@@ -1046,5 +1098,37 @@ ORC_API int64_t orc_check_recip_division(float s, int steps) {
       if (nearbyintf(q) != nearbyintf(t)) bad++;
     }
   }
+  return bad;
+}
+
+/* The same identity over EVERY scale the quantiser can meet: a row's scale is s = RN(amax / 127) with amax a
+ * positive finite value of the input type, so there are 32,639 (bf16) or 31,743 (f16) of them.  For each s inside
+ * the range in which the CUDA kernel uses the reciprocal form (2^-60 < s < 2^60; outside it the kernel divides) and
+ * every x of the input type with |x| <= amax -- the only x such a row can hold -- one refinement step must round
+ * to the same integer as the IEEE quotient.  Returns the number of mismatches; *checked counts the (s, x) pairs.
+ * OpenMP over amax when threads are enabled. */
+ORC_API int64_t orc_check_recip_division_all(int is_f16, int64_t *checked) {
+  const uint32_t top = is_f16 ? 0x7c00u : 0x7f80u;   /* first non-finite pattern */
+  int64_t bad = 0, seen = 0;
+#pragma omp parallel for schedule(dynamic, 64) reduction(+ : bad, seen) if (g_threads > 1)
+  for (uint32_t a = 1; a < top; a++) {
+    float amax = is_f16 ? f16_to_f32((uint16_t)a) : bf16_to_f32((uint16_t)a);
+    float s = amax / 127.0f;
+    if (!(s > 8.6736174e-19f && s < 1.1529215e18f)) continue;
+    float r = 1.0f / s;
+    for (uint32_t h = 0; h <= a; h++) {               /* |x| <= amax: the patterns are ordered like the values */
+      float ax = is_f16 ? f16_to_f32((uint16_t)h) : bf16_to_f32((uint16_t)h);
+      for (int sg = 0; sg < 2; sg++) {
+        float x = sg ? -ax : ax;
+        float t = x / s;
+        float q = x * r;
+        float e = fmaf(-q, s, x);
+        q = fmaf(e, r, q);
+        seen++;
+        if (nearbyintf(q) != nearbyintf(t) || !(fabsf(t) <= 127.5f)) bad++;
+      }
+    }
+  }
+  if (checked) *checked = seen;
   return bad;
 }

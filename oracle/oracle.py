@@ -225,22 +225,74 @@ def cumulative(kind, dt, src, axis=1, reverse=False, propagate_nan=True):
     return out
 
 
-def sort_last_axis(dt, src, descending=False):
-    """hivm.hir.vsort over the last axis (HIVMVectorOps.td:2222-2283): (sorted values in src's storage type, int32
-    source indices).  Stable; -0 = +0; NaN after every number ascending, before every number descending."""
+def interleave(srcs):
+    """hfusion.interleave / hivm.hir.vinterleave: out[.., N*i + ch] = srcs[ch][.., i] -- the loop nest of scalar inserts the
+    reference decomposes it into (bishengir/lib/Dialect/HFusion/Transforms/DecomposeOpInterfaceImpl.cpp:439-560; runner
+    golden test/Dialect/HFusion/test_interleave.mlir:16-18).  A move of bits, so any numpy dtype."""
+    n = len(srcs)
+    out = np.empty(srcs[0].shape[:-1] + (n * srcs[0].shape[-1],), dtype=srcs[0].dtype)
+    for ch, s in enumerate(srcs):
+        out[..., ch::n] = s
+    return out
+
+
+def deinterleave(src, channel, channels=2):
+    """hfusion.deinterleave channel<c>: out[.., i] = src[.., N*i + c] (runner golden test_deinterleave.mlir:83-85)."""
+    return np.ascontiguousarray(src[..., channel::channels])
+
+
+def sort_last_axis_loops(dt, src, descending=False):
+    """hfusion.sort / hivm.hir.vsort exactly as the reference lowers it: n-1 bubble passes of n-1 compare-and-swaps
+    on `cmpf ugt` / `ult` (DecomposeOpInterfaceImpl.cpp:742-838).  O(n^2) per row: small rows only."""
     src = _c(src, dt)
+    cols = src.shape[-1]
+    flat = src.reshape(-1, cols)
+    val = np.empty_like(flat)
+    idx = np.empty(flat.shape, dtype=np.int32)
+    _chk(lib().orc_sort_last_axis(dt, int(bool(descending)), _p(flat), _i64(flat.shape[0]), _i64(cols), _p(val), _p(idx)),
+         "sort_last_axis")
+    return val.reshape(src.shape), idx.reshape(src.shape)
+
+
+def sort_last_axis(dt, src, descending=False):
+    """The closed form of `sort_last_axis_loops` (tests check the two against each other): (sorted values in src's
+    storage type, int32 source indices).  Equal keys keep their source order and -0 = +0 (the strict comparison
+    never swaps them); a NaN that starts at position p of its row ends at (p + 1) mod n in either direction (every
+    pair holding a NaN swaps under the unordered predicates, which moves each NaN one place left per pass and
+    carries the one at the front to the end); the other elements fill the remaining places in stable order."""
+    src = _c(src, dt)
+    n = src.shape[-1]
     if dt in (F32, F16, BF16):
         f = src.astype(np.float32) if dt == F32 else (f16_to_f32(src) if dt == F16 else bf16_to_f32(src))
         bits = f.view(np.uint32).copy()
         bits[bits == 0x80000000] = 0
         order = np.where(bits & 0x80000000, ~bits, bits | np.uint32(0x80000000)).astype(np.uint32)
-        order[np.isnan(f)] = 0xFFFFFFFF
+        nan = np.isnan(f)
     else:
         order = (src.astype(np.int64) + 2 ** 31).astype(np.uint32)
+        nan = np.zeros(src.shape, dtype=bool)
     if descending:
         order = ~order
-    key = (order.astype(np.uint64) << np.uint64(32)) | np.arange(src.shape[-1], dtype=np.uint64)
-    idx = np.argsort(key, axis=-1, kind="stable").astype(np.int32)
+    key = (order.astype(np.uint64) << np.uint64(32)) | np.arange(n, dtype=np.uint64)
+    key[nan] = np.uint64(0xFFFFFFFF00000000) | np.broadcast_to(np.arange(n, dtype=np.uint64), src.shape)[nan]
+    by_key = np.argsort(key, axis=-1, kind="stable")                  # numbers in order, then the NaNs by position
+    if nan.any():
+        flat_nan = nan.reshape(-1, n)
+        flat_by_key = by_key.reshape(-1, n)
+        idx = np.empty_like(flat_by_key)
+        for r in range(flat_nan.shape[0]):
+            p = np.flatnonzero(flat_nan[r])
+            if p.size == 0:
+                idx[r] = flat_by_key[r]
+                continue
+            taken = np.zeros(n, dtype=bool)
+            taken[(p + 1) % n] = True
+            idx[r, (p + 1) % n] = p
+            idx[r, ~taken] = flat_by_key[r, :n - p.size]
+        idx = idx.reshape(src.shape)
+    else:
+        idx = by_key
+    idx = idx.astype(np.int32)
     return np.take_along_axis(src, idx.astype(np.int64), axis=-1), idx
 
 

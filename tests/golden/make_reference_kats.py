@@ -108,12 +108,107 @@ def isnan_runner_golden(ref):
              "expected": [0, 1, 0, 0], "source": f"{rel}:{i + 1}-{i + 2}"}]
 
 
+_HF = "bishengir/test/Dialect/HFusion/"
+
+
+def _check_rows(lines):
+    """`// CHECK: [a, b, ...]` lines of a runner test -> [(1-based line, [tokens])], in file order."""
+    out = []
+    for i, l in enumerate(lines):
+        m = re.search(r"//\s*CHECK:\s*\[([^\]]*)\]", l)
+        if m:
+            out.append((i + 1, [t.strip() for t in m.group(1).split(",")]))
+    return out
+
+
+def _stored_buffer(lines, buf):
+    """Rebuilds what `memref.store %const, %<buf>[%ci, ...]` lines put into a buffer from the literal
+    `arith.constant` each one names (index constants %c<k> are the integer k) -> ({index tuple: token}, first, last)."""
+    consts = {}
+    for l in lines:
+        m = re.match(r"\s*(%[\w.]+)\s*=\s*arith\.constant\s+(\S+)\s*:\s*f32", l)
+        if m:
+            consts[m.group(1)] = {"0x7F800000": "inf", "0xFF800000": "-inf", "0x7FC00000": "nan"}.get(m.group(2), m.group(2))
+    cells, first, last = {}, None, None
+    for i, l in enumerate(lines):
+        m = re.match(r"\s*memref\.store\s+(%[\w.]+),\s*%" + buf + r"\[([^\]]*)\]", l)
+        if m:
+            idx = tuple(int(t.strip().lstrip("%c")) for t in m.group(2).split(","))
+            cells[idx] = consts[m.group(1)]
+            first = first or i + 1
+            last = i + 1
+    return cells, first, last
+
+
+def _matrix(cells):
+    dims = [max(k[d] for k in cells) + 1 for d in range(len(next(iter(cells))))]
+    if len(dims) == 1:
+        return [cells[(j,)] for j in range(dims[0])]
+    return [[cells[(i, j)] for j in range(dims[1])] for i in range(dims[0])]
+
+
+def cumsum_runner_golden(ref):
+    rel = _HF + "test_cumsum_2d.mlir"
+    lines = _lines(os.path.join(ref, rel))
+    rows = _check_rows(lines)
+    cells, s0, s1 = _stored_buffer(lines, "m")
+    x = _matrix(cells)
+    assert [r[1] for r in rows[:2]] == [[v.rstrip("0").rstrip(".") for v in row] for row in x]   # the printed input
+    src = f"{rel}:{rows[0][0]}-{rows[-1][0]} (printed output), :{s0}-{s1} (input)"
+    return [{"name": "cumsum_2d_dim1", "op": "cumsum", "dtype": "f32", "axis": 1, "reverse": False, "input": x,
+             "expected": [rows[2][1], rows[3][1]], "source": src},
+            {"name": "cumsum_2d_dim0_reverse", "op": "cumsum", "dtype": "f32", "axis": 0, "reverse": True, "input": x,
+             "expected": [rows[4][1], rows[5][1]], "source": src}]
+
+
+def interleave_runner_goldens(ref):
+    rel = _HF + "test_interleave.mlir"
+    lines = _lines(os.path.join(ref, rel))
+    rows = _check_rows(lines)
+    a, a0, _ = _stored_buffer(lines, "a")
+    b, _, b1 = _stored_buffer(lines, "b")
+    assert [v.rstrip("0").rstrip(".") for v in _matrix(a)] == rows[0][1] and [v.rstrip("0").rstrip(".") for v in _matrix(b)] == rows[1][1]
+    out = [{"name": "interleave_runner_output", "op": "interleave", "dtype": "f32", "a": rows[0][1], "b": rows[1][1],
+            "expected": rows[2][1], "source": f"{rel}:{rows[0][0]}-{rows[2][0]} (printed), :{a0}-{b1} (inputs)"}]
+    rel = _HF + "test_deinterleave.mlir"
+    lines = _lines(os.path.join(ref, rel))
+    rows = _check_rows(lines)
+    src = f"{rel}:{rows[0][0]}-{rows[2][0]}"
+    out.append({"name": "deinterleave_even_runner_output", "op": "deinterleave", "dtype": "f32", "channel": 0,
+                "input": rows[0][1], "expected": rows[1][1], "source": src})
+    out.append({"name": "deinterleave_odd_runner_output", "op": "deinterleave", "dtype": "f32", "channel": 1,
+                "input": rows[0][1], "expected": rows[2][1], "source": src})
+    return out
+
+
+def sort_runner_goldens(ref):
+    rel = _HF + "test_sort_2d_asc.mlir"
+    lines = _lines(os.path.join(ref, rel))
+    rows = _check_rows(lines)
+    cells, s0, s1 = _stored_buffer(lines, "m")
+    x = _matrix(cells)
+    assert [[v.rstrip("0").rstrip(".") for v in r] for r in x[:2]] == [rows[0][1], rows[1][1]]
+    out = [{"name": "sort_2d_ascending_runner_output", "op": "sort", "dtype": "f32", "descending": False,
+            "input": [rows[0][1], rows[1][1]], "expected": [rows[2][1], rows[3][1]],
+            "note": "the first two rows of the 4x4 tensor: the ones the test checks",
+            "source": f"{rel}:{rows[0][0]}-{rows[3][0]} (printed), :{s0}-{s1} (input)"}]
+    rel = _HF + "test_sort_3d_des.mlir"
+    lines = _lines(os.path.join(ref, rel))
+    rows = _check_rows(lines)
+    out.append({"name": "sort_3d_descending_runner_output", "op": "sort", "dtype": "f32", "descending": True,
+                "input": [rows[0][1]], "expected": [rows[1][1]],
+                "note": "row [0, 0, :] of the 2x3x4 tensor: the one the test checks",
+                "source": f"{rel}:{rows[0][0]}-{rows[1][0]}"})
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
     args = ap.parse_args()
     cases = vecadd(args.reference) + cast_folds(args.reference) + saturate_example(args.reference) + \
-        default_round_modes(args.reference) + isnan_runner_golden(args.reference)
+        default_round_modes(args.reference) + isnan_runner_golden(args.reference) + cumsum_runner_golden(args.reference) + \
+        interleave_runner_goldens(args.reference) + sort_runner_goldens(args.reference)
     out = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_kats.json")
     with open(out, "w", encoding="utf-8") as f:
         json.dump({"cases": cases}, f, indent=1)

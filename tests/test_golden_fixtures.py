@@ -32,7 +32,11 @@ def _expected_bits(dtype, vals):
 def test_fixture_file_is_complete():
     names = {c["name"] for c in CASES}
     assert {"vecadd_i16_e2e", "test_cast_rank0", "test_cst_folding", "test_cst_folding_same_type",
-            "saturate_overflow_mode_example", "default_round_mode_table", "isnan_runner_output"} <= names
+            "saturate_overflow_mode_example", "default_round_mode_table", "isnan_runner_output",
+            "cumsum_2d_dim1", "cumsum_2d_dim0_reverse", "interleave_runner_output", "deinterleave_even_runner_output",
+            "deinterleave_odd_runner_output", "sort_2d_ascending_runner_output",
+            "sort_3d_descending_runner_output"} <= names
+    assert len(CASES) >= 12
     assert all(c.get("source") for c in CASES)
 
 
@@ -68,6 +72,39 @@ def test_default_round_mode_fixture():
         assert bsir.default_round_mode(t[row["src"]], t[row["dst"]]) == row["mode"], row
 
 
+def _f32(tokens):
+    return np.array([[float(v) for v in row] for row in tokens] if isinstance(tokens[0], list) else [float(v) for v in tokens],
+                    np.float32)
+
+
+def _same_f32(got, want):
+    """Equal as the runner prints them: same numbers, NaN where NaN is expected."""
+    return got.shape == want.shape and bool(np.all((got == want) | (np.isnan(got) & np.isnan(want))))
+
+
+@pytest.mark.parametrize("case", [c for c in CASES if c["op"] == "cumsum"], ids=lambda c: c["name"])
+def test_oracle_cumsum_runner_goldens(case):
+    got = O.cumulative("sum", O.F32, _f32(case["input"]), axis=case["axis"], reverse=case["reverse"])
+    assert _same_f32(got, _f32(case["expected"]))
+
+
+def test_oracle_interleave_runner_goldens():
+    c = next(c for c in CASES if c["op"] == "interleave")
+    assert _same_f32(O.interleave([_f32(c["a"]), _f32(c["b"])]), _f32(c["expected"]))
+    for c in (c for c in CASES if c["op"] == "deinterleave"):
+        assert _same_f32(O.deinterleave(_f32(c["input"]), c["channel"]), _f32(c["expected"]))
+
+
+@pytest.mark.parametrize("case", [c for c in CASES if c["op"] == "sort"], ids=lambda c: c["name"])
+def test_oracle_sort_runner_goldens(case):
+    """Both forms of the oracle's sort -- the literal compare-and-swap passes and their closed form."""
+    x = _f32(case["input"])
+    for fn in (O.sort_last_axis_loops, O.sort_last_axis):
+        val, idx = fn(O.F32, x, descending=case["descending"])
+        assert _same_f32(val, _f32(case["expected"])), fn.__name__
+        assert _same_f32(np.take_along_axis(x, idx.astype(np.int64), axis=-1), val)
+
+
 # ------------------------------------------------------------------------------------------------ GPU
 @pytest.fixture(scope="module")
 def bsir():
@@ -98,3 +135,33 @@ def test_gpu_vadd_and_isnan_fixtures(bsir):
     c = next(c for c in CASES if c["op"] == "isnan")
     x = torch.tensor([float(v) for v in c["input"]], device="cuda")
     assert bsir.compare("vne", x, x).to(torch.int32).tolist() == c["expected"]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [c for c in CASES if c["op"] == "cumsum"], ids=lambda c: c["name"])
+def test_gpu_cumsum_runner_goldens(bsir, case):
+    import torch
+    x = torch.from_numpy(_f32(case["input"])).cuda()
+    got = bsir.cumulative("sum", x, dim=case["axis"], reverse=case["reverse"])
+    assert _same_f32(got.cpu().numpy(), _f32(case["expected"]))
+
+
+@pytest.mark.gpu
+def test_gpu_interleave_runner_goldens(bsir):
+    import torch
+    c = next(c for c in CASES if c["op"] == "interleave")
+    got = bsir.interleave([torch.from_numpy(_f32(c["a"])).cuda(), torch.from_numpy(_f32(c["b"])).cuda()])
+    assert _same_f32(got.cpu().numpy(), _f32(c["expected"]))
+    for c in (c for c in CASES if c["op"] == "deinterleave"):
+        outs = bsir.deinterleave(torch.from_numpy(_f32(c["input"])).cuda(), 2, keep=[c["channel"]])
+        assert _same_f32(outs[c["channel"]].cpu().numpy(), _f32(c["expected"]))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", [c for c in CASES if c["op"] == "sort"], ids=lambda c: c["name"])
+def test_gpu_sort_runner_goldens(bsir, case):
+    import torch
+    x = torch.from_numpy(_f32(case["input"])).cuda()
+    val, idx = bsir.sort(x, descending=case["descending"])
+    assert _same_f32(val.cpu().numpy(), _f32(case["expected"]))
+    assert _same_f32(torch.gather(x, 1, idx.long()).cpu().numpy(), val.cpu().numpy())

@@ -364,3 +364,48 @@ def test_argmax_caller_workspace_is_left_zeroed(bsir):
         wv, wi = O.reduce_with_index("max", O.BF16, to_bits(x))
         assert np.array_equal(i.cpu().numpy(), wi)
     assert int(ws[: 8 * 4].sum()) == 0     # the per-row counters are back at zero
+
+
+def test_argmax_refuses_a_workspace_it_cannot_use(bsir):
+    """A workspace that is too small or misaligned is an error, not a reason to allocate behind the caller's back."""
+    from bsir import workloads as W
+    import ctypes as C
+    x = W.argmax_input(8, 152064, seed=3)
+    need = bsir.lib().bsir_reduce_with_index_workspace_bytes(C.c_int64(8), C.c_int64(152064))
+    small = torch.zeros(need - 16, dtype=torch.uint8, device="cuda")
+    with pytest.raises(bsir.BsirError) as e:
+        bsir.reduce_with_index("max", x, workspace=small)
+    assert e.value.status == -10 and "too small" in str(e.value)
+    odd = torch.zeros(need + 16, dtype=torch.uint8, device="cuda")[4:]
+    with pytest.raises(bsir.BsirError) as e:
+        bsir.reduce_with_index("max", x, workspace=odd)
+    assert "misaligned" in str(e.value)
+    _check_rwi(bsir, x, "max")                                    # and the op still works afterwards
+
+
+def test_scratch_users_on_two_streams_do_not_disturb_each_other(bsir):
+    """The library keeps one scratch block per stream: a segmented argmax and a split reduction enqueued on two
+    streams with nothing ordering them give the oracle's results, every time."""
+    from bsir import workloads as W
+    import ctypes as C
+    x = W.argmax_input(64, 152064, seed=9)                        # several parts per row: counters + partial results
+    y = torch.randn(8, 1 << 20, device="cuda")                    # few long rows: a split sum with partial results
+    want_v, want_i = O.reduce_with_index("max", O.BF16, to_bits(x))
+    want_s = O.reduce_last_axis("max", O.F32, y.cpu().numpy())
+    assert bsir.lib().bsir_reserve_workspace(C.c_int64(1 << 22), C.c_void_p(0)) == 0
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    res = []
+    for _ in range(20):
+        with torch.cuda.stream(s1):
+            res.append(("a", bsir.reduce_with_index("max", x)))
+        with torch.cuda.stream(s2):
+            res.append(("r", bsir.reduce("max", y)))
+    torch.cuda.synchronize()
+    for kind, r in res:
+        if kind == "a":
+            assert np.array_equal(r[1].cpu().numpy(), want_i)
+            assert_bits_equal(r[0], want_v, "argmax values")
+        else:
+            assert np.array_equal(r.cpu().numpy(), want_s)
+    assert bsir.device_error() == 0

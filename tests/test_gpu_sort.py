@@ -1,5 +1,5 @@
-"""GPU parity: hivm.hir.vsort through the C ABI against the oracle (values bit for bit, indices exactly: the sort is
-stable on both sides)."""
+"""GPU parity: hivm.hir.vsort through the C ABI against the oracle (values bit for bit, indices exactly: the result of the
+reference's compare-and-swap passes is unique, ties and NaN included)."""
 import numpy as np
 import pytest
 import torch
@@ -34,16 +34,38 @@ def test_sort_values_and_indices(bsir, dtype, rows, cols, descending):
 
 
 def test_sort_special_values(bsir):
-    """NaN after the numbers ascending and before them descending; zeros of either sign tie in source order."""
+    """The reference's compare-and-swap passes swap every pair that holds a NaN, so a NaN that starts at position p ends
+    at (p + 1) mod n in either direction; zeros of either sign tie in source order and keep their own bits."""
     x = torch.tensor([[3.0, float("nan"), -0.0, 0.0, float("-inf"), float("inf"), -0.0, 1.0]], device="cuda")
+    for desc in (False, True):
+        val, idx = bsir.sort(x, descending=desc)
+        wv, wi = O.sort_last_axis_loops(O.F32, to_bits(x), descending=desc)
+        assert np.array_equal(idx.cpu().numpy(), wi)
+        assert np.array_equal(to_bits(val).view(np.uint32), wv.view(np.uint32))
     val, idx = bsir.sort(x)
-    assert idx.tolist() == [[4, 2, 3, 6, 7, 0, 5, 1]]
-    assert torch.isnan(val[0, -1]) and val[0, 0] == float("-inf")
-    assert torch.signbit(val[0, 1:4]).tolist() == [True, False, True]         # the zeros keep their own bits
-    val, idx = bsir.sort(x, descending=True)
-    assert idx.tolist() == [[1, 5, 0, 7, 2, 3, 6, 4]]
-    wv, wi = O.sort_last_axis(O.F32, to_bits(x), descending=True)
+    assert idx.tolist() == [[4, 2, 1, 3, 6, 7, 0, 5]] and torch.isnan(val[0, 2])
+    assert torch.signbit(val[0, [1, 3, 4]]).tolist() == [True, False, True]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("rows,cols", [(40, 1), (40, 2), (33, 7), (16, 100), (9, 1000), (4, 8192), (3, 8193), (2, 40000)])
+@pytest.mark.parametrize("descending", [False, True])
+def test_sort_rows_with_nan(bsir, dtype, rows, cols, descending):
+    """Rows holding no, one, a few and many NaNs (first and last positions among them), against the literal loops where
+    they finish in time and their closed form beyond."""
+    g = torch.Generator(device="cuda").manual_seed(rows * 131 + cols)
+    x = (torch.randn(rows, cols, device="cuda", generator=g) * 4).round().div(2).to(dtype)
+    frac = torch.linspace(0, 0.6, rows, device="cuda")[:, None]
+    x[torch.rand(rows, cols, device="cuda", generator=g) < frac] = float("nan")
+    x[1::4, 0] = float("nan")
+    x[2::4, -1] = float("nan")
+    if rows > 3:
+        x[3] = float("nan")                                  # a row of nothing else
+    val, idx = bsir.sort(x, descending=descending)
+    fn = O.sort_last_axis_loops if cols <= 1000 else O.sort_last_axis
+    wv, wi = fn(oracle_dtype(x), to_bits(x), descending=descending)
     assert np.array_equal(idx.cpu().numpy(), wi)
+    assert np.array_equal(to_bits(val), wv)
 
 
 def test_sort_limits_and_strides(bsir):

@@ -57,19 +57,31 @@ def test_quant_properties():
     assert s0[0] == 0 and not q0.any()
 
 
-@pytest.mark.parametrize("seed", [0, 1])
-def test_reciprocal_division_identity(seed):
-    """The CUDA quantiser replaces x / s by r = RN(1/s), q0 = x r, q = fma(fma(-q0, s, x), r, q0).  For every
-    finite bf16 x with |x / s| <= 127.5 the rounded integer must equal that of the IEEE quotient."""
-    rng = np.random.default_rng(seed)
-    scales = np.exp(rng.uniform(np.log(2.0 ** -59), np.log(2.0 ** 59), 300)).astype(np.float32)
-    scales = np.concatenate([scales, rng.uniform(1e-3, 1.0, 300).astype(np.float32)])
-    bad = sum(O.lib().orc_check_recip_division(float(s), 1) for s in scales)
-    assert bad == 0
-    # f16 rows: scales are (an f16 row maximum) / 127; every finite f16 x
-    am = rng.integers(1, 0x7c00, 400).astype(np.uint16).view(np.float16).astype(np.float32)
-    bad = sum(O.lib().orc_check_recip_division_f16(float(s), 1) for s in (am / np.float32(127)).astype(np.float32))
-    assert bad == 0
+def test_reciprocal_division_identity_over_every_scale():
+    """The CUDA quantiser replaces x / s by r = RN(1/s), q0 = x r, q = fma(fma(-q0, s, x), r, q0) when 2^-60 < s < 2^60.
+    A row's scale is s = RN(amax / 127) with amax a positive finite bf16 (f16) value: 32,639 (31,743) scales in all.
+    For every one of them inside that range and every x of the type with |x| <= amax, the rounded integer must equal that
+    of the IEEE quotient.  Last run: bf16 526,844,418 pairs, f16 1,007,713,278 pairs, 0 mismatches."""
+    import ctypes as C
+    fn = O.lib().orc_check_recip_division_all
+    fn.restype = C.c_int64
+    O.set_threads(O.max_threads())
+    try:
+        for is_f16, pairs in ((0, 526844418), (1, 1007713278)):
+            n = C.c_int64(0)
+            assert fn(is_f16, C.byref(n)) == 0
+            assert n.value == pairs
+    finally:
+        O.set_threads(1)
+
+
+def test_reciprocal_division_identity_on_other_scales():
+    """Scales a row cannot produce (random f32): the identity holds there too for |x / s| <= 127.5."""
+    rng = np.random.default_rng(0)
+    scales = np.exp(rng.uniform(np.log(2.0 ** -59), np.log(2.0 ** 59), 200)).astype(np.float32)
+    assert sum(O.lib().orc_check_recip_division(float(s), 1) for s in scales) == 0
+    am = rng.integers(1, 0x7c00, 100).astype(np.uint16).view(np.float16).astype(np.float32)
+    assert sum(O.lib().orc_check_recip_division_f16(float(s), 1) for s in (am / np.float32(127)).astype(np.float32)) == 0
 
 
 def test_w8a8_against_int64():

@@ -3,14 +3,20 @@
 Some hosts give all device memory to their own pool at start-up, or call from places where the CUDA
 allocator must not be entered, so a library call that reaches cudaMalloc is not an option for them.
 This entry point keeps its scratch in a fixed array inside the library image.  The test drives it
-through the C ABI and checks it against the ordinary entry point (bit-exact: indices and values) on
-two calls in a row, because the array is shared between calls and keeps the previous call's contents.
+through the C ABI and checks it against the ordinary entry point and against the CPU oracle (bit-exact:
+indices and values) on two calls in a row, because the array is shared between calls and keeps the
+previous call's contents.
 The file sorts last on purpose, so a run that stops at the first failure has already run every other
 test; it also passes on its own in a fresh process."""
 import ctypes as C
+import os
 
+import numpy as np
 import pytest
 import torch
+
+import oracle as O
+from conftest import floats_from_bits, oracle_dtype, to_bits
 
 pytestmark = pytest.mark.gpu
 
@@ -38,6 +44,13 @@ def _same_bits(a, b):
     return bool(((ia == ib) | both_nan).all())
 
 
+def _check_against_oracle(x, kind, left, nan_mode, val, idx):
+    ov, oi = O.reduce_with_index(kind, oracle_dtype(x), to_bits(x), tie_break_left=left, nan_mode=nan_mode)
+    assert np.array_equal(idx.cpu().numpy(), oi), f"indices differ from the oracle for {tuple(x.shape)} {kind}"
+    got, want = val.float().cpu().numpy(), floats_from_bits(ov, x.dtype)
+    assert np.array_equal(got, want, equal_nan=True), f"values differ from the oracle for {tuple(x.shape)} {kind}"
+
+
 def test_static_scratch_matches_the_allocating_entry_point_twice_in_a_row():
     import bsir as B
     from bsir import workloads as W
@@ -60,6 +73,7 @@ def test_static_scratch_matches_the_allocating_entry_point_twice_in_a_row():
         torch.cuda.synchronize()
         assert torch.equal(idx, want_idx), f"indices differ for {tuple(x.shape)} {kind} left={left} {nm}"
         assert _same_bits(val, want_val), f"values differ for {tuple(x.shape)} {kind} left={left} {nm}"
+        _check_against_oracle(x, kind, left, nm, val, idx)
 
 
 def test_static_scratch_small_and_unaligned_shapes():
@@ -72,6 +86,7 @@ def test_static_scratch_small_and_unaligned_shapes():
         assert rc == 0
         wv, wi = B.reduce_with_index("max", x)
         assert torch.equal(idx, wi) and _same_bits(val, wv)
+        _check_against_oracle(x, "max", True, "region", val, idx)
 
 
 def test_static_scratch_refuses_what_does_not_fit():
@@ -80,11 +95,16 @@ def test_static_scratch_refuses_what_does_not_fit():
     x = torch.zeros(4097, 8, dtype=torch.bfloat16, device="cuda")            # more rows than counters
     rc, _, _ = _call_static(B, x, "max", True, "region")
     assert rc == -10 and b"4096" in B.lib().bsir_last_error()
-    y = torch.zeros(4000, 8192, dtype=torch.float32, device="cuda")          # rows x segments too large
-    rc, _, _ = _call_static(B, y, "max", True, "region")
-    assert rc in (0, -10)
-    if rc == -10:
-        assert b"partial results" in B.lib().bsir_last_error()
+    # rows x segments too large: with segments capped at 256 vectors, 4000 rows of 2048 vectors make 8 segments each,
+    # 32000 partial results against room for 31744
+    y = torch.zeros(4000, 8192, dtype=torch.float32, device="cuda")
+    os.environ["BSIR_RWI_SEGVECS"] = "256"
+    try:
+        rc, val, idx = _call_static(B, y, "max", True, "region")
+        text = B.lib().bsir_last_error()
+    finally:
+        del os.environ["BSIR_RWI_SEGVECS"]
+    assert rc == -10 and b"partial results" in text
     z = torch.randn(2, 4096, device="cuda")                                 # the library still works afterwards
     rc, val, idx = _call_static(B, z, "max", True, "region")
     assert rc == 0 and torch.equal(idx.long(), z.argmax(dim=1))
