@@ -56,6 +56,7 @@ struct PerDevice {
   // bsir_release_workspace(): a launch already enqueued may still be using it, and nothing here waits for the GPU.
   std::map<cudaStream_t, ScratchBlock> scratch;
   std::vector<void *> retired;
+  ScratchBlock last;   // the block handed out most recently (what a capturing stream borrows)
   int *error_word = nullptr;
 };
 static PerDevice g_dev[kMaxDevices];
@@ -80,15 +81,28 @@ const DeviceInfo &device_info() {
 }
 
 // Scratch of at least `bytes` for work enqueued on `stream`.  Steady state: a map lookup, no CUDA call.  When the
-// stream has no block yet, or one too small, a new one is allocated (cudaMalloc: not allowed while a stream capture
-// is under way -- size the block beforehand with bsir_reserve_workspace or a warm-up call) and cleared on `stream`,
-// which orders the clearing before the caller's kernels without the host waiting.
+// stream has no block yet, or one too small, a new one is allocated and cleared on `stream`, which orders the
+// clearing before the caller's kernels without the host waiting.  A capturing stream cannot allocate: it borrows the
+// block handed out last on this device if that one is large enough (the usual recipe -- warm up on one stream,
+// capture on another -- then just works; the graph must not be replayed while other work uses that stream's
+// scratch), and fails with a message otherwise.
 void *device_workspace(size_t bytes, cudaStream_t stream) {
   PerDevice *p = current();
   if (!p) { fail(BSIR_ERR_WORKSPACE, "no current CUDA device"); return nullptr; }
   std::lock_guard<std::mutex> lock(p->mu);
-  ScratchBlock &b = p->scratch[stream];
-  if (b.ptr && b.bytes >= bytes) return b.ptr;
+  auto it = p->scratch.find(stream);
+  if (it != p->scratch.end() && it->second.ptr && it->second.bytes >= bytes) {
+    p->last = it->second;
+    return it->second.ptr;
+  }
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) cudaGetLastError();
+  if (cap != cudaStreamCaptureStatusNone) {
+    if (p->last.ptr && p->last.bytes >= bytes) return p->last.ptr;
+    fail(BSIR_ERR_WORKSPACE, "%zu bytes of scratch are needed but the stream is being captured: run the op once, or call "
+         "bsir_reserve_workspace, before the capture begins", bytes);
+    return nullptr;
+  }
   size_t want = size_t(1) << 20;
   while (want < bytes) want <<= 1;
   void *q = nullptr;
@@ -103,9 +117,11 @@ void *device_workspace(size_t bytes, cudaStream_t stream) {
     fail(BSIR_ERR_WORKSPACE, "cannot clear %zu bytes of device scratch", want);
     return nullptr;
   }
+  ScratchBlock &b = p->scratch[stream];
   if (b.ptr) p->retired.push_back(b.ptr);
   b.ptr = q;
   b.bytes = want;
+  p->last = b;
   return q;
 }
 
@@ -210,6 +226,7 @@ int32_t bsir_release_workspace(void) {
   for (void *q : p->retired) cudaFree(q);
   p->scratch.clear();
   p->retired.clear();
+  p->last = ScratchBlock{};
   return BSIR_OK;
 }
 

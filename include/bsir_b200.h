@@ -506,8 +506,11 @@ BSIR_API int64_t bsir_launch_count(void);
  * counters or partial results; calls on one stream are ordered by the stream.  A stream's block is
  * created, or replaced by a larger one, inside the first call that needs it (cudaMalloc + a clearing
  * memset enqueued on that stream; no host-side wait, and an outgrown block is kept, not freed, because
- * enqueued work may still use it).  That allocation is not allowed during stream capture: before
- * capturing, run the ops once on the capturing stream or call bsir_reserve_workspace.  The per-row
+ * enqueued work may still use it).  That allocation is not allowed during stream capture: a call on
+ * a capturing stream that has no block of its own borrows the block handed out last on the device
+ * (so "run the ops once, then capture on another stream" works as long as the graph is not replayed
+ * while that first stream runs scratch-using ops), and fails with BSIR_ERR_WORKSPACE when there is
+ * none large enough -- run the ops once or call bsir_reserve_workspace before capturing.  The per-row
  * counters in a block are reset by the kernels themselves; they stay non-zero only if a kernel died,
  * which also ends the CUDA context.
  *
