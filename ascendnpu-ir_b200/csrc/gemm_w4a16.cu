@@ -17,9 +17,8 @@
 //   computation it restates ((q - z) * s needs 13 bits).
 // The k order inside an MMA is free as long as both operands use the same one, so the nibble pairs
 // (i, i + 4) are taken as they come and the activations' 8-element pieces are permuted to match with
-// two byte permutes.  This kernel serves the shapes the tensor-memory kernel further down does not take
-// (groups that are not whole 64-k chunks); larger M runs once per 16 rows (decode path; large M belongs
-// on a dense GEMM).
+// two byte permutes.  Row blocks of 9..16 rows run the tensor-memory kernel further down; larger M
+// runs once per 16 rows (decode path; large M belongs on a dense GEMM).
 #include <cstdlib>
 #include <mutex>
 
@@ -286,43 +285,32 @@ __global__ void __launch_bounds__(kWarps * 32, NP == 1 ? 3 : 2) w4a16_mma_kernel
 
 // ------------------------------------------------------------------ tensor-memory path (tcgen05)
 // out^T[n, m] = W^T[n, k] . a^T[k, m]: the 128 output columns of a CTA are the 128 lanes of tensor
-// memory, the (at most 16) rows of `a` are the MMA's N.  The weights go to the tensor core as the
-// centred integers q - z in bf16 (exact; kind::f16 wants both operands in one format, and the
-// activations are bf16), every group of k gets an f32 accumulator of its own, and the epilogue forms
-// out = sum_g s[g, n] * acc_g  in f32: the scale never touches the individual weight, which leaves
-// a shift, a lop3 and an exact subtraction per pair of weights in the dequantising warps.  Against the
-// composed reference (every weight rounded to bf16 before the product) the result differs by that
-// rounding of the weights only, about 1e-3 of the output's RMS.
-//
-// Roles in a CTA of 800 threads:
+// memory, the (at most 16) rows of `a` are the MMA's N.  Roles in a CTA of 672 threads:
 //   warp 16     TMA producer.  A stage of the ring holds 256 k: one box of packed weights
 //               [32 word rows x 128 columns] (16 KB) and four boxes of activations [16 rows x 64 k]
 //               (2 KB each, 128-byte swizzle: the tensor core's K-major layout as TMA writes it);
-//   warps 0-15  dequantisers: thread = one output column.  Warp w owns lane quadrant w % 4 and chunk
-//               w / 4 (64 k) of every stage: 8 words from the stage -> 32 registers of f16 pairs
-//               (k_i, k_i+4) -> tcgen05.st into one of 12 chunk buffers of tensor memory;
-//   warps 17-20 MMA issuers (one thread each): group g belongs to issuer g % 4, which waits for the
-//               group's chunks, issues tcgen05.mma.kind::f16 (A from tensor memory, B = the stage's
-//               activations) into accumulator g % 8 and commits once per group;
-//   warps 21-24 first put every 16-byte piece of a stage's activations into the pair order the nibble
-//               trick produces (k 0,4,1,5,2,6,3,7; in place, the swizzle only moves whole pieces), then,
-//               two stages behind, read the finished accumulators (tcgen05.ld) and add them, scaled.
-// One mbarrier per chunk ("dequantised") and per group ("MMAs done") is used once each, so only the
-// stage ring and the accumulator ring track phases.  All waits are bounded.
+//   warps 0-15  dequantisers: thread = one output column.  Each reads its column's words from the
+//               stage, turns every word into four bf16 pairs (k_i, k_i+4) and stores them into its own
+//               TMEM lane (tcgen05.st); warp w owns lane quadrant w % 4 and chunk w / 4 of every stage;
+//   warps 17-20 first put every 16-byte piece of the stage's activations into the pair order the nibble
+//               trick produces (k 0,4,1,5,2,6,3,7; in place, the swizzle only moves whole pieces), then
+//               one thread per warp issues tcgen05.mma.kind::f16 for its chunk: A operand from tensor
+//               memory, B = the activations in the stage, f32 accumulator in tensor memory.
+// Nothing is staged up front except the scales and zero points, so the ring is as deep as shared
+// memory allows (8 stages = 128 KB of weight loads in flight per SM): the shape is bound by HBM
+// latency x bandwidth per SM.  All waits are bounded.
 constexpr int kTcCols = 128;            // output columns per CTA
 constexpr int kTcStageRows = 32;        // word rows per weight stage (= 256 k)
 constexpr int kTcWeightBytes = kTcStageRows * kTcCols * 4;   // 16 KB
 constexpr int kTcActBytes = 4 * 2048;                        // four chunks of 16 rows x 128 B
 constexpr int kTcStageBytes = kTcWeightBytes + kTcActBytes;  // 24 KB
 constexpr int kTcMaxStages = 8;
-constexpr int kTcABufs = 12;            // 64-k chunks of dequantised weights in TMEM (12 x 32 columns of bf16 pairs)
-constexpr int kTcAccBufs = 8;           // group accumulators in TMEM (8 x 16 columns)
+constexpr int kTcABufs = 8;             // 64-k chunks of dequantised weights in TMEM (8 x 32 columns)
 constexpr int kTcDqWarps = 16;          // dequantising warps: 4 lane quadrants x 4 chunks of a stage
-constexpr int kTcMmaWarps = 4;          // MMA-issuing warps
-constexpr int kTcAuxWarps = 4;          // activation fix-up + epilogue warps
-constexpr int kTcThreads = (kTcDqWarps + 1 + kTcMmaWarps + kTcAuxWarps) * 32;
-constexpr int kTcSmemBudget = 226 * 1024;
-constexpr int kTcMaxChunks = 512;       // k <= 32768
+constexpr int kTcMmaWarps = 4;          // fix-up + MMA-issuing warps; chunk c belongs to issuer c % 4
+constexpr int kTcFixWarps = 4;          // warps that put the activations into the nibble-pair order
+constexpr int kTcThreads = (kTcDqWarps + 1 + kTcMmaWarps + kTcFixWarps) * 32;
+constexpr int kTcSmemBudget = 222 * 1024;
 
 struct TcLayout {
   int stages;
@@ -331,15 +319,13 @@ struct TcLayout {
 __host__ __device__ inline TcLayout tc_layout(int64_t k, int64_t group) {
   TcLayout L;
   const uint32_t ngroups = static_cast<uint32_t>(k / group);
-  const uint32_t nchunks = static_cast<uint32_t>(k / 64);
-  const uint32_t nbar = 3u * kTcMaxStages + kTcAccBufs + nchunks + ngroups + 2u;
-  const uint32_t tail = ngroups * kTcCols * 2u + ngroups * 64u + nbar * 8u + 16u;   // scales, zero words, barriers
-  int st = (kTcSmemBudget - 1024 - static_cast<int>(tail)) / kTcStageBytes;
+  const uint32_t tail = ngroups * kTcCols * 2u + ngroups * 64u + 512u;   // scales, zero words, barriers
+  int st = static_cast<int>((kTcSmemBudget - 1024 - static_cast<int>(tail)) / kTcStageBytes);
   L.stages = st > kTcMaxStages ? kTcMaxStages : st;
   L.sc_off = static_cast<uint32_t>(L.stages > 0 ? L.stages : 0) * kTcStageBytes;
   L.zp_off = L.sc_off + ngroups * kTcCols * 2u;
   L.bar_off = (L.zp_off + ngroups * 64u + 15u) & ~15u;
-  L.bytes = L.bar_off + nbar * 8u + 1024u;
+  L.bytes = L.bar_off + 512u + 1024u;
   return L;
 }
 
@@ -354,15 +340,14 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   const int nstages = L.stages;
   const int nchunks = static_cast<int>(p.k / 64);
   const int ngroups = static_cast<int>(p.k / p.group);
-  const int cpg = static_cast<int>(p.group / 64);        // chunks per group
   const uint32_t bars = base + L.bar_off;
   auto wfull = [&](int s) { return bars + 8u * s; };
   auto wempty = [&](int s) { return bars + 8u * (kTcMaxStages + s); };
   auto aready = [&](int s) { return bars + 8u * (2 * kTcMaxStages + s); };
-  auto accfree = [&](int b) { return bars + 8u * (3 * kTcMaxStages + b); };
-  auto afull = [&](int c) { return bars + 8u * (3 * kTcMaxStages + kTcAccBufs + c); };
-  auto gdone = [&](int g) { return bars + 8u * (3 * kTcMaxStages + kTcAccBufs + nchunks + g); };
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + L.bar_off + 8 * (3 * kTcMaxStages + kTcAccBufs + nchunks + ngroups));
+  auto afull = [&](int b) { return bars + 8u * (3 * kTcMaxStages + b); };
+  auto aempty = [&](int b) { return bars + 8u * (3 * kTcMaxStages + kTcABufs + b); };
+  const uint32_t dfull = bars + 8u * (3 * kTcMaxStages + 2 * kTcABufs);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + L.bar_off + 8 * (3 * kTcMaxStages + 2 * kTcABufs + 1));
   uint16_t *sm_scales = reinterpret_cast<uint16_t *>(gen + L.sc_off);
   uint32_t *sm_zeros = reinterpret_cast<uint32_t *>(gen + L.zp_off);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -385,12 +370,11 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   if (warp == kTcDqWarps && lane == 0) {
     for (int s = 0; s < nstages; ++s) {
       mbar_init(wfull(s), 1);
-      mbar_init(wempty(s), kTcDqWarps);
-      mbar_init(aready(s), kTcAuxWarps * 32);
+      mbar_init(wempty(s), kTcDqWarps + kTcMmaWarps);
+      mbar_init(aready(s), kTcFixWarps * 32);
     }
-    for (int b = 0; b < kTcAccBufs; ++b) mbar_init(accfree(b), kTcAuxWarps);
-    for (int c = 0; c < nchunks; ++c) mbar_init(afull(c), 4);
-    for (int g = 0; g < ngroups; ++g) mbar_init(gdone(g), 1);
+    for (int b = 0; b < kTcABufs; ++b) { mbar_init(afull(b), 4); mbar_init(aempty(b), 1); }
+    mbar_init(dfull, kTcMmaWarps);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     pdl_wait();
@@ -431,22 +415,19 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_d = tmem_base;                          // kTcAccBufs x 16 columns of f32
-  const uint32_t tmem_a0 = tmem_base + kTcAccBufs * 16;       // kTcABufs x 32 columns of packed bf16 pairs
+  // One f32 accumulator (16 columns) per issuing warp; the epilogue adds them.  A tcgen05.mma costs its
+  // issuing thread ~70 cycles and a commit ~130 whatever the MMA's size, and these MMAs are tiny
+  // (128 x 16 x 16), so a single issuer would be the bottleneck: four warps issue side by side.
+  const uint32_t tmem_d = tmem_base;            // columns 0..63
+  const uint32_t tmem_a0 = tmem_base + 64;      // kTcABufs x 32 columns of packed bf16 pairs
 
   if (warp == kTcDqWarps) {
-    // ---------------- TMA producer: a slot is refilled when the 16 dequantising warps have taken its words
-    // and the MMAs that read its activations have completed
     if (lane == 0) {
       bool ok = true;
       int slot = preissued % nstages;
       uint32_t phase = static_cast<uint32_t>(preissued / nstages) & 1u;
-      for (int s = preissued; s < nstages_total && ok; ++s) {
+      for (int s = preissued; s < nstages_total; ++s) {
         if (!mbar_wait_relaxed(wempty(slot), phase ^ 1u, abort_flag, err)) { ok = false; break; }
-        const int c_first = (s - nstages) * 4, c_last = min(nchunks - 1, c_first + 3);
-        for (int g = c_first / cpg; g <= c_last / cpg; ++g)
-          if (!mbar_wait_relaxed(gdone(g), 0u, abort_flag, err)) { ok = false; break; }
-        if (!ok) break;
         issue_stage(s);
         if (++slot == nstages) { slot = 0; phase ^= 1u; }
       }
@@ -456,35 +437,12 @@ __global__ void __launch_bounds__(kTcThreads, 1)
             if (mbar_try_wait(wfull(s), 0) || mbar_try_wait(wfull(s), 1)) break;
     }
   } else if (warp > kTcDqWarps + kTcMmaWarps) {
-    // ---------------- activation fix-up, then (two stages behind) the epilogue of finished groups
-    const int quad = warp & 3;
+    // ---------------- activation fix-up: every 16-byte piece of the stage into the nibble-pair k order
     const int tix = (warp - kTcDqWarps - kTcMmaWarps - 1) * 32 + lane;
-    const int tid_n = quad * 32 + lane;
-    const int64_t n = n0 + tid_n;
-    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    float accs[16];
-#pragma unroll
-    for (int mm = 0; mm < 16; ++mm) accs[mm] = 0.0f;
-    bool ok = true;
-    int g_next = 0;
-    auto drain_group = [&](int g) {
-      if (!mbar_wait_relaxed(gdone(g), 0u, abort_flag, err)) { ok = false; return; }
-      tc_fence_after();
-      uint32_t t16[16];
-      const int b = g % kTcAccBufs;
-      tmem_ld16(tmem_d + lane_addr + static_cast<uint32_t>(b * 16), t16);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(accfree(b));
-      const float sc = __uint_as_float(static_cast<uint32_t>(sm_scales[g * kTcCols + tid_n]) << 16);
-#pragma unroll
-      for (int mm = 0; mm < 16; ++mm) accs[mm] = fmaf(sc, __uint_as_float(t16[mm]), accs[mm]);
-    };
     int slot = 0;
     uint32_t phase = 0u;
-    for (int s = 0; s < nstages_total && ok; ++s) {
-      if (!mbar_wait_relaxed(wfull(slot), phase, abort_flag, err)) { ok = false; break; }
+    for (int s = 0; s < nstages_total; ++s) {
+      if (!mbar_wait_relaxed(wfull(slot), phase, abort_flag, err)) break;
       uint8_t *act = gen + slot * kTcStageBytes + kTcWeightBytes;
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -500,97 +458,137 @@ __global__ void __launch_bounds__(kTcThreads, 1)
       fence_proxy_async();
       mbar_arrive(aready(slot));
       if (++slot == nstages) { slot = 0; phase ^= 1u; }
-      // groups whose last chunk lies two or more stages back
-      while (ok && g_next < ngroups && ((g_next + 1) * cpg - 1) / 4 <= s - 2) drain_group(g_next++);
-    }
-    while (ok && g_next < ngroups) drain_group(g_next++);
-    if (ok && n < p.n) {
-      const int64_t rows_left = p.m - m0;
-#pragma unroll
-      for (int mm = 0; mm < 16; ++mm)
-        if (mm < rows_left) p.out[(m0 + mm) * p.ldo + n] = __bfloat16_as_ushort(__float2bfloat16_rn(accs[mm]));
     }
   } else if (warp > kTcDqWarps) {
-    // ---------------- MMA issue: one thread per warp, group g belongs to issuer g % 4
-    // D = f32, A = bf16 (tensor memory), B = bf16 (shared memory), both K-major, N = 16, M = 128
+    // ---------------- MMA issue: one thread per warp, chunk c of a stage belongs to issuer c
+    // D = f32, A = B = bf16, both K-major, N = 16, M = 128
     if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(16 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(16 >> 3) << 17) |
+                             (static_cast<uint32_t>(128 >> 4) << 24);
       const int issuer = warp - kTcDqWarps - 1;
-      bool ok = true;
-      for (int g = issuer; g < ngroups && ok; g += kTcMmaWarps) {
-        const int acc = g % kTcAccBufs;
-        if (g >= kTcAccBufs) {
-          if (!mbar_wait(accfree(acc), static_cast<uint32_t>(g / kTcAccBufs - 1) & 1u, abort_flag, err)) break;
+      uint32_t aphase = 0u;   // one parity bit per TMEM buffer
+      int slot = 0;
+      uint32_t phase = 0u;
+      for (int s = 0; s < nstages_total; ++s) {
+        const int c = s * 4 + issuer;
+        if (c < nchunks) {
+          const int b = c % kTcABufs;
+          if (!mbar_wait(aready(slot), phase, abort_flag, err) || !mbar_wait(afull(b), (aphase >> b) & 1u, abort_flag, err)) break;
+          aphase ^= 1u << b;
           tc_fence_after();
-        }
-        for (int c = g * cpg; c < (g + 1) * cpg; ++c) {
-          const int s = c >> 2, slot = s % nstages;
-          if (!mbar_wait(aready(slot), static_cast<uint32_t>(s / nstages) & 1u, abort_flag, err) ||
-              !mbar_wait(afull(c), 0u, abort_flag, err)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t act_addr = base + slot * kTcStageBytes + kTcWeightBytes + static_cast<uint32_t>(c & 3) * 2048u;
-          const uint32_t a_addr = tmem_a0 + static_cast<uint32_t>((c % kTcABufs) * 32);
+          const uint32_t act_addr = base + slot * kTcStageBytes + kTcWeightBytes + static_cast<uint32_t>(issuer) * 2048u;
 #pragma unroll
           for (int j = 0; j < 4; ++j)   // 4 x K=16 per 64-k chunk; 8 TMEM columns and 32 bytes of smem each
-            mma_f16_ts(tmem_d + static_cast<uint32_t>(acc * 16), a_addr + static_cast<uint32_t>(j * 8),
-                       make_desc(act_addr + j * 32, 16, 1024), idesc, (c > g * cpg || j > 0) ? 1u : 0u);
+            mma_f16_ts(tmem_d + static_cast<uint32_t>(issuer * 16), tmem_a0 + static_cast<uint32_t>(b * 32 + j * 8),
+                       make_desc(act_addr + j * 32, 16, 1024), idesc, (c >= kTcMmaWarps || j > 0) ? 1u : 0u);
+          // one commit per chunk: when the stage's four commits and its sixteen reader arrivals are in, the
+          // stage can be refilled, and the unpackers know the tensor-memory buffers of that stage are drained
+          tc_commit(wempty(slot));
+        } else {
+          mbar_arrive(wempty(slot));
         }
-        if (ok) tc_commit(gdone(g));   // arrives when the group's MMAs (and everything before them) are done
+        if (++slot == nstages) { slot = 0; phase ^= 1u; }
       }
+      tc_commit(dfull);   // arrives once this issuer's MMAs are done (immediately if it had none)
     }
   } else {
     // ---------------- dequantisers
     const int quad = warp & 3, sub = warp >> 2;       // sub: which chunk of every stage this warp owns
     const int tid_n = quad * 32 + lane;                 // TMEM lane = column within the tile
+    const int64_t n = n0 + tid_n;
+    const bool n_ok = n < p.n;
     const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
-    const int zword = tid_n >> 3, zshift = 4 * (tid_n & 7);
+    const int chunks_per_group = static_cast<int>(p.group / 64);
     bool ok = true;
+    int cur_group = -1;
+    uint32_t zz = 0x43004300u, ss = 0u;
     // The tensor-memory store of a chunk completes while the next chunk is read and dequantised: the
     // wait for it, and the arrival that hands the chunk to the MMA issuers, come just before the
     // next store.  The stage's weights are released as soon as its words are in registers.
-    int pending_chunk = -1;
+    int pending_buf = -1;
     auto hand_over = [&]() {
-      if (pending_chunk < 0) return;
+      if (pending_buf < 0) return;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(afull(pending_chunk));
-      pending_chunk = -1;
+      if (lane == 0) mbar_arrive(afull(pending_buf));
+      pending_buf = -1;
     };
     int slot = 0;
     uint32_t phase = 0u;
+    int slot2 = 0;            // slot and phase of the stage two before this one: its MMAs read the
+    uint32_t phase2 = 0u;     // tensor-memory buffer this stage's chunk is about to overwrite
     for (int s = 0; s < nstages_total && ok; ++s) {
       if (!mbar_wait_relaxed(wfull(slot), phase, abort_flag, err)) { ok = false; break; }
       const uint32_t *st = reinterpret_cast<const uint32_t *>(gen + slot * kTcStageBytes);
-      const int c = s * 4 + sub;                      // global chunk
+      const int cs = sub;                             // chunk of the stage this warp owns
+      const int c = s * 4 + cs;                       // global chunk
       uint32_t words[8];
       if (c < nchunks) {
 #pragma unroll
-        for (int r = 0; r < 8; ++r) words[r] = st[(sub * 8 + r) * kTcCols + tid_n];
+        for (int r = 0; r < 8; ++r) words[r] = st[(cs * 8 + r) * kTcCols + tid_n];
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(wempty(slot));
       if (c < nchunks) {
-        const uint32_t z = (sm_zeros[(c / cpg) * 16 + zword] >> zshift) & 0xfu;
-        const uint32_t zz = (0x4300u | z) * 0x00010001u;     // (128 + z) twice
+        const int b = c % kTcABufs;
+        const int grp = c / chunks_per_group;
+        if (grp != cur_group) {
+          cur_group = grp;
+          const uint32_t sv = sm_scales[grp * kTcCols + tid_n];
+          const uint32_t z = (sm_zeros[grp * 16 + (tid_n >> 3)] >> (4 * (tid_n & 7))) & 0xfu;
+          ss = sv | (sv << 16);
+          zz = (0x4300u | z) * 0x00010001u;
+        }
         uint32_t qv[32];
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) qv[r * 4 + q] = bf16x2_sub(nibble_pair_bf16(words[r], 4 * q), zz);   // (k_q, k_q+4), exact
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t v = nibble_pair_bf16(words[r], 4 * q);
+            qv[r * 4 + q] = bf16x2_mul(bf16x2_sub(v, zz), ss);
+          }
         }
         hand_over();   // the previous chunk's store
-        // the buffer was last read by the MMAs of the group of chunk c - kTcABufs
-        if (c >= kTcABufs) {
-          if (!mbar_wait_relaxed(gdone((c - kTcABufs) / cpg), 0u, abort_flag, err)) { ok = false; break; }
+        // the buffer must have been drained by the MMAs that read it kTcABufs chunks (two stages) ago:
+        // the "stage empty" barrier of that stage completes only after its four MMA commits
+        if (s >= 2) {
+          if (!mbar_wait_relaxed(wempty(slot2), phase2, abort_flag, err)) { ok = false; }
           tc_fence_after();
         }
-        tmem_st32(tmem_a0 + lane_addr + static_cast<uint32_t>((c % kTcABufs) * 32), qv);
-        pending_chunk = c;
+        tmem_st32(tmem_a0 + lane_addr + static_cast<uint32_t>(b * 32), qv);
+        pending_buf = b;
       }
+      if (s >= 2 && ++slot2 == nstages) { slot2 = 0; phase2 ^= 1u; }
       if (++slot == nstages) { slot = 0; phase ^= 1u; }
     }
     hand_over();
+    // ---------------- epilogue: the four warps of half 0 read the accumulator
+    if (sub == 0 && ok) {
+      if (mbar_wait(dfull, 0, abort_flag, err)) {
+        tc_fence_after();
+        float accs[16];
+#pragma unroll
+        for (int mm = 0; mm < 16; ++mm) accs[mm] = 0.0f;
+        const int nacc = nchunks < kTcMmaWarps ? nchunks : kTcMmaWarps;   // issuers that had a chunk
+        for (int a8 = 0; a8 < nacc; ++a8) {
+          uint32_t t16[16];
+          tmem_ld16(tmem_d + lane_addr + static_cast<uint32_t>(a8 * 16), t16);
+          tmem_ld_wait();
+#pragma unroll
+          for (int mm = 0; mm < 16; ++mm) accs[mm] += __uint_as_float(t16[mm]);
+        }
+        uint32_t r[16];
+#pragma unroll
+        for (int mm = 0; mm < 16; ++mm) r[mm] = __float_as_uint(accs[mm]);
+        const int64_t rows_left = p.m - m0;
+        if (n_ok) {
+#pragma unroll
+          for (int mm = 0; mm < 16; ++mm)
+            if (mm < rows_left) p.out[(m0 + mm) * p.ldo + n] = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[mm])));
+        }
+      }
+    }
   }
   tc_fence_before();
   __syncthreads();
@@ -688,12 +686,14 @@ extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t gr
              static_cast<const uint16_t *>(scales), reinterpret_cast<const uint32_t *>(zeros),
              static_cast<uint16_t *>(out), ldo};
   const bool fast = k > 0 && aligned_to(a, 16) && lda % 8 == 0 && aligned_to(qweight, 16) && aligned_to(scales, 16);
-  // Two kernels stream the packed weights.  The tensor-memory kernel (tcgen05) takes every row block when the
-  // groups are whole 64-k chunks and TMA can address the operands; other shapes (group 32, k not a multiple
-  // of 64) run the register dequantisation + mma.sync kernel.  BSIR_W4A16_PATH=m / t forces one of them.
+  // tensor-memory path: needs sm_100, k <= 4096 (activations resident in shared memory), groups that are
+  // whole 64-k chunks and a weight pitch TMA can address
+  // Two kernels stream the packed weights.  Blocks of up to 8 rows (decode) run the register
+  // dequantisation + mma.sync kernel, whose MMA count halves for 8 rows; taller blocks run the
+  // tensor-memory kernel (tcgen05), where the MMA cost does not depend on the rows: legacy mma.sync
+  // tiles cost about 32 cycles per SM sub-core on this GPU.  BSIR_W4A16_PATH=m / t forces one of them.
   const char *force = std::getenv("BSIR_W4A16_PATH");
-  const bool tc_ok = fast && device_info().cc_major >= 10 && group % 64 == 0 && k % 64 == 0 && k / 64 <= kTcMaxChunks &&
-                     (n * 4) % 16 == 0 && tc_layout(k, group).stages >= 2;
+  const bool tc_ok = fast && device_info().cc_major >= 10 && group % 64 == 0 && k % 64 == 0 && tc_layout(k, group).stages >= 2;
   if (!fast) {
     for (int64_t m0 = 0; m0 < m; m0 += 65535) {
       const int64_t mr = m - m0 < 65535 ? m - m0 : 65535;
@@ -707,8 +707,9 @@ extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t gr
   bool have_map = false;
   for (int64_t m0 = 0; m0 < m; m0 += 16) {
     const bool one_block = m - m0 <= 8;
-    bool use_tc = tc_ok;
+    bool use_tc = tc_ok && !one_block;
     if (force && force[0] == 'm') use_tc = false;
+    if (force && force[0] == 't') use_tc = tc_ok;
     if (use_tc && !have_map) {
       have_map = make_weight_tmap(&tw, p.qw, n, k) && make_act_tmap(&ta, p.a, m, k, lda);
       if (!have_map) use_tc = false;

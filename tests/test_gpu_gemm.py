@@ -120,40 +120,13 @@ def test_w8a8_library_symbol(bsir):
 
 
 # ---------------------------------------------------------------- W4A16 (2e-2 rel, stated by the config)
-def _w4_unpack(qw, s, z, group):
-    """float64 weights (q - z) * s, no rounding: the mathematical value the composed reference rounds to bf16."""
-    shifts = torch.arange(8, device=qw.device, dtype=torch.int32) * 4
-    k8, n = qw.shape
-    q = ((qw.view(k8, 1, n) >> shifts.view(1, 8, 1)) & 15).reshape(k8 * 8, n)
-    zz = ((z.view(z.shape[0], -1, 1) >> shifts.view(1, 1, 8)) & 15).reshape(z.shape[0], n)
-    return (q - zz.repeat_interleave(group, 0)).double() * s.double().repeat_interleave(group, 0)
-
-
-def _w4_check(out, want_bits, a, qw, s, z, group, what):
-    """The bar of the configuration is 2e-2 relative.  The tensor-memory kernel applies the group scale to the
-    group's f32 partial sum instead of rounding every dequantised weight to bf16 first, so it differs from the
-    oracle by the oracle's rounding of the weights: about 1.5e-3 of the output's RMS on average, with tails near
-    1e-2 because a group's equal weights round the same way (measured on the CPU by restating the kernel's
-    arithmetic).  Checked against the oracle -- element by element within 2e-2 relative plus 1.2e-2 of the output's
-    RMS (results near zero have no relative scale of their own), 2e-2 relative outright where |result| >= RMS, RMS
-    error at most 4e-3 of the RMS -- and against the unrounded float64 product, of which the kernel's result must be
-    the bf16 neighbour (one ulp) and from which it must be no further than the oracle."""
-    gf = out.float().cpu().numpy().astype(np.float64)
-    wf = O.bf16_to_f32(want_bits).astype(np.float64).reshape(gf.shape)
-    rms = float(np.sqrt(np.mean(wf ** 2))) + 1e-30
-    err = np.abs(gf - wf)
-    assert (err <= 2e-2 * np.abs(wf) + 1.2e-2 * rms).all(), \
-        f"{what}: worst excess {(err - 2e-2 * np.abs(wf)).max() / rms:.3e} of the rms; {int((err > 2e-2 * np.abs(wf) + 1.2e-2 * rms).sum())} outside"
-    big = np.abs(wf) >= rms
-    assert not big.any() or (err[big] / np.abs(wf[big])).max() <= 2e-2, f"{what}: relative error where |result| >= rms"
-    assert np.sqrt(np.mean(err ** 2)) <= 4e-3 * rms, f"{what}: rms err {np.sqrt(np.mean(err ** 2)):.3e} vs rms {rms:.3e}"
-    exact = (a.double() @ _w4_unpack(qw, s, z, group)).cpu().numpy()
-    ex_err = np.abs(gf - exact)
-    assert (ex_err <= 2.0 ** -8 * np.abs(exact) + 5e-4 * rms).all(), \
-        f"{what}: not the bf16 neighbour of the exact product: excess {(ex_err - 2.0 ** -8 * np.abs(exact)).max() / rms:.3e} of the rms"
-    e_kernel = np.sqrt(np.mean((gf - exact) ** 2))
-    e_oracle = np.sqrt(np.mean((wf - exact) ** 2))
-    assert e_kernel <= 1.05 * e_oracle + 1e-12, f"{what}: rms distance to the exact product {e_kernel:.3e}, oracle's {e_oracle:.3e}"
+def _w4_close(out, want_bits, what):
+    """2e-2 relative is the configuration's bar.  Both kernels round every dequantised weight to bf16 exactly as the
+    oracle does and accumulate the same products in f32, so only the order of the f32 additions differs: in practice
+    the results agree to one bf16 step of the largest output, which is asserted as well."""
+    assert_close(out, want_bits, 2e-2, 2e-2 * 0.05, what)
+    wf = O.bf16_to_f32(want_bits)
+    assert np.abs(out.float().cpu().numpy() - wf).max() <= 1.0 / 128 * np.abs(wf).max() + 1e-6, what
 
 
 @pytest.mark.parametrize("m", [1, 2, 3, 8, 16, 5, 33])
@@ -163,12 +136,13 @@ def test_w4a16(bsir, m, n, k):
     a, qw, s, z = W.w4a16_input(m, n, k, seed=m + n)
     out = bsir.matmul_w4a16(a, qw, s, z)
     want = O.matmul_w4a16(to_bits(a), to_bits(qw), to_bits(s), to_bits(z))
-    _w4_check(out, want, a, qw, s, z, 128, f"w4a16 m={m} n={n} k={k}")
+    _w4_close(out, want, f"w4a16 m={m} n={n} k={k}")
 
 
 @pytest.mark.parametrize("m", [1, 8, 16])
 def test_w4a16_config_shape_error_bounds(bsir, m):
-    """The configuration's shape, all three M: the error against the oracle, stated as numbers."""
+    """The configuration's shape, all three M: the error against the oracle, stated as numbers -- RMS error below
+    1e-3 of the output's RMS, and 2e-2 relative outright wherever |result| >= RMS / 4."""
     from bsir import workloads as W
     a, qw, s, z = W.w4a16_input(m, seed=40 + m)
     out = bsir.matmul_w4a16(a, qw, s, z)
@@ -176,38 +150,33 @@ def test_w4a16_config_shape_error_bounds(bsir, m):
     gf = out.float().cpu().numpy().astype(np.float64)
     wf = O.bf16_to_f32(want).astype(np.float64)
     rms = np.sqrt(np.mean(wf ** 2))
-    big = np.abs(wf) >= rms                                  # where a relative error means something
+    big = np.abs(wf) >= 0.25 * rms
     assert (np.abs(gf - wf)[big] / np.abs(wf)[big]).max() <= 2e-2
-    assert np.sqrt(np.mean((gf - wf) ** 2)) <= 4e-3 * rms
-    _w4_check(out, want, a, qw, s, z, 128, f"w4a16 config m={m}")
+    assert np.sqrt(np.mean((gf - wf) ** 2)) <= 1e-3 * rms
+    _w4_close(out, want, f"w4a16 config m={m}")
 
 
 @pytest.mark.parametrize("group", [64, 256, 32])
 @pytest.mark.parametrize("m,n,k", [(4, 512, 1024), (16, 384, 2048), (9, 136, 768)])
 def test_w4a16_other_group_sizes(bsir, m, n, k, group):
-    """Groups of one, and of four, 64-k chunks on the tensor-memory kernel; group 32 on the mma.sync kernel."""
     from bsir import workloads as W
     a, qw, s, z = W.w4a16_input(m, n, k, group=group, seed=group + m)
     out = bsir.matmul_w4a16(a, qw, s, z, group=group)
     want = O.matmul_w4a16(to_bits(a), to_bits(qw), to_bits(s), to_bits(z), group)
-    if group % 64 == 0:
-        _w4_check(out, want, a, qw, s, z, group, f"w4a16 group={group} m={m} n={n} k={k}")
-    else:   # the register kernel rounds every weight like the oracle
-        assert_close(out, want, 2e-2, 2e-2 * 0.05, f"w4a16 group={group} m={m} n={n} k={k}")
+    _w4_close(out, want, f"w4a16 group={group} m={m} n={n} k={k}")
 
 
+@pytest.mark.parametrize("path", ["m", "t"])
 @pytest.mark.parametrize("m,n,k", [(1, 14336, 4096), (16, 14336, 4096), (7, 1024, 1024), (16, 256, 8192), (3, 136, 384), (9, 128, 2048), (33, 192, 4096)])
-def test_w4a16_register_kernel(bsir, m, n, k, monkeypatch):
-    """The register dequantisation + mma.sync kernel (the fallback) rounds every weight to bf16 like the oracle:
-    same products, only the f32 summation order differs."""
+def test_w4a16_each_kernel(bsir, m, n, k, path, monkeypatch):
+    """Both weight-streaming kernels (register dequantisation + mma.sync, tensor-memory + tcgen05) on the
+    same inputs; shapes a kernel does not take fall through to the other one."""
     from bsir import workloads as W
-    monkeypatch.setenv("BSIR_W4A16_PATH", "m")
+    monkeypatch.setenv("BSIR_W4A16_PATH", path)
     a, qw, s, z = W.w4a16_input(m, n, k, seed=3 * m + n)
     out = bsir.matmul_w4a16(a, qw, s, z)
     want = O.matmul_w4a16(to_bits(a), to_bits(qw), to_bits(s), to_bits(z))
-    wf = O.bf16_to_f32(want)
-    assert_close(out, want, 2e-2, 2e-2 * 0.05, f"w4a16 (register kernel) m={m} n={n} k={k}")
-    assert np.abs(out.float().cpu().numpy() - wf).max() <= 1.0 / 128 * np.abs(wf).max() + 1e-6
+    _w4_close(out, want, f"w4a16 path={path} m={m} n={n} k={k}")
 
 
 def test_w4a16_twice_gives_the_same_bits(bsir):
