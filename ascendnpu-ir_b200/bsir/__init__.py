@@ -648,6 +648,62 @@ def matmul_w8a8(a: torch.Tensor, b: torch.Tensor, scale_a: Optional[torch.Tensor
     return (out, acc) if want_acc else out
 
 
+class MatmulDesc(C.Structure):
+    _fields_ = [("in_dtype", C.c_int32), ("out_dtype", C.c_int32), ("transpose_a", C.c_int32), ("transpose_b", C.c_int32),
+                ("descale_mode", C.c_int32), ("relu", C.c_int32), ("bias_dtype", C.c_int32), ("descale_dtype", C.c_int32),
+                ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64), ("batch", C.c_int64),
+                ("a", C.c_void_p), ("lda", C.c_int64), ("batch_stride_a", C.c_int64),
+                ("b", C.c_void_p), ("ldb", C.c_int64), ("batch_stride_b", C.c_int64),
+                ("bias", C.c_void_p), ("descale", C.c_void_p), ("scale_a", C.c_void_p),
+                ("out", C.c_void_p), ("ldo", C.c_int64), ("batch_stride_out", C.c_int64)]
+
+
+DESCALE_MODE = {"DescaleNull": 0, "DescalePerChannel": 1, "DescalePerTensor": 2, None: 0}
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, *, transpose_a: bool = False, transpose_b: bool = False,
+           bias: Optional[torch.Tensor] = None, descale: Optional[torch.Tensor] = None, descale_mode: Optional[str] = None,
+           scale_a: Optional[torch.Tensor] = None, relu: bool = False, out_dtype: Optional[torch.dtype] = None,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hivm.hir.matmul`` / ``linalg.matmul`` (2-D) or ``batch_matmul`` (3-D operands):
+    ``C = cast(relu(descale * (A @ B + bias) * scale_a))``.  Operands int8 (int32 accumulation), f16 or bf16 (f32
+    accumulation); ``a_transpose`` / ``b_transpose`` as the op's unit attributes; ``descale_mode`` with the reference's
+    spellings (``DescaleNull`` | ``DescalePerChannel`` | ``DescalePerTensor``; inferred from the descale's size when
+    omitted); ``out_dtype`` f16 / bf16 / f32 / int8 (fixpipe ``S322I8``) / int32 (raw accumulators of an int8 product)."""
+    batched = a.dim() == 3
+    a3 = a if batched else a.unsqueeze(0)
+    b3 = b if b.dim() == 3 else b.unsqueeze(0)
+    if (a3.shape[-1] > 1 and a3.stride(-1) != 1) or (b3.shape[-1] > 1 and b3.stride(-1) != 1):
+        raise BsirError(-3, "matmul: the last axis of each operand must be contiguous")
+    batch = a3.shape[0]
+    m, k = (a3.shape[2], a3.shape[1]) if transpose_a else (a3.shape[1], a3.shape[2])
+    n = b3.shape[1] if transpose_b else b3.shape[2]
+    if out_dtype is None:
+        out_dtype = torch.float16 if a.dtype == torch.int8 else a.dtype
+    if out is None:
+        out = torch.empty((batch, m, n) if batched else (m, n), dtype=out_dtype, device=a.device)
+    o3 = out if out.dim() == 3 else out.unsqueeze(0)
+    if descale is not None and descale_mode is None:
+        descale_mode = "DescalePerTensor" if descale.numel() == 1 else "DescalePerChannel"
+    d = MatmulDesc()
+    d.in_dtype, d.out_dtype = _dt(a), _TORCH2DT[out_dtype]
+    d.transpose_a, d.transpose_b = int(transpose_a), int(transpose_b)
+    d.descale_mode = DESCALE_MODE[descale_mode] if descale is not None else 0
+    d.relu = int(relu)
+    d.bias_dtype = _dt(bias) if bias is not None else F32
+    d.descale_dtype = _dt(descale) if descale is not None else F32
+    d.m, d.n, d.k, d.batch = m, n, k, batch
+    # a row pitch only means something with more than one row; a lone row reports its length
+    d.a, d.lda, d.batch_stride_a = a3.data_ptr(), (a3.stride(1) if a3.shape[1] > 1 else a3.shape[2]), (a3.stride(0) if batch > 1 else 0)
+    d.b, d.ldb, d.batch_stride_b = b3.data_ptr(), (b3.stride(1) if b3.shape[1] > 1 else b3.shape[2]), (b3.stride(0) if b3.shape[0] > 1 else 0)
+    d.bias = bias.data_ptr() if bias is not None else None
+    d.descale = descale.data_ptr() if descale is not None else None
+    d.scale_a = scale_a.data_ptr() if scale_a is not None else None
+    d.out, d.ldo, d.batch_stride_out = o3.data_ptr(), (o3.stride(1) if o3.shape[1] > 1 else o3.shape[2]), (o3.stride(0) if batch > 1 else 0)
+    _check(lib().bsir_matmul(C.byref(d), _stream()))
+    return out
+
+
 def matmul_w4a16(a: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,
                  group: int = 128, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     m, k = a.shape

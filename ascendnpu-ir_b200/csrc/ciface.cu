@@ -120,17 +120,30 @@ int32_t rwi_r(const char *what, int kind, int left, int dt, bsir_memref_1d *src,
                                 base_of_mut(dv, dt), static_cast<int32_t *>(base_of_mut(di, BSIR_I32)), nullptr, 0, nullptr);
 }
 
-int32_t matmul_i8_half(const char *what, bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_2d *C, int transpose_b) {
-  if (!A || !B || !C) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
-  const int64_t m = A->sizes[0], k = A->sizes[1];
-  const int64_t n = transpose_b ? B->sizes[0] : B->sizes[1];
-  if ((transpose_b ? B->sizes[1] : B->sizes[0]) != k || C->sizes[0] != m || C->sizes[1] != n)
+// hivm.hir.matmul library call: operands in the op's order, bias / descale optional (null = absent)
+int32_t matmul_call(const char *what, int in_dt, int out_dt, int bias_dt, int descale_dt, int descale_mode, int ta, int tb,
+                    bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_1d *bias, bsir_memref_1d *descale, bsir_memref_2d *C) {
+  if (!A || !B || !C || (descale_mode != BSIR_DESCALE_NULL && !descale)) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  const int64_t m = ta ? A->sizes[1] : A->sizes[0], k = ta ? A->sizes[0] : A->sizes[1];
+  const int64_t n = tb ? B->sizes[0] : B->sizes[1];
+  if ((tb ? B->sizes[1] : B->sizes[0]) != k || C->sizes[0] != m || C->sizes[1] != n)
     return fail(BSIR_ERR_SHAPE, "%s: shapes do not compose", what);
-  if ((k > 1 && A->strides[1] != 1) || B->strides[1] != 1 || (n > 1 && C->strides[1] != 1))
+  if (bias && bias->sizes[0] != n) return fail(BSIR_ERR_SHAPE, "%s: bias of %lld entries for n = %lld", what, (long long)bias->sizes[0], (long long)n);
+  if (descale_mode == BSIR_DESCALE_PER_CHANNEL && descale->sizes[0] != n) return fail(BSIR_ERR_SHAPE, "%s: per-channel descale of %lld entries for n = %lld", what, (long long)descale->sizes[0], (long long)n);
+  if (descale_mode == BSIR_DESCALE_PER_TENSOR && descale->sizes[0] != 1) return fail(BSIR_ERR_SHAPE, "%s: per-tensor descale of %lld entries", what, (long long)descale->sizes[0]);
+  if ((A->sizes[1] > 1 && A->strides[1] != 1) || (B->sizes[1] > 1 && B->strides[1] != 1) || (n > 1 && C->strides[1] != 1) ||
+      (bias && n > 1 && bias->strides[0] != 1) || (descale && descale->sizes[0] > 1 && descale->strides[0] != 1))
     return fail(BSIR_ERR_STRIDE, "%s: innermost dimensions must be unit-stride", what);
-  return bsir_matmul_w8a8(m, n, k, static_cast<const int8_t *>(base_of(A, BSIR_I8)), A->strides[0],
-                          static_cast<const int8_t *>(base_of(B, BSIR_I8)), B->strides[0], transpose_b, nullptr, nullptr,
-                          BSIR_F16, base_of_mut(C, BSIR_F16), C->strides[0], nullptr, nullptr, 0, nullptr);
+  bsir_matmul_desc d{};
+  d.in_dtype = in_dt; d.out_dtype = out_dt; d.transpose_a = ta; d.transpose_b = tb;
+  d.descale_mode = descale_mode; d.bias_dtype = bias_dt; d.descale_dtype = descale_dt;
+  d.m = m; d.n = n; d.k = k; d.batch = 1;
+  d.a = base_of(A, in_dt); d.lda = A->strides[0];
+  d.b = base_of(B, in_dt); d.ldb = B->strides[0];
+  d.bias = bias ? base_of(bias, bias_dt) : nullptr;
+  d.descale = descale ? base_of(descale, descale_dt) : nullptr;
+  d.out = base_of_mut(C, out_dt); d.ldo = C->strides[0];
+  return bsir_matmul(&d, nullptr);
 }
 
 }  // namespace
@@ -239,17 +252,57 @@ BSIR_FOREACH_CAST_WITH_TEMP(BSIR_DEF_CAST_TEMP, 2)
 BSIR_FOREACH_REDUCE(BSIR_DEF_REDUCE)
 BSIR_FOREACH_REDUCE_WITH_INDEX(BSIR_DEF_REDUCE_WITH_INDEX)
 
-int32_t _mlir_ciface_matmul_Xbias_Xdescale_XtransposeA_XtransposeB_TAint8_t_TBint8_t_TChalf(bsir_memref_2d *A,
-                                                                                          bsir_memref_2d *B,
-                                                                                          bsir_memref_2d *C) {
-  clear_error();
-  return matmul_i8_half("matmul_i8_i8_half", A, B, C, 0);
-}
-int32_t _mlir_ciface_matmul_Xbias_Xdescale_XtransposeA_transposeB_TAint8_t_TBint8_t_TChalf(bsir_memref_2d *A,
-                                                                                         bsir_memref_2d *B,
-                                                                                         bsir_memref_2d *C) {
-  clear_error();
-  return matmul_i8_half("matmul_i8_i8T_half", A, B, C, 1);
-}
+#define BSIR_DEF_MM_PLAIN_T(ta, tb, fa, fb, a, c)                                                                   \
+  int32_t _mlir_ciface_matmul_Xbias_Xdescale_##ta##_##tb##_TA##a##_TB##a##_TC##c(bsir_memref_2d *A, bsir_memref_2d *B, \
+                                                                                 bsir_memref_2d *C) {                \
+    clear_error();                                                                                                    \
+    return matmul_call("matmul_" #a "_" #c, BSIR_DT_##a, BSIR_DT_##c, BSIR_F32, BSIR_F32, BSIR_DESCALE_NULL, fa, fb, A, B, \
+                       nullptr, nullptr, C);                                                                          \
+  }
+#define BSIR_DEF_MM_PLAIN(a, c) BSIR_MATMUL_TRANSPOSES(BSIR_DEF_MM_PLAIN_T, a, c)
+#define BSIR_DEF_MM_BIAS_T(ta, tb, fa, fb, a, c, bt)                                                                  \
+  int32_t _mlir_ciface_matmul_bias_TBIAS##bt##_Xdescale_##ta##_##tb##_TA##a##_TB##a##_TC##c(                          \
+      bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_1d *bias, bsir_memref_2d *C) {                                \
+    clear_error();                                                                                                    \
+    if (!bias) return fail(BSIR_ERR_NULL, "matmul with bias: null bias descriptor");                                  \
+    return matmul_call("matmul_bias_" #a "_" #c, BSIR_DT_##a, BSIR_DT_##c, BSIR_DT_##bt, BSIR_F32, BSIR_DESCALE_NULL, fa, fb, \
+                       A, B, bias, nullptr, C);                                                                       \
+  }
+#define BSIR_DEF_MM_BIAS(a, c, bt) BSIR_MATMUL_TRANSPOSES(BSIR_DEF_MM_BIAS_T, a, c, bt)
+#define BSIR_DEF_MM_DESCALE_T(ta, tb, fa, fb, a, c, dt)                                                               \
+  int32_t _mlir_ciface_matmul_Xbias_descalePerChannel_TDESCALE##dt##_##ta##_##tb##_TA##a##_TB##a##_TC##c(             \
+      bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_1d *descale, bsir_memref_2d *C) {                             \
+    clear_error();                                                                                                    \
+    return matmul_call("matmul_descalePerChannel_" #a "_" #c, BSIR_DT_##a, BSIR_DT_##c, BSIR_F32, BSIR_DT_##dt,       \
+                       BSIR_DESCALE_PER_CHANNEL, fa, fb, A, B, nullptr, descale, C);                                  \
+  }                                                                                                                   \
+  int32_t _mlir_ciface_matmul_Xbias_descalePerTensor_TDESCALE##dt##_##ta##_##tb##_TA##a##_TB##a##_TC##c(              \
+      bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_1d *descale, bsir_memref_2d *C) {                             \
+    clear_error();                                                                                                    \
+    return matmul_call("matmul_descalePerTensor_" #a "_" #c, BSIR_DT_##a, BSIR_DT_##c, BSIR_F32, BSIR_DT_##dt,        \
+                       BSIR_DESCALE_PER_TENSOR, fa, fb, A, B, nullptr, descale, C);                                   \
+  }
+#define BSIR_DEF_MM_DESCALE(a, c, dt) BSIR_MATMUL_TRANSPOSES(BSIR_DEF_MM_DESCALE_T, a, c, dt)
+#define BSIR_DEF_MM_BOTH_T(ta, tb, fa, fb, a, c, bt, dt)                                                              \
+  int32_t _mlir_ciface_matmul_bias_TBIAS##bt##_descalePerChannel_TDESCALE##dt##_##ta##_##tb##_TA##a##_TB##a##_TC##c(  \
+      bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_1d *bias, bsir_memref_1d *descale, bsir_memref_2d *C) {       \
+    clear_error();                                                                                                    \
+    if (!bias) return fail(BSIR_ERR_NULL, "matmul with bias: null bias descriptor");                                  \
+    return matmul_call("matmul_bias_descalePerChannel_" #a "_" #c, BSIR_DT_##a, BSIR_DT_##c, BSIR_DT_##bt, BSIR_DT_##dt, \
+                       BSIR_DESCALE_PER_CHANNEL, fa, fb, A, B, bias, descale, C);                                     \
+  }                                                                                                                   \
+  int32_t _mlir_ciface_matmul_bias_TBIAS##bt##_descalePerTensor_TDESCALE##dt##_##ta##_##tb##_TA##a##_TB##a##_TC##c(   \
+      bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_1d *bias, bsir_memref_1d *descale, bsir_memref_2d *C) {       \
+    clear_error();                                                                                                    \
+    if (!bias) return fail(BSIR_ERR_NULL, "matmul with bias: null bias descriptor");                                  \
+    return matmul_call("matmul_bias_descalePerTensor_" #a "_" #c, BSIR_DT_##a, BSIR_DT_##c, BSIR_DT_##bt, BSIR_DT_##dt, \
+                       BSIR_DESCALE_PER_TENSOR, fa, fb, A, B, bias, descale, C);                                      \
+  }
+#define BSIR_DEF_MM_BOTH(a, c, bt, dt) BSIR_MATMUL_TRANSPOSES(BSIR_DEF_MM_BOTH_T, a, c, bt, dt)
+
+BSIR_MATMUL_PLAINSETS(BSIR_DEF_MM_PLAIN)
+BSIR_MATMUL_BIASSETS(BSIR_DEF_MM_BIAS)
+BSIR_MATMUL_DESCALESETS(BSIR_DEF_MM_DESCALE)
+BSIR_MATMUL_TYPESETS(BSIR_DEF_MM_BOTH)
 
 }  // extern "C"

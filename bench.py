@@ -168,9 +168,18 @@ def time_op(torch, fn, iters: int, warm: int = 3):
     return tot / reps, best
 
 
+def sustained_bf16_peak():
+    """bf16 TFLOP/s of a seconds-long cuBLAS loop under the power cap (the pool's measurement), else the stated fallback."""
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p)).get("bf16_tflops_sustained", 0.0)) or None
+    return 1400.0
+
+
 def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters, only=None):
     """The remaining configurations, each with inputs larger than L2 or rotated buffers."""
     res = {}
+    bf16_sustained = sustained_bf16_peak()
 
     def rec(name, algo_bytes, fn, flops=None, note=None):
         if only and name != only:
@@ -298,6 +307,28 @@ def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters, only=None):
             del sets, outs
         except Exception as e:
             res[f"w8a8_m{m}"] = {"error": str(e)[:200]}
+    # linalg.matmul bf16 x bf16 -> bf16 (f32 accumulation), 4096^3, B as [k, n] and as [n, k]; and hivm.hir.matmul with
+    # bias, per-channel descale and relu fused into the way out
+    for nm, tb, fused in (("gemm_bf16_4096", False, False), ("gemm_bf16_4096_tb", True, False), ("gemm_bf16_4096_bias_descale_relu", False, True)):
+        if not want(nm):
+            continue
+        try:
+            g = torch.Generator(device="cuda").manual_seed(1)
+            aa = [torch.randn(4096, 4096, generator=g, device="cuda").to(torch.bfloat16) for _ in range(3)]    # 3 x 96 MB > L2
+            bb = [(torch.randn(4096, 4096, generator=g, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(3)]
+            oo = [torch.empty(4096, 4096, dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+            bias = torch.randn(4096, generator=g, device="cuda").to(torch.bfloat16) if fused else None
+            desc = (torch.rand(4096, generator=g, device="cuda") + 0.5).to(torch.bfloat16) if fused else None
+            rec(nm, 3 * 4096 * 4096 * 2,
+                lambda i: bsir.matmul(aa[i % 3], bb[i % 3], transpose_b=tb, bias=bias, descale=desc, relu=fused, out=oo[i % 3]),
+                flops=2 * 4096 ** 3)
+            if nm in res and "tops" in res[nm]:
+                res[nm]["frac_bf16_sustained"] = res[nm]["tops"] / bf16_sustained if bf16_sustained else None
+                res[nm]["frac_bf16_burst"] = res[nm]["tops"] / tensor_peak
+                res[nm].pop("frac_int8_peak_2x_bf16", None)
+            del aa, bb, oo
+        except Exception as e:
+            res[nm] = {"error": str(e)[:200]}
     for m in (1, 8, 16):
         if not want(f"w4a16_m{m}"):
             continue

@@ -436,6 +436,45 @@ BSIR_API int32_t bsir_matmul_w8a8(int64_t m, int64_t n, int64_t k, const int8_t 
                                   void *out, int64_t ldo, int32_t *acc_out, void *workspace,
                                   int64_t workspace_bytes, void *stream);
 
+/* hivm.hir.matmul, "C = descale * (A * B + bias)" with optional transposed operands
+ * (bishengir/include/bishengir/Dialect/HIVM/IR/HIVMMacroOps.td:364-492; descale modes
+ * HIVMAttrs.td:1061-1071; the device library's variants
+ * bishengir/lib/Template/lib/Cube/GlobalMmad.cpp:176-187 and the names with bias / descale in
+ * bishengir/test/Conversion/HIVMToStandard/HIVMToStandard/matmul.mlir:13-55), followed by what the
+ * reference inlines into the accumulator's way out (hivm.hir.fixpipe, HIVMDMAOps.td:275-335;
+ * InlineFixpipe.cpp:876-884): pre_relu NORMAL_RELU and the pre_quant conversions F322F16, F322BF16 and
+ * S322I8.  One description serves linalg.matmul of int8 (int32 accumulation), f16 and bf16 (f32
+ * accumulation, Normalize.cpp:8224-8257) and batch_matmul (one launch per batch entry):
+ *   acc  = sum_k A[i, k] * B[k, j]                              int32 or f32
+ *   v    = f32(acc + bias[j])                                   int32 add for an int8 product
+ *   v    = v * scale_a[i]                                       optional, the per-token half of a W8A8 dequant
+ *   v    = v * descale[j] (per channel) | descale[0] (per tensor)
+ *   v    = maximumf(v, 0)                                       with relu
+ *   C    = cast_rint(v): f16 (clamped to its range), bf16, f32, int8 (saturating: S322I8); out_dtype
+ *          BSIR_I32 stores acc + bias of an int8 product untouched. */
+typedef struct bsir_matmul_desc {
+  int32_t in_dtype;      /* BSIR_I8, BSIR_F16 or BSIR_BF16: the type of both A and B                  */
+  int32_t out_dtype;     /* BSIR_F16, BSIR_BF16, BSIR_F32, BSIR_I8, and BSIR_I32 for an int8 product   */
+  int32_t transpose_a;   /* 0: a is [m, k] rows; 1: a is [k, m] rows                                 */
+  int32_t transpose_b;   /* 0: b is [k, n] rows (linalg.matmul); 1: b is [n, k] rows                 */
+  int32_t descale_mode;  /* bsir_descale_mode: BSIR_DESCALE_NULL, _PER_CHANNEL or _PER_TENSOR                */
+  int32_t relu;          /* 1: maximumf(v, 0) before the final cast                                  */
+  int32_t bias_dtype;    /* BSIR_I32 with an int8 product; BSIR_F32, BSIR_F16 or BSIR_BF16 otherwise  */
+  int32_t descale_dtype; /* BSIR_F32, BSIR_F16 or BSIR_BF16                                           */
+  int64_t m, n, k;
+  int64_t batch;         /* >= 1; entry e uses a + e * batch_stride_a and so on (strides in elements) */
+  const void *a;
+  int64_t lda, batch_stride_a;
+  const void *b;
+  int64_t ldb, batch_stride_b;
+  const void *bias;      /* [n] or NULL                                                              */
+  const void *descale;   /* [n] (per channel), [1] (per tensor) or NULL; a device pointer either way */
+  const float *scale_a;  /* [m] f32 or NULL                                                          */
+  void *out;
+  int64_t ldo, batch_stride_out;
+} bsir_matmul_desc;
+BSIR_API int32_t bsir_matmul(const bsir_matmul_desc *desc, void *stream);
+
 /* W4A16 group-quantised GEMM: out = bf16_rint( a . bf16_rint((q - z) * s) ), f32
  * accumulation.  a: [m,k] bf16 row-major (lda); qweight: int32 [k/8, n], nibble i
  * of word (r, c) (bits 4i..4i+3) is q[8r+i, c]; scales: bf16 [k/group, n];

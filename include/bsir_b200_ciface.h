@@ -218,14 +218,55 @@ BSIR_FOREACH_CAST_WITH_TEMP(BSIR_DECL_CAST_TEMP, 2)
 BSIR_FOREACH_REDUCE(BSIR_DECL_REDUCE)
 BSIR_FOREACH_REDUCE_WITH_INDEX(BSIR_DECL_REDUCE_WITH_INDEX)
 
-/* GEMM library symbols (names as checked by
- * bishengir/test/Conversion/HIVMToStandard/HIVMToStandard/matmul.mlir:13-55; registered
- * variants bishengir/lib/Template/lib/Cube/GlobalMmad.cpp:176-187).  C = A x B, int8 inputs
- * accumulate in int32 and are converted to half with round-to-nearest-even, saturating
- * at the half range. */
-BSIR_API BSIR_CIFACE_RET _mlir_ciface_matmul_Xbias_Xdescale_XtransposeA_XtransposeB_TAint8_t_TBint8_t_TChalf(
-    bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_2d *C);
-BSIR_API BSIR_CIFACE_RET _mlir_ciface_matmul_Xbias_Xdescale_XtransposeA_transposeB_TAint8_t_TBint8_t_TChalf(
-    bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_2d *C);
+/* GEMM library symbols.  Names as the reference's name builder spells them
+ * (bishengir/lib/Dialect/HIVM/IR/LibraryFunctionOpInterface/LibraryFunctionOpInterfaceImpl.cpp:470-505,
+ * checked by bishengir/test/Conversion/HIVMToStandard/HIVMToStandard/matmul.mlir:13-55):
+ *   matmul_{X,}bias[_TBIAS<t>]_{Xdescale | descalePerChannel_TDESCALE<t> | descalePerTensor_TDESCALE<t>}
+ *         _{X,}transposeA_{X,}transposeB_TA<t>_TB<t>_TC<t>
+ * with the operands in the op's order: A, B, [bias], [descale], C.  The reference's device library registers the
+ * eight Xbias_Xdescale variants of half x half -> half and int8 x int8 -> half
+ * (bishengir/lib/Template/lib/Cube/GlobalMmad.cpp:176-187); here every bias / descale form exists for those two
+ * type sets and for bfloat16_t.  C = descale * (A x B + bias); int8 inputs accumulate in int32 (bias int32_t,
+ * descale float or half), 16-bit float inputs in f32 (bias and descale of the operand type or float); the result
+ * is rounded to nearest even, half saturating at its range.
+ * X(ta, tb): transposeA / transposeB tokens; T(a, c): operand and result element types. */
+#define BSIR_MATMUL_TRANSPOSES(X, ...)                                                              \
+  X(XtransposeA, XtransposeB, 0, 0, __VA_ARGS__) X(transposeA, XtransposeB, 1, 0, __VA_ARGS__)      \
+  X(XtransposeA, transposeB, 0, 1, __VA_ARGS__) X(transposeA, transposeB, 1, 1, __VA_ARGS__)
+/* type sets: (TA = TB, TC, bias type) x the descale types offered */
+#define BSIR_MATMUL_TYPESETS(X)                                                                     \
+  X(half, half, half, half) X(half, half, half, float) X(half, half, float, half) X(half, half, float, float) \
+  X(bfloat16_t, bfloat16_t, bfloat16_t, bfloat16_t) X(bfloat16_t, bfloat16_t, bfloat16_t, float)    \
+  X(bfloat16_t, bfloat16_t, float, bfloat16_t) X(bfloat16_t, bfloat16_t, float, float)              \
+  X(int8_t, half, int32_t, float) X(int8_t, half, int32_t, half)
+#define BSIR_MATMUL_PLAINSETS(X) X(half, half) X(bfloat16_t, bfloat16_t) X(int8_t, half)
+#define BSIR_MATMUL_BIASSETS(X) X(half, half, half) X(half, half, float) X(bfloat16_t, bfloat16_t, bfloat16_t) X(bfloat16_t, bfloat16_t, float) X(int8_t, half, int32_t)
+#define BSIR_MATMUL_DESCALESETS(X) X(half, half, half) X(half, half, float) X(bfloat16_t, bfloat16_t, bfloat16_t) X(bfloat16_t, bfloat16_t, float) X(int8_t, half, float) X(int8_t, half, half)
+
+#define BSIR_DECL_MM_PLAIN_T(ta, tb, fa, fb, a, c)                                                  \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_matmul_Xbias_Xdescale_##ta##_##tb##_TA##a##_TB##a##_TC##c(  \
+      bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_2d *C);
+#define BSIR_DECL_MM_PLAIN(a, c) BSIR_MATMUL_TRANSPOSES(BSIR_DECL_MM_PLAIN_T, a, c)
+#define BSIR_DECL_MM_BIAS_T(ta, tb, fa, fb, a, c, bt)                                               \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_matmul_bias_TBIAS##bt##_Xdescale_##ta##_##tb##_TA##a##_TB##a##_TC##c( \
+      bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_1d *bias, bsir_memref_2d *C);
+#define BSIR_DECL_MM_BIAS(a, c, bt) BSIR_MATMUL_TRANSPOSES(BSIR_DECL_MM_BIAS_T, a, c, bt)
+#define BSIR_DECL_MM_DESCALE_T(ta, tb, fa, fb, a, c, dt)                                            \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_matmul_Xbias_descalePerChannel_TDESCALE##dt##_##ta##_##tb##_TA##a##_TB##a##_TC##c( \
+      bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_1d *descale, bsir_memref_2d *C);            \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_matmul_Xbias_descalePerTensor_TDESCALE##dt##_##ta##_##tb##_TA##a##_TB##a##_TC##c( \
+      bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_1d *descale, bsir_memref_2d *C);
+#define BSIR_DECL_MM_DESCALE(a, c, dt) BSIR_MATMUL_TRANSPOSES(BSIR_DECL_MM_DESCALE_T, a, c, dt)
+#define BSIR_DECL_MM_BOTH_T(ta, tb, fa, fb, a, c, bt, dt)                                           \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_matmul_bias_TBIAS##bt##_descalePerChannel_TDESCALE##dt##_##ta##_##tb##_TA##a##_TB##a##_TC##c( \
+      bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_1d *bias, bsir_memref_1d *descale, bsir_memref_2d *C); \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_matmul_bias_TBIAS##bt##_descalePerTensor_TDESCALE##dt##_##ta##_##tb##_TA##a##_TB##a##_TC##c( \
+      bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_1d *bias, bsir_memref_1d *descale, bsir_memref_2d *C);
+#define BSIR_DECL_MM_BOTH(a, c, bt, dt) BSIR_MATMUL_TRANSPOSES(BSIR_DECL_MM_BOTH_T, a, c, bt, dt)
+
+BSIR_MATMUL_PLAINSETS(BSIR_DECL_MM_PLAIN)
+BSIR_MATMUL_BIASSETS(BSIR_DECL_MM_BIAS)
+BSIR_MATMUL_DESCALESETS(BSIR_DECL_MM_DESCALE)
+BSIR_MATMUL_TYPESETS(BSIR_DECL_MM_BOTH)
 
 #endif /* BSIR_B200_CIFACE_H_ */

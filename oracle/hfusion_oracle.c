@@ -1032,6 +1032,69 @@ ORC_API int orc_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t group, con
   return 0;
 }
 
+/* hivm.hir.matmul, "C = descale * (A * B + bias)" with optional transposed operands
+ * (bishengir/include/bishengir/Dialect/HIVM/IR/HIVMMacroOps.td:364-492), then what the reference inlines into the
+ * accumulator's way out (hivm.hir.fixpipe pre_relu / pre_quant, HIVMDMAOps.td:275-335, InlineFixpipe.cpp:876-884).
+ * The contraction is linalg.matmul's body as convert-linalg-to-loops runs it: both operands extended to the
+ * accumulator type (sext to i32 / extf to f32, f32 accumulation for 16-bit floats: Normalize.cpp:8224-8257),
+ * mul, add, k innermost and sequential.
+ *   acc = sum_k A[i,k] * B[k,j];  v = f32(acc + bias[j]) (int32 add for int8 operands);  v = v * scale_a[i];
+ *   v = v * descale[j] | descale[0];  relu: v = maximumf(v, 0);  C = cast_rint(v) (f16 clamped to its range,
+ *   int8 saturating, NaN -> 0); out_dt i32 (int8 operands) stores acc + bias.
+ * descale_mode: 0 none, 1 per channel, 2 per tensor. */
+static float param_f32(int dt, const void *p, int64_t i) {
+  return dt == ORC_F32 ? ((const float *)p)[i] : load_f(dt, p, i);
+}
+ORC_API int orc_matmul(int in_dt, int out_dt, int transpose_a, int transpose_b, int descale_mode, int relu, int bias_dt,
+                       int descale_dt, int64_t m, int64_t n, int64_t k, const void *a, int64_t lda, const void *b,
+                       int64_t ldb, const void *bias, const void *descale, const float *scale_a, void *out, int64_t ldo) {
+  if (in_dt != ORC_I8 && in_dt != ORC_F16 && in_dt != ORC_BF16) return -1;
+  if (descale_mode < 0 || descale_mode > 2) return -1;
+  ORC_PAR_FOR
+  for (int64_t i = 0; i < m; i++) {
+    for (int64_t j = 0; j < n; j++) {
+      float v;
+      int32_t iacc = 0;
+      if (in_dt == ORC_I8) {
+        for (int64_t kk = 0; kk < k; kk++) {
+          int32_t x = ((const int8_t *)a)[transpose_a ? kk * lda + i : i * lda + kk];
+          int32_t y = ((const int8_t *)b)[transpose_b ? j * ldb + kk : kk * ldb + j];
+          iacc = (int32_t)((uint32_t)iacc + (uint32_t)(x * y));
+        }
+        if (bias) iacc = (int32_t)((uint32_t)iacc + (uint32_t)((const int32_t *)bias)[j]);
+        v = (float)iacc;
+      } else {
+        float acc = 0.0f;
+        for (int64_t kk = 0; kk < k; kk++) {
+          float x = load_f(in_dt, a, transpose_a ? kk * lda + i : i * lda + kk);
+          float y = load_f(in_dt, b, transpose_b ? j * ldb + kk : kk * ldb + j);
+          float prod = x * y;
+          acc = acc + prod;
+        }
+        v = bias ? acc + param_f32(bias_dt, bias, j) : acc;
+      }
+      if (out_dt == ORC_I32) { ((int32_t *)out)[i * ldo + j] = iacc; continue; }
+      float sa = scale_a ? scale_a[i] : 1.0f;
+      float sw = descale_mode == 1 ? param_f32(descale_dt, descale, j) : descale_mode == 2 ? param_f32(descale_dt, descale, 0) : 1.0f;
+      v = v * sa;
+      v = v * sw;
+      if (relu) v = maximumf_(v, 0.0f);
+      switch (out_dt) {
+        case ORC_F32: ((float *)out)[i * ldo + j] = v; break;
+        case ORC_BF16: ((uint16_t *)out)[i * ldo + j] = f32_to_bf16(v); break;
+        case ORC_F16: {
+          float c = v > 65504.0f ? 65504.0f : (v < -65504.0f ? -65504.0f : v);
+          ((uint16_t *)out)[i * ldo + j] = f32_to_f16(c);
+          break;
+        }
+        case ORC_I8: ((int8_t *)out)[i * ldo + j] = (int8_t)float_to_int((double)v, ORC_I8, 0, 1); break;
+        default: break;
+      }
+    }
+  }
+  return (out_dt == ORC_F32 || out_dt == ORC_BF16 || out_dt == ORC_F16 || out_dt == ORC_I8 || (out_dt == ORC_I32 && in_dt == ORC_I8)) ? 0 : -1;
+}
+
 /* ----------------------------------------------------------------- helpers */
 /* Conversions exposed so the tests can check them against independent ones. */
 ORC_API float orc_bf16_to_f32(uint16_t h) { return bf16_to_f32(h); }

@@ -356,6 +356,29 @@ def matmul_w8a8(a, b, sa=None, sw=None, transpose_b=False, out_dt=BF16, want_acc
     return (out, acc) if want_acc else out
 
 
+def matmul(in_dt, a, b, out_dt, transpose_a=False, transpose_b=False, bias=None, bias_dt=None, descale=None,
+           descale_dt=F32, descale_mode=0, scale_a=None, relu=False):
+    """hivm.hir.matmul + fixpipe (see orc_matmul).  a: [m,k] ([k,m] with transpose_a), b: [k,n] ([n,k] with
+    transpose_b), in the storage of in_dt (int8, or uint16 bit patterns for f16 / bf16); bias / descale in the
+    storage of their dtypes.  Returns C in the storage of out_dt."""
+    a, b = _c(a, in_dt), _c(b, in_dt)
+    m, k = (a.shape[1], a.shape[0]) if transpose_a else a.shape
+    n = b.shape[0] if transpose_b else b.shape[1]
+    out = np.empty((m, n), _NP[out_dt])
+    if bias is not None:
+        bias_dt = bias_dt if bias_dt is not None else (I32 if in_dt == I8 else F32)
+        bias = _c(bias, bias_dt)
+    if descale is not None:
+        descale = _c(descale, descale_dt)
+    sa = None if scale_a is None else np.ascontiguousarray(scale_a, dtype=np.float32)
+    _chk(lib().orc_matmul(in_dt, out_dt, int(bool(transpose_a)), int(bool(transpose_b)), int(descale_mode), int(bool(relu)),
+                          int(bias_dt if bias_dt is not None else F32), int(descale_dt), _i64(m), _i64(n), _i64(k), _p(a),
+                          _i64(a.shape[1]), _p(b), _i64(b.shape[1]), _p(bias) if bias is not None else None,
+                          _p(descale) if descale is not None else None, _p(sa) if sa is not None else None, _p(out), _i64(n)),
+         "matmul")
+    return out
+
+
 def matmul_w4a16(a_bits, qweight, scales_bits, zeros, group=128):
     a = _c(a_bits, BF16)
     qw = _c(qweight, I32)
