@@ -655,7 +655,8 @@ class MatmulDesc(C.Structure):
                 ("a", C.c_void_p), ("lda", C.c_int64), ("batch_stride_a", C.c_int64),
                 ("b", C.c_void_p), ("ldb", C.c_int64), ("batch_stride_b", C.c_int64),
                 ("bias", C.c_void_p), ("descale", C.c_void_p), ("scale_a", C.c_void_p),
-                ("out", C.c_void_p), ("ldo", C.c_int64), ("batch_stride_out", C.c_int64)]
+                ("out", C.c_void_p), ("ldo", C.c_int64), ("batch_stride_out", C.c_int64),
+                ("n_peers", C.c_int32), ("peer_out", C.POINTER(C.c_void_p))]
 
 
 DESCALE_MODE = {"DescaleNull": 0, "DescalePerChannel": 1, "DescalePerTensor": 2, None: 0}
@@ -664,7 +665,7 @@ DESCALE_MODE = {"DescaleNull": 0, "DescalePerChannel": 1, "DescalePerTensor": 2,
 def matmul(a: torch.Tensor, b: torch.Tensor, *, transpose_a: bool = False, transpose_b: bool = False,
            bias: Optional[torch.Tensor] = None, descale: Optional[torch.Tensor] = None, descale_mode: Optional[str] = None,
            scale_a: Optional[torch.Tensor] = None, relu: bool = False, out_dtype: Optional[torch.dtype] = None,
-           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+           out: Optional[torch.Tensor] = None, peer_out: Optional[Sequence[int]] = None, ldo: Optional[int] = None):
     """``hivm.hir.matmul`` / ``linalg.matmul`` (2-D) or ``batch_matmul`` (3-D operands):
     ``C = cast(relu(descale * (A @ B + bias) * scale_a))``.  Operands int8 (int32 accumulation), f16 or bf16 (f32
     accumulation); ``a_transpose`` / ``b_transpose`` as the op's unit attributes; ``descale_mode`` with the reference's
@@ -679,10 +680,16 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, transpose_a: bool = False, trans
     m, k = (a3.shape[2], a3.shape[1]) if transpose_a else (a3.shape[1], a3.shape[2])
     n = b3.shape[1] if transpose_b else b3.shape[2]
     if out_dtype is None:
-        out_dtype = torch.float16 if a.dtype == torch.int8 else a.dtype
-    if out is None:
-        out = torch.empty((batch, m, n) if batched else (m, n), dtype=out_dtype, device=a.device)
-    o3 = out if out.dim() == 3 else out.unsqueeze(0)
+        out_dtype = out.dtype if out is not None else (torch.float16 if a.dtype == torch.int8 else a.dtype)
+    if peer_out is not None:
+        # one-sided N-sharding: device addresses of this rank's block in every rank's output buffer, row pitch ldo
+        if batched or ldo is None:
+            raise BsirError(-9, "matmul: peer_out needs 2-D operands and the row pitch ldo of the peers' buffers")
+        o3 = None
+    else:
+        if out is None:
+            out = torch.empty((batch, m, n) if batched else (m, n), dtype=out_dtype, device=a.device)
+        o3 = out if out.dim() == 3 else out.unsqueeze(0)
     if descale is not None and descale_mode is None:
         descale_mode = "DescalePerTensor" if descale.numel() == 1 else "DescalePerChannel"
     d = MatmulDesc()
@@ -699,15 +706,26 @@ def matmul(a: torch.Tensor, b: torch.Tensor, *, transpose_a: bool = False, trans
     d.bias = bias.data_ptr() if bias is not None else None
     d.descale = descale.data_ptr() if descale is not None else None
     d.scale_a = scale_a.data_ptr() if scale_a is not None else None
-    d.out, d.ldo, d.batch_stride_out = o3.data_ptr(), (o3.stride(1) if o3.shape[1] > 1 else o3.shape[2]), (o3.stride(0) if batch > 1 else 0)
+    if o3 is not None:
+        d.out, d.ldo, d.batch_stride_out = o3.data_ptr(), (o3.stride(1) if o3.shape[1] > 1 else o3.shape[2]), (o3.stride(0) if batch > 1 else 0)
+    else:
+        arr = (C.c_void_p * len(peer_out))(*[int(q) for q in peer_out])
+        d.out, d.ldo, d.batch_stride_out, d.n_peers, d.peer_out = None, int(ldo), 0, len(peer_out), arr
     _check(lib().bsir_matmul(C.byref(d), _stream()))
     return out
 
 
 def matmul_w4a16(a: torch.Tensor, qweight: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor,
-                 group: int = 128, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 group: int = 128, out: Optional[torch.Tensor] = None, peer_out: Optional[Sequence[int]] = None,
+                 ldo: Optional[int] = None):
     m, k = a.shape
     n = qweight.shape[1]
+    if peer_out is not None:      # one-sided N-sharding: this rank's block of every rank's output buffer
+        arr = (C.c_void_p * len(peer_out))(*[int(q) for q in peer_out])
+        _check(lib().bsir_matmul_w4a16_peers(C.c_int64(m), C.c_int64(n), C.c_int64(k), C.c_int64(group), _ptr(a),
+                                             C.c_int64(a.stride(0)), _ptr(qweight), _ptr(scales), _ptr(zeros), C.c_int32(len(peer_out)),
+                                             arr, C.c_int64(int(ldo)), _stream()))
+        return None
     out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device) if out is None else out
     _check(lib().bsir_matmul_w4a16(C.c_int64(m), C.c_int64(n), C.c_int64(k), C.c_int64(group), _ptr(a),
                                    C.c_int64(a.stride(0)), _ptr(qweight), _ptr(scales), _ptr(zeros), _ptr(out),

@@ -86,3 +86,26 @@ def gather_rows(local: torch.Tensor, rows_total: int, group=None) -> torch.Tenso
     parts = [torch.empty_like(padded) for _ in ranges]
     dist.all_gather(parts, padded, group=group)
     return torch.cat([p[: hi - lo] for p, (lo, hi) in zip(parts, ranges)], dim=0)
+
+
+# ----------------------------------------------------------------------------------------- N-sharded GEMM steps
+def w8a8_allgather_step(bsir, a, w_local, scale_a, scale_b_local, local_out, gathered, group=None):
+    """One step of the N-sharded W8A8 GEMM the plain way: local GEMM into [M, N/G], NCCL all-gather into
+    [G, M, N/G].  `gathered` is that buffer; `gathered.permute(1, 0, 2).reshape(M, N)` is C."""
+    bsir.matmul_w8a8(a, w_local, scale_a, scale_b_local, out=local_out)
+    dist.all_gather_into_tensor(gathered.view(-1, local_out.shape[1]), local_out, group=group)
+    return gathered
+
+
+def w8a8_onesided_step(bsir, a, w_local, scale_a, scale_b_local, buf, n_total, col0):
+    """The same step one-sided: the GEMM's epilogue stores this rank's column block [M, N/G] straight into every
+    rank's [M, N] buffer (`buf`, a bsir.peer.PeerBuffer), then one flag exchange; afterwards `buf.tensor((M, N),
+    dtype)` holds all of C on every rank."""
+    bsir.matmul(a, w_local, scale_a=scale_a, descale=scale_b_local, descale_mode="DescalePerChannel",
+                out_dtype=__import__("torch").bfloat16, peer_out=buf.block_ptrs(col0 * 2), ldo=n_total)
+    buf.signal_wait()
+
+
+def w4a16_onesided_step(bsir, a, qw_local, scales_local, zeros_local, buf, n_total, col0, group_size=128):
+    bsir.matmul_w4a16(a, qw_local, scales_local, zeros_local, group=group_size, peer_out=buf.block_ptrs(col0 * 2), ldo=n_total)
+    buf.signal_wait()

@@ -63,7 +63,12 @@ struct GemmParams {
   int *err;
   int m_tiles, n_tiles, k_blocks;
   int tma_out;   // 1: the output tile goes through shared memory and TMA stores (16-bit outputs)
+  int n_peers;   // > 0: every store of C goes to each of peer[0 .. n_peers) instead of `out` (one-sided N-sharding)
+  void *peer[8];
 };
+// destination d of the output: the peers' buffers when there are any, else `out`
+__device__ __forceinline__ int out_count(const GemmParams &p) { return p.n_peers > 0 ? p.n_peers : 1; }
+__device__ __forceinline__ void *out_base(const GemmParams &p, int d) { return p.n_peers > 0 ? p.peer[d] : p.out; }
 
 __device__ __forceinline__ float load_f32_as(const void *p, int32_t dtype, int64_t i) {
   if (dtype == BSIR_F16) return __half2float(__ushort_as_half(static_cast<const unsigned short *>(p)[i]));
@@ -225,14 +230,16 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const CUtenso
         if (lane == 0) tma_store_2d(tmap_out, static_cast<int>(col0), static_cast<int>(row_warp0), stage_addr + b * kEpiStageBytes);
         ++nstores;
       } else if (row_ok) {
-        uint16_t *dst = static_cast<uint16_t *>(p.out) + row * p.ldo + col0;
-        if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        for (int d = 0; d < out_count(p); ++d) {
+          uint16_t *dst = static_cast<uint16_t *>(out_base(p, d)) + row * p.ldo + col0;
+          if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
-          for (int j = 0; j < 16; j += 4)
-            *reinterpret_cast<uint4 *>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
-        } else {
-          for (int j = 0; j < 32 && col0 + j < p.n; ++j)
-            dst[j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu));
+            for (int j = 0; j < 16; j += 4)
+              *reinterpret_cast<uint4 *>(dst + 2 * j) = make_uint4(packed[j], packed[j + 1], packed[j + 2], packed[j + 3]);
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.n; ++j)
+              dst[j] = static_cast<uint16_t>((j & 1) ? (packed[j >> 1] >> 16) : (packed[j >> 1] & 0xffffu));
+          }
         }
       }
     } else if (row_ok) {
@@ -247,16 +254,16 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const CUtenso
             w |= sat_i8_bits(scale_relu(acc_plus_bias<KIND>(r[j + e], bias_s[c0 + j + e]), sa, sw_s[c0 + j + e], p.relu)) << (8 * e);
           packed[j >> 2] = w;
         }
-        uint8_t *dst = static_cast<uint8_t *>(p.out) + row * p.ldo + col0;
-        if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-          *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-        } else {
-          for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = static_cast<uint8_t>(packed[j >> 2] >> (8 * (j & 3)));
+        for (int d = 0; d < out_count(p); ++d) {
+          uint8_t *dst = static_cast<uint8_t *>(out_base(p, d)) + row * p.ldo + col0;
+          if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+            *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+          } else {
+            for (int j = 0; j < 32 && col0 + j < p.n; ++j) dst[j] = static_cast<uint8_t>(packed[j >> 2] >> (8 * (j & 3)));
+          }
         }
       } else {
-        uint32_t *dst = static_cast<uint32_t *>(p.out) + row * p.ldo + col0;
-        const bool vec = full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0;
 #pragma unroll
         for (int j = 0; j < 32; j += 4) {
           uint32_t o[4];
@@ -265,12 +272,15 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const CUtenso
             if (p.out_dtype == BSIR_I32) o[e] = r[j + e] + bias_s[c0 + j + e];
             else o[e] = __float_as_uint(scale_relu(acc_plus_bias<KIND>(r[j + e], bias_s[c0 + j + e]), sa, sw_s[c0 + j + e], p.relu));
           }
-          if (vec) {
-            *reinterpret_cast<uint4 *>(dst + j) = make_uint4(o[0], o[1], o[2], o[3]);
-          } else {
+          for (int d = 0; d < out_count(p); ++d) {
+            uint32_t *dst = static_cast<uint32_t *>(out_base(p, d)) + row * p.ldo + col0;
+            if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+              *reinterpret_cast<uint4 *>(dst + j) = make_uint4(o[0], o[1], o[2], o[3]);
+            } else {
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-              if (col0 + j + e < p.n) dst[j + e] = o[e];
+              for (int e = 0; e < 4; ++e)
+                if (col0 + j + e < p.n) dst[j + e] = o[e];
+            }
           }
         }
       }
@@ -626,7 +636,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             } else {
               bits = static_cast<uint16_t>(pack_bf16x2(f, 0.0f) & 0xffffu);
             }
-            static_cast<uint16_t *>(p.out)[row * p.ldo + col] = bits;
+            for (int d = 0; d < out_count(p); ++d) static_cast<uint16_t *>(out_base(p, d))[row * p.ldo + col] = bits;
           }
         }
       }
@@ -874,7 +884,7 @@ __global__ void __launch_bounds__(256) gemm_simple_kernel(GemmParams p, const vo
     else bias_bits = __float_as_uint(load_f32_as(p.bias, p.bias_dtype, col));
   }
   if (p.out_dtype == BSIR_I32) {
-    static_cast<uint32_t *>(p.out)[row * p.ldo + col] = acc_bits + bias_bits;
+    for (int d = 0; d < out_count(p); ++d) static_cast<uint32_t *>(out_base(p, d))[row * p.ldo + col] = acc_bits + bias_bits;
     return;
   }
   const float sa = p.scale_a ? p.scale_a[row] : 1.0f;
@@ -882,10 +892,13 @@ __global__ void __launch_bounds__(256) gemm_simple_kernel(GemmParams p, const vo
   if (p.descale && p.descale_mode == BSIR_DESCALE_PER_CHANNEL) sw = load_f32_as(p.descale, p.descale_dtype, col);
   else if (p.descale && p.descale_mode == BSIR_DESCALE_PER_TENSOR) sw = load_f32_as(p.descale, p.descale_dtype, 0);
   const float f = scale_relu(acc_plus_bias<KIND>(acc_bits, bias_bits), sa, sw, p.relu);
-  if (p.out_dtype == BSIR_F16) static_cast<uint16_t *>(p.out)[row * p.ldo + col] = __half_as_ushort(__float2half_rn(fminf(fmaxf(f, -65504.0f), 65504.0f)));
-  else if (p.out_dtype == BSIR_BF16) static_cast<uint16_t *>(p.out)[row * p.ldo + col] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
-  else if (p.out_dtype == BSIR_I8) static_cast<uint8_t *>(p.out)[row * p.ldo + col] = static_cast<uint8_t>(sat_i8_bits(f));
-  else static_cast<float *>(p.out)[row * p.ldo + col] = f;
+  for (int d = 0; d < out_count(p); ++d) {
+    void *ob = out_base(p, d);
+    if (p.out_dtype == BSIR_F16) static_cast<uint16_t *>(ob)[row * p.ldo + col] = __half_as_ushort(__float2half_rn(fminf(fmaxf(f, -65504.0f), 65504.0f)));
+    else if (p.out_dtype == BSIR_BF16) static_cast<uint16_t *>(ob)[row * p.ldo + col] = __bfloat16_as_ushort(__float2bfloat16_rn(f));
+    else if (p.out_dtype == BSIR_I8) static_cast<uint8_t *>(ob)[row * p.ldo + col] = static_cast<uint8_t>(sat_i8_bits(f));
+    else static_cast<float *>(ob)[row * p.ldo + col] = f;
+  }
 }
 
 // ------------------------------------------------------------------ host side
@@ -1008,7 +1021,7 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
     CUtensorMap ta, tb, tout;
     memset(&tout, 0, sizeof(tout));
     const bool out16 = p.out_dtype == BSIR_BF16 || p.out_dtype == BSIR_F16;
-    p.tma_out = (p.out && out16 && aligned_to(p.out, 16) && p.ldo % 8 == 0 &&
+    p.tma_out = (p.out && p.n_peers == 0 && out16 && aligned_to(p.out, 16) && p.ldo % 8 == 0 &&
                  make_out_tmap(&tout, p.out, static_cast<uint64_t>(n), static_cast<uint64_t>(m), static_cast<uint64_t>(p.ldo))) ? 1 : 0;
     const int bn = pick_bn(m, n, device_info().sm_count > 0 ? device_info().sm_count : 148, b_mn);
     const uint32_t kr = static_cast<uint32_t>(kBK / es);
@@ -1117,7 +1130,10 @@ extern "C" int32_t bsir_matmul(const bsir_matmul_desc *d, void *stream) {
     return fail(BSIR_ERR_DTYPE, "matmul: out dtype %d (f16, bf16, f32, i8; i32 for an int8 product)", od);
   if (d->m < 0 || d->n < 0 || d->k < 0 || d->batch < 0) return fail(BSIR_ERR_SHAPE, "matmul: m=%lld n=%lld k=%lld batch=%lld", (long long)d->m, (long long)d->n, (long long)d->k, (long long)d->batch);
   if (d->m == 0 || d->n == 0 || d->batch == 0) return BSIR_OK;
-  if (!d->out || (d->k > 0 && (!d->a || !d->b))) return fail(BSIR_ERR_NULL, "matmul: null operand");
+  if (d->n_peers < 0 || d->n_peers > 8 || (d->n_peers > 0 && !d->peer_out)) return fail(BSIR_ERR_ARGS, "matmul: n_peers %d (0..8)", d->n_peers);
+  if ((d->n_peers == 0 && !d->out) || (d->k > 0 && (!d->a || !d->b))) return fail(BSIR_ERR_NULL, "matmul: null operand");
+  for (int i = 0; i < d->n_peers; ++i)
+    if (!d->peer_out[i] || !aligned_to(d->peer_out[i], dtype_bytes(d->out_dtype))) return fail(BSIR_ERR_NULL, "matmul: peer_out[%d]", i);
   if (d->m > 0x7fffffffLL || d->n > 0x7fffffffLL || d->k > 0x7fffffffLL) return fail(BSIR_ERR_SHAPE, "matmul: dimension exceeds int32");
   if (d->lda < (d->transpose_a ? d->m : d->k) || d->ldb < (d->transpose_b ? d->k : d->n) || d->ldo < d->n)
     return fail(BSIR_ERR_STRIDE, "matmul: leading dimension too small");
@@ -1128,7 +1144,7 @@ extern "C" int32_t bsir_matmul(const bsir_matmul_desc *d, void *stream) {
     return fail(BSIR_ERR_DTYPE, "matmul: bias dtype %d (i32 with int8 operands, f32 / f16 / bf16 otherwise)", d->bias_dtype);
   const int es = int_in ? 1 : 2;
   const int os = dtype_bytes(od);
-  if (!aligned_to(d->a, es) || !aligned_to(d->b, es) || !aligned_to(d->out, os) || !aligned_to(d->scale_a, 4) ||
+  if (!aligned_to(d->a, es) || !aligned_to(d->b, es) || (d->out && !aligned_to(d->out, os)) || !aligned_to(d->scale_a, 4) ||
       (d->bias && !aligned_to(d->bias, dtype_bytes(d->bias_dtype))) ||
       (d->descale && d->descale_mode != BSIR_DESCALE_NULL && !aligned_to(d->descale, dtype_bytes(d->descale_dtype))))
     return fail(BSIR_ERR_ALIGN, "matmul: misaligned");
@@ -1142,12 +1158,18 @@ extern "C" int32_t bsir_matmul(const bsir_matmul_desc *d, void *stream) {
   p.relu = d->relu ? 1 : 0;
   p.ldo = d->ldo; p.out_dtype = od;
   p.err = device_error_word();
+  p.n_peers = d->n_peers;
+  // the W8A8 form of the epilogue (what the decode kernel serves): f32 scales, no bias, no relu, 16-bit output
+  const bool classic = int_in && !d->bias && !d->relu && (od == BSIR_BF16 || od == BSIR_F16) && !d->transpose_a &&
+                       (d->descale_mode == BSIR_DESCALE_NULL || (d->descale_mode == BSIR_DESCALE_PER_CHANNEL && d->descale_dtype == BSIR_F32));
   for (int64_t e = 0; e < d->batch; ++e) {
-    p.out = static_cast<char *>(d->out) + e * d->batch_stride_out * os;
+    p.out = d->n_peers > 0 ? d->peer_out[0] : static_cast<char *>(d->out) + e * d->batch_stride_out * os;
+    for (int i = 0; i < d->n_peers; ++i) p.peer[i] = static_cast<char *>(d->peer_out[i]) + e * d->batch_stride_out * os;
+    if (d->n_peers > 0) p.out = p.peer[0];
     const Operands o{static_cast<const char *>(d->a) + e * d->batch_stride_a * es, d->lda, d->transpose_a ? 1 : 0,
                      static_cast<const char *>(d->b) + e * d->batch_stride_b * es, d->ldb, d->transpose_b ? 1 : 0};
     int32_t rc;
-    if (in == BSIR_I8) rc = run_gemm<KI8>(p, o, false, st);
+    if (in == BSIR_I8) rc = run_gemm<KI8>(p, o, classic, st);
     else if (in == BSIR_BF16) rc = run_gemm<KBF16>(p, o, false, st);
     else rc = run_gemm<KF16>(p, o, false, st);
     if (rc != BSIR_OK) return rc;

@@ -39,7 +39,13 @@ struct W4Params {
   const uint32_t *zeros;
   uint16_t *out;
   int64_t ldo;
+  int n_peers;          // > 0: every store of the result goes to each of peer[0 .. n_peers) instead of `out`
+  uint16_t *peer[8];
 };
+__device__ __forceinline__ void store_out(const W4Params &p, int64_t index, uint16_t bits) {
+  if (p.n_peers == 0) { p.out[index] = bits; return; }
+  for (int d = 0; d < p.n_peers; ++d) p.peer[d][index] = bits;
+}
 
 __device__ __forceinline__ void mma_bf16_16816(float *c, const uint32_t *a, uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -279,7 +285,7 @@ __global__ void __launch_bounds__(kWarps * 32, NP == 1 ? 3 : 2) w4a16_mma_kernel
     float s = 0.0f;
 #pragma unroll
     for (int wq = 0; wq < kWarps; ++wq) s += red[wq][r][c];
-    p.out[(m0 + r) * p.ldo + col_base + c] = __bfloat16_as_ushort(__float2bfloat16_rn(s));
+    store_out(p, (m0 + r) * p.ldo + col_base + c, __bfloat16_as_ushort(__float2bfloat16_rn(s)));
   }
 }
 
@@ -585,7 +591,7 @@ __global__ void __launch_bounds__(kTcThreads, 1)
         if (n_ok) {
 #pragma unroll
           for (int mm = 0; mm < 16; ++mm)
-            if (mm < rows_left) p.out[(m0 + mm) * p.ldo + n] = __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[mm])));
+            if (mm < rows_left) store_out(p, (m0 + mm) * p.ldo + n, __bfloat16_as_ushort(__float2bfloat16_rn(__uint_as_float(r[mm]))));
         }
       }
     }
@@ -614,7 +620,7 @@ __global__ void __launch_bounds__(128) w4a16_plain_kernel(W4Params p, int64_t m0
     const float av = __uint_as_float(static_cast<uint32_t>(p.a[row * p.lda + kk]) << 16);
     acc = __fmaf_rn(av, wv, acc);
   }
-  p.out[row * p.ldo + c] = __bfloat16_as_ushort(__float2bfloat16_rn(acc));
+  store_out(p, row * p.ldo + c, __bfloat16_as_ushort(__float2bfloat16_rn(acc)));
 }
 
 // ------------------------------------------------------------------ host helpers for the tcgen05 path
@@ -668,10 +674,14 @@ bool make_act_tmap(CUtensorMap *map, const uint16_t *a, int64_t m, int64_t k, in
 
 using namespace bsir;
 
-extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t group, const void *a, int64_t lda,
-                                     const int32_t *qweight, const void *scales, const int32_t *zeros, void *out,
-                                     int64_t ldo, void *stream) {
+static int32_t matmul_w4a16_impl(int64_t m, int64_t n, int64_t k, int64_t group, const void *a, int64_t lda,
+                                 const int32_t *qweight, const void *scales, const int32_t *zeros, void *out,
+                                 int64_t ldo, int32_t n_peers, void *const *peer_out, void *stream) {
   clear_error();
+  if (n_peers < 0 || n_peers > 8 || (n_peers > 0 && !peer_out)) return fail(BSIR_ERR_ARGS, "matmul_w4a16: n_peers %d (0..8)", n_peers);
+  for (int i = 0; i < n_peers; ++i)
+    if (!peer_out[i] || !aligned_to(peer_out[i], 2)) return fail(BSIR_ERR_NULL, "matmul_w4a16: peer_out[%d]", i);
+  if (n_peers > 0) out = peer_out[0];
   if (m < 0 || n < 0 || k < 0) return fail(BSIR_ERR_SHAPE, "matmul_w4a16: m=%lld n=%lld k=%lld", (long long)m, (long long)n, (long long)k);
   if (group <= 0 || group % 32 || k % group || n % 8)
     return fail(BSIR_ERR_SHAPE, "matmul_w4a16: need group %% 32 == 0, k %% group == 0, n %% 8 == 0 (group=%lld k=%lld n=%lld)",
@@ -684,7 +694,8 @@ extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t gr
   cudaStream_t st = resolve_stream(stream);
   W4Params p{m, n, k, group, static_cast<const uint16_t *>(a), lda, reinterpret_cast<const uint32_t *>(qweight),
              static_cast<const uint16_t *>(scales), reinterpret_cast<const uint32_t *>(zeros),
-             static_cast<uint16_t *>(out), ldo};
+             static_cast<uint16_t *>(out), ldo, n_peers, {}};
+  for (int i = 0; i < n_peers; ++i) p.peer[i] = static_cast<uint16_t *>(peer_out[i]);
   const bool fast = k > 0 && aligned_to(a, 16) && lda % 8 == 0 && aligned_to(qweight, 16) && aligned_to(scales, 16);
   // tensor-memory path: needs sm_100, k <= 4096 (activations resident in shared memory), groups that are
   // whole 64-k chunks and a weight pitch TMA can address
@@ -727,4 +738,17 @@ extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t gr
     count_launch();
   }
   return check_launch("matmul_w4a16");
+}
+
+extern "C" int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t group, const void *a, int64_t lda,
+                                     const int32_t *qweight, const void *scales, const int32_t *zeros, void *out,
+                                     int64_t ldo, void *stream) {
+  return matmul_w4a16_impl(m, n, k, group, a, lda, qweight, scales, zeros, out, ldo, 0, nullptr, stream);
+}
+
+extern "C" int32_t bsir_matmul_w4a16_peers(int64_t m, int64_t n, int64_t k, int64_t group, const void *a, int64_t lda,
+                                           const int32_t *qweight, const void *scales, const int32_t *zeros, int32_t n_peers,
+                                           void *const *peer_out, int64_t ldo, void *stream) {
+  if (n_peers <= 0) return fail(BSIR_ERR_ARGS, "matmul_w4a16_peers: n_peers %d", n_peers);
+  return matmul_w4a16_impl(m, n, k, group, a, lda, qweight, scales, zeros, nullptr, ldo, n_peers, peer_out, stream);
 }

@@ -472,6 +472,8 @@ typedef struct bsir_matmul_desc {
   const float *scale_a;  /* [m] f32 or NULL                                                          */
   void *out;
   int64_t ldo, batch_stride_out;
+  int32_t n_peers;       /* 0: C goes to `out`.  > 0 (at most 8): C goes to every peer_out[i] instead --    */
+  void *const *peer_out; /* the same block of each rank's output buffer (N-sharded GEMM, one-sided)        */
 } bsir_matmul_desc;
 BSIR_API int32_t bsir_matmul(const bsir_matmul_desc *desc, void *stream);
 
@@ -483,6 +485,12 @@ BSIR_API int32_t bsir_matmul(const bsir_matmul_desc *desc, void *stream);
 BSIR_API int32_t bsir_matmul_w4a16(int64_t m, int64_t n, int64_t k, int64_t group, const void *a,
                                    int64_t lda, const int32_t *qweight, const void *scales,
                                    const int32_t *zeros, void *out, int64_t ldo, void *stream);
+/* The same product with the result stored into every peer_out[i] (each rank's copy of the output, already
+ * offset to this rank's column block) instead of one `out`: the one-sided form of the N-sharded GEMM. */
+BSIR_API int32_t bsir_matmul_w4a16_peers(int64_t m, int64_t n, int64_t k, int64_t group, const void *a,
+                                         int64_t lda, const int32_t *qweight, const void *scales,
+                                         const int32_t *zeros, int32_t n_peers, void *const *peer_out,
+                                         int64_t ldo, void *stream);
 
 /* ------------------------------------------------------------------------ */
 /* B2: compiled-kernel ABI                                                   */
@@ -536,6 +544,7 @@ BSIR_API int32_t bsir_launch(const char *name, uint32_t block_dim, void **args, 
  * that gave up, BSIR_DEVERR_GATHER_INDEX for a gather index outside its axis); synchronises the device.
  * 0 = clean. */
 #define BSIR_DEVERR_GATHER_INDEX 0x100
+#define BSIR_DEVERR_PEER_WAIT 0x200
 BSIR_API int32_t bsir_device_error(void);
 /* Number of kernel launches this library has enqueued in this process. */
 BSIR_API int64_t bsir_launch_count(void);
@@ -558,6 +567,26 @@ BSIR_API int64_t bsir_launch_count(void);
  * bsir_release_workspace: waits for the device, then frees every block of the current device. */
 BSIR_API int32_t bsir_reserve_workspace(int64_t bytes, void *stream);
 BSIR_API int32_t bsir_release_workspace(void);
+
+/* ------------------------------------------------------------------------ */
+/* one-sided exchange between the GPUs of a node (N-sharded GEMMs)           */
+/* ------------------------------------------------------------------------ */
+/* The reference reaches other devices through put / signal wrappers over aclshmem
+ * (bishengir/lib/Template/lib/Shmem/Shmem.cpp:27-120); here a GEMM's epilogue stores its block of C into every
+ * rank's output buffer (see peer_out in bsir_matmul_desc) and bsir_peer_signal_wait closes the step.
+ * bsir_peer_alloc: a buffer of its own allocation with 256 bytes of flags at *flags_offset_out (one uint32 per
+ * source rank, zeroed).  bsir_peer_export / _open / _close: CUDA IPC handle (64 bytes) out, mapping of another
+ * process's buffer in.  bsir_peer_signal_wait(rank, world, flag_ptrs, epoch, stream): enqueues one small kernel
+ * that stores `epoch` into flag[rank] of every peer (release, system scope: everything this stream stored
+ * before is visible first) and waits until all of this rank's own flags have reached `epoch`.  The wait gives up
+ * after about two seconds with BSIR_DEVERR_PEER_WAIT in the device error word.  flag_ptrs[r] is rank r's flag
+ * array as mapped in this process; epochs must grow from call to call.  One rank per GPU. */
+BSIR_API int32_t bsir_peer_alloc(int64_t payload_bytes, void **ptr_out, int64_t *flags_offset_out);
+BSIR_API int32_t bsir_peer_free(void *ptr);
+BSIR_API int32_t bsir_peer_export(void *ptr, void *handle64);
+BSIR_API int32_t bsir_peer_open(const void *handle64, void **ptr_out);
+BSIR_API int32_t bsir_peer_close(void *ptr);
+BSIR_API int32_t bsir_peer_signal_wait(int32_t rank, int32_t world, void *const *flag_ptrs, uint32_t epoch, void *stream);
 
 /* ------------------------------------------------------------------------ */
 /* B1: op-library symbols                                                    */
