@@ -52,6 +52,7 @@ class PeerBuffer:
             self.ptrs.append(q.value)
             self._opened.append(q.value)
         self._flag_arr = (C.c_void_p * self.world)(*[q + self.flags_offset for q in self.ptrs])
+        self._buf_arr = (C.c_void_p * self.world)(*self.ptrs)
         self.epoch = 0
         dist.barrier(group=group)          # nobody stores into a buffer its owner has not finished setting up
 
@@ -71,11 +72,16 @@ class PeerBuffer:
         """The address `byte_offset` into every rank's buffer (what `peer_out=` takes)."""
         return [q + byte_offset for q in self.ptrs]
 
+    def push(self, byte_offset: int, rows: int, row_bytes: int, pitch_bytes: int) -> None:
+        """Enqueue a copy of a block of this rank's buffer to the same place in every other rank's buffer."""
+        bsir._check(bsir.lib().bsir_peer_push(C.c_int32(self.rank), C.c_int32(self.world), self._buf_arr, C.c_int64(byte_offset),
+                                             C.c_int64(rows), C.c_int64(row_bytes), C.c_int64(pitch_bytes), bsir._stream()))
+
     def signal_wait(self) -> None:
-        """Enqueue, on the current stream: tell every peer that this rank's stores are done, wait for theirs."""
-        self.epoch += 1
+        """Enqueue, on the current stream: tell every peer that this rank's stores are done, wait for theirs.  The step
+        number is kept on the device (epoch 0 form), so the call may be captured in a CUDA graph and replayed."""
         bsir._check(bsir.lib().bsir_peer_signal_wait(C.c_int32(self.rank), C.c_int32(self.world), self._flag_arr,
-                                                    C.c_uint32(self.epoch), bsir._stream()))
+                                                    C.c_uint32(0), bsir._stream()))
 
     def close(self) -> None:
         torch.cuda.synchronize()

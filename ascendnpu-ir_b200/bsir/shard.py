@@ -97,12 +97,23 @@ def w8a8_allgather_step(bsir, a, w_local, scale_a, scale_b_local, local_out, gat
     return gathered
 
 
+ONESIDED_FUSED_MAX_ROWS = 256   # up to here the GEMM's epilogue stores into the peers itself
+
+
 def w8a8_onesided_step(bsir, a, w_local, scale_a, scale_b_local, buf, n_total, col0):
-    """The same step one-sided: the GEMM's epilogue stores this rank's column block [M, N/G] straight into every
-    rank's [M, N] buffer (`buf`, a bsir.peer.PeerBuffer), then one flag exchange; afterwards `buf.tensor((M, N),
-    dtype)` holds all of C on every rank."""
-    bsir.matmul(a, w_local, scale_a=scale_a, descale=scale_b_local, descale_mode="DescalePerChannel",
-                out_dtype=__import__("torch").bfloat16, peer_out=buf.block_ptrs(col0 * 2), ldo=n_total)
+    """The same step one-sided, C assembled in every rank's [M, N] buffer (`buf`, a bsir.peer.PeerBuffer).  Few rows:
+    the GEMM's epilogue stores this rank's column block straight into every rank's buffer.  Many rows: the GEMM writes
+    its block of its own buffer through TMA at full speed and `buf.push` copies it to the peers in a pass of its own.
+    Either way one flag exchange closes the step."""
+    import torch
+    m, nl = a.shape[0], w_local.shape[1]
+    if m <= ONESIDED_FUSED_MAX_ROWS:
+        bsir.matmul(a, w_local, scale_a=scale_a, descale=scale_b_local, descale_mode="DescalePerChannel",
+                    out_dtype=torch.bfloat16, peer_out=buf.block_ptrs(col0 * 2), ldo=n_total)
+    else:
+        mine = buf.tensor((m, n_total), torch.bfloat16)[:, col0:col0 + nl]
+        bsir.matmul_w8a8(a, w_local, scale_a, scale_b_local, out=mine)
+        buf.push(col0 * 2, m, nl * 2, n_total * 2)
     buf.signal_wait()
 
 

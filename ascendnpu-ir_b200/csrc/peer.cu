@@ -29,25 +29,52 @@ struct PeerFlags {
   uint32_t *flags[kMaxPeers];   // flags[r]: rank r's flag array (uint32 per source rank), as mapped in this process
 };
 
+// epoch == 0: the step number lives in this rank's flag page (word kEpochWord) and advances by one per launch, so
+// a launch captured in a CUDA graph exchanges a fresh epoch at every replay.  All ranks must then use this form
+// for every exchange on the buffer, so that their counters stay in step.
+constexpr int kEpochWord = 32;
+
 __global__ void peer_signal_wait_kernel(PeerFlags pf, int rank, int world, uint32_t epoch, int *err) {
+  __shared__ uint32_t e_sh;
+  if (threadIdx.x == 0) e_sh = epoch != 0u ? epoch : pf.flags[rank][kEpochWord] + 1u;
+  __syncthreads();
+  const uint32_t e = e_sh;
   const int r = threadIdx.x;
-  if (r >= world) return;
-  if (r != rank) {
+  if (r < world && r != rank) {
     __threadfence_system();   // the stores of the kernels ahead in this stream are ordered before the flag
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pf.flags[r] + rank), "r"(epoch) : "memory");
-  }
-  const uint32_t *mine = pf.flags[rank] + r;
-  if (r == rank) return;
-  const long long t0 = clock64();
-  for (uint32_t spin = 0;; ++spin) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-    if (static_cast<int32_t>(v - epoch) >= 0) return;          // flags only grow; wrap-around safe
-    if ((spin & 63u) == 63u && clock64() - t0 > 4000000000LL) {   // about two seconds
-      if (err) atomicOr(err, BSIR_DEVERR_PEER_WAIT);
-      return;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(pf.flags[r] + rank), "r"(e) : "memory");
+    const uint32_t *mine = pf.flags[rank] + r;
+    const long long t0 = clock64();
+    for (uint32_t spin = 0;; ++spin) {
+      uint32_t v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if (static_cast<int32_t>(v - e) >= 0) break;                 // flags only grow; wrap-around safe
+      if ((spin & 63u) == 63u && clock64() - t0 > 4000000000LL) {    // about two seconds
+        if (err) atomicOr(err, BSIR_DEVERR_PEER_WAIT);
+        break;
+      }
+      __nanosleep(200);
     }
-    __nanosleep(200);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && epoch == 0u) pf.flags[rank][kEpochWord] = e;
+}
+
+// Copies a [rows x row_bytes] block (row pitch `pitch` bytes, the same in every buffer) from this rank's buffer to
+// the same place in each peer's: 16-byte loads of local memory, 16-byte stores through the peer mappings, a warp on
+// 512 contiguous bytes.  Used for large blocks, where a GEMM writes its own copy through TMA at full speed and the
+// exchange is worth a pass of its own; small blocks are stored by the GEMM's epilogue directly.
+struct PushDst {
+  char *dst[kMaxPeers];
+};
+__global__ void __launch_bounds__(256) peer_push_kernel(const char *__restrict__ src, PushDst pd, int n_dst, int64_t rows,
+                                                        int64_t vec_per_row, int64_t pitch) {
+  const int64_t total = rows * vec_per_row;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / vec_per_row, c = i - r * vec_per_row;
+    const int64_t off = r * pitch + c * 16;
+    const uint4 v = *reinterpret_cast<const uint4 *>(src + off);
+    for (int d = 0; d < n_dst; ++d) *reinterpret_cast<uint4 *>(pd.dst[d] + off) = v;
   }
 }
 
@@ -96,6 +123,29 @@ int32_t bsir_peer_open(const void *handle64, void **ptr_out) {
 int32_t bsir_peer_close(void *ptr) {
   if (ptr && cudaIpcCloseMemHandle(ptr) != cudaSuccess) { cudaGetLastError(); return fail(BSIR_ERR_UNSUPPORTED, "peer_close failed"); }
   return BSIR_OK;
+}
+
+int32_t bsir_peer_push(int32_t rank, int32_t world, void *const *buffer_ptrs, int64_t byte_offset, int64_t rows, int64_t row_bytes,
+                       int64_t pitch_bytes, void *stream) {
+  clear_error();
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || !buffer_ptrs) return fail(BSIR_ERR_ARGS, "peer_push: rank %d of %d", rank, world);
+  if (rows < 0 || row_bytes < 0 || pitch_bytes < row_bytes) return fail(BSIR_ERR_SHAPE, "peer_push: rows=%lld row_bytes=%lld pitch=%lld", (long long)rows, (long long)row_bytes, (long long)pitch_bytes);
+  if (rows == 0 || row_bytes == 0 || world == 1) return BSIR_OK;
+  if (row_bytes % 16 || pitch_bytes % 16 || byte_offset % 16) return fail(BSIR_ERR_ALIGN, "peer_push: offsets and sizes must be multiples of 16 bytes");
+  PushDst pd{};
+  int n = 0;
+  for (int r = 0; r < world; ++r) {
+    if (!buffer_ptrs[r] || !aligned_to(buffer_ptrs[r], 16)) return fail(BSIR_ERR_NULL, "peer_push: buffer pointer %d", r);
+    if (r != rank) pd.dst[n++] = static_cast<char *>(buffer_ptrs[r]) + byte_offset;
+  }
+  const int64_t total = rows * (row_bytes / 16);
+  int64_t blocks = ceil_div(total, 256 * 4);
+  const int64_t cap = static_cast<int64_t>(device_info().sm_count > 0 ? device_info().sm_count : 148) * 8;
+  if (blocks > cap) blocks = cap;
+  peer_push_kernel<<<static_cast<unsigned>(blocks), 256, 0, resolve_stream(stream)>>>(static_cast<const char *>(buffer_ptrs[rank]) + byte_offset, pd, n, rows,
+                                                                                      row_bytes / 16, pitch_bytes);
+  count_launch();
+  return check_launch("peer_push");
 }
 
 int32_t bsir_peer_signal_wait(int32_t rank, int32_t world, void *const *flag_ptrs, uint32_t epoch, void *stream) {

@@ -176,6 +176,120 @@ def sustained_bf16_peak():
     return 1400.0
 
 
+def sharded_gemm_ops(torch, dist, bsir, W, rank, world, iters):
+    """N-sharded GEMMs on `world` GPUs (configurations 4 and 5): every rank holds W[:, n0:n1] and the whole of A, and C
+    [M, 14336] is reassembled on every rank (a) by an NCCL all-gather of the [M, N/G] blocks plus the copy that puts
+    them side by side, (b) one-sidedly: the GEMM's epilogue stores its block into every rank's C, a flag exchange
+    closes the step.  Each variant is one CUDA graph of `iters` steps timed with CUDA events, max over ranks; weight
+    sets are rotated so that a step does not find its weights in L2.  `t1_ms` is the same GEMM with all 14336
+    columns on one GPU, timed in the same run; efficiency = t1 / (G x t)."""
+    from bsir import peer, shard
+    res = {}
+    N, K = 14336, 4096
+
+    def timed(fn, reps=3):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        dist.barrier()
+        st = torch.cuda.Stream()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(iters):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(reps):
+            dist.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            best = float(t) if best is None else min(best, float(t))
+        del g
+        return best
+
+    def run(name, m, flops, make_full, shard_fn, gemm_local, gemm_full, gemm_peers, multiple):
+        try:
+            c0, c1 = shard.my_columns(N, rank, world, multiple)
+            nl = c1 - c0
+            full_sets = [make_full(s) for s in range(2)]
+            shard_bytes = max(1, K * nl // (2 if "w4a16" in name else 1))
+            nsets = int(min(24, max(3, (256 << 20) // shard_bytes)))
+            locs = []
+            for s_ in range(nsets):
+                full = full_sets[s_ % 2] if s_ < 2 else make_full(s_)
+                locs.append(shard_fn(full))
+                if s_ >= 2:
+                    del full
+            a_ref = full_sets[0][0]
+            out_full = [torch.empty(m, N, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+            t1 = timed(lambda i: gemm_full(full_sets[i % 2], out_full[i % 2]))
+            out_l = [torch.empty(m, nl, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+            t_local = timed(lambda i: gemm_local(locs[i % nsets], out_l[i % 2]))
+            equal = N % world == 0 and nl == N // world
+            gathered = torch.empty(world, m, nl, dtype=torch.bfloat16, device="cuda")
+            c_full = torch.empty(m, N, dtype=torch.bfloat16, device="cuda")
+
+            def step_nccl(i):
+                gemm_local(locs[i % nsets], out_l[i % 2])
+                dist.all_gather_into_tensor(gathered.view(world * m, nl), out_l[i % 2])
+                c_full.view(m, world, nl).copy_(gathered.permute(1, 0, 2))
+
+            t_nccl = timed(step_nccl) if equal else None
+            buf = peer.PeerBuffer(m * N * 2)
+            ptrs = buf.block_ptrs(c0 * 2)
+
+            def step_peer(i):
+                l = locs[i % nsets]
+                if gemm_peers is None:      # W8A8: fused epilogue stores for few rows, TMA + push pass for many
+                    shard.w8a8_onesided_step(bsir, l[0], l[2], l[1], l[3], buf, N, c0)
+                else:
+                    gemm_peers(l, ptrs)
+                    buf.signal_wait()
+
+            t_peer = timed(step_peer)
+            torch.cuda.synchronize()
+            same = bool(torch.equal(buf.tensor((m, N), torch.bfloat16)[:, c0:c1], out_l[(iters - 1) % 2])) if True else None
+            buf.close()
+            r = {"t1_ms": t1, "local_gemm_ms": t_local, "allgather_step_ms": t_nccl, "onesided_step_ms": t_peer,
+                 "allgather_share_of_step": None if t_nccl is None else max(0.0, 1.0 - t_local / t_nccl),
+                 "speedup_allgather": None if t_nccl is None else t1 / t_nccl, "speedup_onesided": t1 / t_peer,
+                 "efficiency_allgather": None if t_nccl is None else t1 / t_nccl / world, "efficiency_onesided": t1 / t_peer / world,
+                 "tops_allgather": None if t_nccl is None else flops / t_nccl / 1e9, "tops_onesided": flops / t_peer / 1e9,
+                 "onesided_block_matches_local": same, "weight_sets_rotated": nsets, "columns_per_rank": nl}
+            res[name] = r
+            del locs, full_sets, out_full, out_l, gathered, c_full
+            torch.cuda.empty_cache()
+        except Exception as e:   # one failing variant must not hide the others
+            res[name] = {"error": repr(e)[:300]}
+            try:
+                dist.barrier()
+            except Exception:
+                pass
+
+    for m in (16, 128, 4096):
+        run(f"w8a8_m{m}_nshard", m, 2 * m * K * N,
+            lambda s, m=m: W.w8a8_input(m, seed=s),                                   # (a, sa, w, sw)
+            lambda f: (f[0], f[1]) + shard.shard_w8a8_weights(f[2], f[3], rank, world)[:2],
+            lambda l, o: bsir.matmul_w8a8(l[0], l[2], l[1], l[3], out=o),
+            lambda f, o: bsir.matmul_w8a8(f[0], f[2], f[1], f[3], out=o),
+            None, 16)
+    for m in (1, 8, 16):
+        run(f"w4a16_m{m}_nshard", m, 2 * m * K * N,
+            lambda s, m=m: W.w4a16_input(m, seed=s),                                   # (a, qw, scales, zeros)
+            lambda f: (f[0],) + shard.shard_w4a16_weights(f[1], f[2], f[3], rank, world)[:3],
+            lambda l, o: bsir.matmul_w4a16(l[0], l[1], l[2], l[3], out=o),
+            lambda f, o: bsir.matmul_w4a16(f[0], f[1], f[2], f[3], out=o),
+            lambda l, ptrs: bsir.matmul_w4a16(l[0], l[1], l[2], l[3], peer_out=ptrs, ldo=N),
+            8)
+    return res
+
+
 def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters, only=None):
     """The remaining configurations, each with inputs larger than L2 or rotated buffers."""
     res = {}
@@ -491,6 +605,14 @@ def run_ours(args):
                 torch.cuda.empty_cache()
                 line["ops"] = other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters=max(3, min(args.steps, 20)),
                                         only=args.only_op)
+    if dist and world > 1 and not args.no_ops:
+        # the N-sharded GEMMs with their exchange step: every rank takes part, rank 0 reports
+        del xs, qs, ss
+        torch.cuda.empty_cache()
+        sharded = sharded_gemm_ops(torch, dist, bsir, W, rank, world, iters=max(3, min(args.steps, 20)))
+        if rank == 0:
+            line["ops"] = sharded
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if dist:
         dist.barrier()

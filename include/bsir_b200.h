@@ -580,12 +580,20 @@ BSIR_API int32_t bsir_release_workspace(void);
  * that stores `epoch` into flag[rank] of every peer (release, system scope: everything this stream stored
  * before is visible first) and waits until all of this rank's own flags have reached `epoch`.  The wait gives up
  * after about two seconds with BSIR_DEVERR_PEER_WAIT in the device error word.  flag_ptrs[r] is rank r's flag
- * array as mapped in this process; epochs must grow from call to call.  One rank per GPU. */
+ * array as mapped in this process; epochs must grow from call to call.  epoch = 0 takes the step number from a
+ * counter in this rank's flag page instead and advances it, which is the form to capture in a CUDA graph (every
+ * replay then exchanges a fresh epoch); a buffer is driven either with explicit epochs or with epoch 0 by all
+ * ranks, not a mix.  One rank per GPU. */
 BSIR_API int32_t bsir_peer_alloc(int64_t payload_bytes, void **ptr_out, int64_t *flags_offset_out);
 BSIR_API int32_t bsir_peer_free(void *ptr);
 BSIR_API int32_t bsir_peer_export(void *ptr, void *handle64);
 BSIR_API int32_t bsir_peer_open(const void *handle64, void **ptr_out);
 BSIR_API int32_t bsir_peer_close(void *ptr);
+/* Copies the block [rows x row_bytes] at byte_offset (row pitch pitch_bytes, all multiples of 16) of this rank's
+ * buffer to the same place in every other rank's buffer: for blocks large enough that the GEMM should write its
+ * own copy at full speed (TMA stores) and exchange it in a pass of its own. */
+BSIR_API int32_t bsir_peer_push(int32_t rank, int32_t world, void *const *buffer_ptrs, int64_t byte_offset, int64_t rows,
+                                int64_t row_bytes, int64_t pitch_bytes, void *stream);
 BSIR_API int32_t bsir_peer_signal_wait(int32_t rank, int32_t world, void *const *flag_ptrs, uint32_t epoch, void *stream);
 
 /* ------------------------------------------------------------------------ */

@@ -38,7 +38,7 @@ def main():
     assert np.array_equal(q.cpu().numpy(), wq[lo:hi]) and np.array_equal(s.cpu().numpy(), ws[lo:hi])
 
     # ---- W8A8, N-sharded (same seeded data on every rank)
-    for m, n, k in ((16, 1024, 512), (130, 768, 640)):
+    for m, n, k in ((16, 1024, 512), (130, 768, 640), (300, 512, 256)):      # the last one takes the TMA + push form
         g = torch.Generator(device=dev).manual_seed(m)
         a = torch.randint(-127, 128, (m, k), generator=g, device=dev, dtype=torch.int8)
         w = torch.randint(-127, 128, (k, n), generator=g, device=dev, dtype=torch.int8)
