@@ -42,7 +42,7 @@ BINARY_FN = {"vor": 0, "vand": 1, "vxor": 2, "minf": 3, "maxf": 4, "powf": 5, "m
              "max_unsigned": 107, "min_unsigned": 108}
 COMPARE_FN = {"veq": 0, "vne": 1, "vle": 2, "vlt": 3, "vge": 4, "vgt": 5, "vule": 6, "vult": 7, "vuge": 8, "vugt": 9}
 REDUCE_KIND = {"sum": 0, "prod": 1, "max": 2, "min": 3, "any": 4, "all": 5, "xori": 6, "ori": 7, "andi": 8}
-RWI_KIND = {"min": 0, "max": 1}
+RWI_KIND = {"min": 0, "max": 1, "minui": 2, "maxui": 3}
 KERNEL_KIND = {"elemwise_binary": 0, "elemwise_unary": 1, "cast": 2, "rms_norm": 3, "softmax": 4,
                "quant_per_token": 5, "reduce_with_index": 6, "reduce": 7, "matmul_w8a8": 8, "matmul_w4a16": 9}
 
@@ -194,6 +194,19 @@ def elemwise_binary(fun: str, a, b, out: Optional[torch.Tensor] = None) -> torch
     oa, ob = _operand(a, shape, ref.dtype), _operand(b, shape, ref.dtype)
     _check(lib().bsir_elemwise_binary(BINARY_FN[fun], _dt(ref), len(shape), _i64arr(shape), C.byref(oa), C.byref(ob),
                                       _ptr(out), _i64arr(out.stride()), _stream()))
+    return out
+
+
+def elemwise_ternary(fun: str, a, b, c, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``hfusion.elemwise_ternary`` {fun = fma}: a * b + c with one rounding; any operand may be a Python scalar."""
+    if fun != "fma":
+        raise BsirError(-5, "elemwise_ternary: fun must be 'fma' (select is bsir.select)")
+    ref = _first_tensor(a, b, c)
+    shape = _result_shape(a, b, c)
+    out = torch.empty(shape, dtype=ref.dtype, device=ref.device) if out is None else out
+    oa, ob, oc = (_operand(x, shape, ref.dtype) for x in (a, b, c))
+    _check(lib().bsir_elemwise_ternary(1, _dt(ref), len(shape), _i64arr(shape), C.byref(oa), C.byref(ob), C.byref(oc),
+                                       _ptr(out), _i64arr(out.stride()), _stream()))
     return out
 
 

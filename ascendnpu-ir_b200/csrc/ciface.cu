@@ -120,6 +120,82 @@ int32_t rwi_r(const char *what, int kind, int left, int dt, bsir_memref_1d *src,
                                 base_of_mut(dv, dt), static_cast<int32_t *>(base_of_mut(di, BSIR_I32)), nullptr, 0, nullptr);
 }
 
+// ---- further HIVM vector ops: descriptors unpacked onto the typed entry points
+int32_t cum_ra(const char *what, int kind, int dt, int reverse, bsir_memref_2d *src, bsir_memref_2d *dst) {
+  if (!src || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  if (src->sizes[0] != dst->sizes[0] || src->sizes[1] != dst->sizes[1]) return fail(BSIR_ERR_SHAPE, "%s: shapes differ", what);
+  if ((src->sizes[1] > 1 && (src->strides[1] != 1 || dst->strides[1] != 1))) return fail(BSIR_ERR_STRIDE, "%s: last axis must be unit-stride", what);
+  return bsir_cumulative(kind, dt, 0, reverse, 1, src->sizes[0], src->sizes[1], base_of(src, dt), src->sizes[0] > 1 ? src->strides[0] : src->sizes[1],
+                         base_of_mut(dst, dt), dst->sizes[0] > 1 ? dst->strides[0] : dst->sizes[1], nullptr);
+}
+int32_t cum_ara(const char *what, int kind, int dt, int reverse, bsir_memref_3d *src, bsir_memref_3d *dst) {
+  if (!src || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  for (int i = 0; i < 3; ++i)
+    if (src->sizes[i] != dst->sizes[i]) return fail(BSIR_ERR_SHAPE, "%s: shapes differ", what);
+  if (src->sizes[2] > 1 && (src->strides[2] != 1 || dst->strides[2] != 1)) return fail(BSIR_ERR_STRIDE, "%s: last axis must be unit-stride", what);
+  const int eb = dtype_bytes(dt);
+  for (int64_t i = 0; i < src->sizes[0]; ++i) {
+    const int32_t rc = bsir_cumulative(kind, dt, 0, reverse, 1, src->sizes[1], src->sizes[2],
+                                       static_cast<const char *>(base_of(src, dt)) + i * src->strides[0] * eb,
+                                       src->sizes[1] > 1 ? src->strides[1] : src->sizes[2],
+                                       static_cast<char *>(base_of_mut(dst, dt)) + i * dst->strides[0] * eb,
+                                       dst->sizes[1] > 1 ? dst->strides[1] : dst->sizes[2], nullptr);
+    if (rc) return rc;
+  }
+  return BSIR_OK;
+}
+int32_t sort_1d(const char *what, int dt, bsir_memref_1d *src, bsir_memref_1d *dst, bsir_memref_1d *index, bool descending) {
+  if (!src || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  if (src->sizes[0] != dst->sizes[0] || (index && index->sizes[0] != src->sizes[0])) return fail(BSIR_ERR_SHAPE, "%s: lengths differ", what);
+  if (src->sizes[0] > 1 && (src->strides[0] != 1 || dst->strides[0] != 1 || (index && index->strides[0] != 1)))
+    return fail(BSIR_ERR_STRIDE, "%s: unit strides only", what);
+  const int64_t n = src->sizes[0];
+  return bsir_sort(dt, descending ? 1 : 0, 1, n, base_of(src, dt), n, base_of_mut(dst, dt), n,
+                   index ? static_cast<int32_t *>(base_of_mut(index, BSIR_I32)) : nullptr, n, nullptr);
+}
+template <class M>
+bool dense_last(const M *m, int rank) { return m->sizes[rank - 1] <= 1 || m->strides[rank - 1] == 1; }
+int32_t interleave_1d(const char *what, int dt, bsir_memref_1d *a, bsir_memref_1d *b, bsir_memref_1d *dst) {
+  if (!a || !b || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  if (a->sizes[0] != b->sizes[0] || dst->sizes[0] != 2 * a->sizes[0]) return fail(BSIR_ERR_SHAPE, "%s: lengths do not compose", what);
+  if (!dense_last(a, 1) || !dense_last(b, 1) || !dense_last(dst, 1)) return fail(BSIR_ERR_STRIDE, "%s: unit strides only", what);
+  const void *srcs[2] = {base_of(a, dt), base_of(b, dt)};
+  return bsir_interleave(dt, 2, 1, a->sizes[0], srcs, base_of_mut(dst, dt), nullptr);
+}
+// channel `ch` of `channels` (0 = derive the count from the lengths) out of rows x (channels * cols)
+int32_t deinterleave_rows(const char *what, int dt, int ch, int channels, int64_t rows, int64_t src_cols, int64_t dst_cols, const void *src, void *dst) {
+  if (channels == 0) {
+    if (dst_cols <= 0 || src_cols % dst_cols) return fail(BSIR_ERR_SHAPE, "%s: %lld is not a multiple of %lld", what, (long long)src_cols, (long long)dst_cols);
+    channels = static_cast<int>(src_cols / dst_cols);
+  }
+  if (channels < 1 || channels > 8 || src_cols != dst_cols * channels) return fail(BSIR_ERR_SHAPE, "%s: lengths do not compose", what);
+  void *dsts[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  dsts[ch] = dst;
+  return bsir_deinterleave(dt, channels, rows, dst_cols, src, dsts, nullptr);
+}
+template <int RANK, class M>
+int32_t arange_nd(const char *what, int dt, M *dst, int64_t offset, const int64_t *strides) {
+  if (!dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  return bsir_arange(dt, RANK, dst->sizes, offset, strides, base_of_mut(dst, dt), dst->strides, nullptr);
+}
+// dst = src with its axes permuted: dst axis i is src axis perm[i]
+template <int RANK, class M>
+int32_t transpose_nd(const char *what, int dt, M *src, M *dst, const int *perm) {
+  if (!src || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  int64_t st[3] = {0, 0, 0};
+  for (int i = 0; i < RANK; ++i) {
+    if (dst->sizes[i] != src->sizes[perm[i]]) return fail(BSIR_ERR_SHAPE, "%s: shapes do not compose", what);
+    st[i] = src->strides[perm[i]];
+  }
+  return bsir_copy(dt, RANK, dst->sizes, base_of(src, dt), st, base_of_mut(dst, dt), dst->strides, nullptr);
+}
+int32_t gather_1d(const char *what, int dt, bsir_memref_1d *src, bsir_memref_1d *idx, bsir_memref_1d *dst) {
+  if (!src || !idx || !dst) return fail(BSIR_ERR_NULL, "%s: null descriptor", what);
+  if (idx->sizes[0] != dst->sizes[0]) return fail(BSIR_ERR_SHAPE, "%s: indices and dst differ in length", what);
+  if (!dense_last(src, 1) || !dense_last(idx, 1) || !dense_last(dst, 1)) return fail(BSIR_ERR_STRIDE, "%s: unit strides only", what);
+  return bsir_gather(dt, BSIR_I32, 1, src->sizes[0], dst->sizes[0], 1, base_of(src, dt), base_of(idx, BSIR_I32), base_of_mut(dst, dt), nullptr);
+}
+
 // hivm.hir.matmul library call: operands in the op's order, bias / descale optional (null = absent)
 int32_t matmul_call(const char *what, int in_dt, int out_dt, int bias_dt, int descale_dt, int descale_mode, int ta, int tb,
                     bsir_memref_2d *A, bsir_memref_2d *B, bsir_memref_1d *bias, bsir_memref_1d *descale, bsir_memref_2d *C) {
@@ -251,6 +327,80 @@ BSIR_FOREACH_CAST_WITH_TEMP(BSIR_DEF_CAST_TEMP, 1)
 BSIR_FOREACH_CAST_WITH_TEMP(BSIR_DEF_CAST_TEMP, 2)
 BSIR_FOREACH_REDUCE(BSIR_DEF_REDUCE)
 BSIR_FOREACH_REDUCE_WITH_INDEX(BSIR_DEF_REDUCE_WITH_INDEX)
+
+#define BSIR_DEF_CUM(tok, op)                                                                                                    \
+  int32_t _mlir_ciface_##op##_ra_##tok(bsir_memref_2d *src, bsir_memref_2d *dst) { clear_error(); return cum_ra(#op "_ra", BSIR_KIND_##op, BSIR_DT_##tok, 0, src, dst); } \
+  int32_t _mlir_ciface_##op##_ra_reverse_##tok(bsir_memref_2d *src, bsir_memref_2d *dst) { clear_error(); return cum_ra(#op "_ra_reverse", BSIR_KIND_##op, BSIR_DT_##tok, 1, src, dst); } \
+  int32_t _mlir_ciface_##op##_ara_##tok(bsir_memref_3d *src, bsir_memref_3d *dst) { clear_error(); return cum_ara(#op "_ara", BSIR_KIND_##op, BSIR_DT_##tok, 0, src, dst); } \
+  int32_t _mlir_ciface_##op##_ara_reverse_##tok(bsir_memref_3d *src, bsir_memref_3d *dst) { clear_error(); return cum_ara(#op "_ara_reverse", BSIR_KIND_##op, BSIR_DT_##tok, 1, src, dst); }
+#define BSIR_KIND_cumsum 0
+#define BSIR_KIND_cumprod 1
+BSIR_TYPES_CUM(BSIR_DEF_CUM, cumsum)
+BSIR_TYPES_CUM(BSIR_DEF_CUM, cumprod)
+#define BSIR_DEF_SORT(tok)                                                                                                       \
+  int32_t _mlir_ciface_sort_1d_##tok(bsir_memref_1d *src, bsir_memref_1d *dst, bsir_memref_1d *tmp, bool descending) {            \
+    (void)tmp; clear_error(); return sort_1d("sort_1d", BSIR_DT_##tok, src, dst, nullptr, descending);                            \
+  }                                                                                                                              \
+  int32_t _mlir_ciface_sort_with_index_1d_##tok(bsir_memref_1d *src, bsir_memref_1d *dst, bsir_memref_1d *index, bsir_memref_1d *tmp, bool descending) { \
+    (void)tmp; clear_error();                                                                                                    \
+    if (!index) return fail(BSIR_ERR_NULL, "sort_with_index_1d: null index descriptor");                                         \
+    return sort_1d("sort_with_index_1d", BSIR_DT_##tok, src, dst, index, descending);                                            \
+  }
+BSIR_TYPES_SORT(BSIR_DEF_SORT)
+#define BSIR_DEF_LEAVE(tok, unused)                                                                                              \
+  int32_t _mlir_ciface_interleave_1d_##tok(bsir_memref_1d *src0, bsir_memref_1d *src1, bsir_memref_1d *dst, bsir_memref_1d *temp) { \
+    (void)temp; clear_error(); return interleave_1d("interleave_1d", BSIR_DT_##tok, src0, src1, dst);                             \
+  }                                                                                                                              \
+  int32_t _mlir_ciface_deinterleave_channel_0_from_2_channels_1d_##tok(bsir_memref_1d *src, bsir_memref_1d *dst) {               \
+    clear_error();                                                                                                               \
+    if (!src || !dst || !dense_last(src, 1) || !dense_last(dst, 1)) return fail(BSIR_ERR_STRIDE, "deinterleave: null or strided descriptor"); \
+    return deinterleave_rows("deinterleave_channel_0_from_2_channels_1d", BSIR_DT_##tok, 0, 2, 1, src->sizes[0], dst->sizes[0], base_of(src, BSIR_DT_##tok), base_of_mut(dst, BSIR_DT_##tok)); \
+  }                                                                                                                              \
+  int32_t _mlir_ciface_deinterleave_channel_1_from_2_channels_1d_##tok(bsir_memref_1d *src, bsir_memref_1d *dst) {               \
+    clear_error();                                                                                                               \
+    if (!src || !dst || !dense_last(src, 1) || !dense_last(dst, 1)) return fail(BSIR_ERR_STRIDE, "deinterleave: null or strided descriptor"); \
+    return deinterleave_rows("deinterleave_channel_1_from_2_channels_1d", BSIR_DT_##tok, 1, 2, 1, src->sizes[0], dst->sizes[0], base_of(src, BSIR_DT_##tok), base_of_mut(dst, BSIR_DT_##tok)); \
+  }                                                                                                                              \
+  int32_t _mlir_ciface_deinterleave_channel_0_from_n_channels_1d_##tok(bsir_memref_1d *src, bsir_memref_1d *dst) {               \
+    clear_error();                                                                                                               \
+    if (!src || !dst || !dense_last(src, 1) || !dense_last(dst, 1)) return fail(BSIR_ERR_STRIDE, "deinterleave: null or strided descriptor"); \
+    return deinterleave_rows("deinterleave_channel_0_from_n_channels_1d", BSIR_DT_##tok, 0, 0, 1, src->sizes[0], dst->sizes[0], base_of(src, BSIR_DT_##tok), base_of_mut(dst, BSIR_DT_##tok)); \
+  }                                                                                                                              \
+  int32_t _mlir_ciface_deinterleave_channel_0_from_n_channels_2d_##tok(bsir_memref_2d *src, bsir_memref_2d *dst) {               \
+    clear_error();                                                                                                               \
+    if (!src || !dst || !dense_last(src, 2) || !dense_last(dst, 2) || src->sizes[0] != dst->sizes[0] ||                          \
+        (src->sizes[0] > 1 && (src->strides[0] != src->sizes[1] || dst->strides[0] != dst->sizes[1])))                           \
+      return fail(BSIR_ERR_STRIDE, "deinterleave_2d: null, mismatched or non-contiguous descriptor");                            \
+    return deinterleave_rows("deinterleave_channel_0_from_n_channels_2d", BSIR_DT_##tok, 0, 0, src->sizes[0], src->sizes[1], dst->sizes[1], base_of(src, BSIR_DT_##tok), base_of_mut(dst, BSIR_DT_##tok)); \
+  }
+BSIR_TYPES_LEAVE(BSIR_DEF_LEAVE, 0)
+#define BSIR_DEF_ARANGE(tok)                                                                                                     \
+  int32_t _mlir_ciface_arange_1d_##tok(bsir_memref_1d *dst, int64_t offset, int64_t stride) {                                    \
+    clear_error(); const int64_t st[1] = {stride}; return arange_nd<1>("arange_1d", BSIR_DT_##tok, dst, offset, st);              \
+  }                                                                                                                              \
+  int32_t _mlir_ciface_arange_2d_##tok(bsir_memref_2d *dst, int64_t offset, int64_t stride0, int64_t stride1) {                  \
+    clear_error(); const int64_t st[2] = {stride0, stride1}; return arange_nd<2>("arange_2d", BSIR_DT_##tok, dst, offset, st);    \
+  }                                                                                                                              \
+  int32_t _mlir_ciface_arange_3d_##tok(bsir_memref_3d *dst, int64_t offset, int64_t stride0, int64_t stride1, int64_t stride2) { \
+    clear_error(); const int64_t st[3] = {stride0, stride1, stride2}; return arange_nd<3>("arange_3d", BSIR_DT_##tok, dst, offset, st); \
+  }
+BSIR_TYPES_ARANGE(BSIR_DEF_ARANGE)
+#define BSIR_DEF_TRANSPOSE(tok)                                                                                                  \
+  int32_t _mlir_ciface_transpose_2d_with_last_axis_##tok(bsir_memref_2d *src, bsir_memref_2d *dst) {                             \
+    clear_error(); const int perm[2] = {1, 0}; return transpose_nd<2>("transpose_2d_with_last_axis", BSIR_DT_##tok, src, dst, perm); \
+  }                                                                                                                              \
+  int32_t _mlir_ciface_transpose_3d_with_last_axis_##tok(bsir_memref_3d *src, bsir_memref_3d *dst) {                             \
+    clear_error(); const int perm[3] = {2, 1, 0}; return transpose_nd<3>("transpose_3d_with_last_axis", BSIR_DT_##tok, src, dst, perm); \
+  }                                                                                                                              \
+  int32_t _mlir_ciface_transpose_3d_without_last_axis_##tok(bsir_memref_3d *src, bsir_memref_3d *dst) {                          \
+    clear_error(); const int perm[3] = {1, 0, 2}; return transpose_nd<3>("transpose_3d_without_last_axis", BSIR_DT_##tok, src, dst, perm); \
+  }
+BSIR_TYPES_TRANSPOSE(BSIR_DEF_TRANSPOSE)
+#define BSIR_DEF_GATHER(tok)                                                                                                     \
+  int32_t _mlir_ciface_gather_1d_##tok(bsir_memref_1d *src, bsir_memref_1d *indices, bsir_memref_1d *dst, bsir_memref_1d *tmp) { \
+    (void)tmp; clear_error(); return gather_1d("gather_1d", BSIR_DT_##tok, src, indices, dst);                                    \
+  }
+BSIR_TYPES_GATHER(BSIR_DEF_GATHER)
 
 #define BSIR_DEF_MM_PLAIN_T(ta, tb, fa, fb, a, c)                                                                   \
   int32_t _mlir_ciface_matmul_Xbias_Xdescale_##ta##_##tb##_TA##a##_TB##a##_TC##c(bsir_memref_2d *A, bsir_memref_2d *B, \

@@ -44,6 +44,10 @@ int *device_error_word();
 // uint32 per row of a launch, at most 65535 rows); everything else starts after them.
 constexpr size_t kScratchCounterBytes = 256 * 1024;
 
+// hfusion.reduce_with_index over integer rows / with the unsigned kinds (reduce_index_int.cu)
+int32_t reduce_with_index_int(int32_t kind, int32_t dtype, int32_t tie_break_left, int64_t rows, int64_t cols, const void *src,
+                              int64_t src_row_stride, void *dst_value, int32_t *dst_index, cudaStream_t st);
+
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
 // dtype helpers

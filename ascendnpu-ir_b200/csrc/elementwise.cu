@@ -40,6 +40,7 @@ __device__ __forceinline__ bool unary_f32(int fn, const float *x, float *r) {
     case BSIR_UNARY_LOG1P: U(log1pf(v))
     case BSIR_UNARY_EXP2: U(exp2f(v))
     case BSIR_UNARY_EXPM1: U(expm1f(v))
+    case BSIR_UNARY_ILOGB: U(logbf(v))   // floor(log2(|x|)), exactly: the exponent (Normalize.cpp:6782-6830)
     case BSIR_UNARY_ASIN: U(asinf(v))
     case BSIR_UNARY_ACOS: U(acosf(v))
     case BSIR_UNARY_ASINH: U(asinhf(v))
@@ -562,7 +563,7 @@ bool fn_is_valid(int kind, int fn, int dt) {
   if (kind == kOpUnary) {
     if (f) {
       switch (fn) {
-        case BSIR_UNARY_VNOT: case BSIR_UNARY_ABSI: case BSIR_UNARY_ILOGB: return false;
+        case BSIR_UNARY_VNOT: case BSIR_UNARY_ABSI: return false;
         default: return (fn >= 0 && fn <= 26) || (fn >= 100 && fn <= 112);
       }
     }

@@ -1159,9 +1159,13 @@ int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie_break_le
                                int64_t cols, const void *src, int64_t src_row_stride, void *dst_value,
                                int32_t *dst_index, void *workspace, int64_t workspace_bytes, void *stream) {
   clear_error();
-  if (!dtype_is_float(dtype)) return fail(BSIR_ERR_DTYPE, "reduce_with_index: dtype %d (f32, f16 or bf16)", dtype);
+  if (kind < BSIR_RWI_MIN || kind > BSIR_RWI_MAXUI) return fail(BSIR_ERR_ATTR, "reduce_with_index: kind %d", kind);
+  if (!dtype_is_float(dtype)) {
+    if (dtype == BSIR_BOOL || dtype_bytes(dtype) == 0) return fail(BSIR_ERR_DTYPE, "reduce_with_index: dtype %d", dtype);
+    return reduce_with_index_int(kind, dtype, tie_break_left, rows, cols, src, src_row_stride, dst_value, dst_index, resolve_stream(stream));
+  }
   if (kind != BSIR_RWI_MAX && kind != BSIR_RWI_MIN)
-    return fail(BSIR_ERR_ATTR, "reduce_with_index: kind %d (unsigned kinds need integer inputs)", kind);
+    return fail(BSIR_ERR_ATTR, "reduce_with_index: kind %d (the unsigned kinds take integer inputs)", kind);
   if (nan_mode != BSIR_RWI_NAN_REGION && nan_mode != BSIR_RWI_NAN_FIRST)
     return fail(BSIR_ERR_ATTR, "reduce_with_index: nan_mode %d", nan_mode);
   if (rows < 0 || cols < 0) return fail(BSIR_ERR_SHAPE, "reduce_with_index: rows=%lld cols=%lld", (long long)rows, (long long)cols);

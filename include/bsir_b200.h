@@ -230,6 +230,13 @@ BSIR_API int32_t bsir_elemwise_binary(int32_t fn, int32_t dtype, int32_t rank, c
 BSIR_API int32_t bsir_compare(int32_t fn, int32_t dtype, int32_t rank, const int64_t *sizes,
                               const bsir_operand *a, const bsir_operand *b, void *out,
                               const int64_t *out_strides, void *stream);
+/* hfusion.elemwise_ternary (yaml:193-272; TernaryFn select = 0, fma = 1, HFusionEnums.td:105-110).  fma is math.fma
+ * (HFusionOps.cpp:737-739): out = a * b + c with one rounding, f32 / f16 / bf16; select has its own entry below. */
+#define BSIR_TERNARY_SELECT 0
+#define BSIR_TERNARY_FMA 1
+BSIR_API int32_t bsir_elemwise_ternary(int32_t fn, int32_t dtype, int32_t rank, const int64_t *sizes,
+                                       const bsir_operand *a, const bsir_operand *b, const bsir_operand *c,
+                                       void *out, const int64_t *out_strides, void *stream);
 /* out = cond ? a : b; hfusion.select (HFusionOps.cpp:723-743); cond is bool bytes. */
 BSIR_API int32_t bsir_select(int32_t dtype, int32_t rank, const int64_t *sizes,
                              const bsir_operand *cond, const bsir_operand *a, const bsir_operand *b,
@@ -400,9 +407,13 @@ BSIR_API int32_t bsir_interleave(int32_t dtype, int32_t channels, int64_t rows, 
 BSIR_API int32_t bsir_deinterleave(int32_t dtype, int32_t channels, int64_t rows, int64_t cols, const void *src,
                                    void *const *dsts, void *stream);
 
-/* hivm.hir.vsort {descending, sort_axis = last} (HIVMVectorOps.td:2222-2283): every row sorted by value, with the
- * source index of each sorted element (int32).  Equal values keep their source order; -0 = +0; NaN comes after
- * every number when ascending, before every number when descending.  dst_value or dst_index may be NULL.
+/* hivm.hir.vsort / hfusion.sort {descending, sort_axis = last} (HIVMVectorOps.td:2222-2283): every row sorted by
+ * value, with the source index of each sorted element (int32).  The result is the one the reference's lowering
+ * produces (n-1 bubble passes of compare-and-swap on `cmpf ugt` / `ult`,
+ * bishengir/lib/Dialect/HFusion/Transforms/DecomposeOpInterfaceImpl.cpp:742-838; runner goldens
+ * test/Dialect/HFusion/test_sort_2d_asc.mlir:16-19): equal values keep their source order, -0 = +0, and a NaN that
+ * starts at position p of its row ends at (p + 1) mod n in either direction, the numbers filling the other places
+ * in order.  dst_value or dst_index may be NULL.
  * dtype: f32, f16, bf16, i8, i16, i32.  Rows of up to 8192 elements are sorted in shared memory by one CTA; longer
  * rows (up to 2^30 elements) keep 8 bytes per padded element in the library's device scratch. */
 BSIR_API int32_t bsir_sort(int32_t dtype, int32_t descending, int64_t rows, int64_t cols, const void *src,

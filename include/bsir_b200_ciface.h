@@ -218,6 +218,62 @@ BSIR_FOREACH_CAST_WITH_TEMP(BSIR_DECL_CAST_TEMP, 2)
 BSIR_FOREACH_REDUCE(BSIR_DECL_REDUCE)
 BSIR_FOREACH_REDUCE_WITH_INDEX(BSIR_DECL_REDUCE_WITH_INDEX)
 
+/* Library symbols of the further HIVM vector ops (declarations in bishengir/lib/Template/include/Vector/:
+ * Cumulative/CumsumUtils.h:31-49 and CumprodUtils.h, Sort/SortUtils.h:45-66, Interleave/InterleaveUtils.h:47-58,
+ * Deinterleave/DeinterleaveUtils.h:36-45, Arange/ArangeUtils.h:26-49, Transpose/TransposeUtils.h:87-120,
+ * Gather/GatherUtils.h:48-54; registered type lists in the matching lib/Template/lib/Vector .cpp files).
+ *   cumsum / cumprod _ra_<t>  (src [r, a], dst): running sum / product along the first axis; _ara_ (3-D [a, r, a]):
+ *       along the middle axis; _reverse_ from the far end
+ *   sort_1d_<t> (src, dst, tmp, descending), sort_with_index_1d_<t> (src, dst, index, tmp, descending)
+ *   interleave_1d_<t> (src0, src1, dst, temp); deinterleave_channel_{0,1}_from_2_channels_1d_<t> (src, dst),
+ *       deinterleave_channel_0_from_n_channels_{1,2}d_<t> (n = src length / dst length)
+ *   arange_{1,2,3}d_<t> (dst, offset, stride...); transpose_2d_with_last_axis_<t> (dst = src^T),
+ *       transpose_3d_with_last_axis_<t> ((a, b, c) -> (c, b, a)), transpose_3d_without_last_axis_<t> ((a, b, c) -> (b, a, c))
+ *   gather_1d_<t> (src, indices, dst, tmp): dst[i] = src[indices[i]]
+ * Scratch arguments (tmp) are accepted and unused. */
+#define BSIR_TYPES_CUM(X, ...) X(int16_t, __VA_ARGS__) X(int32_t, __VA_ARGS__) X(half, __VA_ARGS__) X(float, __VA_ARGS__)
+#define BSIR_TYPES_SORT(X) X(half) X(float)
+#define BSIR_TYPES_LEAVE(X, ...)                                                                     \
+  X(half, __VA_ARGS__) X(bfloat16_t, __VA_ARGS__) X(float, __VA_ARGS__) X(int16_t, __VA_ARGS__)     \
+  X(int32_t, __VA_ARGS__) X(uint16_t, __VA_ARGS__) X(uint32_t, __VA_ARGS__)
+#define BSIR_TYPES_ARANGE(X) X(int16_t) X(int32_t) X(half) X(float) X(int64_t)
+#define BSIR_TYPES_TRANSPOSE(X)                                                                      \
+  X(uint8_t) X(int8_t) X(uint16_t) X(int16_t) X(half) X(bfloat16_t) X(uint32_t) X(int32_t) X(float)
+#define BSIR_TYPES_GATHER(X) X(uint16_t) X(uint32_t) X(int16_t) X(int32_t) X(half) X(float) X(bfloat16_t)
+
+#define BSIR_DECL_CUM(tok, op)                                                                                       \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##op##_ra_##tok(bsir_memref_2d *src, bsir_memref_2d *dst);                   \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##op##_ra_reverse_##tok(bsir_memref_2d *src, bsir_memref_2d *dst);           \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##op##_ara_##tok(bsir_memref_3d *src, bsir_memref_3d *dst);                  \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_##op##_ara_reverse_##tok(bsir_memref_3d *src, bsir_memref_3d *dst);
+BSIR_TYPES_CUM(BSIR_DECL_CUM, cumsum)
+BSIR_TYPES_CUM(BSIR_DECL_CUM, cumprod)
+#define BSIR_DECL_SORT(tok)                                                                                          \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_sort_1d_##tok(bsir_memref_1d *src, bsir_memref_1d *dst, bsir_memref_1d *tmp, bool descending); \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_sort_with_index_1d_##tok(bsir_memref_1d *src, bsir_memref_1d *dst, bsir_memref_1d *index, \
+                                                                 bsir_memref_1d *tmp, bool descending);
+BSIR_TYPES_SORT(BSIR_DECL_SORT)
+#define BSIR_DECL_LEAVE(tok, unused)                                                                                 \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_interleave_1d_##tok(bsir_memref_1d *src0, bsir_memref_1d *src1, bsir_memref_1d *dst, bsir_memref_1d *temp); \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_deinterleave_channel_0_from_2_channels_1d_##tok(bsir_memref_1d *src, bsir_memref_1d *dst); \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_deinterleave_channel_1_from_2_channels_1d_##tok(bsir_memref_1d *src, bsir_memref_1d *dst); \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_deinterleave_channel_0_from_n_channels_1d_##tok(bsir_memref_1d *src, bsir_memref_1d *dst); \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_deinterleave_channel_0_from_n_channels_2d_##tok(bsir_memref_2d *src, bsir_memref_2d *dst);
+BSIR_TYPES_LEAVE(BSIR_DECL_LEAVE, 0)
+#define BSIR_DECL_ARANGE(tok)                                                                                        \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_arange_1d_##tok(bsir_memref_1d *dst, int64_t offset, int64_t stride);        \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_arange_2d_##tok(bsir_memref_2d *dst, int64_t offset, int64_t stride0, int64_t stride1); \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_arange_3d_##tok(bsir_memref_3d *dst, int64_t offset, int64_t stride0, int64_t stride1, int64_t stride2);
+BSIR_TYPES_ARANGE(BSIR_DECL_ARANGE)
+#define BSIR_DECL_TRANSPOSE(tok)                                                                                     \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_transpose_2d_with_last_axis_##tok(bsir_memref_2d *src, bsir_memref_2d *dst); \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_transpose_3d_with_last_axis_##tok(bsir_memref_3d *src, bsir_memref_3d *dst); \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_transpose_3d_without_last_axis_##tok(bsir_memref_3d *src, bsir_memref_3d *dst);
+BSIR_TYPES_TRANSPOSE(BSIR_DECL_TRANSPOSE)
+#define BSIR_DECL_GATHER(tok)                                                                                        \
+  BSIR_API BSIR_CIFACE_RET _mlir_ciface_gather_1d_##tok(bsir_memref_1d *src, bsir_memref_1d *indices, bsir_memref_1d *dst, bsir_memref_1d *tmp);
+BSIR_TYPES_GATHER(BSIR_DECL_GATHER)
+
 /* GEMM library symbols.  Names as the reference's name builder spells them
  * (bishengir/lib/Dialect/HIVM/IR/LibraryFunctionOpInterface/LibraryFunctionOpInterfaceImpl.cpp:470-505,
  * checked by bishengir/test/Conversion/HIVMToStandard/HIVMToStandard/matmul.mlir:13-55):

@@ -216,6 +216,7 @@ static int unary_f32(int fn, float x, float *out) {
   case 14: *out = log1pf(x); return 0;
   case 15: *out = exp2f(x); return 0;
   case 16: *out = expm1f(x); return 0;
+  case 17: *out = logbf(x); return 0;                    /* ilogb = floor(log2(|x|)) (Normalize.cpp:6782-6830): the exponent, -inf at 0 */
   case 18: *out = asinf(x); return 0;
   case 19: *out = acosf(x); return 0;
   case 20: *out = asinhf(x); return 0;
@@ -364,6 +365,18 @@ ORC_API int orc_elemwise_binary(int fn, int dt, const void *a, int64_t a_stride,
     }
   }
   return rc;
+}
+
+/* hfusion.elemwise_ternary {fma} (HFusionNamedStructuredOps.yaml:193-272; TernaryFn fma = 1, HFusionEnums.td:105-110):
+ * the region is math.fma (HFusionOps.cpp:737-739), one rounding; 16-bit floats compute in f32 and round once more on
+ * the way out like every other elementwise op. */
+ORC_API int orc_elemwise_fma(int dt, const void *a, int64_t a_stride, const void *b, int64_t b_stride, const void *c,
+                             int64_t c_stride, void *out, int64_t n) {
+  if (!is_float(dt)) return -1;
+  ORC_PAR_FOR
+  for (int64_t i = 0; i < n; i++)
+    store_f(dt, out, i, fmaf(load_f(dt, a, i * a_stride), load_f(dt, b, i * b_stride), load_f(dt, c, i * c_stride)));
+  return 0;
 }
 
 /* hfusion.compare (yaml:275-322; HFusionOps.cpp:642-720): float predicates are
@@ -773,7 +786,25 @@ ORC_API int orc_reduce_first_axis(int kind, int dt, const void *src, int64_t row
 ORC_API int orc_reduce_with_index(int kind, int dt, int tie_break_left, int nan_mode, const void *src,
                                   int64_t rows, int64_t cols, int64_t row_stride, void *dst_value,
                                   int32_t *dst_index) {
-  if (kind != 0 && kind != 1) return -1;
+  if (kind < 0 || kind > 3 || (is_float(dt) && kind > 1)) return -1;
+  if (!is_float(dt) && (kind > 1 || is_unsigned(dt))) {
+    /* minui / maxui (HFusionEnums.td:303-311): the same bits compared as unsigned numbers (cmpi ult / ugt) */
+    int is_max = kind & 1, bits = 8 * dtype_size(dt);
+    uint64_t mask = bits == 64 ? ~0ull : ((1ull << bits) - 1ull);
+    for (int64_t r = 0; r < rows; r++) {
+      uint64_t acc = is_max ? 0ull : mask;
+      int32_t idx = 0;
+      for (int64_t j = 0; j < cols; j++) {
+        uint64_t x = (uint64_t)load_i(dt, src, r * row_stride + j) & mask;
+        int p = is_max ? (tie_break_left ? x > acc : x >= acc) : (tie_break_left ? x < acc : x <= acc);
+        if (p) { idx = (int32_t)j; acc = x; }
+      }
+      store_i(dt, dst_value, r, (int64_t)acc);
+      dst_index[r] = idx;
+    }
+    return 0;
+  }
+  kind &= 1;
   ORC_PAR_FOR
   for (int64_t r = 0; r < rows; r++) {
     int32_t idx = 0;

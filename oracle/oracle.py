@@ -145,6 +145,17 @@ def elemwise_binary(fn, dt, a, b):
     return out
 
 
+def elemwise_fma(dt, a, b, c):
+    """hfusion.elemwise_ternary {fma}: a * b + c with one rounding; operands of one shape or 1-element (scalar)."""
+    a, b, c = _c(a, dt), _c(b, dt), _c(c, dt)
+    n = max(a.size, b.size, c.size)
+    shape = next(x.shape for x in (a, b, c) if x.size == n)
+    out = np.empty(shape, _NP[dt])
+    _chk(lib().orc_elemwise_fma(dt, _p(a), _i64(1 if a.size == n else 0), _p(b), _i64(1 if b.size == n else 0), _p(c),
+                                _i64(1 if c.size == n else 0), _p(out), _i64(n)), "elemwise_fma")
+    return out
+
+
 def compare(fn, dt, a, b):
     fn = COMPARE[fn] if isinstance(fn, str) else fn
     a, b = _c(a, dt), _c(b, dt)
@@ -297,8 +308,8 @@ def sort_last_axis(dt, src, descending=False):
 
 
 def reduce_with_index(kind, dt, src, tie_break_left=True, nan_mode="region"):
-    """kind: 'max' | 'min'.  Returns (values, int32 indices)."""
-    k = {"min": 0, "max": 1}[kind]
+    """kind: 'max' | 'min' | 'maxui' | 'minui' (the unsigned kinds: integer inputs).  Returns (values, int32 indices)."""
+    k = {"min": 0, "max": 1, "minui": 2, "maxui": 3}[kind]
     nm = {"region": 0, "nan_first": 1}[nan_mode]
     src = _c(src, dt)
     rows, cols = src.shape

@@ -107,3 +107,76 @@ def test_errors_do_not_abort(bsir):
     out = bsir.vadd(a, a)                            # the context is still usable
     assert torch.equal(out, a + a)
     assert bsir.device_error() == 0
+
+
+def test_further_vector_op_library_symbols(bsir):
+    """cumsum / cumprod, sort, interleave / deinterleave, arange, transpose, gather under the reference's symbol names."""
+    L = bsir.lib()
+    L.bsir_set_stream(C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    mr = lambda t: C.byref(bsir.memref(t))
+    g = torch.Generator(device="cuda").manual_seed(4)
+    # cumsum along the first axis of [r, a]; reverse; the middle axis of [a, r, a]
+    x = torch.randn(37, 96, generator=g, device="cuda")
+    y = torch.empty_like(x)
+    assert L._mlir_ciface_cumsum_ra_float(mr(x), mr(y)) == 0
+    assert np.array_equal(y.cpu().numpy(), O.cumulative("sum", O.F32, x.cpu().numpy(), axis=0))
+    assert L._mlir_ciface_cumsum_ra_reverse_float(mr(x), mr(y)) == 0
+    assert np.array_equal(y.cpu().numpy(), O.cumulative("sum", O.F32, x.cpu().numpy(), axis=0, reverse=True))
+    xi = torch.randint(-3, 4, (5, 11, 64), generator=g, device="cuda", dtype=torch.int32)
+    yi = torch.empty_like(xi)
+    assert L._mlir_ciface_cumprod_ara_int32_t(mr(xi), mr(yi)) == 0
+    for a0 in range(5):
+        assert np.array_equal(yi[a0].cpu().numpy(), O.cumulative("prod", O.I32, xi[a0].cpu().numpy(), axis=0))
+    assert L._mlir_ciface_cumsum_ara_reverse_int32_t(mr(xi), mr(yi)) == 0
+    assert np.array_equal(yi[2].cpu().numpy(), O.cumulative("sum", O.I32, xi[2].cpu().numpy(), axis=0, reverse=True))
+    # sort with index, NaN included
+    s = torch.randn(1000, generator=g, device="cuda")
+    s[[5, 999]] = float("nan")
+    sv, si, tmp = torch.empty_like(s), torch.empty(1000, dtype=torch.int32, device="cuda"), torch.empty(1, device="cuda")
+    L._mlir_ciface_sort_with_index_1d_float.argtypes = [C.c_void_p] * 4 + [C.c_bool]
+    assert L._mlir_ciface_sort_with_index_1d_float(mr(s), mr(sv), mr(si), mr(tmp), True) == 0
+    wv, wi = O.sort_last_axis(O.F32, s.cpu().numpy()[None, :], descending=True)
+    assert np.array_equal(si.cpu().numpy(), wi[0]) and np.array_equal(sv.cpu().numpy().view(np.uint32), wv[0].view(np.uint32))
+    L._mlir_ciface_sort_1d_half.argtypes = [C.c_void_p] * 3 + [C.c_bool]
+    h = torch.randn(333, generator=g, device="cuda").half()
+    hv = torch.empty_like(h)
+    assert L._mlir_ciface_sort_1d_half(mr(h), mr(hv), mr(tmp.half()), False) == 0
+    assert torch.equal(hv, torch.sort(h).values)
+    # interleave / deinterleave
+    a, b = torch.randn(640, generator=g, device="cuda").to(torch.bfloat16), torch.randn(640, generator=g, device="cuda").to(torch.bfloat16)
+    ab = torch.empty(1280, dtype=torch.bfloat16, device="cuda")
+    assert L._mlir_ciface_interleave_1d_bfloat16_t(mr(a), mr(b), mr(ab), mr(ab)) == 0
+    assert torch.equal(ab[0::2], a) and torch.equal(ab[1::2], b)
+    back = torch.empty_like(a)
+    assert L._mlir_ciface_deinterleave_channel_1_from_2_channels_1d_bfloat16_t(mr(ab), mr(back)) == 0
+    assert torch.equal(back, b)
+    m4 = torch.arange(6 * 32, device="cuda", dtype=torch.int32).reshape(6, 32)
+    c0 = torch.empty(6, 8, dtype=torch.int32, device="cuda")
+    assert L._mlir_ciface_deinterleave_channel_0_from_n_channels_2d_int32_t(mr(m4), mr(c0)) == 0
+    assert torch.equal(c0, m4[:, 0::4])
+    # arange
+    ar = torch.empty(7, 9, dtype=torch.int32, device="cuda")
+    L._mlir_ciface_arange_2d_int32_t.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_int64]
+    assert L._mlir_ciface_arange_2d_int32_t(mr(ar), 5, 100, -2) == 0
+    want = 5 + 100 * torch.arange(7, device="cuda")[:, None] - 2 * torch.arange(9, device="cuda")[None, :]
+    assert torch.equal(ar.long(), want)
+    # transposes
+    t2 = torch.randn(50, 70, generator=g, device="cuda").half()
+    o2 = torch.empty(70, 50, dtype=torch.float16, device="cuda")
+    assert L._mlir_ciface_transpose_2d_with_last_axis_half(mr(t2), mr(o2)) == 0
+    assert torch.equal(o2, t2.t())
+    t3 = torch.randint(-100, 100, (4, 6, 40), generator=g, device="cuda", dtype=torch.int32)
+    o3 = torch.empty(6, 4, 40, dtype=torch.int32, device="cuda")
+    assert L._mlir_ciface_transpose_3d_without_last_axis_int32_t(mr(t3), mr(o3)) == 0
+    assert torch.equal(o3, t3.permute(1, 0, 2))
+    o3b = torch.empty(40, 6, 4, dtype=torch.int32, device="cuda")
+    assert L._mlir_ciface_transpose_3d_with_last_axis_int32_t(mr(t3), mr(o3b)) == 0
+    assert torch.equal(o3b, t3.permute(2, 1, 0))
+    # gather
+    src = torch.randn(500, generator=g, device="cuda")
+    idx = torch.randint(0, 500, (333,), generator=g, device="cuda", dtype=torch.int32)
+    dst = torch.empty(333, device="cuda")
+    assert L._mlir_ciface_gather_1d_float(mr(src), mr(idx), mr(dst), mr(idx)) == 0
+    assert torch.equal(dst, src[idx.long()])
+    torch.cuda.synchronize()
+    assert bsir.device_error() == 0

@@ -399,3 +399,48 @@ def test_row_strided_views_run_as_compiled_chains(bsir):
     assert_bits_equal(y, O.elemwise_unary("exp", O.F16, to_bits(a.contiguous())), "strided exp")
     odd = big_a[:, 3:259]                                          # rows not 16-byte aligned: the indexed kernel
     assert_bits_equal(bsir.elemwise_unary("abs", odd), O.elemwise_unary("abs", O.F16, to_bits(odd.contiguous())), "unaligned abs")
+
+
+# ---------------------------------------------------------------- elemwise_ternary {fma}, unary ilogb
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1 << 16,), (33, 100), (5, 7, 64), (3, 1000)])
+def test_ternary_fma_bit_exact(bsir, dtype, shape):
+    """math.fma: one rounding of a * b + c (then the storage rounding of 16-bit types), against the oracle's fmaf."""
+    g = torch.Generator(device="cuda").manual_seed(len(shape) * 7 + shape[-1])
+    a, b, c = (torch.randn(shape, generator=g, device="cuda").to(dtype) for _ in range(3))
+    out = bsir.elemwise_ternary("fma", a, b, c)
+    want = O.elemwise_fma(oracle_dtype(a), to_bits(a), to_bits(b), to_bits(c))
+    assert_bits_equal(out, want, f"fma {dtype} {shape}")
+
+
+def test_ternary_fma_scalars_broadcasts_and_views(bsir):
+    g = torch.Generator(device="cuda").manual_seed(2)
+    a = torch.randn(40, 96, generator=g, device="cuda")
+    row = torch.randn(1, 96, generator=g, device="cuda")
+    col = torch.randn(40, 1, generator=g, device="cuda")
+    out = bsir.elemwise_ternary("fma", a, row, col)                       # inline broadcasts (stride 0)
+    ref = O.elemwise_fma(O.F32, a.cpu().numpy(), row.expand(40, 96).contiguous().cpu().numpy(), col.expand(40, 96).contiguous().cpu().numpy())
+    assert np.array_equal(out.cpu().numpy(), ref)
+    out = bsir.elemwise_ternary("fma", a, 2.5, -1.25)                     # scalar operands
+    ref = O.elemwise_fma(O.F32, a.cpu().numpy(), np.array([2.5], np.float32), np.array([-1.25], np.float32))
+    assert np.array_equal(out.cpu().numpy(), ref)
+    view = torch.randn(40, 200, generator=g, device="cuda")[:, 3:99]       # strided, unaligned view
+    out = bsir.elemwise_ternary("fma", view, a, a)
+    ref = O.elemwise_fma(O.F32, view.contiguous().cpu().numpy(), a.cpu().numpy(), a.cpu().numpy())
+    assert np.array_equal(out.cpu().numpy(), ref)
+    with pytest.raises(bsir.BsirError):
+        bsir.elemwise_ternary("fma", a.to(torch.int32), a.to(torch.int32), a.to(torch.int32))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_unary_ilogb(bsir, dtype):
+    """ilogb(x) = floor(log2(|x|)) (Normalize.cpp:6782-6830): the exponent, -inf at zero, +inf at infinities, NaN kept."""
+    x = torch.tensor([1.0, 1.5, 2.0, 3.99, 4.0, 0.75, -0.3, 1e-3, 1000.0, 0.0, -0.0, float("inf"), -float("inf"), float("nan"), 6e-8, 255.0],
+                     device="cuda").to(dtype)
+    out = bsir.elemwise_unary("ilogb", x)
+    want = O.elemwise_unary("ilogb", oracle_dtype(x), to_bits(x))
+    assert_bits_equal(out, want, f"ilogb {dtype}")
+    f = out.float().cpu().numpy()
+    assert f[:5].tolist() == [0.0, 0.0, 1.0, 1.0, 2.0] and f[9] == -np.inf and f[11] == np.inf and np.isnan(f[13])
+    big = (torch.randn(1 << 16, device="cuda") * 100).to(dtype)
+    assert_bits_equal(bsir.elemwise_unary("ilogb", big), O.elemwise_unary("ilogb", oracle_dtype(big), to_bits(big)), "ilogb random")

@@ -409,3 +409,25 @@ def test_scratch_users_on_two_streams_do_not_disturb_each_other(bsir):
         else:
             assert np.array_equal(r.cpu().numpy(), want_s)
     assert bsir.device_error() == 0
+
+
+# ---------------------------------------------------------------- reduce_with_index on integers, unsigned kinds
+@pytest.mark.parametrize("dtype", [torch.int8, torch.int16, torch.int32, torch.int64])
+@pytest.mark.parametrize("kind", ["max", "min", "maxui", "minui"])
+@pytest.mark.parametrize("rows,cols", [(1, 1), (7, 33), (64, 1000), (3, 152064)])
+def test_integer_reduce_with_index(bsir, dtype, kind, rows, cols):
+    """Signed kinds compare with sgt / slt, the *ui kinds the same bits as unsigned numbers; ties per tie_break_left."""
+    info = torch.iinfo(dtype)
+    g = torch.Generator(device="cuda").manual_seed(rows * 13 + cols)
+    lo, hi = max(info.min, -1000), min(info.max, 1000)
+    x = torch.randint(lo, hi + 1, (rows, cols), generator=g, device="cuda", dtype=torch.int64).to(dtype)      # many ties
+    if cols > 4:
+        x[0, 1] = info.min
+        x[0, cols - 2] = info.min          # as unsigned the most negative number is large
+    for left in (True, False):
+        v, i = bsir.reduce_with_index(kind, x, tie_break_left=left)
+        wv, wi = O.reduce_with_index(kind, oracle_dtype(x), to_bits(x), tie_break_left=left)
+        assert np.array_equal(i.cpu().numpy(), wi), f"{kind} {dtype} left={left}"
+        assert np.array_equal(v.cpu().numpy(), wv)
+    with pytest.raises(bsir.BsirError):
+        bsir.reduce_with_index("maxui", x.float())                         # the unsigned kinds are for integers
