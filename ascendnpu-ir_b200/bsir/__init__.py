@@ -494,15 +494,15 @@ def _rows(x: torch.Tensor):
     return x.shape[0], x.shape[1], (x.stride(0) if x.shape[0] > 1 else max(x.shape[1], 1))
 
 
-def reduce(kind: str, x: torch.Tensor, dim: int = 1) -> torch.Tensor:
+def reduce(kind: str, x: torch.Tensor, dim: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``linalg.reduce`` / ``hivm.hir.vreduce <kind>`` over dim 0 or 1 of a 2-D tensor."""
     rows, cols, rs = _rows(x)
     if dim in (1, -1):
-        out = torch.empty(rows, dtype=x.dtype, device=x.device)
+        out = torch.empty(rows, dtype=x.dtype, device=x.device) if out is None else out
         _check(lib().bsir_reduce_last_axis(REDUCE_KIND[kind], _dt(x), C.c_int64(rows), C.c_int64(cols), _ptr(x),
                                            C.c_int64(rs), _ptr(out), _stream()))
     else:
-        out = torch.empty(cols, dtype=x.dtype, device=x.device)
+        out = torch.empty(cols, dtype=x.dtype, device=x.device) if out is None else out
         _check(lib().bsir_reduce_first_axis(REDUCE_KIND[kind], _dt(x), C.c_int64(rows), C.c_int64(cols), _ptr(x),
                                             C.c_int64(rs), _ptr(out), _stream()))
     return out
@@ -568,12 +568,12 @@ def deinterleave(x: torch.Tensor, channels: int = 2, keep: Optional[Sequence[int
     return outs
 
 
-def sort(x: torch.Tensor, descending: bool = False):
+def sort(x: torch.Tensor, descending: bool = False, out_val: Optional[torch.Tensor] = None, out_idx: Optional[torch.Tensor] = None):
     """``hivm.hir.vsort {descending}`` over the last axis of a 1-D or 2-D tensor -> (values, int32 indices); stable."""
     two_d = x if x.dim() == 2 else x.reshape(1, -1)
     rows, cols, rs = _rows(two_d)
-    val = torch.empty((rows, cols), dtype=x.dtype, device=x.device)
-    idx = torch.empty((rows, cols), dtype=torch.int32, device=x.device)
+    val = torch.empty((rows, cols), dtype=x.dtype, device=x.device) if out_val is None else out_val
+    idx = torch.empty((rows, cols), dtype=torch.int32, device=x.device) if out_idx is None else out_idx
     _check(lib().bsir_sort(_dt(x), int(bool(descending)), C.c_int64(rows), C.c_int64(cols), _ptr(two_d), C.c_int64(rs), _ptr(val),
                            C.c_int64(max(cols, 1)), _ptr(idx), C.c_int64(max(cols, 1)), _stream()))
     return val.reshape(x.shape), idx.reshape(x.shape)
@@ -594,11 +594,12 @@ def cumulative(kind: str, x: torch.Tensor, dim: int = 1, reverse: bool = False, 
 
 
 def reduce_with_index(kind: str, x: torch.Tensor, tie_break_left: bool = True, nan_mode: str = "region",
-                      workspace: Optional[torch.Tensor] = None):
-    """``hfusion.reduce_with_index <max|min> {tie_break_left}`` over the last axis -> (values, int32 indices)."""
+                      workspace: Optional[torch.Tensor] = None, out_val: Optional[torch.Tensor] = None,
+                      out_idx: Optional[torch.Tensor] = None):
+    """``hfusion.reduce_with_index <max|min|maxui|minui> {tie_break_left}`` over the last axis -> (values, int32 indices)."""
     rows, cols, rs = _rows(x)
-    val = torch.empty(rows, dtype=x.dtype, device=x.device)
-    idx = torch.empty(rows, dtype=torch.int32, device=x.device)
+    val = torch.empty(rows, dtype=x.dtype, device=x.device) if out_val is None else out_val
+    idx = torch.empty(rows, dtype=torch.int32, device=x.device) if out_idx is None else out_idx
     ws_ptr = _ptr(workspace) if workspace is not None else C.c_void_p(0)
     ws_bytes = workspace.numel() * workspace.element_size() if workspace is not None else 0
     _check(lib().bsir_reduce_with_index(RWI_KIND[kind], _dt(x), int(bool(tie_break_left)),
