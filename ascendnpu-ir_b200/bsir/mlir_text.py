@@ -572,18 +572,22 @@ def parse(text: str) -> Dict[str, Function]:
     for m in re.finditer(r"func\.func\s+(?:private\s+)?@([\w.]+)\s*\(", text):
         args_end = _balanced(text, m.end() - 1, "(", ")")
         arg_text = text[m.end():args_end - 1]
-        args = []
+        args, arg_attrs = [], []
         for a in _split_top(arg_text):
             if not a:
                 continue
             nm, ty = a.split(":", 1)
+            am = re.search(r"\{[^}]*\}\s*$", ty)
+            arg_attrs.append(am.group(0).strip() if am else "")       # e.g. {hacc.arg_type = #hacc.arg_type<output>}
             args.append((nm.strip(), re.sub(r"\{[^}]*\}\s*$", "", ty).strip()))
         brace = text.find("{", args_end)
         # skip `attributes {...}` dictionaries: the body is the last brace group that follows the signature
+        fn_attrs = ""
         while True:
             head = text[args_end:brace]
             end = _balanced(text, brace, "{", "}")
             if re.search(r"attributes\s*$", head):
+                fn_attrs = text[brace:end]
                 args_end = end
                 brace = text.find("{", end)
                 if brace < 0:
@@ -593,7 +597,9 @@ def parse(text: str) -> Dict[str, Function]:
         if brace < 0:
             continue                                   # a declaration
         body = text[brace + 1:end - 1]
-        fns[m.group(1)] = Function(m.group(1), args, _statements(body))
+        fn = Function(m.group(1), args, _statements(body))
+        fn.arg_attrs, fn.attrs = arg_attrs, fn_attrs
+        fns[m.group(1)] = fn
     if not fns:
         raise MlirTextError("no func.func found")
     return fns
