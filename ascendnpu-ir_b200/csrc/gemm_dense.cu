@@ -33,6 +33,7 @@
 //
 // Shapes the TMA path cannot address (row pitches that are not multiples of 16 bytes, unaligned bases) run on
 // a plain CUDA-core kernel instead.
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -65,7 +66,22 @@ struct GemmParams {
   int tma_out;   // 1: the output tile goes through shared memory and TMA stores (16-bit outputs)
   int n_peers;   // > 0: every store of C goes to each of peer[0 .. n_peers) instead of `out` (one-sided N-sharding)
   void *peer[8];
+  // decode kernel, K split over CTAs: one arrival word per tile, two partial-tile slots per CTA, launch tag
+  unsigned long long *tile_arrivals;
+  int32_t *partials;
+  uint32_t launch_tag;
+  int dk_levels, dk_len, dk_helpers;   // 0 levels: whole tiles, no scratch
+  int dk_vec_out;                      // 1: 16-byte stores of C (n and ldo multiples of 8, 16-byte aligned bases)
+#ifdef BSIR_DEC_TIMELINE
+  unsigned long long *tl;
+#endif
 };
+#ifdef BSIR_DEC_TIMELINE
+__device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define TL(i) do { if (p.tl) { p.tl[blockIdx.x * 32 + (i)] = gtime(); p.tl[blockIdx.x * 32 + 16 + (i)] = clock64(); } } while (0)
+#else
+#define TL(i) do { } while (0)
+#endif
 // destination d of the output: the peers' buffers when there are any, else `out`
 __device__ __forceinline__ int out_count(const GemmParams &p) { return p.n_peers > 0 ? p.n_peers : 1; }
 __device__ __forceinline__ void *out_base(const GemmParams &p, int d) { return p.n_peers > 0 ? p.peer[d] : p.out; }
@@ -195,25 +211,27 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const CUtenso
     }
     if (!p.out) continue;
     if (p.out_dtype == BSIR_BF16 || p.out_dtype == BSIR_F16) {
+      // straight-line: the output type and relu are decided once per chunk, not per element, so that the 32
+      // independent chains can overlap (one warp per scheduler has nothing else to hide latencies with)
       uint32_t packed[16];
+      float f[32];
+      const float floor_v = p.relu ? 0.0f : __int_as_float(0xff800000);   // maximumf(x, -inf) = x, NaN stays NaN
 #pragma unroll
       for (int j4 = 0; j4 < 32; j4 += 4) {
         const float4 sw = *reinterpret_cast<const float4 *>(sw_s + c0 + j4);   // same address in every lane: broadcast
         const uint4 bb = *reinterpret_cast<const uint4 *>(bias_s + c0 + j4);
-        const float swv[4] = {sw.x, sw.y, sw.z, sw.w};
-        const uint32_t bv[4] = {bb.x, bb.y, bb.z, bb.w};
+        f[j4 + 0] = maximumf(__fmul_rn(__fmul_rn(acc_plus_bias<KIND>(r[j4 + 0], bb.x), sa), sw.x), floor_v);
+        f[j4 + 1] = maximumf(__fmul_rn(__fmul_rn(acc_plus_bias<KIND>(r[j4 + 1], bb.y), sa), sw.y), floor_v);
+        f[j4 + 2] = maximumf(__fmul_rn(__fmul_rn(acc_plus_bias<KIND>(r[j4 + 2], bb.z), sa), sw.z), floor_v);
+        f[j4 + 3] = maximumf(__fmul_rn(__fmul_rn(acc_plus_bias<KIND>(r[j4 + 3], bb.w), sa), sw.w), floor_v);
+      }
+      if (p.out_dtype == BSIR_F16) {
 #pragma unroll
-        for (int j = 0; j < 4; j += 2) {
-          float f0 = scale_relu(acc_plus_bias<KIND>(r[j4 + j], bv[j]), sa, swv[j], p.relu);
-          float f1 = scale_relu(acc_plus_bias<KIND>(r[j4 + j + 1], bv[j + 1]), sa, swv[j + 1], p.relu);
-          if (p.out_dtype == BSIR_F16) {
-            f0 = fminf(fmaxf(f0, -65504.0f), 65504.0f);
-            f1 = fminf(fmaxf(f1, -65504.0f), 65504.0f);
-            packed[(j4 + j) >> 1] = pack_f16x2(f0, f1);
-          } else {
-            packed[(j4 + j) >> 1] = pack_bf16x2(f0, f1);
-          }
-        }
+        for (int j = 0; j < 16; ++j)
+          packed[j] = pack_f16x2(fminf(fmaxf(f[2 * j], -65504.0f), 65504.0f), fminf(fmaxf(f[2 * j + 1], -65504.0f), 65504.0f));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) packed[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
       }
       if (p.tma_out) {
         const uint32_t b = nstores & 1u;
@@ -478,6 +496,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 // bandwidth per SM, not by the tensor core.  Roles and barriers as in the kernel above; the
 // epilogue reads the accumulator with lanes = output columns and writes 64-byte runs per row.
 // It serves the W8A8 form of the epilogue (f32 per-row and per-channel scales, 16-bit output).
+//
+// With fewer tiles than SMs (112 for n = 14336) whole tiles leave SMs idle, so K is split -- in a way that keeps the
+// CTAs that run side by side on the same k blocks of neighbouring tiles, because a weight tile is 128 rows of 128
+// bytes and only neighbours in n at the same k make those rows one contiguous stretch of DRAM (dealing out
+// (tile, k block) ranges with every CTA at another k measured 25 us against 14 us for whole tiles).  With G CTAs
+// and T tiles, G >= T: CTA b < levels * T (levels = G / T) takes k blocks [lvl * len, (lvl + 1) * len) of tile
+// b % T, lvl = b / T; the remaining G % T "helper" CTAs share the last range [levels * len, k_blocks), helper h
+// taking tiles h, h + helpers, ... one after the other.  len is the smallest block count that leaves a helper no
+// more work than anyone else.  Every CTA writes its int32 partial tile to its slot of the scratch block and arrives
+// on the tile's word; the CTA that arrives last adds the other parts to its accumulator and runs the epilogue.
+// Nobody waits for anybody, int32 addition is exact, so the result has the bits of the unsplit product in every
+// schedule.  An arrival word is {launch tag, count}: a count left behind by a launch that failed carries another
+// tag and reads as zero; the last arrival writes zero back, so a replayed CUDA graph (same tag) finds it clean.
 constexpr int kDecStageW = kBM * kBK;             // weight tile: 128 columns x 128 k
 constexpr int kDecMaxStages = 12;
 constexpr int kDecSmemBudget = 200 * 1024;
@@ -494,8 +525,39 @@ inline DecodeCfg decode_cfg(int64_t m) {
   c.stage = kDecStageW + c.nb * kBK;
   c.stages = kDecSmemBudget / c.stage;
   if (c.stages > kDecMaxStages) c.stages = kDecMaxStages;
-  c.smem = static_cast<uint32_t>(c.stages * c.stage + 1024 /*barriers*/ + 1024 /*alignment slack*/);
+  c.smem = static_cast<uint32_t>(c.stages * c.stage + 1024 /*barriers*/ + 4096 /*output staging*/ + 1024 /*alignment slack*/);
   return c;
+}
+
+__device__ __forceinline__ bool tile_arrive(unsigned long long *word, uint32_t tag, int parts, int *err) {
+  unsigned long long old = *reinterpret_cast<volatile unsigned long long *>(word);
+  for (int tries = 0; tries < 4096; ++tries) {        // a failed swap means another part arrived: at most parts - 1 of them
+    const uint32_t cnt = static_cast<uint32_t>(old >> 32) == tag ? static_cast<uint32_t>(old) : 0u;
+    const bool last = static_cast<int>(cnt) + 1 >= parts;
+    const unsigned long long next = last ? 0ull : ((static_cast<unsigned long long>(tag) << 32) | (cnt + 1u));
+    const unsigned long long prev = atomicCAS(word, old, next);
+    if (prev == old) return last;
+    old = prev;
+  }
+  if (err) atomicOr(err, static_cast<int>(kErrGemmWait));
+  return false;
+}
+
+// Which k blocks of which tiles CTA `b` works on (its s-th segment).  See the plan in the header comment above.
+struct DecodeSeg { int tile, kb0, kb1, part; };
+__device__ __forceinline__ bool decode_segment(const GemmParams &p, int b, int grid, int s, DecodeSeg &g) {
+  if (p.dk_levels == 0) {                                  // whole tiles, round-robin
+    g.tile = b + s * grid; g.kb0 = 0; g.kb1 = p.k_blocks; g.part = 0;
+    return g.tile < p.n_tiles;
+  }
+  if (b < p.dk_levels * p.n_tiles) {                       // one k range of one tile
+    const int lvl = b / p.n_tiles;
+    g.tile = b - lvl * p.n_tiles; g.kb0 = lvl * p.dk_len; g.kb1 = min(p.k_blocks, g.kb0 + p.dk_len); g.part = lvl;
+    return s == 0 && g.kb0 < p.k_blocks;
+  }
+  const int h = b - p.dk_levels * p.n_tiles;               // the last k range of every dk_helpers-th tile
+  g.tile = h + s * p.dk_helpers; g.kb0 = p.dk_levels * p.dk_len; g.kb1 = p.k_blocks; g.part = p.dk_levels;
+  return g.kb0 < p.k_blocks && g.tile < p.n_tiles;
 }
 
 template <bool W_MN>
@@ -513,19 +575,30 @@ __global__ void __launch_bounds__(kThreads, 1)
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * kDecMaxStages + 2 + a); };
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen_base + nstages * stage_bytes + 8 * (2 * kDecMaxStages + 4));
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile int *last_flag = reinterpret_cast<volatile int *>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_tiles = p.n_tiles;
+  const int cta = blockIdx.x, grid = gridDim.x;
   const uint32_t tmem_cols = 2 * nb < 32 ? 32u : (2 * nb <= 64 ? 64u : (2 * nb <= 128 ? 128u : 256u));
   const float *scale_b = static_cast<const float *>(p.descale);
 
-  // (tile, k block) pairs of this CTA in issue order; pair `it` uses stage it % nstages
-  const int my_tiles = (total_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
-  const int total_its = my_tiles * p.k_blocks;
+  // Load number `it` of this CTA uses stage it % nstages.  All segments of a CTA have the same number of k blocks,
+  // so load `it` is block it % seg_len of segment it / seg_len.
+  DecodeSeg seg0;
+  const bool any = decode_segment(p, cta, grid, 0, seg0);
+  const int seg_len = any ? seg0.kb1 - seg0.kb0 : 1;
+  int nsegs = 0;
+  if (any) {
+    if (p.dk_levels == 0) nsegs = (p.n_tiles - cta + grid - 1) / grid;
+    else if (cta < p.dk_levels * p.n_tiles) nsegs = 1;
+    else nsegs = (p.n_tiles - (cta - p.dk_levels * p.n_tiles) + p.dk_helpers - 1) / p.dk_helpers;
+  }
+  const int total_its = nsegs * seg_len;
   auto issue = [&](int it) {
-    const int tile = static_cast<int>(blockIdx.x) + (it / p.k_blocks) * static_cast<int>(gridDim.x);
-    const int kb = it % p.k_blocks, stage = it % nstages;
-    const int n0 = tile * kBM;
+    DecodeSeg g;
+    decode_segment(p, cta, grid, it / seg_len, g);
+    const int kb = g.kb0 + it % seg_len, stage = it % nstages;
+    const int n0 = g.tile * kBM;
     const uint32_t sw = base + stage * stage_bytes;
     mbar_expect_tx(full_bar(stage), static_cast<uint32_t>(stage_bytes));
     if constexpr (W_MN) tma_load_2d(sw, &tmap_w, n0, kb * kBK, full_bar(stage));   // [128 k rows x 128 n bytes]
@@ -537,18 +610,28 @@ __global__ void __launch_bounds__(kThreads, 1)
   // blocks take SMs as ours leave them), and this kernel touches global memory only after the one before it
   // has completed -- so launch latency and the barrier / tensor-memory set-up overlap the predecessor's tail.
   pdl_launch_dependents();
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < nstages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
-    *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tmap(&tmap_w);
+      prefetch_tmap(&tmap_a);
+      for (int s = 0; s < nstages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+      for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+      *abort_flag = 0;
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
     pdl_wait();
-    // the first ring of loads goes out before the CTA meets: a launch this short (about 9 us of
-    // transfer) cannot afford to wait for the tensor-memory allocation first
-    for (int it = 0; it < preissued; ++it) issue(it);
+    TL(0);
+    // The first ring of loads goes out before the CTA meets: a launch this short cannot afford to wait for the
+    // tensor-memory allocation first.  One thread issues them in order: the copy engine takes about 200 cycles per
+    // 18 KB stage whoever issues it (one load per lane was tried: the ring took as long to go out and its first
+    // stage arrived 1.5 us later, the engine having started with another one).
+    if (lane == 0)
+      for (int it = 0; it < preissued; ++it) issue(it);
+    TL(1);
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), tmem_cols);
-  if (threadIdx.x != 0) pdl_wait();
+  if (warp != 0) pdl_wait();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -580,23 +663,26 @@ __global__ void __launch_bounds__(kThreads, 1)
       int acc = 0;
       uint32_t acc_phase[2] = {0u, 0u};
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      DecodeSeg g;
+      for (int s = 0; ok && decode_segment(p, cta, grid, s, g); ++s) {
         if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * nb);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = g.kb0; kb < g.kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.err)) { ok = false; break; }
+          if (s == 0 && kb == g.kb0) TL(2);
           tc_fence_after();
           const uint32_t sw = base + stage * stage_bytes;
           const uint32_t sa = sw + kDecStageW;
 #pragma unroll
           for (int kk = 0; kk < kBK / kUmmaK; ++kk)
-            mma_ss<KI8>(d_tmem, operand_desc<KI8>(sw, kk, W_MN), operand_desc<KI8>(sa, kk, false), idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            mma_ss<KI8>(d_tmem, operand_desc<KI8>(sw, kk, W_MN), operand_desc<KI8>(sa, kk, false), idesc, (kb > g.kb0 || kk > 0) ? 1u : 0u);
           tc_commit(empty_bar(stage));
           if (++stage == nstages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
         tc_commit(tfull_bar(acc));
+        TL(3);
         acc_phase[acc] ^= 1u;
         acc ^= 1;
       }
@@ -607,41 +693,123 @@ __global__ void __launch_bounds__(kThreads, 1)
     int acc = 0;
     uint32_t acc_phase[2] = {0u, 0u};
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const int64_t col = static_cast<int64_t>(tile) * kBM + quad * 32 + lane;
+    const size_t slot_words = static_cast<size_t>(nb) * kBM;
+    // parts a tile is computed in: the k ranges that are not empty
+    int parts = 1;
+    if (p.dk_levels > 0) {
+      const int lv = (p.k_blocks + p.dk_len - 1) / p.dk_len;
+      parts = (lv < p.dk_levels ? lv : p.dk_levels) + (p.dk_levels * p.dk_len < p.k_blocks ? 1 : 0);
+    }
+    DecodeSeg g;
+    for (int s = 0; ok && decode_segment(p, cta, grid, s, g); ++s) {
+      const int64_t col = static_cast<int64_t>(g.tile) * kBM + quad * 32 + lane;
       const bool col_ok = col < p.n;
       const float sw = (scale_b && col_ok) ? scale_b[col] : 1.0f;
       const float sa_lane = (p.scale_a && lane < p.m) ? p.scale_a[lane] : 1.0f;   // rows 0..31, one per lane
       if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, p.err)) { ok = false; break; }
+      if (threadIdx.x == 64) TL(4);
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * nb);
-      for (int c0 = 0; c0 < nb; c0 += 16) {
+      bool finish = true;
+      int32_t *tile_slots = nullptr;
+      if (parts > 1) {
+        tile_slots = p.partials + static_cast<size_t>(g.tile) * parts * slot_words;
+        int32_t *mine = tile_slots + g.part * slot_words;
+        for (int c0 = 0; c0 < nb && c0 < p.m; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(t_row + static_cast<uint32_t>(c0), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c0 + j < p.m) __stcg(mine + static_cast<size_t>(c0 + j) * kBM + quad * 32 + lane, static_cast<int32_t>(r[j]));
+        }
+        if (threadIdx.x == 64) TL(5);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) TL(6);
+        if (warp == 2 && lane == 0) *last_flag = tile_arrive(p.tile_arrivals + g.tile, p.launch_tag, parts, p.err) ? 1 : 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        finish = *last_flag != 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");     // all have read the flag before the next segment's arrival rewrites it
+        if (finish) __threadfence();
+        if (threadIdx.x == 64) TL(7);
+      }
+      for (int c0 = 0; c0 < nb && finish; c0 += 16) {
         uint32_t r[16];
         tmem_ld16(t_row + static_cast<uint32_t>(c0), r);
         tmem_ld_wait();
+        if (parts > 1 && c0 < p.m) {
+          for (int q = 0; q < parts; ++q) {
+            if (q == g.part) continue;
+            const int32_t *theirs = tile_slots + q * slot_words;
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int64_t row = c0 + j;
-          if (row >= p.m) break;               // uniform over the warp
-          const int32_t v = static_cast<int32_t>(r[j]);
-          // all lanes take part in the shuffle (row is uniform over the warp)
-          const float sa = row < 32 ? __shfl_sync(0xffffffffu, sa_lane, static_cast<int>(row)) : (p.scale_a ? __ldg(p.scale_a + row) : 1.0f);
-          if (p.acc_out && col_ok) p.acc_out[row * p.ldacc + col] = v;
-          if (p.out && col_ok) {
-            float f = __fmul_rn(__fmul_rn(static_cast<float>(v), sa), sw);
-            uint16_t bits;
-            if (p.out_dtype == BSIR_F16) {
-              f = fminf(fmaxf(f, -65504.0f), 65504.0f);
-              bits = static_cast<uint16_t>(pack_f16x2(f, 0.0f) & 0xffffu);
-            } else {
-              bits = static_cast<uint16_t>(pack_bf16x2(f, 0.0f) & 0xffffu);
-            }
-            for (int d = 0; d < out_count(p); ++d) static_cast<uint16_t *>(out_base(p, d))[row * p.ldo + col] = bits;
+            for (int j = 0; j < 16; ++j)
+              if (c0 + j < p.m) r[j] += static_cast<uint32_t>(__ldcg(theirs + static_cast<size_t>(c0 + j) * kBM + quad * 32 + lane));
           }
+        }
+        // scale and convert; the 16 rows x 32 columns of this warp go through shared memory so that a lane stores
+        // 16 bytes of one row (2-byte stores, one per row and lane, cost this epilogue 2.5 us of a 14 us launch)
+        uint16_t *stg = reinterpret_cast<uint16_t *>(gen_base + nstages * stage_bytes + 1024) + quad * 512;
+        if (threadIdx.x == 64 && c0 == 0) TL(13);
+        // straight-line code, no branch per row: one warp per scheduler has only instruction-level parallelism
+        // to hide latencies with (a loop with the dtype test and the bounds tests inside ran 220 cycles per row)
+        float f[16];
+        if (nb <= 32) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) f[j] = __shfl_sync(0xffffffffu, sa_lane, (c0 + j) & 31);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) f[j] = (p.scale_a && c0 + j < p.m) ? __ldg(p.scale_a + c0 + j) : 1.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) f[j] = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j])), f[j]), sw);
+        if (p.acc_out && col_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (c0 + j < p.m) p.acc_out[static_cast<int64_t>(c0 + j) * p.ldacc + col] = static_cast<int32_t>(r[j]);
+        }
+        uint32_t pk[8];
+        if (p.out_dtype == BSIR_F16) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            pk[j] = pack_f16x2(fminf(fmaxf(f[2 * j], -65504.0f), 65504.0f), fminf(fmaxf(f[2 * j + 1], -65504.0f), 65504.0f));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) pk[j] = pack_bf16x2(f[2 * j], f[2 * j + 1]);
+        }
+        if (p.dk_vec_out) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            stg[(2 * j) * 32 + lane] = static_cast<uint16_t>(pk[j] & 0xffffu);
+            stg[(2 * j + 1) * 32 + lane] = static_cast<uint16_t>(pk[j] >> 16);
+          }
+        } else if (p.out && col_ok) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const uint16_t bits = static_cast<uint16_t>((j & 1) ? (pk[j >> 1] >> 16) : (pk[j >> 1] & 0xffffu));
+            if (c0 + j < p.m)
+              for (int d = 0; d < out_count(p); ++d) static_cast<uint16_t *>(out_base(p, d))[static_cast<int64_t>(c0 + j) * p.ldo + col] = bits;
+          }
+        }
+        if (threadIdx.x == 64 && c0 == 0) TL(14);
+        if (p.dk_vec_out) {
+          __syncwarp();
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            const int id = lane + 32 * t, rr = id >> 2, part = id & 3;
+            const int64_t row = c0 + rr, col0 = static_cast<int64_t>(g.tile) * kBM + quad * 32 + part * 8;
+            if (row < p.m && col0 < p.n) {
+              const uint4 v = *reinterpret_cast<const uint4 *>(stg + rr * 32 + part * 8);
+              for (int d = 0; d < out_count(p); ++d)
+                *reinterpret_cast<uint4 *>(static_cast<uint16_t *>(out_base(p, d)) + row * p.ldo + col0) = v;
+            }
+          }
+          __syncwarp();
         }
       }
       tc_fence_before();
       __syncwarp();
+      if (threadIdx.x == 64) TL(8 + (s < 4 ? s : 4));
       if (lane == 0) mbar_arrive(tempty_bar(acc));
       acc_phase[acc] ^= 1u;
       acc ^= 1;
@@ -1056,8 +1224,48 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
         ok3 = ok3 && make_tmap(&tact, o.a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(o.lda), static_cast<uint32_t>(dc.nb));
         if (ok3) {
           p.n_tiles = static_cast<int>(ceil_div(n, kBM));
-          int grid = device_info().sm_count > 0 ? device_info().sm_count : 148;
-          if (grid > p.n_tiles) grid = p.n_tiles;
+          const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
+          const int64_t items = static_cast<int64_t>(p.n_tiles) * p.k_blocks;
+          int grid = p.n_tiles < sms ? p.n_tiles : sms;
+          // K is split over CTAs when whole tiles would leave SMs idle (BSIR_W8A8_SPLITK=0: never)
+          const char *split_env = std::getenv("BSIR_W8A8_SPLITK");
+          p.partials = nullptr;
+          p.tile_arrivals = nullptr;
+          p.dk_levels = p.dk_len = p.dk_helpers = 0;
+          p.launch_tag = 0;
+#ifdef BSIR_DEC_TIMELINE
+          { const char *e = std::getenv("BSIR_DEC_TL_PTR"); p.tl = e ? reinterpret_cast<unsigned long long *>(std::strtoull(e, nullptr, 0)) : nullptr; }
+#endif
+          p.dk_vec_out = (p.out || p.n_peers > 0) && n % 8 == 0 && p.ldo % 8 == 0 && (p.n_peers > 0 || aligned_to(p.out, 16));
+          for (int d = 0; d < p.n_peers; ++d) p.dk_vec_out = p.dk_vec_out && aligned_to(p.peer[d], 16);
+          // 112 CTAs already stream n = 14336 at the HBM rate, so K is split only when a third of the SMs or more would idle
+          if (!(split_env && split_env[0] == '0') && p.n_tiles * 3 <= sms * 2 && p.k_blocks > 1 && static_cast<size_t>(p.n_tiles) * 8 <= kScratchCounterBytes) {
+            const int g2 = static_cast<int>(items < sms ? items : sms);
+            const int levels = g2 / p.n_tiles, helpers = g2 % p.n_tiles;
+            int len;
+            if (helpers == 0) {
+              len = static_cast<int>(ceil_div(p.k_blocks, levels));
+            } else {
+              const int64_t q = ceil_div(p.n_tiles, helpers);              // tiles per helper
+              len = static_cast<int>(ceil_div(static_cast<int64_t>(p.k_blocks) * q, 1 + levels * q));
+            }
+            if (len < 1) len = 1;
+            if (len * 10 <= p.k_blocks * 9) {                                // worth it: the longest share shrinks by a tenth or more
+              const int lv = static_cast<int>(ceil_div(p.k_blocks, len));
+              const int parts = (lv < levels ? lv : levels) + (levels * len < p.k_blocks ? 1 : 0);
+              const size_t need = kScratchCounterBytes + static_cast<size_t>(p.n_tiles) * parts * dc.nb * kBM * sizeof(int32_t);
+              char *ws = static_cast<char *>(device_workspace(need, st));
+              if (!ws) return BSIR_ERR_WORKSPACE;
+              static std::atomic<uint32_t> tag{0};
+              uint32_t t = ++tag;
+              if (t == 0) t = ++tag;
+              p.tile_arrivals = reinterpret_cast<unsigned long long *>(ws);
+              p.partials = reinterpret_cast<int32_t *>(ws + kScratchCounterBytes);
+              p.launch_tag = t;
+              p.dk_levels = levels; p.dk_len = len; p.dk_helpers = helpers;
+              grid = g2;
+            }
+          }
           if (b_mn) {
             cudaFuncSetAttribute(w8a8_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dc.smem));
             launch_pdl(w8a8_decode_kernel<true>, dim3(grid), dim3(kThreads), dc.smem, st, tw, tact, p, dc.nb, dc.stage, dc.stages);

@@ -60,6 +60,34 @@ def test_w8a8_decode_kernel_exact(bsir, m, n, k, transpose_b, monkeypatch):
     _w8a8_case(bsir, m, n, k, transpose_b, seed=m + n + k + 11)
 
 
+@pytest.mark.parametrize("m,n,k", [(16, 14336, 4096), (8, 14336 + 72, 4096 + 128), (24, 7168, 4096), (3, 640, 128 * 37), (16, 128 * 147, 256)])
+def test_w8a8_decode_k_split_over_ctas(bsir, m, n, k, monkeypatch):
+    """Fewer tiles than SMs: a tile's k blocks are shared out over two or more CTAs and the partial tiles meet in
+    scratch.  Same bits as whole tiles per CTA, launch after launch on the same scratch, and under a replayed graph."""
+    _w8a8_case(bsir, m, n, k, False, seed=5)
+    g = torch.Generator(device="cuda").manual_seed(9)
+    a = torch.randint(-127, 128, (m, k), generator=g, device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (k, n), generator=g, device="cuda", dtype=torch.int8)
+    sa = torch.rand(m, generator=g, device="cuda") * 9e-3 + 1e-3
+    sw = torch.rand(n, generator=g, device="cuda") * 9e-3 + 1e-3
+    outs = [bsir.matmul_w8a8(a, w, sa, sw) for _ in range(6)]
+    monkeypatch.setenv("BSIR_W8A8_SPLITK", "0")
+    whole = bsir.matmul_w8a8(a, w, sa, sw)
+    monkeypatch.delenv("BSIR_W8A8_SPLITK")
+    for o in outs:
+        assert torch.equal(o.view(torch.int16), whole.view(torch.int16))
+    out = torch.empty_like(whole)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        bsir.matmul_w8a8(a, w, sa, sw, out=out)
+    for _ in range(3):                                   # the same launch tag every replay: the arrival words were left at zero
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), whole.view(torch.int16))
+    assert bsir.device_error() == 0
+
+
 def test_w8a8_f16_output_and_unaligned_fallback(bsir):
     _w8a8_case(bsir, 64, 256, 256, False, seed=3, out_dtype=torch.float16)
     # k = 100: the row pitch is not a multiple of 16 bytes -> plain path
