@@ -594,16 +594,24 @@ __global__ void __launch_bounds__(kThreads, 1)
     else nsegs = (p.n_tiles - (cta - p.dk_levels * p.n_tiles) + p.dk_helpers - 1) / p.dk_helpers;
   }
   const int total_its = nsegs * seg_len;
-  auto issue = [&](int it) {
-    DecodeSeg g;
-    decode_segment(p, cta, grid, it / seg_len, g);
-    const int kb = g.kb0 + it % seg_len, stage = it % nstages;
-    const int n0 = g.tile * kBM;
-    const uint32_t sw = base + stage * stage_bytes;
-    mbar_expect_tx(full_bar(stage), static_cast<uint32_t>(stage_bytes));
-    if constexpr (W_MN) tma_load_2d(sw, &tmap_w, n0, kb * kBK, full_bar(stage));   // [128 k rows x 128 n bytes]
-    else tma_load_2d(sw, &tmap_w, kb * kBK, n0, full_bar(stage));                 // [128 n rows x 128 k bytes]
-    tma_load_2d(sw + kDecStageW, &tmap_a, kb * kBK, 0, full_bar(stage));          // [nb rows x 128 k bytes]
+  // The producer's cursor: counters that step, no division per load.  (A CTA streams one 18 KB stage per 570 cycles,
+  // 60 GB/s, however fast the loads are issued: the ring of 200 KB is what an SM keeps in flight, and it takes
+  // 3.3 us to land.  Only more CTAs stream faster, which is what the K split is for.)
+  DecodeSeg pseg = seg0;
+  int p_seg = 0, p_kb = seg0.kb0, p_stage = 0;
+  uint32_t p_round = 0;
+  auto issue_next = [&]() {
+    const uint32_t sw = base + p_stage * stage_bytes;
+    const uint32_t bar = full_bar(p_stage);
+    mbar_expect_tx(bar, static_cast<uint32_t>(stage_bytes));
+    if constexpr (W_MN) tma_load_2d(sw, &tmap_w, pseg.tile * kBM, p_kb * kBK, bar);   // [128 k rows x 128 n bytes]
+    else tma_load_2d(sw, &tmap_w, p_kb * kBK, pseg.tile * kBM, bar);                 // [128 n rows x 128 k bytes]
+    tma_load_2d(sw + kDecStageW, &tmap_a, p_kb * kBK, 0, bar);                       // [nb rows x 128 k bytes]
+    if (++p_kb == pseg.kb1) {
+      decode_segment(p, cta, grid, ++p_seg, pseg);
+      p_kb = pseg.kb0;
+    }
+    if (++p_stage == nstages) { p_stage = 0; ++p_round; }
   };
   const int preissued = total_its < nstages ? total_its : nstages;
   // Programmatic dependent launch: the next kernel of the stream may be scheduled while this one runs (its
@@ -627,7 +635,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // 18 KB stage whoever issues it (one load per lane was tried: the ring took as long to go out and its first
     // stage arrived 1.5 us later, the engine having started with another one).
     if (lane == 0)
-      for (int it = 0; it < preissued; ++it) issue(it);
+      for (int it = 0; it < preissued; ++it) issue_next();
     TL(1);
   }
   if (warp == 1) tmem_alloc(smem_u32(tmem_slot), tmem_cols);
@@ -642,10 +650,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       bool ok = true;
       for (int it = preissued; it < total_its; ++it) {
-        const int stage = it % nstages;
-        const uint32_t phase = static_cast<uint32_t>(it / nstages) & 1u;
-        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.err)) { ok = false; break; }
-        issue(it);
+        if (!mbar_wait(empty_bar(p_stage), (p_round & 1u) ^ 1u, abort_flag, p.err)) { ok = false; break; }
+        issue_next();
       }
       if (!ok) {
         for (int s = 0; s < nstages; ++s)
@@ -1240,8 +1246,10 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
           for (int d = 0; d < p.n_peers; ++d) p.dk_vec_out = p.dk_vec_out && aligned_to(p.peer[d], 16);
           // 112 CTAs already stream n = 14336 at the HBM rate, so K is split only when a third of the SMs or more would idle
           if (!(split_env && split_env[0] == '0') && p.n_tiles * 3 <= sms * 2 && p.k_blocks > 1 && static_cast<size_t>(p.n_tiles) * 8 <= kScratchCounterBytes) {
-            const int g2 = static_cast<int>(items < sms ? items : sms);
-            const int levels = g2 / p.n_tiles, helpers = g2 % p.n_tiles;
+            // at most six parts per tile: the CTA that arrives last reads the others' partial tiles one after the other
+            int64_t g2 = items < sms ? items : sms;
+            if (g2 > static_cast<int64_t>(p.n_tiles) * 6) g2 = static_cast<int64_t>(p.n_tiles) * 6;
+            const int levels = static_cast<int>(g2 / p.n_tiles), helpers = static_cast<int>(g2 % p.n_tiles);
             int len;
             if (helpers == 0) {
               len = static_cast<int>(ceil_div(p.k_blocks, levels));
@@ -1263,7 +1271,7 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
               p.partials = reinterpret_cast<int32_t *>(ws + kScratchCounterBytes);
               p.launch_tag = t;
               p.dk_levels = levels; p.dk_len = len; p.dk_helpers = helpers;
-              grid = g2;
+              grid = static_cast<int>(g2);
             }
           }
           if (b_mn) {

@@ -274,13 +274,13 @@ def test_argmax_ties_and_specials(bsir):
     _check_rwi(bsir, -x, "min")
 
 
+@pytest.mark.parametrize("rows", [80, 150, 256, 40])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_argmax_long_rows_streaming_path(bsir, dtype):
-    """Enough long rows that the persistent streaming kernel runs (each CTA's share starts and ends
-    inside rows): duplicates, signed zeros, -inf rows, NaNs before/after the extreme, extremes at
-    both ends of a row and at share boundaries."""
+def test_argmax_long_rows_streaming_path(bsir, dtype, rows):
+    """Enough long rows that the streaming kernel runs, a row cut into 7, 3 or 2 parts that meet in the shared memory
+    of a thread-block cluster (40 rows: 9 parts, which meet in scratch): duplicates, signed zeros, -inf rows, NaNs
+    before/after the extreme, extremes at both ends of a row and at part boundaries."""
     cols = 152064 if dtype == torch.bfloat16 else 76032
-    rows = 80
     g = torch.Generator(device="cuda").manual_seed(11)
     x = torch.randn(rows, cols, device="cuda", generator=g).clamp(-3, 3).to(dtype)
     x[0, [5, cols // 2, cols - 1]] = 9.0
