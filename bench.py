@@ -323,6 +323,22 @@ def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters, only=None):
         outs = [torch.empty_like(b[0]) for b in bufs]
         rec(nm, 3 * n * bufs[0][0].element_size(), lambda i: bsir.vadd(*bufs[i % 3], out=outs[i % 3]))
         del bufs, outs
+    if want("bias_add_bf16_32768x4096") or want("row_scale_bf16_32768x4096") or want("slice_mul_bf16_32768x4096"):
+        # hivm's inline broadcast (a per-column bias, a per-row scale) and row-strided views of wider tensors
+        xs = [W.rmsnorm_input(32768, 4096, seed=s) for s in range(2)]                 # (x bf16 [32768, 4096], w bf16 [4096])
+        ys = [torch.empty_like(x[0]) for x in xs]
+        scale = (torch.rand(32768, 1, device="cuda") + 0.5).to(torch.bfloat16)
+        wide = [torch.randn(32768, 4608, device="cuda").to(torch.bfloat16) for _ in range(2)]
+        if want("bias_add_bf16_32768x4096"):
+            rec("bias_add_bf16_32768x4096", 2 * 32768 * 4096 * 2 + 8192,
+                lambda i: bsir.elemwise_binary("add", xs[i % 2][0], xs[i % 2][1].view(1, -1).expand(32768, 4096), out=ys[i % 2]))
+        if want("row_scale_bf16_32768x4096"):
+            rec("row_scale_bf16_32768x4096", 2 * 32768 * 4096 * 2 + 65536,
+                lambda i: bsir.elemwise_binary("mul", xs[i % 2][0], scale.expand(32768, 4096), out=ys[i % 2]))
+        if want("slice_mul_bf16_32768x4096"):
+            rec("slice_mul_bf16_32768x4096", 3 * 32768 * 4096 * 2,
+                lambda i: bsir.elemwise_binary("mul", xs[i % 2][0], wide[i % 2][:, 256:4352], out=ys[i % 2]))
+        del xs, ys, scale, wide
     if want("rmsnorm_bf16_32768x4096"):
         xs = [W.rmsnorm_input(32768, 4096, seed=s) for s in range(2)]
         ys = [torch.empty_like(x[0]) for x in xs]

@@ -365,38 +365,82 @@ def test_interleave_and_deinterleave_are_inverse_bit_moves(bsir, dtype, channels
     assert torch.equal(only[channels - 1], srcs[-1]) and all(o is None for o in only[:-1])
 
 
-def test_broadcast_binary_ops_run_as_compiled_chains(bsir):
-    """A float binary op with a per-column or per-row operand takes the fused-chain kernel (16-byte accesses); the
-    bits are those of the indexed kernel, which still serves ragged rows."""
+def _in_fresh_thread(fn):
+    """Runs fn in a new thread and returns (its result, the fused-chain path that thread used: "none" when the chain
+    executor, and with it the runtime compiler, was never entered)."""
+    import threading
+    box = {}
+
+    def run():
+        try:
+            box["out"] = fn()
+        except BaseException as e:                                   # noqa: BLE001 - re-raised in the caller's thread
+            box["err"] = e
+        box["path"] = bsir_mod().FusedChain.last_path()
+    t = threading.Thread(target=run)
+    t.start()
+    t.join()
+    if "err" in box:
+        raise box["err"]
+    return box["out"], box["path"]
+
+
+def bsir_mod():
+    import bsir
+    return bsir
+
+
+def test_broadcast_binary_ops_use_the_precompiled_vector_kernel(bsir):
+    """A binary op with a per-column or per-row operand (hivm's inline broadcast), an immediate or an in-memory scalar
+    runs the library's own 16-byte-vector kernel: no fused-chain call, no runtime compiler.  Bits as the oracle's;
+    ragged rows still go to the indexed kernel."""
     x = torch.randn(300, 1024, device="cuda").to(torch.bfloat16)
     bias = torch.randn(1024, device="cuda").to(torch.bfloat16)
     scale = (torch.rand(300, 1, device="cuda") + 0.5).to(torch.bfloat16)
-    for fn, other in (("add", bias.view(1, -1).expand(300, 1024)), ("mul", scale.expand(300, 1024)), ("sub", bias.view(1, -1).expand(300, 1024))):
-        y = bsir.elemwise_binary(fn, x, other)
-        assert bsir.FusedChain.last_path() == "compiled"
+    one = torch.full((1, 1), 1.5, device="cuda", dtype=torch.bfloat16)
+    for fn, other in (("add", bias.view(1, -1).expand(300, 1024)), ("mul", scale.expand(300, 1024)), ("sub", bias.view(1, -1).expand(300, 1024)),
+                      ("div", one.expand(300, 1024)), ("maxf", scale.expand(300, 1024)), ("powf", one.expand(300, 1024))):
+        y, path = _in_fresh_thread(lambda: bsir.elemwise_binary(fn, x, other))
+        assert path == "none"
         want = O.elemwise_binary(fn, O.BF16, to_bits(x), to_bits(other.contiguous()))
         assert_bits_equal(y, want, f"broadcast {fn}")
         z = bsir.elemwise_binary(fn, other, x)                     # the broadcast operand on the left
         assert_bits_equal(z, O.elemwise_binary(fn, O.BF16, to_bits(other.contiguous()), to_bits(x)), f"broadcast r{fn}")
+    # row vector against column vector: both operands broadcast
+    outer = bsir.elemwise_binary("mul", bias.view(1, -1).expand(300, 1024), scale.expand(300, 1024))
+    assert_bits_equal(outer, O.elemwise_binary("mul", O.BF16, to_bits(bias.view(1, -1).expand(300, 1024).contiguous()),
+                                               to_bits(scale.expand(300, 1024).contiguous())), "outer mul")
+    # f32 and integers take the same kernel
+    xf = torch.randn(64, 260, device="cuda")
+    bf = torch.randn(260, device="cuda")
+    assert_bits_equal(bsir.elemwise_binary("add", xf, bf.view(1, -1).expand(64, 260)),
+                      O.elemwise_binary("add", O.F32, to_bits(xf), to_bits(bf.view(1, -1).expand(64, 260).contiguous())), "f32 bias")
+    xi = torch.randint(-1000, 1000, (70, 64), device="cuda", dtype=torch.int32)
+    ci = torch.randint(-1000, 1000, (70, 1), device="cuda", dtype=torch.int32)
+    for fn in ("add", "mul", "max_signed"):
+        assert torch.equal(bsir.elemwise_binary(fn, xi, ci.expand(70, 64)).cpu(),
+                           torch.from_numpy(O.elemwise_binary(fn, O.I32, xi.cpu().numpy(), ci.expand(70, 64).contiguous().cpu().numpy())))
     ragged = torch.randn(50, 1001, device="cuda")
-    y = bsir.elemwise_binary("add", ragged, torch.randn(1001, device="cuda").view(1, -1).expand(50, 1001))
-    assert y.shape == ragged.shape
+    rb = torch.randn(1001, device="cuda").view(1, -1).expand(50, 1001)
+    assert_bits_equal(bsir.elemwise_binary("add", ragged, rb), O.elemwise_binary("add", O.F32, to_bits(ragged), to_bits(rb.contiguous())), "ragged")
 
 
-def test_row_strided_views_run_as_compiled_chains(bsir):
+def test_row_strided_views_use_the_precompiled_vector_kernel(bsir):
     """Slices of wider tensors (row stride > row length, 16-byte aligned rows) as operands and as the result."""
     big_a = torch.randn(200, 512, device="cuda").to(torch.float16)
     big_b = torch.randn(200, 640, device="cuda").to(torch.float16)
     a, b = big_a[:, 64:320], big_b[:, 128:384]                     # 256 columns each
     out_big = torch.zeros(200, 400, device="cuda", dtype=torch.float16)
     out = out_big[:, 8:264]
-    bsir.elemwise_binary("mul", a, b, out=out)
-    assert bsir.FusedChain.last_path() == "compiled"
+    _, path = _in_fresh_thread(lambda: bsir.elemwise_binary("mul", a, b, out=out))
+    assert path == "none"
     assert_bits_equal(out.contiguous(), O.elemwise_binary("mul", O.F16, to_bits(a.contiguous()), to_bits(b.contiguous())), "strided mul")
     assert out_big[:, :8].abs().sum().item() == 0 and out_big[:, 264:].abs().sum().item() == 0
-    y = bsir.elemwise_unary("exp", a)
-    assert bsir.FusedChain.last_path() == "compiled"
+    y, path = _in_fresh_thread(lambda: bsir.elemwise_unary("exp", a))
+    assert path == "none"
     assert_bits_equal(y, O.elemwise_unary("exp", O.F16, to_bits(a.contiguous())), "strided exp")
+    z = bsir.elemwise_binary("add", a, 2.5)                         # strided tensor and an immediate
+    assert_bits_equal(z, O.elemwise_binary("add", O.F16, to_bits(a.contiguous()), to_bits(torch.full_like(a, 2.5).contiguous())), "strided + imm")
     odd = big_a[:, 3:259]                                          # rows not 16-byte aligned: the indexed kernel
     assert_bits_equal(bsir.elemwise_unary("abs", odd), O.elemwise_unary("abs", O.F16, to_bits(odd.contiguous())), "unaligned abs")
 
