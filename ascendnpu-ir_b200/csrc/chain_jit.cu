@@ -85,6 +85,7 @@ struct Args {
   i64 in_stride[8];
   void *out[4];
   i64 out_stride[4];
+  int *err;
 };
 __device__ __forceinline__ V4 ld_stream(const void *p) {
   V4 v;
@@ -173,6 +174,33 @@ ROW_REDUCE(row_sum, red_sum)
 ROW_REDUCE(row_prod, red_prod)
 ROW_REDUCE(row_max, red_max)
 ROW_REDUCE(row_min, red_min)
+)SRC";
+
+// Persistent row programs: rows arrive in shared memory through bulk copies that complete on an mbarrier.
+const char *kRing = R"SRC(
+__device__ __forceinline__ u32 smem_u32(const void *p) { return (u32)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool mbar_try(u32 bar, u32 parity) {
+  u32 ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// bounded: gives up after about two seconds and raises the device error word
+__device__ __forceinline__ bool mbar_wait_bounded(u32 bar, u32 parity, int *err) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (u32 spin = 0;; ++spin) {
+    if (mbar_try(bar, parity)) return true;
+    if ((spin & 1023u) == 1023u && clock64() - t0 > 4000000000LL) {
+      if (err) atomicOr(err, 0x20);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void bulk_row(u32 dst, const void *src, u32 bytes, u32 bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
 )SRC";
 
 const char *dtype_tag(int dt) { return dt == BSIR_F32 ? "f32" : dt == BSIR_BF16 ? "bf16" : "f16"; }
@@ -453,6 +481,49 @@ std::string row_source(const ChainJitSpec &s) {
   std::string c = kPrelude;
   appendf(c, "#define TPR %d\n#define VPT %d\n#define BT %d\n", tpr, vpt, bt);
   c += kRowReduce;
+  const bool ring = s.ring > 0;
+  if (ring) {
+    // one row per block at a time (TPR == BT); row k of this block is row blockIdx.x + k * gridDim.x
+    c += kRing;
+    appendf(c, "#define NBUF %d\n", s.ring);
+    int group_bytes = 0;   // bytes of one 8-element group over all staged operands
+    for (int i = 0; i < s.n_in; ++i)
+      if (s.in_kind[i] == BSIR_CHAIN_FULL) group_bytes += s.in_dtype[i] == BSIR_F32 ? 32 : 16;
+    c += "extern \"C\" __global__ void __launch_bounds__(BT) bsir_chain(const __grid_constant__ Args a) {\n"
+         "  extern __shared__ __align__(128) unsigned char ring_mem[];\n"
+         "  __shared__ float red[BT / 32];\n"
+         "  __shared__ __align__(8) unsigned long long bars[NBUF];\n"
+         "  const int lane = threadIdx.x;\n"
+         "  bool live[VPT];\n  i64 c0v[VPT];\n"
+         "#pragma unroll\n  for (int q = 0; q < VPT; ++q) { const i64 g = lane + q * TPR; live[q] = g < a.gpr; c0v[q] = g * 8; }\n";
+    appendf(c, "  const u32 row_bytes = (u32)a.gpr * %du;\n", group_bytes);
+    c += "  const i64 my_rows = (a.rows - blockIdx.x + gridDim.x - 1) / gridDim.x;\n"
+         "  if (threadIdx.x == 0) {\n"
+         "    for (int b = 0; b < NBUF; ++b) asm volatile(\"mbarrier.init.shared::cta.b64 [%0], 1;\" ::\"r\"(smem_u32(&bars[b])) : \"memory\");\n"
+         "    asm volatile(\"fence.mbarrier_init.release.cluster;\" ::: \"memory\");\n"
+         "  }\n"
+         "  __syncthreads();\n"
+         "  auto issue = [&](i64 kk) {   // bulk copies of this block's kk-th row into buffer kk % NBUF\n"
+         "    const int b = (int)(kk % NBUF);\n"
+         "    const i64 r = blockIdx.x + kk * gridDim.x;\n"
+         "    const u32 bar = smem_u32(&bars[b]), dst = smem_u32(ring_mem) + (u32)b * row_bytes;\n"
+         "    asm volatile(\"mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\" ::\"r\"(bar), \"r\"(row_bytes) : \"memory\");\n";
+    int off = 0;
+    for (int i = 0; i < s.n_in; ++i) {
+      if (s.in_kind[i] != BSIR_CHAIN_FULL) continue;
+      const int eb = s.in_dtype[i] == BSIR_F32 ? 4 : 2;
+      appendf(c, "    bulk_row(dst + (u32)a.gpr * %du, (const char *)a.in[%d] + r * a.in_stride[%d] * %d, (u32)a.gpr * %du, bar);\n", off, i, i, eb, 8 * eb);
+      off += 8 * eb;
+    }
+    c += "  };\n"
+         "  if (threadIdx.x == 0)\n    for (i64 kk = 0; kk < NBUF - 1 && kk < my_rows; ++kk) issue(kk);\n"
+         "  bool ok = true;\n"
+         "  for (i64 k = 0; k < my_rows; ++k) {\n"
+         "  const i64 row = blockIdx.x + k * gridDim.x;\n"
+         "  if (ok && !mbar_wait_bounded(smem_u32(&bars[k % NBUF]), (u32)((k / NBUF) & 1), a.err)) ok = false;\n"
+         "  const bool row_ok = ok;\n"
+         "  const unsigned char *buf = ring_mem + (size_t)(k % NBUF) * row_bytes;\n";
+  } else {
   c += "extern \"C\" __global__ void __launch_bounds__(BT) bsir_chain(const __grid_constant__ Args a) {\n"
        "  __shared__ float red[BT / 32];\n"
        "  const int lane = threadIdx.x % TPR;\n"
@@ -461,6 +532,7 @@ std::string row_source(const ChainJitSpec &s) {
        "  const i64 row = row_ok ? row_id : 0;          // threads past the last row redo row 0 and store nothing\n"
        "  bool live[VPT];\n  i64 c0v[VPT];\n"
        "#pragma unroll\n  for (int q = 0; q < VPT; ++q) { const i64 g = lane + q * TPR; live[q] = g < a.gpr; c0v[q] = g * 8; }\n";
+  }
   for (int i = 0; i < s.n_in; ++i) {
     const char *tag = dtype_tag(s.in_dtype[i]);
     switch (s.in_kind[i]) {
@@ -474,9 +546,22 @@ std::string row_source(const ChainJitSpec &s) {
     }
   }
   c += "#pragma unroll\n  for (int q = 0; q < VPT; ++q) {\n    const i64 c0 = c0v[q];\n";
+  int ring_off = 0;
   for (int i = 0; i < s.n_in; ++i) {
     const int k = s.in_kind[i];
     if (k != BSIR_CHAIN_FULL && k != BSIR_CHAIN_ROW_VECTOR) continue;
+    if (ring && k == BSIR_CHAIN_FULL) {
+      // from this row's buffer: operand i's row starts a.gpr * ring_off bytes in
+      const int eb = s.in_dtype[i] == BSIR_F32 ? 4 : 2;
+      if (s.in_dtype[i] == BSIR_F32) {
+        appendf(c, "    r%da[q] = r%db[q] = V4{0, 0, 0, 0};\n", i, i);
+        appendf(c, "    if (live[q]) { const V4 *sp = (const V4 *)(buf + (size_t)a.gpr * %d + c0 * 4); r%da[q] = sp[0]; r%db[q] = sp[1]; }\n", ring_off, i, i);
+      } else {
+        appendf(c, "    r%d[q] = V4{0, 0, 0, 0};\n    if (live[q]) r%d[q] = *(const V4 *)(buf + (size_t)a.gpr * %d + c0 * 2);\n", i, i, ring_off);
+      }
+      ring_off += 8 * eb;
+      continue;
+    }
     const char *ld = k == BSIR_CHAIN_ROW_VECTOR ? "ld_keep" : s.alias ? "ld_plain" : "ld_stream";
     std::string off = k == BSIR_CHAIN_ROW_VECTOR ? "c0" : std::string("(row * a.in_stride[") + std::to_string(i) + "] + c0)";
     if (s.in_dtype[i] == BSIR_F32) {
@@ -488,6 +573,11 @@ std::string row_source(const ChainJitSpec &s) {
     }
   }
   c += "  }\n";
+  if (ring)
+    c += "  // every thread has its part of this row in registers, and the buffer the row before was read from is free:\n"
+         "  // start the copy of the row NBUF - 1 ahead into it\n"
+         "  __syncthreads();\n"
+         "  if (threadIdx.x == 0 && k + NBUF - 1 < my_rows) issue(k + NBUF - 1);\n";
   bool tmp_used[4] = {false, false, false, false};
   for (int i = 0; i < s.n_instr; ++i)
     if (s.tape[i].op == BSIR_CHAIN_SAVE) tmp_used[s.tape[i].src] = true;
@@ -571,6 +661,7 @@ std::string row_source(const ChainJitSpec &s) {
     }
     c += "  }\n";
   }
+  if (ring) c += "  }\n";   // the row loop
   c += "}\n";
   return c;
 }
@@ -590,7 +681,7 @@ std::string spec_key(const ChainJitSpec &s) {
   std::string k;
   auto put = [&](int32_t v) { k.append(reinterpret_cast<const char *>(&v), sizeof v); };
   put(s.n_in); put(s.n_instr); put(s.n_out);
-  put(s.flat); put(s.alias); put(s.row_grid); put(chain_jit_unroll(s)); put(s.tpr); put(s.vpt);
+  put(s.flat); put(s.alias); put(s.row_grid); put(chain_jit_unroll(s)); put(s.tpr); put(s.vpt); put(s.ring);
   for (int i = 0; i < s.n_in; ++i) { put(s.in_dtype[i]); put(s.in_kind[i]); }
   for (int i = 0; i < s.n_instr; ++i) {
     const bsir_chain_instr &t = s.tape[i];
@@ -630,6 +721,27 @@ int chain_jit_launch(const ChainJitSpec &s, const ChainJitArgs &args, cudaStream
       return -1;
     }
     kernel = it->second.kernel;
+  }
+  if (s.tpr > 0 && s.ring > 0) {
+    // persistent blocks, as many as are resident at once; the ring lives in dynamic shared memory
+    size_t row_bytes = 0;
+    for (int i = 0; i < s.n_in; ++i)
+      if (s.in_kind[i] == BSIR_CHAIN_FULL) row_bytes += static_cast<size_t>(args.gpr) * (s.in_dtype[i] == BSIR_F32 ? 32 : 16);
+    const size_t smem = row_bytes * s.ring;
+    const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
+    int64_t nblocks = sms;   // 1024 threads with the registers a row takes: one block per SM
+    if (nblocks > args.rows) nblocks = args.rows;
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void *>(kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    ChainJitArgs copy = args;
+    void *params[] = {&copy};
+    if (e == cudaSuccess)
+      e = cudaLaunchKernel(reinterpret_cast<const void *>(kernel), dim3(static_cast<unsigned>(nblocks)), dim3(s.tpr), params, smem, st);
+    if (e != cudaSuccess) {
+      *why = std::string("launching the compiled chain: ") + cudaGetErrorString(e);
+      (void)cudaGetLastError();
+      return -1;
+    }
+    return 0;
   }
   if (s.tpr > 0) {
     const int bt = s.tpr > 128 ? s.tpr : 128;

@@ -23,6 +23,9 @@ struct ChainJitSpec {
   // a chain with last-axis reductions (a row program): threads per row and groups per thread; 0: no reductions
   int tpr = 0, vpt = 0;
   bool out_per_row[4] = {};   // the output is a [rows] vector (its value is the same along the row)
+  // > 0: the block is persistent and its rows arrive through a ring of this many shared-memory buffers filled by bulk
+  // copies (rows so long that one or two blocks fill an SM: without the ring the SM loads, computes and stores in turn)
+  int ring = 0;
 };
 
 // The kernel's parameter block (the generated source declares the same layout).
@@ -32,6 +35,7 @@ struct ChainJitArgs {
   long long in_stride[8];
   void *out[4];
   long long out_stride[4];
+  int *err;   // device error word (a bounded wait that gave up sets a bit in it)
 };
 
 int chain_jit_unroll(const ChainJitSpec &s);          // groups per thread

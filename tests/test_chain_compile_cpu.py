@@ -110,6 +110,10 @@ def test_chains_with_reductions_compile_for_short_and_long_rows():
     assert "row_sum(p, red)" in mid and "((float *)a.out[1])[row] = t0[0][0]" in mid
     for cols in (64, 4096, 32768):
         assert ch.compile(outs=outs, cols=cols) > 1000
+    # rows that fill an SM's registers: persistent blocks, rows through a ring of bulk copies; not when in place
+    long_rows = ch.source(outs=outs, cols=32768)
+    assert "#define TPR 1024\n" in long_rows and "#define NBUF 3\n" in long_rows and "cp.async.bulk.shared::cluster.global" in long_rows
+    assert "NBUF" not in mid and "NBUF" not in ch.source(outs=outs, cols=32768, in_place=True)
     with pytest.raises(bsir.BsirError):
         ch.source(outs=outs, cols=1 << 20)                       # a row that no block can hold
     ch2 = bsir.FusedChain()

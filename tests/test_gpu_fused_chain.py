@@ -166,7 +166,8 @@ def _rms_chain(bsir, x, gamma, eps):
 
 
 @pytest.mark.parametrize("dtype,rows,cols", [(torch.bfloat16, 64, 4096), (torch.float16, 40, 512), (torch.float32, 1001, 64),
-                                             (torch.bfloat16, 7, 8192), (torch.bfloat16, 3, 32768), (torch.float16, 300, 8)])
+                                             (torch.bfloat16, 7, 8192), (torch.bfloat16, 3, 32768), (torch.float16, 300, 8),
+                                             (torch.bfloat16, 600, 32768)])
 def test_rms_norm_as_a_chain_with_a_reduction(bsir, dtype, rows, cols):
     """A whole RMSNorm (LAST_AXIS_PBR): square, row sum, scalar tail, two multiplies, the per-row rstd as a second
     output -- one kernel, against the oracle's RMSNorm (the row sum associates differently: tolerance as for the
@@ -184,8 +185,11 @@ def test_rms_norm_as_a_chain_with_a_reduction(bsir, dtype, rows, cols):
     assert_close(rstd, wr, 1e-2, 1e-3, "rstd of the chain")
 
 
-@pytest.mark.parametrize("dtype,rows,cols", [(torch.bfloat16, 33, 4096), (torch.float32, 257, 1000), (torch.float16, 5, 32768)])
+@pytest.mark.parametrize("dtype,rows,cols", [(torch.bfloat16, 33, 4096), (torch.float32, 257, 1000), (torch.float16, 5, 32768),
+                                             (torch.bfloat16, 700, 32768), (torch.float32, 333, 24576)])
 def test_softmax_as_a_chain_with_two_reductions(bsir, dtype, rows, cols):
+    """The last two shapes: rows that fill an SM's registers run as persistent blocks fed by a ring of bulk copies,
+    each block going through four or five rows (every buffer of the ring is reused)."""
     g = torch.Generator(device="cuda").manual_seed(rows)
     x = (4 * torch.randn(rows, cols, device="cuda", generator=g)).to(dtype)
     ch = bsir.FusedChain()
