@@ -136,7 +136,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_total / n * 1e3 * (ROWS / sample_rows),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32->i8", "data": "synthetic",
-        "config": {"workload": "per-token int8 quant bf16 [16384,4096]", "rows": ROWS, "cols": COLS},
+        "config": {"workload": "per-token int8 quant bf16 [16384,4096]", "rows": ROWS, "cols": COLS,
+                   "sample": f"each step runs {sample_rows} of the {ROWS} rows; value is bytes of the sample / its time, ms_per_step is scaled to the full batch"},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
                          "sample": f"{sample_rows} of {ROWS} rows per step; ms_per_step scaled to the full batch"},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -18,6 +18,9 @@
  */
 #ifndef BSIR_B200_CIFACE_H_
 #define BSIR_B200_CIFACE_H_
+#ifndef __cplusplus
+#include <stdbool.h> /* the sort symbols take the reference's `bool descending` */
+#endif
 
 /* The reference's library functions return void; these return a bsir_status in the integer return
  * register, which a caller that declared them void simply does not read (the C calling conventions
