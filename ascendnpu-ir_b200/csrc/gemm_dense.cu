@@ -560,8 +560,15 @@ __device__ __forceinline__ bool decode_segment(const GemmParams &p, int b, int g
   return g.kb0 < p.k_blocks && g.tile < p.n_tiles;
 }
 
+// Four threads issue the MMAs: the thread that issues a tcgen05.mma is held for about 140 cycles by each one
+// whatever its shape, so one issuer spent 570 cycles on the four MMAs of a 128-byte k block -- 60 GB/s of weights per
+// CTA, which is what bounded this kernel.  Issuer j (warp 1 and the three warps after the epilogue warps) takes the
+// j-th 32-byte k step of every block into an accumulator of its own; the epilogue adds the four (int32: exact, so
+// the bits do not depend on the order).
+constexpr int kDecIssuers = 4;
+constexpr int kDecThreads = kThreads + 32 * (kDecIssuers - 1);
 template <bool W_MN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kDecThreads, 1)
     w8a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, GemmParams p,
                        int nb, int stage_bytes, int nstages) {
   extern __shared__ uint8_t smem_raw[];
@@ -579,7 +586,10 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x, grid = gridDim.x;
-  const uint32_t tmem_cols = 2 * nb < 32 ? 32u : (2 * nb <= 64 ? 64u : (2 * nb <= 128 ? 128u : 256u));
+  // one accumulator per issuer when they fit (4 x 2 x nb columns of tensor memory), else all into one
+  const int nacc = nb <= 64 ? kDecIssuers : 1;
+  const uint32_t want_cols = static_cast<uint32_t>(2 * nacc * nb);
+  const uint32_t tmem_cols = want_cols <= 32 ? 32u : (want_cols <= 64 ? 64u : (want_cols <= 128 ? 128u : (want_cols <= 256 ? 256u : 512u)));
   const float *scale_b = static_cast<const float *>(p.descale);
 
   // Load number `it` of this CTA uses stage it % nstages.  All segments of a CTA have the same number of k blocks,
@@ -622,8 +632,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (lane == 0) {
       prefetch_tmap(&tmap_w);
       prefetch_tmap(&tmap_a);
-      for (int s = 0; s < nstages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-      for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+      for (int s = 0; s < nstages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), kDecIssuers); }
+      for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), kDecIssuers); mbar_init(tempty_bar(a), 4); }
       *abort_flag = 0;
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -659,9 +669,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (mbar_try_wait(full_bar(s), 0) || mbar_try_wait(full_bar(s), 1)) break;
       }
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer
+  } else if (warp == 1 || warp >= 6) {
+    // ---------------- MMA issuers: warp 1 takes k step 0 of every block, warps 6..8 steps 1..3
     if (lane == 0) {
+      const int issuer = warp == 1 ? 0 : warp - 5;
       // D = s32, A (weights) and B (activations) signed int8; A's major per the weight layout; N = nb, M = 128
       const uint32_t idesc = make_idesc<KI8>(W_MN, false, nb, kBM);
       int stage = 0;
@@ -673,22 +684,30 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int s = 0; ok && decode_segment(p, cta, grid, s, g); ++s) {
         if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * nb);
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((acc * nacc + (nacc > 1 ? issuer : 0)) * nb);
         for (int kb = g.kb0; kb < g.kb1; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.err)) { ok = false; break; }
-          if (s == 0 && kb == g.kb0) TL(2);
+          if (s == 0 && kb == g.kb0 && issuer == 0) TL(2);
           tc_fence_after();
           const uint32_t sw = base + stage * stage_bytes;
           const uint32_t sa = sw + kDecStageW;
+          if (nacc > 1) {
+            mma_ss<KI8>(d_tmem, operand_desc<KI8>(sw, issuer, W_MN), operand_desc<KI8>(sa, issuer, false), idesc, kb > g.kb0 ? 1u : 0u);
+            tc_commit(empty_bar(stage));
+          } else if (issuer == 0) {     // one accumulator for all: a single issuer keeps the k steps in order
 #pragma unroll
-          for (int kk = 0; kk < kBK / kUmmaK; ++kk)
-            mma_ss<KI8>(d_tmem, operand_desc<KI8>(sw, kk, W_MN), operand_desc<KI8>(sa, kk, false), idesc, (kb > g.kb0 || kk > 0) ? 1u : 0u);
-          tc_commit(empty_bar(stage));
+            for (int kk = 0; kk < kBK / kUmmaK; ++kk)
+              mma_ss<KI8>(d_tmem, operand_desc<KI8>(sw, kk, W_MN), operand_desc<KI8>(sa, kk, false), idesc, (kb > g.kb0 || kk > 0) ? 1u : 0u);
+            tc_commit(empty_bar(stage));
+          } else {
+            mbar_arrive(empty_bar(stage));
+          }
           if (++stage == nstages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        tc_commit(tfull_bar(acc));
-        TL(3);
+        if (nacc > 1 || issuer == 0) tc_commit(tfull_bar(acc));
+        else mbar_arrive(tfull_bar(acc));
+        if (issuer == 0) TL(3);
         acc_phase[acc] ^= 1u;
         acc ^= 1;
       }
@@ -715,7 +734,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, p.err)) { ok = false; break; }
       if (threadIdx.x == 64) TL(4);
       tc_fence_after();
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * nb);
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * nacc * nb);
+      auto load_sum16 = [&](int c0, uint32_t (&r)[16]) {      // the issuers' accumulators added up, 16 rows of `a`
+        tmem_ld16(t_row + static_cast<uint32_t>(c0), r);
+        for (int j = 1; j < nacc; ++j) {
+          uint32_t q[16];
+          tmem_ld16(t_row + static_cast<uint32_t>(j * nb + c0), q);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) r[e] += q[e];
+        }
+        tmem_ld_wait();
+      };
       bool finish = true;
       int32_t *tile_slots = nullptr;
       if (parts > 1) {
@@ -723,8 +753,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         int32_t *mine = tile_slots + g.part * slot_words;
         for (int c0 = 0; c0 < nb && c0 < p.m; c0 += 16) {
           uint32_t r[16];
-          tmem_ld16(t_row + static_cast<uint32_t>(c0), r);
-          tmem_ld_wait();
+          load_sum16(c0, r);
 #pragma unroll
           for (int j = 0; j < 16; ++j)
             if (c0 + j < p.m) __stcg(mine + static_cast<size_t>(c0 + j) * kBM + quad * 32 + lane, static_cast<int32_t>(r[j]));
@@ -742,8 +771,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       for (int c0 = 0; c0 < nb && finish; c0 += 16) {
         uint32_t r[16];
-        tmem_ld16(t_row + static_cast<uint32_t>(c0), r);
-        tmem_ld_wait();
+        load_sum16(c0, r);
         if (parts > 1 && c0 < p.m) {
           for (int q = 0; q < parts; ++q) {
             if (q == g.part) continue;
@@ -1276,10 +1304,10 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
           }
           if (b_mn) {
             cudaFuncSetAttribute(w8a8_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dc.smem));
-            launch_pdl(w8a8_decode_kernel<true>, dim3(grid), dim3(kThreads), dc.smem, st, tw, tact, p, dc.nb, dc.stage, dc.stages);
+            launch_pdl(w8a8_decode_kernel<true>, dim3(grid), dim3(kDecThreads), dc.smem, st, tw, tact, p, dc.nb, dc.stage, dc.stages);
           } else {
             cudaFuncSetAttribute(w8a8_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dc.smem));
-            launch_pdl(w8a8_decode_kernel<false>, dim3(grid), dim3(kThreads), dc.smem, st, tw, tact, p, dc.nb, dc.stage, dc.stages);
+            launch_pdl(w8a8_decode_kernel<false>, dim3(grid), dim3(kDecThreads), dc.smem, st, tw, tact, p, dc.nb, dc.stage, dc.stages);
           }
           count_launch();
           return check_launch("matmul (decode)");

@@ -604,6 +604,283 @@ __global__ void __launch_bounds__(kTcThreads, 1)
   }
 }
 
+// ------------------------------------------------------------------ folded-scale kernel (tcgen05, bf16 operands from shared memory)
+// out[m, n] = sum over groups g of  s[g, n] * ( sum_{k in g} a[m, k] * (q[k, n] - 8)  -  (z[g, n] - 8) * A[g, m] ),
+// A[g, m] = sum_{k in g} a[m, k].  The inner sum is a bf16 x bf16 product on the tensor core; a packed word turns
+// into its eight operand values q - 8 with twelve instructions (four shifts, four lop3, four exact sub.bf16x2) and
+// no per-weight multiplication or rounding -- the zero point and the scale act once per group and column, on the
+// group's accumulator, in the epilogue.  The exact-rounding kernels above spend fifteen instructions per word.  Against the oracle (every dequantised weight
+// rounded to bf16 first) the result differs by those roundings: a relative RMS of about 1e-3, inside the 2e-2 bar.
+//
+// One CTA per 128 output columns, all of K.  Roles: warp 0 issues TMA loads (a stage = 64 k: 4 KB of packed weights
+// + the 16 x 64 activations), warps 6-21 turn a packed stage into the tensor core's K-major bf16 tile (128 rows =
+// output columns x 128 bytes, 128-byte swizzle) in a ring of operand slots and put the activations into the same
+// nibble-pair k order, warp 1 issues four MMAs (M = 128, N = 16, K = 16) per stage into one of two group
+// accumulators in tensor memory, warps 2-5 fold a finished group into f32 partial sums held in registers.
+constexpr int kFoldCols = 128;
+constexpr int kFoldPStage = 8 * kFoldCols * 4 + 2048;        // packed weights + activations: 6 KB
+constexpr int kFoldPStages = 24;     // 144 KB of packed stages in flight: a CTA streams what it keeps in flight per memory latency
+constexpr int kFoldOStage = kFoldCols * 128 + 2048;          // bf16 weight tile + permuted activations: 18 KB
+constexpr int kFoldOStages = 4;
+constexpr int kFoldDqWarps = 16;
+constexpr int kFoldThreads = (6 + kFoldDqWarps) * 32;
+constexpr int kFoldMaxGroups = 512;
+
+// Nibbles t and t + 4 of a packed word as the bf16 pair (q_t - 8, q_{t+4} - 8): 16 + q is the bf16 with bit pattern
+// 0x4180 | q << 3 (one shift, one lop3), and subtracting 24 is exact.  The operand is centred because the tensor
+// core adds the products of one instruction with about 13 bits below the largest addend: with 128 + q as the operand
+// (no subtraction) the group sums came back with a relative error of 2^-11.6, which the zero-point term magnified.
+__device__ __forceinline__ uint32_t centred_pair_bf16(uint32_t w, int t) {
+  uint32_t r;
+  const uint32_t sh = t == 0 ? (w << 3) : (w >> (4 * t - 3));
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(sh), "r"(0x00780078u), "r"(0x41804180u));
+  return bf16x2_sub(r, 0x41C041C0u);        // 24.0 in both halves
+}
+
+__device__ __forceinline__ void mma_bf16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+inline size_t fold_smem_bytes(int64_t groups) {
+  return 1024 /*alignment*/ + static_cast<size_t>(kFoldOStages) * kFoldOStage + static_cast<size_t>(kFoldPStages) * kFoldPStage +
+         static_cast<size_t>(groups) * 16 * 4 /*activation sums*/ + 4096 /*output staging*/ + 1024 /*barriers*/;
+}
+
+#ifdef BSIR_FOLD_TL
+__device__ unsigned long long *g_fold_tl = nullptr;
+#define FW(var, call) ([&] { const long long t0_ = clock64(); const bool r_ = (call); (var) += clock64() - t0_; return r_; }())
+#define FTL(i, v) do { if (g_fold_tl && blockIdx.x == 0) g_fold_tl[i] = static_cast<unsigned long long>(v); } while (0)
+#else
+#define FW(var, call) (call)
+#define FTL(i, v) do { } while (0)
+#endif
+__global__ void __launch_bounds__(kFoldThreads, 1)
+    w4a16_fold_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, W4Params p, int64_t m0, int *err) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;                    // operand slots first: 1024-byte aligned swizzle atoms
+  uint8_t *gen = smem_raw + (base - raw);
+  const uint32_t o_base = base, p_base = base + kFoldOStages * kFoldOStage;
+  const int groups = static_cast<int>(p.k / p.group), spg = static_cast<int>(p.group / 64), nstages = static_cast<int>(p.k / 64);
+  float *asum = reinterpret_cast<float *>(gen + kFoldOStages * kFoldOStage + kFoldPStages * kFoldPStage);   // [groups][16]
+  uint16_t *stg = reinterpret_cast<uint16_t *>(reinterpret_cast<uint8_t *>(asum) + static_cast<size_t>(groups) * 64);
+  const uint32_t bars = smem_u32(stg) + 4096;
+  auto full_p = [&](int s) { return bars + 8u * s; };
+  auto empty_p = [&](int s) { return bars + 8u * (kFoldPStages + s); };
+  auto full_o = [&](int s) { return bars + 8u * (2 * kFoldPStages + s); };
+  auto empty_o = [&](int s) { return bars + 8u * (2 * kFoldPStages + kFoldOStages + s); };
+  auto tfull = [&](int a) { return bars + 8u * (2 * kFoldPStages + 2 * kFoldOStages + a); };
+  auto tempty = [&](int a) { return bars + 8u * (2 * kFoldPStages + 2 * kFoldOStages + 2 + a); };
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(stg) + 4096 + 8 * (2 * kFoldPStages + 2 * kFoldOStages + 4));
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * kFoldCols;
+  const int rows = static_cast<int>(p.m - m0 < 16 ? p.m - m0 : 16);
+
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    prefetch_tmap(&tmap_w);
+    prefetch_tmap(&tmap_a);
+    for (int s = 0; s < kFoldPStages; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), 4); }
+    for (int s = 0; s < kFoldOStages; ++s) { mbar_init(full_o(s), 4); mbar_init(empty_o(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 4); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 32);
+  pdl_wait();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  long long wt0 = 0, wt1 = 0;
+  const long long tstart = clock64();
+  (void)wt0; (void)wt1; (void)tstart;
+
+  if (warp == 0) {
+    // ---------------- TMA producer
+    if (lane == 0) {
+      int slot = 0;
+      uint32_t round = 0;
+      bool ok = true;
+      for (int s = 0; s < nstages; ++s) {
+        if (!FW(wt0, mbar_wait(empty_p(slot), (round & 1u) ^ 1u, abort_flag, err))) { ok = false; break; }
+        const uint32_t dst = p_base + slot * kFoldPStage;
+        mbar_expect_tx(full_p(slot), kFoldPStage);
+        tma_load_2d(dst, &tmap_w, n0, s * 8, full_p(slot));                               // [8 word rows x 128 columns]
+        tma_load_2d(dst + 8 * kFoldCols * 4, &tmap_a, s * 64, static_cast<int>(m0), full_p(slot));   // [16 rows x 64 k]
+        if (++slot == kFoldPStages) { slot = 0; ++round; }
+      }
+      FTL(0, wt0); FTL(1, clock64() - tstart);
+      if (!ok) {
+        for (int q = 0; q < kFoldPStages; ++q)
+          for (int i = 0; i < 200000; ++i)
+            if (mbar_try_wait(full_p(q), 0) || mbar_try_wait(full_p(q), 1)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer
+    if (lane == 0) {
+      // D = f32, A = B = bf16, both K-major, N = 16, M = 128
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(16 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+      int slot = 0;
+      uint32_t round = 0, acc_phase[2] = {0u, 0u};
+      bool ok = true;
+      for (int g = 0; g < groups && ok; ++g) {
+        const int acc = g & 1;
+        if (!FW(wt1, mbar_wait(tempty(acc), acc_phase[acc] ^ 1u, abort_flag, err))) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 16);
+        for (int s = 0; s < spg; ++s) {
+          if (!FW(wt0, mbar_wait(full_o(slot), round & 1u, abort_flag, err))) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t wt = o_base + slot * kFoldOStage, at = wt + kFoldCols * 128;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk)
+            mma_bf16_ss(d_tmem, make_desc(wt + kk * 32, 16, 1024), make_desc(at + kk * 32, 16, 1024), idesc, (s > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(empty_o(slot));
+          if (++slot == kFoldOStages) { slot = 0; ++round; }
+        }
+        if (!ok) break;
+        tc_commit(tfull(acc));
+        acc_phase[acc] ^= 1u;
+      }
+      FTL(2, wt0); FTL(3, wt1); FTL(4, clock64() - tstart);
+    }
+  } else if (warp < 6) {
+    // ---------------- group fold + output: warps 2..5, TMEM lane quadrant = warp % 4; lane = output column
+    const int quad = warp & 3, et = (warp - 2) * 32 + lane;
+    // sums of the activations per (group, row): each of the 128 threads takes pairs et, et + 128, ...
+    for (int pr = et; pr < groups * 16; pr += 128) {
+      const int g = pr >> 4, r = pr & 15;
+      float sum = 0.0f;
+      if (r < rows) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(p.a + (m0 + r) * p.lda + static_cast<int64_t>(g) * p.group);
+        for (int i = 0; i < static_cast<int>(p.group / 8); ++i) {
+          const uint4 v = __ldg(src + i);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) sum += __uint_as_float(w[j] << 16) + __uint_as_float(w[j] & 0xffff0000u);
+        }
+      }
+      asum[pr] = sum;
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (threadIdx.x == 64) FTL(5, clock64() - tstart);
+    const int64_t col = static_cast<int64_t>(n0) + quad * 32 + lane;
+    const bool col_ok = col < p.n;
+    const int64_t cc = col_ok ? col : 0;
+    float part[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) part[j] = 0.0f;
+    uint32_t acc_phase[2] = {0u, 0u};
+    bool ok = true;
+    float s_next = __uint_as_float(static_cast<uint32_t>(p.scales[cc]) << 16);
+    uint32_t z_next = (p.zeros[cc >> 3] >> (4 * (cc & 7))) & 0xfu;
+    for (int g = 0; g < groups && ok; ++g) {
+      const int acc = g & 1;
+      const float sc = s_next, zc = static_cast<float>(static_cast<int>(z_next) - 8);
+      if (g + 1 < groups) {
+        s_next = __uint_as_float(static_cast<uint32_t>(p.scales[static_cast<int64_t>(g + 1) * p.n + cc]) << 16);
+        z_next = (p.zeros[static_cast<int64_t>(g + 1) * (p.n >> 3) + (cc >> 3)] >> (4 * (cc & 7))) & 0xfu;
+      }
+      if (!FW(wt0, mbar_wait(tfull(acc), acc_phase[acc], abort_flag, err))) { ok = false; break; }
+      tc_fence_after();
+      uint32_t r[16];
+      tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * 16), r);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty(acc));
+      acc_phase[acc] ^= 1u;
+      const float4 *as4 = reinterpret_cast<const float4 *>(asum + g * 16);
+#pragma unroll
+      for (int j4 = 0; j4 < 4; ++j4) {
+        const float4 av = as4[j4];          // same address in every lane: broadcast
+        part[4 * j4 + 0] = fmaf(sc, fmaf(-zc, av.x, __uint_as_float(r[4 * j4 + 0])), part[4 * j4 + 0]);
+        part[4 * j4 + 1] = fmaf(sc, fmaf(-zc, av.y, __uint_as_float(r[4 * j4 + 1])), part[4 * j4 + 1]);
+        part[4 * j4 + 2] = fmaf(sc, fmaf(-zc, av.z, __uint_as_float(r[4 * j4 + 2])), part[4 * j4 + 2]);
+        part[4 * j4 + 3] = fmaf(sc, fmaf(-zc, av.w, __uint_as_float(r[4 * j4 + 3])), part[4 * j4 + 3]);
+      }
+    }
+    if (threadIdx.x == 64) { FTL(6, wt0); FTL(7, clock64() - tstart); }
+    if (ok) {
+      uint32_t pk[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) pk[j] = pack_bf16x2(part[2 * j], part[2 * j + 1]);
+      const bool vec = p.n % 8 == 0 && p.ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(p.n_peers ? p.peer[0] : p.out) & 15u) == 0 && p.n_peers <= 1;
+      uint16_t *wst = stg + quad * 512;                     // this warp's 16 rows x 32 columns
+      if (vec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          wst[(2 * j) * 32 + lane] = static_cast<uint16_t>(pk[j] & 0xffffu);
+          wst[(2 * j + 1) * 32 + lane] = static_cast<uint16_t>(pk[j] >> 16);
+        }
+        __syncwarp();
+        uint16_t *dst = p.n_peers ? p.peer[0] : p.out;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          const int id = lane + 32 * t, rr = id >> 2, part4 = id & 3;
+          const int64_t c0 = static_cast<int64_t>(n0) + quad * 32 + part4 * 8;
+          if (rr < rows && c0 < p.n)
+            *reinterpret_cast<uint4 *>(dst + (m0 + rr) * p.ldo + c0) = *reinterpret_cast<const uint4 *>(wst + rr * 32 + part4 * 8);
+        }
+      } else if (col_ok) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (j < rows) store_out(p, (m0 + j) * p.ldo + col, static_cast<uint16_t>((j & 1) ? (pk[j >> 1] >> 16) : (pk[j >> 1] & 0xffffu)));
+      }
+    }
+  } else {
+    // ---------------- packed words -> bf16 operand tile; activations into the nibble-pair k order
+    // Four teams of four warps; team t owns operand slot t and takes stages t, t + 4, ...: the teams work on four
+    // different stages at once, so the latency of a stage's hand-over (barrier round trips, the proxy fence) is hidden
+    // by the other three.  A thread converts the eight words of one column and one 16-byte piece of activations.
+    const int dw = warp - 6, team = dw >> 2, tw = dw & 3;
+    static_assert(kFoldOStages == 4 && kFoldDqWarps == 16 && kFoldPStages % 4 == 0, "one operand slot per team");
+    uint8_t *ost = gen + team * kFoldOStage;
+    const int c = tw * 32 + lane;                                  // column = row of the operand tile
+    int pslot = team;
+    uint32_t pround = 0, oround = 0;
+    bool ok = true;
+    for (int s = team; s < nstages && ok; s += 4, ++oround) {
+      if (!FW(wt0, mbar_wait(full_p(pslot), pround & 1u, abort_flag, err))) { ok = false; break; }
+      const uint8_t *pst = gen + kFoldOStages * kFoldOStage + pslot * kFoldPStage;
+      uint32_t w[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) w[r] = reinterpret_cast<const uint32_t *>(pst)[r * kFoldCols + c];
+      const uint4 av = *reinterpret_cast<const uint4 *>(pst + 8 * kFoldCols * 4 + c * 16);
+      if (!FW(wt1, mbar_wait(empty_o(team), (oround & 1u) ^ 1u, abort_flag, err))) { ok = false; break; }
+#pragma unroll
+      for (int r = 0; r < 8; ++r)
+        *reinterpret_cast<uint4 *>(ost + c * 128 + ((r ^ (c & 7)) << 4)) =
+            make_uint4(centred_pair_bf16(w[r], 0), centred_pair_bf16(w[r], 1), centred_pair_bf16(w[r], 2), centred_pair_bf16(w[r], 3));
+      // (a0 .. a7) -> (a0, a4, a1, a5, a2, a6, a3, a7), piece by piece in the swizzled tile
+      *reinterpret_cast<uint4 *>(ost + kFoldCols * 128 + c * 16) =
+          make_uint4(__byte_perm(av.x, av.z, 0x5410), __byte_perm(av.x, av.z, 0x7632), __byte_perm(av.y, av.w, 0x5410), __byte_perm(av.y, av.w, 0x7632));
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) { mbar_arrive(full_o(team)); mbar_arrive(empty_p(pslot)); }
+      pslot += 4;
+      if (pslot >= kFoldPStages) { pslot -= kFoldPStages; ++pround; }
+    }
+    if (dw == 0 && lane == 0) { FTL(8, wt0); FTL(9, wt1); FTL(10, clock64() - tstart); }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 32);
+  }
+}
+
 // Plain path: any alignment; one thread per output column, one row block of up to 4 rows.
 __global__ void __launch_bounds__(128) w4a16_plain_kernel(W4Params p, int64_t m0) {
   const int64_t c = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -643,12 +920,12 @@ EncodeFnW4 encode_fn_w4() {
 }
 
 // qweight as a 2-D int32 tensor [k/8 rows, n columns]; box = [32 rows x 128 columns], no swizzle.
-bool make_weight_tmap(CUtensorMap *map, const uint32_t *qw, int64_t n, int64_t k) {
+bool make_weight_tmap(CUtensorMap *map, const uint32_t *qw, int64_t n, int64_t k, int box_rows = kTcStageRows) {
   EncodeFnW4 enc = encode_fn_w4();
   if (!enc) return false;
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(k / 8)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(n) * 4u};
-  cuuint32_t box[2] = {static_cast<cuuint32_t>(kTcCols), static_cast<cuuint32_t>(kTcStageRows)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kTcCols), static_cast<cuuint32_t>(box_rows)};
   cuuint32_t estr[2] = {1u, 1u};
   return enc(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<uint32_t *>(qw), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -713,6 +990,27 @@ static int32_t matmul_w4a16_impl(int64_t m, int64_t n, int64_t k, int64_t group,
       count_launch();
     }
     return check_launch("matmul_w4a16");
+  }
+  // The folded-scale kernel (scale and zero point applied per group in the epilogue) serves every row block when
+  // its shape fits; BSIR_W4A16_PATH=m / t keep to the exact-rounding kernels, =f insists on this one.
+  const bool fold_ok = fast && device_info().cc_major >= 10 && group % 64 == 0 && k % 64 == 0 && k / group <= kFoldMaxGroups &&
+                       fold_smem_bytes(k / group) <= 226 * 1024 && n_peers <= 1;
+  if (fold_ok && !(force && (force[0] == 'm' || force[0] == 't'))) {
+    CUtensorMap fw, fa;
+    if (make_weight_tmap(&fw, p.qw, n, k, 8) && make_act_tmap(&fa, p.a, m, k, lda)) {
+      const size_t smem = fold_smem_bytes(k / group);
+#ifdef BSIR_FOLD_TL
+      { const char *e = std::getenv("BSIR_FOLD_TL_PTR"); unsigned long long *ptr = e ? reinterpret_cast<unsigned long long *>(std::strtoull(e, nullptr, 0)) : nullptr;
+        cudaMemcpyToSymbol(g_fold_tl, &ptr, sizeof(ptr)); }
+#endif
+      cudaFuncSetAttribute(w4a16_fold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      for (int64_t m0 = 0; m0 < m; m0 += 16) {
+        launch_pdl(w4a16_fold_kernel, dim3(static_cast<unsigned>(ceil_div(n, kFoldCols))), dim3(kFoldThreads), smem, st, fw, fa, p, m0,
+                   device_error_word());
+        count_launch();
+      }
+      return check_launch("matmul_w4a16 (folded scales)");
+    }
   }
   CUtensorMap tw, ta;
   bool have_map = false;
