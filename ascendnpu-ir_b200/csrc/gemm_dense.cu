@@ -497,10 +497,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 // epilogue reads the accumulator with lanes = output columns and writes 64-byte runs per row.
 // It serves the W8A8 form of the epilogue (f32 per-row and per-channel scales, 16-bit output).
 //
-// With fewer tiles than SMs (112 for n = 14336) whole tiles leave SMs idle, so K is split -- in a way that keeps the
+// With two thirds of the SMs or fewer holding a tile (N-sharded decode), K is split -- in a way that keeps the
 // CTAs that run side by side on the same k blocks of neighbouring tiles, because a weight tile is 128 rows of 128
-// bytes and only neighbours in n at the same k make those rows one contiguous stretch of DRAM (dealing out
-// (tile, k block) ranges with every CTA at another k measured 25 us against 14 us for whole tiles).  With G CTAs
+// bytes and only neighbours in n at the same k make those rows one contiguous stretch of DRAM.  With G CTAs
 // and T tiles, G >= T: CTA b < levels * T (levels = G / T) takes k blocks [lvl * len, (lvl + 1) * len) of tile
 // b % T, lvl = b / T; the remaining G % T "helper" CTAs share the last range [levels * len, k_blocks), helper h
 // taking tiles h, h + helpers, ... one after the other.  len is the smallest block count that leaves a helper no
@@ -604,9 +603,7 @@ __global__ void __launch_bounds__(kDecThreads, 1)
     else nsegs = (p.n_tiles - (cta - p.dk_levels * p.n_tiles) + p.dk_helpers - 1) / p.dk_helpers;
   }
   const int total_its = nsegs * seg_len;
-  // The producer's cursor: counters that step, no division per load.  (A CTA streams one 18 KB stage per 570 cycles,
-  // 60 GB/s, however fast the loads are issued: the ring of 200 KB is what an SM keeps in flight, and it takes
-  // 3.3 us to land.  Only more CTAs stream faster, which is what the K split is for.)
+  // The producer's cursor: counters that step, no division per load.
   DecodeSeg pseg = seg0;
   int p_seg = 0, p_kb = seg0.kb0, p_stage = 0;
   uint32_t p_round = 0;

@@ -615,15 +615,19 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 // One CTA per 128 output columns, all of K.  Roles: warp 0 issues TMA loads (a stage = 64 k: 4 KB of packed weights
 // + the 16 x 64 activations), warps 6-21 turn a packed stage into the tensor core's K-major bf16 tile (128 rows =
 // output columns x 128 bytes, 128-byte swizzle) in a ring of operand slots and put the activations into the same
-// nibble-pair k order, warp 1 issues four MMAs (M = 128, N = 16, K = 16) per stage into one of two group
-// accumulators in tensor memory, warps 2-5 fold a finished group into f32 partial sums held in registers.
+// nibble-pair k order, warps 1-4 issue the MMAs (stage s is issued by warp 1 + s % 4: four MMAs M = 128, N = 16,
+// K = 16 into one of that issuer's two accumulators), warps 5-8 add the accumulators of a finished group's stages
+// and fold them into f32 partial sums held in registers.  Stage s always uses operand slot s % 4, packed slot s % 24,
+// dequantising team s % 4 and issuer s % 4: every barrier has the same waiters in every phase (a waiter that sits
+// out a phase cannot tell the phase it wants from the one two before it).
 constexpr int kFoldCols = 128;
 constexpr int kFoldPStage = 8 * kFoldCols * 4 + 2048;        // packed weights + activations: 6 KB
 constexpr int kFoldPStages = 24;     // 144 KB of packed stages in flight: a CTA streams what it keeps in flight per memory latency
 constexpr int kFoldOStage = kFoldCols * 128 + 2048;          // bf16 weight tile + permuted activations: 18 KB
 constexpr int kFoldOStages = 4;
 constexpr int kFoldDqWarps = 16;
-constexpr int kFoldThreads = (6 + kFoldDqWarps) * 32;
+constexpr int kFoldIssuers = 4;          // the thread that issues a tcgen05.mma is held about 140 cycles by each: stage s is issuer s % 4's
+constexpr int kFoldThreads = (1 + kFoldIssuers + 4 + kFoldDqWarps) * 32;
 constexpr int kFoldMaxGroups = 512;
 
 // Nibbles t and t + 4 of a packed word as the bf16 pair (q_t - 8, q_{t+4} - 8): 16 + q is the bf16 with bit pattern
@@ -651,14 +655,6 @@ inline size_t fold_smem_bytes(int64_t groups) {
          static_cast<size_t>(groups) * 16 * 4 /*activation sums*/ + 4096 /*output staging*/ + 1024 /*barriers*/;
 }
 
-#ifdef BSIR_FOLD_TL
-__device__ unsigned long long *g_fold_tl = nullptr;
-#define FW(var, call) ([&] { const long long t0_ = clock64(); const bool r_ = (call); (var) += clock64() - t0_; return r_; }())
-#define FTL(i, v) do { if (g_fold_tl && blockIdx.x == 0) g_fold_tl[i] = static_cast<unsigned long long>(v); } while (0)
-#else
-#define FW(var, call) (call)
-#define FTL(i, v) do { } while (0)
-#endif
 __global__ void __launch_bounds__(kFoldThreads, 1)
     w4a16_fold_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, W4Params p, int64_t m0, int *err) {
   extern __shared__ uint8_t smem_raw[];
@@ -674,9 +670,9 @@ __global__ void __launch_bounds__(kFoldThreads, 1)
   auto empty_p = [&](int s) { return bars + 8u * (kFoldPStages + s); };
   auto full_o = [&](int s) { return bars + 8u * (2 * kFoldPStages + s); };
   auto empty_o = [&](int s) { return bars + 8u * (2 * kFoldPStages + kFoldOStages + s); };
-  auto tfull = [&](int a) { return bars + 8u * (2 * kFoldPStages + 2 * kFoldOStages + a); };
-  auto tempty = [&](int a) { return bars + 8u * (2 * kFoldPStages + 2 * kFoldOStages + 2 + a); };
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(stg) + 4096 + 8 * (2 * kFoldPStages + 2 * kFoldOStages + 4));
+  auto tfull = [&](int a) { return bars + 8u * (2 * kFoldPStages + 2 * kFoldOStages + a); };                        // a = issuer * 2 + buffer
+  auto tempty = [&](int a) { return bars + 8u * (2 * kFoldPStages + 2 * kFoldOStages + 2 * kFoldIssuers + a); };
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(stg) + 4096 + 8 * (2 * kFoldPStages + 2 * kFoldOStages + 4 * kFoldIssuers));
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -689,19 +685,16 @@ __global__ void __launch_bounds__(kFoldThreads, 1)
     prefetch_tmap(&tmap_a);
     for (int s = 0; s < kFoldPStages; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), 4); }
     for (int s = 0; s < kFoldOStages; ++s) { mbar_init(full_o(s), 4); mbar_init(empty_o(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 4); }
+    for (int a = 0; a < 2 * kFoldIssuers; ++a) { mbar_init(tfull(a), 1); mbar_init(tempty(a), 4); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 32);
+  if (warp == 1) tmem_alloc(smem_u32(tmem_slot), 128);
   pdl_wait();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  long long wt0 = 0, wt1 = 0;
-  const long long tstart = clock64();
-  (void)wt0; (void)wt1; (void)tstart;
 
   if (warp == 0) {
     // ---------------- TMA producer
@@ -710,95 +703,104 @@ __global__ void __launch_bounds__(kFoldThreads, 1)
       uint32_t round = 0;
       bool ok = true;
       for (int s = 0; s < nstages; ++s) {
-        if (!FW(wt0, mbar_wait(empty_p(slot), (round & 1u) ^ 1u, abort_flag, err))) { ok = false; break; }
+        if (!mbar_wait(empty_p(slot), (round & 1u) ^ 1u, abort_flag, err)) { ok = false; break; }
         const uint32_t dst = p_base + slot * kFoldPStage;
         mbar_expect_tx(full_p(slot), kFoldPStage);
         tma_load_2d(dst, &tmap_w, n0, s * 8, full_p(slot));                               // [8 word rows x 128 columns]
         tma_load_2d(dst + 8 * kFoldCols * 4, &tmap_a, s * 64, static_cast<int>(m0), full_p(slot));   // [16 rows x 64 k]
         if (++slot == kFoldPStages) { slot = 0; ++round; }
       }
-      FTL(0, wt0); FTL(1, clock64() - tstart);
       if (!ok) {
         for (int q = 0; q < kFoldPStages; ++q)
           for (int i = 0; i < 200000; ++i)
             if (mbar_try_wait(full_p(q), 0) || mbar_try_wait(full_p(q), 1)) break;
       }
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer
+  } else if (warp <= kFoldIssuers + 4) {
+    // sums of the activations per (group, row), by the issuing and the folding warps together (they have nothing
+    // else to do yet): every load of a pair is issued before the first is used
+    {
+      const int t12 = (warp - 1) * 32 + lane;
+      for (int pr = t12; pr < groups * 16; pr += (kFoldIssuers + 4) * 32) {
+        const int g = pr >> 4, r = pr & 15;
+        float sum = 0.0f;
+        if (r < rows) {
+          const uint4 *src = reinterpret_cast<const uint4 *>(p.a + (m0 + r) * p.lda + static_cast<int64_t>(g) * p.group);
+          for (int i0 = 0; i0 < static_cast<int>(p.group / 8); i0 += 16) {
+            uint4 v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] = (i0 + i < static_cast<int>(p.group / 8)) ? __ldg(src + i0 + i) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) sum += __uint_as_float(w[j] << 16) + __uint_as_float(w[j] & 0xffff0000u);
+            }
+          }
+        }
+        asum[pr] = sum;
+      }
+      asm volatile("bar.sync 1, %0;" ::"n"((kFoldIssuers + 4) * 32) : "memory");
+    }
+    if (warp <= kFoldIssuers) {
+    // ---------------- MMA issuers
     if (lane == 0) {
+      const int issuer = warp - 1;
       // D = f32, A = B = bf16, both K-major, N = 16, M = 128
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(16 >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
-      int slot = 0;
-      uint32_t round = 0, acc_phase[2] = {0u, 0u};
       bool ok = true;
-      for (int g = 0; g < groups && ok; ++g) {
-        const int acc = g & 1;
-        if (!FW(wt1, mbar_wait(tempty(acc), acc_phase[acc] ^ 1u, abort_flag, err))) { ok = false; break; }
+      static_assert(kFoldIssuers == kFoldOStages, "an issuer per operand slot");
+      // spg is 1, 2 or 4: every stage of this issuer belongs to another group, its c-th stage (c = s / 4) goes to its
+      // accumulator c % 2, whose (c / 2)-th use this is
+      for (int s = issuer; s < nstages && ok; s += kFoldIssuers) {
+        const int c = s / kFoldIssuers, buf = c & 1;
+        const uint32_t use = static_cast<uint32_t>(c >> 1);
+        if (!mbar_wait(tempty(issuer * 2 + buf), (use & 1u) ^ 1u, abort_flag, err)) { ok = false; break; }
+        if (!mbar_wait(full_o(issuer), static_cast<uint32_t>(c) & 1u, abort_flag, err)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 16);
-        for (int s = 0; s < spg; ++s) {
-          if (!FW(wt0, mbar_wait(full_o(slot), round & 1u, abort_flag, err))) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t wt = o_base + slot * kFoldOStage, at = wt + kFoldCols * 128;
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((issuer * 2 + buf) * 16);
+        const uint32_t wt = o_base + issuer * kFoldOStage, at = wt + kFoldCols * 128;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk)
-            mma_bf16_ss(d_tmem, make_desc(wt + kk * 32, 16, 1024), make_desc(at + kk * 32, 16, 1024), idesc, (s > 0 || kk > 0) ? 1u : 0u);
-          tc_commit(empty_o(slot));
-          if (++slot == kFoldOStages) { slot = 0; ++round; }
-        }
-        if (!ok) break;
-        tc_commit(tfull(acc));
-        acc_phase[acc] ^= 1u;
+        for (int kk = 0; kk < 4; ++kk)
+          mma_bf16_ss(d_tmem, make_desc(wt + kk * 32, 16, 1024), make_desc(at + kk * 32, 16, 1024), idesc, kk > 0 ? 1u : 0u);
+        tc_commit(empty_o(issuer));
+        tc_commit(tfull(issuer * 2 + buf));
       }
-      FTL(2, wt0); FTL(3, wt1); FTL(4, clock64() - tstart);
     }
-  } else if (warp < 6) {
+    } else {
     // ---------------- group fold + output: warps 2..5, TMEM lane quadrant = warp % 4; lane = output column
-    const int quad = warp & 3, et = (warp - 2) * 32 + lane;
-    // sums of the activations per (group, row): each of the 128 threads takes pairs et, et + 128, ...
-    for (int pr = et; pr < groups * 16; pr += 128) {
-      const int g = pr >> 4, r = pr & 15;
-      float sum = 0.0f;
-      if (r < rows) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(p.a + (m0 + r) * p.lda + static_cast<int64_t>(g) * p.group);
-        for (int i = 0; i < static_cast<int>(p.group / 8); ++i) {
-          const uint4 v = __ldg(src + i);
-          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) sum += __uint_as_float(w[j] << 16) + __uint_as_float(w[j] & 0xffff0000u);
-        }
-      }
-      asum[pr] = sum;
-    }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    if (threadIdx.x == 64) FTL(5, clock64() - tstart);
+    const int quad = warp & 3;
     const int64_t col = static_cast<int64_t>(n0) + quad * 32 + lane;
     const bool col_ok = col < p.n;
     const int64_t cc = col_ok ? col : 0;
     float part[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) part[j] = 0.0f;
-    uint32_t acc_phase[2] = {0u, 0u};
     bool ok = true;
     float s_next = __uint_as_float(static_cast<uint32_t>(p.scales[cc]) << 16);
     uint32_t z_next = (p.zeros[cc >> 3] >> (4 * (cc & 7))) & 0xfu;
     for (int g = 0; g < groups && ok; ++g) {
-      const int acc = g & 1;
       const float sc = s_next, zc = static_cast<float>(static_cast<int>(z_next) - 8);
       if (g + 1 < groups) {
         s_next = __uint_as_float(static_cast<uint32_t>(p.scales[static_cast<int64_t>(g + 1) * p.n + cc]) << 16);
         z_next = (p.zeros[static_cast<int64_t>(g + 1) * (p.n >> 3) + (cc >> 3)] >> (4 * (cc & 7))) & 0xfu;
       }
-      if (!FW(wt0, mbar_wait(tfull(acc), acc_phase[acc], abort_flag, err))) { ok = false; break; }
-      tc_fence_after();
+      // the accumulators of this group's stages (stage s: issuer s % 4, its accumulator (s / 4) % 2), added in stage order
       uint32_t r[16];
-      tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * 16), r);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty(acc));
-      acc_phase[acc] ^= 1u;
+      for (int i = 0; i < spg && ok; ++i) {
+        const int st = g * spg + i, issuer = st & (kFoldIssuers - 1), c = st / kFoldIssuers, a2 = issuer * 2 + (c & 1);
+        if (!mbar_wait(tfull(a2), static_cast<uint32_t>(c >> 1) & 1u, abort_flag, err)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t q[16];
+        tmem_ld16(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(a2 * 16), q);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty(a2));
+#pragma unroll
+        for (int e = 0; e < 16; ++e) r[e] = i == 0 ? q[e] : __float_as_uint(__uint_as_float(r[e]) + __uint_as_float(q[e]));
+      }
+      if (!ok) break;
       const float4 *as4 = reinterpret_cast<const float4 *>(asum + g * 16);
 #pragma unroll
       for (int j4 = 0; j4 < 4; ++j4) {
@@ -809,7 +811,6 @@ __global__ void __launch_bounds__(kFoldThreads, 1)
         part[4 * j4 + 3] = fmaf(sc, fmaf(-zc, av.w, __uint_as_float(r[4 * j4 + 3])), part[4 * j4 + 3]);
       }
     }
-    if (threadIdx.x == 64) { FTL(6, wt0); FTL(7, clock64() - tstart); }
     if (ok) {
       uint32_t pk[8];
 #pragma unroll
@@ -837,12 +838,13 @@ __global__ void __launch_bounds__(kFoldThreads, 1)
           if (j < rows) store_out(p, (m0 + j) * p.ldo + col, static_cast<uint16_t>((j & 1) ? (pk[j >> 1] >> 16) : (pk[j >> 1] & 0xffffu)));
       }
     }
+    }
   } else {
     // ---------------- packed words -> bf16 operand tile; activations into the nibble-pair k order
     // Four teams of four warps; team t owns operand slot t and takes stages t, t + 4, ...: the teams work on four
     // different stages at once, so the latency of a stage's hand-over (barrier round trips, the proxy fence) is hidden
     // by the other three.  A thread converts the eight words of one column and one 16-byte piece of activations.
-    const int dw = warp - 6, team = dw >> 2, tw = dw & 3;
+    const int dw = warp - (1 + kFoldIssuers + 4), team = dw >> 2, tw = dw & 3;
     static_assert(kFoldOStages == 4 && kFoldDqWarps == 16 && kFoldPStages % 4 == 0, "one operand slot per team");
     uint8_t *ost = gen + team * kFoldOStage;
     const int c = tw * 32 + lane;                                  // column = row of the operand tile
@@ -850,13 +852,13 @@ __global__ void __launch_bounds__(kFoldThreads, 1)
     uint32_t pround = 0, oround = 0;
     bool ok = true;
     for (int s = team; s < nstages && ok; s += 4, ++oround) {
-      if (!FW(wt0, mbar_wait(full_p(pslot), pround & 1u, abort_flag, err))) { ok = false; break; }
+      if (!mbar_wait(full_p(pslot), pround & 1u, abort_flag, err)) { ok = false; break; }
       const uint8_t *pst = gen + kFoldOStages * kFoldOStage + pslot * kFoldPStage;
       uint32_t w[8];
 #pragma unroll
       for (int r = 0; r < 8; ++r) w[r] = reinterpret_cast<const uint32_t *>(pst)[r * kFoldCols + c];
       const uint4 av = *reinterpret_cast<const uint4 *>(pst + 8 * kFoldCols * 4 + c * 16);
-      if (!FW(wt1, mbar_wait(empty_o(team), (oround & 1u) ^ 1u, abort_flag, err))) { ok = false; break; }
+      if (!mbar_wait(empty_o(team), (oround & 1u) ^ 1u, abort_flag, err)) { ok = false; break; }
 #pragma unroll
       for (int r = 0; r < 8; ++r)
         *reinterpret_cast<uint4 *>(ost + c * 128 + ((r ^ (c & 7)) << 4)) =
@@ -870,14 +872,13 @@ __global__ void __launch_bounds__(kFoldThreads, 1)
       pslot += 4;
       if (pslot >= kFoldPStages) { pslot -= kFoldPStages; ++pround; }
     }
-    if (dw == 0 && lane == 0) { FTL(8, wt0); FTL(9, wt1); FTL(10, clock64() - tstart); }
   }
 
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 32);
+    tmem_dealloc(tmem_base, 128);
   }
 }
 
@@ -991,18 +992,17 @@ static int32_t matmul_w4a16_impl(int64_t m, int64_t n, int64_t k, int64_t group,
     }
     return check_launch("matmul_w4a16");
   }
-  // The folded-scale kernel (scale and zero point applied per group in the epilogue) serves every row block when
-  // its shape fits; BSIR_W4A16_PATH=m / t keep to the exact-rounding kernels, =f insists on this one.
-  const bool fold_ok = fast && device_info().cc_major >= 10 && group % 64 == 0 && k % 64 == 0 && k / group <= kFoldMaxGroups &&
+  // The folded-scale kernel (scale and zero point applied per group in the epilogue) runs on request only
+  // (BSIR_W4A16_PATH=f): it is correct and halves the dequantisation work, but with the weights as the MMA's A
+  // operand a 128-column tile needs K / 16 MMAs of M = 128, each of which holds the tensor core for about 128 cycles
+  // whatever its N -- 17 us for K = 4096 before anything else (measured 36-41 us with one, four and eight issuing
+  // threads).  The form that would pay has the weights as the B operand (N = 256 per MMA) and K split over all SMs.
+  const bool fold_ok = fast && device_info().cc_major >= 10 && (group == 64 || group == 128 || group == 256) && k % 64 == 0 && k / group <= kFoldMaxGroups &&
                        fold_smem_bytes(k / group) <= 226 * 1024 && n_peers <= 1;
-  if (fold_ok && !(force && (force[0] == 'm' || force[0] == 't'))) {
+  if (fold_ok && force && force[0] == 'f') {
     CUtensorMap fw, fa;
     if (make_weight_tmap(&fw, p.qw, n, k, 8) && make_act_tmap(&fa, p.a, m, k, lda)) {
       const size_t smem = fold_smem_bytes(k / group);
-#ifdef BSIR_FOLD_TL
-      { const char *e = std::getenv("BSIR_FOLD_TL_PTR"); unsigned long long *ptr = e ? reinterpret_cast<unsigned long long *>(std::strtoull(e, nullptr, 0)) : nullptr;
-        cudaMemcpyToSymbol(g_fold_tl, &ptr, sizeof(ptr)); }
-#endif
       cudaFuncSetAttribute(w4a16_fold_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
       for (int64_t m0 = 0; m0 < m; m0 += 16) {
         launch_pdl(w4a16_fold_kernel, dim3(static_cast<unsigned>(ceil_div(n, kFoldCols))), dim3(kFoldThreads), smem, st, fw, fa, p, m0,
