@@ -994,8 +994,8 @@ static int32_t matmul_w4a16_impl(int64_t m, int64_t n, int64_t k, int64_t group,
   }
   // The folded-scale kernel (scale and zero point applied per group in the epilogue) runs on request only
   // (BSIR_W4A16_PATH=f): it is correct and halves the dequantisation work, but with the weights as the MMA's A
-  // operand a 128-column tile needs K / 16 MMAs of M = 128, each of which holds the tensor core for about 128 cycles
-  // whatever its N -- 17 us for K = 4096 before anything else (measured 36-41 us with one, four and eight issuing
+  // operand a 128-column tile needs K / 16 MMAs, and an SM accepts one tcgen05.mma per 115-140 cycles whatever its
+  // shape -- 15-17 us for K = 4096 before anything else (measured 36-41 us with one, four and eight issuing
   // threads).  The form that would pay has the weights as the B operand (N = 256 per MMA) and K split over all SMs.
   const bool fold_ok = fast && device_info().cc_major >= 10 && (group == 64 || group == 128 || group == 256) && k % 64 == 0 && k / group <= kFoldMaxGroups &&
                        fold_smem_bytes(k / group) <= 226 * 1024 && n_peers <= 1;
