@@ -1245,8 +1245,9 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
     }
     if constexpr (KIND == KI8) {
       // few rows: operands swapped, deep ring of weight tiles (BSIR_W8A8_PATH=3 forces it for m <= 128, =1 avoids it)
-      // measured on B200 (k 4096, n 14336): 13.5-16 us against 19-20 us for m <= 24, slower from m = 32 on
-      const bool want_decode = classic_w8a8 && !a_mn && ((force && force[0] == '3') ? m <= 128 : (!force && m <= 24));
+      // measured on B200 (k 4096, n 14336), this kernel against the 128-row-tile one: m = 16 12.5 / 19.8 us, 32 13.0 / 14.5,
+      // 48 13.9 / 14.6, 64 14.7 / 14.6, 96 18.0 / 14.8
+      const bool want_decode = classic_w8a8 && !a_mn && ((force && force[0] == '3') ? m <= 128 : (!force && m <= 48));
       if (ok && want_decode) {
         const DecodeCfg dc = decode_cfg(m);
         CUtensorMap tw, tact;

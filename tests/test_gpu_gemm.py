@@ -35,7 +35,8 @@ def _w8a8_case(bsir, m, n, k, transpose_b, seed=0, out_dtype=torch.bfloat16):
 
 @pytest.mark.parametrize("transpose_b", [True, False])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 128), (128, 128, 512), (16, 256, 4096), (1, 128, 128), (200, 384, 640),
-                                   (130, 320, 208), (256, 512, 1024), (128, 1000, 256), (300, 136, 144)])
+                                   (130, 320, 208), (256, 512, 1024), (128, 1000, 256), (300, 136, 144), (40, 1000, 640),
+                                   (48, 14336, 512), (49, 384, 256)])
 def test_w8a8_small_shapes_exact(bsir, m, n, k, transpose_b):
     _w8a8_case(bsir, m, n, k, transpose_b, seed=m + n + k)
 
