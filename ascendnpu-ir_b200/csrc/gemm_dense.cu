@@ -76,6 +76,9 @@ struct GemmParams {
   unsigned long long *tl;
 #endif
 };
+// Built with -DBSIR_DEC_TIMELINE the decode kernel stamps %globaltimer and clock64() at the points marked TL(i) into
+// the buffer whose device address the environment variable BSIR_DEC_TL_PTR holds (32 words of 8 bytes per CTA):
+// where a launch's microseconds go (first stage landed, last MMA committed, epilogue done) was read off such stamps.
 #ifdef BSIR_DEC_TIMELINE
 __device__ __forceinline__ unsigned long long gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 #define TL(i) do { if (p.tl) { p.tl[blockIdx.x * 32 + (i)] = gtime(); p.tl[blockIdx.x * 32 + 16 + (i)] = clock64(); } } while (0)
