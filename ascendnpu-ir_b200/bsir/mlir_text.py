@@ -11,7 +11,8 @@ Covered (attribute spellings as in the reference):
   hfusion.compare {compare_fn = #hfusion.compare_fn<..>}, hfusion.select, hfusion.isnan
   hfusion.reduce_with_index {tie_break_left} <max|min>
   linalg.fill, linalg.broadcast dimensions = [..], linalg.reduce {arith.<combiner>} dimensions = [k] (short form and a
-  region with one combiner op), linalg.matmul (i8 x i8 -> i32), linalg.copy
+  region with one combiner op), linalg.matmul / matmul_transpose_a / matmul_transpose_b / batch_matmul (i8 -> i32, f16, bf16),
+  linalg.copy
   hivm.hir.load (pad_mode / pad_value / left_padding_num / right_padding_num), hivm.hir.store (atomic = <kind>),
   hivm.hir.copy, hivm.hir.vadd / vsub / vmul / vdiv / vmax / vmin, hivm.hir.vcast, hivm.hir.vreduce <kind>,
   hivm.hir.vcumsum / vcumprod / vcummax / vcummin (and hfusion.cumsum ...) cum_dims = [k] reverse = <bool>,
@@ -209,7 +210,7 @@ class Function:
     # ------------------------------------------------------------------ execution
     def __call__(self, *tensors):
         import torch
-        from . import (cast, compare, copy, cumulative, elemwise_binary, elemwise_unary, gather, load, matmul_w8a8, reduce,
+        from . import (cast, compare, copy, cumulative, elemwise_binary, elemwise_unary, gather, load, matmul, reduce,
                        reduce_with_index, select, sort, store)
         if len(tensors) != len(self.args):
             raise MlirTextError(f"@{self.name} takes {len(self.args)} arguments, got {len(tensors)}")
@@ -229,6 +230,7 @@ class Function:
 
         from . import fusion
         arg_ptrs = {t.data_ptr() for t in tensors if isinstance(t, torch.Tensor)}
+        uninitialised = set()                                  # results of tensor.empty / memref.alloc nothing has written yet
         requests: List[tuple] = []                             # (Lazy, destination) pairs waiting to run together
         consumed = set()                                       # deferred values folded into another expression
 
@@ -427,6 +429,7 @@ class Function:
             elif name in ("tensor.empty", "memref.alloc"):
                 st = ShapedType(op.text.split(":", 1)[1])
                 define(op, [torch.empty(st.shape, dtype=tdtype(st.elem), device=dev)])
+                uninitialised.add(op.results[0])
             elif name == "tensor.dim":
                 t_name, i_name = [n.strip() for n in _split_top(op.text.split(":")[0])]
                 src = env.get(t_name)
@@ -554,12 +557,25 @@ class Function:
                 kind = re.search(r"<(max|min)>", op.text).group(1)
                 v, i = reduce_with_index(kind, val(ins[0]), tie_break_left=bool(op.attr("tie_break_left", True)))
                 define(op, [write_out(val(outs[0]), v), write_out(val(outs[1]), i)])
-            elif name == "linalg.matmul":
+            elif name in ("linalg.matmul", "linalg.matmul_transpose_a", "linalg.matmul_transpose_b", "linalg.batch_matmul"):
+                # C = C + A.B (the op accumulates onto its init; an init that is a bare tensor.empty counts as zero).
+                # i8 x i8 -> i32 exactly; f16 / bf16 products are accumulated in f32 on the tensor core and rounded
+                # once to the result type (the device rule: bishengir/lib/Dialect/HFusion/Transforms/Normalize.cpp:8224-8257)
                 a, b, c = val(ins[0]), val(ins[1]), val(outs[0])
-                if a.dtype != torch.int8 or c.dtype != torch.int32:
-                    raise MlirTextError("linalg.matmul: i8 x i8 -> i32 is supported")
-                _, acc = matmul_w8a8(a, b, want_acc=True)
-                define(op, [write_out(c, acc)])
+                ta, tb = name.endswith("transpose_a"), name.endswith("transpose_b")
+                if a.dtype != b.dtype or a.dtype not in (torch.int8, torch.float16, torch.bfloat16):
+                    raise MlirTextError(f"{name}: operands {a.dtype} x {b.dtype} (i8, f16 or bf16 pairs are supported)")
+                acc_t = torch.int32 if a.dtype == torch.int8 else torch.float32
+                if c.dtype not in (acc_t, a.dtype) or (a.dtype == torch.int8 and c.dtype != torch.int32):
+                    raise MlirTextError(f"{name}: result type {c.dtype} for {a.dtype} operands")
+                fresh = outs[0] in uninitialised
+                prod = matmul(a, b, transpose_a=ta, transpose_b=tb, out_dtype=(c.dtype if fresh else acc_t))
+                if fresh:
+                    define(op, [write_out(c, prod)])
+                else:
+                    init = c if c.dtype == acc_t else cast(c, acc_t)
+                    total = elemwise_binary("add", prod, init)
+                    define(op, [write_out(c, total if c.dtype == acc_t else cast(total, c.dtype))])
             else:
                 raise MlirTextError(f"op {name} is not supported by this front end")
         return None

@@ -417,3 +417,46 @@ def test_cumulative_ops_in_both_spellings(bsir):
     fns["sort"](s, sv, si)
     want = torch.sort(s, dim=1, descending=True, stable=True)
     assert torch.equal(sv, want.values) and torch.equal(si.long(), want.indices)
+
+
+MATMUL_IR = """
+func.func @single_cube(%a: tensor<48x256xf16>, %w: tensor<384x256xf16>, %c: tensor<48x384xf16> {hacc.arg_type = #hacc.arg_type<output>})
+    -> tensor<48x384xf16> attributes {hacc.entry, hfusion.fusion_kind = #hfusion.fusion_kind<SINGLE_CUBE>} {
+  %0 = linalg.matmul_transpose_b ins(%a, %w : tensor<48x256xf16>, tensor<384x256xf16>) outs(%c : tensor<48x384xf16>) -> tensor<48x384xf16>
+  return %0 : tensor<48x384xf16>
+}
+func.func @dot_int8(%a: tensor<32x128xi8>, %b: tensor<128x256xi8>) -> tensor<32x256xi32> {
+  %e = tensor.empty() : tensor<32x256xi32>
+  %0 = linalg.matmul ins(%a, %b : tensor<32x128xi8>, tensor<128x256xi8>) outs(%e : tensor<32x256xi32>) -> tensor<32x256xi32>
+  %1 = linalg.matmul ins(%a, %b : tensor<32x128xi8>, tensor<128x256xi8>) outs(%0 : tensor<32x256xi32>) -> tensor<32x256xi32>
+  return %1 : tensor<32x256xi32>
+}
+func.func @batched(%a: tensor<3x16x64xbf16>, %b: tensor<3x64x128xbf16>) -> tensor<3x16x128xf32> {
+  %e = tensor.empty() : tensor<3x16x128xf32>
+  %0 = linalg.batch_matmul ins(%a, %b : tensor<3x16x64xbf16>, tensor<3x64x128xbf16>) outs(%e : tensor<3x16x128xf32>) -> tensor<3x16x128xf32>
+  return %0 : tensor<3x16x128xf32>
+}
+"""
+
+
+@pytest.mark.gpu
+def test_matmul_forms_accumulate_onto_their_init(bsir):
+    """linalg.matmul and its transposed / batched forms run on the tensor core; the op adds to its init, a bare
+    tensor.empty counting as zero (the SINGLE_CUBE function of the reference's compile tests has this shape)."""
+    import torch
+    from bsir import mlir_text
+    fns = mlir_text.parse(MATMUL_IR)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = torch.randn(48, 256, generator=g, device="cuda").half()
+    w = torch.randn(384, 256, generator=g, device="cuda").half()
+    c = torch.randn(48, 384, generator=g, device="cuda").half()
+    want = (c.float() + a.float() @ w.float().t()).half()
+    got = fns["single_cube"](a, w, c.clone())
+    assert torch.allclose(got.float(), want.float(), rtol=2e-3, atol=2e-2)
+    ai = torch.randint(-127, 128, (32, 128), generator=g, device="cuda", dtype=torch.int8)
+    bi = torch.randint(-127, 128, (128, 256), generator=g, device="cuda", dtype=torch.int8)
+    prod = (ai.cpu().int() @ bi.cpu().int()).cuda()
+    assert torch.equal(fns["dot_int8"](ai, bi), 2 * prod)             # the second matmul accumulates onto the first
+    ab = torch.randn(3, 16, 64, generator=g, device="cuda").bfloat16()
+    bb = torch.randn(3, 64, 128, generator=g, device="cuda").bfloat16()
+    assert torch.allclose(fns["batched"](ab, bb), torch.bmm(ab.float(), bb.float()), rtol=1e-3, atol=1e-2)
