@@ -18,7 +18,8 @@ Covered (attribute spellings as in the reference):
   hivm.hir.vcumsum / vcumprod / vcummax / vcummin (and hfusion.cumsum ...) cum_dims = [k] reverse = <bool>,
   hivm.hir.vgather ins(..) indices(..) outs(..) gather_axis = k, hivm.hir.vsort ins(..) outs(%v, %i) descending = <bool>
   tensor.empty, tensor.dim, tensor.collapse_shape / expand_shape / reshape, tensor.extract_slice (static), linalg.transpose, memref.alloc, arith.constant (scalars, splat `dense<..>`), arith.{addf,subf,mulf,divf,addi,subi,muli},
-  arith.{index_cast,index_castui,uitofp,sitofp,extf,truncf}, return
+  arith.{index_cast,index_castui,uitofp,sitofp,extf,truncf}, arith.{divsi,divui,remsi,remui,ceildivsi,floordivsi,maxsi,minsi,andi,ori,xori,cmpi,select}
+  on scalars, tensor.from_elements, tensor.concat, return
 Scalar arithmetic is done in the scalar's own type (f32 ops round to f32).  Anything else raises MlirTextError
 with the op's name, so an unsupported file fails loudly instead of computing something different.
 
@@ -55,10 +56,10 @@ class ShapedType:
         if not m:
             raise MlirTextError(f"not a tensor/memref type: {text}")
         inner = m.group(2).split(",")[0].strip()          # drops the memory space of a memref
-        parts = inner.split("x")
-        self.elem = parts[-1]
+        m2 = re.match(r"((?:(?:\d+|\?)x)*)(.*)$", inner)        # sizes, then the element type ("index" has an x of its own)
+        self.elem = m2.group(2)
         self.shape = []
-        for p in parts[:-1]:
+        for p in m2.group(1).split("x")[:-1]:
             if p == "?":
                 raise MlirTextError("dynamic shapes are not supported by this front end")
             self.shape.append(int(p))
@@ -421,6 +422,50 @@ class Function:
                     define(op, [Scalar(f(np.float32(a.value), np.float32(b.value)), ty)])
                 else:
                     define(op, [Scalar(f(a.value, b.value), ty)])
+            elif name in ("arith.divsi", "arith.divui", "arith.remsi", "arith.remui", "arith.ceildivsi", "arith.floordivsi", "arith.maxsi",
+                          "arith.minsi", "arith.andi", "arith.ori", "arith.xori"):
+                a, b = [val(n.strip()) for n in _split_top(op.text.split(":")[0])]
+                ty = op.text.rsplit(":", 1)[1].strip()
+                x, y = int(a.value), int(b.value)
+                if name in ("arith.divsi", "arith.divui", "arith.remsi", "arith.remui", "arith.ceildivsi", "arith.floordivsi") and y == 0:
+                    raise MlirTextError(f"{name}: division by zero")
+                trunc_div = lambda p, q: abs(p) // abs(q) * (1 if (p >= 0) == (q >= 0) else -1)   # C division: toward zero
+                r = {"arith.divsi": lambda: trunc_div(x, y), "arith.divui": lambda: x // y, "arith.remsi": lambda: x - trunc_div(x, y) * y,
+                     "arith.remui": lambda: x % y, "arith.ceildivsi": lambda: -((-x) // y), "arith.floordivsi": lambda: x // y,
+                     "arith.maxsi": lambda: max(x, y), "arith.minsi": lambda: min(x, y), "arith.andi": lambda: x & y,
+                     "arith.ori": lambda: x | y, "arith.xori": lambda: x ^ y}[name]()
+                define(op, [Scalar(r, ty)])
+            elif name == "arith.cmpi":
+                # `%p = arith.cmpi slt, %a, %b : index`
+                parts = [n.strip() for n in _split_top(op.text.split(":")[0])]
+                a, b = int(val(parts[1]).value), int(val(parts[2]).value)
+                pred = parts[0]
+                if pred in ("ult", "ule", "ugt", "uge") and (a < 0 or b < 0):
+                    raise MlirTextError("arith.cmpi: unsigned predicate on a negative scalar")
+                r = {"eq": a == b, "ne": a != b, "slt": a < b, "sle": a <= b, "sgt": a > b, "sge": a >= b,
+                     "ult": a < b, "ule": a <= b, "ugt": a > b, "uge": a >= b}[pred]
+                define(op, [Scalar(1 if r else 0, "i1")])
+            elif name == "arith.select" and isinstance(env.get(_split_top(op.text.split(":")[0])[0].strip()), Scalar):
+                c, a, b = [val(n.strip()) for n in _split_top(op.text.split(":")[0])]
+                define(op, [a if int(c.value) else b])
+            elif name == "tensor.from_elements":
+                # `%t = tensor.from_elements %a, %b : tensor<2xindex>`: a small tensor made of scalars
+                st = ShapedType(op.text.rsplit(":", 1)[1])
+                vals = [val(n.strip()).value for n in _split_top(op.text.rsplit(":", 1)[0]) if n.strip()]
+                define(op, [torch.tensor(vals, dtype=tdtype(st.elem), device=dev).reshape(st.shape)])
+            elif name == "tensor.concat":
+                # `%r = tensor.concat dim(1) %a, %b : (tensor<4x8xf32>, tensor<4x8xf32>) -> tensor<4x16xf32>`: strided copies
+                dim = int(re.search(r"dim\((\d+)\)", op.text).group(1))
+                srcs = [val(n) for n in re.findall(r"%[\w.]+", op.text.split(":")[0])]
+                st = ShapedType(op.text.rsplit("->", 1)[1])
+                res = torch.empty(st.shape, dtype=tdtype(st.elem), device=dev)
+                off = 0
+                for t in srcs:
+                    copy(t, out=res.narrow(dim, off, t.shape[dim]))
+                    off += t.shape[dim]
+                if off != st.shape[dim]:
+                    raise MlirTextError("tensor.concat: the operands do not fill the result")
+                define(op, [res])
             elif name in ("arith.index_cast", "arith.index_castui", "arith.uitofp", "arith.sitofp", "arith.extf", "arith.truncf",
                           "arith.extsi", "arith.extui", "arith.trunci"):
                 src = val(op.text.split(":")[0].strip())

@@ -460,3 +460,29 @@ def test_matmul_forms_accumulate_onto_their_init(bsir):
     ab = torch.randn(3, 16, 64, generator=g, device="cuda").bfloat16()
     bb = torch.randn(3, 64, 128, generator=g, device="cuda").bfloat16()
     assert torch.allclose(fns["batched"](ab, bb), torch.bmm(ab.float(), bb.float()), rtol=1e-3, atol=1e-2)
+
+
+SCALAR_IR = """
+func.func @pieces(%a: tensor<4x8xf32>, %b: tensor<4x24xf32>) -> (tensor<4x32xf32>, tensor<3xindex>) {
+  %c7 = arith.constant 7 : index
+  %c2 = arith.constant 2 : index
+  %cm7 = arith.constant -7 : index
+  %q = arith.divui %c7, %c2 : index
+  %r = arith.remsi %cm7, %c2 : index
+  %p = arith.cmpi slt, %r, %q : index
+  %s = arith.select %p, %q, %r : index
+  %t = tensor.from_elements %q, %r, %s : tensor<3xindex>
+  %cat = tensor.concat dim(1) %a, %b : (tensor<4x8xf32>, tensor<4x24xf32>) -> tensor<4x32xf32>
+  return %cat, %t : tensor<4x32xf32>, tensor<3xindex>
+}
+"""
+
+
+@pytest.mark.gpu
+def test_scalar_arithmetic_from_elements_and_concat(bsir):
+    import torch
+    from bsir import mlir_text
+    a, b = torch.randn(4, 8, device="cuda"), torch.randn(4, 24, device="cuda")
+    cat, t = mlir_text.parse(SCALAR_IR)["pieces"](a, b)
+    assert torch.equal(cat, torch.cat([a, b], dim=1))
+    assert t.tolist() == [3, -1, 3]                                   # 7 / 2, -7 rem 2 (sign of the dividend), select
