@@ -231,7 +231,7 @@ class Function:
 
         from . import fusion
         arg_ptrs = {t.data_ptr() for t in tensors if isinstance(t, torch.Tensor)}
-        uninitialised = set()                                  # results of tensor.empty / memref.alloc nothing has written yet
+        uninitialised = set()                                  # results of tensor.empty: values without contents
         requests: List[tuple] = []                             # (Lazy, destination) pairs waiting to run together
         consumed = set()                                       # deferred values folded into another expression
 
@@ -474,7 +474,8 @@ class Function:
             elif name in ("tensor.empty", "memref.alloc"):
                 st = ShapedType(op.text.split(":", 1)[1])
                 define(op, [torch.empty(st.shape, dtype=tdtype(st.elem), device=dev)])
-                uninitialised.add(op.results[0])
+                if name == "tensor.empty":                     # a tensor value is never written again; a memref may be
+                    uninitialised.add(op.results[0])
             elif name == "tensor.dim":
                 t_name, i_name = [n.strip() for n in _split_top(op.text.split(":")[0])]
                 src = env.get(t_name)
