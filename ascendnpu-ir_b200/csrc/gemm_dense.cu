@@ -904,8 +904,14 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {   // arrives on `
                : "memory");
 }
 
+// Int8 products have two issuing threads in the leader CTA (warps 1 and 6): the thread that issues a tcgen05.mma is
+// held about 140 cycles by each, four per k block are 560 cycles, and the arithmetic of the block is 512.  Thread 0
+// takes k steps 0 and 1 of every block, thread 1 steps 2 and 3, into the same accumulator: int32 sums do not depend
+// on the order.  The second thread's first MMA of a tile waits until the first thread has issued the one that
+// overwrites the accumulator.  Float products keep one issuer: their sums would depend on the order of arrival.
+constexpr int kPairThreads = kThreads + 32;
 template <int KIND, bool A_MN, bool B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
     gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ CUtensorMap tmap_out, GemmParams p) {
   constexpr int kEs = kEsize<KIND>;
@@ -921,6 +927,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * kPairStages + 2 + a); };
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen_base + kPairStages * kPairStage + 8 * (2 * kPairStages + 4));
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile uint32_t *tiles_started = tmem_slot + 2;     // tiles whose overwriting MMA the first issuer has issued
+  constexpr int kIssuers = KIND == KI8 ? 2 : 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_rank();
@@ -929,9 +937,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
   const int total_tiles = m_tiles2 * p.n_tiles;         // p.n_tiles counts 256-wide tiles
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kPairStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 8); }
+    for (int s = 0; s < kPairStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), kIssuers); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), kIssuers); mbar_init(tempty_bar(a), 8); }
     *abort_flag = 0;
+    *tiles_started = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
@@ -977,16 +986,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
         }
       }
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer: leader CTA only
-    if (lane == 0 && rank == 0) {
+  } else if (warp == 1 || warp == 6) {
+    // ---------------- MMA issuers: leader CTA only
+    const int issuer = warp == 1 ? 0 : 1;
+    if (lane == 0 && rank == 0 && issuer < kIssuers) {
       const uint32_t idesc = make_idesc<KIND>(A_MN, B_MN, kPairBN, 256);
+      constexpr int kSteps = kBK / kUmmaK / kIssuers;       // k steps of a block per issuer
       int stage = 0;
-      uint32_t phase = 0;
+      uint32_t phase = 0, tile_seq = 0;
       int acc = 0;
       uint32_t acc_phase[2] = {0u, 0u};
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += npairs) {
+      for (int tile = pair; tile < total_tiles && ok; tile += npairs, ++tile_seq) {
         if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kPairBN);
@@ -995,9 +1006,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
           tc_fence_after();
           const uint32_t sa = base + stage * kPairStage;
           const uint32_t sb = sa + kPairStageA;
+          if (issuer == 1 && kb == 0) {        // not before the MMA that overwrites the accumulator is on its way
+            const long long t0 = clock64();
+            while (*tiles_started <= tile_seq) {
+              if (*abort_flag || clock64() - t0 > 4000000000LL) {
+                *abort_flag = 1;
+                if (p.err) atomicOr(p.err, static_cast<int>(kErrGemmWait));
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+          }
 #pragma unroll
-          for (int kk = 0; kk < kBK / kUmmaK; ++kk)
+          for (int kk = issuer * kSteps; kk < (issuer + 1) * kSteps; ++kk) {
             mma_ss_pair<KIND>(d_tmem, operand_desc<KIND>(sa, kk, A_MN), operand_desc<KIND>(sb, kk, B_MN), idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            if (kIssuers > 1 && issuer == 0 && kb == 0 && kk == 0) {
+              __threadfence_block();
+              *tiles_started = tile_seq + 1u;
+            }
+          }
           tc_commit_pair(empty_bar(stage));
           if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
         }
@@ -1179,7 +1207,7 @@ int32_t launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensor
   const int total = static_cast<int>(ceil_div(p.m, 256)) * p.n_tiles;
   if (grid > 2 * total) grid = 2 * total;
   cudaFuncSetAttribute(gemm_pair_kernel<KIND, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmem);
-  gemm_pair_kernel<KIND, A_MN, B_MN><<<grid, kThreads, kPairSmem, st>>>(ta, tb, tout, p);
+  gemm_pair_kernel<KIND, A_MN, B_MN><<<grid, kPairThreads, kPairSmem, st>>>(ta, tb, tout, p);
   count_launch();
   return check_launch("matmul (CTA pairs)");
 }
