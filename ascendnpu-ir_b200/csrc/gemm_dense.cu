@@ -341,7 +341,7 @@ struct TileCfg {
 
 // ------------------------------------------------------------------ the kernel
 template <int KIND, int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads + 32, 1)
     gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                    const __grid_constant__ CUtensorMap tmap_out, GemmParams p) {
   using Cfg = TileCfg<BN>;
@@ -359,15 +359,19 @@ __global__ void __launch_bounds__(kThreads, 1)
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * Cfg::kStages + 2 + a); };
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen_base + Cfg::kStages * Cfg::kStage + 8 * (2 * Cfg::kStages + 4));
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  volatile uint32_t *tiles_started = tmem_slot + 2;     // tiles whose overwriting MMA the first issuer has issued
+  // int8 products: two issuing threads (warps 1 and 6), as in the CTA-pair kernel below
+  constexpr int kIssuers = KIND == KI8 ? 2 : 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = p.m_tiles * p.n_tiles;
 
   pdl_launch_dependents();   // the set-up below overlaps the tail of the kernel ahead (see launch_pdl)
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    for (int s = 0; s < Cfg::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), kIssuers); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), kIssuers); mbar_init(tempty_bar(a), 4); }
     *abort_flag = 0;
+    *tiles_started = 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     prefetch_tmap(&tmap_a);
     prefetch_tmap(&tmap_b);
@@ -421,16 +425,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer
-    if (lane == 0) {
+  } else if (warp == 1 || warp == 6) {
+    // ---------------- MMA issuers
+    const int issuer = warp == 1 ? 0 : 1;
+    if (lane == 0 && issuer < kIssuers) {
       const uint32_t idesc = make_idesc<KIND>(A_MN, B_MN, BN, kBM);
+      constexpr int kSteps = kBK / kUmmaK / kIssuers;       // k steps of a block per issuer
       int stage = 0;
-      uint32_t phase = 0;
+      uint32_t phase = 0, tile_seq = 0;
       int acc = 0;
       uint32_t acc_phase[2] = {0u, 0u};
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_seq) {
         if (!mbar_wait(tempty_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
@@ -439,9 +445,26 @@ __global__ void __launch_bounds__(kThreads, 1)
           tc_fence_after();
           const uint32_t sa = base + stage * Cfg::kStage;
           const uint32_t sb = sa + Cfg::kStageA;
+          if (issuer == 1 && kb == 0) {        // not before the MMA that overwrites the accumulator is on its way
+            const long long t0 = clock64();
+            while (*tiles_started <= tile_seq) {
+              if (*abort_flag || clock64() - t0 > 4000000000LL) {
+                *abort_flag = 1;
+                if (p.err) atomicOr(p.err, static_cast<int>(kErrGemmWait));
+                ok = false;
+                break;
+              }
+            }
+            if (!ok) break;
+          }
 #pragma unroll
-          for (int kk = 0; kk < kBK / kUmmaK; ++kk)
+          for (int kk = issuer * kSteps; kk < (issuer + 1) * kSteps; ++kk) {
             mma_ss<KIND>(d_tmem, operand_desc<KIND>(sa, kk, A_MN), operand_desc<KIND>(sb, kk, B_MN), idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+            if (kIssuers > 1 && issuer == 0 && kb == 0 && kk == 0) {
+              __threadfence_block();
+              *tiles_started = tile_seq + 1u;
+            }
+          }
           tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
         }
@@ -1187,7 +1210,7 @@ int32_t launch_tc(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMa
   const int total = p.m_tiles * p.n_tiles;
   int grid = device_info().sm_count > 0 ? device_info().sm_count : 148;
   if (grid > total) grid = total;
-  launch_pdl(gemm_tc_kernel<KIND, BN, A_MN, B_MN>, dim3(grid), dim3(kThreads), Cfg::kSmemBytes, st, ta, tb, tout, p);
+  launch_pdl(gemm_tc_kernel<KIND, BN, A_MN, B_MN>, dim3(grid), dim3(kThreads + 32), Cfg::kSmemBytes, st, ta, tb, tout, p);
   count_launch();
   return check_launch("matmul");
 }
