@@ -14,7 +14,9 @@ Covered (attribute spellings as in the reference):
   region with one combiner op), linalg.matmul / matmul_transpose_a / matmul_transpose_b / batch_matmul (i8 -> i32, f16, bf16),
   linalg.copy
   hivm.hir.load (pad_mode / pad_value / left_padding_num / right_padding_num), hivm.hir.store (atomic = <kind>),
-  hivm.hir.copy, hivm.hir.vadd / vsub / vmul / vdiv / vmax / vmin, hivm.hir.vcast, hivm.hir.vreduce <kind>,
+  hivm.hir.copy, hivm.hir.vadd / vsub / vmul / vdiv / vmax / vmin / vand / vor / vxor / vpow / vmod / vmodui / vshl / vshr,
+  hivm.hir.vexp / vln / vabs / vsqrt / vrsqrt / vrelu / vnot / vrec / vtanh / verf / vsin / vcos, vcmp [compare_mode = <..>], vsel,
+  vbrc, vtranspose permutation = [..], varange offset[..] strides[..], vinterleave, vdeinterleave, hivm.hir.vcast, hivm.hir.vreduce <kind>,
   hivm.hir.vcumsum / vcumprod / vcummax / vcummin (and hfusion.cumsum ...) cum_dims = [k] reverse = <bool>,
   hivm.hir.vgather ins(..) indices(..) outs(..) gather_axis = k, hivm.hir.vsort ins(..) outs(%v, %i) descending = <bool>
   tensor.empty, tensor.dim, tensor.collapse_shape / expand_shape / reshape, tensor.extract_slice (static), linalg.transpose, memref.alloc, arith.constant (scalars, splat `dense<..>`), arith.{addf,subf,mulf,divf,addi,subi,muli},
@@ -46,7 +48,12 @@ _TORCH_NAMES = {"f32": "float32", "f16": "float16", "bf16": "bfloat16", "i8": "i
 _REDUCE_COMBINERS = {"arith.addf": "sum", "arith.addi": "sum", "arith.mulf": "prod", "arith.muli": "prod",
                      "arith.maximumf": "max", "arith.maxsi": "max", "arith.minimumf": "min", "arith.minsi": "min",
                      "arith.ori": "ori", "arith.andi": "andi", "arith.xori": "xori"}
-_HIVM_BINARY = {"vadd": "add", "vsub": "sub", "vmul": "mul", "vdiv": "div", "vmax": "maxf", "vmin": "minf"}
+_HIVM_BINARY = {"vadd": "add", "vsub": "sub", "vmul": "mul", "vdiv": "div", "vmax": "maxf", "vmin": "minf", "vand": "vand",
+                "vor": "vor", "vxor": "vxor", "vpow": "powf", "vmod": "mod", "vmodui": "modui", "vshl": "shli", "vshr": "shrsi"}
+_HIVM_INT_BINARY = {"vmax": "max_signed", "vmin": "min_signed"}     # vmax / vmin of integers
+_HIVM_UNARY = {"vexp": "exp", "vln": "log", "vabs": "abs", "vsqrt": "sqrt", "vrsqrt": "rsqrt", "vrelu": "relu", "vnot": "vnot",
+               "vrec": "rec", "vtanh": "tanh", "verf": "erf", "vsin": "sin", "vcos": "cos"}
+_HIVM_COMPARE = {"eq": "veq", "ne": "vne", "le": "vle", "lt": "vlt", "ge": "vge", "gt": "vgt"}
 _LINALG_UNARY = {"exp", "log", "abs", "ceil", "floor", "negf", "reciprocal", "round", "sqrt", "rsqrt", "square", "tanh", "erf"}
 
 
@@ -211,8 +218,8 @@ class Function:
     # ------------------------------------------------------------------ execution
     def __call__(self, *tensors):
         import torch
-        from . import (cast, compare, copy, cumulative, elemwise_binary, elemwise_unary, gather, load, matmul, reduce,
-                       reduce_with_index, select, sort, store)
+        from . import (arange, cast, compare, copy, cumulative, deinterleave, elemwise_binary, elemwise_unary, gather, interleave,
+                       load, matmul, reduce, reduce_with_index, select, sort, store, transpose)
         if len(tensors) != len(self.args):
             raise MlirTextError(f"@{self.name} takes {len(self.args)} arguments, got {len(tensors)}")
         env: Dict[str, object] = {}
@@ -514,7 +521,87 @@ class Function:
                 fun = op.attr("fun") or "add"
                 define(op, [elemwise_binary(fun, operand(ins[0]), operand(ins[1]), out=val(outs[0]))])
             elif name.startswith("hivm.hir.") and name[9:] in _HIVM_BINARY:
-                define(op, [elemwise_binary(_HIVM_BINARY[name[9:]], operand(ins[0]), operand(ins[1]), out=val(outs[0]))])
+                dst = val(outs[0])
+                fun = _HIVM_BINARY[name[9:]]
+                if not dst.dtype.is_floating_point and name[9:] in _HIVM_INT_BINARY:
+                    fun = _HIVM_INT_BINARY[name[9:]]
+                define(op, [elemwise_binary(fun, operand(ins[0]), operand(ins[1]), out=dst)])
+            elif name.startswith("hivm.hir.") and name[9:] in _HIVM_UNARY:
+                x, dst = val(ins[0]), val(outs[0])
+                fun = _HIVM_UNARY[name[9:]]
+                if fun == "abs" and not x.dtype.is_floating_point:
+                    fun = "absi"
+                define(op, [elemwise_unary(fun, x, out=dst)])
+            elif name == "hivm.hir.vcmp":
+                # `hivm.hir.vcmp ins(%a, %b : T, T) outs(%o : Ti1) [compare_mode = <lt>]` (eq when absent)
+                m = re.search(r"compare_mode\s*=\s*(?:#hivm\.compare_mode)?<(\w+)>", op.text)
+                mode = m.group(1) if m else "eq"
+                if mode not in _HIVM_COMPARE:
+                    raise MlirTextError(f"hivm.hir.vcmp: compare_mode {mode}")
+                define(op, [write_out(val(outs[0]), compare(_HIVM_COMPARE[mode], operand(ins[0]), operand(ins[1])))])
+            elif name == "hivm.hir.vsel":
+                cond = operand(ins[0])
+                if not isinstance(cond, torch.Tensor):                 # a scalar i1 picks one operand whole
+                    dst = val(outs[0])
+                    pick = operand(ins[1]) if int(cond) else operand(ins[2])
+                    define(op, [copy(pick, out=dst) if isinstance(pick, torch.Tensor) else
+                                elemwise_binary("add", torch.zeros_like(dst), pick, out=dst)])
+                else:
+                    define(op, [write_out(val(outs[0]), select(cond, operand(ins[1]), operand(ins[2])))])
+            elif name == "hivm.hir.vbrc":
+                # a scalar, or a tensor with unit axes listed in broadcast_dims, spread over the destination
+                dst = val(outs[0])
+                src = operand(ins[0])
+                if isinstance(src, torch.Tensor):
+                    if src.dim() != dst.dim():
+                        raise MlirTextError("hivm.hir.vbrc: source and destination ranks differ")
+                    define(op, [copy(src.expand(dst.shape), out=dst)])
+                elif dst.dtype == torch.bool:
+                    define(op, [dst.fill_(bool(src))])
+                else:
+                    define(op, [elemwise_binary("add", torch.zeros_like(dst), src, out=dst)])
+            elif name == "hivm.hir.vtranspose":
+                src, dst = val(ins[0]), val(outs[0])
+                perm = op.int_list("permutation")
+                if perm is None or sorted(perm) != list(range(src.dim())):
+                    raise MlirTextError("hivm.hir.vtranspose: permutation = [..] expected")
+                if perm[:-2] == list(range(src.dim() - 2)) and perm[-2:] == [src.dim() - 1, src.dim() - 2]:
+                    lead = int(np.prod(src.shape[:-2])) if src.dim() > 2 else 1     # the last two axes swapped: tiled kernel
+                    transpose(src.reshape(lead, src.shape[-2], src.shape[-1]), out=dst.view(lead, dst.shape[-2], dst.shape[-1]))
+                    define(op, [dst])
+                elif src.dim() <= 3:
+                    define(op, [copy(src.permute(perm), out=dst)])
+                else:
+                    raise MlirTextError("hivm.hir.vtranspose: beyond rank 3 only the last two axes may be swapped")
+            elif name == "hivm.hir.varange":
+                # `hivm.hir.varange offset[%o] strides[%s0, %s1] outs(%d : T)`
+                dst = val(outs[0])
+                mo = re.search(r"offset\[([^\]]*)\]", op.text)
+                ms = re.search(r"strides\[([^\]]*)\]", op.text)
+                off = int(val(mo.group(1).strip()).value) if mo and mo.group(1).strip() else 0
+                strides = [int(val(t.strip()).value) for t in ms.group(1).split(",")] if ms and ms.group(1).strip() else None
+                if strides is None:                                    # row-major positions
+                    strides, acc_s = [], 1
+                    for d in reversed(dst.shape):
+                        strides.insert(0, acc_s)
+                        acc_s *= d
+                define(op, [arange(list(dst.shape), strides, off, dtype=dst.dtype, out=dst)])
+            elif name == "hivm.hir.vinterleave":
+                define(op, [interleave([val(n) for n in ins], out=val(outs[0]))])
+            elif name == "hivm.hir.vdeinterleave":
+                # `... channel_num = 32 index_mode = <CHANNEL_0>`: the even (CHANNEL_0) or odd (CHANNEL_1) elements, or both
+                src = val(ins[0])
+                m = re.search(r"index_mode\s*=\s*(?:#hivm\.deinterleave_mode)?<(\w+)>", op.text)
+                mode = m.group(1) if m else "ALL_CHANNELS"
+                dsts = [val(n) for n in outs]
+                if mode == "ALL_CHANNELS":
+                    parts = deinterleave(src, 2)
+                    define(op, [write_out(d, ptn) for d, ptn in zip(dsts, parts)])
+                elif mode in ("CHANNEL_0", "CHANNEL_1"):
+                    ch = int(mode[-1])
+                    define(op, [write_out(dsts[0], deinterleave(src, 2, keep=[ch])[ch])])
+                else:
+                    raise MlirTextError(f"hivm.hir.vdeinterleave: index_mode {mode}")
             elif name == "hfusion.compare":
                 define(op, [write_out(val(outs[0]), compare(op.attr("compare_fn") or "veq", operand(ins[0]), operand(ins[1])))])
             elif name == "hfusion.isnan":

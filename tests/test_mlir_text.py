@@ -486,3 +486,54 @@ def test_scalar_arithmetic_from_elements_and_concat(bsir):
     cat, t = mlir_text.parse(SCALAR_IR)["pieces"](a, b)
     assert torch.equal(cat, torch.cat([a, b], dim=1))
     assert t.tolist() == [3, -1, 3]                                   # 7 / 2, -7 rem 2 (sign of the dividend), select
+
+
+HIVM_MORE_IR = """
+func.func @vector_ops(%x: tensor<16x64xf32>, %y: tensor<16x64xf32>, %row: tensor<1x64xf32>, %i: tensor<16x64xi32>, %j: tensor<16x64xi32>)
+    -> (tensor<16x64xf32>, tensor<16x64xf32>, tensor<64x16xf32>, tensor<16x64xi32>, tensor<16x128xf32>, tensor<16x32xf32>, tensor<16x64xi32>) {
+  %e0 = tensor.empty() : tensor<16x64xf32>
+  %ex = hivm.hir.vexp ins(%x : tensor<16x64xf32>) outs(%e0 : tensor<16x64xf32>) -> tensor<16x64xf32>
+  %e1 = tensor.empty() : tensor<16x64xi1>
+  %lt = hivm.hir.vcmp ins(%x, %y : tensor<16x64xf32>, tensor<16x64xf32>) outs(%e1 : tensor<16x64xi1>) compare_mode = <lt> -> tensor<16x64xi1>
+  %e2 = tensor.empty() : tensor<16x64xf32>
+  %sel = hivm.hir.vsel ins(%lt, %ex, %y : tensor<16x64xi1>, tensor<16x64xf32>, tensor<16x64xf32>) outs(%e2 : tensor<16x64xf32>) -> tensor<16x64xf32>
+  %e3 = tensor.empty() : tensor<16x64xf32>
+  %b = hivm.hir.vbrc ins(%row : tensor<1x64xf32>) outs(%e3 : tensor<16x64xf32>) broadcast_dims = [0] -> tensor<16x64xf32>
+  %e4 = tensor.empty() : tensor<16x64xf32>
+  %sum = hivm.hir.vadd ins(%sel, %b : tensor<16x64xf32>, tensor<16x64xf32>) outs(%e4 : tensor<16x64xf32>) -> tensor<16x64xf32>
+  %e5 = tensor.empty() : tensor<64x16xf32>
+  %t = hivm.hir.vtranspose ins(%sum : tensor<16x64xf32>) outs(%e5 : tensor<64x16xf32>) permutation = [1, 0] -> tensor<64x16xf32>
+  %e6 = tensor.empty() : tensor<16x64xi32>
+  %a = hivm.hir.vand ins(%i, %j : tensor<16x64xi32>, tensor<16x64xi32>) outs(%e6 : tensor<16x64xi32>) -> tensor<16x64xi32>
+  %e7 = tensor.empty() : tensor<16x128xf32>
+  %il = hivm.hir.vinterleave ins(%x, %y : tensor<16x64xf32>, tensor<16x64xf32>) outs(%e7 : tensor<16x128xf32>) interleave_channel_nums = 2 -> tensor<16x128xf32>
+  %e8 = tensor.empty() : tensor<16x32xf32>
+  %odd = hivm.hir.vdeinterleave ins(%x : tensor<16x64xf32>) outs(%e8 : tensor<16x32xf32>) channel_num = 32 index_mode = <CHANNEL_1> -> tensor<16x32xf32>
+  %c5 = arith.constant 5 : index
+  %c64 = arith.constant 64 : index
+  %c1 = arith.constant 1 : index
+  %e9 = tensor.empty() : tensor<16x64xi32>
+  %ar = hivm.hir.varange offset[%c5] strides[%c64, %c1] outs(%e9 : tensor<16x64xi32>) -> tensor<16x64xi32>
+  return %sel, %sum, %t, %a, %il, %odd, %ar : tensor<16x64xf32>, tensor<16x64xf32>, tensor<64x16xf32>, tensor<16x64xi32>, tensor<16x128xf32>, tensor<16x32xf32>, tensor<16x64xi32>
+}
+"""
+
+
+@pytest.mark.gpu
+def test_more_hivm_vector_ops(bsir):
+    import torch
+    from bsir import mlir_text
+    g = torch.Generator(device="cuda").manual_seed(3)
+    x, y = torch.randn(16, 64, generator=g, device="cuda"), torch.randn(16, 64, generator=g, device="cuda")
+    row = torch.randn(1, 64, generator=g, device="cuda")
+    i = torch.randint(0, 1 << 20, (16, 64), generator=g, device="cuda", dtype=torch.int32)
+    j = torch.randint(0, 1 << 20, (16, 64), generator=g, device="cuda", dtype=torch.int32)
+    fn = mlir_text.parse(HIVM_MORE_IR)["vector_ops"]
+    fn.fuse = False                                     # op by op: every op through its own library call
+    sel, total, t, a, il, odd, ar = fn(x, y, row, i, j)
+    ex = bsir.elemwise_unary("exp", x)
+    want_sel = torch.where(x < y, ex, y)
+    assert torch.equal(sel, want_sel) and torch.equal(total, want_sel + row) and torch.equal(t, (want_sel + row).t())
+    assert torch.equal(a, i & j)
+    assert torch.equal(il, torch.stack([x, y], dim=-1).reshape(16, 128)) and torch.equal(odd, x[:, 1::2])
+    assert torch.equal(ar.cpu(), (5 + torch.arange(16 * 64, dtype=torch.int32)).reshape(16, 64))
