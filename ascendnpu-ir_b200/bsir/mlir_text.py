@@ -8,7 +8,8 @@ ops around them) and runs it op by op through the CUDA library.
 Covered (attribute spellings as in the reference):
   hfusion.cast {round_mode | mode = #hfusion.round_mode<..>, enable_saturate, overflow_mode}      HFusionNamedStructuredOps.yaml:373-432
   hfusion.elemwise_unary / elemwise_binary {fun = #hfusion.unary_fn<..>}, linalg.elemwise_unary / elemwise_binary
-  hfusion.compare {compare_fn = #hfusion.compare_fn<..>}, hfusion.select, hfusion.isnan
+  hfusion.compare {compare_fn = #hfusion.compare_fn<..>}, hfusion.select, hfusion.isnan, hfusion.elemwise_ternary {fun = select | fma},
+  hfusion.bitcast, hfusion.load / store
   hfusion.reduce_with_index {tie_break_left} <max|min>
   linalg.fill, linalg.broadcast dimensions = [..], linalg.reduce {arith.<combiner>} dimensions = [k] (short form and a
   region with one combiner op), linalg.matmul / matmul_transpose_a / matmul_transpose_b / batch_matmul (i8 -> i32, f16, bf16),
@@ -218,7 +219,8 @@ class Function:
     # ------------------------------------------------------------------ execution
     def __call__(self, *tensors):
         import torch
-        from . import (arange, cast, compare, copy, cumulative, deinterleave, elemwise_binary, elemwise_unary, gather, interleave,
+        from . import (arange, cast, compare, copy, cumulative, deinterleave, elemwise_binary, elemwise_ternary, elemwise_unary, gather,
+                       interleave,
                        load, matmul, reduce, reduce_with_index, select, sort, store, transpose)
         if len(tensors) != len(self.args):
             raise MlirTextError(f"@{self.name} takes {len(self.args)} arguments, got {len(tensors)}")
@@ -620,8 +622,21 @@ class Function:
                 for d in sorted(dims):
                     view = view.unsqueeze(d)
                 define(op, [copy(view.expand(dst.shape), out=dst)])
-            elif name in ("linalg.copy", "hivm.hir.copy"):
+            elif name in ("linalg.copy", "hivm.hir.copy", "hfusion.load", "hfusion.store"):
                 define(op, [copy(val(ins[0]), out=val(outs[0]))])
+            elif name == "hfusion.bitcast":
+                src, dst = val(ins[0]), val(outs[0])
+                if src.element_size() != dst.element_size():
+                    raise MlirTextError("hfusion.bitcast: element sizes differ")
+                define(op, [copy(src.view(dst.dtype), out=dst)])
+            elif name == "hfusion.elemwise_ternary":
+                fun = op.attr("fun") or "select"                      # #hfusion.ternary_fn<select | fma>
+                if fun == "select":
+                    define(op, [write_out(val(outs[0]), select(val(ins[0]), operand(ins[1]), operand(ins[2])))])
+                elif fun == "fma":
+                    define(op, [write_out(val(outs[0]), elemwise_ternary("fma", operand(ins[0]), operand(ins[1]), operand(ins[2])))])
+                else:
+                    raise MlirTextError(f"hfusion.elemwise_ternary: fun {fun}")
             elif name == "hivm.hir.load":
                 pm = op.attr("pad_mode")
                 if pm is None:

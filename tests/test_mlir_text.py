@@ -537,3 +537,27 @@ def test_more_hivm_vector_ops(bsir):
     assert torch.equal(a, i & j)
     assert torch.equal(il, torch.stack([x, y], dim=-1).reshape(16, 128)) and torch.equal(odd, x[:, 1::2])
     assert torch.equal(ar.cpu(), (5 + torch.arange(16 * 64, dtype=torch.int32)).reshape(16, 64))
+
+
+TERNARY_IR = """
+func.func @fma_and_bits(%a: tensor<8x32xf32>, %b: tensor<8x32xf32>, %c: tensor<8x32xf32>) -> (tensor<8x32xf32>, tensor<8x32xi32>) {
+  %e = tensor.empty() : tensor<8x32xf32>
+  %l = hfusion.load ins(%a : tensor<8x32xf32>) outs(%e : tensor<8x32xf32>) -> tensor<8x32xf32>
+  %e1 = tensor.empty() : tensor<8x32xf32>
+  %f = hfusion.elemwise_ternary {fun = #hfusion.ternary_fn<fma>} ins(%l, %b, %c : tensor<8x32xf32>, tensor<8x32xf32>, tensor<8x32xf32>) outs(%e1 : tensor<8x32xf32>) -> tensor<8x32xf32>
+  %e2 = tensor.empty() : tensor<8x32xi32>
+  %bits = hfusion.bitcast ins(%f : tensor<8x32xf32>) outs(%e2 : tensor<8x32xi32>) -> tensor<8x32xi32>
+  return %f, %bits : tensor<8x32xf32>, tensor<8x32xi32>
+}
+"""
+
+
+@pytest.mark.gpu
+def test_ternary_bitcast_load(bsir):
+    import torch
+    from bsir import mlir_text
+    a, b, c = (torch.randn(8, 32, device="cuda") for _ in range(3))
+    f, bits = mlir_text.parse(TERNARY_IR)["fma_and_bits"](a, b, c)
+    want = torch.from_numpy(np.asarray([float(np.float32(np.float64(x) * np.float64(y) + np.float64(z))) for x, y, z in
+                                        zip(a.flatten().tolist(), b.flatten().tolist(), c.flatten().tolist())], dtype=np.float32)).reshape(8, 32)
+    assert torch.equal(f.cpu(), want) and torch.equal(bits.cpu(), want.view(torch.int32))
