@@ -13,7 +13,7 @@ Covered (attribute spellings as in the reference):
   hfusion.reduce_with_index {tie_break_left} <max|min>
   linalg.fill, linalg.broadcast dimensions = [..], linalg.reduce {arith.<combiner>} dimensions = [k] (short form and a
   region with one combiner op), linalg.matmul / matmul_transpose_a / matmul_transpose_b / batch_matmul (i8 -> i32, f16, bf16),
-  linalg.copy
+  linalg.copy, linalg.generic (elementwise bodies over identity maps: one fused kernel; last-axis reductions of one combiner)
   hivm.hir.load (pad_mode / pad_value / left_padding_num / right_padding_num), hivm.hir.store (atomic = <kind>),
   hivm.hir.copy, hivm.hir.vadd / vsub / vmul / vdiv / vmax / vmin / vand / vor / vxor / vpow / vmod / vmodui / vshl / vshr,
   hivm.hir.vexp / vln / vabs / vsqrt / vrsqrt / vrelu / vnot / vrec / vtanh / verf / vsin / vcos, vcmp [compare_mode = <..>], vsel,
@@ -652,6 +652,8 @@ class Function:
             elif name == "hivm.hir.store":
                 m = re.search(r"atomic\s*=\s*<(\w+)>", op.text)
                 define(op, [store(val(ins[0]), val(outs[0]), atomic=m.group(1) if m else "none")])
+            elif name == "linalg.generic":
+                define(op, [self._generic(op, ins, outs, val, operand)])
             elif name == "linalg.reduce" or name == "hivm.hir.vreduce":
                 src, dst = val(ins[0]), val(outs[0])
                 if name == "linalg.reduce":
@@ -727,6 +729,91 @@ class Function:
             else:
                 raise MlirTextError(f"op {name} is not supported by this front end")
         return None
+
+
+_GENERIC_UNARY = {"math.exp": "exp", "math.log": "log", "math.sqrt": "sqrt", "math.rsqrt": "rsqrt", "math.tanh": "tanh", "math.absf": "abs",
+                  "math.ceil": "ceil", "math.floor": "floor", "math.erf": "erf", "math.sin": "sin", "math.cos": "cos", "math.exp2": "exp2",
+                  "math.log2": "log2", "arith.negf": "negf"}
+_GENERIC_BINARY = {"arith.addf": "add", "arith.subf": "sub", "arith.mulf": "mul", "arith.divf": "div", "arith.maximumf": "maxf",
+                   "arith.minimumf": "minf", "arith.maxnumf": "maxnumf", "arith.minnumf": "minnumf", "math.powf": "powf"}
+
+
+def _generic(self, op, ins, outs, val, operand):
+    """linalg.generic in the two shapes the reference's tests write by hand: an elementwise body over identity maps
+    (all iterators parallel; f32; the body becomes one fused kernel) and a reduction of the last axis whose body is a
+    single combiner of the input element and the accumulator (what linalg.reduce says in short)."""
+    import torch
+    from . import fusion, reduce as reduce_op
+    maps = re.findall(r"affine_map<\(([^)]*)\)\s*->\s*\(([^)]*)\)>", op.text)
+    iters = re.findall(r'"(parallel|reduction)"', op.text.split("ins(")[0].split("outs(")[0])
+    m = re.search(r"\{\s*\^bb0\(([^)]*)\)\s*:(.*)\}\s*(?:->.*)?$", op.text, re.S)
+    if not maps or not m:
+        raise MlirTextError("linalg.generic: indexing_maps and a region with ^bb0 expected")
+    args = [a.split(":")[0].strip() for a in m.group(1).split(",") if a.strip()]
+    body = _statements(m.group(2))
+    dst = val(outs[0])
+    srcs = [val(n) for n in ins]
+    ident = lambda mp: [d.strip() for d in mp[0].split(",")] == [d.strip() for d in mp[1].split(",")]
+    if len(maps) != len(srcs) + 1 or len(args) != len(srcs) + 1:
+        raise MlirTextError("linalg.generic: one indexing map and one block argument per operand expected")
+    local = {}                                              # SSA names of the body -> fusion nodes
+
+    def node(name):
+        if name in local:
+            return local[name]
+        v = operand(name)                                   # a value from outside the region
+        if isinstance(v, torch.Tensor):
+            raise MlirTextError("linalg.generic: the body uses a tensor from outside the region")
+        return ("imm", float(v))
+
+    if all(i == "parallel" for i in iters) and all(ident(mp) for mp in maps):
+        prob = fusion.problem(list(dst.shape))
+        if prob is None or dst.dtype != torch.float32 or any(t.dtype != torch.float32 or t.shape != dst.shape or not t.is_contiguous() for t in srcs):
+            raise MlirTextError("linalg.generic: an elementwise body is run for contiguous f32 tensors of rank 1 or 2 of one shape")
+        for a, t in zip(args, srcs + [dst]):
+            local[a] = ("leaf", t.view(*prob), "full")
+        result = None
+        for b in body:
+            names = re.findall(r"%[\w.]+", b.text.split(":")[0])
+            if b.name == "linalg.yield":
+                result = node(names[0])
+            elif b.name == "arith.constant":
+                v, ty = b.text.rsplit(":", 1)
+                local[b.results[0]] = ("imm", _float_literal(v.strip(), ty.strip()))
+            elif b.name in _GENERIC_UNARY:
+                local[b.results[0]] = ("un", _GENERIC_UNARY[b.name], node(names[0]))
+            elif b.name in _GENERIC_BINARY:
+                local[b.results[0]] = ("bin", _GENERIC_BINARY[b.name], node(names[0]), node(names[1]))
+            else:
+                raise MlirTextError(f"linalg.generic: {b.name} in an elementwise body is not supported")
+        if result is None:
+            raise MlirTextError("linalg.generic: the body does not yield")
+        if result[0] == "imm":                               # a fill
+            from . import elemwise_binary
+            return elemwise_binary("add", torch.zeros_like(dst), result[1], out=dst)
+        if not fusion.fits(result):
+            raise MlirTextError("linalg.generic: the body is too large for one fused kernel")
+        fusion.run([(fusion.Lazy(result, list(dst.shape), prob), dst)], prob)
+        return dst
+    # last-axis reduction: in (d0, .., dk) -> identity, out drops dk, iterators [.., "reduction"], body = one combiner
+    if len(srcs) == 1 and iters and iters[-1] == "reduction" and all(i == "parallel" for i in iters[:-1]) and ident(maps[0]) and \
+            [d.strip() for d in maps[1][1].split(",") if d.strip()] == [d.strip() for d in maps[0][0].split(",")][:-1]:
+        comb = [b for b in body if b.name != "linalg.yield"]
+        if len(comb) != 1 or comb[0].name not in _REDUCE_COMBINERS:
+            raise MlirTextError("linalg.generic: a reduction body of one combiner op is supported")
+        used = set(re.findall(r"%[\w.]+", comb[0].text.split(":")[0]))
+        if used != set(args):
+            raise MlirTextError("linalg.generic: the combiner must take the input element and the accumulator")
+        src = srcs[0]
+        rows = src.numel() // max(src.shape[-1], 1)
+        out = reduce_op(_REDUCE_COMBINERS[comb[0].name], src.reshape(rows, src.shape[-1]), dim=1)
+        from . import copy as copy_op
+        copy_op(out.view(-1), out=dst.view(-1))               # a rank-0 result is one element
+        return dst
+    raise MlirTextError("linalg.generic: only identity-map elementwise bodies and last-axis reductions are supported")
+
+
+Function._generic = _generic
 
 
 def parse(text: str) -> Dict[str, Function]:

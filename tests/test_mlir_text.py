@@ -561,3 +561,48 @@ def test_ternary_bitcast_load(bsir):
     want = torch.from_numpy(np.asarray([float(np.float32(np.float64(x) * np.float64(y) + np.float64(z))) for x, y, z in
                                         zip(a.flatten().tolist(), b.flatten().tolist(), c.flatten().tolist())], dtype=np.float32)).reshape(8, 32)
     assert torch.equal(f.cpu(), want) and torch.equal(bits.cpu(), want.view(torch.int32))
+
+
+GENERIC_IR = """
+func.func @generic_forms(%x: tensor<300x128xf32>, %y: tensor<300x128xf32>, %v: tensor<128xf32>) -> (tensor<300x128xf32>, tensor<300xf32>, tensor<f32>) {
+  %half = arith.constant 5.000000e-01 : f32
+  %e = tensor.empty() : tensor<300x128xf32>
+  %d = linalg.generic {indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0, d1)>],
+                       iterator_types = ["parallel", "parallel"]} ins(%x, %y : tensor<300x128xf32>, tensor<300x128xf32>) outs(%e : tensor<300x128xf32>) {
+  ^bb0(%in: f32, %in_1: f32, %out: f32):
+    %0 = arith.subf %in, %in_1 : f32
+    %1 = arith.mulf %0, %half : f32
+    %2 = math.exp %1 : f32
+    linalg.yield %2 : f32
+  } -> tensor<300x128xf32>
+  %r0 = tensor.empty() : tensor<300xf32>
+  %r = linalg.generic {indexing_maps = [affine_map<(d0, d1) -> (d0, d1)>, affine_map<(d0, d1) -> (d0)>], iterator_types = ["parallel", "reduction"]}
+       ins(%d : tensor<300x128xf32>) outs(%r0 : tensor<300xf32>) {
+  ^bb0(%in: f32, %out: f32):
+    %0 = arith.addf %in, %out : f32
+    linalg.yield %0 : f32
+  } -> tensor<300xf32>
+  %s0 = tensor.empty() : tensor<f32>
+  %s = linalg.generic {indexing_maps = [affine_map<(d0) -> (d0)>, affine_map<(d0) -> ()>], iterator_types = ["reduction"]} ins(%v : tensor<128xf32>) outs(%s0 : tensor<f32>) {
+  ^bb0(%in: f32, %out: f32):
+    %0 = arith.maximumf %in, %out : f32
+    linalg.yield %0 : f32
+  } -> tensor<f32>
+  return %d, %r, %s : tensor<300x128xf32>, tensor<300xf32>, tensor<f32>
+}
+"""
+
+
+@pytest.mark.gpu
+def test_linalg_generic_elementwise_and_reduction_bodies(bsir):
+    """The hand-written linalg.generic forms of the reference's tile-reduction tests: an elementwise body runs as one
+    fused kernel with the bits of op-by-op execution, a one-combiner body over the last axis as a row reduction."""
+    import torch
+    from bsir import mlir_text
+    g = torch.Generator(device="cuda").manual_seed(8)
+    x, y = torch.randn(300, 128, generator=g, device="cuda"), torch.randn(300, 128, generator=g, device="cuda")
+    v = torch.randn(128, generator=g, device="cuda")
+    d, r, s = mlir_text.parse(GENERIC_IR)["generic_forms"](x, y, v)
+    want = bsir.elemwise_unary("exp", bsir.elemwise_binary("mul", bsir.elemwise_binary("sub", x, y), 0.5))
+    assert torch.equal(d, want)
+    assert torch.allclose(r, want.sum(dim=1), rtol=1e-5, atol=1e-4) and s.item() == v.max().item() and s.dim() == 0
