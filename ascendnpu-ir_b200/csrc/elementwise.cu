@@ -513,7 +513,7 @@ __device__ __forceinline__ Vec16 rows_expand(Vec16 v) {
 }
 
 template <int DT, int KIND, int KA, int KB>
-__global__ void __launch_bounds__(kStreamThreads)
+__global__ void __launch_bounds__(kStreamThreads, 4)
     rows_kernel(int fn, int64_t rows, int64_t vpr, RowsOperand a, RowsOperand b, void *__restrict__ outp, int64_t out_rs) {
   using T = typename CType<DT>::type;
   constexpr int kPerVec = 16 / sizeof(T);
