@@ -12,9 +12,10 @@
 // that compare like the values; descending complements it; NaN is the largest key in both directions), so one
 // integer comparison decides value and tie at once and the bitonic network -- not stable by itself -- gives a
 // stable result with the NaNs at the end in source order; the write-out then moves them to their places.  A CTA sorts one row in shared memory
-// (rows of up to 8192 elements: 64 KB of keys); longer rows keep their keys in device scratch and run the wide
-// steps of the network on global memory.  The values are read back from the source by index, so their bits
-// (the sign of a zero, the payload of a NaN) are the source's.
+// (rows of up to 8192 elements: 64 KB of keys); longer rows keep their keys in device scratch and are sorted by
+// radix passes instead (below).  The values are read back from the source by index (the long-row path rebuilds
+// them from the key and reads back only zeros and NaNs), so their bits -- the sign of a zero, the payload of a
+// NaN -- are the source's.
 #include <cstdint>
 
 #include "common.cuh"
@@ -131,119 +132,292 @@ __global__ void __launch_bounds__(kSortThreads) sort_rows_kernel(const typename 
 }
 
 // ------------------------------------------------------------------ rows longer than one CTA's shared memory
-// The same network over keys kept in device scratch ([rows][npow2] 64-bit words): one launch sorts every 8192-key
-// chunk in shared memory (all steps with k <= 8192, directions taken from the position in the whole row), then
-// for k = 16384, 32768, ...: the steps whose partners are 8192 or more apart run on global memory, one launch
-// each, and the steps below that again in shared memory, one launch per k.
+// A least-significant-digit radix sort, eight bits a pass, over keys kept in device scratch ([rows][cols] 64-bit
+// words, two copies).  Every pass is stable, so equal values stay in source order without the index taking part;
+// only the bits that can differ are visited (four passes for 32-bit elements, two for 16-bit ones, one for int8).
+// A pass is three launches over tiles of 4096 keys: count the digits of each tile; turn the counts of a row, in
+// (digit, tile) order, into the place where each tile's run of each digit starts; move the keys.  Nothing is
+// counted with atomics on global memory and no tile waits for another, so the result does not depend on timing.
+constexpr int kRadixTile = 4096;
+constexpr int kRadixThreads = 256;
+constexpr int kRadixWarps = kRadixThreads / 32;
+constexpr int kRadixIters = kRadixTile / kRadixThreads;       // keys per thread
+
+// The bits the passes sort on, in the upper half of the key.  32-bit elements use all of sort_order(); narrower
+// ones put their 16 (8) ordered bits at the top, so the digits below hold nothing that could differ between two
+// elements whose upper digits agree.  A NaN is 0xffffffff in both directions and no number maps there.
 template <int DT>
-__global__ void __launch_bounds__(kSortThreads) sort_chunks_kernel(const typename SortElem<DT>::type *__restrict__ src, int64_t src_stride,
-                                                                   unsigned long long *__restrict__ keys_g, int64_t cols, int npow2,
-                                                                   int descending, int k_first, int k_last) {
-  // k_first == 2: build the keys from the source and run k = 2 .. k_last; otherwise k = k_first only, with the
-  // steps j < kSortMaxLen (the wider ones were done on global memory)
-  extern __shared__ unsigned long long keys[];
-  const int64_t row = blockIdx.y;
-  const int64_t base = static_cast<int64_t>(blockIdx.x) * kSortMaxLen;      // position of this chunk in the row
-  unsigned long long *g = keys_g + row * npow2 + base;
-  if (k_first == 2) {
-    const auto *s = src + row * src_stride;
-    for (int i = threadIdx.x; i < kSortMaxLen; i += kSortThreads) {
-      const int64_t pos = base + i;
-      unsigned long long k = ~0ull;
-      if (pos < cols) k = sort_key<DT>(s[pos], pos, descending);
-      keys[i] = k;
-    }
+__device__ __forceinline__ uint32_t radix_order(typename SortElem<DT>::type v, int descending) {
+  uint32_t o;
+  if constexpr (DT == BSIR_I8) {
+    o = (static_cast<uint32_t>(static_cast<uint8_t>(v)) ^ 0x80u) << 24;
+  } else if constexpr (DT == BSIR_I16) {
+    o = (static_cast<uint32_t>(static_cast<uint16_t>(v)) ^ 0x8000u) << 16;
+  } else if constexpr (DT == BSIR_F16) {
+    uint32_t h = v;
+    if ((h & 0x7fffu) > 0x7c00u) return 0xffffffffu;
+    if (h == 0x8000u) h = 0u;                                 // -0 ties with +0
+    o = ((h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u)) << 16;
   } else {
-    for (int i = threadIdx.x; i < kSortMaxLen; i += kSortThreads) keys[i] = g[i];
+    o = sort_order<DT>(v);                                    // bf16: the lower half follows from the sign bit
+    if (kSortFloat<DT> && o == 0xffffffffu) return o;
   }
-  __syncthreads();
-  for (int64_t k = k_first; k <= k_last; k <<= 1) {
-    for (int j = static_cast<int>(k >> 1 < kSortMaxLen ? k >> 1 : kSortMaxLen >> 1); j > 0; j >>= 1) {
-      for (int t = threadIdx.x; t < kSortMaxLen / 2; t += kSortThreads) {
-        const int lo = ((t & ~(j - 1)) << 1) | (t & (j - 1)), hi = lo | j;
-        const bool up = ((base + lo) & k) == 0;
-        const unsigned long long a = keys[lo], b = keys[hi];
-        if ((a > b) == up) {
-          keys[lo] = b;
-          keys[hi] = a;
-        }
-      }
-      __syncthreads();
-    }
-  }
-  for (int i = threadIdx.x; i < kSortMaxLen; i += kSortThreads) g[i] = keys[i];
+  return descending ? ~o : o;
+}
+template <int DT> constexpr int kRadixFirstShift = (DT == BSIR_F32 || DT == BSIR_I32) ? 0 : DT == BSIR_I8 ? 24 : 16;
+
+template <int DT, bool FIRST>
+__device__ __forceinline__ unsigned long long radix_load(const typename SortElem<DT>::type *__restrict__ src_row,
+                                                         const unsigned long long *__restrict__ keys_row, int64_t pos, int descending) {
+  if constexpr (FIRST) return (static_cast<unsigned long long>(radix_order<DT>(src_row[pos], descending)) << 32) | static_cast<uint32_t>(pos);
+  else return keys_row[pos];
 }
 
-// one compare-exchange step (partners j apart, j >= kSortMaxLen) of stage k on global memory
-__global__ void __launch_bounds__(256) sort_global_step_kernel(unsigned long long *__restrict__ keys_g, int npow2, int64_t k, int64_t j) {
-  const int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (t >= npow2 / 2) return;
-  unsigned long long *g = keys_g + static_cast<int64_t>(blockIdx.y) * npow2;
-  const int64_t lo = ((t & ~(j - 1)) << 1) | (t & (j - 1)), hi = lo | j;
-  const bool up = (lo & k) == 0;
-  const unsigned long long a = g[lo], b = g[hi];
-  if ((a > b) == up) {
-    g[lo] = b;
-    g[hi] = a;
+// digit counts of one tile -> hist[row][digit][tile]
+template <int DT, bool FIRST>
+__global__ void __launch_bounds__(kRadixThreads) radix_count_kernel(const typename SortElem<DT>::type *__restrict__ src, int64_t src_stride,
+                                                                    const unsigned long long *__restrict__ keys_in, int64_t cols, int descending,
+                                                                    int shift, uint32_t *__restrict__ hist, int64_t ntiles) {
+  __shared__ uint32_t count[256];
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int64_t row = blockIdx.y, tile = blockIdx.x, base = tile * kRadixTile;
+  count[tid] = 0;
+  __syncthreads();
+  const auto *src_row = src + row * src_stride;
+  const unsigned long long *keys_row = keys_in + row * cols;
+#pragma unroll 4
+  for (int i = 0; i < kRadixIters; ++i) {
+    const int64_t pos = base + i * kRadixThreads + tid;
+    const bool valid = pos < cols;
+    uint32_t digit = 256;                                     // lanes past the row's end match only one another
+    if (valid) digit = static_cast<uint32_t>(radix_load<DT, FIRST>(src_row, keys_row, pos, descending) >> (32 + shift)) & 255u;
+    const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+    if (valid && (peers & ((1u << lane) - 1)) == 0) atomicAdd(&count[digit], __popc(peers));   // one add per distinct digit of the warp
+  }
+  __syncthreads();
+  hist[(row * 256 + tid) * ntiles + tile] = count[tid];
+}
+
+// hist[row] holds 256 x ntiles counts; in (digit, tile) order each becomes the sum of the ones before it
+__global__ void __launch_bounds__(kRadixThreads) radix_offsets_kernel(uint32_t *__restrict__ hist, int64_t ntiles) {
+  __shared__ uint32_t total[256];
+  __shared__ uint32_t warp_sum[kRadixWarps];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  uint32_t *h = hist + static_cast<int64_t>(blockIdx.x) * 256 * ntiles;
+  for (int d = warp; d < 256; d += kRadixWarps) {
+    uint32_t sum = 0;
+    for (int64_t t = lane; t < ntiles; t += 32) sum += h[d * ntiles + t];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) total[d] = sum;
+  }
+  __syncthreads();
+  {   // exclusive scan of the 256 digit totals
+    const uint32_t mine = total[tid];
+    uint32_t incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane == 31) warp_sum[warp] = incl;
+    __syncthreads();
+    uint32_t before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_sum[w];
+    total[tid] = before + incl - mine;
+  }
+  __syncthreads();
+  for (int d = warp; d < 256; d += kRadixWarps) {
+    uint32_t running = total[d];
+    for (int64_t t0 = 0; t0 < ntiles; t0 += 32) {
+      const int64_t t = t0 + lane;
+      const uint32_t mine = t < ntiles ? h[d * ntiles + t] : 0u;
+      uint32_t incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      if (t < ntiles) h[d * ntiles + t] = running + incl - mine;
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+  }
+}
+
+// Moves the keys of one tile to their places of this pass.  A warp owns 512 consecutive keys and takes them 32 at
+// a time in order; within such a group a key's rank among the keys of its digit is the number of lower lanes with
+// that digit, and the warp's running count of the digit carries the rank from group to group -- source order is
+// kept.  The warps' counts are then chained, the tile is put in digit order in shared memory and written out from
+// there, so that the stores of a warp fall into a few runs of the row instead of 32 places.
+template <int DT, bool FIRST>
+__global__ void __launch_bounds__(kRadixThreads) radix_move_kernel(const typename SortElem<DT>::type *__restrict__ src, int64_t src_stride,
+                                                                   const unsigned long long *__restrict__ keys_in,
+                                                                   unsigned long long *__restrict__ keys_out, int64_t cols, int descending,
+                                                                   int shift, const uint32_t *__restrict__ hist, int64_t ntiles) {
+  __shared__ unsigned long long sorted[kRadixTile];
+  __shared__ uint32_t count[kRadixWarps][256];
+  __shared__ uint32_t to_row[256];
+  __shared__ uint32_t warp_sum[kRadixWarps];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t row = blockIdx.y, tile = blockIdx.x;
+  const int64_t base = tile * kRadixTile + warp * (kRadixTile / kRadixWarps);
+#pragma unroll
+  for (int w = 0; w < kRadixWarps; ++w) count[w][tid] = 0;
+  __syncthreads();
+  const auto *src_row = src + row * src_stride;
+  const unsigned long long *keys_row = keys_in + row * cols;
+  unsigned long long key[kRadixIters];
+  uint32_t rank[kRadixIters];
+#pragma unroll
+  for (int i = 0; i < kRadixIters; ++i) {
+    const int64_t pos = base + i * 32 + lane;
+    key[i] = pos < cols ? radix_load<DT, FIRST>(src_row, keys_row, pos, descending) : 0ull;
+  }
+#pragma unroll
+  for (int i = 0; i < kRadixIters; ++i) {
+    const bool valid = base + i * 32 + lane < cols;
+    const uint32_t digit = valid ? static_cast<uint32_t>(key[i] >> (32 + shift)) & 255u : 256u;
+    const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+    const uint32_t below = __popc(peers & ((1u << lane) - 1));
+    uint32_t before = 0;
+    if (valid) before = count[warp][digit];
+    __syncwarp();
+    if (valid && below == 0) count[warp][digit] = before + __popc(peers);
+    __syncwarp();
+    rank[i] = before + below;
+  }
+  __syncthreads();
+  {   // digit tid: where the tile's keys of the digit start within the tile (digits in order), each warp's share
+      // behind that, and what turns a place in the tile into the place in the row
+    uint32_t mine = 0;
+#pragma unroll
+    for (int w = 0; w < kRadixWarps; ++w) mine += count[w][tid];
+    uint32_t incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane == 31) warp_sum[warp] = incl;
+    __syncthreads();
+    uint32_t start = incl - mine;
+    for (int w = 0; w < warp; ++w) start += warp_sum[w];
+    to_row[tid] = hist[(row * 256 + tid) * ntiles + tile] - start;
+    uint32_t running = start;
+#pragma unroll
+    for (int w = 0; w < kRadixWarps; ++w) {
+      const uint32_t c = count[w][tid];
+      count[w][tid] = running;
+      running += c;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < kRadixIters; ++i) {
+    if (base + i * 32 + lane < cols) {
+      const uint32_t digit = static_cast<uint32_t>(key[i] >> (32 + shift)) & 255u;
+      sorted[count[warp][digit] + rank[i]] = key[i];
+    }
+  }
+  __syncthreads();
+  // the tile, now in digit order, goes out in runs: neighbouring threads write neighbouring places of the row
+  const int64_t left = cols - tile * kRadixTile;
+  const int in_tile = left < kRadixTile ? static_cast<int>(left) : kRadixTile;
+  unsigned long long *out_row = keys_out + row * cols;
+#pragma unroll 4
+  for (int j = tid; j < in_tile; j += kRadixThreads) {
+    const unsigned long long k = sorted[j];
+    const uint32_t digit = static_cast<uint32_t>(k >> (32 + shift)) & 255u;
+    out_row[to_row[digit] + static_cast<uint32_t>(j)] = k;
+  }
+}
+
+// The element a key stands for, from the key alone; false for a zero (either sign maps to the same key) or a NaN,
+// whose bits are the source's.
+template <int DT>
+__device__ __forceinline__ bool radix_value(uint32_t o, int descending, typename SortElem<DT>::type &v) {
+  if (kSortFloat<DT> && o == 0xffffffffu) return false;
+  if (descending) o = ~o;
+  if constexpr (DT == BSIR_I32) { v = static_cast<int32_t>(o ^ 0x80000000u); return true; }
+  else if constexpr (DT == BSIR_I16) { v = static_cast<int16_t>((o >> 16) ^ 0x8000u); return true; }
+  else if constexpr (DT == BSIR_I8) { v = static_cast<int8_t>((o >> 24) ^ 0x80u); return true; }
+  else if constexpr (DT == BSIR_F16) {
+    const uint32_t h = (o & 0x80000000u) ? (o >> 16) & 0x7fffu : (~o >> 16) & 0xffffu;
+    v = static_cast<uint16_t>(h);
+    return h != 0;
+  } else {
+    const uint32_t b = (o & 0x80000000u) ? o & 0x7fffffffu : ~o;
+    if constexpr (DT == BSIR_F32) v = __uint_as_float(b);
+    else v = static_cast<uint16_t>(b >> 16);
+    return b != 0;
   }
 }
 
 template <int DT>
 __global__ void __launch_bounds__(256) sort_emit_kernel(const typename SortElem<DT>::type *__restrict__ src, int64_t src_stride,
-                                                        const unsigned long long *__restrict__ keys_g, int npow2,
+                                                        const unsigned long long *__restrict__ keys_g, int64_t keys_stride,
                                                         typename SortElem<DT>::type *__restrict__ dst_value, int64_t val_stride,
-                                                        int32_t *__restrict__ dst_index, int64_t idx_stride, int64_t cols) {
+                                                        int32_t *__restrict__ dst_index, int64_t idx_stride, int64_t cols, int descending) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= cols) return;
   const int64_t row = blockIdx.y;
-  const unsigned long long *keys = keys_g + row * npow2;
-  const uint32_t idx = static_cast<uint32_t>(keys[i]);
+  const unsigned long long *keys = keys_g + row * keys_stride;
+  const unsigned long long key = keys[i];
+  const uint32_t idx = static_cast<uint32_t>(key);
   int64_t at = i;
   if constexpr (kSortFloat<DT>) {
     const int64_t nan = sort_count_nan(keys, cols);          // one load when the row has no NaN
     if (nan) at = sort_place(keys, i, cols, nan);
   }
-  if (dst_value) dst_value[row * val_stride + at] = src[row * src_stride + idx];
+  if (dst_value) {
+    typename SortElem<DT>::type v;
+    if (!radix_value<DT>(static_cast<uint32_t>(key >> 32), descending, v)) v = src[row * src_stride + idx];
+    dst_value[row * val_stride + at] = v;
+  }
   if (dst_index) dst_index[row * idx_stride + at] = static_cast<int32_t>(idx);
 }
 
-// rows per pass such that the keys fit `budget` bytes of scratch
+// as many rows at a time as fit `budget` bytes of scratch (two copies of the keys and the digit counts)
 template <int DT>
 int32_t launch_sort_long(const void *src, int64_t ss, void *dv, int64_t vs, int32_t *di, int64_t is, int64_t rows, int64_t cols,
                          int descending, cudaStream_t st) {
   using T = typename SortElem<DT>::type;
-  int64_t npow2 = kSortMaxLen;
-  while (npow2 < cols) npow2 <<= 1;
-  if (npow2 > (int64_t(1) << 30)) return fail(BSIR_ERR_UNSUPPORTED, "sort: rows of %lld elements", (long long)cols);
-  const int64_t row_bytes = npow2 * 8;
-  const int64_t budget = int64_t(1) << 30;                       // at most 1 GiB of keys at a time
+  if (cols > (int64_t(1) << 30)) return fail(BSIR_ERR_UNSUPPORTED, "sort: rows of %lld elements", (long long)cols);
+  const int64_t ntiles = ceil_div(cols, static_cast<int64_t>(kRadixTile));
+  const int64_t keys_bytes = (cols * 8 + 255) / 256 * 256, hist_bytes = ntiles * 256 * 4;
+  const int64_t row_bytes = 2 * keys_bytes + hist_bytes;
+  const int64_t budget = int64_t(1) << 30;
   int64_t rows_per_pass = budget / row_bytes;
   if (rows_per_pass < 1) rows_per_pass = 1;
   if (rows_per_pass > rows) rows_per_pass = rows;
   if (rows_per_pass > 65535) rows_per_pass = 65535;
   char *ws = static_cast<char *>(device_workspace(kScratchCounterBytes + static_cast<size_t>(rows_per_pass * row_bytes), st));
   if (!ws) return BSIR_ERR_WORKSPACE;
-  unsigned long long *keys = reinterpret_cast<unsigned long long *>(ws + kScratchCounterBytes);
-  // the attribute belongs to the current device's copy of the kernel: set it on every call, not once per process
-  cudaFuncSetAttribute(sort_chunks_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSortMaxLen * 8);
+  // each row's keys start where the row index times cols puts them; the two copies and the counts follow one another
+  unsigned long long *keys_a = reinterpret_cast<unsigned long long *>(ws + kScratchCounterBytes);
+  unsigned long long *keys_b = reinterpret_cast<unsigned long long *>(ws + kScratchCounterBytes + rows_per_pass * keys_bytes);
+  uint32_t *hist = reinterpret_cast<uint32_t *>(ws + kScratchCounterBytes + 2 * rows_per_pass * keys_bytes);
   const T *s = static_cast<const T *>(src);
   T *d = static_cast<T *>(dv);
-  const int n = static_cast<int>(npow2);
   for (int64_t r0 = 0; r0 < rows; r0 += rows_per_pass) {
     const unsigned nr = static_cast<unsigned>(rows - r0 < rows_per_pass ? rows - r0 : rows_per_pass);
-    const dim3 chunks(static_cast<unsigned>(npow2 / kSortMaxLen), nr);
-    sort_chunks_kernel<DT><<<chunks, kSortThreads, kSortMaxLen * 8, st>>>(s + r0 * ss, ss, keys, cols, n, descending, 2, kSortMaxLen);
-    count_launch();
-    for (int64_t k = 2 * kSortMaxLen; k <= npow2; k <<= 1) {
-      for (int64_t j = k >> 1; j >= kSortMaxLen; j >>= 1) {
-        sort_global_step_kernel<<<dim3(static_cast<unsigned>(ceil_div(npow2 / 2, 256)), nr), 256, 0, st>>>(keys, n, k, j);
-        count_launch();
-      }
-      sort_chunks_kernel<DT><<<chunks, kSortThreads, kSortMaxLen * 8, st>>>(s, ss, keys, cols, n, descending, static_cast<int>(k), static_cast<int>(k));
+    const dim3 tiles(static_cast<unsigned>(ntiles), nr);
+    const unsigned long long *in = nullptr;
+    unsigned long long *out = keys_a;
+    for (int shift = kRadixFirstShift<DT>; shift < 32; shift += 8) {
+      if (!in) radix_count_kernel<DT, true><<<tiles, kRadixThreads, 0, st>>>(s + r0 * ss, ss, nullptr, cols, descending, shift, hist, ntiles);
+      else radix_count_kernel<DT, false><<<tiles, kRadixThreads, 0, st>>>(s, ss, in, cols, descending, shift, hist, ntiles);
+      radix_offsets_kernel<<<nr, kRadixThreads, 0, st>>>(hist, ntiles);
+      if (!in) radix_move_kernel<DT, true><<<tiles, kRadixThreads, 0, st>>>(s + r0 * ss, ss, nullptr, out, cols, descending, shift, hist, ntiles);
+      else radix_move_kernel<DT, false><<<tiles, kRadixThreads, 0, st>>>(s, ss, in, out, cols, descending, shift, hist, ntiles);
       count_launch();
+      count_launch();
+      count_launch();
+      in = out;
+      out = out == keys_a ? keys_b : keys_a;
     }
     sort_emit_kernel<DT><<<dim3(static_cast<unsigned>(ceil_div(cols, 256)), nr), 256, 0, st>>>(
-        s + r0 * ss, ss, keys, n, d ? d + r0 * vs : nullptr, vs, di ? di + r0 * is : nullptr, is, cols);
+        s + r0 * ss, ss, in, cols, d ? d + r0 * vs : nullptr, vs, di ? di + r0 * is : nullptr, is, cols, descending);
   }
   return BSIR_OK;
 }
@@ -284,7 +458,7 @@ extern "C" int32_t bsir_sort(int32_t dtype, int32_t descending, int64_t rows, in
   if (!aligned_to(src, eb) || !aligned_to(dst_value, eb) || !aligned_to(dst_index, 4)) return fail(BSIR_ERR_ALIGN, "sort: misaligned");
   cudaStream_t st = resolve_stream(stream);
   const int desc = descending != 0;
-  if (cols > kSortMaxLen) {   // keys in device scratch, the wide steps of the network on global memory
+  if (cols > kSortMaxLen) {   // keys in device scratch, radix passes
     int32_t rc;
     switch (dtype) {
       case BSIR_F32: rc = launch_sort_long<BSIR_F32>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;

@@ -424,6 +424,11 @@ def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters, only=None):
         rec("sort_f32_1024x8192", 1024 * 8192 * (4 + 4 + 4), lambda i: bsir.sort(xs[i % 2], descending=True),
             note="values + int32 indices; shared-memory bitonic network, not bandwidth-bound")
         del xs
+    if want("sort_f32_256x152064"):
+        xs = [torch.randn(256, 152064, device="cuda") for _ in range(2)]
+        rec("sort_f32_256x152064", 256 * 152064 * (4 + 4 + 4), lambda i: bsir.sort(xs[i % 2], descending=True),
+            note="values + int32 indices; four stable radix passes over keys in device scratch")
+        del xs
     for m in (16, 128, 4096):
         if not want(f"w8a8_m{m}"):
             continue

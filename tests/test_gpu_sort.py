@@ -76,17 +76,43 @@ def test_sort_limits_and_strides(bsir):
     assert torch.equal(idx.long(), torch.sort(view, dim=1, stable=True).indices)
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.int8, torch.int16, torch.int32])
 @pytest.mark.parametrize("rows,cols", [(2, 8193), (3, 20000), (5, 65536), (2, 152064)])
 @pytest.mark.parametrize("descending", [False, True])
 def test_sort_rows_longer_than_shared_memory(bsir, dtype, rows, cols, descending):
-    """Keys in device scratch, the wide steps of the network on global memory: the same rule, the same bits."""
+    """Keys in device scratch, sorted by stable radix passes: the same rule, the same bits."""
     g = torch.Generator(device="cuda").manual_seed(cols)
     if dtype.is_floating_point:
         x = (torch.randn(rows, cols, device="cuda", generator=g) * 8).round().div(4).to(dtype)
     else:
-        x = torch.randint(-3000, 3000, (rows, cols), device="cuda", generator=g).to(dtype)
+        hi = 100 if dtype == torch.int8 else 3000
+        x = torch.randint(-hi, hi, (rows, cols), device="cuda", generator=g).to(dtype)
     val, idx = bsir.sort(x, descending=descending)
     wv, wi = O.sort_last_axis(oracle_dtype(x), to_bits(x), descending=descending)
     assert np.array_equal(idx.cpu().numpy(), wi)
     assert np.array_equal(to_bits(val), wv)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.int32])
+def test_sort_long_rows_every_digit(bsir, dtype):
+    """Values that differ in every byte of the key (the whole range of the type, infinities, both zeros), rows that
+    do not fill their last tile, a strided source: every radix pass has work to do."""
+    g = torch.Generator(device="cuda").manual_seed(5)
+    rows, cols = 3, 70001
+    if dtype == torch.int32:
+        x = torch.randint(-2**31, 2**31 - 1, (rows, cols + 7), device="cuda", generator=g, dtype=torch.int64).to(torch.int32)
+    else:
+        bits = torch.randint(0, 2**16, (rows, cols + 7), device="cuda", generator=g)
+        if dtype == torch.float16:
+            x = bits.to(torch.int16).view(torch.float16)
+        else:
+            lo = torch.randint(0, 2**16, (rows, cols + 7), device="cuda", generator=g)
+            x = ((bits << 16) | lo).to(torch.int32).view(torch.float32)
+        x = torch.where(torch.isnan(x), torch.zeros_like(x), x)
+        x[:, 5] = float("inf"); x[:, 9] = float("-inf"); x[:, 11] = -0.0; x[:, 12] = 0.0
+    view = x[:, :cols]
+    for descending in (False, True):
+        val, idx = bsir.sort(view, descending=descending)
+        wv, wi = O.sort_last_axis(oracle_dtype(x), to_bits(view.contiguous()), descending=descending)
+        assert np.array_equal(idx.cpu().numpy(), wi)
+        assert np.array_equal(to_bits(val), wv)
