@@ -11,12 +11,13 @@
 // A row becomes 64-bit keys  order(value) << 32 | index  (order() maps the element type to unsigned integers
 // that compare like the values; descending complements it; NaN is the largest key in both directions), so one
 // integer comparison decides value and tie at once and the bitonic network -- not stable by itself -- gives a
-// stable result with the NaNs at the end in source order; the write-out then moves them to their places.  A CTA sorts one row in shared memory
-// (rows of up to 8192 elements: 64 KB of keys); longer rows keep their keys in device scratch and are sorted by
-// radix passes instead (below).  The values are read back from the source by index (the long-row path rebuilds
-// them from the key and reads back only zeros and NaNs), so their bits -- the sign of a zero, the payload of a
-// NaN -- are the source's.
+// stable result with the NaNs at the end in source order; the write-out then moves them to their places.  Short
+// rows (a few hundred elements) are sorted this way by one CTA in shared memory; longer ones by stable radix
+// passes on the same keys (below): in one CTA's shared memory up to 4096 elements, over device scratch beyond.
+// The values' bits are the source's -- the sign of a zero, the payload of a NaN: the network's write-out reads
+// them back by index; the radix paths rebuild them from the key and read back only zeros and NaNs.
 #include <cstdint>
+#include <cstdlib>
 
 #include "common.cuh"
 
@@ -166,6 +167,20 @@ __device__ __forceinline__ uint32_t radix_order(typename SortElem<DT>::type v, i
 }
 template <int DT> constexpr int kRadixFirstShift = (DT == BSIR_F32 || DT == BSIR_I32) ? 0 : DT == BSIR_I8 ? 24 : 16;
 
+// The lanes of the warp that hold the same digit as this one, among the lanes with `valid` set (the answer of a lane
+// without it means nothing).  Eight ballots, one per bit of the digit: the cost does not depend on how many
+// different digits the warp holds, which a match instruction's does.
+__device__ __forceinline__ uint32_t digit_peers(uint32_t digit, bool valid) {
+  uint32_t peers = __ballot_sync(0xffffffffu, valid);
+#pragma unroll
+  for (int b = 0; b < 8; ++b) {
+    const bool bit = (digit >> b) & 1u;
+    const uint32_t with_bit = __ballot_sync(0xffffffffu, bit);
+    peers &= bit ? with_bit : ~with_bit;
+  }
+  return peers;
+}
+
 template <int DT, bool FIRST>
 __device__ __forceinline__ unsigned long long radix_load(const typename SortElem<DT>::type *__restrict__ src_row,
                                                          const unsigned long long *__restrict__ keys_row, int64_t pos, int descending) {
@@ -178,10 +193,11 @@ template <int DT, bool FIRST>
 __global__ void __launch_bounds__(kRadixThreads) radix_count_kernel(const typename SortElem<DT>::type *__restrict__ src, int64_t src_stride,
                                                                     const unsigned long long *__restrict__ keys_in, int64_t cols, int descending,
                                                                     int shift, uint32_t *__restrict__ hist, int64_t ntiles) {
-  __shared__ uint32_t count[256];
-  const int tid = threadIdx.x, lane = tid & 31;
+  __shared__ uint32_t count[4][256];                          // four copies: fewer adds meet on one word when the digits are few
+  const int tid = threadIdx.x, warp = tid >> 5;
   const int64_t row = blockIdx.y, tile = blockIdx.x, base = tile * kRadixTile;
-  count[tid] = 0;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) count[c][tid] = 0;
   __syncthreads();
   const auto *src_row = src + row * src_stride;
   const unsigned long long *keys_row = keys_in + row * cols;
@@ -189,21 +205,49 @@ __global__ void __launch_bounds__(kRadixThreads) radix_count_kernel(const typena
   for (int i = 0; i < kRadixIters; ++i) {
     const int64_t pos = base + i * kRadixThreads + tid;
     const bool valid = pos < cols;
-    uint32_t digit = 256;                                     // lanes past the row's end match only one another
-    if (valid) digit = static_cast<uint32_t>(radix_load<DT, FIRST>(src_row, keys_row, pos, descending) >> (32 + shift)) & 255u;
-    const uint32_t peers = __match_any_sync(0xffffffffu, digit);
-    if (valid && (peers & ((1u << lane) - 1)) == 0) atomicAdd(&count[digit], __popc(peers));   // one add per distinct digit of the warp
+    if (valid) {
+      const uint32_t digit = static_cast<uint32_t>(radix_load<DT, FIRST>(src_row, keys_row, pos, descending) >> (32 + shift)) & 255u;
+      atomicAdd(&count[warp & 3][digit], 1u);
+    }
   }
   __syncthreads();
-  hist[(row * 256 + tid) * ntiles + tile] = count[tid];
+  hist[(row * 256 + tid) * ntiles + tile] = count[0][tid] + count[1][tid] + count[2][tid] + count[3][tid];
 }
 
 // hist[row] holds 256 x ntiles counts; in (digit, tile) order each becomes the sum of the ones before it
+constexpr int kRadixOffsetsTiles = 44;                         // rows of up to this many tiles take the counts into shared memory
 __global__ void __launch_bounds__(kRadixThreads) radix_offsets_kernel(uint32_t *__restrict__ hist, int64_t ntiles) {
   __shared__ uint32_t total[256];
   __shared__ uint32_t warp_sum[kRadixWarps];
+  __shared__ uint32_t staged[256 * kRadixOffsetsTiles];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   uint32_t *h = hist + static_cast<int64_t>(blockIdx.x) * 256 * ntiles;
+  if (ntiles <= kRadixOffsetsTiles) {
+    // one coalesced read, thread d walks digit d's tiles in shared memory, one coalesced write
+    const int nt = static_cast<int>(ntiles), entries = 256 * nt;
+    for (int e = tid; e < entries; e += kRadixThreads) staged[e] = h[e];
+    __syncthreads();
+    uint32_t mine = 0;
+    for (int t = 0; t < nt; ++t) mine += staged[tid * nt + t];
+    uint32_t incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    if (lane == 31) warp_sum[warp] = incl;
+    __syncthreads();
+    uint32_t running = incl - mine;
+    for (int w = 0; w < warp; ++w) running += warp_sum[w];
+    for (int t = 0; t < nt; ++t) {
+      const uint32_t c = staged[tid * nt + t];
+      staged[tid * nt + t] = running;
+      running += c;
+    }
+    __syncthreads();
+    for (int e = tid; e < entries; e += kRadixThreads) h[e] = staged[e];
+    return;
+  }
   for (int d = warp; d < 256; d += kRadixWarps) {
     uint32_t sum = 0;
     for (int64_t t = lane; t < ntiles; t += 32) sum += h[d * ntiles + t];
@@ -244,89 +288,110 @@ __global__ void __launch_bounds__(kRadixThreads) radix_offsets_kernel(uint32_t *
   }
 }
 
-// Moves the keys of one tile to their places of this pass.  A warp owns 512 consecutive keys and takes them 32 at
-// a time in order; within such a group a key's rank among the keys of its digit is the number of lower lanes with
-// that digit, and the warp's running count of the digit carries the rank from group to group -- source order is
-// kept.  The warps' counts are then chained, the tile is put in digit order in shared memory and written out from
-// there, so that the stores of a warp fall into a few runs of the row instead of 32 places.
-template <int DT, bool FIRST>
-__global__ void __launch_bounds__(kRadixThreads) radix_move_kernel(const typename SortElem<DT>::type *__restrict__ src, int64_t src_stride,
-                                                                   const unsigned long long *__restrict__ keys_in,
-                                                                   unsigned long long *__restrict__ keys_out, int64_t cols, int descending,
-                                                                   int shift, const uint32_t *__restrict__ hist, int64_t ntiles) {
-  __shared__ unsigned long long sorted[kRadixTile];
-  __shared__ uint32_t count[kRadixWarps][256];
-  __shared__ uint32_t to_row[256];
-  __shared__ uint32_t warp_sum[kRadixWarps];
+// One pass over one tile of 256 * ITERS keys (in registers; a warp owns 32 * ITERS consecutive keys and takes them
+// 32 at a time in order): the tile's keys end up in shared memory in the order of the digit at `shift`, source order
+// kept within a digit.  Within a group of 32 a key's rank among the keys of its digit is the number of lower lanes
+// with that digit, and the warp's running count of the digit carries the rank from group to group; the warps'
+// counts are then chained behind one another, digit by digit.  Returns, for digit threadIdx.x, where its keys start
+// in the tile.  `warp_valid` is how many of the warp's keys exist (the row may end inside the tile).
+template <int ITERS>
+struct RadixShared {
+  unsigned long long sorted[kRadixThreads * ITERS];
+  uint32_t count[kRadixWarps][256];
+  uint32_t warp_sum[kRadixWarps];
+};
+
+template <int ITERS>
+__device__ __forceinline__ uint32_t radix_tile_pass(RadixShared<ITERS> &sm, const unsigned long long (&key)[ITERS], int warp_valid, int shift) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int64_t row = blockIdx.y, tile = blockIdx.x;
-  const int64_t base = tile * kRadixTile + warp * (kRadixTile / kRadixWarps);
 #pragma unroll
-  for (int w = 0; w < kRadixWarps; ++w) count[w][tid] = 0;
-  __syncthreads();
-  const auto *src_row = src + row * src_stride;
-  const unsigned long long *keys_row = keys_in + row * cols;
-  unsigned long long key[kRadixIters];
-  uint32_t rank[kRadixIters];
+  for (int w = 0; w < kRadixWarps; ++w) sm.count[w][tid] = 0;
+  __syncthreads();                                            // also: every reader of sm.sorted from the pass before is done
+  uint32_t rank2[(ITERS + 1) / 2];                            // two 16-bit ranks a word
 #pragma unroll
-  for (int i = 0; i < kRadixIters; ++i) {
-    const int64_t pos = base + i * 32 + lane;
-    key[i] = pos < cols ? radix_load<DT, FIRST>(src_row, keys_row, pos, descending) : 0ull;
-  }
-#pragma unroll
-  for (int i = 0; i < kRadixIters; ++i) {
-    const bool valid = base + i * 32 + lane < cols;
-    const uint32_t digit = valid ? static_cast<uint32_t>(key[i] >> (32 + shift)) & 255u : 256u;
-    const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+  for (int i = 0; i < ITERS; ++i) {
+    const bool valid = i * 32 + lane < warp_valid;
+    const uint32_t digit = static_cast<uint32_t>(key[i] >> (32 + shift)) & 255u;
+    const uint32_t peers = digit_peers(digit, valid);
     const uint32_t below = __popc(peers & ((1u << lane) - 1));
     uint32_t before = 0;
-    if (valid) before = count[warp][digit];
+    if (valid) before = sm.count[warp][digit];
     __syncwarp();
-    if (valid && below == 0) count[warp][digit] = before + __popc(peers);
+    if (valid && below == 0) sm.count[warp][digit] = before + __popc(peers);
     __syncwarp();
-    rank[i] = before + below;
+    if (i & 1) rank2[i >> 1] |= (before + below) << 16;
+    else rank2[i >> 1] = before + below;
   }
   __syncthreads();
-  {   // digit tid: where the tile's keys of the digit start within the tile (digits in order), each warp's share
-      // behind that, and what turns a place in the tile into the place in the row
+  uint32_t start;
+  {
     uint32_t mine = 0;
 #pragma unroll
-    for (int w = 0; w < kRadixWarps; ++w) mine += count[w][tid];
+    for (int w = 0; w < kRadixWarps; ++w) mine += sm.count[w][tid];
     uint32_t incl = mine;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
       if (lane >= o) incl += up;
     }
-    if (lane == 31) warp_sum[warp] = incl;
+    if (lane == 31) sm.warp_sum[warp] = incl;
     __syncthreads();
-    uint32_t start = incl - mine;
-    for (int w = 0; w < warp; ++w) start += warp_sum[w];
-    to_row[tid] = hist[(row * 256 + tid) * ntiles + tile] - start;
+    start = incl - mine;
+    for (int w = 0; w < warp; ++w) start += sm.warp_sum[w];
     uint32_t running = start;
 #pragma unroll
     for (int w = 0; w < kRadixWarps; ++w) {
-      const uint32_t c = count[w][tid];
-      count[w][tid] = running;
+      const uint32_t c = sm.count[w][tid];
+      sm.count[w][tid] = running;
       running += c;
     }
   }
   __syncthreads();
 #pragma unroll
-  for (int i = 0; i < kRadixIters; ++i) {
-    if (base + i * 32 + lane < cols) {
+  for (int i = 0; i < ITERS; ++i) {
+    if (i * 32 + lane < warp_valid) {
       const uint32_t digit = static_cast<uint32_t>(key[i] >> (32 + shift)) & 255u;
-      sorted[count[warp][digit] + rank[i]] = key[i];
+      sm.sorted[sm.count[warp][digit] + ((rank2[i >> 1] >> (16 * (i & 1))) & 0xffffu)] = key[i];
     }
   }
   __syncthreads();
-  // the tile, now in digit order, goes out in runs: neighbouring threads write neighbouring places of the row
+  return start;
+}
+
+__device__ __forceinline__ int radix_warp_valid(int64_t cols, int64_t warp_base, int per_warp) {
+  const int64_t left = cols - warp_base;
+  return left <= 0 ? 0 : left < per_warp ? static_cast<int>(left) : per_warp;
+}
+
+// Moves the keys of one tile to their places of this pass: the tile, in digit order in shared memory, goes out in
+// runs, so that the stores of a warp fall into a few stretches of the row instead of 32 places.
+template <int DT, bool FIRST>
+__global__ void __launch_bounds__(kRadixThreads, 3) radix_move_kernel(const typename SortElem<DT>::type *__restrict__ src, int64_t src_stride,
+                                                                      const unsigned long long *__restrict__ keys_in,
+                                                                      unsigned long long *__restrict__ keys_out, int64_t cols, int descending,
+                                                                      int shift, const uint32_t *__restrict__ hist, int64_t ntiles) {
+  __shared__ RadixShared<kRadixIters> sm;
+  __shared__ uint32_t to_row[256];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t row = blockIdx.y, tile = blockIdx.x;
+  const int64_t base = tile * kRadixTile + warp * (kRadixTile / kRadixWarps);
+  const auto *src_row = src + row * src_stride;
+  const unsigned long long *keys_row = keys_in + row * cols;
+  unsigned long long key[kRadixIters];
+#pragma unroll
+  for (int i = 0; i < kRadixIters; ++i) {
+    const int64_t pos = base + i * 32 + lane;
+    key[i] = pos < cols ? radix_load<DT, FIRST>(src_row, keys_row, pos, descending) : 0ull;
+  }
+  const uint32_t start = radix_tile_pass<kRadixIters>(sm, key, radix_warp_valid(cols, base, kRadixTile / kRadixWarps), shift);
+  to_row[tid] = hist[(row * 256 + tid) * ntiles + tile] - start;   // turns a place in the tile into the place in the row
+  __syncthreads();
   const int64_t left = cols - tile * kRadixTile;
   const int in_tile = left < kRadixTile ? static_cast<int>(left) : kRadixTile;
   unsigned long long *out_row = keys_out + row * cols;
 #pragma unroll 4
   for (int j = tid; j < in_tile; j += kRadixThreads) {
-    const unsigned long long k = sorted[j];
+    const unsigned long long k = sm.sorted[j];
     const uint32_t digit = static_cast<uint32_t>(k >> (32 + shift)) & 255u;
     out_row[to_row[digit] + static_cast<uint32_t>(j)] = k;
   }
@@ -375,6 +440,65 @@ __global__ void __launch_bounds__(256) sort_emit_kernel(const typename SortElem<
     dst_value[row * val_stride + at] = v;
   }
   if (dst_index) dst_index[row * idx_stride + at] = static_cast<int32_t>(idx);
+}
+
+// Rows of up to 256 * ITERS elements: one CTA sorts a row with every pass in shared memory and writes values and
+// indices itself.
+template <int DT, int ITERS>
+__global__ void __launch_bounds__(kRadixThreads, ITERS > 8 ? 3 : 4) radix_rows_kernel(const typename SortElem<DT>::type *__restrict__ src,
+                                                                                        int64_t src_stride,
+                                                                                        typename SortElem<DT>::type *__restrict__ dst_value,
+                                                                                        int64_t val_stride, int32_t *__restrict__ dst_index,
+                                                                                        int64_t idx_stride, int cols, int descending) {
+  __shared__ RadixShared<ITERS> sm;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t row = blockIdx.x;
+  const auto *s = src + row * src_stride;
+  const int base = warp * 32 * ITERS;
+  const int warp_valid = radix_warp_valid(cols, base, 32 * ITERS);
+  unsigned long long key[ITERS];
+#pragma unroll
+  for (int i = 0; i < ITERS; ++i) {
+    const int pos = base + i * 32 + lane;
+    key[i] = pos < cols ? radix_load<DT, true>(s, nullptr, pos, descending) : 0ull;
+  }
+  for (int shift = kRadixFirstShift<DT>; shift < 32; shift += 8) {
+    radix_tile_pass<ITERS>(sm, key, warp_valid, shift);
+    if (shift < 24) {
+#pragma unroll
+      for (int i = 0; i < ITERS; ++i) {
+        const int pos = base + i * 32 + lane;
+        if (pos < cols) key[i] = sm.sorted[pos];
+      }
+    }
+  }
+  int64_t nan = 0;
+  if constexpr (kSortFloat<DT>) nan = sort_count_nan(sm.sorted, cols);
+  for (int i = tid; i < cols; i += kRadixThreads) {
+    const unsigned long long k = sm.sorted[i];
+    const uint32_t idx = static_cast<uint32_t>(k);
+    const int64_t at = nan ? sort_place(sm.sorted, i, cols, nan) : i;
+    if (dst_value) {
+      typename SortElem<DT>::type v;
+      if (!radix_value<DT>(static_cast<uint32_t>(k >> 32), descending, v)) v = s[idx];
+      dst_value[row * val_stride + at] = v;
+    }
+    if (dst_index) dst_index[row * idx_stride + at] = static_cast<int32_t>(idx);
+  }
+}
+
+template <int DT>
+void launch_radix_rows(const void *src, int64_t ss, void *dv, int64_t vs, int32_t *di, int64_t is, int64_t rows, int64_t cols, int descending,
+                       cudaStream_t st) {
+  using T = typename SortElem<DT>::type;
+  const T *s = static_cast<const T *>(src);
+  T *d = static_cast<T *>(dv);
+  const unsigned g = static_cast<unsigned>(rows);
+  const int n = static_cast<int>(cols);
+  if (cols <= kRadixThreads * 2) radix_rows_kernel<DT, 2><<<g, kRadixThreads, 0, st>>>(s, ss, d, vs, di, is, n, descending);
+  else if (cols <= kRadixThreads * 4) radix_rows_kernel<DT, 4><<<g, kRadixThreads, 0, st>>>(s, ss, d, vs, di, is, n, descending);
+  else if (cols <= kRadixThreads * 8) radix_rows_kernel<DT, 8><<<g, kRadixThreads, 0, st>>>(s, ss, d, vs, di, is, n, descending);
+  else radix_rows_kernel<DT, 16><<<g, kRadixThreads, 0, st>>>(s, ss, d, vs, di, is, n, descending);
 }
 
 // as many rows at a time as fit `budget` bytes of scratch (two copies of the keys and the digit counts)
@@ -458,28 +582,31 @@ extern "C" int32_t bsir_sort(int32_t dtype, int32_t descending, int64_t rows, in
   if (!aligned_to(src, eb) || !aligned_to(dst_value, eb) || !aligned_to(dst_index, 4)) return fail(BSIR_ERR_ALIGN, "sort: misaligned");
   cudaStream_t st = resolve_stream(stream);
   const int desc = descending != 0;
-  if (cols > kSortMaxLen) {   // keys in device scratch, radix passes
-    int32_t rc;
-    switch (dtype) {
-      case BSIR_F32: rc = launch_sort_long<BSIR_F32>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
-      case BSIR_F16: rc = launch_sort_long<BSIR_F16>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
-      case BSIR_BF16: rc = launch_sort_long<BSIR_BF16>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
-      case BSIR_I8: rc = launch_sort_long<BSIR_I8>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
-      case BSIR_I16: rc = launch_sort_long<BSIR_I16>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
-      default: rc = launch_sort_long<BSIR_I32>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
-    }
-    if (rc != BSIR_OK) return rc;
-    count_launch();
-    return check_launch("sort");
-  }
+  // Which of the three ways: rows above one tile of the radix sort (4096) keep their keys in device scratch and
+  // take the radix passes; rows of `radix_from` elements or more that fit a tile are radix-sorted by one CTA in
+  // shared memory; shorter rows by the bitonic network.
+  // (measured on [rows, cols] with rows * cols = 8M: the network wins up to 256 columns of 32-bit elements, 128 of 16-bit ones)
+  int64_t radix_from = eb == 4 ? 385 : eb == 2 ? 225 : 129;
+  if (const char *e = std::getenv("BSIR_SORT_RADIX_FROM")) { const long c = std::atol(e); if (c >= 2 && c <= kSortMaxLen) radix_from = c; }
+  const int way = cols > kSortMaxLen || (cols >= radix_from && cols > kRadixTile) ? 2 : cols >= radix_from ? 1 : 0;
+  int32_t rc = BSIR_OK;
+#define BSIR_SORT_CASE(DT)                                                                                                      \
+  case DT:                                                                                                                      \
+    if (way == 2) rc = launch_sort_long<DT>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); \
+    else if (way == 1) launch_radix_rows<DT>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); \
+    else launch_sort<DT>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st);  \
+    break;
   switch (dtype) {
-    case BSIR_F32: launch_sort<BSIR_F32>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
-    case BSIR_F16: launch_sort<BSIR_F16>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
-    case BSIR_BF16: launch_sort<BSIR_BF16>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
-    case BSIR_I8: launch_sort<BSIR_I8>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
-    case BSIR_I16: launch_sort<BSIR_I16>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
-    default: launch_sort<BSIR_I32>(src, src_row_stride, dst_value, value_row_stride, dst_index, index_row_stride, rows, cols, desc, st); break;
+    BSIR_SORT_CASE(BSIR_F32)
+    BSIR_SORT_CASE(BSIR_F16)
+    BSIR_SORT_CASE(BSIR_BF16)
+    BSIR_SORT_CASE(BSIR_I8)
+    BSIR_SORT_CASE(BSIR_I16)
+    default:
+    BSIR_SORT_CASE(BSIR_I32)
   }
+#undef BSIR_SORT_CASE
+  if (rc != BSIR_OK) return rc;
   count_launch();
   return check_launch("sort");
 }

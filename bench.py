@@ -422,7 +422,7 @@ def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters, only=None):
     if want("sort_f32_1024x8192"):
         xs = [torch.randn(1024, 8192, device="cuda") for _ in range(2)]
         rec("sort_f32_1024x8192", 1024 * 8192 * (4 + 4 + 4), lambda i: bsir.sort(xs[i % 2], descending=True),
-            note="values + int32 indices; shared-memory bitonic network, not bandwidth-bound")
+            note="values + int32 indices; four stable radix passes over keys in device scratch, two tiles a row")
         del xs
     if want("sort_f32_256x152064"):
         xs = [torch.randn(256, 152064, device="cuda") for _ in range(2)]

@@ -116,3 +116,24 @@ def test_sort_long_rows_every_digit(bsir, dtype):
         wv, wi = O.sort_last_axis(oracle_dtype(x), to_bits(view.contiguous()), descending=descending)
         assert np.array_equal(idx.cpu().numpy(), wi)
         assert np.array_equal(to_bits(val), wv)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.int8, torch.int16, torch.int32])
+@pytest.mark.parametrize("rows,cols", [(3, 2), (7, 33), (64, 100), (5, 512), (9, 513), (17, 1000), (3, 2048), (4, 2049), (5, 4096), (2, 5000)])
+@pytest.mark.parametrize("descending", [False, True])
+def test_sort_radix_in_one_cta(bsir, monkeypatch, dtype, rows, cols, descending):
+    """Every row length through the radix kernels (the switch moves the point from which they are used down to 2):
+    ties, NaNs at random places, both directions, the same bits as the reference's rule."""
+    monkeypatch.setenv("BSIR_SORT_RADIX_FROM", "2")
+    g = torch.Generator(device="cuda").manual_seed(rows * 77 + cols)
+    if dtype.is_floating_point:
+        x = (torch.randn(rows, cols, device="cuda", generator=g) * 4).round().div(2).to(dtype)
+        x[torch.rand(rows, cols, device="cuda", generator=g) < 0.02] = float("nan")
+        x[0, 0] = -0.0
+    else:
+        hi = 100 if dtype == torch.int8 else 3000
+        x = torch.randint(-hi, hi, (rows, cols), device="cuda", generator=g).to(dtype)
+    val, idx = bsir.sort(x, descending=descending)
+    wv, wi = O.sort_last_axis(oracle_dtype(x), to_bits(x), descending=descending)
+    assert np.array_equal(idx.cpu().numpy(), wi)
+    assert np.array_equal(to_bits(val).view(np.uint8), wv.view(np.uint8))         # bits: NaN is not equal to itself
