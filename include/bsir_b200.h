@@ -414,8 +414,9 @@ BSIR_API int32_t bsir_deinterleave(int32_t dtype, int32_t channels, int64_t rows
  * test/Dialect/HFusion/test_sort_2d_asc.mlir:16-19): equal values keep their source order, -0 = +0, and a NaN that
  * starts at position p of its row ends at (p + 1) mod n in either direction, the numbers filling the other places
  * in order.  dst_value or dst_index may be NULL.
- * dtype: f32, f16, bf16, i8, i16, i32.  Rows of up to 8192 elements are sorted in shared memory by one CTA; longer
- * rows (up to 2^30 elements) keep 8 bytes per padded element in the library's device scratch. */
+ * dtype: f32, f16, bf16, i8, i16, i32.  Rows of up to 4096 elements are sorted in shared memory by one CTA; longer
+ * rows (up to 2^30 elements) keep two copies of their 8-byte keys and 1 KB of digit counts per 4096 elements in the
+ * library's device scratch (about 16.3 bytes an element, at most 1 GiB at a time: more rows are sorted in turns). */
 BSIR_API int32_t bsir_sort(int32_t dtype, int32_t descending, int64_t rows, int64_t cols, const void *src,
                            int64_t src_row_stride, void *dst_value, int64_t value_row_stride, int32_t *dst_index,
                            int64_t index_row_stride, void *stream);
