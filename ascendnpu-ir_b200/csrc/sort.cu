@@ -149,44 +149,32 @@ constexpr int kRadixIters = kRadixTile / kRadixThreads;       // keys per thread
 // elements whose upper digits agree.  A NaN is 0xffffffff in both directions and no number maps there.
 template <int DT>
 __device__ __forceinline__ uint32_t radix_order(typename SortElem<DT>::type v, int descending) {
+  // selects, no branches: the loads of a thread's keys must not wait for one another behind a jump
   uint32_t o;
+  bool nan = false;
   if constexpr (DT == BSIR_I8) {
     o = (static_cast<uint32_t>(static_cast<uint8_t>(v)) ^ 0x80u) << 24;
   } else if constexpr (DT == BSIR_I16) {
     o = (static_cast<uint32_t>(static_cast<uint16_t>(v)) ^ 0x8000u) << 16;
+  } else if constexpr (DT == BSIR_I32) {
+    o = static_cast<uint32_t>(v) ^ 0x80000000u;
   } else if constexpr (DT == BSIR_F16) {
     uint32_t h = v;
-    if ((h & 0x7fffu) > 0x7c00u) return 0xffffffffu;
-    if (h == 0x8000u) h = 0u;                                 // -0 ties with +0
+    nan = (h & 0x7fffu) > 0x7c00u;
+    h = h == 0x8000u ? 0u : h;                                // -0 ties with +0
     o = ((h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u)) << 16;
   } else {
-    o = sort_order<DT>(v);                                    // bf16: the lower half follows from the sign bit
-    if (kSortFloat<DT> && o == 0xffffffffu) return o;
+    uint32_t b;
+    if constexpr (DT == BSIR_F32) b = __float_as_uint(v);
+    else b = static_cast<uint32_t>(v) << 16;                  // bf16: the lower half follows from the sign bit
+    nan = (b & 0x7fffffffu) > 0x7f800000u;
+    b = b == 0x80000000u ? 0u : b;
+    o = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
   }
-  return descending ? ~o : o;
+  o = descending ? ~o : o;
+  return nan ? 0xffffffffu : o;
 }
 template <int DT> constexpr int kRadixFirstShift = (DT == BSIR_F32 || DT == BSIR_I32) ? 0 : DT == BSIR_I8 ? 24 : 16;
-
-// The lanes of the warp that hold the same digit as this one, among the lanes with `valid` set (the answer of a lane
-// without it means nothing).  Eight ballots, one per bit of the digit: the cost does not depend on how many
-// different digits the warp holds, which a match instruction's does.
-__device__ __forceinline__ uint32_t digit_peers(uint32_t digit, bool valid) {
-  uint32_t peers = __ballot_sync(0xffffffffu, valid);
-#pragma unroll
-  for (int b = 0; b < 8; ++b) {
-    const bool bit = (digit >> b) & 1u;
-    const uint32_t with_bit = __ballot_sync(0xffffffffu, bit);
-    peers &= bit ? with_bit : ~with_bit;
-  }
-  return peers;
-}
-
-template <int DT, bool FIRST>
-__device__ __forceinline__ unsigned long long radix_load(const typename SortElem<DT>::type *__restrict__ src_row,
-                                                         const unsigned long long *__restrict__ keys_row, int64_t pos, int descending) {
-  if constexpr (FIRST) return (static_cast<unsigned long long>(radix_order<DT>(src_row[pos], descending)) << 32) | static_cast<uint32_t>(pos);
-  else return keys_row[pos];
-}
 
 // digit counts of one tile -> hist[row][digit][tile]
 template <int DT, bool FIRST>
@@ -201,15 +189,26 @@ __global__ void __launch_bounds__(kRadixThreads) radix_count_kernel(const typena
   __syncthreads();
   const auto *src_row = src + row * src_stride;
   const unsigned long long *keys_row = keys_in + row * cols;
-#pragma unroll 4
-  for (int i = 0; i < kRadixIters; ++i) {
-    const int64_t pos = base + i * kRadixThreads + tid;
-    const bool valid = pos < cols;
-    if (valid) {
-      const uint32_t digit = static_cast<uint32_t>(radix_load<DT, FIRST>(src_row, keys_row, pos, descending) >> (32 + shift)) & 255u;
-      atomicAdd(&count[warp & 3][digit], 1u);
+  uint32_t order[kRadixIters];
+  if constexpr (FIRST) {
+    typename SortElem<DT>::type raw[kRadixIters];
+#pragma unroll
+    for (int i = 0; i < kRadixIters; ++i) {
+      const int64_t pos = base + i * kRadixThreads + tid;
+      raw[i] = src_row[pos < cols ? pos : 0];
+    }
+#pragma unroll
+    for (int i = 0; i < kRadixIters; ++i) order[i] = radix_order<DT>(raw[i], descending);
+  } else {
+#pragma unroll
+    for (int i = 0; i < kRadixIters; ++i) {
+      const int64_t pos = base + i * kRadixThreads + tid;
+      order[i] = static_cast<uint32_t>(keys_row[pos < cols ? pos : 0] >> 32);
     }
   }
+#pragma unroll
+  for (int i = 0; i < kRadixIters; ++i)
+    if (base + i * kRadixThreads + tid < cols) atomicAdd(&count[warp & 3][(order[i] >> shift) & 255u], 1u);
   __syncthreads();
   hist[(row * 256 + tid) * ntiles + tile] = count[0][tid] + count[1][tid] + count[2][tid] + count[3][tid];
 }
@@ -291,13 +290,14 @@ __global__ void __launch_bounds__(kRadixThreads) radix_offsets_kernel(uint32_t *
 // One pass over one tile of 256 * ITERS keys (in registers; a warp owns 32 * ITERS consecutive keys and takes them
 // 32 at a time in order): the tile's keys end up in shared memory in the order of the digit at `shift`, source order
 // kept within a digit.  Within a group of 32 a key's rank among the keys of its digit is the number of lower lanes
-// with that digit, and the warp's running count of the digit carries the rank from group to group; the warps'
+// with that digit (the lanes of a digit meet in a word of shared memory, each setting its bit), and the warp's running count of the digit carries the rank from group to group; the warps'
 // counts are then chained behind one another, digit by digit.  Returns, for digit threadIdx.x, where its keys start
 // in the tile.  `warp_valid` is how many of the warp's keys exist (the row may end inside the tile).
 template <int ITERS>
 struct RadixShared {
   unsigned long long sorted[kRadixThreads * ITERS];
-  uint32_t count[kRadixWarps][256];
+  uint32_t lanes[kRadixWarps][256];                            // per warp and digit: the lanes holding it in the current group
+  uint16_t count[kRadixWarps][256];                            // at most 4096 keys a tile
   uint32_t warp_sum[kRadixWarps];
 };
 
@@ -305,19 +305,31 @@ template <int ITERS>
 __device__ __forceinline__ uint32_t radix_tile_pass(RadixShared<ITERS> &sm, const unsigned long long (&key)[ITERS], int warp_valid, int shift) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 #pragma unroll
-  for (int w = 0; w < kRadixWarps; ++w) sm.count[w][tid] = 0;
+  for (int w = 0; w < kRadixWarps; ++w) {
+    sm.count[w][tid] = 0;
+    sm.lanes[w][tid] = 0;
+  }
   __syncthreads();                                            // also: every reader of sm.sorted from the pass before is done
   uint32_t rank2[(ITERS + 1) / 2];                            // two 16-bit ranks a word
 #pragma unroll
   for (int i = 0; i < ITERS; ++i) {
+    // The lanes with this key's digit, found by each lane setting its bit in the digit's word: one shared-memory
+    // operation a key where eight ballots would take some forty instructions a group.
     const bool valid = i * 32 + lane < warp_valid;
     const uint32_t digit = static_cast<uint32_t>(key[i] >> (32 + shift)) & 255u;
-    const uint32_t peers = digit_peers(digit, valid);
-    const uint32_t below = __popc(peers & ((1u << lane) - 1));
-    uint32_t before = 0;
-    if (valid) before = sm.count[warp][digit];
+    if (valid) atomicOr(&sm.lanes[warp][digit], 1u << lane);
     __syncwarp();
-    if (valid && below == 0) sm.count[warp][digit] = before + __popc(peers);
+    uint32_t peers = 0, before = 0;
+    if (valid) {
+      peers = sm.lanes[warp][digit];
+      before = sm.count[warp][digit];
+    }
+    __syncwarp();
+    const uint32_t below = __popc(peers & ((1u << lane) - 1));
+    if (valid && below == 0) {
+      sm.count[warp][digit] = static_cast<uint16_t>(before + __popc(peers));
+      sm.lanes[warp][digit] = 0;
+    }
     __syncwarp();
     if (i & 1) rank2[i >> 1] |= (before + below) << 16;
     else rank2[i >> 1] = before + below;
@@ -342,7 +354,7 @@ __device__ __forceinline__ uint32_t radix_tile_pass(RadixShared<ITERS> &sm, cons
 #pragma unroll
     for (int w = 0; w < kRadixWarps; ++w) {
       const uint32_t c = sm.count[w][tid];
-      sm.count[w][tid] = running;
+      sm.count[w][tid] = static_cast<uint16_t>(running);
       running += c;
     }
   }
@@ -378,10 +390,22 @@ __global__ void __launch_bounds__(kRadixThreads, 3) radix_move_kernel(const type
   const auto *src_row = src + row * src_stride;
   const unsigned long long *keys_row = keys_in + row * cols;
   unsigned long long key[kRadixIters];
+  if constexpr (FIRST) {   // every load first, the keys from them afterwards
+    typename SortElem<DT>::type raw[kRadixIters];
 #pragma unroll
-  for (int i = 0; i < kRadixIters; ++i) {
-    const int64_t pos = base + i * 32 + lane;
-    key[i] = pos < cols ? radix_load<DT, FIRST>(src_row, keys_row, pos, descending) : 0ull;
+    for (int i = 0; i < kRadixIters; ++i) {
+      const int64_t pos = base + i * 32 + lane;
+      raw[i] = src_row[pos < cols ? pos : 0];
+    }
+#pragma unroll
+    for (int i = 0; i < kRadixIters; ++i)
+      key[i] = (static_cast<unsigned long long>(radix_order<DT>(raw[i], descending)) << 32) | static_cast<uint32_t>(base + i * 32 + lane);
+  } else {
+#pragma unroll
+    for (int i = 0; i < kRadixIters; ++i) {
+      const int64_t pos = base + i * 32 + lane;
+      key[i] = keys_row[pos < cols ? pos : 0];
+    }
   }
   const uint32_t start = radix_tile_pass<kRadixIters>(sm, key, radix_warp_valid(cols, base, kRadixTile / kRadixWarps), shift);
   to_row[tid] = hist[(row * 256 + tid) * ntiles + tile] - start;   // turns a place in the tile into the place in the row
@@ -457,10 +481,16 @@ __global__ void __launch_bounds__(kRadixThreads, ITERS > 8 ? 3 : 4) radix_rows_k
   const int base = warp * 32 * ITERS;
   const int warp_valid = radix_warp_valid(cols, base, 32 * ITERS);
   unsigned long long key[ITERS];
+  {   // every load first, the keys from them afterwards
+    typename SortElem<DT>::type raw[ITERS];
 #pragma unroll
-  for (int i = 0; i < ITERS; ++i) {
-    const int pos = base + i * 32 + lane;
-    key[i] = pos < cols ? radix_load<DT, true>(s, nullptr, pos, descending) : 0ull;
+    for (int i = 0; i < ITERS; ++i) {
+      const int pos = base + i * 32 + lane;
+      raw[i] = s[pos < cols ? pos : 0];
+    }
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i)
+      key[i] = (static_cast<unsigned long long>(radix_order<DT>(raw[i], descending)) << 32) | static_cast<uint32_t>(base + i * 32 + lane);
   }
   for (int shift = kRadixFirstShift<DT>; shift < 32; shift += 8) {
     radix_tile_pass<ITERS>(sm, key, warp_valid, shift);
