@@ -150,7 +150,7 @@ def test_row_kernels_stay_inside_their_outputs(bsir, rows, cols):
     c.check(f"reduce first axis ({rows},{cols})")
 
 
-@pytest.mark.parametrize("rows,cols", [(3, 2), (64, 100), (5, 8193), (2, 40000)])
+@pytest.mark.parametrize("rows,cols", [(3, 2), (64, 100), (7, 1000), (2, 2049), (3, 4096), (5, 8193), (2, 40000)])
 def test_sort_cumulative_transpose_stay_inside(bsir, rows, cols):
     x = torch.randn(rows, cols, device="cuda")
     sv, si = Guarded((rows, cols), torch.float32), Guarded((rows, cols), torch.int32)

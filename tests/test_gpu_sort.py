@@ -77,7 +77,7 @@ def test_sort_limits_and_strides(bsir):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16, torch.int8, torch.int16, torch.int32])
-@pytest.mark.parametrize("rows,cols", [(2, 8193), (3, 20000), (5, 65536), (2, 152064)])
+@pytest.mark.parametrize("rows,cols", [(2, 8193), (3, 20000), (5, 65536), (2, 152064), (2, 200001)])
 @pytest.mark.parametrize("descending", [False, True])
 def test_sort_rows_longer_than_shared_memory(bsir, dtype, rows, cols, descending):
     """Keys in device scratch, sorted by stable radix passes: the same rule, the same bits."""
