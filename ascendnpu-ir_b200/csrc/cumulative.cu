@@ -9,14 +9,16 @@
 // and the parallelism is across the other axis:
 //   * axis 0: a thread owns a column (or the 16 bytes of columns of one vector) and walks down the rows,
 //     loads of the next rows in flight while it adds;
-//   * axis 1: a warp owns 32 rows; it brings a 32 x 128-byte tile into shared memory with coalesced
-//     16-byte cp.async copies (a ring of four tiles in flight per warp), every lane scans its own row of the tile 16 bytes
-//     at a time (row pitch 36 words: conflict-free 16-byte accesses), and the tile goes back with coalesced 16-byte stores.
+//   * axis 1: a warp owns 32 rows and every lane scans its own row of a 32-row x 128-byte tile in shared memory,
+//     16 bytes at a time.  The tiles come and go through the copy engine (a tensor map over the rows as bytes,
+//     128-byte swizzle); without a tensor-map encoder, with coalesced 16-byte cp.async copies into tiles of row
+//     pitch 36 words (conflict-free 16-byte accesses) and coalesced 16-byte stores, a ring of six tiles per warp.
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 #include <type_traits>
 
-#include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace bsir {
 namespace {
@@ -89,7 +91,7 @@ __global__ void __launch_bounds__(64) cum_first_seq_kernel(const T *__restrict__
 }
 
 // ------------------------------------------------------------------ axis 1: a warp per 32 rows, tiles of 128 bytes
-constexpr int kCumWarps = 2;   // two warps x four tiles of 4.5 KB: 36 KB of static shared memory
+constexpr int kCumWarps = 1;   // one warp x six tiles of 4.5 KB: 27 KB of static shared memory (the path without tensor maps)
 // words per tile row in shared memory: 36, so that every row starts on a 16-byte boundary and the rows of the
 // eight lanes that share a 16-byte access phase start in different banks (lane * 36 mod 32 = 4 * lane)
 constexpr int kCumPitch = 36;
@@ -100,7 +102,7 @@ __global__ void __launch_bounds__(kCumWarps * 32) cum_last_kernel(const T *__res
   using A = typename CumAcc<T>::type;
   constexpr int EPT = 128 / sizeof(T);              // elements of a tile row
   constexpr int EPV = 16 / sizeof(T);               // elements of a 16-byte chunk
-  constexpr int kDepth = 4;                          // tiles in flight per warp (cp.async ring)
+  constexpr int kDepth = 6;                          // tiles in flight per warp (cp.async ring)
   __shared__ __align__(16) uint32_t sm[kCumWarps][kDepth][32 * kCumPitch];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t row0 = (static_cast<int64_t>(blockIdx.x) * kCumWarps + warp) * 32;
@@ -171,6 +173,106 @@ __global__ void __launch_bounds__(kCumWarps * 32) cum_last_kernel(const T *__res
   }
 }
 
+// The same walk with the tiles moved by the copy engine: a 2-D tensor map over the rows as bytes (box 32 rows x 128
+// bytes, 128-byte swizzle, so that the 32 lanes' 16-byte accesses to their own rows fall into different banks) brings
+// a tile with one instruction and takes it back with another, which leaves the warp's instruction stream to the
+// scan itself -- with one lane a row and two warps a scheduler at best, every instruction it does not issue counts.
+// A ring of `depth` steps per warp (as many as the warps that share an SM leave room for); the load that refills a
+// buffer is issued a scan after the store that emptied it.  Rows past the end read as zero and are not written.
+constexpr int kCumTmaMaxDepth = 11;                  // 44 KB of tiles: within the shared memory a kernel gets unasked
+constexpr int kCumTileBytes = 32 * 128;
+
+template <typename T, int KIND, bool NANP, int W>
+__global__ void __launch_bounds__(32) cum_last_tma_kernel(const __grid_constant__ CUtensorMap tsrc, const __grid_constant__ CUtensorMap tdst,
+                                                          int64_t cols, int reverse, int depth, int *err) {
+  // a step is W neighbouring tiles of a row block (W x 128 bytes of each row), fetched together: the wider the
+  // stretch of a row that is asked for at once, the fewer times DRAM opens a page for 128 bytes
+  using A = typename CumAcc<T>::type;
+  constexpr int EPV = 16 / sizeof(T);               // elements of a 16-byte chunk
+  constexpr int kStepBytes = W * kCumTileBytes;
+  extern __shared__ __align__(1024) uint8_t tiles[];   // depth steps
+  __shared__ __align__(8) uint64_t full[kCumTmaMaxDepth];
+  __shared__ int abort_flag;
+  const int lane = threadIdx.x;
+  const int row0 = static_cast<int>(blockIdx.x) * 32;
+  const int64_t ntiles = cols * static_cast<int64_t>(sizeof(T)) / 128;
+  const int64_t nsteps = (ntiles + W - 1) / W;
+  if (lane == 0) {
+#pragma unroll
+    for (int b = 0; b < kCumTmaMaxDepth; ++b) mbar_init(smem_u32(&full[b]), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tsrc);
+    prefetch_tmap(&tdst);
+  }
+  __syncwarp();
+  auto fetch = [&](int64_t it) {                      // lane 0 only
+    if (it < nsteps) {
+      const int64_t s = reverse ? nsteps - 1 - it : it;
+      const int b = static_cast<int>(it % depth);
+      const int nb = static_cast<int>(ntiles - s * W < W ? ntiles - s * W : W);
+      mbar_expect_tx(smem_u32(&full[b]), static_cast<uint32_t>(nb) * kCumTileBytes);
+      for (int j = 0; j < nb; ++j)
+        tma_load_2d(smem_u32(tiles + b * kStepBytes + j * kCumTileBytes), &tsrc, static_cast<int>((s * W + j) * 128), row0, smem_u32(&full[b]));
+    }
+  };
+  if (lane == 0)
+    for (int64_t it = 0; it < depth - 1; ++it) fetch(it);
+  A acc{};
+  for (int64_t it = 0; it < nsteps; ++it) {
+    const int64_t s = reverse ? nsteps - 1 - it : it;
+    const int b = static_cast<int>(it % depth);
+    const int nb = static_cast<int>(ntiles - s * W < W ? ntiles - s * W : W);
+    if (!mbar_wait(smem_u32(&full[b]), static_cast<uint32_t>(it / depth) & 1u, &abort_flag, err)) break;
+#pragma unroll
+    for (int jj = 0; jj < W; ++jj) {
+      if (jj < nb) {
+        const int j = reverse ? nb - 1 - jj : jj;
+        // lane = row: chunk c of the row sits at c ^ (row % 8) within the row's 128 bytes
+        uint4 *mine = reinterpret_cast<uint4 *>(tiles + b * kStepBytes + j * kCumTileBytes + lane * 128);
+        uint4 raw[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) raw[c] = mine[c ^ (lane & 7)];
+        auto scan = [&](auto rev_tag) {               // the direction is a compile-time constant inside
+          constexpr bool REV = decltype(rev_tag)::value;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const int cc = REV ? 7 - c : c;
+            T x[EPV];
+            memcpy(x, &raw[cc], 16);
+#pragma unroll
+            for (int e = 0; e < EPV; ++e) {
+              const int k = REV ? EPV - 1 - e : e;
+              acc = cum_step<T, KIND, NANP>(acc, x[k], it == 0 && jj == 0 && c == 0 && e == 0);
+              x[k] = cum_narrow<T>(acc);
+            }
+            memcpy(&raw[cc], x, 16);
+          }
+        };
+        if (reverse) scan(std::true_type{});
+        else scan(std::false_type{});
+#pragma unroll
+        for (int c = 0; c < 8; ++c) mine[c ^ (lane & 7)] = raw[c];
+      }
+    }
+    if (lane == 0) {
+      // the buffer of step it + depth - 1 went out one step ago, a whole scan back: its store has read it by now
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      fetch(it + depth - 1);
+    }
+    fence_proxy_async();                              // the lanes' writes, before the copy engine reads them
+    __syncwarp();
+    if (lane == 0) {
+      for (int j = 0; j < nb; ++j)
+        asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(reinterpret_cast<uint64_t>(&tdst)),
+                     "r"(static_cast<int>((s * W + j) * 128)), "r"(row0), "r"(smem_u32(tiles + b * kStepBytes + j * kCumTileBytes))
+                     : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  }
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 // generality path for axis 1: a thread per row (ragged or unaligned rows)
 template <typename T, int KIND, bool NANP>
 __global__ void __launch_bounds__(128) cum_last_seq_kernel(const T *__restrict__ src, T *__restrict__ dst, int64_t rows, int64_t cols,
@@ -197,6 +299,26 @@ void launch_cum(int axis, int reverse, int64_t rows, int64_t cols, const void *s
   }
   constexpr int64_t ept = 128 / sizeof(T);
   const bool tiles = cols % ept == 0 && aligned_to(src, 16) && aligned_to(dst, 16) && (ss * sizeof(T)) % 16 == 0 && (ds * sizeof(T)) % 16 == 0;
+  if (tiles && rows <= 0x7fffffffLL && cols * static_cast<int64_t>(sizeof(T)) <= 0x7fffffffLL && std::getenv("BSIR_CUM_NO_TMA") == nullptr) {
+    CUtensorMap tsrc, tdst;
+    if (make_byte_tmap(&tsrc, src, static_cast<uint64_t>(cols) * sizeof(T), static_cast<uint64_t>(rows), static_cast<uint64_t>(ss) * sizeof(T), 32) &&
+        make_byte_tmap(&tdst, dst, static_cast<uint64_t>(cols) * sizeof(T), static_cast<uint64_t>(rows), static_cast<uint64_t>(ds) * sizeof(T), 32)) {
+      // the ring as deep as the warps that will share an SM leave room for (about 200 KB among them)
+      const int64_t blocks = ceil_div(rows, static_cast<int64_t>(32));
+      const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
+      int64_t per_sm = ceil_div(blocks, static_cast<int64_t>(sms));
+      if (per_sm > 16) per_sm = 16;
+      const int room = static_cast<int>((200 * 1024 / per_sm - 1024) / kCumTileBytes);      // tiles a warp may hold
+      int wide = room >= 6 ? 2 : 1;
+      if (const char *e = std::getenv("BSIR_CUM_WIDE")) wide = std::atoi(e) == 2 ? 2 : 1;
+      int depth = room / wide;
+      depth = depth < 2 ? 2 : depth * wide > kCumTmaMaxDepth ? kCumTmaMaxDepth / wide : depth;
+      const size_t smem = static_cast<size_t>(depth) * wide * kCumTileBytes;
+      if (wide == 2) cum_last_tma_kernel<T, KIND, NANP, 2><<<static_cast<unsigned>(blocks), 32, smem, st>>>(tsrc, tdst, cols, reverse, depth, device_error_word());
+      else cum_last_tma_kernel<T, KIND, NANP, 1><<<static_cast<unsigned>(blocks), 32, smem, st>>>(tsrc, tdst, cols, reverse, depth, device_error_word());
+      return;
+    }
+  }
   if (tiles) cum_last_kernel<T, KIND, NANP><<<static_cast<unsigned>(ceil_div(rows, 32 * kCumWarps)), kCumWarps * 32, 0, st>>>(s, d, rows, cols, ss, ds, reverse);
   else cum_last_seq_kernel<T, KIND, NANP><<<static_cast<unsigned>(ceil_div(rows, 128)), 128, 0, st>>>(s, d, rows, cols, ss, ds, reverse);
 }

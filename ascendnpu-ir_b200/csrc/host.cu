@@ -9,6 +9,8 @@
 // up by name and receives one bare device pointer per memref argument, inputs
 // first, outputs last, exactly like a kernel compiled with static shapes
 // (enable-static-bare-ptr, bishengir/include/bishengir/Tools/bishengir-compile/Options.td:149-156).
+#include <cuda.h>
+
 #include <atomic>
 #include <map>
 #include <mutex>
@@ -123,6 +125,29 @@ void *device_workspace(size_t bytes, cudaStream_t stream) {
   b.bytes = want;
   p->last = b;
   return q;
+}
+
+bool make_byte_tmap(CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t outer, uint64_t pitch, uint32_t box_rows) {
+  using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn enc = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      enc = reinterpret_cast<EncodeFn>(sym);
+    else
+      cudaGetLastError();
+  });
+  if (!enc) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch};
+  cuuint32_t box[2] = {128u, box_rows};
+  cuuint32_t estr[2] = {1u, 1u};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 int *device_error_word() {

@@ -56,6 +56,23 @@ def test_cumulative_nan_modes_and_strided_rows(bsir):
     assert out_big[:, 256:].abs().sum().item() == 0
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int8])
+@pytest.mark.parametrize("reverse", [False, True])
+def test_row_scan_with_many_rows_and_without_tensor_maps(bsir, monkeypatch, dtype, reverse):
+    """So many rows that ten warps share an SM (the ring of tiles per warp is then short and one tile wide), and the
+    same problem through the kernel that copies its tiles without a tensor map."""
+    rows, cols = 48000, 384
+    x = _data((rows, cols), dtype, 11)
+    want = O.cumulative("sum", oracle_dtype(x), to_bits(x), axis=1, reverse=reverse)
+    assert_bits_equal(bsir.cumulative("sum", x, dim=1, reverse=reverse), want, f"cumsum {dtype} many rows")
+    monkeypatch.setenv("BSIR_CUM_NO_TMA", "1")
+    assert_bits_equal(bsir.cumulative("sum", x, dim=1, reverse=reverse), want, f"cumsum {dtype} many rows, no tensor map")
+    monkeypatch.delenv("BSIR_CUM_NO_TMA")
+    monkeypatch.setenv("BSIR_CUM_WIDE", "1")
+    y = bsir.cumulative("sum", x[:200].contiguous(), dim=1, reverse=reverse)
+    assert_bits_equal(y, want[:200], f"cumsum {dtype} one tile a step")
+
+
 def test_cumulative_config_shape_and_validation(bsir):
     """A decode-time top-p shape: many rows, sorted probabilities along the row."""
     p = torch.softmax(torch.randn(2048, 4096, device="cuda"), dim=1).sort(dim=1, descending=True).values.contiguous()
