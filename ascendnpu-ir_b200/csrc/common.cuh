@@ -43,9 +43,11 @@ void *device_workspace(size_t bytes, cudaStream_t stream);
 // bounded wait gives up.
 int *device_error_word();
 // 2-D tensor map over bytes: `inner` contiguous bytes a row, `outer` rows `pitch` bytes apart, box = box_rows x 128
-// bytes with the 128-byte swizzle; bytes outside read as zero and are not written.  The base must be 16-byte
-// aligned and the pitch a multiple of 16.  False when the driver has no encoder or refuses the shape.
-bool make_byte_tmap(::CUtensorMap_st *map, const void *ptr, uint64_t inner, uint64_t outer, uint64_t pitch, uint32_t box_rows);
+// bytes, with the 128-byte swizzle unless `swizzle` is false; bytes outside read as zero and are not written.  The
+// base must be 16-byte aligned and the pitch a multiple of 16.  False when the driver has no encoder or refuses the
+// shape.
+bool make_byte_tmap(::CUtensorMap_st *map, const void *ptr, uint64_t inner, uint64_t outer, uint64_t pitch, uint32_t box_rows,
+                    bool swizzle = true);
 // The first kScratchCounterBytes of any scratch block hold self-resetting counters only (one
 // uint32 per row of a launch, at most 65535 rows); everything else starts after them.
 constexpr size_t kScratchCounterBytes = 256 * 1024;

@@ -7,8 +7,9 @@
 // lib/Dialect/HIVM/Transforms/regbase/Normalize/NormalizeTypeConversion.cpp:714-745,818-822); integers
 // wrap in their own width.  Float sums are not associative, so the scan along the axis stays sequential
 // and the parallelism is across the other axis:
-//   * axis 0: a thread owns a column (or the 16 bytes of columns of one vector) and walks down the rows,
-//     loads of the next rows in flight while it adds;
+//   * axis 0: a warp owns 128 bytes of columns and walks down the rows through tiles the copy engine brings and
+//     takes back (without a tensor-map encoder, or for short or unaligned problems: a thread per column, the loads
+//     of the next 16 rows in flight while it adds);
 //   * axis 1: a warp owns 32 rows and every lane scans its own row of a 32-row x 128-byte tile in shared memory,
 //     16 bytes at a time.  The tiles come and go through the copy engine (a tensor map over the rows as bytes,
 //     128-byte swizzle); without a tensor-map encoder, with coalesced 16-byte cp.async copies into tiles of row
@@ -88,6 +89,132 @@ __global__ void __launch_bounds__(64) cum_first_seq_kernel(const T *__restrict__
       dst[(reverse ? rows - 1 - r : r) * ds + c] = cum_narrow<T>(acc);
     }
   }
+}
+
+// The same walk down the rows with the copy engine doing the memory side: a warp owns 128 bytes of columns (a lane
+// the 4-byte word of one, two or four of them) and gets tiles of 64 or 128 rows x 128 bytes through a 2-D tensor map over the
+// rows as bytes, scans them in place in shared memory and hands them back the same way.  What the thread-per-column
+// kernel can keep in flight is what fits its registers (16 rows); here it is the ring of tiles -- up to
+// 192 KB an SM -- which is what a column-wise walk over rows 16 KB apart needs to keep HBM busy.
+constexpr int kCumColMaxDepth = 24;                  // 192 KB of 64-row tiles
+
+// A whole tile that is not the first of its columns: every offset is a constant, so a row costs its load,
+// its adds and its store -- with one warp on its scheduler each instruction waits for the one before, and every
+// instruction saved shows.
+template <typename T, int KIND, bool NANP, bool REV, int kCumColRows>
+__device__ __forceinline__ void cum_col_full_tile(uint32_t *col, typename CumAcc<T>::type (&acc)[4 / sizeof(T)]) {
+  constexpr int EPW = 4 / sizeof(T);
+  constexpr int kGroups = kCumColRows / 8;
+  auto at = [](int q) { return (REV ? kCumColRows - 1 - q : q) * 32; };
+  uint32_t w[2][8];                                   // the next eight rows are loaded while these eight are added
+#pragma unroll
+  for (int k = 0; k < 8; ++k) w[0][k] = col[at(k)];
+#pragma unroll
+  for (int g = 0; g < kGroups; ++g) {
+    if (g + 1 < kGroups) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) w[(g + 1) & 1][k] = col[at((g + 1) * 8 + k)];
+    }
+    uint32_t out[8];                                  // the chain of adds first, its eight stores after it
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      T x[EPW];
+      memcpy(x, &w[g & 1][k], 4);
+#pragma unroll
+      for (int e = 0; e < EPW; ++e) {
+        acc[e] = cum_step<T, KIND, NANP>(acc[e], x[e], false);
+        x[e] = cum_narrow<T>(acc[e]);
+      }
+      memcpy(&out[k], x, 4);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) col[at(g * 8 + k)] = out[k];
+  }
+}
+
+template <typename T, int KIND, bool NANP, int kCumColRows>
+__global__ void __launch_bounds__(32) cum_first_tma_kernel(const __grid_constant__ CUtensorMap tsrc, const __grid_constant__ CUtensorMap tdst,
+                                                           int64_t rows, int reverse, int depth, int *err) {
+  using A = typename CumAcc<T>::type;
+  constexpr int EPW = 4 / sizeof(T);                 // columns in a lane's word
+  constexpr int kCumColTileBytes = kCumColRows * 128;
+  extern __shared__ __align__(1024) uint8_t tiles[];   // depth tiles
+  __shared__ __align__(8) uint64_t full[kCumColMaxDepth];
+  __shared__ int abort_flag;
+  const int lane = threadIdx.x;
+  const int x0 = static_cast<int>(blockIdx.x) * 128;
+  const int64_t ntiles = (rows + kCumColRows - 1) / kCumColRows;
+  if (lane == 0) {
+    for (int b = 0; b < kCumColMaxDepth; ++b) mbar_init(smem_u32(&full[b]), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    prefetch_tmap(&tsrc);
+    prefetch_tmap(&tdst);
+  }
+  __syncwarp();
+  auto fetch = [&](int64_t it) {                      // lane 0 only
+    if (it < ntiles) {
+      const int64_t s = reverse ? ntiles - 1 - it : it;
+      const int b = static_cast<int>(it % depth);
+      mbar_expect_tx(smem_u32(&full[b]), kCumColTileBytes);
+      tma_load_2d(smem_u32(tiles + b * kCumColTileBytes), &tsrc, x0, static_cast<int>(s * kCumColRows), smem_u32(&full[b]));
+    }
+  };
+  if (lane == 0)
+    for (int64_t it = 0; it < depth - 2; ++it) fetch(it);
+  A acc[EPW];
+#pragma unroll
+  for (int e = 0; e < EPW; ++e) acc[e] = A{};
+  for (int64_t it = 0; it < ntiles; ++it) {
+    const int64_t s = reverse ? ntiles - 1 - it : it;
+    const int b = static_cast<int>(it % depth);
+    const int64_t left = rows - s * kCumColRows;
+    const int nv = left < kCumColRows ? static_cast<int>(left) : kCumColRows;       // rows of this tile that exist
+    if (!mbar_wait(smem_u32(&full[b]), static_cast<uint32_t>(it / depth) & 1u, &abort_flag, err)) break;
+    uint32_t *col = reinterpret_cast<uint32_t *>(tiles + b * kCumColTileBytes) + lane;   // 32 words a row
+    if (it > 0 && nv == kCumColRows) {
+      if (reverse) cum_col_full_tile<T, KIND, NANP, true, kCumColRows>(col, acc);
+      else cum_col_full_tile<T, KIND, NANP, false, kCumColRows>(col, acc);
+    } else
+    for (int q0 = 0; q0 < nv; q0 += 8) {
+      uint32_t w[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {                   // all eight loads before the first add
+        const int q = q0 + k < nv ? q0 + k : nv - 1;
+        w[k] = col[(reverse ? nv - 1 - q : q) * 32];
+      }
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int q = q0 + k;
+        if (q < nv) {
+          T x[EPW];
+          memcpy(x, &w[k], 4);
+#pragma unroll
+          for (int e = 0; e < EPW; ++e) {
+            acc[e] = cum_step<T, KIND, NANP>(acc[e], x[e], it == 0 && q == 0);
+            x[e] = cum_narrow<T>(acc[e]);
+          }
+          uint32_t out;
+          memcpy(&out, x, 4);
+          col[(reverse ? nv - 1 - q : q) * 32] = out;
+        }
+      }
+    }
+    if (lane == 0) {
+      // the buffer of tile it + depth - 2 went out two tiles ago; only the last store may still be reading its own
+      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      fetch(it + depth - 2);
+    }
+    fence_proxy_async();                              // the lanes' writes, before the copy engine reads them
+    __syncwarp();
+    if (lane == 0) {
+      asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];" ::"l"(reinterpret_cast<uint64_t>(&tdst)),
+                   "r"(x0), "r"(static_cast<int>(s * kCumColRows)), "r"(smem_u32(tiles + b * kCumColTileBytes))
+                   : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  }
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
 // ------------------------------------------------------------------ axis 1: a warp per 32 rows, tiles of 128 bytes
@@ -293,6 +420,35 @@ void launch_cum(int axis, int reverse, int64_t rows, int64_t cols, const void *s
   const T *s = static_cast<const T *>(src);
   T *d = static_cast<T *>(dst);
   if (axis == 0) {
+    if constexpr (sizeof(T) <= 4) {
+      const int64_t row_bytes = cols * static_cast<int64_t>(sizeof(T));
+      if (rows >= 256 && rows <= 0x7fffffffLL && row_bytes <= 0x7fffffffLL && aligned_to(src, 16) && aligned_to(dst, 16) &&
+          (ss * sizeof(T)) % 16 == 0 && (ds * sizeof(T)) % 16 == 0 && std::getenv("BSIR_CUM_NO_TMA") == nullptr) {
+        // the ring as deep as the warps that will share an SM leave room for (about 200 KB among them); tiles of 128
+        // rows (half as many waits, fences and copies a row) when that still leaves a ring of four
+        const int64_t groups = ceil_div(row_bytes, static_cast<int64_t>(128));
+        const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
+        int64_t per_sm = ceil_div(groups, static_cast<int64_t>(sms));
+        if (per_sm > 16) per_sm = 16;
+        const int room = static_cast<int>((200 * 1024 / per_sm - 1024) / (64 * 128));     // 64-row tiles a warp may hold
+        const int tile_rows = room >= 8 ? 128 : 64;
+        int depth = tile_rows == 128 ? room / 2 : room;
+        depth = depth < 3 ? 3 : depth > kCumColMaxDepth * 64 / tile_rows ? kCumColMaxDepth * 64 / tile_rows : depth;   // three at least: in use, going out, coming in
+        const size_t smem = static_cast<size_t>(depth) * tile_rows * 128;
+        CUtensorMap tsrc, tdst;
+        if (make_byte_tmap(&tsrc, src, static_cast<uint64_t>(row_bytes), static_cast<uint64_t>(rows), static_cast<uint64_t>(ss) * sizeof(T), tile_rows, false) &&
+            make_byte_tmap(&tdst, dst, static_cast<uint64_t>(row_bytes), static_cast<uint64_t>(rows), static_cast<uint64_t>(ds) * sizeof(T), tile_rows, false)) {
+          if (tile_rows == 128) {
+            cudaFuncSetAttribute(cum_first_tma_kernel<T, KIND, NANP, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCumColMaxDepth * 64 * 128);
+            cum_first_tma_kernel<T, KIND, NANP, 128><<<static_cast<unsigned>(groups), 32, smem, st>>>(tsrc, tdst, rows, reverse, depth, device_error_word());
+          } else {
+            cudaFuncSetAttribute(cum_first_tma_kernel<T, KIND, NANP, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCumColMaxDepth * 64 * 128);
+            cum_first_tma_kernel<T, KIND, NANP, 64><<<static_cast<unsigned>(groups), 32, smem, st>>>(tsrc, tdst, rows, reverse, depth, device_error_word());
+          }
+          return;
+        }
+      }
+    }
     // small blocks: a tall, narrow problem has few columns, and they should spread over the SMs
     cum_first_seq_kernel<T, KIND, NANP><<<static_cast<unsigned>(ceil_div(cols, 64)), 64, 0, st>>>(s, d, rows, cols, ss, ds, reverse);
     return;

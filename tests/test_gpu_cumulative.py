@@ -73,6 +73,29 @@ def test_row_scan_with_many_rows_and_without_tensor_maps(bsir, monkeypatch, dtyp
     assert_bits_equal(y, want[:200], f"cumsum {dtype} one tile a step")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.int8, torch.int16, torch.int32])
+@pytest.mark.parametrize("kind", ["sum", "max"])
+def test_first_axis_scan_of_tall_problems(bsir, dtype, kind):
+    """Down the rows through tiles of 128 rows: a last tile of 44 rows, a last column group of 32 bytes (a strided
+    view), both directions; and a problem tall enough for the ring to wrap many times."""
+    big = _data((300, 1024), dtype, 21)
+    eb = big.element_size()
+    view = big[:, :1024 - 96 // eb]                              # row pitch stays 1024 elements
+    out = torch.zeros_like(big)
+    for reverse in (False, True):
+        bsir.cumulative(kind, view, dim=0, reverse=reverse, out=out[:, :view.shape[1]])
+        assert_bits_equal(out[:, :view.shape[1]].contiguous(),
+                          O.cumulative(kind, oracle_dtype(big), to_bits(view.contiguous()), axis=0, reverse=reverse),
+                          f"cum{kind} {dtype} first axis, reverse {reverse}")
+        assert out[:, view.shape[1]:].abs().sum().item() == 0
+    tall = _data((5000, 96), dtype, 22)
+    assert_bits_equal(bsir.cumulative(kind, tall, dim=0), O.cumulative(kind, oracle_dtype(tall), to_bits(tall), axis=0), "tall")
+    wide = _data((300, 65536 // eb), dtype, 23)                  # 512 column groups: four warps an SM, tiles of 64 rows
+    for reverse in (False, True):
+        assert_bits_equal(bsir.cumulative(kind, wide, dim=0, reverse=reverse),
+                          O.cumulative(kind, oracle_dtype(wide), to_bits(wide), axis=0, reverse=reverse), f"wide, reverse {reverse}")
+
+
 def test_cumulative_config_shape_and_validation(bsir):
     """A decode-time top-p shape: many rows, sorted probabilities along the row."""
     p = torch.softmax(torch.randn(2048, 4096, device="cuda"), dim=1).sort(dim=1, descending=True).values.contiguous()
@@ -86,8 +109,7 @@ def test_cumulative_config_shape_and_validation(bsir):
 @pytest.mark.parametrize("dtype,cols", [(torch.bfloat16, 16384), (torch.float32, 8192), (torch.int8, 32768), (torch.int16, 16384)])
 @pytest.mark.parametrize("kind", ["sum", "max"])
 def test_first_axis_scan_of_wide_problems(bsir, dtype, cols, kind):
-    """Wide problems scanned down the rows (a thread per column; 16 bytes of columns per thread measured slower: fewer
-    loads in flight)."""
+    """Wide, short problems scanned down the rows (37 rows: the thread-per-column kernel)."""
     x = _data((37, cols), dtype, cols)
     for reverse in (False, True):
         y = bsir.cumulative(kind, x, dim=0, reverse=reverse)
