@@ -6,10 +6,9 @@
 //   vinterleave:    dst[r, N * i + ch] = src_ch[r, i]      (N = interleave_channel_nums sources of one shape)
 //   vdeinterleave:  dst_ch[r, i] = src[r, N * i + ch]      (a NULL destination skips its channel: the op's
 //                   CHANNEL_0 / CHANNEL_1 index modes)
-// All three are pure data movement: a thread writes one 16-byte vector of the contiguous side (or one
-// element when the row is not a whole number of vectors) and reads what it needs with scalar loads, which
-// the neighbouring threads' loads complete into full sectors.
+// All three are pure data movement.
 #include <cstdint>
+#include <cstring>
 #include <type_traits>
 
 #include "common.cuh"
@@ -36,31 +35,115 @@ __global__ void __launch_bounds__(256) arange_kernel(T *dst, int64_t n0, int64_t
   dst[i0 * d0 + i1 * d1 + i2 * d2] = out;
 }
 
-// one thread per element of the interleaved side; consecutive threads -> consecutive interleaved columns
+// The operands are contiguous, so interleaving the last axis of [rows, cols] is interleaving the flat arrays:
+// dst[N * j + ch] = src_ch[j].  Two channels (the op's default) with 16-byte aligned operands move 16-byte vectors
+// -- a thread reads one from each source and writes the two vectors they interleave into, or the other way round;
+// everything else takes a thread per j that loops over the channels: no division anywhere, reads coalesced per
+// channel, writes contiguous across the warp.
+template <typename T>
+__global__ void __launch_bounds__(256) interleave2_vec_kernel(const uint4 *__restrict__ a, const uint4 *__restrict__ b, uint4 *__restrict__ dst,
+                                                              int64_t nvec) {
+  constexpr int V = 16 / sizeof(T);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    const uint4 ra = __ldg(a + v), rb = __ldg(b + v);
+    T xa[V], xb[V], o[2 * V];
+    memcpy(xa, &ra, 16);
+    memcpy(xb, &rb, 16);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      o[2 * k] = xa[k];
+      o[2 * k + 1] = xb[k];
+    }
+    uint4 w[2];
+    memcpy(w, o, 32);
+    dst[2 * v] = w[0];
+    dst[2 * v + 1] = w[1];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) deinterleave2_vec_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ a, uint4 *__restrict__ b,
+                                                                int64_t nvec) {
+  constexpr int V = 16 / sizeof(T);
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t v = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < nvec; v += stride) {
+    uint4 w[2];
+    w[0] = __ldg(src + 2 * v);
+    w[1] = __ldg(src + 2 * v + 1);
+    T o[2 * V], xa[V], xb[V];
+    memcpy(o, w, 32);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      xa[k] = o[2 * k];
+      xb[k] = o[2 * k + 1];
+    }
+    uint4 ra, rb;
+    memcpy(&ra, xa, 16);
+    memcpy(&rb, xb, 16);
+    if (a) a[v] = ra;
+    if (b) b[v] = rb;
+  }
+}
+
+// flat j in [first, n): one thread each, every channel in turn
 template <typename T, bool INTERLEAVE>
-__global__ void __launch_bounds__(256) interleave_kernel(ChannelPtrs p, T *dst, const T *src, int channels, int64_t rows, int64_t cols) {
-  const int64_t wide = cols * channels;
-  const int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (e >= rows * wide) return;
-  const int64_t r = e / wide, c = e - r * wide;
-  const int ch = static_cast<int>(c % channels);
-  const int64_t i = c / channels;
-  if constexpr (INTERLEAVE) {
-    dst[e] = static_cast<const T *>(p.in[ch])[r * cols + i];
-  } else {
-    T *d = static_cast<T *>(p.out[ch]);
-    if (d) d[r * cols + i] = src[e];
+__global__ void __launch_bounds__(256) interleave_kernel(ChannelPtrs p, T *dst, const T *src, int channels, int64_t first, int64_t n) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  for (int64_t j = first + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; j < n; j += stride) {
+    for (int ch = 0; ch < channels; ++ch) {
+      if constexpr (INTERLEAVE) {
+        dst[j * channels + ch] = static_cast<const T *>(p.in[ch])[j];
+      } else {
+        T *d = static_cast<T *>(p.out[ch]);
+        if (d) d[j] = src[j * channels + ch];
+      }
+    }
+  }
+}
+
+template <typename T, bool INTERLEAVE>
+void launch_interleave_typed(const ChannelPtrs &p, void *dst, const void *src, int channels, int64_t n, cudaStream_t st) {
+  const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
+  const int64_t cap = static_cast<int64_t>(sms) * 16;           // blocks: a grid-stride loop beyond that
+  int64_t first = 0;
+  if (channels == 2) {
+    bool vec = aligned_to(INTERLEAVE ? dst : src, 16);
+    for (int c = 0; c < 2; ++c) {
+      const void *q = INTERLEAVE ? p.in[c] : p.out[c];
+      vec = vec && (q == nullptr || aligned_to(q, 16));
+    }
+    constexpr int V = 16 / sizeof(T);
+    const int64_t nvec = n / V;
+    if (vec && nvec > 0) {
+      const int64_t want = ceil_div(nvec, static_cast<int64_t>(256));
+      const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
+      if constexpr (INTERLEAVE)
+        interleave2_vec_kernel<T><<<blocks, 256, 0, st>>>(static_cast<const uint4 *>(p.in[0]), static_cast<const uint4 *>(p.in[1]),
+                                                          static_cast<uint4 *>(dst), nvec);
+      else
+        deinterleave2_vec_kernel<T><<<blocks, 256, 0, st>>>(static_cast<const uint4 *>(src), static_cast<uint4 *>(p.out[0]),
+                                                            static_cast<uint4 *>(p.out[1]), nvec);
+      count_launch();
+      first = nvec * V;                                        // the few elements past the last whole vector follow
+    }
+  }
+  if (first < n) {
+    const int64_t want = ceil_div(n - first, static_cast<int64_t>(256));
+    const unsigned blocks = static_cast<unsigned>(want < cap ? want : cap);
+    interleave_kernel<T, INTERLEAVE><<<blocks, 256, 0, st>>>(p, static_cast<T *>(dst), static_cast<const T *>(src), channels, first, n);
+    count_launch();
   }
 }
 
 template <bool INTERLEAVE>
 void launch_interleave(int eb, const ChannelPtrs &p, void *dst, const void *src, int channels, int64_t rows, int64_t cols, cudaStream_t st) {
-  const unsigned blocks = static_cast<unsigned>(ceil_div(rows * cols * channels, 256));
+  const int64_t n = rows * cols;
   switch (eb) {
-    case 1: interleave_kernel<uint8_t, INTERLEAVE><<<blocks, 256, 0, st>>>(p, static_cast<uint8_t *>(dst), static_cast<const uint8_t *>(src), channels, rows, cols); break;
-    case 2: interleave_kernel<uint16_t, INTERLEAVE><<<blocks, 256, 0, st>>>(p, static_cast<uint16_t *>(dst), static_cast<const uint16_t *>(src), channels, rows, cols); break;
-    case 4: interleave_kernel<uint32_t, INTERLEAVE><<<blocks, 256, 0, st>>>(p, static_cast<uint32_t *>(dst), static_cast<const uint32_t *>(src), channels, rows, cols); break;
-    default: interleave_kernel<uint64_t, INTERLEAVE><<<blocks, 256, 0, st>>>(p, static_cast<uint64_t *>(dst), static_cast<const uint64_t *>(src), channels, rows, cols); break;
+    case 1: launch_interleave_typed<uint8_t, INTERLEAVE>(p, dst, src, channels, n, st); break;
+    case 2: launch_interleave_typed<uint16_t, INTERLEAVE>(p, dst, src, channels, n, st); break;
+    case 4: launch_interleave_typed<uint32_t, INTERLEAVE>(p, dst, src, channels, n, st); break;
+    default: launch_interleave_typed<uint64_t, INTERLEAVE>(p, dst, src, channels, n, st); break;
   }
 }
 
@@ -126,7 +209,6 @@ extern "C" int32_t bsir_interleave(int32_t dtype, int32_t channels, int64_t rows
   }
   if (!aligned_to(dst, eb)) return fail(BSIR_ERR_ALIGN, "interleave: dst misaligned");
   launch_interleave<true>(eb, p, dst, nullptr, channels, rows, cols, resolve_stream(stream));
-  count_launch();
   return check_launch("interleave");
 }
 
@@ -147,6 +229,5 @@ extern "C" int32_t bsir_deinterleave(int32_t dtype, int32_t channels, int64_t ro
   if (!any) return fail(BSIR_ERR_NULL, "deinterleave: every destination is null");
   if (!aligned_to(src, eb)) return fail(BSIR_ERR_ALIGN, "deinterleave: src misaligned");
   launch_interleave<false>(eb, p, nullptr, src, channels, rows, cols, resolve_stream(stream));
-  count_launch();
   return check_launch("deinterleave");
 }

@@ -365,6 +365,23 @@ def test_interleave_and_deinterleave_are_inverse_bit_moves(bsir, dtype, channels
     assert torch.equal(only[channels - 1], srcs[-1]) and all(o is None for o in only[:-1])
 
 
+@pytest.mark.parametrize("dtype", [torch.int8, torch.float16, torch.float32])
+def test_interleave_two_channels_at_any_alignment(bsir, dtype):
+    """Two channels take 16-byte vectors when every operand is 16-byte aligned; operands that start on an odd element
+    take the element path.  Both must move the same bits."""
+    n = 100003
+    g = torch.Generator(device="cuda").manual_seed(3)
+    pool = [torch.randint(-100, 100, (n + 8,), device="cuda", generator=g).to(dtype) for _ in range(2)]
+    for off in (0, 1, 3):
+        a, b = pool[0][off:off + n], pool[1][off:off + n]
+        y = bsir.interleave([a, b])
+        assert torch.equal(y, torch.stack([a, b], dim=-1).reshape(-1))
+        src = torch.zeros(2 * n + 8, device="cuda", dtype=dtype)
+        src[off:off + 2 * n] = y
+        back = bsir.deinterleave(src[off:off + 2 * n], 2)
+        assert torch.equal(back[0], a) and torch.equal(back[1], b)
+
+
 def _in_fresh_thread(fn):
     """Runs fn in a new thread and returns (its result, the fused-chain path that thread used: "none" when the chain
     executor, and with it the runtime compiler, was never entered)."""
