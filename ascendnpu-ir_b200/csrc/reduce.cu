@@ -263,63 +263,74 @@ __global__ void __launch_bounds__(256) reduce_last_vec_kernel(int64_t rows, int6
   }
 }
 
-// First axis.  A thread owns one 16-byte column vector; block = 32 column vectors x 8 row slices;
-// grid = (column groups, row slabs).
-template <int DT, int KIND>
+// First axis.  A thread owns CW 16-byte column vectors 512 bytes apart, so a warp reads CW x 512 contiguous bytes of
+// a row (rows lie a whole row pitch apart in DRAM: the longer the stretch read from one, the fewer pages are opened
+// for it); block = 32 x CW column vectors x 8 row slices; grid = (column groups, row slabs).
+template <int DT, int KIND, int CW>
 __global__ void __launch_bounds__(256) reduce_first_vec_kernel(int64_t rows, int64_t cvecs, int64_t row_stride,
                                                                const void *__restrict__ src, int64_t slab_rows, int nslabs,
                                                                void *__restrict__ dst, unsigned long long *partials) {
   using A = typename Acc<DT>::type;
   using E = typename Acc<DT>::elem;
   constexpr int kPerVec = 16 / sizeof(E);
+  constexpr int kRowsAhead = CW == 1 ? 4 : 2;        // rows a thread asks for before it adds the first
   __shared__ unsigned long long red[7][32][kPerVec < 8 ? kPerVec : 8];
   pdl_launch_dependents();   // the finishing launch (or the next op) is scheduled while this one runs (launch_pdl) ...
   pdl_wait();                // ... and global memory is touched only after the kernel ahead has completed
   const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
-  const int64_t cv = static_cast<int64_t>(blockIdx.x) * 32 + cx;
+  const int64_t cv0 = static_cast<int64_t>(blockIdx.x) * (32 * CW) + cx;
   const int slab = blockIdx.y;
   const int64_t r0 = static_cast<int64_t>(slab) * slab_rows, r1 = min(rows, r0 + slab_rows);
-  A acc[kPerVec];
+  A acc[CW][kPerVec];
 #pragma unroll
-  for (int k = 0; k < kPerVec; ++k) acc[k] = identity<DT, KIND>();
-  if (cv < cvecs) {
-    const E *base = static_cast<const E *>(src) + cv * kPerVec;
-    for (int64_t r = r0 + ry; r < r1; r += 32) {
-      Vec16 v[4];
+  for (int w = 0; w < CW; ++w)
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (r + 8 * u < r1) v[u] = ld_stream(reinterpret_cast<const Vec16 *>(base + (r + 8 * u) * row_stride));
+    for (int k = 0; k < kPerVec; ++k) acc[w][k] = identity<DT, KIND>();
+  const E *base = static_cast<const E *>(src) + cv0 * kPerVec;
+  for (int64_t r = r0 + ry; r < r1; r += 8 * kRowsAhead) {
+    Vec16 v[kRowsAhead][CW];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (r + 8 * u < r1) {
+    for (int u = 0; u < kRowsAhead; ++u)
 #pragma unroll
-          for (int k = 0; k < kPerVec; ++k) acc[k] = combine<KIND, A>(acc_from_vec<DT>(v[u], k), acc[k]);
+      for (int w = 0; w < CW; ++w)
+        if (r + 8 * u < r1 && cv0 + 32 * w < cvecs)
+          v[u][w] = ld_stream(reinterpret_cast<const Vec16 *>(base + (r + 8 * u) * row_stride + 32 * w * kPerVec));
+#pragma unroll
+    for (int u = 0; u < kRowsAhead; ++u)
+#pragma unroll
+      for (int w = 0; w < CW; ++w)
+        if (r + 8 * u < r1 && cv0 + 32 * w < cvecs) {
+#pragma unroll
+          for (int k = 0; k < kPerVec; ++k) acc[w][k] = combine<KIND, A>(acc_from_vec<DT>(v[u][w], k), acc[w][k]);
         }
-    }
   }
-  // the eight row slices meet in shared memory, 8 elements of the vector at a time
+  // the eight row slices meet in shared memory, 8 elements of a vector at a time
   constexpr int kChunk = kPerVec < 8 ? kPerVec : 8;
 #pragma unroll
-  for (int c0 = 0; c0 < kPerVec; c0 += kChunk) {
-    if (ry > 0) {
+  for (int w = 0; w < CW; ++w) {
+    const bool mine = cv0 + 32 * w < cvecs;
 #pragma unroll
-      for (int k = 0; k < kChunk; ++k) red[ry - 1][cx][k] = acc_bits(acc[c0 + k]);
+    for (int c0 = 0; c0 < kPerVec; c0 += kChunk) {
+      if (ry > 0) {
+#pragma unroll
+        for (int k = 0; k < kChunk; ++k) red[ry - 1][cx][k] = acc_bits(acc[w][c0 + k]);
+      }
+      __syncthreads();
+      if (ry == 0 && mine) {
+#pragma unroll
+        for (int s = 0; s < 7; ++s)
+#pragma unroll
+          for (int k = 0; k < kChunk; ++k) acc[w][c0 + k] = combine<KIND, A>(acc[w][c0 + k], acc_of_bits<A>(red[s][cx][k]));
+      }
+      __syncthreads();
     }
-    __syncthreads();
-    if (ry == 0 && cv < cvecs) {
+    if (ry == 0 && mine) {
 #pragma unroll
-      for (int s = 0; s < 7; ++s)
-#pragma unroll
-        for (int k = 0; k < kChunk; ++k) acc[c0 + k] = combine<KIND, A>(acc[c0 + k], acc_of_bits<A>(red[s][cx][k]));
-    }
-    __syncthreads();
-  }
-  if (ry == 0 && cv < cvecs) {
-#pragma unroll
-    for (int k = 0; k < kPerVec; ++k) {
-      const int64_t c = cv * kPerVec + k;
-      if (nslabs == 1) store_acc<DT>(dst, c, acc[k]);
-      else partials[static_cast<int64_t>(slab) * (cvecs * kPerVec) + c] = acc_bits(acc[k]);
+      for (int k = 0; k < kPerVec; ++k) {
+        const int64_t c = (cv0 + 32 * w) * kPerVec + k;
+        if (nslabs == 1) store_acc<DT>(dst, c, acc[w][k]);
+        else partials[static_cast<int64_t>(slab) * (cvecs * kPerVec) + c] = acc_bits(acc[w][k]);
+      }
     }
   }
 }
@@ -385,7 +396,10 @@ void launch_reduce(bool last, int64_t rows, int64_t cols, const void *src, int64
   }
   if (!last && vec_ok) {
     const int64_t cvecs = cols / kPerVec;
-    const int64_t col_groups = ceil_div(cvecs, 32);
+    // four column vectors a thread (2 KB of a row a warp) for 4- and 8-byte elements when the rows are long enough and
+    // there are enough of them to cut into slabs that still fill the SMs: [32768,4096] f32 116 -> 105 us
+    const int cw = kPerVec <= 4 && cvecs >= 128 && rows >= 512 ? 4 : 1;   // (16-bit elements: 32 accumulators a thread cost more than the longer stretches gain)
+    const int64_t col_groups = ceil_div(cvecs, static_cast<int64_t>(32 * cw));
     int64_t slabs = 1;
     if (col_groups < 4 * sms) {
       slabs = ceil_div(4 * sms, col_groups);
@@ -402,8 +416,12 @@ void launch_reduce(bool last, int64_t rows, int64_t cols, const void *src, int64
       else slabs = 1;
     }
     const dim3 grid(static_cast<unsigned>(col_groups), static_cast<unsigned>(slabs));
-    launch_pdl(reduce_first_vec_kernel<DT, KIND>, grid, dim3(256), 0, st, rows, cvecs, rs, src, slabs > 1 ? slab_rows : rows,
-               static_cast<int>(slabs), dst, partials);
+    if (cw == 4)
+      launch_pdl(reduce_first_vec_kernel<DT, KIND, 4>, grid, dim3(256), 0, st, rows, cvecs, rs, src, slabs > 1 ? slab_rows : rows,
+                 static_cast<int>(slabs), dst, partials);
+    else
+      launch_pdl(reduce_first_vec_kernel<DT, KIND, 1>, grid, dim3(256), 0, st, rows, cvecs, rs, src, slabs > 1 ? slab_rows : rows,
+                 static_cast<int>(slabs), dst, partials);
     if (slabs > 1) {
       launch_pdl(reduce_finish_kernel<DT, KIND>, dim3(static_cast<unsigned>(ceil_div(cols, 256))), dim3(256), 0, st, cols,
                  static_cast<int>(slabs), static_cast<int64_t>(1), cols, partials, dst);
