@@ -632,30 +632,62 @@ __global__ void __launch_bounds__(kStreamThreads)
       if constexpr (KIND == kOpSelect) fc[u] = static_cast<const Flags *>(cp)[v];
     }
   }
+  // the predicate is chosen once, outside the loops: inside them it is a constant and the comparison one instruction
+  auto all_vectors = [&](auto fn_tag) {
 #pragma unroll
-  for (int u = 0; u < kStreamUnroll; ++u) {
-    const int64_t v = base + static_cast<int64_t>(u) * kStreamThreads;
-    if (v >= nvec) continue;
-    T x[kPerVec], y[kPerVec];
-    if (ap) memcpy(x, &va[u], 16);
-    else
-      for (int e = 0; e < kPerVec; ++e) x[e] = sa;
-    if (bp) memcpy(y, &vb[u], 16);
-    else
-      for (int e = 0; e < kPerVec; ++e) y[e] = sb;
-    if constexpr (KIND == kOpCompare) {
-      Flags r;
+    for (int u = 0; u < kStreamUnroll; ++u) {
+      const int64_t v = base + static_cast<int64_t>(u) * kStreamThreads;
+      if (v >= nvec) continue;
+      T x[kPerVec], y[kPerVec];
+      if (ap) memcpy(x, &va[u], 16);
+      else
+        for (int e = 0; e < kPerVec; ++e) x[e] = sa;
+      if (bp) memcpy(y, &vb[u], 16);
+      else
+        for (int e = 0; e < kPerVec; ++e) y[e] = sb;
+      if constexpr (KIND == kOpCompare) {
+        // the vector's bool bytes are put together in registers and leave as one store of their whole width
+        if constexpr (kPerVec == 2) {
+          const uint32_t w = (compare_elem<DT>(decltype(fn_tag)::value, x[0], y[0]) ? 1u : 0u) |
+                             (compare_elem<DT>(decltype(fn_tag)::value, x[1], y[1]) ? 0x100u : 0u);
+          static_cast<uint16_t *>(outp)[v] = static_cast<uint16_t>(w);
+        } else {
+          uint32_t w[kPerVec / 4];
 #pragma unroll
-      for (int e = 0; e < kPerVec; ++e) r.f[e] = compare_elem<DT>(fn, x[e], y[e]) ? 1 : 0;
-      static_cast<Flags *>(outp)[v] = r;
-    } else {
-      T r[kPerVec];
+          for (int q = 0; q < kPerVec / 4; ++q) {
+            w[q] = 0;
 #pragma unroll
-      for (int e = 0; e < kPerVec; ++e) r[e] = fc[u].f[e] ? x[e] : y[e];
-      Vec16 vo;
-      memcpy(&vo, r, 16);
-      st_stream(static_cast<Vec16 *>(outp) + v, vo);
+            for (int e = 0; e < 4; ++e) w[q] |= (compare_elem<DT>(decltype(fn_tag)::value, x[4 * q + e], y[4 * q + e]) ? 1u : 0u) << (8 * e);
+          }
+          if constexpr (kPerVec == 4) static_cast<uint32_t *>(outp)[v] = w[0];
+          else if constexpr (kPerVec == 8) static_cast<uint2 *>(outp)[v] = make_uint2(w[0], w[1]);
+          else static_cast<uint4 *>(outp)[v] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+        T r[kPerVec];
+#pragma unroll
+        for (int e = 0; e < kPerVec; ++e) r[e] = fc[u].f[e] ? x[e] : y[e];
+        Vec16 vo;
+        memcpy(&vo, r, 16);
+        st_stream(static_cast<Vec16 *>(outp) + v, vo);
+      }
     }
+  };
+  if constexpr (KIND == kOpCompare) {
+    switch (fn) {
+      case BSIR_CMP_VEQ: all_vectors(std::integral_constant<int, BSIR_CMP_VEQ>{}); break;
+      case BSIR_CMP_VNE: all_vectors(std::integral_constant<int, BSIR_CMP_VNE>{}); break;
+      case BSIR_CMP_VLE: all_vectors(std::integral_constant<int, BSIR_CMP_VLE>{}); break;
+      case BSIR_CMP_VLT: all_vectors(std::integral_constant<int, BSIR_CMP_VLT>{}); break;
+      case BSIR_CMP_VGE: all_vectors(std::integral_constant<int, BSIR_CMP_VGE>{}); break;
+      case BSIR_CMP_VGT: all_vectors(std::integral_constant<int, BSIR_CMP_VGT>{}); break;
+      case BSIR_CMP_VULE: all_vectors(std::integral_constant<int, BSIR_CMP_VULE>{}); break;
+      case BSIR_CMP_VULT: all_vectors(std::integral_constant<int, BSIR_CMP_VULT>{}); break;
+      case BSIR_CMP_VUGE: all_vectors(std::integral_constant<int, BSIR_CMP_VUGE>{}); break;
+      default: all_vectors(std::integral_constant<int, BSIR_CMP_VUGT>{}); break;
+    }
+  } else {
+    all_vectors(std::integral_constant<int, 0>{});
   }
   // ragged tail (< one vector): the first threads of block 0, one element each
   const int64_t i = nvec * kPerVec + threadIdx.x;

@@ -419,6 +419,17 @@ def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters, only=None):
         rec("cumsum_f32_32768x4096", 2 * 32768 * 4096 * 4, lambda i: bsir.cumulative("sum", xs[i % 2], dim=1, out=ys[i % 2]),
             note="sequential along the row, as the reference's loop: exact float sums")
         del xs, ys
+    if want("cumsum_f32_32768x4096_axis0"):
+        xs = [torch.randn(32768, 4096, device="cuda") for _ in range(2)]
+        ys = [torch.empty_like(x) for x in xs]
+        rec("cumsum_f32_32768x4096_axis0", 2 * 32768 * 4096 * 4, lambda i: bsir.cumulative("sum", xs[i % 2], dim=0, out=ys[i % 2]),
+            note="sequential down the rows: 32768 dependent adds a column, 128 warps in all (one per 128 bytes of columns)")
+        del xs, ys
+    if want("interleave2_f32_32768x2048"):
+        xs = [[torch.randn(32768, 2048, device="cuda") for _ in range(2)] for _ in range(2)]
+        ys = [torch.empty(32768, 4096, device="cuda") for _ in range(2)]
+        rec("interleave2_f32_32768x2048", 2 * 32768 * 4096 * 4, lambda i: bsir.interleave(xs[i % 2], out=ys[i % 2]))
+        del xs, ys
     if want("sort_f32_1024x8192"):
         xs = [torch.randn(1024, 8192, device="cuda") for _ in range(2)]
         rec("sort_f32_1024x8192", 1024 * 8192 * (4 + 4 + 4), lambda i: bsir.sort(xs[i % 2], descending=True),
