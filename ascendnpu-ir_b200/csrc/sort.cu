@@ -195,7 +195,7 @@ __global__ void __launch_bounds__(kRadixThreads) radix_count_kernel(const typena
 #pragma unroll
     for (int i = 0; i < kRadixIters; ++i) {
       const int64_t pos = base + i * kRadixThreads + tid;
-      raw[i] = src_row[pos < cols ? pos : 0];
+      raw[i] = pos < cols ? src_row[pos] : typename SortElem<DT>::type(0);
     }
 #pragma unroll
     for (int i = 0; i < kRadixIters; ++i) order[i] = radix_order<DT>(raw[i], descending);
@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(kRadixThreads) radix_count_kernel(const typena
 #pragma unroll
     for (int i = 0; i < kRadixIters; ++i) {
       const int64_t pos = base + i * kRadixThreads + tid;
-      order[i] = static_cast<uint32_t>(keys_row[pos < cols ? pos : 0] >> 32);
+      order[i] = pos < cols ? static_cast<uint32_t>(keys_row[pos] >> 32) : 0u;
     }
   }
 #pragma unroll
@@ -395,7 +395,7 @@ __global__ void __launch_bounds__(kRadixThreads, 3) radix_move_kernel(const type
 #pragma unroll
     for (int i = 0; i < kRadixIters; ++i) {
       const int64_t pos = base + i * 32 + lane;
-      raw[i] = src_row[pos < cols ? pos : 0];
+      raw[i] = pos < cols ? src_row[pos] : typename SortElem<DT>::type(0);
     }
 #pragma unroll
     for (int i = 0; i < kRadixIters; ++i)
@@ -404,7 +404,7 @@ __global__ void __launch_bounds__(kRadixThreads, 3) radix_move_kernel(const type
 #pragma unroll
     for (int i = 0; i < kRadixIters; ++i) {
       const int64_t pos = base + i * 32 + lane;
-      key[i] = keys_row[pos < cols ? pos : 0];
+      key[i] = pos < cols ? keys_row[pos] : 0ull;
     }
   }
   const uint32_t start = radix_tile_pass<kRadixIters>(sm, key, radix_warp_valid(cols, base, kRadixTile / kRadixWarps), shift);
@@ -486,7 +486,7 @@ __global__ void __launch_bounds__(kRadixThreads, ITERS > 8 ? 3 : 4) radix_rows_k
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
       const int pos = base + i * 32 + lane;
-      raw[i] = s[pos < cols ? pos : 0];
+      raw[i] = pos < cols ? s[pos] : typename SortElem<DT>::type(0);
     }
 #pragma unroll
     for (int i = 0; i < ITERS; ++i)
