@@ -308,6 +308,14 @@ __global__ void __launch_bounds__(256) cast_stream_kernel(int64_t n, const void 
       done = true;
     }
   }
+  if constexpr (!kFloatToInt) {
+    // round-to-nearest-even, the mode conversions between float types and from integers default to: known at
+    // compile time the conversion is one instruction per element or pair
+    if (mode == BSIR_ROUND_RINT) {
+      body(fixed(integral_constant<int, BSIR_ROUND_RINT>{}), [overflow]() { return overflow; });
+      done = true;
+    }
+  }
   if (!done) body([mode]() { return mode; }, [overflow]() { return overflow; });
   const int64_t tail0 = ngroups * kElems;
   if (blockIdx.x == 0 && tail0 + threadIdx.x < n)
