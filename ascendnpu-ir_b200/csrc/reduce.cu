@@ -366,6 +366,9 @@ void launch_reduce(bool last, int64_t rows, int64_t cols, const void *src, int64
     const int64_t nvec = cols / kPerVec;
     int tpr = 4;
     while (tpr < 256 && nvec > tpr * 4) tpr <<= 1;          // about 4 vectors per thread before a row gets more threads
+    // with rows enough to fill every SM with warps, a warp a row: the row's sum ends in shuffles, no block-wide barrier
+    // ([32768,4096] f32: 89.6 -> 77.1 us; bf16 45.2 -> 41.5 us)
+    if (tpr > 32 && rows >= static_cast<int64_t>(sms) * 64) tpr = 32;
     const int rpc = 256 / tpr;
     const int64_t row_groups = ceil_div(rows, rpc);
     // few long rows: cut them so that about 4 CTAs per SM have work, parts of at least 1024 vectors

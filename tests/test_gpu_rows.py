@@ -204,6 +204,23 @@ def test_reduce_float(bsir, kind, dtype, rows, cols):
             assert_close(out, want, tol, tol, what=f"reduce {kind} {dtype} dim{dim}")
 
 
+@pytest.mark.parametrize("kind", ["sum", "max"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_reduce_many_long_rows(bsir, kind, dtype):
+    """Enough rows to fill every SM with warps: a warp a row along the rows (2048 columns, eight or more vectors a lane),
+    four column vectors a thread down them."""
+    g = torch.Generator(device="cuda").manual_seed(17)
+    x = (torch.rand(12000, 2048, generator=g, device="cuda") * 2 - 1).to(dtype)
+    for dim in (1, 0):
+        out = bsir.reduce(kind, x, dim=dim)
+        want = (O.reduce_last_axis if dim == 1 else O.reduce_first_axis)(kind, oracle_dtype(x), to_bits(x))
+        if kind == "max":
+            assert_bits_equal(out, want, f"reduce max dim{dim}")
+        else:
+            tol = 1e-4 if dtype == torch.float32 else 2e-2
+            assert_close(out, want, tol, tol * 8, what=f"reduce sum {dtype} dim{dim}")
+
+
 def test_reduce_max_nan_and_zero(bsir):
     x = torch.tensor([[1.0, float("nan"), 3.0], [-0.0, 0.0, -0.0], [-0.0, -0.0, -0.0]], device="cuda")
     out = bsir.reduce("max", x)
