@@ -332,6 +332,29 @@ def test_gather_reports_indices_outside_the_axis(bsir):
     assert bsir.device_error() == 0                              # reading clears it
 
 
+@pytest.mark.parametrize("dtype", [torch.int8, torch.bfloat16, torch.float32, torch.int64])
+@pytest.mark.parametrize("idx_dtype", [torch.int16, torch.int32, torch.int64])
+@pytest.mark.parametrize("rows,axis,n", [(5, 3000, 5000), (300, 4096, 4096), (3, 6144, 100), (2, 6145, 70), (700, 129, 64)])
+def test_gather_along_the_last_axis_from_rows_in_shared_memory(bsir, dtype, idx_dtype, rows, axis, n):
+    """Source rows of up to 48 KB are staged in shared memory (6144 int64 = 48 KB: the largest; 6145: the general kernel
+    again); few rows share their destination row out over several CTAs; bad indices leave their elements alone."""
+    g = torch.Generator(device="cuda").manual_seed(n + axis)
+    x = torch.randint(-100, 100, (rows, axis), device="cuda", generator=g).to(dtype)
+    idx = torch.randint(0, axis, (rows, n), device="cuda", generator=g).to(idx_dtype)
+    y = bsir.gather(x, idx, dim=1)
+    assert torch.equal(y, torch.gather(x, 1, idx.long()))
+    assert bsir.device_error() == 0
+    idx[0, 3] = -1
+    idx[rows - 1, n - 1] = axis
+    out = torch.full((rows, n), 77, device="cuda").to(dtype)
+    bsir.gather(x, idx, dim=1, out=out)
+    assert bsir.device_error() == 0x100
+    want = torch.gather(x, 1, idx.long().clamp(0, axis - 1))
+    want[0, 3] = 77
+    want[rows - 1, n - 1] = 77
+    assert torch.equal(out, want)
+
+
 # ---------------------------------------------------------------- varange, vinterleave, vdeinterleave
 def test_arange_example_of_the_op_definition(bsir):
     """HIVMVectorOps.td:1518-1522: offset 1, strides [1, 2], shape 2x4 -> [[1, 3, 5, 7], [2, 4, 6, 8]]."""
