@@ -543,7 +543,9 @@ __global__ void __launch_bounds__(kStreamThreads, 4)
     Vec16 xb = xa;
     if constexpr (KIND == kOpBinary) xb = rows_expand<DT, KB>(vb[u]);
     Vec16 vo;
-    if constexpr (IsFloat<DT>::value) {
+    if constexpr (KIND == kOpCopy) {
+      vo = xa;
+    } else if constexpr (IsFloat<DT>::value) {
       constexpr int kPerWord = FloatTraits<DT>::kPerWord;
       float x[4 * kPerWord], y[4 * kPerWord], r[4 * kPerWord];
 #pragma unroll
@@ -872,7 +874,7 @@ using namespace bsir;
 extern "C" {
 
 namespace {
-bool try_rows_route(bool binary, int fn, int dtype, const Prepared &p, const Operand &a, const Operand &b, void *out, void *stream,
+bool try_rows_route(int kind, int fn, int dtype, const Prepared &p, const Operand &a, const Operand &b, void *out, void *stream,
                     int32_t *rc);
 }
 
@@ -892,7 +894,7 @@ int32_t bsir_elemwise_unary(int32_t fn, int32_t dtype, int32_t rank, const int64
   bool ac;
   Operand a = make_operand(x, rank, sizes, &ac), none{nullptr, 0, 0, 0, 0};
   int32_t rc = BSIR_OK;
-  if (!(ac && p.out_contig) && try_rows_route(false, fn, dtype, p, a, none, out, stream, &rc)) return rc;
+  if (!(ac && p.out_contig) && try_rows_route(kOpUnary, fn, dtype, p, a, none, out, stream, &rc)) return rc;
   return launch_by_dtype<kOpUnary>("elemwise_unary", fn, dtype, p, a, ac, none, true, none, out, resolve_stream(stream));
 }
 
@@ -909,10 +911,17 @@ int32_t launch_rows(int fn, int dt, int64_t rows, int64_t vpr, const RowsOperand
   const unsigned grid = static_cast<unsigned>(ceil_div(total, static_cast<int64_t>(kStreamThreads) * kStreamUnroll));
 #define D(code) \
   case code: launch_pdl(rows_kernel<code, KIND, KA, KB>, dim3(grid), dim3(kStreamThreads), 0, st, fn, rows, vpr, a, b, out, out_rs); break;
-  switch (dt) {
-    D(BSIR_F32) D(BSIR_F16) D(BSIR_BF16) D(BSIR_I8) D(BSIR_I16) D(BSIR_I32) D(BSIR_I64) D(BSIR_U8) D(BSIR_U16)
-    D(BSIR_U32) D(BSIR_U64) D(BSIR_BOOL)
-    default: return fail(BSIR_ERR_DTYPE, "elemwise: dtype %d", dt);
+  if constexpr (KIND == kOpCopy) {        // a copy moves bits: the callers pass the unsigned type of the element's width
+    switch (dt) {
+      D(BSIR_U8) D(BSIR_U16) D(BSIR_U32) D(BSIR_U64)
+      default: return fail(BSIR_ERR_DTYPE, "copy: dtype %d", dt);
+    }
+  } else {
+    switch (dt) {
+      D(BSIR_F32) D(BSIR_F16) D(BSIR_BF16) D(BSIR_I8) D(BSIR_I16) D(BSIR_I32) D(BSIR_I64) D(BSIR_U8) D(BSIR_U16)
+      D(BSIR_U32) D(BSIR_U64) D(BSIR_BOOL)
+      default: return fail(BSIR_ERR_DTYPE, "elemwise: dtype %d", dt);
+    }
   }
 #undef D
   count_launch();
@@ -920,8 +929,9 @@ int32_t launch_rows(int fn, int dt, int64_t rows, int64_t vpr, const RowsOperand
 }
 }  // extern "C++"
 
-bool try_rows_route(bool binary, int fn, int dtype, const Prepared &p, const Operand &a, const Operand &b, void *out, void *stream,
+bool try_rows_route(int kind, int fn, int dtype, const Prepared &p, const Operand &a, const Operand &b, void *out, void *stream,
                     int32_t *rc) {
+  const bool binary = kind == kOpBinary;
   const int64_t n0 = p.sh.n0, n1 = p.sh.n1, n2 = p.sh.n2, rows = n0 * n1, cols = n2;
   const int eb = dtype_bytes(dtype);
   const int per_vec = 16 / eb;
@@ -952,8 +962,15 @@ bool try_rows_route(bool binary, int fn, int dtype, const Prepared &p, const Ope
   const RowsOperand oa{a.p, ra, ka}, ob{b.p, rb, kb};
   cudaStream_t st = resolve_stream(stream);
   const int64_t vpr = cols / per_vec;
-  if (!binary) *rc = launch_rows<kOpUnary, 0, 0>(fn, dtype, rows, vpr, oa, ob, out, out_rs, st);
-  else if (ka == 0 && kb == 0) *rc = launch_rows<kOpBinary, 0, 0>(fn, dtype, rows, vpr, oa, ob, out, out_rs, st);
+  if (kind == kOpCopy) {
+    if (ka == 0) *rc = launch_rows<kOpCopy, 0, 0>(fn, dtype, rows, vpr, oa, ob, out, out_rs, st);
+    else if (ka == 1) *rc = launch_rows<kOpCopy, 1, 0>(fn, dtype, rows, vpr, oa, ob, out, out_rs, st);
+    else *rc = launch_rows<kOpCopy, 2, 0>(fn, dtype, rows, vpr, oa, ob, out, out_rs, st);
+  } else if (!binary) {
+    if (ka == 0) *rc = launch_rows<kOpUnary, 0, 0>(fn, dtype, rows, vpr, oa, ob, out, out_rs, st);
+    else if (ka == 1) *rc = launch_rows<kOpUnary, 1, 0>(fn, dtype, rows, vpr, oa, ob, out, out_rs, st);
+    else *rc = launch_rows<kOpUnary, 2, 0>(fn, dtype, rows, vpr, oa, ob, out, out_rs, st);
+  } else if (ka == 0 && kb == 0) *rc = launch_rows<kOpBinary, 0, 0>(fn, dtype, rows, vpr, oa, ob, out, out_rs, st);
   else if (ka == 0 && kb == 1) *rc = launch_rows<kOpBinary, 0, 1>(fn, dtype, rows, vpr, oa, ob, out, out_rs, st);
   else if (ka == 0 && kb == 2) *rc = launch_rows<kOpBinary, 0, 2>(fn, dtype, rows, vpr, oa, ob, out, out_rs, st);
   else if (ka == 1) *rc = launch_rows<kOpBinary, 1, 0>(fn, dtype, rows, vpr, oa, ob, out, out_rs, st);
@@ -980,7 +997,7 @@ int32_t bsir_elemwise_binary(int32_t fn, int32_t dtype, int32_t rank, const int6
   bool ac, bc;
   Operand oa = make_operand(a, rank, sizes, &ac), ob = make_operand(b, rank, sizes, &bc), none{nullptr, 0, 0, 0, 0};
   int32_t rc = BSIR_OK;
-  if (!(ac && bc && p.out_contig) && try_rows_route(true, fn, dtype, p, oa, ob, out, stream, &rc)) return rc;
+  if (!(ac && bc && p.out_contig) && try_rows_route(kOpBinary, fn, dtype, p, oa, ob, out, stream, &rc)) return rc;
   return launch_by_dtype<kOpBinary>("elemwise_binary", fn, dtype, p, oa, ac, ob, bc, none, out, resolve_stream(stream));
 }
 
@@ -1046,6 +1063,10 @@ int32_t bsir_copy(int32_t dtype, int32_t rank, const int64_t *sizes, const void 
   bool ac;
   Operand oa = make_operand(&s, rank, sizes, &ac), none{nullptr, 0, 0, 0, 0};
   const int dt = dtype_bytes(dtype) == 8 ? BSIR_U64 : dtype_bytes(dtype) == 4 ? BSIR_U32 : dtype_bytes(dtype) == 2 ? BSIR_U16 : BSIR_U8;
+  // row-strided views (slices of a wider tensor, a destination with padded rows) and broadcasts of a row, a column or
+  // one element (hivm.hir.vbrc arrives as a copy from a stride-0 view): 16-byte vectors through rows_kernel
+  int32_t rc = BSIR_OK;
+  if (!(ac && p.out_contig) && try_rows_route(kOpCopy, 0, dt, p, oa, none, dst, stream, &rc)) return rc;
   return launch_by_dtype<kOpCopy>("copy", 0, dt, p, oa, ac, none, true, none, dst, resolve_stream(stream));
 }
 

@@ -497,6 +497,31 @@ def test_ternary_fma_bit_exact(bsir, dtype, shape):
     assert_bits_equal(out, want, f"fma {dtype} {shape}")
 
 
+@pytest.mark.parametrize("dtype", [torch.int8, torch.bfloat16, torch.float32, torch.int64])
+def test_copies_of_strided_and_broadcast_views(bsir, dtype):
+    """Slices of a wider tensor, destinations with padded rows, and broadcasts of a row, a column and one element
+    (hivm.hir.vbrc arrives as a copy from a stride-0 view) move 16-byte vectors; ragged or misaligned rows take the
+    element kernel.  Same bits either way, nothing outside the destination's rows."""
+    g = torch.Generator(device="cuda").manual_seed(9)
+    wide = torch.randint(-100, 100, (300, 512), device="cuda", generator=g).to(dtype)
+    for view in (wide[:, 64:320], wide[:, 3:200], wide[5:6].expand(300, 512), wide[:, 7:8].expand(300, 512),
+                 wide[2:3, 9:10].expand(300, 512), wide[:, 64:320].reshape(10, 30, 256)):
+        assert torch.equal(bsir.copy(view), view.contiguous())
+    padded = torch.full((300, 600), 55, device="cuda").to(dtype)
+    bsir.copy(wide, out=padded[:, 16:528])
+    assert torch.equal(padded[:, 16:528], wide)
+    assert (padded[:, :16] == 55).all() and (padded[:, 528:] == 55).all()
+
+
+def test_unary_ops_on_broadcast_operands(bsir):
+    x = torch.randn(200, 256, device="cuda")
+    for view in (x[3:4].expand(200, 256), x[:, 5:6].expand(200, 256), x[1:2, 2:3].expand(200, 256)):
+        for dt in (torch.float32, torch.bfloat16):
+            v = view.to(dt) if dt == torch.float32 else view.to(dt)
+            got = bsir.elemwise_unary("abs", v)
+            assert torch.equal(got, v.contiguous().abs())
+
+
 def test_ternary_fma_scalars_broadcasts_and_views(bsir):
     g = torch.Generator(device="cuda").manual_seed(2)
     a = torch.randn(40, 96, generator=g, device="cuda")
