@@ -513,6 +513,29 @@ def test_copies_of_strided_and_broadcast_views(bsir, dtype):
     assert (padded[:, :16] == 55).all() and (padded[:, 528:] == 55).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.int32])
+def test_broadcasts_over_three_axes_take_the_vector_kernel(bsir, dtype):
+    """[n0, n1, cols] against [n0, 1, cols], [1, n1, cols], [n0, 1, 1], [1, n1, 1], [n0, n1, 1], a strided column of a
+    wider tensor, and a batch-padded full operand: the operand's outer and row strides (either may be 0) go into the
+    kernel; results are the element kernel's bits."""
+    g = torch.Generator(device="cuda").manual_seed(4)
+    mk = (lambda *sh: torch.randint(-50, 50, sh, device="cuda", generator=g).to(dtype))
+    x = mk(6, 40, 256)
+    fn, tf = ("add", torch.add) if dtype == torch.int32 else ("mul", torch.mul)
+    for other in (mk(6, 1, 256), mk(1, 40, 256), mk(6, 1, 1), mk(1, 40, 1), mk(6, 40, 1), mk(1, 1, 256), mk(1, 1, 1),
+                  mk(6, 40, 300)[:, :, 7:8], mk(6, 64, 256)[:, :40, :], mk(8, 40, 512)[1:7, :, 256:]):
+        want = tf(x, other.expand_as(x) if other.shape != x.shape else other)
+        assert torch.equal(bsir.elemwise_binary(fn, x, other.expand_as(x)), want), f"{tuple(other.shape)} {other.stride()}"
+        assert torch.equal(bsir.elemwise_binary(fn, other.expand_as(x), x), want), f"{tuple(other.shape)} first"
+    wide = mk(240, 512)
+    col = wide[:, 5:6]                                          # one value per row, 512 elements apart
+    y = mk(240, 256)
+    assert torch.equal(bsir.elemwise_binary(fn, y, col.expand_as(y)), tf(y, col))
+    out = torch.zeros(6, 48, 256, device="cuda").to(dtype)      # a result with padded outer stride
+    bsir.elemwise_binary(fn, x, mk(6, 1, 256).expand_as(x), out=out[:, :40, :])
+    assert (out[:, 40:, :] == 0).all()
+
+
 def test_unary_ops_on_broadcast_operands(bsir):
     x = torch.randn(200, 256, device="cuda")
     for view in (x[3:4].expand(200, 256), x[:, 5:6].expand(200, 256), x[1:2, 2:3].expand(200, 256)):
