@@ -138,6 +138,112 @@ __global__ void __launch_bounds__(256) store_atomic_kernel(DmaShape s, const T *
   }
 }
 
+// ---- 16-byte-vector forms.  Both sides are [rows, n] views with unit element stride and one row stride each, the
+// destination's rows on 16-byte boundaries.  A thread takes four destination vectors of the flattened
+// [rows x vectors per row] space; every source load is issued before the first store.
+struct DmaRows {
+  int64_t rows, n;            // n: the source's last extent
+  int64_t src_rs, dst_rs;     // row strides (elements)
+};
+bool as_rows(const DmaShape &s, const void *dst, int eb, DmaRows *r) {
+  if (s.ss2 != 1 || s.ds2 != 1) return false;
+  const bool one = s.d0 == 1 || s.d1 == 1;
+  if (!one && (s.ss0 != s.d1 * s.ss1 || s.ds0 != s.d1 * s.ds1)) return false;      // the two leading axes must collapse
+  r->rows = s.d0 * s.d1;
+  r->n = s.n;
+  r->src_rs = s.d1 == 1 ? s.ss0 : s.ss1;
+  r->dst_rs = s.d1 == 1 ? s.ds0 : s.ds1;
+  if (r->rows == 1) { r->src_rs = 0; r->dst_rs = 0; }
+  return aligned_to(dst, 16) && (r->dst_rs * eb) % 16 == 0;
+}
+
+constexpr int kDmaThreads = 256;
+constexpr int kDmaUnroll = 4;
+
+template <typename T, bool SRC_VEC>
+__global__ void __launch_bounds__(kDmaThreads) load_pad_vec_kernel(DmaRows g, const T *__restrict__ src, T *__restrict__ dst, int64_t left,
+                                                                    int64_t width, int first_elem, T pad) {
+  constexpr int V = 16 / sizeof(T);
+  const int64_t vpr = (width + V - 1) / V;          // destination vectors a row; the last may be partial
+  const int64_t total = g.rows * vpr;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * (kDmaThreads * kDmaUnroll) + threadIdx.x;
+  T x[kDmaUnroll][V];
+  T fill[kDmaUnroll];
+  int64_t row[kDmaUnroll], c0[kDmaUnroll];
+#pragma unroll
+  for (int u = 0; u < kDmaUnroll; ++u) {
+    const int64_t v = base + static_cast<int64_t>(u) * kDmaThreads;
+    row[u] = -1;
+    if (v < total) {
+      row[u] = total <= 0x7fffffff ? static_cast<int64_t>(static_cast<uint32_t>(v) / static_cast<uint32_t>(vpr)) : v / vpr;
+      c0[u] = (v - row[u] * vpr) * V;
+      const T *srow = src + row[u] * g.src_rs;
+      const int64_t k0 = c0[u] - left;              // source column of the vector's first element
+      fill[u] = (first_elem && g.n > 0) ? srow[0] : pad;
+      if (SRC_VEC && k0 >= 0 && k0 + V <= g.n) {    // inside the data, and the data's vectors line up with the destination's
+        const uint4 q = *reinterpret_cast<const uint4 *>(srow + k0);
+        memcpy(x[u], &q, 16);
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const int64_t k = k0 + e;
+          x[u][e] = (k >= 0 && k < g.n) ? srow[k] : fill[u];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kDmaUnroll; ++u) {
+    if (row[u] < 0) continue;
+    T *d = dst + row[u] * g.dst_rs + c0[u];
+    if (c0[u] + V <= width) {
+      uint4 q;
+      memcpy(&q, x[u], 16);
+      *reinterpret_cast<uint4 *>(d) = q;
+    } else {                                         // the row's last, partial vector: nothing beyond `width` is written
+      for (int e = 0; e < V && c0[u] + e < width; ++e) d[e] = x[u][e];
+    }
+  }
+}
+
+// out += x with one reduction of 16 bytes a vector (f32: four adds, f16 / bf16: eight, each rounded as the scalar
+// atomic rounds it)
+template <typename T>
+__device__ __forceinline__ void red_add_vec(T *p, uint4 q) {
+  if constexpr (std::is_same<T, float>::value)
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(__uint_as_float(q.x)), "f"(__uint_as_float(q.y)),
+                 "f"(__uint_as_float(q.z)), "f"(__uint_as_float(q.w))
+                 : "memory");
+  else if constexpr (std::is_same<T, __half>::value)
+    asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(q.x), "r"(q.y), "r"(q.z), "r"(q.w) : "memory");
+  else
+    asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(q.x), "r"(q.y), "r"(q.z), "r"(q.w) : "memory");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kDmaThreads) store_add_vec_kernel(DmaRows g, const T *__restrict__ src, T *dst) {
+  constexpr int V = 16 / sizeof(T);
+  const int64_t vpr = g.n / V;
+  const int64_t total = g.rows * vpr;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * (kDmaThreads * kDmaUnroll) + threadIdx.x;
+  uint4 q[kDmaUnroll];
+  int64_t off[kDmaUnroll];
+#pragma unroll
+  for (int u = 0; u < kDmaUnroll; ++u) {
+    const int64_t v = base + static_cast<int64_t>(u) * kDmaThreads;
+    off[u] = -1;
+    if (v < total) {
+      const int64_t row = total <= 0x7fffffff ? static_cast<int64_t>(static_cast<uint32_t>(v) / static_cast<uint32_t>(vpr)) : v / vpr;
+      const int64_t c = (v - row * vpr) * V;
+      off[u] = row * g.dst_rs + c;
+      q[u] = *reinterpret_cast<const uint4 *>(src + row * g.src_rs + c);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kDmaUnroll; ++u)
+    if (off[u] >= 0) red_add_vec<T>(dst + off[u], q[u]);
+}
+
 dim3 dma_grid(int64_t width, int64_t rows) {
   int64_t bx = ceil_div(width, 256);
   if (bx > 1024) bx = 1024;
@@ -150,6 +256,22 @@ int32_t launch_load(const DmaShape &s, const void *src, void *dst, int64_t left,
                     const void *pad_value, cudaStream_t st) {
   T pad{};
   if (pad_value) memcpy(&pad, pad_value, sizeof(T));
+  DmaRows g;
+  constexpr int V = 16 / sizeof(T);
+  const int64_t width = left + s.n + right;
+  if (as_rows(s, dst, sizeof(T), &g) && width >= V) {
+    const int64_t total = g.rows * ceil_div(width, static_cast<int64_t>(V));
+    const int64_t blocks = ceil_div(total, static_cast<int64_t>(kDmaThreads) * kDmaUnroll);
+    if (blocks <= 0x7fffffffLL) {
+      // the data's 16-byte vectors line up with the destination's when the left padding is whole vectors and the
+      // source rows start on 16-byte boundaries
+      const bool src_vec = left % V == 0 && aligned_to(src, 16) && (g.src_rs * sizeof(T)) % 16 == 0;
+      if (src_vec) load_pad_vec_kernel<T, true><<<static_cast<unsigned>(blocks), kDmaThreads, 0, st>>>(g, static_cast<const T *>(src), static_cast<T *>(dst), left, width, first_elem, pad);
+      else load_pad_vec_kernel<T, false><<<static_cast<unsigned>(blocks), kDmaThreads, 0, st>>>(g, static_cast<const T *>(src), static_cast<T *>(dst), left, width, first_elem, pad);
+      count_launch();
+      return check_launch("load");
+    }
+  }
   load_pad_kernel<T><<<dma_grid(left + s.n + right, s.d0 * s.d1), 256, 0, st>>>(s, static_cast<const T *>(src), static_cast<T *>(dst), left, right,
                                                                              first_elem, pad);
   count_launch();
@@ -158,6 +280,18 @@ int32_t launch_load(const DmaShape &s, const void *src, void *dst, int64_t left,
 
 template <typename T, int KIND>
 int32_t launch_store(const DmaShape &s, const void *src, void *dst, cudaStream_t st) {
+  if constexpr (KIND == BSIR_ATOMIC_ADD && (std::is_same<T, float>::value || std::is_same<T, __half>::value || std::is_same<T, __nv_bfloat16>::value)) {
+    DmaRows g;
+    constexpr int V = 16 / sizeof(T);
+    if (as_rows(s, dst, sizeof(T), &g) && s.n % V == 0 && aligned_to(src, 16) && (g.src_rs * sizeof(T)) % 16 == 0) {
+      const int64_t blocks = ceil_div(g.rows * (s.n / V), static_cast<int64_t>(kDmaThreads) * kDmaUnroll);
+      if (blocks <= 0x7fffffffLL) {
+        store_add_vec_kernel<T><<<static_cast<unsigned>(blocks), kDmaThreads, 0, st>>>(g, static_cast<const T *>(src), static_cast<T *>(dst));
+        count_launch();
+        return check_launch("store");
+      }
+    }
+  }
   store_atomic_kernel<T, KIND><<<dma_grid(s.n, s.d0 * s.d1), 256, 0, st>>>(s, static_cast<const T *>(src), static_cast<T *>(dst));
   count_launch();
   return check_launch("store");

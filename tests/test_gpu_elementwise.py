@@ -272,6 +272,28 @@ def test_store_atomic_kinds(bsir, dtype, kinds):
         bsir.store(src, out, atomic="cas")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+def test_load_and_atomic_add_on_row_strided_views(bsir, dtype):
+    """Rows of wider tensors on both sides (16-byte aligned: the vector kernels) and from an odd column (the element
+    kernels): a padded load and an adding store, against the oracle; nothing outside the views changes."""
+    src_wide = _rand((50, 640), dtype, seed=11)
+    for c0 in (64, 3):
+        src = src_wide[:, c0:c0 + 256]
+        dst_wide = _rand((50, 512), dtype, seed=12)
+        before = dst_wide.clone()
+        bsir.load(src, dst_wide[:, 128:448], pad_mode="value", pad_value=1.5, left_padding_num=32, right_padding_num=32)
+        want = O.load_pad(oracle_dtype(src), to_bits(src.contiguous()), to_bits(before[:, 128:448].contiguous()), "value",
+                          to_bits(torch.tensor([1.5], dtype=dtype)), 32, 32)
+        assert_bits_equal(dst_wide[:, 128:448].contiguous(), want.reshape(50, 320), f"strided load from column {c0}")
+        assert torch.equal(dst_wide[:, :128], before[:, :128]) and torch.equal(dst_wide[:, 448:], before[:, 448:])
+        acc_wide = _rand((50, 512), dtype, seed=13)
+        before = acc_wide.clone()
+        bsir.store(src, acc_wide[:, 64:320], atomic="add")
+        want = O.store_atomic(oracle_dtype(src), "add", to_bits(src.contiguous()), to_bits(before[:, 64:320].contiguous()))
+        assert_bits_equal(acc_wide[:, 64:320].contiguous(), want.reshape(50, 256), f"strided adding store from column {c0}")
+        assert torch.equal(acc_wide[:, :64], before[:, :64]) and torch.equal(acc_wide[:, 320:], before[:, 320:])
+
+
 def test_store_atomic_adds_up_over_calls(bsir):
     acc = torch.zeros(4, 257, dtype=torch.int32, device="cuda")
     parts = [torch.randint(-100, 100, (4, 257), dtype=torch.int32, device="cuda") for _ in range(5)]
