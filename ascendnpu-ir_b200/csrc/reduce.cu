@@ -1034,9 +1034,13 @@ __global__ void __launch_bounds__(256, 4) rwi_stream_kernel(RwiParams p, const v
 // Short rows (at most 64 vectors): `gs` lanes (4, 8, 16 or 32) share a row, so a warp holds 32 / gs rows and
 // every lane has a load in flight; no shared memory, no barrier; a lane holds up to two vectors.  Same
 // result as the kernels above.
-template <int DT, bool IS_MAX>
+template <int DT, bool IS_MAX, int NV>
 __global__ void __launch_bounds__(256) rwi_warp_kernel(RwiParams p, int gs, const void *__restrict__ src,
                                                        void *__restrict__ dst_val, int32_t *__restrict__ dst_idx) {
+  // gs lanes share a row, each holding up to NV of its 16-byte vectors; no block-wide barrier anywhere.  The common
+  // row has no NaN: its extreme comes from packed max / min (16-bit types), the position from a second look at the
+  // registers by the lanes that hold the extreme, and nothing else runs.  maximum / minimum propagate NaN, so a NaN
+  // anywhere in a row shows in its extreme, and only then is the prefix before the first NaN searched.
   constexpr int kPerWord = FloatTraits<DT>::kPerWord;
   constexpr int kPerVec = 4 * kPerWord;
   using E = typename std::conditional<DT == BSIR_F32, float, uint16_t>::type;
@@ -1047,16 +1051,16 @@ __global__ void __launch_bounds__(256) rwi_warp_kernel(RwiParams p, int gs, cons
   const bool row_ok = row < p.rows;                           // lanes of missing rows still take part in the shuffles
   const float ident = IS_MAX ? __int_as_float(0xff800000) : __int_as_float(0x7f800000);
   const Vec16 *xv = reinterpret_cast<const Vec16 *>(static_cast<const E *>(src) + (row_ok ? row : 0) * p.row_stride);
-  Vec16 v[2];
-  bool have[2];
+  Vec16 v[NV];
+  bool have[NV];
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < NV; ++i) {
     have[i] = row_ok && sl + gs * i < p.nvec;
     if (have[i]) v[i] = ld_stream(xv + sl + gs * i);
   }
   auto for_each = [&](auto f) {   // f(row index of the element, its value)
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < NV; ++i)
       if (have[i]) {
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
@@ -1084,7 +1088,34 @@ __global__ void __launch_bounds__(256) rwi_warp_kernel(RwiParams p, int gs, cons
     return b;
   };
   float tm = ident;
-  for_each([&](int, float e) { tm = ext_nan<IS_MAX>(tm, e); });
+  if constexpr (kPerWord == 2) {   // 16-bit types stay packed: one max / min.NaN.x2 per word
+    constexpr uint32_t kIdent2 = DT == BSIR_BF16 ? (IS_MAX ? 0xff80ff80u : 0x7f807f80u) : (IS_MAX ? 0xfc00fc00u : 0x7c007c00u);
+    uint32_t m2 = kIdent2;
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (have[i]) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          if constexpr (DT == BSIR_BF16) {
+            if constexpr (IS_MAX) asm("max.NaN.bf16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
+            else asm("min.NaN.bf16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
+          } else {
+            if constexpr (IS_MAX) asm("max.NaN.f16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
+            else asm("min.NaN.f16x2 %0, %1, %2;" : "=r"(m2) : "r"(m2), "r"(v[i].w[w]));
+          }
+        }
+      }
+    float e2[2];
+    FloatTraits<DT>::unpack(m2, e2);
+    tm = ext_nan<IS_MAX>(e2[0], e2[1]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (have[i]) {
+#pragma unroll
+        for (int w = 0; w < 4; ++w) tm = ext_nan<IS_MAX>(tm, __uint_as_float(v[i].w[w]));
+      }
+  }
   float m = group_ext(tm);
   // rows of one warp may differ in whether they hold a NaN: both searches run for all lanes, each row
   // keeps the one that applies to it
@@ -1092,14 +1123,14 @@ __global__ void __launch_bounds__(256) rwi_warp_kernel(RwiParams p, int gs, cons
   if (m == m && tm == m) for_each([&](int gi, float e) { if (e == m) best = p.tie_left ? min(best, gi) : max(best, gi); });
   best = group_pick(best);
   int nanpos = INT_MAX;
-  for_each([&](int gi, float e) { if (e != e) nanpos = min(nanpos, gi); });
+  if (__any_sync(0xffffffffu, m != m)) {
+    // some row holds a NaN: its first position, the extreme of the prefix before it and that extreme's position
+    for_each([&](int gi, float e) { if (e != e) nanpos = min(nanpos, gi); });
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const int other = __shfl_xor_sync(0xffffffffu, nanpos, o);
-    if (o < gs) nanpos = min(nanpos, other);
-  }
-  if (__any_sync(0xffffffffu, nanpos != INT_MAX)) {
-    // some row holds a NaN: the extreme of its prefix before the first NaN and that extreme's position
+    for (int o = 16; o > 0; o >>= 1) {
+      const int other = __shfl_xor_sync(0xffffffffu, nanpos, o);
+      if (o < gs) nanpos = min(nanpos, other);
+    }
     float tm2 = ident;
     for_each([&](int gi, float e) { if (gi < nanpos) tm2 = ext_nan<IS_MAX>(tm2, e); });
     const float m2 = group_ext(tm2);
@@ -1248,21 +1279,34 @@ int32_t bsir_reduce_with_index(int32_t kind, int32_t dtype, int32_t tie_break_le
   // short rows: one warp per row, any number of rows in one launch
   if (rows > 0 && cols > 0 && src && dst_value && dst_index) {
     const int eb0 = dtype_bytes(dtype), pv0 = 16 / eb0;
-    if (cols % pv0 == 0 && cols / pv0 <= 64 && src_row_stride >= cols && aligned_to(src, 16) && (src_row_stride * eb0) % 16 == 0 &&
+    // up to two vectors a lane for any number of rows; up to four (a row of 128 vectors: 1024 bf16) when there are rows
+    // enough to fill every SM with warps.  Beyond that a block a row wins: every row's warp has to look through its
+    // registers for the position of the extreme, which in a block only the one warp that holds it does (measured on
+    // bf16 [32768,4096]: 68 us with sixteen vectors a lane against 56 us with a block a row).
+    const int sms0 = device_info().sm_count > 0 ? device_info().sm_count : 148;
+    const int64_t nvec0 = cols % pv0 == 0 ? cols / pv0 : 0;
+    const bool many_rows = rows >= static_cast<int64_t>(sms0) * 64;
+    if (nvec0 > 0 && (nvec0 <= 64 || (many_rows && nvec0 <= 128)) && src_row_stride >= cols &&
+        aligned_to(src, 16) && (src_row_stride * eb0) % 16 == 0 &&
         aligned_to(dst_value, eb0) && aligned_to(dst_index, 4) && rows <= 0x7fffffffLL * 8) {
       RwiParams q{};
       q.rows = rows; q.cols = cols; q.row_stride = src_row_stride; q.nvec = cols / pv0; q.nseg = 1;
       q.tie_left = tie_break_left ? 1 : 0;
       q.nan_first = nan_mode == BSIR_RWI_NAN_FIRST;
       cudaStream_t st0 = resolve_stream(stream);
-      int gs = 4;                                           // lanes per row: each lane holds up to two vectors
+      int gs = 4;                                           // lanes per row: each lane holds up to two vectors ...
       while (gs < 32 && q.nvec > 2 * gs) gs <<= 1;
+      int nv = 2;                                           // ... or, with a whole warp on the row, up to four
+      while (nv < 4 && q.nvec > static_cast<int64_t>(nv) * gs) nv <<= 1;
       const unsigned blocks = static_cast<unsigned>(ceil_div(rows, 8 * (32 / gs)));
       const bool mx = kind == BSIR_RWI_MAX;
-#define W(D)                                                                                        \
-  if (mx) rwi_warp_kernel<D, true><<<blocks, 256, 0, st0>>>(q, gs, src, dst_value, dst_index);        \
-  else rwi_warp_kernel<D, false><<<blocks, 256, 0, st0>>>(q, gs, src, dst_value, dst_index);
+#define W2(D, NV)                                                                                       \
+  if (mx) rwi_warp_kernel<D, true, NV><<<blocks, 256, 0, st0>>>(q, gs, src, dst_value, dst_index);        \
+  else rwi_warp_kernel<D, false, NV><<<blocks, 256, 0, st0>>>(q, gs, src, dst_value, dst_index);
+#define W(D) \
+  if (nv == 2) { W2(D, 2) } else { W2(D, 4) }
       if (dtype == BSIR_F32) { W(BSIR_F32) } else if (dtype == BSIR_F16) { W(BSIR_F16) } else { W(BSIR_BF16) }
+#undef W2
 #undef W
       count_launch();
       return check_launch("reduce_with_index");

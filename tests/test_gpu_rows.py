@@ -247,7 +247,7 @@ def _check_rwi(bsir, x, kind="max", left=True, nan_mode="region"):
     assert_bits_equal(v, wv, "values")
 
 
-@pytest.mark.parametrize("rows,cols", [(1, 8), (5, 100), (3, 4096), (4, 152064), (2, 300000), (300, 2048), (2, 9)])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (5, 100), (3, 4096), (4, 152064), (2, 300000), (300, 2048), (2, 9), (9600, 1024), (9500, 768)])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("kind", ["max", "min"])
 def test_argmax_shapes(bsir, rows, cols, dtype, kind):
@@ -328,9 +328,11 @@ def test_argmax_long_rows_streaming_path(bsir, dtype, rows):
 
 
 @pytest.mark.parametrize("dtype,cols", [(torch.bfloat16, 64), (torch.bfloat16, 256), (torch.bfloat16, 512), (torch.float16, 8),
-                                        (torch.float32, 256), (torch.float32, 4)])
+                                        (torch.float32, 256), (torch.float32, 4), (torch.bfloat16, 1024), (torch.float16, 776),
+                                        (torch.float32, 512)])
 def test_argmax_short_rows_warp_per_row(bsir, dtype, cols):
-    """Rows of at most 64 vectors take the warp-per-row kernel: many rows, planted ties, zeros, -inf, NaNs."""
+    """Rows of at most 64 vectors -- 128 when the rows fill the SMs, as here -- take the warp-per-row kernel: many rows,
+    planted ties, zeros, -inf, NaNs."""
     rows = 70001                                   # more rows than a grid dimension of 65535
     g = torch.Generator(device="cuda").manual_seed(cols)
     x = torch.randn(rows, cols, device="cuda", generator=g).clamp(-3, 3).to(dtype)
