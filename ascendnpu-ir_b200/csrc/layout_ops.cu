@@ -22,17 +22,48 @@ struct ChannelPtrs {
   void *out[kMaxChannels];
 };
 
+// 4-byte elements into rows that start on 16-byte boundaries: a thread writes four consecutive values as one vector
+template <typename T>
+__global__ void __launch_bounds__(256) arange_vec4_kernel(T *dst, int64_t n0, int64_t n1, int64_t n2, int64_t d0, int64_t d1,
+                                                          int64_t offset, int64_t s0, int64_t s1, int64_t s2) {
+  static_assert(sizeof(T) == 4, "four elements a 16-byte vector");
+  for (int64_t row = blockIdx.y; row < n0 * n1; row += gridDim.y) {
+    const int64_t i0 = row / n1, i1 = row - i0 * n1;
+    const int64_t v0 = offset + i0 * s0 + i1 * s1;
+    T *drow = dst + i0 * d0 + i1 * d1;
+    for (int64_t q = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; q * 4 < n2; q += static_cast<int64_t>(gridDim.x) * 256) {
+      T out[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) out[e] = static_cast<T>(v0 + (q * 4 + e) * s2);
+      uint4 w;
+      memcpy(&w, out, 16);
+      *reinterpret_cast<uint4 *>(drow + q * 4) = w;
+    }
+  }
+}
+
+// a block row of the grid per (i0, i1), threads along i2: one division a row, none an element
 template <typename T>
 __global__ void __launch_bounds__(256) arange_kernel(T *dst, int64_t n0, int64_t n1, int64_t n2, int64_t d0, int64_t d1, int64_t d2,
                                                      int64_t offset, int64_t s0, int64_t s1, int64_t s2) {
-  const int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (e >= n0 * n1 * n2) return;
-  const int64_t i2 = e % n2, i1 = (e / n2) % n1, i0 = e / (n2 * n1);
-  const int64_t v = offset + i0 * s0 + i1 * s1 + i2 * s2;
-  T out;
-  if constexpr (std::is_same<T, __half>::value) out = __float2half_rn(static_cast<float>(v));
-  else out = static_cast<T>(v);
-  dst[i0 * d0 + i1 * d1 + i2 * d2] = out;
+  for (int64_t row = blockIdx.y; row < n0 * n1; row += gridDim.y) {
+    const int64_t i0 = row / n1, i1 = row - i0 * n1;
+    const int64_t v0 = offset + i0 * s0 + i1 * s1;
+    T *drow = dst + i0 * d0 + i1 * d1;
+    for (int64_t c = static_cast<int64_t>(blockIdx.x) * 1024 + threadIdx.x; c < n2; c += static_cast<int64_t>(gridDim.x) * 1024) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int64_t i2 = c + u * 256;
+        if (i2 < n2) {
+          const int64_t v = v0 + i2 * s2;
+          T out;
+          if constexpr (std::is_same<T, __half>::value) out = __float2half_rn(static_cast<float>(v));
+          else out = static_cast<T>(v);
+          drow[i2 * d2] = out;
+        }
+      }
+    }
+  }
 }
 
 // The operands are contiguous, so interleaving the last axis of [rows, cols] is interleaving the flat arrays:
@@ -182,7 +213,19 @@ extern "C" int32_t bsir_arange(int32_t dtype, int32_t rank, const int64_t *sizes
   if (!aligned_to(dst, dtype_bytes(dtype))) return fail(BSIR_ERR_ALIGN, "arange: misaligned");
   if (ceil_div(total, 256) > 0x7fffffffLL) return fail(BSIR_ERR_SHAPE, "arange: too many elements");
   cudaStream_t st = resolve_stream(stream);
-  const unsigned blocks = static_cast<unsigned>(ceil_div(total, 256));
+  int64_t bx = ceil_div(n[2], static_cast<int64_t>(1024)), by = n[0] * n[1];
+  if (bx > 4096) bx = 4096;
+  if (by > 65535) by = 65535;                    // the kernel loops over what the grid does not cover
+  const dim3 blocks(static_cast<unsigned>(bx), static_cast<unsigned>(by));
+  if ((dtype == BSIR_I32 || dtype == BSIR_F32) && d[2] == 1 && n[2] % 4 == 0 && aligned_to(dst, 16) && d[1] % 4 == 0 && d[0] % 4 == 0) {
+    int64_t vx = ceil_div(n[2] / 4, static_cast<int64_t>(256));
+    if (vx > 4096) vx = 4096;
+    const dim3 vblocks(static_cast<unsigned>(vx), static_cast<unsigned>(by));
+    if (dtype == BSIR_I32) arange_vec4_kernel<int32_t><<<vblocks, 256, 0, st>>>(static_cast<int32_t *>(dst), n[0], n[1], n[2], d[0], d[1], offset, s[0], s[1], s[2]);
+    else arange_vec4_kernel<float><<<vblocks, 256, 0, st>>>(static_cast<float *>(dst), n[0], n[1], n[2], d[0], d[1], offset, s[0], s[1], s[2]);
+    count_launch();
+    return check_launch("arange");
+  }
   switch (dtype) {
     case BSIR_I16: arange_kernel<int16_t><<<blocks, 256, 0, st>>>(static_cast<int16_t *>(dst), n[0], n[1], n[2], d[0], d[1], d[2], offset, s[0], s[1], s[2]); break;
     case BSIR_I32: arange_kernel<int32_t><<<blocks, 256, 0, st>>>(static_cast<int32_t *>(dst), n[0], n[1], n[2], d[0], d[1], d[2], offset, s[0], s[1], s[2]); break;
