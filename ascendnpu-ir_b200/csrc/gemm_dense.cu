@@ -72,6 +72,10 @@ struct GemmParams {
   uint32_t launch_tag;
   int dk_levels, dk_len, dk_helpers;   // 0 levels: whole tiles, no scratch
   int dk_vec_out;                      // 1: 16-byte stores of C (n and ldo multiples of 8, 16-byte aligned bases)
+  // single-CTA kernel over a batch of products in one launch: the tensor maps are then rank 3 (z = the product) and
+  // tile t belongs to product t / (m_tiles * n_tiles); 0 or 1: one product, rank-2 maps
+  int batch;
+  int64_t out_bs;                      // elements between the outputs of consecutive products
 #ifdef BSIR_DEC_TIMELINE
   unsigned long long *tl;
 #endif
@@ -186,12 +190,21 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, int x, int 
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int x, int y, int z, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(reinterpret_cast<uint64_t>(map)),
+               "r"(x), "r"(y), "r"(z), "r"(src)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// zb: the product of a batched launch this tile belongs to (-1: one product, rank-2 output map)
 template <int KIND, int BN>
 __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const CUtensorMap *tmap_out, uint32_t t_row,
                                               int64_t row, int64_t row_warp0, int64_t n0, int lane, uint8_t *stage_gen,
                                               uint32_t stage_addr, const float *sw_s, const uint32_t *bias_s,
-                                              uint32_t &nstores) {
+                                              uint32_t &nstores, int zb = -1) {
   const bool row_ok = row < p.m;
+  const int64_t out_off = zb > 0 ? static_cast<int64_t>(zb) * p.out_bs : 0;   // in elements of the output
   const float sa = (p.scale_a && row_ok) ? p.scale_a[row] : 1.0f;
 #pragma unroll 1
   for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -248,11 +261,14 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const CUtenso
               make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) tma_store_2d(tmap_out, static_cast<int>(col0), static_cast<int>(row_warp0), stage_addr + b * kEpiStageBytes);
+        if (lane == 0) {
+          if (zb >= 0) tma_store_3d(tmap_out, static_cast<int>(col0), static_cast<int>(row_warp0), zb, stage_addr + b * kEpiStageBytes);
+          else tma_store_2d(tmap_out, static_cast<int>(col0), static_cast<int>(row_warp0), stage_addr + b * kEpiStageBytes);
+        }
         ++nstores;
       } else if (row_ok) {
         for (int d = 0; d < out_count(p); ++d) {
-          uint16_t *dst = static_cast<uint16_t *>(out_base(p, d)) + row * p.ldo + col0;
+          uint16_t *dst = static_cast<uint16_t *>(out_base(p, d)) + out_off + row * p.ldo + col0;
           if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
             for (int j = 0; j < 16; j += 4)
@@ -276,7 +292,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const CUtenso
           packed[j >> 2] = w;
         }
         for (int d = 0; d < out_count(p); ++d) {
-          uint8_t *dst = static_cast<uint8_t *>(out_base(p, d)) + row * p.ldo + col0;
+          uint8_t *dst = static_cast<uint8_t *>(out_base(p, d)) + out_off + row * p.ldo + col0;
           if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
             *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
@@ -294,7 +310,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams &p, const CUtenso
             else o[e] = __float_as_uint(scale_relu(acc_plus_bias<KIND>(r[j + e], bias_s[c0 + j + e]), sa, sw_s[c0 + j + e], p.relu));
           }
           for (int d = 0; d < out_count(p); ++d) {
-            uint32_t *dst = static_cast<uint32_t *>(out_base(p, d)) + row * p.ldo + col0;
+            uint32_t *dst = static_cast<uint32_t *>(out_base(p, d)) + out_off + row * p.ldo + col0;
             if (full && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
               *reinterpret_cast<uint4 *>(dst + j) = make_uint4(o[0], o[1], o[2], o[3]);
             } else {
@@ -364,7 +380,9 @@ __global__ void __launch_bounds__(kThreads + 32, 1)
   constexpr int kIssuers = KIND == KI8 ? 2 : 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int tiles_per = p.m_tiles * p.n_tiles;           // of one product
+  const bool batched = p.batch > 1;
+  const int total_tiles = tiles_per * (batched ? p.batch : 1);
 
   pdl_launch_dependents();   // the set-up below overlaps the tail of the kernel ahead (see launch_pdl)
   if (threadIdx.x == 0) {
@@ -390,8 +408,14 @@ __global__ void __launch_bounds__(kThreads + 32, 1)
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % p.m_tiles) * kBM;
-        const int n0 = (tile / p.m_tiles) * BN;
+        const int zb = tile / tiles_per, t = tile - zb * tiles_per;
+        const int m0 = (t % p.m_tiles) * kBM;
+        const int n0 = (t / p.m_tiles) * BN;
+        // one product: rank-2 maps; a batch: rank-3 maps, the product is the third coordinate
+        auto load = [&](uint32_t dst, const CUtensorMap *map, int x, int y) {
+          if (batched) tma_load_3d(dst, map, x, y, zb, full_bar(stage));
+          else tma_load_2d(dst, map, x, y, full_bar(stage));
+        };
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.err)) { ok = false; break; }
           const uint32_t sa = base + stage * Cfg::kStage;
@@ -400,19 +424,19 @@ __global__ void __launch_bounds__(kThreads + 32, 1)
           if constexpr (A_MN) {
             // A is [k, m]: chunks of [kKr k rows x 128 m bytes]
 #pragma unroll
-            for (int c = 0; c < kBM * kEs / 128; ++c) tma_load_2d(sa + c * (kKr * 128), &tmap_a, m0 * kEs + c * 128, kb * kKr, full_bar(stage));
+            for (int c = 0; c < kBM * kEs / 128; ++c) load(sa + c * (kKr * 128), &tmap_a, m0 * kEs + c * 128, kb * kKr);
           } else {
-            tma_load_2d(sa, &tmap_a, kb * kBK, m0, full_bar(stage));   // [128 m rows x 128 k bytes]
+            load(sa, &tmap_a, kb * kBK, m0);   // [128 m rows x 128 k bytes]
           }
           if constexpr (B_MN) {
             // B is [k, n]: chunks of [kKr k rows x 128 n bytes]
 #pragma unroll
-            for (int c = 0; c < BN * kEs / 128; ++c) tma_load_2d(sb + c * (kKr * 128), &tmap_b, n0 * kEs + c * 128, kb * kKr, full_bar(stage));
+            for (int c = 0; c < BN * kEs / 128; ++c) load(sb + c * (kKr * 128), &tmap_b, n0 * kEs + c * 128, kb * kKr);
           } else {
             // B is [n, k]: boxes of [128 n rows x 128 k bytes]
 #pragma unroll
             for (int c = 0; c < (BN + 127) / 128; ++c)
-              tma_load_2d(sb + c * (128 * kBK), &tmap_b, kb * kBK, n0 + c * 128, full_bar(stage));
+              load(sb + c * (128 * kBK), &tmap_b, kb * kBK, n0 + c * 128);
           }
           if (++stage == Cfg::kStages) { stage = 0; phase ^= 1u; }
         }
@@ -487,15 +511,17 @@ __global__ void __launch_bounds__(kThreads + 32, 1)
     uint32_t acc_phase[2] = {0u, 0u};
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const int64_t m0 = static_cast<int64_t>(tile % p.m_tiles) * kBM;
-      const int64_t n0 = static_cast<int64_t>(tile / p.m_tiles) * BN;
+      const int zb = tile / tiles_per, t = tile - zb * tiles_per;
+      const int64_t m0 = static_cast<int64_t>(t % p.m_tiles) * kBM;
+      const int64_t n0 = static_cast<int64_t>(t / p.m_tiles) * BN;
       float *sw_s = sw_all + ((warp - 2) * 2 + acc) * BN;
       uint32_t *bias_s = bias_all + ((warp - 2) * 2 + acc) * BN;
       stage_scales<KIND, BN>(p, n0, sw_s, bias_s, lane);         // overlaps the tile's main loop
       if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, p.err)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN);
-      epilogue_tile<KIND, BN>(p, &tmap_out, t_row, m0 + row_in_tile, m0 + quad * 32, n0, lane, stage_gen, stage_addr, sw_s, bias_s, nstores);
+      epilogue_tile<KIND, BN>(p, &tmap_out, t_row, m0 + row_in_tile, m0 + quad * 32, n0, lane, stage_gen, stage_addr, sw_s, bias_s, nstores,
+                              batched ? zb : -1);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));  // 4 arrivals (one per epilogue warp) free the buffer
@@ -1201,15 +1227,38 @@ bool make_tmap(CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t outer
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The same maps over a batch of matrices `bstride` bytes apart (rank 3, one matrix a box).
+bool make_tmap3(CUtensorMap *map, const void *ptr, uint64_t inner, uint64_t outer, uint64_t batch, uint64_t pitch, uint64_t bstride,
+                uint32_t box_rows) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {inner, outer, batch};
+  cuuint64_t strides[2] = {pitch, bstride};
+  cuuint32_t box[3] = {128u, box_rows, 1u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+bool make_out_tmap3(CUtensorMap *map, void *ptr, uint64_t n, uint64_t m, uint64_t batch, uint64_t ldo, uint64_t out_bs) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {n, m, batch};
+  cuuint64_t strides[2] = {ldo * 2u, out_bs * 2u};
+  cuuint32_t box[3] = {32u, 32u, 1u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 3, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int KIND, int BN, bool A_MN, bool B_MN>
 int32_t launch_tc(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tout, GemmParams p, cudaStream_t st) {
   using Cfg = TileCfg<BN>;
   // the attribute is per device and cheap to set
   cudaFuncSetAttribute(gemm_tc_kernel<KIND, BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
   p.n_tiles = static_cast<int>(ceil_div(p.n, BN));
-  const int total = p.m_tiles * p.n_tiles;
+  const int64_t total = static_cast<int64_t>(p.m_tiles) * p.n_tiles * (p.batch > 1 ? p.batch : 1);
   int grid = device_info().sm_count > 0 ? device_info().sm_count : 148;
-  if (grid > total) grid = total;
+  if (grid > total) grid = static_cast<int>(total);
   launch_pdl(gemm_tc_kernel<KIND, BN, A_MN, B_MN>, dim3(grid), dim3(kThreads + 32), Cfg::kSmemBytes, st, ta, tb, tout, p);
   count_launch();
   return check_launch("matmul");
@@ -1236,8 +1285,8 @@ int32_t launch_pair(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensor
 }
 
 // Tile width: the widest N tile whose tile count still covers the SMs reasonably.
-int pick_bn(int64_t m, int64_t n, int sm_count, bool b_mn) {
-  const int64_t m_tiles = ceil_div(m, kBM);
+int pick_bn(int64_t m, int64_t n, int sm_count, bool b_mn, int64_t batch = 1) {
+  const int64_t m_tiles = ceil_div(m, kBM) * batch;
   const int min_bn = b_mn ? 128 : 64;
   int best = 256;
   double best_eff = -1.0;
@@ -1259,6 +1308,41 @@ struct Operands {
   int64_t ldb;
   int transpose_b;
 };
+
+// `batch` products of one shape, `bsa` / `bsb` / `p.out_bs` elements apart, in one launch of the single-CTA kernel over
+// rank-3 tensor maps.  false: not possible here (alignment, no encoder, tiles too many for int) -- the caller then
+// launches product by product.
+template <int KIND>
+bool run_gemm_batched(GemmParams p, const Operands &o, int64_t batch, int64_t bsa, int64_t bsb, cudaStream_t st, int32_t *rc) {
+  constexpr int es = kEsize<KIND>;
+  const int64_t m = p.m, n = p.n, k = p.k;
+  p.m_tiles = static_cast<int>(ceil_div(m, kBM));
+  p.k_blocks = static_cast<int>(ceil_div(k * es, kBK));
+  const bool a_mn = o.transpose_a != 0, b_mn = o.transpose_b == 0;
+  if (!(k > 0 && device_info().cc_major >= 10 && aligned_to(o.a, 16) && aligned_to(o.b, 16) && (o.lda * es) % 16 == 0 &&
+        (o.ldb * es) % 16 == 0 && (bsa * es) % 16 == 0 && (bsb * es) % 16 == 0 && encode_fn() != nullptr && batch <= 65535))
+    return false;
+  const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
+  const int bn = pick_bn(m, n, sms, b_mn, batch);
+  if (static_cast<int64_t>(p.m_tiles) * ceil_div(n, bn) * batch > 0x3fffffffLL) return false;
+  CUtensorMap ta, tb, tout;
+  memset(&tout, 0, sizeof(tout));
+  const bool out16 = p.out_dtype == BSIR_BF16 || p.out_dtype == BSIR_F16;
+  p.tma_out = (p.out && out16 && aligned_to(p.out, 16) && p.ldo % 8 == 0 && p.out_bs % 8 == 0 &&
+               make_out_tmap3(&tout, p.out, static_cast<uint64_t>(n), static_cast<uint64_t>(m), static_cast<uint64_t>(batch),
+                              static_cast<uint64_t>(p.ldo), static_cast<uint64_t>(p.out_bs))) ? 1 : 0;
+  const uint32_t kr = static_cast<uint32_t>(kBK / es);
+  const uint64_t ub = static_cast<uint64_t>(batch);
+  bool ok = a_mn ? make_tmap3(&ta, o.a, static_cast<uint64_t>(m) * es, static_cast<uint64_t>(k), ub, static_cast<uint64_t>(o.lda) * es, static_cast<uint64_t>(bsa) * es, kr)
+                 : make_tmap3(&ta, o.a, static_cast<uint64_t>(k) * es, static_cast<uint64_t>(m), ub, static_cast<uint64_t>(o.lda) * es, static_cast<uint64_t>(bsa) * es, kBM);
+  if (b_mn) ok = ok && make_tmap3(&tb, o.b, static_cast<uint64_t>(n) * es, static_cast<uint64_t>(k), ub, static_cast<uint64_t>(o.ldb) * es, static_cast<uint64_t>(bsb) * es, kr);
+  else ok = ok && make_tmap3(&tb, o.b, static_cast<uint64_t>(k) * es, static_cast<uint64_t>(n), ub, static_cast<uint64_t>(o.ldb) * es, static_cast<uint64_t>(bsb) * es, bn < 128 ? bn : 128);
+  if (!ok) return false;
+  p.batch = static_cast<int>(batch);
+  if (a_mn) *rc = b_mn ? launch_tc_bn<KIND, true, true>(bn, ta, tb, tout, p, st) : launch_tc_bn<KIND, true, false>(bn, ta, tb, tout, p, st);
+  else *rc = b_mn ? launch_tc_bn<KIND, false, true>(bn, ta, tb, tout, p, st) : launch_tc_bn<KIND, false, false>(bn, ta, tb, tout, p, st);
+  return true;
+}
 
 // One [m, k] x [k, n] product.  p holds the epilogue; sizes are validated by the callers.
 template <int KIND>
@@ -1458,6 +1542,24 @@ extern "C" int32_t bsir_matmul(const bsir_matmul_desc *d, void *stream) {
   // the W8A8 form of the epilogue (what the decode kernel serves): f32 scales, no bias, no relu, 16-bit output
   const bool classic = int_in && !d->bias && !d->relu && (od == BSIR_BF16 || od == BSIR_F16) && !d->transpose_a &&
                        (d->descale_mode == BSIR_DESCALE_NULL || (d->descale_mode == BSIR_DESCALE_PER_CHANNEL && d->descale_dtype == BSIR_F32));
+  // a batch of small products: one launch over rank-3 tensor maps (a launch a product leaves the GPU to one product's
+  // few tiles at a time: 8 x [512,1024] x [1024,512] bf16 took 72 us on the device, product after product).  Products
+  // large enough for the CTA-pair kernel, or int8 products of the decode shape, keep their kernels, one launch each.
+  if (d->batch > 1 && d->n_peers == 0 && d->out && std::getenv("BSIR_GEMM_NO_BATCH_LAUNCH") == nullptr) {
+    const bool pair_sized = d->m >= 192 && ceil_div(d->m, static_cast<int64_t>(256)) * ceil_div(d->n, static_cast<int64_t>(256)) >= 56;
+    const bool decode_sized = classic && d->m <= 48;
+    if (!pair_sized && !decode_sized) {
+      p.out = d->out;
+      p.out_bs = d->batch_stride_out;
+      const Operands o{d->a, d->lda, d->transpose_a ? 1 : 0, d->b, d->ldb, d->transpose_b ? 1 : 0};
+      int32_t rc = BSIR_OK;
+      const bool done = in == BSIR_I8 ? run_gemm_batched<KI8>(p, o, d->batch, d->batch_stride_a, d->batch_stride_b, st, &rc)
+                        : in == BSIR_BF16 ? run_gemm_batched<KBF16>(p, o, d->batch, d->batch_stride_a, d->batch_stride_b, st, &rc)
+                                          : run_gemm_batched<KF16>(p, o, d->batch, d->batch_stride_a, d->batch_stride_b, st, &rc);
+      if (done) return rc;
+      p.out_bs = 0;
+    }
+  }
   for (int64_t e = 0; e < d->batch; ++e) {
     p.out = d->n_peers > 0 ? d->peer_out[0] : static_cast<char *>(d->out) + e * d->batch_stride_out * os;
     for (int i = 0; i < d->n_peers; ++i) p.peer[i] = static_cast<char *>(d->peer_out[i]) + e * d->batch_stride_out * os;

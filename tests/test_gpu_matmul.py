@@ -151,6 +151,40 @@ def test_batch_matmul(bsir):
         assert_bits_equal(shared[e], O.matmul(O.BF16, to_bits(a[e]), to_bits(b[0]), O.BF16), f"shared B, entry {e}")
 
 
+@pytest.mark.parametrize("dtype,out_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float16, torch.float32), (torch.int8, torch.float16),
+                                             (torch.int8, torch.int8), (torch.int8, torch.int32)])
+@pytest.mark.parametrize("ta,tb", [(False, False), (True, True)])
+def test_batch_matmul_in_one_launch(bsir, dtype, out_dtype, ta, tb):
+    """A batch of small products runs as one launch over rank-3 tensor maps: ragged m (the last tile of a product must
+    not reach into the next product's rows), every store path of the epilogue, transposed operands, and operands that
+    are views with padded batch strides."""
+    g = torch.Generator(device="cuda").manual_seed(8)
+    batch, m, n, k = 5, 130, 192, 256
+    mk = (lambda *sh: torch.randint(-4, 5, sh, generator=g, device="cuda").to(dtype))
+    a_big = mk(batch + 1, *( (k, m) if ta else (m, k) ))
+    b_big = mk(batch + 2, *( (n, k) if tb else (k, n) ))
+    a, b = a_big[1:], b_big[:batch]                                   # views: the same batch stride, another base
+    int_in = dtype == torch.int8
+    bias = (torch.randint(-50, 50, (n,), generator=g, device="cuda", dtype=torch.int32) if int_in else mk(n))
+    desc = torch.full((1,), 0.01 if int_in else 0.5, device="cuda", dtype=torch.float32 if int_in else dtype)
+    out = bsir.matmul(a, b, transpose_a=ta, transpose_b=tb, bias=bias, descale=desc, descale_mode="DescalePerTensor", relu=True,
+                      out_dtype=out_dtype)
+    for e in range(batch):
+        want = O.matmul(_ODT[dtype], to_bits(a[e].contiguous()), to_bits(b[e].contiguous()), _ODT[out_dtype], transpose_a=ta,
+                        transpose_b=tb, bias=to_bits(bias), bias_dt=_ODT[bias.dtype], descale=to_bits(desc), descale_dt=_ODT[desc.dtype],
+                        descale_mode=2, relu=True)
+        assert_bits_equal(out[e], want, f"{dtype} -> {out_dtype} ta={ta} tb={tb}, product {e}")
+    assert bsir.device_error() == 0
+
+
+def test_batch_matmul_many_products(bsir):
+    g = torch.Generator(device="cuda").manual_seed(9)
+    a = torch.randint(-3, 4, (8, 512, 1024), generator=g, device="cuda").to(torch.bfloat16)
+    b = torch.randint(-3, 4, (8, 1024, 512), generator=g, device="cuda").to(torch.bfloat16)
+    out = bsir.matmul(a, b)
+    assert torch.equal(out.float(), torch.bmm(a.float(), b.float()).to(torch.bfloat16).float())
+
+
 def test_matmul_unaligned_operands_take_the_plain_kernel(bsir):
     a = torch.randint(-4, 5, (37, 101), device="cuda").to(torch.float16)     # row pitch 202 bytes: not a TMA pitch
     b = torch.randint(-4, 5, (101, 45), device="cuda").to(torch.float16)
