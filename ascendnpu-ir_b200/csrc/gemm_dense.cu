@@ -76,6 +76,8 @@ struct GemmParams {
   // tile t belongs to product t / (m_tiles * n_tiles); 0 or 1: one product, rank-2 maps
   int batch;
   int64_t out_bs;                      // elements between the outputs of consecutive products
+  int split_k;                         // 1: the `batch` "products" are the K parts of one product (rank-2 maps; part z covers
+                                       // k blocks [z * k_blocks, (z + 1) * k_blocks) and writes its partial result at z * out_bs)
 #ifdef BSIR_DEC_TIMELINE
   unsigned long long *tl;
 #endif
@@ -413,10 +415,12 @@ __global__ void __launch_bounds__(kThreads + 32, 1)
         const int n0 = (t / p.m_tiles) * BN;
         // one product: rank-2 maps; a batch: rank-3 maps, the product is the third coordinate
         auto load = [&](uint32_t dst, const CUtensorMap *map, int x, int y) {
-          if (batched) tma_load_3d(dst, map, x, y, zb, full_bar(stage));
+          if (batched && !p.split_k) tma_load_3d(dst, map, x, y, zb, full_bar(stage));
           else tma_load_2d(dst, map, x, y, full_bar(stage));
         };
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const int kb0 = p.split_k ? zb * p.k_blocks : 0;           // K split over CTAs: this part's first k block
+        for (int kq = 0; kq < p.k_blocks; ++kq) {
+          const int kb = kb0 + kq;
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.err)) { ok = false; break; }
           const uint32_t sa = base + stage * Cfg::kStage;
           const uint32_t sb = sa + Cfg::kStageA;
@@ -1309,6 +1313,32 @@ struct Operands {
   int transpose_b;
 };
 
+// Second step of a float product whose K was split over CTAs: the `parts` f32 partial products of every element are
+// added in part order (so the result is the same from run to run) and go through the epilogue's arithmetic --
+// bias, per-row scale, descale, relu, conversion -- exactly as epilogue_tile applies it to an accumulator.
+__global__ void __launch_bounds__(256) splitk_finish_kernel(GemmParams p, const float *__restrict__ partials, int parts, int64_t part_stride,
+                                                            int64_t ldp) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t total = p.m * p.n;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t row = i / p.n, col = i - row * p.n;
+    float acc = partials[row * ldp + col];
+    for (int e = 1; e < parts; ++e) acc = __fadd_rn(acc, partials[e * part_stride + row * ldp + col]);
+    const float sa = p.scale_a ? p.scale_a[row] : 1.0f;
+    const float sw = !p.descale ? 1.0f
+                     : p.descale_mode == BSIR_DESCALE_PER_CHANNEL ? load_f32_as(p.descale, p.descale_dtype, col)
+                                                                  : load_f32_as(p.descale, p.descale_dtype, 0);
+    const float bias = p.bias ? load_f32_as(p.bias, p.bias_dtype, col) : 0.0f;
+    const float f = scale_relu(__fadd_rn(acc, bias), sa, sw, p.relu);
+    const int64_t o = row * p.ldo + col;
+    if (p.out_dtype == BSIR_BF16) static_cast<__nv_bfloat16 *>(p.out)[o] = __float2bfloat16_rn(f);
+    else if (p.out_dtype == BSIR_F16) static_cast<__half *>(p.out)[o] = __float2half_rn(fminf(fmaxf(f, -65504.0f), 65504.0f));
+    else if (p.out_dtype == BSIR_I8) static_cast<uint8_t *>(p.out)[o] = static_cast<uint8_t>(sat_i8_bits(f));
+    else static_cast<float *>(p.out)[o] = f;
+  }
+}
+
 // `batch` products of one shape, `bsa` / `bsb` / `p.out_bs` elements apart, in one launch of the single-CTA kernel over
 // rank-3 tensor maps.  false: not possible here (alignment, no encoder, tiles too many for int) -- the caller then
 // launches product by product.
@@ -1360,17 +1390,34 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
     const bool out16 = p.out_dtype == BSIR_BF16 || p.out_dtype == BSIR_F16;
     p.tma_out = (p.out && p.n_peers == 0 && out16 && aligned_to(p.out, 16) && p.ldo % 8 == 0 &&
                  make_out_tmap(&tout, p.out, static_cast<uint64_t>(n), static_cast<uint64_t>(m), static_cast<uint64_t>(p.ldo))) ? 1 : 0;
-    const int bn = pick_bn(m, n, device_info().sm_count > 0 ? device_info().sm_count : 148, b_mn);
+    int bn = pick_bn(m, n, device_info().sm_count > 0 ? device_info().sm_count : 148, b_mn);
+    const char *force = std::getenv("BSIR_W8A8_PATH");
+    // BSIR_W8A8_PATH=1 / 2 forces the single-CTA / CTA-pair kernel (tests use it on small shapes)
+    const bool want_pair = (force && force[0] == '2') ||
+                           (!(force && force[0] == '1') && m >= 192 && ceil_div(m, 256) * ceil_div(n, 256) >= 56);   // measured, k 4096, n 14336: m = 128 19.2 / 14.8 us (pair / single CTA), 192 19.3 / 19.8, 384 27.9 / 31.1, 511 28.3 / 31.4
+    // Float products with too few tiles for the SMs: K is split into `parts` (2, 4 or 8 whole shares of k blocks), every
+    // part a "product" of a batched launch that writes its f32 partial result into scratch, and a second launch adds
+    // the parts in order and applies the epilogue.  A tile of K = 4096 is 64 k blocks of four MMAs from one issuing
+    // thread -- 19 us of MMA issue alone, whatever the tile's width; so the widest tile that leaves the most parts wins.
+    int parts = 1;
+    if constexpr (KIND != KI8) {
+      const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
+      // (measured, bf16, K = N = 4096, device time: m = 1 24.3 -> 20.6 us, 16 24.4 -> 21.2, 128 24.6 -> 24.5, 512 26.8 -> 37.7 --
+      // the partial results of many rows cost more than the split saves, so it is for few rows only)
+      if (m <= 64 && !want_pair && p.n_peers == 0 && p.out && !p.acc_out && !force && (k * es) % kBK == 0 && std::getenv("BSIR_GEMM_NO_SPLITK") == nullptr) {
+        for (int cand = 256; cand >= (b_mn ? 128 : 64); cand >>= 1) {
+          const int64_t tiles = static_cast<int64_t>(p.m_tiles) * ceil_div(n, static_cast<int64_t>(cand));
+          for (int c = 8; c > parts; c >>= 1)
+            if (p.k_blocks % c == 0 && p.k_blocks / c >= 4 && tiles * c <= sms) { parts = c; bn = cand; break; }
+        }
+      }
+    }
     const uint32_t kr = static_cast<uint32_t>(kBK / es);
     // A: [m rows x k bytes] boxes of 128 rows, or (transposed) [k rows x m bytes] boxes of kr rows
     bool ok = a_mn ? make_tmap(&ta, o.a, static_cast<uint64_t>(m) * es, static_cast<uint64_t>(k), static_cast<uint64_t>(o.lda) * es, kr)
                    : make_tmap(&ta, o.a, static_cast<uint64_t>(k) * es, static_cast<uint64_t>(m), static_cast<uint64_t>(o.lda) * es, kBM);
     if (b_mn) ok = ok && make_tmap(&tb, o.b, static_cast<uint64_t>(n) * es, static_cast<uint64_t>(k), static_cast<uint64_t>(o.ldb) * es, kr);
     else ok = ok && make_tmap(&tb, o.b, static_cast<uint64_t>(k) * es, static_cast<uint64_t>(n), static_cast<uint64_t>(o.ldb) * es, bn < 128 ? bn : 128);
-    const char *force = std::getenv("BSIR_W8A8_PATH");
-    // BSIR_W8A8_PATH=1 / 2 forces the single-CTA / CTA-pair kernel (tests use it on small shapes)
-    const bool want_pair = (force && force[0] == '2') ||
-                           (!(force && force[0] == '1') && m >= 192 && ceil_div(m, 256) * ceil_div(n, 256) >= 56);   // measured, k 4096, n 14336: m = 128 19.2 / 14.8 us (pair / single CTA), 192 19.3 / 19.8, 384 27.9 / 31.1, 511 28.3 / 31.4
     if (ok && want_pair) {
       // CTA pairs: A as before; B boxes of 128 columns (MN-major: kr rows of 128 bytes) / 128 rows (K-major)
       CUtensorMap tb2;
@@ -1379,6 +1426,34 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
       if (ok2) {
         if (a_mn) return b_mn ? launch_pair<KIND, true, true>(ta, tb2, tout, p, st) : launch_pair<KIND, true, false>(ta, tb2, tout, p, st);
         return b_mn ? launch_pair<KIND, false, true>(ta, tb2, tout, p, st) : launch_pair<KIND, false, false>(ta, tb2, tout, p, st);
+      }
+    }
+    if constexpr (KIND != KI8) {
+      const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
+      if (!ok) parts = 1;
+      if (parts > 1) {
+        const int64_t ldp = (n + 3) / 4 * 4;                       // f32 rows on 16-byte boundaries
+        const int64_t part_elems = m * ldp;
+        char *ws = static_cast<char *>(device_workspace(kScratchCounterBytes + static_cast<size_t>(parts) * part_elems * 4, st));
+        if (ws) {
+          float *partials = reinterpret_cast<float *>(ws + kScratchCounterBytes);
+          GemmParams q{};
+          q.m = m; q.n = n; q.k = k / parts;
+          q.m_tiles = p.m_tiles; q.k_blocks = p.k_blocks / parts;
+          q.out = partials; q.ldo = ldp; q.out_dtype = BSIR_F32; q.out_bs = part_elems;
+          q.err = p.err;
+          q.batch = parts; q.split_k = 1;
+          int32_t rc;
+          if (a_mn) rc = b_mn ? launch_tc_bn<KIND, true, true>(bn, ta, tb, tout, q, st) : launch_tc_bn<KIND, true, false>(bn, ta, tb, tout, q, st);
+          else rc = b_mn ? launch_tc_bn<KIND, false, true>(bn, ta, tb, tout, q, st) : launch_tc_bn<KIND, false, false>(bn, ta, tb, tout, q, st);
+          if (rc != BSIR_OK) return rc;
+          int64_t blocks = ceil_div(m * n, static_cast<int64_t>(256));
+          if (blocks > sms * 8) blocks = sms * 8;
+          launch_pdl(splitk_finish_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, st, p, static_cast<const float *>(partials), parts,
+                     part_elems, ldp);
+          count_launch();
+          return check_launch("matmul (K split)");
+        }
       }
     }
     if constexpr (KIND == KI8) {

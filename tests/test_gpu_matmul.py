@@ -185,6 +185,21 @@ def test_batch_matmul_many_products(bsir):
     assert torch.equal(out.float(), torch.bmm(a.float(), b.float()).to(torch.bfloat16).float())
 
 
+@pytest.mark.parametrize("dtype,out_dtype", [(torch.bfloat16, torch.bfloat16), (torch.float16, torch.float16), (torch.bfloat16, torch.float32),
+                                             (torch.float16, torch.int8)])
+@pytest.mark.parametrize("ta,tb", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("m,n,k", [(16, 4096, 4096), (1, 1000, 2048), (64, 520, 1024), (33, 4096, 512)])
+def test_float_matmul_with_k_split_over_ctas(bsir, dtype, out_dtype, m, n, k, ta, tb):
+    """Few tiles and a long K: the k blocks are shared out over 2, 4 or 8 CTAs a tile, the partial results added in
+    part order by a second launch that applies bias, scales, relu and the conversion.  Exact on small integers, within
+    tolerance on real data, the same bits on every run."""
+    _check(bsir, dtype, m, n, k, ta, tb, bias=True, descale="channel", relu=True, scale_a=True, out_dtype=out_dtype, seed=m + n + k,
+           small_ints=True, exact=out_dtype != torch.int8, param_dtype=torch.float32)
+    first = _check(bsir, dtype, m, n, k, ta, tb, bias=True, descale="tensor", out_dtype=out_dtype, seed=m + n)
+    again = _check(bsir, dtype, m, n, k, ta, tb, bias=True, descale="tensor", out_dtype=out_dtype, seed=m + n)
+    assert torch.equal(first.view(torch.uint8), again.view(torch.uint8))
+
+
 def test_matmul_unaligned_operands_take_the_plain_kernel(bsir):
     a = torch.randint(-4, 5, (37, 101), device="cuda").to(torch.float16)     # row pitch 202 bytes: not a TMA pitch
     b = torch.randint(-4, 5, (101, 45), device="cuda").to(torch.float16)
