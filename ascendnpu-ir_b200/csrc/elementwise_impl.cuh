@@ -923,6 +923,8 @@ int32_t launch_rows_outer(int kind, int ka, int kb, int fn, int dt, int64_t rows
   if (ka == 0 && kb == 0) R(kOpBinary, 0, 0);
   if (ka == 0 && kb == 1) R(kOpBinary, 0, 1);
   if (ka == 0 && kb == 2) R(kOpBinary, 0, 2);
+  if (ka == 1 && kb == 2) R(kOpBinary, 1, 2);
+  if (ka == 2 && kb == 1) R(kOpBinary, 2, 1);
   if (ka == 1) R(kOpBinary, 1, 0);
   R(kOpBinary, 2, 0);
 #undef R
@@ -1031,7 +1033,8 @@ bool try_rows_route(int kind, int fn, int dtype, const Prepared &p, const Operan
   if (p.os[2] != 1 || !vector_rows(out, out_rs, out_os) || (n1 > 1 && out_rs < cols) || (n0 > 1 && out_os < n1 * out_rs)) return false;
   const View va = classify(a), vb = binary ? classify(b) : View{0, 0, 0};
   const int ka = va.kind, kb = vb.kind;
-  if (ka < 0 || kb < 0 || (ka != 0 && kb != 0)) return false;          // one operand at least is a full tensor
+  if (ka < 0 || kb < 0) return false;
+  if (ka != 0 && kb != 0 && !(ka + kb == 3)) return false;             // two broadcast operands: a row vector against values per row (an outer sum)
   // the outer index matters only to an operand (or a result) whose outer stride is not n1 row strides
   auto collapses = [&](int64_t rs, int64_t os) { return n0 == 1 || os == n1 * rs; };
   const bool outer = !(collapses(out_rs, out_os) && collapses(va.rs, va.os) && (!binary || collapses(vb.rs, vb.os)));
@@ -1051,6 +1054,8 @@ bool try_rows_route(int kind, int fn, int dtype, const Prepared &p, const Operan
   } else if (ka == 0 && kb == 0) *rc = launch_rows<kOpBinary, 0, 0>(fn, dtype, rows, n1k, vpr, oa, ob, out, out_rs, out_os, st);
   else if (ka == 0 && kb == 1) *rc = launch_rows<kOpBinary, 0, 1>(fn, dtype, rows, n1k, vpr, oa, ob, out, out_rs, out_os, st);
   else if (ka == 0 && kb == 2) *rc = launch_rows<kOpBinary, 0, 2>(fn, dtype, rows, n1k, vpr, oa, ob, out, out_rs, out_os, st);
+  else if (ka == 1 && kb == 2) *rc = launch_rows<kOpBinary, 1, 2>(fn, dtype, rows, n1k, vpr, oa, ob, out, out_rs, out_os, st);
+  else if (ka == 2 && kb == 1) *rc = launch_rows<kOpBinary, 2, 1>(fn, dtype, rows, n1k, vpr, oa, ob, out, out_rs, out_os, st);
   else if (ka == 1) *rc = launch_rows<kOpBinary, 1, 0>(fn, dtype, rows, n1k, vpr, oa, ob, out, out_rs, out_os, st);
   else *rc = launch_rows<kOpBinary, 2, 0>(fn, dtype, rows, n1k, vpr, oa, ob, out, out_rs, out_os, st);
   return true;

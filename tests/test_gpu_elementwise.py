@@ -549,6 +549,12 @@ def test_broadcasts_over_three_axes_take_the_vector_kernel(bsir, dtype):
         want = tf(x, other.expand_as(x) if other.shape != x.shape else other)
         assert torch.equal(bsir.elemwise_binary(fn, x, other.expand_as(x)), want), f"{tuple(other.shape)} {other.stride()}"
         assert torch.equal(bsir.elemwise_binary(fn, other.expand_as(x), x), want), f"{tuple(other.shape)} first"
+    rowv, colv = mk(1, 1, 256), mk(6, 40, 1)                    # two broadcast operands: an outer sum
+    want = tf(rowv.expand_as(x), colv.expand_as(x))
+    assert torch.equal(bsir.elemwise_binary(fn, rowv.expand_as(x), colv.expand_as(x)), want)
+    assert torch.equal(bsir.elemwise_binary(fn, colv.expand_as(x), rowv.expand_as(x)), want)
+    r3, c3 = mk(6, 1, 256), mk(1, 40, 1)                        # the same with an outer index on the row vector
+    assert torch.equal(bsir.elemwise_binary(fn, r3.expand_as(x), c3.expand_as(x)), tf(r3.expand_as(x), c3.expand_as(x)))
     wide = mk(240, 512)
     col = wide[:, 5:6]                                          # one value per row, 512 elements apart
     y = mk(240, 256)
