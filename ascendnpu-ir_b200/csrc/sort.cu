@@ -610,6 +610,11 @@ extern "C" int32_t bsir_sort(int32_t dtype, int32_t descending, int64_t rows, in
     return fail(BSIR_ERR_STRIDE, "sort: row stride below the row length");
   const int eb = dtype_bytes(dtype);
   if (!aligned_to(src, eb) || !aligned_to(dst_value, eb) || !aligned_to(dst_index, 4)) return fail(BSIR_ERR_ALIGN, "sort: misaligned");
+  if (dst_value) {   // zeros and NaNs are read back from the source after other values have been written
+    const char *s0 = static_cast<const char *>(src), *s1 = s0 + ((rows - 1) * src_row_stride + cols) * eb;
+    const char *d0 = static_cast<const char *>(dst_value), *d1 = d0 + ((rows - 1) * value_row_stride + cols) * eb;
+    if (s0 < d1 && d0 < s1) return fail(BSIR_ERR_UNSUPPORTED, "sort: the sorted values may not overlap the source");
+  }
   cudaStream_t st = resolve_stream(stream);
   const int desc = descending != 0;
   // Which of the three ways: rows above one tile of the radix sort (4096) keep their keys in device scratch and

@@ -413,7 +413,7 @@ BSIR_API int32_t bsir_deinterleave(int32_t dtype, int32_t channels, int64_t rows
  * bishengir/lib/Dialect/HFusion/Transforms/DecomposeOpInterfaceImpl.cpp:742-838; runner goldens
  * test/Dialect/HFusion/test_sort_2d_asc.mlir:16-19): equal values keep their source order, -0 = +0, and a NaN that
  * starts at position p of its row ends at (p + 1) mod n in either direction, the numbers filling the other places
- * in order.  dst_value or dst_index may be NULL.
+ * in order.  dst_value or dst_index may be NULL; dst_value may not overlap src (BSIR_ERR_UNSUPPORTED).
  * dtype: f32, f16, bf16, i8, i16, i32.  Rows of up to 4096 elements are sorted in shared memory by one CTA; longer
  * rows (up to 2^30 elements) keep two copies of their 8-byte keys and 1 KB of digit counts per 4096 elements in the
  * library's device scratch (about 16.3 bytes an element, at most 1 GiB at a time: more rows are sorted in turns). */

@@ -137,3 +137,11 @@ def test_sort_radix_in_one_cta(bsir, monkeypatch, dtype, rows, cols, descending)
     wv, wi = O.sort_last_axis(oracle_dtype(x), to_bits(x), descending=descending)
     assert np.array_equal(idx.cpu().numpy(), wi)
     assert np.array_equal(to_bits(val).view(np.uint8), wv.view(np.uint8))         # bits: NaN is not equal to itself
+
+
+def test_sort_refuses_to_write_values_over_the_source(bsir):
+    x = torch.randn(4, 100, device="cuda")
+    keep = x.clone()
+    with pytest.raises(bsir.BsirError):
+        bsir.sort(x, out_val=x)
+    assert torch.equal(x, keep)
