@@ -126,6 +126,11 @@ extern "C" int32_t bsir_gather(int32_t dtype, int32_t index_dtype, int64_t outer
   if (src_axis == 0) return fail(BSIR_ERR_SHAPE, "gather: the source axis is empty");
   if (!aligned_to(src, eb) || !aligned_to(dst, eb) || !aligned_to(indices, dtype_bytes(index_dtype))) return fail(BSIR_ERR_ALIGN, "gather: misaligned");
   if (ceil_div(total, 256) > 0x7fffffffLL) return fail(BSIR_ERR_SHAPE, "gather: %lld elements", (long long)total);
+  {   // an element is read where an index sends the read: nothing may have been written there before
+    const char *s0 = static_cast<const char *>(src), *s1 = s0 + outer * src_axis * inner * eb;
+    const char *d0 = static_cast<const char *>(dst), *d1 = d0 + total * eb;
+    if (s0 < d1 && d0 < s1) return fail(BSIR_ERR_UNSUPPORTED, "gather: the destination may not overlap the source");
+  }
   int *err = device_error_word();
   if (!err) return fail(BSIR_ERR_WORKSPACE, "gather: no device error word");
   cudaStream_t st = resolve_stream(stream);

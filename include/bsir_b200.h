@@ -390,7 +390,7 @@ BSIR_API int32_t bsir_cumulative(int32_t kind, int32_t dtype, int32_t axis, int3
  * dst[o][j][k] = src[o][indices[o][j][k]][k]; src is [outer, src_axis, inner], indices and dst are
  * [outer, dst_axis, inner].  index_dtype: BSIR_I16 / I32 (the op's types) or I64.  An index outside
  * [0, src_axis) leaves its element untouched and sets BSIR_DEVERR_GATHER_INDEX in the device error word
- * (bsir_device_error). */
+ * (bsir_device_error).  The destination may not overlap the source (BSIR_ERR_UNSUPPORTED). */
 BSIR_API int32_t bsir_gather(int32_t dtype, int32_t index_dtype, int64_t outer, int64_t src_axis, int64_t dst_axis,
                              int64_t inner, const void *src, const void *indices, void *dst, void *stream);
 
