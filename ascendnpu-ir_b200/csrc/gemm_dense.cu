@@ -622,10 +622,15 @@ __device__ __forceinline__ bool decode_segment(const GemmParams &p, int b, int g
 // the bits do not depend on the order).
 constexpr int kDecIssuers = 4;
 constexpr int kDecThreads = kThreads + 32 * (kDecIssuers - 1);
-template <bool W_MN>
+// KIND = KI8: the W8A8 form (int32 accumulators, f32 scales).  KIND = KBF16 / KF16: hivm.hir.matmul of few rows with
+// f32 accumulators -- each issuer's accumulator is a partial sum over its k steps, the epilogue adds the four in issuer
+// order (the same bits on every run) and applies bias, scales and relu as the tile kernels' epilogue does.
+template <int KIND, bool W_MN>
 __global__ void __launch_bounds__(kDecThreads, 1)
     w8a8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_a, GemmParams p,
                        int nb, int stage_bytes, int nstages) {
+  constexpr int kEs = kEsize<KIND>;
+  constexpr int kKr = kBK / kEs;                    // K rows of an MN-major weight chunk
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -667,8 +672,12 @@ __global__ void __launch_bounds__(kDecThreads, 1)
     const uint32_t sw = base + p_stage * stage_bytes;
     const uint32_t bar = full_bar(p_stage);
     mbar_expect_tx(bar, static_cast<uint32_t>(stage_bytes));
-    if constexpr (W_MN) tma_load_2d(sw, &tmap_w, pseg.tile * kBM, p_kb * kBK, bar);   // [128 k rows x 128 n bytes]
-    else tma_load_2d(sw, &tmap_w, p_kb * kBK, pseg.tile * kBM, bar);                 // [128 n rows x 128 k bytes]
+    if constexpr (W_MN) {                                                             // chunks of [kKr k rows x 128 n bytes]
+#pragma unroll
+      for (int c = 0; c < kBM * kEs / 128; ++c) tma_load_2d(sw + c * (kKr * 128), &tmap_w, pseg.tile * kBM * kEs + c * 128, p_kb * kKr, bar);
+    } else {
+      tma_load_2d(sw, &tmap_w, p_kb * kBK, pseg.tile * kBM, bar);                     // [128 n rows x 128 k bytes]
+    }
     tma_load_2d(sw + kDecStageW, &tmap_a, p_kb * kBK, 0, bar);                       // [nb rows x 128 k bytes]
     if (++p_kb == pseg.kb1) {
       decode_segment(p, cta, grid, ++p_seg, pseg);
@@ -727,7 +736,7 @@ __global__ void __launch_bounds__(kDecThreads, 1)
     if (lane == 0) {
       const int issuer = warp == 1 ? 0 : warp - 5;
       // D = s32, A (weights) and B (activations) signed int8; A's major per the weight layout; N = nb, M = 128
-      const uint32_t idesc = make_idesc<KI8>(W_MN, false, nb, kBM);
+      const uint32_t idesc = make_idesc<KIND>(W_MN, false, nb, kBM);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -745,12 +754,12 @@ __global__ void __launch_bounds__(kDecThreads, 1)
           const uint32_t sw = base + stage * stage_bytes;
           const uint32_t sa = sw + kDecStageW;
           if (nacc > 1) {
-            mma_ss<KI8>(d_tmem, operand_desc<KI8>(sw, issuer, W_MN), operand_desc<KI8>(sa, issuer, false), idesc, kb > g.kb0 ? 1u : 0u);
+            mma_ss<KIND>(d_tmem, operand_desc<KIND>(sw, issuer, W_MN), operand_desc<KIND>(sa, issuer, false), idesc, kb > g.kb0 ? 1u : 0u);
             tc_commit(empty_bar(stage));
           } else if (issuer == 0) {     // one accumulator for all: a single issuer keeps the k steps in order
 #pragma unroll
             for (int kk = 0; kk < kBK / kUmmaK; ++kk)
-              mma_ss<KI8>(d_tmem, operand_desc<KI8>(sw, kk, W_MN), operand_desc<KI8>(sa, kk, false), idesc, (kb > g.kb0 || kk > 0) ? 1u : 0u);
+              mma_ss<KIND>(d_tmem, operand_desc<KIND>(sw, kk, W_MN), operand_desc<KIND>(sa, kk, false), idesc, (kb > g.kb0 || kk > 0) ? 1u : 0u);
             tc_commit(empty_bar(stage));
           } else {
             mbar_arrive(empty_bar(stage));
@@ -782,7 +791,15 @@ __global__ void __launch_bounds__(kDecThreads, 1)
     for (int s = 0; ok && decode_segment(p, cta, grid, s, g); ++s) {
       const int64_t col = static_cast<int64_t>(g.tile) * kBM + quad * 32 + lane;
       const bool col_ok = col < p.n;
-      const float sw = (scale_b && col_ok) ? scale_b[col] : 1.0f;
+      float sw, bias_col = 0.0f;
+      if constexpr (KIND == KI8) {
+        sw = (scale_b && col_ok) ? scale_b[col] : 1.0f;
+      } else {   // descale of any float type per channel or per tensor, bias per channel
+        sw = !p.descale ? 1.0f
+             : p.descale_mode == BSIR_DESCALE_PER_TENSOR ? load_f32_as(p.descale, p.descale_dtype, 0)
+             : col_ok ? load_f32_as(p.descale, p.descale_dtype, col) : 1.0f;
+        bias_col = (p.bias && col_ok) ? load_f32_as(p.bias, p.bias_dtype, col) : 0.0f;
+      }
       const float sa_lane = (p.scale_a && lane < p.m) ? p.scale_a[lane] : 1.0f;   // rows 0..31, one per lane
       if (!mbar_wait(tfull_bar(acc), acc_phase[acc], abort_flag, p.err)) { ok = false; break; }
       if (threadIdx.x == 64) TL(4);
@@ -795,7 +812,10 @@ __global__ void __launch_bounds__(kDecThreads, 1)
           tmem_ld16(t_row + static_cast<uint32_t>(j * nb + c0), q);
           tmem_ld_wait();
 #pragma unroll
-          for (int e = 0; e < 16; ++e) r[e] += q[e];
+          for (int e = 0; e < 16; ++e) {
+            if constexpr (KIND == KI8) r[e] += q[e];
+            else r[e] = __float_as_uint(__fadd_rn(__uint_as_float(r[e]), __uint_as_float(q[e])));   // issuer order: 0, 1, 2, 3
+          }
         }
         tmem_ld_wait();
       };
@@ -848,8 +868,14 @@ __global__ void __launch_bounds__(kDecThreads, 1)
 #pragma unroll
           for (int j = 0; j < 16; ++j) f[j] = (p.scale_a && c0 + j < p.m) ? __ldg(p.scale_a + c0 + j) : 1.0f;
         }
+        if constexpr (KIND == KI8) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) f[j] = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j])), f[j]), sw);
+          for (int j = 0; j < 16; ++j) f[j] = __fmul_rn(__fmul_rn(static_cast<float>(static_cast<int32_t>(r[j])), f[j]), sw);
+        } else {
+          const float floor_v = p.relu ? 0.0f : __int_as_float(0xff800000);   // maximumf(x, -inf) = x, NaN stays NaN
+#pragma unroll
+          for (int j = 0; j < 16; ++j) f[j] = maximumf(__fmul_rn(__fmul_rn(__fadd_rn(__uint_as_float(r[j]), bias_col), f[j]), sw), floor_v);
+        }
         if (p.acc_out && col_ok) {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
@@ -1395,7 +1421,7 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
     // BSIR_W8A8_PATH=1 / 2 forces the single-CTA / CTA-pair kernel (tests use it on small shapes)
     const bool want_pair = (force && force[0] == '2') ||
                            (!(force && force[0] == '1') && m >= 192 && ceil_div(m, 256) * ceil_div(n, 256) >= 56);   // measured, k 4096, n 14336: m = 128 19.2 / 14.8 us (pair / single CTA), 192 19.3 / 19.8, 384 27.9 / 31.1, 511 28.3 / 31.4
-    // Float products with too few tiles for the SMs: K is split into `parts` (2, 4 or 8 whole shares of k blocks), every
+    // Float products with too few tiles for the SMs: K is split into `parts` (4 or 8 whole shares of k blocks), every
     // part a "product" of a batched launch that writes its f32 partial result into scratch, and a second launch adds
     // the parts in order and applies the epilogue.  A tile of K = 4096 is 64 k blocks of four MMAs from one issuing
     // thread -- 19 us of MMA issue alone, whatever the tile's width; so the widest tile that leaves the most parts wins.
@@ -1407,7 +1433,7 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
       if (m <= 64 && !want_pair && p.n_peers == 0 && p.out && !p.acc_out && !force && (k * es) % kBK == 0 && std::getenv("BSIR_GEMM_NO_SPLITK") == nullptr) {
         for (int cand = 256; cand >= (b_mn ? 128 : 64); cand >>= 1) {
           const int64_t tiles = static_cast<int64_t>(p.m_tiles) * ceil_div(n, static_cast<int64_t>(cand));
-          for (int c = 8; c > parts; c >>= 1)
+          for (int c = 8; c > parts && c >= 4; c >>= 1)          // (two parts do not pay for the second launch: n = 14336, m = 64 27 -> 39 us)
             if (p.k_blocks % c == 0 && p.k_blocks / c >= 4 && tiles * c <= sms) { parts = c; bn = cand; break; }
         }
       }
@@ -1431,6 +1457,14 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
     if constexpr (KIND != KI8) {
       const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
       if (!ok) parts = 1;
+      // The decode form below also serves these rows.  Measured (bf16, device time): a k block costs a CTA of the decode
+      // form about 0.26 us and there are k_blocks of them a tile; a K part costs about 0.95 us a k block plus 7 us for the
+      // second launch.  n = 14336, k = 4096: 22 us against 35 us; n = 4096, k = 14336: 58 us against 34 us.
+      if (parts > 1 && !a_mn && m <= 48 && out16 && std::getenv("BSIR_GEMM_NO_FLOAT_DECODE") == nullptr) {
+        const double decode_us = 0.26 * p.k_blocks * static_cast<double>(ceil_div(ceil_div(n, static_cast<int64_t>(kBM)), static_cast<int64_t>(sms)));
+        const double split_us = 0.95 * p.k_blocks / parts + 7.0;
+        if (decode_us <= 1.25 * split_us) parts = 1;
+      }
       if (parts > 1) {
         const int64_t ldp = (n + 3) / 4 * 4;                       // f32 rows on 16-byte boundaries
         const int64_t part_elems = m * ldp;
@@ -1456,17 +1490,19 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
         }
       }
     }
-    if constexpr (KIND == KI8) {
+    {
       // few rows: operands swapped, deep ring of weight tiles (BSIR_W8A8_PATH=3 forces it for m <= 128, =1 avoids it)
       // measured on B200 (k 4096, n 14336), this kernel against the 128-row-tile one: m = 16 12.5 / 19.8 us, 32 13.0 / 14.5,
-      // 48 13.9 / 14.6, 64 14.7 / 14.6, 96 18.0 / 14.8
-      const bool want_decode = classic_w8a8 && !a_mn && ((force && force[0] == '3') ? m <= 128 : (!force && m <= 48));
+      // 48 13.9 / 14.6, 64 14.7 / 14.6, 96 18.0 / 14.8.  Float products take it with 16-bit outputs (its store path).
+      const bool decode_form = KIND == KI8 ? classic_w8a8 : (out16 && !p.acc_out && std::getenv("BSIR_GEMM_NO_FLOAT_DECODE") == nullptr);
+      const bool want_decode = decode_form && !a_mn && ((force && force[0] == '3') ? m <= 128 : (!force && m <= 48));
       if (ok && want_decode) {
         const DecodeCfg dc = decode_cfg(m);
         CUtensorMap tw, tact;
-        bool ok3 = b_mn ? make_tmap(&tw, o.b, static_cast<uint64_t>(n), static_cast<uint64_t>(k), static_cast<uint64_t>(o.ldb), kBK)
-                        : make_tmap(&tw, o.b, static_cast<uint64_t>(k), static_cast<uint64_t>(n), static_cast<uint64_t>(o.ldb), kBM);
-        ok3 = ok3 && make_tmap(&tact, o.a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), static_cast<uint64_t>(o.lda), static_cast<uint32_t>(dc.nb));
+        // weights [k, n] (MN-major): chunks of kr k rows x 128 n bytes; [n, k]: boxes of 128 n rows x 128 k bytes
+        bool ok3 = b_mn ? make_tmap(&tw, o.b, static_cast<uint64_t>(n) * es, static_cast<uint64_t>(k), static_cast<uint64_t>(o.ldb) * es, kr)
+                        : make_tmap(&tw, o.b, static_cast<uint64_t>(k) * es, static_cast<uint64_t>(n), static_cast<uint64_t>(o.ldb) * es, kBM);
+        ok3 = ok3 && make_tmap(&tact, o.a, static_cast<uint64_t>(k) * es, static_cast<uint64_t>(m), static_cast<uint64_t>(o.lda) * es, static_cast<uint32_t>(dc.nb));
         if (ok3) {
           p.n_tiles = static_cast<int>(ceil_div(n, kBM));
           const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
@@ -1484,7 +1520,7 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
           p.dk_vec_out = (p.out || p.n_peers > 0) && n % 8 == 0 && p.ldo % 8 == 0 && (p.n_peers > 0 || aligned_to(p.out, 16));
           for (int d = 0; d < p.n_peers; ++d) p.dk_vec_out = p.dk_vec_out && aligned_to(p.peer[d], 16);
           // 112 CTAs already stream n = 14336 at the HBM rate, so K is split only when a third of the SMs or more would idle
-          if (!(split_env && split_env[0] == '0') && p.n_tiles * 3 <= sms * 2 && p.k_blocks > 1 && static_cast<size_t>(p.n_tiles) * 8 <= kScratchCounterBytes) {
+          if (KIND == KI8 && !(split_env && split_env[0] == '0') && p.n_tiles * 3 <= sms * 2 && p.k_blocks > 1 && static_cast<size_t>(p.n_tiles) * 8 <= kScratchCounterBytes) {   // (int32 parts add exactly; float parts are not split here)
             // at most six parts per tile: the CTA that arrives last reads the others' partial tiles one after the other
             int64_t g2 = items < sms ? items : sms;
             if (g2 > static_cast<int64_t>(p.n_tiles) * 6) g2 = static_cast<int64_t>(p.n_tiles) * 6;
@@ -1514,11 +1550,11 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
             }
           }
           if (b_mn) {
-            cudaFuncSetAttribute(w8a8_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dc.smem));
-            launch_pdl(w8a8_decode_kernel<true>, dim3(grid), dim3(kDecThreads), dc.smem, st, tw, tact, p, dc.nb, dc.stage, dc.stages);
+            cudaFuncSetAttribute(w8a8_decode_kernel<KIND, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dc.smem));
+            launch_pdl(w8a8_decode_kernel<KIND, true>, dim3(grid), dim3(kDecThreads), dc.smem, st, tw, tact, p, dc.nb, dc.stage, dc.stages);
           } else {
-            cudaFuncSetAttribute(w8a8_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dc.smem));
-            launch_pdl(w8a8_decode_kernel<false>, dim3(grid), dim3(kDecThreads), dc.smem, st, tw, tact, p, dc.nb, dc.stage, dc.stages);
+            cudaFuncSetAttribute(w8a8_decode_kernel<KIND, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dc.smem));
+            launch_pdl(w8a8_decode_kernel<KIND, false>, dim3(grid), dim3(kDecThreads), dc.smem, st, tw, tact, p, dc.nb, dc.stage, dc.stages);
           }
           count_launch();
           return check_launch("matmul (decode)");

@@ -200,6 +200,22 @@ def test_float_matmul_with_k_split_over_ctas(bsir, dtype, out_dtype, m, n, k, ta
     assert torch.equal(first.view(torch.uint8), again.view(torch.uint8))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("tb", [False, True])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 14336, 1024), (33, 1000, 640), (48, 264, 2048), (7, 136, 128)])
+def test_float_matmul_of_few_rows_with_swapped_operands(bsir, dtype, tb, m, n, k):
+    """Float products of up to 48 rows and a 16-bit result take the decode kernel's form (weights on the tensor-memory
+    lanes, four issuing threads with an accumulator each, added in issuer order): both weight layouts, ragged n and m,
+    bias + descale + relu + per-row scale; exact on small integers, the same bits on every run, within tolerance on
+    real data."""
+    _check(bsir, dtype, m, n, k, False, tb, bias=True, descale="channel", relu=True, scale_a=True, seed=m + n + k, small_ints=True,
+           exact=True, param_dtype=torch.float32)
+    _check(bsir, dtype, m, n, k, False, tb, descale="tensor", seed=m + n, small_ints=True, exact=True)
+    first = _check(bsir, dtype, m, n, k, False, tb, bias=True, seed=m + k)
+    again = _check(bsir, dtype, m, n, k, False, tb, bias=True, seed=m + k)
+    assert torch.equal(first.view(torch.uint8), again.view(torch.uint8))
+
+
 def test_matmul_unaligned_operands_take_the_plain_kernel(bsir):
     a = torch.randint(-4, 5, (37, 101), device="cuda").to(torch.float16)     # row pitch 202 bytes: not a TMA pitch
     b = torch.randint(-4, 5, (101, 45), device="cuda").to(torch.float16)
