@@ -846,12 +846,27 @@ __global__ void __launch_bounds__(kDecThreads, 1)
         uint32_t r[16];
         load_sum16(c0, r);
         if (parts > 1 && c0 < p.m) {
-          for (int q = 0; q < parts; ++q) {
-            if (q == g.part) continue;
-            const int32_t *theirs = tile_slots + q * slot_words;
+          if constexpr (KIND == KI8) {
+            for (int q = 0; q < parts; ++q) {
+              if (q == g.part) continue;
+              const int32_t *theirs = tile_slots + q * slot_words;
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (c0 + j < p.m) r[j] += static_cast<uint32_t>(__ldcg(theirs + static_cast<size_t>(c0 + j) * kBM + quad * 32 + lane));
+              for (int j = 0; j < 16; ++j)
+                if (c0 + j < p.m) r[j] += static_cast<uint32_t>(__ldcg(theirs + static_cast<size_t>(c0 + j) * kBM + quad * 32 + lane));
+            }
+          } else {
+            // float parts are added in part order whoever arrived last -- this CTA's own part is read back from its
+            // slot like the others -- so the sum is the same from run to run
+            // (parts outside, rows inside: sixteen loads in flight a part, not one)
+            for (int q = 0; q < parts; ++q) {
+              const int32_t *slot = tile_slots + q * slot_words;
+              uint32_t v[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                v[j] = c0 + j < p.m ? static_cast<uint32_t>(__ldcg(slot + static_cast<size_t>(c0 + j) * kBM + quad * 32 + lane)) : 0u;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r[j] = q == 0 ? v[j] : __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(v[j])));
+            }
           }
         }
         // scale and convert; the 16 rows x 32 columns of this warp go through shared memory so that a lane stores
@@ -1457,14 +1472,8 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
     if constexpr (KIND != KI8) {
       const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
       if (!ok) parts = 1;
-      // The decode form below also serves these rows.  Measured (bf16, device time): a k block costs a CTA of the decode
-      // form about 0.26 us and there are k_blocks of them a tile; a K part costs about 0.95 us a k block plus 7 us for the
-      // second launch.  n = 14336, k = 4096: 22 us against 35 us; n = 4096, k = 14336: 58 us against 34 us.
-      if (parts > 1 && !a_mn && m <= 48 && out16 && std::getenv("BSIR_GEMM_NO_FLOAT_DECODE") == nullptr) {
-        const double decode_us = 0.26 * p.k_blocks * static_cast<double>(ceil_div(ceil_div(n, static_cast<int64_t>(kBM)), static_cast<int64_t>(sms)));
-        const double split_us = 0.95 * p.k_blocks / parts + 7.0;
-        if (decode_us <= 1.25 * split_us) parts = 1;
-      }
+      // up to 48 rows with a 16-bit result take the decode form below, which shares a tile's k blocks out itself
+      if (parts > 1 && !a_mn && m <= 48 && out16 && std::getenv("BSIR_GEMM_NO_FLOAT_DECODE") == nullptr) parts = 1;
       if (parts > 1) {
         const int64_t ldp = (n + 3) / 4 * 4;                       // f32 rows on 16-byte boundaries
         const int64_t part_elems = m * ldp;
@@ -1520,7 +1529,7 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
           p.dk_vec_out = (p.out || p.n_peers > 0) && n % 8 == 0 && p.ldo % 8 == 0 && (p.n_peers > 0 || aligned_to(p.out, 16));
           for (int d = 0; d < p.n_peers; ++d) p.dk_vec_out = p.dk_vec_out && aligned_to(p.peer[d], 16);
           // 112 CTAs already stream n = 14336 at the HBM rate, so K is split only when a third of the SMs or more would idle
-          if (KIND == KI8 && !(split_env && split_env[0] == '0') && p.n_tiles * 3 <= sms * 2 && p.k_blocks > 1 && static_cast<size_t>(p.n_tiles) * 8 <= kScratchCounterBytes) {   // (int32 parts add exactly; float parts are not split here)
+          if (!(split_env && split_env[0] == '0') && p.n_tiles * 3 <= sms * 2 && p.k_blocks > 1 && static_cast<size_t>(p.n_tiles) * 8 <= kScratchCounterBytes) {
             // at most six parts per tile: the CTA that arrives last reads the others' partial tiles one after the other
             int64_t g2 = items < sms ? items : sms;
             if (g2 > static_cast<int64_t>(p.n_tiles) * 6) g2 = static_cast<int64_t>(p.n_tiles) * 6;

@@ -202,7 +202,8 @@ def test_float_matmul_with_k_split_over_ctas(bsir, dtype, out_dtype, m, n, k, ta
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("tb", [False, True])
-@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 14336, 1024), (33, 1000, 640), (48, 264, 2048), (7, 136, 128)])
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 4096), (16, 14336, 1024), (33, 1000, 640), (48, 264, 2048), (7, 136, 128), (24, 7168, 4096),
+                                   (3, 640, 64 * 37), (16, 128 * 147, 256)])
 def test_float_matmul_of_few_rows_with_swapped_operands(bsir, dtype, tb, m, n, k):
     """Float products of up to 48 rows and a 16-bit result take the decode kernel's form (weights on the tensor-memory
     lanes, four issuing threads with an accumulator each, added in issuer order): both weight layouts, ragged n and m,
