@@ -476,6 +476,22 @@ def other_ops(torch, bsir, W, hbm_peak, tensor_peak, iters, only=None):
             del aa, bb, oo
         except Exception as e:
             res[nm] = {"error": str(e)[:200]}
+    # hivm.hir.matmul bf16 of few rows against [14336, 4096] weights (the decode kernel's form: bound by the 117 MB of weights)
+    for m in (1, 16):
+        if not want(f"gemm_bf16_m{m}_n14336_k4096"):
+            continue
+        try:
+            g = torch.Generator(device="cuda").manual_seed(2)
+            ww = [(torch.randn(14336, 4096, generator=g, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(2)]   # 2 x 117 MB > L2
+            aa = torch.randn(m, 4096, generator=g, device="cuda").to(torch.bfloat16)
+            oo = torch.empty(m, 14336, dtype=torch.bfloat16, device="cuda")
+            rec(f"gemm_bf16_m{m}_n14336_k4096", 14336 * 4096 * 2 + m * 4096 * 2 + m * 14336 * 2,
+                lambda i: bsir.matmul(aa, ww[i % 2], transpose_b=True, out=oo), flops=2 * m * 4096 * 14336)
+            if f"gemm_bf16_m{m}_n14336_k4096" in res:
+                res[f"gemm_bf16_m{m}_n14336_k4096"].pop("frac_int8_peak_2x_bf16", None)
+            del ww, aa, oo
+        except Exception as e:
+            res[f"gemm_bf16_m{m}_n14336_k4096"] = {"error": str(e)[:200]}
     for m in (1, 8, 16):
         if not want(f"w4a16_m{m}"):
             continue
