@@ -1444,8 +1444,9 @@ int32_t run_gemm(GemmParams p, const Operands &o, bool classic_w8a8, cudaStream_
     if constexpr (KIND != KI8) {
       const int sms = device_info().sm_count > 0 ? device_info().sm_count : 148;
       // (measured, bf16, K = N = 4096, device time: m = 1 24.3 -> 20.6 us, 16 24.4 -> 21.2, 128 24.6 -> 24.5, 512 26.8 -> 37.7 --
-      // the partial results of many rows cost more than the split saves, so it is for few rows only)
-      if (m <= 64 && !want_pair && p.n_peers == 0 && p.out && !p.acc_out && !force && (k * es) % kBK == 0 && std::getenv("BSIR_GEMM_NO_SPLITK") == nullptr) {
+      // the partial results of many rows cost more than the split saves, so it is for few rows only; up to 128 rows when K is
+      // very long: n = 4096, k = 14336, m = 128 72.9 -> 41.2 us)
+      if ((m <= 64 || (m <= 128 && p.k_blocks >= 128)) && !want_pair && p.n_peers == 0 && p.out && !p.acc_out && !force && (k * es) % kBK == 0 && std::getenv("BSIR_GEMM_NO_SPLITK") == nullptr) {
         for (int cand = 256; cand >= (b_mn ? 128 : 64); cand >>= 1) {
           const int64_t tiles = static_cast<int64_t>(p.m_tiles) * ceil_div(n, static_cast<int64_t>(cand));
           for (int c = 8; c > parts && c >= 4; c >>= 1)          // (two parts do not pay for the second launch: n = 14336, m = 64 27 -> 39 us)
