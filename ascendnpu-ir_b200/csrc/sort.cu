@@ -144,7 +144,7 @@ constexpr int kRadixThreads = 256;
 constexpr int kRadixWarps = kRadixThreads / 32;
 constexpr int kRadixIters = kRadixTile / kRadixThreads;       // keys per thread
 
-// The bits the passes sort on, in the upper half of the key.  32-bit elements use all of sort_order(); narrower
+// The bits the passes sort on, in the upper half of the key.  32-bit elements use all 32 bits of their order; narrower
 // ones put their 16 (8) ordered bits at the top, so the digits below hold nothing that could differ between two
 // elements whose upper digits agree.  A NaN is 0xffffffff in both directions and no number maps there.
 template <int DT>
