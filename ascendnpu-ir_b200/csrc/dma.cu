@@ -12,6 +12,10 @@
 // ConvertHIVMToUpstream.cpp:1715).  With add / max / min (the kinds the op allows, HIVMDMAOps.td:176) and the
 // bitwise and unsigned kinds of the enum (HIVMAttrs.td:792-803) the destination is combined with the
 // source by device-wide atomics, so stores of several streams or GPUs' kernels into one buffer add up.
+//
+// Row views with unit element stride and 16-byte aligned destination rows move as 16-byte vectors (a padded load
+// builds each destination vector from the data, the padding, or both; an adding store of f32 / f16 / bf16 is one
+// vector reduction per 16 bytes); everything else takes an element per thread.
 #include <cstdint>
 #include <cstring>
 #include <type_traits>
